@@ -1,0 +1,528 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a.
+//
+//   D[M,N] = sum_s  A_s[M,K_s] * B_s[N,K_s]^T      (s = 0, or 0..1 "dual source")
+//
+// * operands are staged by TMA into 128-byte-swizzled shared memory tiles,
+// * one elected thread issues tcgen05.mma (128 x 256 x 16, bf16 -> fp32),
+// * the fp32 accumulator lives in tensor memory (two 256-column buffers so the
+//   epilogue of tile i overlaps the main loop of tile i+1),
+// * four epilogue warps read the accumulator back with tcgen05.ld.
+//
+// Either operand may be K-major (the reduction index is contiguous in global
+// memory: x[M,K], W[N,K] of a Linear forward) or MN-major (the output index is
+// contiguous: the same W[N,K] read as the B operand of dX = dY * W, or dY / X
+// read as operands of dW = dY^T * X), so forward, input-gradient and
+// weight-gradient GEMMs all run without a transposed copy.
+//
+// Epilogues (template parameter):
+//   EPI_STORE      D -> bf16 (or fp32), optional "+= C" residual / accumulate
+//   EPI_ROWSTATS   D -> bf16 logits, plus per (row, n-tile) softmax partials
+//                  (max, sum exp) in fp32: the vocabulary-head forward
+//   EPI_SWIGLU     B holds gate/up rows interleaved in blocks of 128 output
+//                  columns per half; D -> silu(gate) * up in bf16
+//
+// All waits are bounded (common.cuh); a timeout is reported in status[0].
+#include "common.cuh"
+
+#include <stdio.h>
+
+namespace ab {
+
+static constexpr int BM = 128;
+static constexpr int BN = 256;
+static constexpr int BK = 64;          // 64 bf16 = one 128-byte swizzle row
+static constexpr int UMMA_K = 16;
+static constexpr int kStages = 4;
+static constexpr int kAccBufs = 2;
+static constexpr int kTmemCols = 512;  // 2 x 256 fp32 columns
+static constexpr int kThreads = 192;   // warp0 TMA, warp1 MMA, warps 2..5 epilogue
+static constexpr int kATileBytes = BM * BK * 2;
+static constexpr int kBTileBytes = BN * BK * 2;
+static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+
+enum { EPI_STORE = 0, EPI_ROWSTATS = 1, EPI_SWIGLU = 2 };
+
+struct GemmParams {
+  int M, N;
+  int k_blocks0;        // K_0 / 64 (rounded up)
+  int k_blocks1;        // K_1 / 64 (0 when single source)
+  int m_tiles, n_tiles;
+  // output
+  void* D;              // bf16 or fp32, row-major, leading dimension ldd
+  long long ldd;
+  int d_is_fp32;
+  const void* C;        // optional addend with the layout and type of D
+  float alpha;          // D = alpha * acc (+ C)
+  // EPI_ROWSTATS: partial softmax statistics [n_tiles, M, 2] fp32
+  float* stats;
+  float logit_scale;    // logits = acc * logit_scale (applied before stats/store)
+  int* status;
+};
+
+struct alignas(64) GemmMaps {
+  CUtensorMap a0, b0, a1, b1;
+};
+
+// Tile order: n-tile major, m-tile minor.  A wave of CTAs shares a handful of
+// B (weight) tiles while A (activations, small) stays in L2, so the weight
+// matrix is streamed from HBM once.
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int& mt, int& nt) {
+  nt = tile / m_tiles;
+  mt = tile - nt * m_tiles;
+}
+
+template <int A_MN, int B_MN, int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atom (8 rows x 128 B).
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* full_bar = bars;                       // [kStages]
+  uint64_t* empty_bar = bars + kStages;            // [kStages]
+  uint64_t* acc_full = bars + 2 * kStages;         // [kAccBufs]
+  uint64_t* acc_empty = bars + 2 * kStages + kAccBufs;  // [kAccBufs]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccBufs);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int k_blocks = p.k_blocks0 + p.k_blocks1;
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < kAccBufs; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrive per epilogue warp
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&maps.a0);
+    tma_prefetch_desc(&maps.b0);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer ---------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        int mt, nt;
+        tile_coords(tile, p.m_tiles, mt, nt);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word)) { alive = false; break; }
+          const bool second = kb >= p.k_blocks0;
+          const CUtensorMap* ma = second ? &maps.a1 : &maps.a0;
+          const CUtensorMap* mb = second ? &maps.b1 : &maps.b0;
+          const int k0 = (second ? kb - p.k_blocks0 : kb) * BK;
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kATileBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+          if (A_MN) {
+            // global A^T is [K, M] row-major: box = 64 (m) x 64 (k rows)
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * (BK * 128), ma, &full_bar[stage], mt * BM + j * 64, k0);
+          } else {
+            tma_load_2d(sa, ma, &full_bar[stage], k0, mt * BM);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (BK * 128), mb, &full_bar[stage], nt * BN + j * 64, k0);
+          } else {
+            tma_load_2d(sb, mb, &full_bar[stage], k0, nt * BN);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer -----------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_word)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_word)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kATileBytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: advance 16 elements = 32 B inside the swizzle row.
+            // MN-major: advance 16 k-rows of 128 B = 2048 B.
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sb + k * 32, 16, 1024);
+            tc_mma_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);  // frees the smem stage when the MMAs retire
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (alive) tc_commit(&acc_full[acc]);
+        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------ epilogue warps -------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      int mt, nt;
+      tile_coords(tile, p.m_tiles, mt, nt);
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_word)) break;
+      tc_fence_after();
+      const int row = mt * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                             static_cast<uint32_t>(acc * BN);
+      const int col0 = nt * BN;
+
+      if (EPI == EPI_ROWSTATS) {
+        // Online softmax partials over this tile's 256 columns + bf16 logits.
+        float run_max = -INFINITY, run_sum = 0.f;
+        const float sc = p.logit_scale;
+        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c, r);
+          tmem_ld_wait();
+          float v[32];
+          float cmax = -INFINITY;
+          const int ncol = p.N - (col0 + c);  // valid columns in this chunk
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            // Statistics are taken on the bf16-rounded value that is stored, so
+            // that the loss kernel sees exactly the distribution normalised here.
+            float x = __bfloat162float(__float2bfloat16(__uint_as_float(r[i]) * sc));
+            v[i] = (i < ncol) ? x : -INFINITY;
+            cmax = fmaxf(cmax, v[i]);
+          }
+          const float new_max = fmaxf(run_max, cmax);
+          if (new_max > -INFINITY) {
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) s += fast_exp2((v[i] - new_max) * 1.4426950408889634f);
+            run_sum = run_sum * fast_exp2((run_max - new_max) * 1.4426950408889634f) + s;
+            run_max = new_max;
+          }
+          if (row_ok && ncol > 0) {
+            if (ncol >= 32 && (p.ldd & 7) == 0) {
+              uint4* dst = reinterpret_cast<uint4*>(drow + col0 + c);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 o;
+                o.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+                o.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+                o.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+                o.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+                dst[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && i < ncol; ++i) drow[col0 + c + i] = __float2bfloat16(v[i]);
+            }
+          }
+        }
+        if (row_ok) {
+          float2* st = reinterpret_cast<float2*>(p.stats) + ((long long)nt * p.M + row);
+          *st = make_float2(run_max, run_sum);
+        }
+      } else if (EPI == EPI_SWIGLU) {
+        // Columns [0,128) of the tile are gate, [128,256) the matching up rows.
+        __nv_bfloat16* drow =
+            reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + nt * (BN / 2);
+        const int n_half = p.N / 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 2; c += 32) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_row + c, g);
+          tmem_ld_32x32(t_row + BN / 2 + c, u);
+          tmem_ld_wait();
+          const int ncol = n_half - (nt * (BN / 2) + c);
+          if (row_ok && ncol > 0) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float gf = __uint_as_float(g[i]);
+              const float uf = __uint_as_float(u[i]);
+              v[i] = gf / (1.f + __expf(-gf)) * uf;
+            }
+            if (ncol >= 32 && (p.ldd & 7) == 0) {
+              uint4* dst = reinterpret_cast<uint4*>(drow + c);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 o;
+                o.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+                o.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+                o.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+                o.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+                dst[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && i < ncol; ++i) drow[c + i] = __float2bfloat16(v[i]);
+            }
+          }
+        }
+      } else {
+        const float alpha = p.alpha;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c, r);
+          tmem_ld_wait();
+          const int ncol = p.N - (col0 + c);
+          if (row_ok && ncol > 0) {
+            if (p.d_is_fp32) {
+              float* drow = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0 + c;
+              const float* crow =
+                  p.C ? reinterpret_cast<const float*>(p.C) + (long long)row * p.ldd + col0 + c
+                      : nullptr;
+              if (ncol >= 32 && (p.ldd & 3) == 0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  float4 o = make_float4(__uint_as_float(r[4 * i]) * alpha,
+                                         __uint_as_float(r[4 * i + 1]) * alpha,
+                                         __uint_as_float(r[4 * i + 2]) * alpha,
+                                         __uint_as_float(r[4 * i + 3]) * alpha);
+                  if (crow) {
+                    const float4 cc = reinterpret_cast<const float4*>(crow)[i];
+                    o.x += cc.x; o.y += cc.y; o.z += cc.z; o.w += cc.w;
+                  }
+                  reinterpret_cast<float4*>(drow)[i] = o;
+                }
+              } else {
+                for (int i = 0; i < 32 && i < ncol; ++i)
+                  drow[i] = __uint_as_float(r[i]) * alpha + (crow ? crow[i] : 0.f);
+              }
+            } else {
+              __nv_bfloat16* drow =
+                  reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col0 + c;
+              const __nv_bfloat16* crow =
+                  p.C ? reinterpret_cast<const __nv_bfloat16*>(p.C) + (long long)row * p.ldd +
+                            col0 + c
+                      : nullptr;
+              if (ncol >= 32 && (p.ldd & 7) == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float v[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * i + j]) * alpha;
+                  if (crow) {
+                    const uint4 cc = reinterpret_cast<const uint4*>(crow)[i];
+                    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&cc);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      const float2 f = __bfloat1622float2(c2[j]);
+                      v[2 * j] += f.x;
+                      v[2 * j + 1] += f.y;
+                    }
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(v[0], v[1]);
+                  o.y = pack_bf16x2(v[2], v[3]);
+                  o.z = pack_bf16x2(v[4], v[5]);
+                  o.w = pack_bf16x2(v[6], v[7]);
+                  reinterpret_cast<uint4*>(drow)[i] = o;
+                }
+              } else {
+                for (int i = 0; i < 32 && i < ncol; ++i) {
+                  float v = __uint_as_float(r[i]) * alpha;
+                  if (crow) v += __bfloat162float(crow[i]);
+                  drow[i] = __float2bfloat16(v);
+                }
+              }
+            }
+          }
+        }
+      }
+      // Accumulator buffer drained: hand it back to the MMA warp.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---------------------------------------------------------- teardown -----
+  if (*abort_word) {
+    // A wait ran out.  Give copies already issued time to land before the CTA
+    // (and its shared memory) goes away, then report.
+    __nanosleep(200000);
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, kStatusWaitTimeout);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) !=
+            cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 row-major matrix [rows, cols] with leading dimension ld (elements);
+// box = box_cols x box_rows, 128-byte swizzle.
+static int make_map_bf16(CUtensorMap* map, const void* base, long long rows, long long cols,
+                         long long ld, int box_cols, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_num_sms;
+}
+
+template <int A_MN, int B_MN, int EPI>
+static int launch(const GemmMaps& maps, const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+        cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  int grid = p.m_tiles * p.n_tiles;
+  int cap = max_ctas > 0 ? max_ctas : num_sms();
+  if (grid > cap) grid = cap;
+  if (grid <= 0) return 0;
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(maps, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace ab
+
+// Operand description passed from Python: a bf16 matrix as stored in memory.
+//   mn_major = 0: stored [MN, K] (reduction index contiguous)
+//   mn_major = 1: stored [K, MN] (output index contiguous)
+struct AbOperand {
+  const void* ptr;
+  long long ld;   // leading dimension in elements
+  int mn_major;
+};
+
+extern "C" {
+
+// D[M,N] = alpha * (A0*B0^T + A1*B1^T) (+ C).  Returns 0 on a successful launch.
+//   epi: 0 store, 1 row statistics (vocabulary head), 2 SwiGLU (N = 2 * out)
+//   k1 = 0 disables the second source.  K extents must be multiples of 8.
+int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOperand* b0,
+                 const AbOperand* a1, const AbOperand* b1, void* D, long long ldd, int d_is_fp32,
+                 const void* C, float alpha, int epi, float* stats, float logit_scale, int* status,
+                 int max_ctas, void* stream) {
+  using namespace ab;
+  if (M <= 0 || N <= 0 || K0 <= 0 || (K0 & 7) || (K1 & 7)) return -10;
+  if (K1 > 0 && (a1->mn_major != a0->mn_major || b1->mn_major != b0->mn_major)) return -11;
+  GemmMaps maps;
+  auto mk = [&](CUtensorMap* m, const AbOperand* o, int mn_extent, int k_extent, int tile_mn) {
+    if ((reinterpret_cast<uintptr_t>(o->ptr) & 15) || (o->ld & 7)) return -12;
+    if (o->mn_major)  // memory is [K, MN]: box 64 (mn) x 64 (k)
+      return make_map_bf16(m, o->ptr, k_extent, mn_extent, o->ld, 64, BK);
+    return make_map_bf16(m, o->ptr, mn_extent, k_extent, o->ld, BK, tile_mn);
+  };
+  int rc;
+  if ((rc = mk(&maps.a0, a0, M, K0, BM))) return rc;
+  if ((rc = mk(&maps.b0, b0, N, K0, BN))) return rc;
+  if (K1 > 0) {
+    if ((rc = mk(&maps.a1, a1, M, K1, BM))) return rc;
+    if ((rc = mk(&maps.b1, b1, N, K1, BN))) return rc;
+  } else {
+    maps.a1 = maps.a0;
+    maps.b1 = maps.b0;
+  }
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.k_blocks0 = (K0 + BK - 1) / BK;
+  p.k_blocks1 = K1 > 0 ? (K1 + BK - 1) / BK : 0;
+  p.m_tiles = (M + BM - 1) / BM;
+  p.n_tiles = (N + BN - 1) / BN;
+  p.D = D;
+  p.ldd = ldd;
+  p.d_is_fp32 = d_is_fp32;
+  p.C = C;
+  p.alpha = alpha;
+  p.stats = stats;
+  p.logit_scale = logit_scale;
+  p.status = status;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int amn = a0->mn_major, bmn = b0->mn_major;
+#define AB_DISPATCH(EPI)                                                         \
+  if (!amn && !bmn) return launch<0, 0, EPI>(maps, p, max_ctas, s);              \
+  if (!amn && bmn) return launch<0, 1, EPI>(maps, p, max_ctas, s);               \
+  if (amn && !bmn) return launch<1, 0, EPI>(maps, p, max_ctas, s);               \
+  return launch<1, 1, EPI>(maps, p, max_ctas, s);
+  if (epi == EPI_STORE) { AB_DISPATCH(EPI_STORE) }
+  if (epi == EPI_ROWSTATS) {
+    if (amn || bmn || d_is_fp32) return -13;
+    return launch<0, 0, EPI_ROWSTATS>(maps, p, max_ctas, s);
+  }
+  if (epi == EPI_SWIGLU) {
+    if (amn || bmn || d_is_fp32 || (N & 1)) return -13;
+    return launch<0, 0, EPI_SWIGLU>(maps, p, max_ctas, s);
+  }
+#undef AB_DISPATCH
+  return -14;
+}
+
+int ab_gemm_tile_n() { return ab::BN; }
+
+}  // extern "C"

@@ -1,0 +1,100 @@
+"""bf16 GEMM on the tcgen05 tensor cores (``csrc/gemm_sm100.cu``).
+
+``gemm(a, b)`` computes ``a @ b.T`` for bf16 CUDA tensors.  Either operand can be
+given "as stored the other way round" (``a_t=True`` means the tensor passed is
+``a.T`` in memory, i.e. ``[K, M]``), which maps to the MN-major shared-memory
+descriptors of the kernel - no transposed copy is ever made.  The three GEMMs of
+a Linear layer therefore are::
+
+    y  = gemm(x, w)                       # [M,K] x [N,K]^T
+    dx = gemm(dy, w, b_t=True)            # [M,N] x ([N,K] read as B^T stored)
+    dw = gemm(dy, x, a_t=True, b_t=True)  # dy^T x  -> [N,K]
+
+The reference routes all of these through cuBLAS via ``nn.Linear``
+(aspec/models/draft/dflash.py:432-507, 968-981).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from aspec_b200 import _native
+
+EPI_STORE, EPI_ROWSTATS, EPI_SWIGLU = 0, 1, 2
+TILE_N = 256
+
+
+class _Operand(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("ld", ctypes.c_longlong), ("mn_major", ctypes.c_int)]
+
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word that kernels set when a bounded wait ran out."""
+    key = torch.device(device).index or 0
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_status(device) -> None:
+    """Raise if any kernel launched so far reported a timeout (synchronises)."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise RuntimeError(f"aspec_b200 kernel reported status {code} (1 = wait timeout)")
+
+
+def _operand(t: torch.Tensor, transposed: bool) -> _Operand:
+    if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError("GEMM operands must be 2-D bf16 with unit inner stride")
+    return _Operand(t.data_ptr(), t.stride(0), 1 if transposed else 0)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = False,
+         a2: Optional[torch.Tensor] = None, b2: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+         addend: Optional[torch.Tensor] = None, alpha: float = 1.0,
+         epilogue: int = EPI_STORE, stats: Optional[torch.Tensor] = None,
+         logit_scale: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
+    """``alpha * (A @ B^T [+ A2 @ B2^T]) [+ addend]`` with a fused epilogue."""
+    M = a.shape[1] if a_t else a.shape[0]
+    K = a.shape[0] if a_t else a.shape[1]
+    N = b.shape[1] if b_t else b.shape[0]
+    Kb = b.shape[0] if b_t else b.shape[1]
+    if K != Kb:
+        raise ValueError(f"reduction extents differ: {K} vs {Kb}")
+    K2 = 0
+    if a2 is not None:
+        K2 = a2.shape[0] if a_t else a2.shape[1]
+    n_out = N // 2 if epilogue == EPI_SWIGLU else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
+    if out.stride(1) != 1:
+        raise ValueError("output must have unit inner stride")
+    if addend is not None and (addend.dtype != out.dtype or addend.stride() != out.stride()):
+        raise ValueError("addend must match the output's dtype and strides")
+    lib = _native.kernels()
+    oa, ob = _operand(a, a_t), _operand(b, b_t)
+    oa2 = _operand(a2, a_t) if a2 is not None else oa
+    ob2 = _operand(b2, b_t) if b2 is not None else ob
+    st = status_word(a.device)
+    rc = lib.ab_gemm_bf16(
+        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(K2),
+        ctypes.byref(oa), ctypes.byref(ob), ctypes.byref(oa2), ctypes.byref(ob2),
+        ctypes.c_void_p(out.data_ptr()), ctypes.c_longlong(out.stride(0)),
+        ctypes.c_int(1 if out.dtype == torch.float32 else 0),
+        ctypes.c_void_p(addend.data_ptr() if addend is not None else 0),
+        ctypes.c_float(alpha), ctypes.c_int(epilogue),
+        ctypes.c_void_p(stats.data_ptr() if stats is not None else 0),
+        ctypes.c_float(logit_scale), ctypes.c_void_p(st.data_ptr()),
+        ctypes.c_int(max_ctas),
+        ctypes.c_void_p(torch.cuda.current_stream(a.device).cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"ab_gemm_bf16 refused the launch (code {rc}) for M={M} N={N} K={K}")
+    return out
