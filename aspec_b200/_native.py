@@ -37,7 +37,6 @@ _runtime = None
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "--use_fast_math",
     "-Xcompiler", "-fPIC",
 ]
 

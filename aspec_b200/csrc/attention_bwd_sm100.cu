@@ -1,0 +1,609 @@
+// Interval-masked flash attention backward for sm_100a (tcgen05 + TMEM + TMA).
+//
+// Three kernels:
+//   attn_bwd_prep   delta[h, i] = sum_d O[i,h,d] dO[i,h,d], and per query tile the
+//                   key ranges it can see (used by the dK/dV kernel to skip tiles)
+//   attn_bwd_dq     one CTA per query tile (rows = positions x heads-in-group):
+//                   S = Q K^T, dP = dO V^T, dS = P o (dP - delta) * scale, dQ += dS K
+//   attn_bwd_dkv    one CTA per key tile of one key/value head; it walks the
+//                   query tiles that see it:  S^T = K Q^T, dP^T = V dO^T,
+//                   dV += P^T dO, dK += dS^T Q.  Because the G query heads of the
+//                   group are folded into the row dimension, their contributions
+//                   are summed on chip and dK / dV are written once, in bf16.
+//
+// P / dS are handed to the second MMA through tensor memory (bf16 pairs); in
+// the dK/dV kernel they alias the S^T / dP^T columns they were computed from.
+// Shared-memory tiles are used under two descriptor views: [rows, 64] K-major
+// when the tile is the left/right operand of a d-reduction, and MN-major when
+// the same bytes are the right operand of a row-reduction.
+#include "common.cuh"
+
+namespace ab {
+namespace attn {
+
+int make_map_rows_heads(CUtensorMap* map, const void* base, long long rows, int heads, long long ld,
+                        int box_heads, int box_rows);
+
+static constexpr int BM = 128;
+static constexpr int BN = 128;
+static constexpr int HD = 128;
+static constexpr int kThreads = 192;
+static constexpr int kTile = 128 * HD * 2;   // 32 KB: one 128 x 128 bf16 tile (two swizzled chunks)
+static constexpr int kChunk = 128 * 128;     // bytes per 64-column chunk
+static constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdParams {
+  const int* intervals;       // [Qtot, 4]
+  const float* lse;           // [Hq, Qtot] natural log
+  const float* delta;         // [Hq, Qtot]
+  const int* tile_ranges;     // [n_qtiles, 4]  (c_lo, c_hi, b_lo, b_hi) in key index units
+  __nv_bfloat16* dq;          // [Qtot, Hq, HD]
+  __nv_bfloat16* dk;          // [Tk, Hkv, HD]
+  __nv_bfloat16* dv;          // [Tk, Hkv, HD]
+  int q_total, hq, hkv, group, tk, n_qtiles;
+  float scale, scale_log2;
+  int* status;
+};
+struct alignas(64) BwdMaps {
+  CUtensorMap q, k, v, dout;
+};
+
+// ------------------------------------------------------------------ prep ----
+// grid = ceil(Qtot / 8) x ...: one warp per (position, head): delta.  Block 0.. also ranges.
+__global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ out,
+                                     const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
+                                     const int* __restrict__ intervals, int* __restrict__ tile_ranges,
+                                     int q_total, int hq, int pm, int n_qtiles) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nw = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long r = w; r < (long long)q_total * hq; r += nw) {
+    const uint2 a = reinterpret_cast<const uint2*>(out + r * HD)[lane];
+    const uint2 b = reinterpret_cast<const uint2*>(dout + r * HD)[lane];
+    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(b2[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+      const long long pos = r / hq;
+      const int h = (int)(r - pos * hq);
+      delta[(size_t)h * q_total + pos] = s;
+    }
+  }
+  // tile ranges: warp w handles query tile w
+  for (long long t = w; t < n_qtiles; t += nw) {
+    int c_lo = 0x7fffffff, c_hi = 0, b_lo = 0x7fffffff, b_hi = 0;
+    for (int i = lane; i < pm; i += 32) {
+      const long long pos = t * pm + i;
+      if (pos < q_total) {
+        const int4 iv = reinterpret_cast<const int4*>(intervals)[pos];
+        if (iv.y > iv.x) { c_lo = min(c_lo, iv.x); c_hi = max(c_hi, iv.y); }
+        if (iv.w > iv.z) { b_lo = min(b_lo, iv.z); b_hi = max(b_hi, iv.w); }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      c_lo = min(c_lo, __shfl_xor_sync(0xffffffffu, c_lo, o));
+      c_hi = max(c_hi, __shfl_xor_sync(0xffffffffu, c_hi, o));
+      b_lo = min(b_lo, __shfl_xor_sync(0xffffffffu, b_lo, o));
+      b_hi = max(b_hi, __shfl_xor_sync(0xffffffffu, b_hi, o));
+    }
+    if (lane == 0) reinterpret_cast<int4*>(tile_ranges)[t] = make_int4(c_lo, c_hi, b_lo, b_hi);
+  }
+}
+
+__device__ __forceinline__ bool visible(int kk, int a0, int a1, int b0, int b1) {
+  return (kk >= a0 && kk < a1) || (kk >= b0 && kk < b1);
+}
+
+// -------------------------------------------------------------------- dQ ----
+// TMEM: S [0,128)  dP [128,256)  dQ [256,384)  dS0 [384,448)  dS1 [448,512)
+static constexpr int kDqSmem = 2 * kTile /*Q,dO*/ + 2 * 2 * kTile /*K,V x2 stages*/ + 1024 + 256;
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = smem + kTile;
+  uint8_t* sKV = smem + 2 * kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + 4 * kTile);
+  uint64_t* q_full = bars;        // Q and dO
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* sp_full = bars + 5;   // S and dP ready
+  uint64_t* ds_full = bars + 6;   // dS written (4 arrivals)
+  uint64_t* dq_done = bars + 7;   // [2] dQ MMA of tile j retired -> dq_done[j & 1] (frees dS buffer j & 1)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* range = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.group, pm = BM / G;
+  const int qt = gridDim.x - 1 - blockIdx.x;   // late tiles (longest prefixes) first
+  const int q0 = qt * pm;
+  const int kvh = blockIdx.y;
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(sp_full, 1);
+    mbar_init(ds_full, 4);
+    mbar_init(&dq_done[0], 1);
+    mbar_init(&dq_done[1], 1);
+    fence_barrier_init();
+    const int4 r = reinterpret_cast<const int4*>(p.tile_ranges)[qt];
+    range[0] = r.x / BN; range[1] = (r.y + BN - 1) / BN;
+    range[2] = r.z / BN; range[3] = (r.w + BN - 1) / BN;
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  int ca = range[0], cb = range[1], da = range[2], db = range[3];
+  if (cb <= ca) { ca = 0; cb = 0; }
+  if (db <= da) { da = 0; db = 0; }
+  if (cb > ca && db > da) {
+    if (da < ca) { int t0 = ca, t1 = cb; ca = da; cb = db; da = t0; db = t1; }
+    if (da < cb) da = cb;
+    if (db < da) db = da;
+  }
+  const int n_tiles = (cb - ca) + (db - da);
+  auto tile_index = [&](int j) { return j < (cb - ca) ? ca + j : da + (j - (cb - ca)); };
+
+  if (warp == 0) {
+    if (lane == 0 && n_tiles > 0) {
+      mbar_arrive_expect_tx(q_full, 2 * kTile);
+      tma_load_3d(sQ, &maps.q, q_full, 0, kvh * G, q0);
+      tma_load_3d(sQ + kChunk, &maps.q, q_full, 64, kvh * G, q0);
+      tma_load_3d(sdO, &maps.dout, q_full, 0, kvh * G, q0);
+      tma_load_3d(sdO + kChunk, &maps.dout, q_full, 64, kvh * G, q0);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_word)) break;
+        uint8_t* sK = sKV + st * 2 * kTile;
+        uint8_t* sV = sK + kTile;
+        const int k0 = tile_index(j) * BN;
+        mbar_arrive_expect_tx(&kv_full[st], 2 * kTile);
+        tma_load_3d(sK, &maps.k, &kv_full[st], 0, kvh, k0);
+        tma_load_3d(sK + kChunk, &maps.k, &kv_full[st], 64, kvh, k0);
+        tma_load_3d(sV, &maps.v, &kv_full[st], 0, kvh, k0);
+        tma_load_3d(sV + kChunk, &maps.v, &kv_full[st], 64, kvh, k0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(BM, BN, 0, 0);   // both K-major (d-reduction)
+      constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);   // dS (TMEM) x K (MN-major view)
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
+      auto issue_s_dp = [&](int j) {
+        const uint32_t k_addr = smem_u32(sKV + (j & 1) * 2 * kTile);
+        const uint32_t v_addr = k_addr + kTile;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kChunk + (k & 3) * 32;
+          tc_mma_ss(tmem + 0, make_smem_desc(q_addr + off, 16, 1024),
+                    make_smem_desc(k_addr + off, 16, 1024), idesc_kk, k ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kChunk + (k & 3) * 32;
+          tc_mma_ss(tmem + 128, make_smem_desc(do_addr + off, 16, 1024),
+                    make_smem_desc(v_addr + off, 16, 1024), idesc_kk, k ? 1u : 0u);
+        }
+        tc_commit(sp_full);
+      };
+      bool alive = mbar_wait(q_full, 0, abort_word) && mbar_wait(&kv_full[0], 0, abort_word);
+      if (alive) { tc_fence_after(); issue_s_dp(0); }
+      for (int j = 0; j < n_tiles && alive; ++j) {
+        if (j + 1 < n_tiles && !mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_word)) break;
+        if (!mbar_wait(ds_full, j & 1, abort_word)) break;
+        tc_fence_after();
+        if (j + 1 < n_tiles) issue_s_dp(j + 1);
+        const uint32_t k_addr = smem_u32(sKV + (j & 1) * 2 * kTile);
+        const uint32_t ds_col = tmem + 384 + (j & 1) * 64;
+#pragma unroll
+        for (int k = 0; k < BN / 16; ++k)
+          tc_mma_ts(tmem + 256, ds_col + k * 8, make_smem_desc(k_addr + k * 2048, kChunk, 1024), idesc_dq,
+                    (j | k) ? 1u : 0u);
+        tc_commit(&kv_empty[j & 1]);
+        tc_commit(&dq_done[j & 1]);
+      }
+    }
+  } else {
+    const int qd = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(qd * 32) << 16;
+    const int t = qd * 32 + lane;
+    const int pos = q0 + t / G;
+    const int head = kvh * G + t % G;
+    const bool row_ok = pos < p.q_total;
+    int a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+    float lse2 = 0.f, delta = 0.f;
+    if (row_ok) {
+      const int4 iv = reinterpret_cast<const int4*>(p.intervals)[pos];
+      a0 = iv.x; a1 = iv.y; b0 = iv.z; b1 = iv.w;
+      lse2 = p.lse[(size_t)head * p.q_total + pos] * kLog2e;
+      delta = p.delta[(size_t)head * p.q_total + pos];
+    }
+    bool alive = true;
+    for (int j = 0; j < n_tiles && alive; ++j) {
+      if (!mbar_wait(sp_full, j & 1, abort_word)) { alive = false; break; }
+      // dS buffer j&1 was last read by the dQ MMA of tile j-2
+      if (j >= 2 && !mbar_wait(&dq_done[j & 1], ((j >> 1) - 1) & 1, abort_word)) { alive = false; break; }
+      tc_fence_after();
+      const int k0 = tile_index(j) * BN;
+      const uint32_t ds_addr = tmem + lane_base + 384 + (j & 1) * 64;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t s[32], dp[32], pk[16];
+        tmem_ld_32x32(tmem + lane_base + c, s);
+        tmem_ld_32x32(tmem + lane_base + 128 + c, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kk = k0 + c + i + u;
+            const bool vis = row_ok && visible(kk, a0, a1, b0, b1);
+            const float pr = vis ? fast_exp2(__uint_as_float(s[i + u]) * p.scale_log2 - lse2) : 0.f;
+            e[u] = pr * (__uint_as_float(dp[i + u]) - delta) * p.scale;
+          }
+          pk[i / 2] = pack_bf16x2(e[0], e[1]);
+        }
+        // 16 packed columns
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+            "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+            ::"r"(ds_addr + c / 2), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]),
+            "r"(pk[6]), "r"(pk[7]), "r"(pk[8]), "r"(pk[9]), "r"(pk[10]), "r"(pk[11]), "r"(pk[12]),
+            "r"(pk[13]), "r"(pk[14]), "r"(pk[15])
+            : "memory");
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+    }
+    if (alive && n_tiles > 0)
+      alive = mbar_wait(&dq_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_word);
+    if (alive) {
+      tc_fence_after();
+      __nv_bfloat16* row = p.dq + ((size_t)(row_ok ? pos : 0) * p.hq + head) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 32) {
+        uint32_t r[32];
+        if (n_tiles > 0) { tmem_ld_32x32(tmem + lane_base + 256 + c, r); tmem_ld_wait(); }
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 o = make_uint4(0, 0, 0, 0);
+            if (n_tiles > 0) {
+              o.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+            }
+            reinterpret_cast<uint4*>(row + c)[i] = o;
+          }
+        }
+      }
+    }
+  }
+  if (*abort_word) {
+    __nanosleep(200000);
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, kStatusWaitTimeout);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tmem_dealloc(tmem, 512); }
+}
+
+// ------------------------------------------------------------------ dK/dV ---
+// TMEM: S^T / P^T [0,128)   dP^T / dS^T [128,256)   dV [256,384)   dK [384,512)
+static constexpr int kListCap = 4096;
+static constexpr int kDkvSmem = 2 * kTile /*K,V*/ + 2 * 2 * kTile /*Q,dO x2 stages*/ +
+                                2 * 128 * 24 /*row metadata x2*/ + kListCap * 4 + 1024 + 256;
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + kTile;
+  uint8_t* sQdO = smem + 2 * kTile;           // stage s: Q at +s*2*kTile, dO right after
+  uint8_t* meta = sQdO + 4 * kTile;           // stage s: int4 iv[128]; float lse2[128]; float delta[128]
+  int* list = reinterpret_cast<int*>(meta + 2 * 128 * 24);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(list + kListCap);
+  uint64_t* kv_full = bars;         // 1
+  uint64_t* qdo_full = bars + 1;    // [2]
+  uint64_t* qdo_empty = bars + 3;   // [2]
+  uint64_t* st_full = bars + 5;     // S^T and dP^T ready
+  uint64_t* pds_full = bars + 6;    // P^T and dS^T written (4 arrivals)
+  uint64_t* acc_done = bars + 7;    // dV/dK MMAs of the tile retired
+  uint64_t* meta_bar = bars + 8;    // row metadata of the tile staged by all 128 softmax threads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* n_list = reinterpret_cast<int*>(tmem_slot + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.group, pm = BM / G;
+  const int k0 = blockIdx.x * BN;
+  const int kvh = blockIdx.y;
+
+  if (threadIdx.x == 0) {
+    *abort_word = 0;
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
+    mbar_init(st_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(acc_done, 1);
+    mbar_init(meta_bar, 128);
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  if (warp == 0) {
+    // Query tiles whose visible key ranges intersect [k0, k0 + BN): ordered compaction by ballot.
+    int count = 0;
+    for (int base = 0; base < p.n_qtiles; base += 32) {
+      const int t = base + lane;
+      bool hit = false;
+      if (t < p.n_qtiles) {
+        const int4 r = reinterpret_cast<const int4*>(p.tile_ranges)[t];
+        hit = (r.y > r.x && r.x < k0 + BN && r.y > k0) || (r.w > r.z && r.z < k0 + BN && r.w > k0);
+      }
+      const uint32_t m = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int idx = count + __popc(m & ((1u << lane) - 1));
+        if (idx < kListCap) list[idx] = t;
+      }
+      count += __popc(m);
+    }
+    if (lane == 0) *n_list = count;   // the host guarantees n_qtiles <= kListCap
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const int n = *n_list;
+
+  if (warp == 0) {
+    if (lane == 0 && n > 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * kTile);
+      tma_load_3d(sK, &maps.k, kv_full, 0, kvh, k0);
+      tma_load_3d(sK + kChunk, &maps.k, kv_full, 64, kvh, k0);
+      tma_load_3d(sV, &maps.v, kv_full, 0, kvh, k0);
+      tma_load_3d(sV + kChunk, &maps.v, kv_full, 64, kvh, k0);
+      for (int i = 0; i < n; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(&qdo_empty[st], ((i >> 1) & 1) ^ 1u, abort_word)) break;
+        uint8_t* sQ = sQdO + st * 2 * kTile;
+        uint8_t* sdO = sQ + kTile;
+        const int q0 = list[i] * pm;
+        mbar_arrive_expect_tx(&qdo_full[st], 2 * kTile);
+        tma_load_3d(sQ, &maps.q, &qdo_full[st], 0, kvh * G, q0);
+        tma_load_3d(sQ + kChunk, &maps.q, &qdo_full[st], 64, kvh * G, q0);
+        tma_load_3d(sdO, &maps.dout, &qdo_full[st], 0, kvh * G, q0);
+        tma_load_3d(sdO + kChunk, &maps.dout, &qdo_full[st], 64, kvh * G, q0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(BN, BM, 0, 0);   // K/V (K-major) x Q/dO (K-major)
+      constexpr uint32_t idesc_acc = make_idesc_bf16(BN, HD, 0, 1);  // P^T/dS^T (TMEM) x dO/Q (MN-major)
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      bool alive = mbar_wait(kv_full, 0, abort_word);
+      for (int i = 0; i < n && alive; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(&qdo_full[st], (i >> 1) & 1, abort_word)) break;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQdO + st * 2 * kTile);
+        const uint32_t do_addr = q_addr + kTile;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kChunk + (k & 3) * 32;
+          tc_mma_ss(tmem + 0, make_smem_desc(k_addr + off, 16, 1024),
+                    make_smem_desc(q_addr + off, 16, 1024), idesc_kk, k ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kChunk + (k & 3) * 32;
+          tc_mma_ss(tmem + 128, make_smem_desc(v_addr + off, 16, 1024),
+                    make_smem_desc(do_addr + off, 16, 1024), idesc_kk, k ? 1u : 0u);
+        }
+        tc_commit(st_full);
+        if (!mbar_wait(pds_full, i & 1, abort_word)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BM / 16; ++k)   // reduction over the 128 query rows of the tile
+          tc_mma_ts(tmem + 256, tmem + 0 + k * 8, make_smem_desc(do_addr + k * 2048, kChunk, 1024),
+                    idesc_acc, (i | k) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < BM / 16; ++k)
+          tc_mma_ts(tmem + 384, tmem + 128 + k * 8, make_smem_desc(q_addr + k * 2048, kChunk, 1024),
+                    idesc_acc, (i | k) ? 1u : 0u);
+        tc_commit(&qdo_empty[st]);
+        tc_commit(acc_done);
+      }
+    }
+  } else {
+    const int qd = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(qd * 32) << 16;
+    const int t = qd * 32 + lane;          // key row of the tile == TMEM lane
+    const int kk = k0 + t;
+    bool alive = true;
+    for (int i = 0; i < n && alive; ++i) {
+      // Row metadata of query tile i (thread t fetches query row t) into shared memory.
+      uint8_t* mb = meta + (i & 1) * 128 * 24;
+      int4* m_iv = reinterpret_cast<int4*>(mb);
+      float* m_lse = reinterpret_cast<float*>(mb + 128 * 16);
+      float* m_delta = m_lse + 128;
+      {
+        const int pos = list[i] * pm + t / G;
+        const int head = kvh * G + t % G;
+        int4 iv = make_int4(0, 0, 0, 0);
+        float l2 = 0.f, dl = 0.f;
+        if (pos < p.q_total) {
+          iv = reinterpret_cast<const int4*>(p.intervals)[pos];
+          l2 = p.lse[(size_t)head * p.q_total + pos] * kLog2e;
+          dl = p.delta[(size_t)head * p.q_total + pos];
+        }
+        m_iv[t] = iv;
+        m_lse[t] = l2;
+        m_delta[t] = dl;
+      }
+      mbar_arrive(meta_bar);
+      if (!mbar_wait(meta_bar, i & 1, abort_word)) { alive = false; break; }
+      if (!mbar_wait(st_full, i & 1, abort_word)) { alive = false; break; }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < BM; c += 32) {
+        uint32_t s[32], dp[32], pp[16], ds[16];
+        tmem_ld_32x32(tmem + lane_base + c, s);
+        tmem_ld_32x32(tmem + lane_base + 128 + c, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int r = 0; r < 32; r += 2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int4 iv = m_iv[c + r + u];
+            const bool vis = visible(kk, iv.x, iv.y, iv.z, iv.w);
+            const float pr =
+                vis ? fast_exp2(__uint_as_float(s[r + u]) * p.scale_log2 - m_lse[c + r + u]) : 0.f;
+            pv[u] = pr;
+            dsv[u] = pr * (__uint_as_float(dp[r + u]) - m_delta[c + r + u]) * p.scale;
+          }
+          pp[r / 2] = pack_bf16x2(pv[0], pv[1]);
+          ds[r / 2] = pack_bf16x2(dsv[0], dsv[1]);
+        }
+        // P^T over the S^T columns already consumed, dS^T over the dP^T columns already consumed
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+            "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+            ::"r"(tmem + lane_base + c / 2), "r"(pp[0]), "r"(pp[1]), "r"(pp[2]), "r"(pp[3]), "r"(pp[4]),
+            "r"(pp[5]), "r"(pp[6]), "r"(pp[7]), "r"(pp[8]), "r"(pp[9]), "r"(pp[10]), "r"(pp[11]),
+            "r"(pp[12]), "r"(pp[13]), "r"(pp[14]), "r"(pp[15])
+            : "memory");
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+            "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+            ::"r"(tmem + lane_base + 128 + c / 2), "r"(ds[0]), "r"(ds[1]), "r"(ds[2]), "r"(ds[3]),
+            "r"(ds[4]), "r"(ds[5]), "r"(ds[6]), "r"(ds[7]), "r"(ds[8]), "r"(ds[9]), "r"(ds[10]),
+            "r"(ds[11]), "r"(ds[12]), "r"(ds[13]), "r"(ds[14]), "r"(ds[15])
+            : "memory");
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+    }
+    if (alive && n > 0) alive = mbar_wait(acc_done, (n - 1) & 1, abort_word);
+    if (alive) {
+      tc_fence_after();
+      const bool row_ok = kk < p.tk;
+      __nv_bfloat16* dvrow = p.dv + ((size_t)(row_ok ? kk : 0) * p.hkv + kvh) * HD;
+      __nv_bfloat16* dkrow = p.dk + ((size_t)(row_ok ? kk : 0) * p.hkv + kvh) * HD;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        __nv_bfloat16* row = half ? dkrow : dvrow;
+        const uint32_t col0 = half ? 384 : 256;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t r[32];
+          if (n > 0) { tmem_ld_32x32(tmem + lane_base + col0 + c, r); tmem_ld_wait(); }
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 o = make_uint4(0, 0, 0, 0);
+              if (n > 0) {
+                o.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                o.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                o.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                o.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+              }
+              reinterpret_cast<uint4*>(row + c)[i] = o;
+            }
+          }
+        }
+      }
+    }
+  }
+  if (*abort_word) {
+    __nanosleep(200000);
+    if (threadIdx.x == 0 && p.status) atomicExch(p.status, kStatusWaitTimeout);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { __syncwarp(); tmem_dealloc(tmem, 512); }
+}
+
+}  // namespace attn
+}  // namespace ab
+
+// dq [Qtot,Hq,128], dk/dv [Tk,Hkv,128] contiguous bf16.  Scratch supplied by the caller and filled
+// here: delta [Hq,Qtot] fp32 and ranges [ceil(Qtot / (128 / G)), 4] int32.
+extern "C" int ab_attn_bwd(const void* q, const void* k, const void* v, const int* intervals,
+                           const void* out, const float* lse, const void* dout, float* delta,
+                           int* ranges, void* dq,
+                           void* dk, void* dv, int q_total, int tk, int hq, int hkv, int head_dim,
+                           long long k_ld, long long v_ld, float scale, int* status, void* stream_) {
+  using namespace ab;
+  using namespace ab::attn;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (head_dim != HD || hq % hkv) return -10;
+  const int G = hq / hkv;
+  if (G > 16 || (BM % G)) return -11;
+  if (q_total <= 0 || tk <= 0) return 0;
+  const int pm = BM / G;
+  const int n_qtiles = (q_total + pm - 1) / pm;
+  const int n_ktiles = (tk + BN - 1) / BN;
+  if (n_qtiles > kListCap) return -15;
+  long long prep_blocks = ((long long)q_total * hq + 7) / 8;
+  if (prep_blocks > 148 * 8) prep_blocks = 148 * 8;
+  attn_bwd_prep_kernel<<<(int)prep_blocks, 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta,
+      intervals, ranges, q_total, hq, pm, n_qtiles);
+  BwdMaps maps;
+  int rc;
+  if ((rc = make_map_rows_heads(&maps.q, q, q_total, hq, (long long)hq * HD, G, pm))) return rc;
+  if ((rc = make_map_rows_heads(&maps.dout, dout, q_total, hq, (long long)hq * HD, G, pm))) return rc;
+  if ((rc = make_map_rows_heads(&maps.k, k, tk, hkv, k_ld, 1, BN))) return rc;
+  if ((rc = make_map_rows_heads(&maps.v, v, tk, hkv, v_ld, 1, BN))) return rc;
+  BwdParams p;
+  p.intervals = intervals;
+  p.lse = lse;
+  p.delta = delta;
+  p.tile_ranges = ranges;
+  p.dq = reinterpret_cast<__nv_bfloat16*>(dq);
+  p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
+  p.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.q_total = q_total;
+  p.hq = hq;
+  p.hkv = hkv;
+  p.group = G;
+  p.tk = tk;
+  p.n_qtiles = n_qtiles;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.status = status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem) != cudaSuccess)
+      return -3;
+    attr_set = true;
+  }
+  attn_bwd_dq_kernel<<<dim3(n_qtiles, hkv), kThreads, kDqSmem, stream>>>(maps, p);
+  attn_bwd_dkv_kernel<<<dim3(n_ktiles, hkv), kThreads, kDkvSmem, stream>>>(maps, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

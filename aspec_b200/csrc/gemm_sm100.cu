@@ -463,13 +463,14 @@ extern "C" {
 
 // D[M,N] = alpha * (A0*B0^T + A1*B1^T) (+ C).  Returns 0 on a successful launch.
 //   epi: 0 store, 1 row statistics (vocabulary head), 2 SwiGLU (N = 2 * out)
-//   k1 = 0 disables the second source.  K extents must be multiples of 8.
+//   k1 = 0 disables the second source.  Leading dimensions must be multiples of 8 elements and
+//   base pointers 16-byte aligned (TMA); M, N and K themselves are arbitrary (tails are zero-filled).
 int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOperand* b0,
                  const AbOperand* a1, const AbOperand* b1, void* D, long long ldd, int d_is_fp32,
                  const void* C, float alpha, int epi, float* stats, float logit_scale, int* status,
                  int max_ctas, void* stream) {
   using namespace ab;
-  if (M <= 0 || N <= 0 || K0 <= 0 || (K0 & 7) || (K1 & 7)) return -10;
+  if (M <= 0 || N <= 0 || K0 <= 0 || K1 < 0) return -10;
   if (K1 > 0 && (a1->mn_major != a0->mn_major || b1->mn_major != b0->mn_major)) return -11;
   GemmMaps maps;
   auto mk = [&](CUtensorMap* m, const AbOperand* o, int mn_extent, int k_extent, int tile_mn) {

@@ -1,0 +1,84 @@
+"""ctypes bindings of the interval flash-attention kernels (``csrc/attention_*_sm100.cu``)."""
+from __future__ import annotations
+
+import ctypes as _c
+import math
+from typing import Tuple
+
+import torch
+
+from aspec_b200 import _native
+from aspec_b200.ops.gemm import status_word
+
+HEAD_DIM = 128
+
+
+def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    """The tcgen05 kernels cover bf16, head dim 128 for q/k/v and group size Hq/Hkv in {1,2,4,8,16}."""
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        return False
+    if q.shape[-1] != HEAD_DIM or k.shape[-1] != HEAD_DIM or v.shape[-1] != HEAD_DIM:
+        return False
+    hq, hkv = q.shape[1], k.shape[1]
+    return hq % hkv == 0 and (hq // hkv) in (1, 2, 4, 8, 16)
+
+
+def unsupported_shape_fallback(q, k, v, intervals, scale):
+    """Shapes outside the kernel's coverage (e.g. MLA 192/128 heads) run the dense-mask statement in
+    fp32 on the device.  This is a correctness path for small auxiliary configurations only."""
+    from aspec_b200.ops.attention import interval_attention_reference
+    return interval_attention_reference(q, k, v, intervals, scale)
+
+
+def _rows_view(t: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """``[N, H, d]`` with unit strides inside a row (head stride d); returns (tensor, row stride)."""
+    if t.stride(2) != 1 or t.stride(1) != t.shape[2] or t.stride(0) % 8 or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t, t.stride(0)
+
+
+def forward(q, k, v, intervals, scale) -> Tuple[torch.Tensor, torch.Tensor]:
+    Q, hq, d = q.shape
+    tk, hkv = k.shape[0], k.shape[1]
+    q = q.contiguous()
+    k, k_ld = _rows_view(k)
+    v, v_ld = _rows_view(v)
+    out = torch.empty_like(q)
+    lse = torch.empty(hq, Q, dtype=torch.float32, device=q.device)
+    st = status_word(q.device)
+    rc = _native.kernels().ab_attn_fwd(
+        _c.c_void_p(q.data_ptr()), _c.c_void_p(k.data_ptr()), _c.c_void_p(v.data_ptr()),
+        _c.c_void_p(intervals.data_ptr()), _c.c_void_p(out.data_ptr()), _c.c_void_p(lse.data_ptr()),
+        Q, tk, hq, hkv, d, _c.c_longlong(k_ld), _c.c_longlong(v_ld), _c.c_float(scale),
+        _c.c_void_p(st.data_ptr()), _c.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"ab_attn_fwd refused the launch (code {rc})")
+    return out, lse
+
+
+def backward(q, k, v, intervals, out, lse, dout, scale):
+    Q, hq, d = q.shape
+    tk, hkv = k.shape[0], k.shape[1]
+    lib = _native.kernels()
+    if not hasattr(lib, "ab_attn_bwd"):
+        raise RuntimeError("attention backward kernel is missing from the kernel library")
+    k, k_ld = _rows_view(k)
+    v, v_ld = _rows_view(v)
+    dq = torch.empty_like(q)
+    dk = torch.empty(tk, hkv, d, dtype=q.dtype, device=q.device)
+    dv = torch.empty(tk, hkv, d, dtype=q.dtype, device=q.device)
+    delta = torch.empty(hq, Q, dtype=torch.float32, device=q.device)
+    pm = 128 // (hq // hkv)
+    ranges = torch.empty((Q + pm - 1) // pm, 4, dtype=torch.int32, device=q.device)
+    st = status_word(q.device)
+    rc = lib.ab_attn_bwd(
+        _c.c_void_p(q.data_ptr()), _c.c_void_p(k.data_ptr()), _c.c_void_p(v.data_ptr()),
+        _c.c_void_p(intervals.data_ptr()), _c.c_void_p(out.data_ptr()), _c.c_void_p(lse.data_ptr()),
+        _c.c_void_p(dout.data_ptr()), _c.c_void_p(delta.data_ptr()), _c.c_void_p(ranges.data_ptr()),
+        _c.c_void_p(dq.data_ptr()),
+        _c.c_void_p(dk.data_ptr()), _c.c_void_p(dv.data_ptr()), Q, tk, hq, hkv, d,
+        _c.c_longlong(k_ld), _c.c_longlong(v_ld), _c.c_float(scale), _c.c_void_p(st.data_ptr()),
+        _c.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
+    if rc != 0:
+        raise RuntimeError(f"ab_attn_bwd refused the launch (code {rc})")
+    return dq, dk, dv
