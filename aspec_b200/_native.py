@@ -122,7 +122,34 @@ def build_all(force: bool = False, verbose: bool = False) -> None:
     build_runtime(force=force)
 
 
-def kernels() -> ctypes.CDLL:
+# GPU kernels launched by one call of each exported entry point (for launch accounting).
+_LAUNCHES_PER_CALL = {"ab_attn_bwd": 3}
+launch_count = 0
+
+
+class _CountingLibrary:
+    """Forwards to the ctypes library and counts kernel launches made through it."""
+
+    def __init__(self, lib: ctypes.CDLL):
+        self._lib = lib
+        self._cache = {}
+
+    def __getattr__(self, name: str):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._lib, name)
+            weight = _LAUNCHES_PER_CALL.get(name, 1)
+
+            def fn(*args, _raw=raw, _w=weight):
+                global launch_count
+                launch_count += _w
+                return _raw(*args)
+
+            self._cache[name] = fn
+        return fn
+
+
+def kernels() -> "_CountingLibrary":
     """The CUDA kernel library.  Raises if it has not been built."""
     global _kernels
     with _lock:
@@ -131,7 +158,7 @@ def kernels() -> ctypes.CDLL:
                 raise RuntimeError(
                     f"{_KERNEL_LIB} is missing: run `python -c 'import __graft_entry__ as g; g.build()'`"
                     " or `python -m aspec_b200.build` first")
-            _kernels = ctypes.CDLL(str(_KERNEL_LIB))
+            _kernels = _CountingLibrary(ctypes.CDLL(str(_KERNEL_LIB)))
         return _kernels
 
 

@@ -195,7 +195,8 @@ class DFlashModel(nn.Module):
         n = layout.n
         keep_flat = keep.to(dev).reshape(-1)[layout.row * layout.n_slots + layout.slot]
 
-        ctx = self.draft_model.extract_context_feature(hidden_states.reshape(B * T, -1))
+        wdtype = self.draft_model.context_proj.weight.dtype
+        ctx = self.draft_model.extract_context_feature(hidden_states.reshape(B * T, -1).to(wdtype))
         ctx_pos = (base_position_ids.reshape(-1).long() if base_position_ids is not None
                    else torch.arange(T, device=dev).repeat(B))
         fa = layout.flat_anchor
@@ -278,7 +279,7 @@ class DFlashModel(nn.Module):
         Returns ``(teacher_hidden, t_index)``: the whole context with an index table when that is
         fewer rows than the supervised set (each context row is projected once), else gathered rows.
         """
-        flat = last_hidden_states.reshape(-1, last_hidden_states.shape[-1])
+        flat = last_hidden_states.reshape(-1, last_hidden_states.shape[-1]).to(self.draft_model.context_proj.weight.dtype)
         if self.context_parallel is not None and self.context_parallel.size > 1:
             return self.context_parallel.gather_teacher_rows(flat, flat_index), None
         if flat.shape[0] <= flat_index.numel():

@@ -1,0 +1,161 @@
+"""Single-process-per-GPU Draft trainer: micro-batch loop, loss pooling, optimizer step, metrics.
+
+What one optimizer update does (reference: aspec/training/trainer.py:641-760,
+aspec/training/dflash_trainer.py:489-533, 747-806):
+
+1. for each of ``accumulation`` micro-batches: forward the training wrapper, ``backward`` the raw loss
+   *numerator* (weight gradients accumulate in fp32 ``main_grad`` buffers);
+2. after the last one: SUM-reduce the flat gradient and the pooled denominators over the data-parallel
+   group, and fold ``1 / denominator`` into the optimizer's gradient scale - equivalent to the
+   reference's "rescale by world * accumulation / denominator after a mean reduction", without touching
+   the gradients twice;
+3. fused norm / clip / non-finite skip / AdamW / bf16 write-back; scheduler step; router-bias hooks.
+
+Loss components travel as ``(numerator, denominator)`` pairs and are pooled on the device; ``metrics()``
+performs the single device->host read of an update.
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from aspec_b200.training.optimizer import BF16Optimizer
+
+_BATCH_TENSOR_KEYS = ("input_ids", "hidden_states", "loss_mask", "last_hidden_states", "attention_mask",
+                      "ctx_doc_ids", "base_position_ids", "packed_context_positions",
+                      "injected_anchors", "injected_keep_mask")
+
+
+class DraftTrainer:
+    def __init__(self, model: torch.nn.Module, lm_head_weight: torch.Tensor, *, lr: float = 6e-4,
+                 min_lr: float = 6e-5, weight_decay: float = 0.0, max_grad_norm: float = 1.0,
+                 total_steps: int = 1000, warmup_ratio: float = 0.04, decay_style: str = "cosine",
+                 accumulation: int = 1, dp_group: Optional[dist.ProcessGroup] = None,
+                 device: Optional[torch.device] = None, betas=(0.9, 0.999)):
+        self.model = model
+        self.draft = model.draft_model
+        self.lm_head_weight = lm_head_weight
+        self.accumulation = int(accumulation)
+        self.dp_group = dp_group
+        self.device = device or next(model.parameters()).device
+        self.optimizer = BF16Optimizer(self.draft, lr=lr, weight_decay=weight_decay,
+                                       max_grad_norm=max_grad_norm, total_steps=total_steps,
+                                       warmup_ratio=warmup_ratio, decay_style=decay_style, min_lr=min_lr,
+                                       betas=betas)
+        self.global_step = 0
+        self._pool: Dict[str, List[torch.Tensor]] = {}
+        self._last: Dict[str, torch.Tensor] = {}
+        self.post_step_hooks = []
+        self._copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+
+    # -- host -> device -------------------------------------------------------------
+    def to_device(self, batch: dict) -> dict:
+        """Copy a host batch (ideally pinned) to the device; tensors already there pass through."""
+        out = {}
+        for k, v in batch.items():
+            if torch.is_tensor(v) and k in _BATCH_TENSOR_KEYS and k != "injected_keep_mask":
+                out[k] = v.to(self.device, non_blocking=True)
+            else:
+                out[k] = v
+        return out
+
+    @staticmethod
+    def h2d_bytes(batch: dict) -> int:
+        return sum(v.numel() * v.element_size() for k, v in batch.items()
+                   if torch.is_tensor(v) and k in _BATCH_TENSOR_KEYS and not v.is_cuda and k != "injected_keep_mask")
+
+    # -- one micro-batch ----------------------------------------------------------------
+    def _forward_backward(self, batch: dict) -> None:
+        out = self.model(
+            batch["input_ids"], batch["hidden_states"], batch["loss_mask"], self.lm_head_weight,
+            last_hidden_states=batch.get("last_hidden_states"), ctx_doc_ids=batch.get("ctx_doc_ids"),
+            base_position_ids=batch.get("base_position_ids"),
+            packed_context_positions=batch.get("packed_context_positions"),
+            injected_anchors=batch.get("injected_anchors"),
+            injected_keep_mask=batch.get("injected_keep_mask"),
+            packed_document_lengths=batch.get("packed_document_lengths"),
+            attention_mask=batch.get("attention_mask"))
+        loss, acc, loss_pp, acc_pp, count_pp, comps, (num, den) = out
+        if num.requires_grad:
+            num.backward()
+        pool = self._pool
+        pool.setdefault("loss", []).append(torch.stack([num.detach().float(), den.float()]))
+        pool.setdefault("acc_pp", []).append(torch.stack([acc_pp * count_pp.clamp(min=1.0) * (count_pp > 0), count_pp]))
+        pool.setdefault("loss_pp", []).append(torch.stack([loss_pp * count_pp.clamp(min=1.0) * (count_pp > 0), count_pp]))
+        for key, (n_, d_) in comps.items():
+            pool.setdefault("c/" + key, []).append(torch.stack([n_.float().reshape(()), d_.float().reshape(())]))
+
+    # -- one optimizer update -------------------------------------------------------------
+    def train_update(self, batches: Iterable[dict]) -> None:
+        """Run ``accumulation`` micro-batches and one optimizer step.  No host synchronisation."""
+        self.model.train()
+        self._pool = {}
+        n = 0
+        for batch in batches:
+            self._forward_backward(self.to_device(batch))
+            n += 1
+        if n == 0:
+            raise ValueError("train_update needs at least one micro-batch")
+        opt = self.optimizer
+        opt.fold_autograd_grads()
+        pooled = {k: torch.stack(v).sum(0) for k, v in self._pool.items()}
+        world = dist.get_world_size(self.dp_group) if (dist.is_available() and dist.is_initialized()) else 1
+        if world > 1:
+            keys = sorted(pooled)
+            flat = torch.cat([pooled[k].reshape(-1) for k in keys])
+            dist.all_reduce(flat, group=self.dp_group)
+            off = 0
+            for k in keys:
+                m = pooled[k].numel()
+                pooled[k] = flat[off:off + m].view_as(pooled[k])
+                off += m
+            dist.all_reduce(opt.flat_grad, group=self.dp_group)
+        den = pooled["loss"][1]
+        opt.set_grad_scale(torch.where(den > 0, 1.0 / den.clamp(min=1e-12), torch.zeros_like(den)))
+        grad_norm = opt.step()
+        self.global_step += 1
+        for hook in self.post_step_hooks:
+            hook(self)
+        pooled["grad_norm"] = grad_norm
+        self._last = pooled
+
+    def metrics(self) -> Dict[str, float]:
+        """Metrics of the last update (one device->host transfer)."""
+        p = self._last
+        if not p:
+            return {}
+        keys = sorted(k for k in p if k != "grad_norm")
+        flat = torch.cat([p[k].reshape(-1).float() for k in keys] + [p["grad_norm"].reshape(1).float()]).cpu()
+        out: Dict[str, float] = {}
+        off = 0
+        vals = {}
+        for k in keys:
+            m = p[k].numel()
+            vals[k] = flat[off:off + m].view_as(p[k].cpu())
+            off += m
+        out["train/grad_norm"] = float(flat[-1])
+        num, den = vals["loss"]
+        out["train/avg_loss"] = float(num / den) if den > 0 else 0.0
+        a, c = vals["acc_pp"]
+        out["train/avg_acc"] = float(a.sum() / c.sum()) if c.sum() > 0 else 0.0
+        accs = (a / c.clamp(min=1.0)).tolist()
+        tau, run = 0.0, 1.0
+        for i, v in enumerate(accs):
+            out[f"train/acc_{i}"] = v
+            if c[i] > 0:
+                run *= v
+                tau += run
+        out["train/simulated_acc_len"] = tau
+        l_, c2 = vals["loss_pp"]
+        for i, v in enumerate((l_ / c2.clamp(min=1.0)).tolist()):
+            out[f"train/ploss_{i}"] = v
+        for k in keys:
+            if k.startswith("c/"):
+                n_, d_ = vals[k]
+                out["train/" + k[2:]] = float(n_ / d_) if d_ > 0 else 0.0
+        out["train/lr"] = self.optimizer.get_learning_rate()
+        out["train/global_step"] = self.global_step
+        return out

@@ -1,0 +1,260 @@
+#!/usr/bin/env python
+"""Headline benchmark: Draft input tokens/s of Qwen3-8B-shaped DSpark training at 4K.
+
+``python bench.py --gpus N --steps K --warmup W`` (torchrun-launched for N > 1, one rank per GPU).
+
+One *step* is one optimizer update over ``--accum`` documents per rank: forward, backward, gradient
+reduction across ranks, clip, AdamW.  Documents follow the benchmark config: lengths log-uniform in
+[256, 4096], uniform token ids, loss mask on the final 60 %, 512 anchors x block 7, one document per
+micro-batch.  Features are synthetic (random bf16 captured layers) and weights random-init.
+
+* ``value``: tokens/s with the documents' features resident on the GPU (the reference's Draft-only
+  methodology), device-timed with CUDA events, max over ranks.
+* ``e2e.value``: the same metric through ``DraftTrainer.train_update`` fed from pinned host memory,
+  every step including the host->device copy of its inputs and a device->host read of its metrics.
+* ``--impl reference`` runs the unmodified reference package from ``baseline/_ref``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_1GPU = 15256.44   # published Draft-only tok/s, 1 x H200
+BASELINE_8GPU = 77721.37   # published online tok/s, 8 x H200
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--accum", type=int, default=16, help="documents (micro-batches) per optimizer update per rank")
+    ap.add_argument("--layers", type=int, default=1, help="Draft decoder layers (benchmark config: 1; reference recipe: 5)")
+    ap.add_argument("--target-layers", type=int, default=3)
+    ap.add_argument("--min-len", type=int, default=256)
+    ap.add_argument("--max-len", type=int, default=4096)
+    ap.add_argument("--pool", type=int, default=0, help="distinct documents per rank (0 = accum * 2)")
+    ap.add_argument("--small", action="store_true", help="tiny shapes (CPU smoke / debugging only; not a valid bench)")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self._stop, self._proc = index, [], False, None
+
+    def start(self):
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self._thread = threading.Thread(target=self._read, daemon=True)
+        self._thread.start()
+
+    def _read(self):
+        for line in self._proc.stdout:
+            if self._stop:
+                break
+            self.samples.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        self._stop = True
+        if self._proc is not None:
+            self._proc.terminate()
+        mhz, mx, reasons = [], 0, set()
+        for s in self.samples:
+            try:
+                mhz.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def build_ours(args, device, dtype):
+    import torch
+    from aspec_b200.config.draft_config import DSparkConfig
+    from aspec_b200.models.draft.dspark import DSparkDraftModel
+    from aspec_b200.models.dspark import DSparkModel
+    if args.small:
+        dims = dict(hidden_size=256, intermediate_size=512, num_attention_heads=2, num_key_value_heads=1,
+                    head_dim=128, vocab_size=4096, target_hidden_size=256, markov_rank=32, mask_token_id=4095)
+    else:
+        dims = dict(hidden_size=4096, intermediate_size=12288, num_attention_heads=32, num_key_value_heads=8,
+                    vocab_size=151936, target_hidden_size=4096, markov_rank=256, mask_token_id=151669)
+    n_tl = args.target_layers
+    ids = {3: [2, 18, 33], 5: [1, 9, 17, 25, 33]}.get(n_tl)
+    cfg = DSparkConfig(num_hidden_layers=args.layers, num_target_layers=n_tl, target_layer_ids=ids,
+                       target_num_hidden_layers=36, rope_theta=1e6, max_position_embeddings=40960, **dims)
+    torch.manual_seed(1234)
+    draft = DSparkDraftModel(cfg).to(device=device, dtype=dtype)
+    model = DSparkModel(draft, block_size=7, num_anchors=512 if not args.small else 64,
+                        loss_decay_gamma=4.0, ce_loss_alpha=0.1, l1_loss_alpha=0.9, confidence_head_alpha=1.0)
+    lm_head = (torch.randn(cfg.vocab_size, cfg.hidden_size, device=device, dtype=torch.float32) * 0.02).to(dtype)
+    return cfg, model, lm_head
+
+
+def make_pool(args, cfg, model, rank, n_docs, pin):
+    """Host-side documents with features and pre-sampled anchors (the collator's job)."""
+    import torch
+    from aspec_b200.data.synthetic import SyntheticSpec, make_document, synthetic_features
+    spec = SyntheticSpec(vocab_size=cfg.vocab_size - 1024, min_len=min(args.min_len, args.max_len), max_len=args.max_len, seed=17)
+    pool = []
+    for i in range(n_docs):
+        row = rank * 100003 + i
+        doc = make_document(spec, row)
+        T = doc["seq_len"]
+        feats = synthetic_features(T, cfg.num_target_layers, cfg.target_hidden_size, row, pin=pin)
+        lm = doc["loss_mask"][None]
+        g = torch.Generator().manual_seed(row)
+        from aspec_b200.ops.anchors import sample_anchor_positions
+        anchors, keep = sample_anchor_positions(T, lm, model.num_anchors, model.block_size, generator=g)
+        batch = {"input_ids": doc["input_ids"][None], "loss_mask": lm,
+                 "hidden_states": feats["hidden_states"][None], "last_hidden_states": feats["last_hidden_states"][None],
+                 "injected_anchors": anchors, "injected_keep_mask": keep, "seq_len": T}
+        if pin and torch.cuda.is_available():
+            for k in ("input_ids", "loss_mask", "injected_anchors"):
+                batch[k] = batch[k].pin_memory()
+        pool.append(batch)
+    return pool
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    cuda = torch.cuda.is_available()
+    device = torch.device("cuda", local) if cuda else torch.device("cpu")
+    dtype = torch.bfloat16 if cuda else torch.float32
+    if cuda:
+        torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl" if cuda else "gloo", device_id=device if cuda else None)
+    from aspec_b200 import _native
+    from aspec_b200.training.draft_trainer import DraftTrainer
+    cfg, model, lm_head = build_ours(args, device, dtype)
+    total_updates = args.steps * 2 + args.warmup * 2 + 8
+    trainer = DraftTrainer(model, lm_head, lr=6e-4, min_lr=6e-5, weight_decay=0.0, max_grad_norm=1.0,
+                           total_steps=max(total_updates, 32), warmup_ratio=0.04, accumulation=args.accum,
+                           device=device)
+    n_docs = args.pool or args.accum * 2
+    pool = make_pool(args, cfg, model, rank, n_docs, pin=cuda)
+    resident = [trainer.to_device(b) for b in pool]
+    if cuda:
+        torch.cuda.synchronize()
+
+    def batches_for(step, source):
+        return [source[(step * args.accum + i) % n_docs] for i in range(args.accum)]
+
+    def tokens_for(step):
+        return sum(pool[(step * args.accum + i) % n_docs]["seq_len"] for i in range(args.accum))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        if cuda:
+            torch.cuda.synchronize()
+
+    def timed(source, read_metrics):
+        for w in range(args.warmup):
+            trainer.train_update(batches_for(w, source))
+            if read_metrics:
+                trainer.metrics()
+        barrier()
+        sampler = ClockSampler(local) if (cuda and rank == 0) else None
+        if sampler:
+            sampler.start()
+        launches0 = _native.launch_count
+        if cuda:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        t0 = time.perf_counter()
+        toks = 0
+        last = {}
+        for s in range(args.steps):
+            trainer.train_update(batches_for(args.warmup + s, source))
+            toks += tokens_for(args.warmup + s)
+            if read_metrics:
+                last = trainer.metrics()
+        if cuda:
+            e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) if cuda else (time.perf_counter() - t0) * 1e3
+        clocks = sampler.stop() if sampler else None
+        launches = _native.launch_count - launches0
+        stats = torch.tensor([ms, float(toks)], dtype=torch.float64, device=device)
+        if world > 1:
+            mx = stats.clone()
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+            sm = stats.clone()
+            dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+            ms, toks = float(mx[0]), float(sm[1])
+        return ms, toks, clocks, launches, last
+
+    ms, toks, clocks, launches, _ = timed(resident, read_metrics=False)
+    if cuda:
+        from aspec_b200.ops.gemm import check_status
+        check_status(device)
+    value = toks / (ms / 1e3)
+    e2e = None
+    if not args.no_e2e:
+        ms2, toks2, _, _, last = timed(pool, read_metrics=True)
+        h2d = sum(DraftTrainer.h2d_bytes(b) for b in batches_for(args.warmup, pool))
+        e2e = {"value": toks2 / (ms2 / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": 4 * (3 * 2 * model.block_size + 2 + 2 * 12 + 1),
+               "ms_per_step": ms2 / args.steps, "loss": last.get("train/avg_loss")}
+    if rank == 0:
+        base = BASELINE_1GPU if world == 1 else None
+        line = {
+            "metric": "Draft input tokens/s, Qwen3-8B DSpark 4K (Draft-only, resident features)",
+            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / base) if base else None, "dtype": "bf16" if cuda else "fp32",
+            "data": "synthetic (uniform token ids, log-uniform lengths, random bf16 features, random-init weights)",
+            "config": {"model": f"Qwen3-8B-shaped DSpark draft, {args.layers} layer(s), {args.target_layers} captured layers, vocab {cfg.vocab_size}",
+                       "global_batch": args.accum * world, "seq_len": args.max_len,
+                       "doc_lengths": f"log-uniform [{args.min_len},{args.max_len}]",
+                       "parallelism": f"dp{world}", "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,
+                       "block_size": model.block_size,
+                       "l2_policy": "inputs larger than L2 (1.2 GB lm_head + per-document features stream from HBM every micro-batch)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours",
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    from baseline import reference_arm
+    reference_arm.main(args)
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)
