@@ -607,3 +607,59 @@ extern "C" int ab_attn_bwd(const void* q, const void* k, const void* v, const in
   attn_bwd_dkv_kernel<<<dim3(n_ktiles, hkv), kThreads, kDkvSmem, stream>>>(maps, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that cannot allocate (see aspec_b200_noalloc.h for who they are and why).
+// The scratch that ab_attn_bwd takes from its caller lives here instead, in module memory.
+#include "aspec_b200_noalloc.h"
+
+#include <mutex>
+
+namespace {
+
+// delta [hq * q_total] fp32 first, then the per-query-tile key ranges [tiles, 4] int32.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[AB_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};   // device address of the block, per GPU
+std::mutex g_noalloc_mutex;
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address; the
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device
+// current.
+unsigned char* noalloc_scratch_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) return nullptr;
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(ptr);
+  }
+  return g_noalloc_ptr[dev];
+}
+
+}  // namespace
+
+extern "C" int ab_attn_bwd_static_scratch(const void* q, const void* k, const void* v,
+                                          const int* intervals, const void* out, const float* lse,
+                                          const void* dout, void* dq, void* dk, void* dv, int q_total,
+                                          int tk, int hq, int hkv, int head_dim, long long k_ld,
+                                          long long v_ld, float scale, int* status, void* stream) {
+  if (q_total <= 0 || tk <= 0) return 0;
+  if (hq <= 0 || hkv <= 0 || hq % hkv) return -10;
+  const int group = hq / hkv;
+  if (group > 16 || (128 % group)) return -11;
+  const int positions_per_tile = 128 / group;
+  const long long tiles = ((long long)q_total + positions_per_tile - 1) / positions_per_tile;
+  if ((long long)hq * q_total > AB_NOALLOC_MAX_ROW_STATS || tiles > AB_NOALLOC_MAX_QUERY_TILES)
+    return AB_NOALLOC_TOO_LARGE;   // larger than the built-in scratch block: nothing is launched
+  unsigned char* base = noalloc_scratch_for_current_device();
+  if (!base) return AB_NOALLOC_SETUP_FAILED;
+  float* delta = reinterpret_cast<float*>(base);
+  int* ranges = reinterpret_cast<int*>(base + (size_t)AB_NOALLOC_MAX_ROW_STATS * 4);
+  // Every word of delta / ranges that the two main kernels read is written by the preparation
+  // kernel of this same call, so stale contents from an earlier call are never observed.
+  return ab_attn_bwd(q, k, v, intervals, out, lse, dout, delta, ranges, dq, dk, dv, q_total, tk, hq, hkv,
+                     head_dim, k_ld, v_ld, scale, status, stream);
+}
