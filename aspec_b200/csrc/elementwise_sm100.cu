@@ -222,8 +222,14 @@ __global__ void qk_norm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
     }
   }
   if (w && dw) {
+    // combine the block's warps in shared memory first: one atomic per column per CTA
+    __shared__ float red[D];
+    for (int i = threadIdx.x; i < D; i += blockDim.x) red[i] = 0.f;
+    __syncthreads();
 #pragma unroll
-    for (int e = 0; e < E; ++e) atomicAdd(dw + lane * E + e, acc[e]);
+    for (int e = 0; e < E; ++e) atomicAdd(&red[lane * E + e], acc[e]);
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(dw + i, red[i]);
   }
 }
 
@@ -528,7 +534,7 @@ int ab_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rs
   int block = 256;
   while (8 * 4 * block < H && block < 1024) block <<= 1;
   if (8 * 4 * block < H) return -11;
-  const int grid = rows < 148 * 4 ? rows : 148 * 4;
+  const int grid = rows < 148 ? rows : 148;   // persistent: one dw flush (H atomics) per CTA
   rmsnorm_bwd_kernel<<<grid, block, 0, STREAM>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                  (const __nv_bfloat16*)w, rstd, (__nv_bfloat16*)dx,
                                                  dw, rows, H);
@@ -557,7 +563,7 @@ int ab_qk_norm_rope_bwd(const void* dy, const void* x, const void* w, const int*
                         int H, int D, float scaling, void* stream) {
   const long long rows = N * H;
   if (rows <= 0) return 0;
-  const int grid = grid_for(rows, 8, 148 * 4);
+  const int grid = grid_for(rows, 8, 148 * 2);
 #define QKB(DD)                                                                                    \
   qk_norm_rope_bwd_kernel<DD><<<grid, 256, 0, STREAM>>>(                                           \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, pos, inv_freq,   \

@@ -58,6 +58,11 @@ struct GemmParams {
   float* stats;
   float logit_scale;    // logits = acc * logit_scale (applied before stats/store)
   int* status;
+  // Stream-K: every CTA takes an equal, contiguous share of the (tile, k-block) space.  A tile whose
+  // k-range is split over CTAs is combined with fp32 atomic adds (D is fp32 and either zeroed by the
+  // caller or equal to C, the in-place accumulate case).
+  int stream_k;
+  long long units_per_cta;
 };
 
 struct alignas(64) GemmMaps {
@@ -70,6 +75,34 @@ struct alignas(64) GemmMaps {
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int& mt, int& nt) {
   nt = tile / m_tiles;
   mt = tile - nt * m_tiles;
+}
+
+// Work iterator shared by the three warp roles.  Data-parallel: whole tiles, strided by the grid.
+// Stream-K: contiguous units [cta * units_per_cta, (cta + 1) * units_per_cta) cut at tile borders.
+__device__ __forceinline__ long long work_begin(const GemmParams& p) {
+  return p.stream_k ? (long long)blockIdx.x * p.units_per_cta : (long long)blockIdx.x;
+}
+__device__ __forceinline__ bool next_work(const GemmParams& p, int total_tiles, int k_blocks,
+                                          long long& cursor, int& tile, int& kb0, int& kb1) {
+  if (!p.stream_k) {
+    if (cursor >= total_tiles) return false;
+    tile = (int)cursor;
+    kb0 = 0;
+    kb1 = k_blocks;
+    cursor += gridDim.x;
+    return true;
+  }
+  long long end = ((long long)blockIdx.x + 1) * p.units_per_cta;
+  const long long total = (long long)total_tiles * k_blocks;
+  if (end > total) end = total;
+  if (cursor >= end) return false;
+  tile = (int)(cursor / k_blocks);
+  kb0 = (int)(cursor - (long long)tile * k_blocks);
+  long long seg_end = ((long long)tile + 1) * k_blocks;
+  if (seg_end > end) seg_end = end;
+  kb1 = kb0 + (int)(seg_end - cursor);
+  cursor = seg_end;
+  return true;
 }
 
 template <int A_MN, int B_MN, int EPI>
@@ -121,10 +154,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      long long cursor = work_begin(p);
+      int tile, kb0, kb1;
+      while (alive && next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
         int mt, nt;
         tile_coords(tile, p.m_tiles, mt, nt);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word)) { alive = false; break; }
           const bool second = kb >= p.k_blocks0;
           const CUtensorMap* ma = second ? &maps.a1 : &maps.a0;
@@ -161,11 +196,13 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      long long cursor = work_begin(p);
+      int tile, kb0, kb1;
+      while (alive && next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_word)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_word)) { alive = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * kStageBytes);
@@ -178,7 +215,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                                      : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
                                      : make_smem_desc(sb + k * 32, 16, 1024);
-            tc_mma_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_ss(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);  // frees the smem stage when the MMAs retire
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -192,9 +229,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+    long long cursor = work_begin(p);
+    int tile, kb0, kb1;
+    while (next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
       int mt, nt;
       tile_coords(tile, p.m_tiles, mt, nt);
+      const bool partial = p.stream_k && !(kb0 == 0 && kb1 == k_blocks);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_word)) break;
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
@@ -297,7 +337,20 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
           tmem_ld_32x32(t_row + c, r);
           tmem_ld_wait();
           const int ncol = p.N - (col0 + c);
-          if (row_ok && ncol > 0) {
+          if (row_ok && ncol > 0 && partial) {
+            // part of a split tile: combine in fp32 with vector reductions
+            float* drow = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0 + c;
+            if (ncol >= 32 && (p.ldd & 3) == 0) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(drow + 4 * i),
+                             "f"(__uint_as_float(r[4 * i]) * alpha), "f"(__uint_as_float(r[4 * i + 1]) * alpha),
+                             "f"(__uint_as_float(r[4 * i + 2]) * alpha), "f"(__uint_as_float(r[4 * i + 3]) * alpha)
+                             : "memory");
+            } else {
+              for (int i = 0; i < 32 && i < ncol; ++i) atomicAdd(drow + i, __uint_as_float(r[i]) * alpha);
+            }
+          } else if (row_ok && ncol > 0) {
             if (p.d_is_fp32) {
               float* drow = reinterpret_cast<float*>(p.D) + (long long)row * p.ldd + col0 + c;
               const float* crow =
@@ -444,7 +497,13 @@ static int launch(const GemmMaps& maps, const GemmParams& p, int max_ctas, cudaS
   int cap = max_ctas > 0 ? max_ctas : num_sms();
   if (grid > cap) grid = cap;
   if (grid <= 0) return 0;
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(maps, p);
+  GemmParams q = p;
+  if (q.stream_k) {
+    const long long total = (long long)p.m_tiles * p.n_tiles * (p.k_blocks0 + p.k_blocks1);
+    grid = total < cap ? (int)total : cap;
+    q.units_per_cta = (total + grid - 1) / grid;
+  }
+  kern<<<grid, kThreads, kSmemBytes, stream>>>(maps, q);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -468,7 +527,7 @@ extern "C" {
 int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOperand* b0,
                  const AbOperand* a1, const AbOperand* b1, void* D, long long ldd, int d_is_fp32,
                  const void* C, float alpha, int epi, float* stats, float logit_scale, int* status,
-                 int max_ctas, void* stream) {
+                 int max_ctas, int stream_k, void* stream) {
   using namespace ab;
   if (M <= 0 || N <= 0 || K0 <= 0 || K1 < 0) return -10;
   if (K1 > 0 && (a1->mn_major != a0->mn_major || b1->mn_major != b0->mn_major)) return -11;
@@ -504,6 +563,13 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
   p.stats = stats;
   p.logit_scale = logit_scale;
   p.status = status;
+  p.stream_k = 0;
+  p.units_per_cta = 0;
+  if (stream_k) {
+    // split tiles are combined in fp32: D must be fp32 and either zero-filled or accumulated in place
+    if (epi != EPI_STORE || !d_is_fp32 || (C != nullptr && C != D)) return -16;
+    p.stream_k = 1;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int amn = a0->mn_major, bmn = b0->mn_major;
 #define AB_DISPATCH(EPI)                                                         \

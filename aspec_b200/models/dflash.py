@@ -48,6 +48,9 @@ class BlockLayout:
         self.row, self.anchor, self.slot = row, anchor, slot      # [n] int64 each
         self.n_rows, self.seq_len, self.n_slots = n_rows, seq_len, n_slots
         self.n = int(row.shape[0])
+        # [lo, hi) over the flattened context of every position a kept block touches (anchor .. anchor +
+        # block_size); known without a device round trip when the anchors came from the host
+        self.host_span = None
 
     @property
     def flat_anchor(self) -> torch.Tensor:
@@ -148,16 +151,26 @@ class DFlashModel(nn.Module):
 
     @staticmethod
     def _layout(anchors: torch.Tensor, keep: torch.Tensor, seq_len: int, device, compact: bool) -> BlockLayout:
+        """Kept blocks in packed order.  With a host-side keep mask the compaction runs on the host and
+        one small pinned table is copied asynchronously: no device synchronisation."""
         B, S = anchors.shape
+        if not keep.is_cuda and torch.device(device).type == "cuda":
+            idx = keep.reshape(-1).nonzero(as_tuple=False).squeeze(-1) if compact else torch.arange(B * S)
+            table = torch.stack([idx // S, anchors.cpu().reshape(-1)[idx].long(), idx % S])
+            span = None
+            if idx.numel():
+                flat = table[0] * seq_len + table[1]
+                span = (int(flat.min()), int(flat.max()))
+            table = table.pin_memory().to(device, non_blocking=True)
+            layout = BlockLayout(table[0], table[1], table[2], B, seq_len, S)
+            layout.host_span = span
+            return layout
         if compact:
-            idx = keep.reshape(-1).nonzero(as_tuple=False).squeeze(-1)   # host op when keep is on CPU
+            idx = keep.reshape(-1).nonzero(as_tuple=False).squeeze(-1)
         else:
             idx = torch.arange(B * S, device=keep.device)
         idx = idx.to(device)
-        row = idx // S
-        slot = idx % S
-        anchor = anchors.to(device).reshape(-1)[idx]
-        return BlockLayout(row, anchor, slot, B, seq_len, S)
+        return BlockLayout(idx // S, anchors.to(device).reshape(-1)[idx], idx % S, B, seq_len, S)
 
     # ---------------------------------------------------------------- backbone --
     def _doc_start(self, layout: BlockLayout, ctx_doc_ids, base_position_ids):
@@ -193,7 +206,12 @@ class DFlashModel(nn.Module):
         self._step_counter += 1
         layout = self._layout(anchors, keep, T, dev, compact)
         n = layout.n
-        keep_flat = keep.to(dev).reshape(-1)[layout.row * layout.n_slots + layout.slot]
+        if not keep.is_cuda and dev.type == "cuda":
+            # host-side compaction kept exactly the blocks whose flag is set
+            keep_flat = torch.ones(n, dtype=torch.bool, device=dev) if compact else \
+                keep.pin_memory().to(dev, non_blocking=True).reshape(-1)
+        else:
+            keep_flat = keep.to(dev).reshape(-1)[layout.row * layout.n_slots + layout.slot]
 
         wdtype = self.draft_model.context_proj.weight.dtype
         ctx = self.draft_model.extract_context_feature(hidden_states.reshape(B * T, -1).to(wdtype))
@@ -273,7 +291,7 @@ class DFlashModel(nn.Module):
             return torch.exp(-(k - self.prediction_start).clamp_min(0).float() / self.loss_decay_gamma)
         return torch.ones(self.block_size, device=device)
 
-    def _teacher_rows(self, last_hidden_states, flat_index):
+    def _teacher_rows(self, last_hidden_states, flat_index, layout=None):
         """Teacher hidden rows for ``flat_index`` (positions in the flattened ``[B*T]`` context).
 
         Returns ``(teacher_hidden, t_index)``: the whole context with an index table when that is
@@ -282,6 +300,12 @@ class DFlashModel(nn.Module):
         flat = last_hidden_states.reshape(-1, last_hidden_states.shape[-1]).to(self.draft_model.context_proj.weight.dtype)
         if self.context_parallel is not None and self.context_parallel.size > 1:
             return self.context_parallel.gather_teacher_rows(flat, flat_index), None
+        if layout is not None and layout.host_span is not None:
+            # only the context rows between the first anchor and the last block end can be a teacher row
+            lo = max(layout.host_span[0] - 1, 0)
+            hi = min(layout.host_span[1] + self.block_size + 1, flat.shape[0])
+            if hi - lo <= flat_index.numel():
+                return flat[lo:hi], (flat_index - lo).to(torch.int32)
         if flat.shape[0] <= flat_index.numel():
             return flat, flat_index.to(torch.int32)
         return flat[flat_index], None
@@ -325,7 +349,7 @@ class DFlashModel(nn.Module):
             if last_hidden_states is None:
                 raise ValueError("DFlash L1 distillation (l1_loss_alpha > 0) requires target last_hidden_states")
             teacher_hidden, t_index = self._teacher_rows(
-                last_hidden_states, (layout.row[:, None] * T + (safe - 1).clamp(min=0)).reshape(-1))
+                last_hidden_states, (layout.row[:, None] * T + (safe - 1).clamp(min=0)).reshape(-1), layout)
 
         if self.loss_objective == "decay":
             obj_w = binary * decay

@@ -102,7 +102,7 @@ class DSparkModel(DFlashModel):
                 raise ValueError("DSpark L1/confidence losses require target last_hidden_states; set "
                                  "inference.store_last_hidden_states=true in the run config.")
             t_flat = (layout.row[:, None] * T + (safe - 1).clamp(min=0)).reshape(-1)
-            teacher_hidden, t_index = self._teacher_rows(last_hidden_states, t_flat)
+            teacher_hidden, t_index = self._teacher_rows(last_hidden_states, t_flat, layout)
 
         markov = self.draft_model.markov_head
         prev_emb = markov.get_prev_embeddings(prev_ids.reshape(-1)).to(hidden.dtype) if markov is not None else None

@@ -16,6 +16,7 @@ The reference routes all of these through cuBLAS via ``nn.Linear``
 from __future__ import annotations
 
 import ctypes
+import math
 from typing import Optional
 
 import torch
@@ -24,6 +25,15 @@ from aspec_b200 import _native
 
 EPI_STORE, EPI_ROWSTATS, EPI_SWIGLU = 0, 1, 2
 TILE_N = 256
+
+
+NUM_SMS = 148
+
+
+def _wave_efficiency(M: int, N: int) -> float:
+    tiles = -(-M // 128) * -(-N // TILE_N)
+    waves = tiles / NUM_SMS
+    return waves / math.ceil(waves)
 
 
 class _Operand(ctypes.Structure):
@@ -61,8 +71,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          addend: Optional[torch.Tensor] = None, alpha: float = 1.0,
          epilogue: int = EPI_STORE, stats: Optional[torch.Tensor] = None,
-         logit_scale: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
-    """``alpha * (A @ B^T [+ A2 @ B2^T]) [+ addend]`` with a fused epilogue."""
+         logit_scale: float = 1.0, max_ctas: int = 0, stream_k: Optional[bool] = None) -> torch.Tensor:
+    """``alpha * (A @ B^T [+ A2 @ B2^T]) [+ addend]`` with a fused epilogue.
+
+    ``stream_k=None`` picks the schedule: when whole output tiles would leave more than ~12 % of the last
+    wave of CTAs idle (for example 448 tiles on 148 SMs), the (tile, k-block) space is divided evenly
+    over the CTAs instead and split tiles are combined with fp32 reductions.  A bf16 result then goes
+    through an fp32 workspace and one cast pass.
+    """
     M = a.shape[1] if a_t else a.shape[0]
     K = a.shape[0] if a_t else a.shape[1]
     N = b.shape[1] if b_t else b.shape[0]
@@ -73,6 +89,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     if a2 is not None:
         K2 = a2.shape[0] if a_t else a2.shape[1]
     n_out = N // 2 if epilogue == EPI_SWIGLU else N
+    inplace_acc = addend is not None and out is not None and addend.data_ptr() == out.data_ptr()
+    if stream_k is None:
+        stream_k = (epilogue == EPI_STORE and (addend is None or inplace_acc)
+                    and _wave_efficiency(M, N) < 0.88 and (K + K2) >= 1024)
+    workspace_for = None
+    if stream_k:
+        if epilogue != EPI_STORE or not (addend is None or inplace_acc):
+            raise ValueError("stream-K needs the plain store epilogue without a separate addend")
+        want_dtype = out.dtype if out is not None else out_dtype
+        if want_dtype != torch.float32:
+            workspace_for = out if out is not None else True
+            out = torch.zeros((M, N), dtype=torch.float32, device=a.device)
+        elif out is None:
+            out = torch.zeros((M, N), dtype=torch.float32, device=a.device)
+        elif not inplace_acc:
+            out.zero_()
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
     if out.stride(1) != 1:
@@ -93,8 +125,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         ctypes.c_float(alpha), ctypes.c_int(epilogue),
         ctypes.c_void_p(stats.data_ptr() if stats is not None else 0),
         ctypes.c_float(logit_scale), ctypes.c_void_p(st.data_ptr()),
-        ctypes.c_int(max_ctas),
+        ctypes.c_int(max_ctas), ctypes.c_int(1 if stream_k else 0),
         ctypes.c_void_p(torch.cuda.current_stream(a.device).cuda_stream))
     if rc != 0:
         raise RuntimeError(f"ab_gemm_bf16 refused the launch (code {rc}) for M={M} N={N} K={K}")
+    if workspace_for is not None:
+        from aspec_b200.ops import elementwise_sm100 as E
+        cast = E.cast_scale(out)
+        if workspace_for is True:
+            return cast
+        workspace_for.copy_(cast)
+        return workspace_for
     return out

@@ -29,6 +29,10 @@ _BATCH_TENSOR_KEYS = ("input_ids", "hidden_states", "loss_mask", "last_hidden_st
                       "injected_anchors", "injected_keep_mask")
 
 
+# anchors sampled by the data pipeline stay on the host: the block layout is compacted there
+_HOST_KEYS = ("injected_anchors", "injected_keep_mask")
+
+
 class DraftTrainer:
     def __init__(self, model: torch.nn.Module, lm_head_weight: torch.Tensor, *, lr: float = 6e-4,
                  min_lr: float = 6e-5, weight_decay: float = 0.0, max_grad_norm: float = 1.0,
@@ -56,7 +60,7 @@ class DraftTrainer:
         """Copy a host batch (ideally pinned) to the device; tensors already there pass through."""
         out = {}
         for k, v in batch.items():
-            if torch.is_tensor(v) and k in _BATCH_TENSOR_KEYS and k != "injected_keep_mask":
+            if torch.is_tensor(v) and k in _BATCH_TENSOR_KEYS and k not in _HOST_KEYS:
                 out[k] = v.to(self.device, non_blocking=True)
             else:
                 out[k] = v
@@ -65,7 +69,7 @@ class DraftTrainer:
     @staticmethod
     def h2d_bytes(batch: dict) -> int:
         return sum(v.numel() * v.element_size() for k, v in batch.items()
-                   if torch.is_tensor(v) and k in _BATCH_TENSOR_KEYS and not v.is_cuda and k != "injected_keep_mask")
+                   if torch.is_tensor(v) and k in _BATCH_TENSOR_KEYS and not v.is_cuda and k not in _HOST_KEYS)
 
     # -- one micro-batch ----------------------------------------------------------------
     def _forward_backward(self, batch: dict) -> None:

@@ -81,3 +81,22 @@ def test_gemm_swiglu():
     u = _ref(x, wu)
     ref = torch.nn.functional.silu(g) * u
     assert (out.float() - ref).abs().max().item() < 3e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(384, 512, 2048), (3584, 4096, 1536), (200, 300, 1000)])
+def test_gemm_stream_k(M, N, K):
+    from aspec_b200.ops import gemm as G
+    torch.manual_seed(5)
+    Kp = (K + 7) // 8 * 8
+    a = (torch.randn(M, Kp, device="cuda") * 0.2).bfloat16()[:, :K]
+    b = (torch.randn(N, Kp, device="cuda") * 0.2).bfloat16()[:, :K]
+    ref = _ref(a, b)
+    out32 = G.gemm(a, b, out_dtype=torch.float32, stream_k=True)
+    out16 = G.gemm(a, b, stream_k=True)
+    acc = torch.ones(M, N, device="cuda")
+    G.gemm(a, b, out=acc, addend=acc, out_dtype=torch.float32, stream_k=True)
+    G.check_status("cuda")
+    tol = 2e-2 * (K ** 0.5) * 0.1 + 1e-2
+    assert (out32 - ref).abs().max().item() < tol
+    assert (out16.float() - ref).abs().max().item() < tol + 0.05
+    assert (acc - 1 - ref).abs().max().item() < tol
