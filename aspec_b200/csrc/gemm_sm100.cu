@@ -62,6 +62,7 @@ struct GemmParams {
   // k-range is split over CTAs is combined with fp32 atomic adds (D is fp32 and either zeroed by the
   // caller or equal to C, the in-place accumulate case).
   int stream_k;
+  int full_tiles;
   long long units_per_cta;
 };
 
@@ -77,31 +78,48 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int& mt, int&
   mt = tile - nt * m_tiles;
 }
 
-// Work iterator shared by the three warp roles.  Data-parallel: whole tiles, strided by the grid.
-// Stream-K: contiguous units [cta * units_per_cta, (cta + 1) * units_per_cta) cut at tile borders.
-__device__ __forceinline__ long long work_begin(const GemmParams& p) {
-  return p.stream_k ? (long long)blockIdx.x * p.units_per_cta : (long long)blockIdx.x;
+// Work iterator shared by the three warp roles.
+// Phase 1 (always): whole tiles, strided by the grid, for the `full_tiles` tiles that fill complete
+// waves.  Concurrent CTAs then walk the reduction dimension in step, so the A / B k-slabs they share
+// are fetched from HBM once and served from L2.
+// Phase 2 (stream-K only): the tiles of the last, partial wave are cut along K into equal contiguous
+// shares, one per CTA; those split tiles are combined with fp32 reductions.
+struct Work {
+  long long cur;
+  int in_tail;
+};
+__device__ __forceinline__ Work work_begin(const GemmParams& p) {
+  Work w;
+  w.cur = blockIdx.x;
+  w.in_tail = 0;
+  return w;
 }
-__device__ __forceinline__ bool next_work(const GemmParams& p, int total_tiles, int k_blocks,
-                                          long long& cursor, int& tile, int& kb0, int& kb1) {
-  if (!p.stream_k) {
-    if (cursor >= total_tiles) return false;
-    tile = (int)cursor;
-    kb0 = 0;
-    kb1 = k_blocks;
-    cursor += gridDim.x;
-    return true;
+__device__ __forceinline__ bool next_work(const GemmParams& p, int total_tiles, int k_blocks, Work& w,
+                                          int& tile, int& kb0, int& kb1) {
+  const int full_tiles = p.stream_k ? p.full_tiles : total_tiles;
+  if (!w.in_tail) {
+    if (w.cur < full_tiles) {
+      tile = (int)w.cur;
+      kb0 = 0;
+      kb1 = k_blocks;
+      w.cur += gridDim.x;
+      return true;
+    }
+    if (!p.stream_k) return false;
+    w.in_tail = 1;
+    w.cur = (long long)blockIdx.x * p.units_per_cta;
   }
   long long end = ((long long)blockIdx.x + 1) * p.units_per_cta;
-  const long long total = (long long)total_tiles * k_blocks;
+  const long long total = (long long)(total_tiles - full_tiles) * k_blocks;
   if (end > total) end = total;
-  if (cursor >= end) return false;
-  tile = (int)(cursor / k_blocks);
-  kb0 = (int)(cursor - (long long)tile * k_blocks);
-  long long seg_end = ((long long)tile + 1) * k_blocks;
+  if (w.cur >= end) return false;
+  const int t = (int)(w.cur / k_blocks);
+  tile = full_tiles + t;
+  kb0 = (int)(w.cur - (long long)t * k_blocks);
+  long long seg_end = ((long long)t + 1) * k_blocks;
   if (seg_end > end) seg_end = end;
-  kb1 = kb0 + (int)(seg_end - cursor);
-  cursor = seg_end;
+  kb1 = kb0 + (int)(seg_end - w.cur);
+  w.cur = seg_end;
   return true;
 }
 
@@ -154,7 +172,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      long long cursor = work_begin(p);
+      Work cursor = work_begin(p);
       int tile, kb0, kb1;
       while (alive && next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
         int mt, nt;
@@ -196,7 +214,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      long long cursor = work_begin(p);
+      Work cursor = work_begin(p);
       int tile, kb0, kb1;
       while (alive && next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_word)) break;
@@ -229,7 +247,7 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    long long cursor = work_begin(p);
+    Work cursor = work_begin(p);
     int tile, kb0, kb1;
     while (next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
       int mt, nt;
@@ -499,9 +517,14 @@ static int launch(const GemmMaps& maps, const GemmParams& p, int max_ctas, cudaS
   if (grid <= 0) return 0;
   GemmParams q = p;
   if (q.stream_k) {
-    const long long total = (long long)p.m_tiles * p.n_tiles * (p.k_blocks0 + p.k_blocks1);
-    grid = total < cap ? (int)total : cap;
-    q.units_per_cta = (total + grid - 1) / grid;
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int kb = p.k_blocks0 + p.k_blocks1;
+    grid = cap;
+    if ((long long)tiles * kb < grid) grid = (int)((long long)tiles * kb);
+    q.full_tiles = (tiles / grid) * grid;
+    const long long tail_units = (long long)(tiles - q.full_tiles) * kb;
+    q.units_per_cta = (tail_units + grid - 1) / grid;
+    if (tail_units == 0) q.stream_k = 0;
   }
   kern<<<grid, kThreads, kSmemBytes, stream>>>(maps, q);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -564,6 +587,7 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
   p.logit_scale = logit_scale;
   p.status = status;
   p.stream_k = 0;
+  p.full_tiles = 0;
   p.units_per_cta = 0;
   if (stream_k) {
     // split tiles are combined in fp32: D must be fp32 and either zero-filled or accumulated in place

@@ -91,8 +91,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     n_out = N // 2 if epilogue == EPI_SWIGLU else N
     inplace_acc = addend is not None and out is not None and addend.data_ptr() == out.data_ptr()
     if stream_k is None:
+        tiles = -(-M // 128) * -(-N // TILE_N)
         stream_k = (epilogue == EPI_STORE and (addend is None or inplace_acc)
-                    and _wave_efficiency(M, N) < 0.88 and (K + K2) >= 1024)
+                    and ((_wave_efficiency(M, N) < 0.88 and (K + K2) >= 8192)
+                         or (tiles < NUM_SMS // 2 and (K + K2) >= 16384)))
     workspace_for = None
     if stream_k:
         if epilogue != EPI_STORE or not (addend is None or inplace_acc):
