@@ -1,0 +1,113 @@
+"""Native Draft assets: validation, strict loading, and proposal-time consumers.
+
+``validate_native_asset`` re-hashes ``config.json`` and ``model.safetensors`` against
+``export_manifest.json`` and re-derives the algorithm before anything is allocated;
+``load_native_draft`` loads strictly (no dropped indexer / head tensors).  ``BlockDraftConsumer``
+proposes one block from a known prefix: the backbone runs once with a single anchor at the last token;
+DFlash returns the argmax of slots ``1..bs-1``; DSpark decodes the block sequentially through the Markov
+head only and also returns confidence logits.  Verification and acceptance belong to the caller
+(reference: aspec/draft_artifact.py:58-286).
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from aspec_b200.commands.convert_to_hf import SCHEMA, sha256_file
+from aspec_b200.config.draft_config import AutoDraftModelConfig, resolve_draft_algorithm
+from aspec_b200.models.draft.auto import AutoEagle3DraftModel
+
+
+def validate_native_asset(asset_dir) -> dict:
+    asset_dir = Path(asset_dir)
+    manifest = json.loads((asset_dir / "export_manifest.json").read_text())
+    if manifest.get("schema_version") != SCHEMA or manifest.get("storage_format") != "aspec_native":
+        raise ValueError("not a native aspec asset (schema or storage format mismatch)")
+    if sha256_file(asset_dir / "config.json") != manifest["config_sha256"]:
+        raise ValueError("config.json does not match the export manifest")
+    if sha256_file(asset_dir / "model.safetensors") != manifest["model_sha256"]:
+        raise ValueError("model.safetensors does not match the export manifest")
+    raw = json.loads((asset_dir / "config.json").read_text())
+    if resolve_draft_algorithm(raw) != manifest["algorithm"]:
+        raise ValueError("asset algorithm disagrees with its config")
+    return manifest
+
+
+def load_native_draft(asset_dir, *, device="cpu", dtype: Optional[torch.dtype] = None):
+    """Returns ``(model, manifest)``; every tensor of the asset must be consumed and none may be missing."""
+    from safetensors.torch import load_file
+    asset_dir = Path(asset_dir)
+    manifest = validate_native_asset(asset_dir)
+    raw = json.loads((asset_dir / "config.json").read_text())
+    raw = {k: v for k, v in raw.items() if k not in ("_aspec_version", "torch_dtype")}
+    config = AutoDraftModelConfig.from_dict(raw)
+    tensors = load_file(str(asset_dir / "model.safetensors"))
+    if len(tensors) != manifest["tensor_count"]:
+        raise ValueError("asset tensor count disagrees with its manifest")
+    model = AutoEagle3DraftModel.from_config(config)
+    model.load_state_dict(tensors, strict=True)
+    if dtype is not None:
+        model = model.to(dtype)
+    return model.to(device).eval(), manifest
+
+
+class BlockDraftConsumer:
+    def __init__(self, draft_model, *, block_size: int):
+        from aspec_b200.models.dflash import DFlashModel
+        self.model = draft_model.eval()
+        if getattr(draft_model.config, "mtp_conditioning", None):
+            raise ValueError("MTP-conditioned assets require an MTP-aware proposal consumer")
+        self.algorithm = resolve_draft_algorithm(draft_model.config.to_dict())
+        if self.algorithm not in ("dspark", "dflash"):
+            raise ValueError("BlockDraftConsumer requires a DSpark or DFlash asset")
+        if type(block_size) is not int or block_size < 2:
+            raise ValueError("block_size must be an integer >= 2")
+        saved = getattr(draft_model.config, "block_size", None)
+        if saved is not None and saved != block_size:
+            raise ValueError("Proposal block size disagrees with the trained asset")
+        self.block_size = block_size
+        self.backbone = DFlashModel(draft_model, block_size=block_size, num_anchors=1)
+
+    @torch.no_grad()
+    def propose(self, input_ids, target_features, *, lm_head_weight) -> dict:
+        if input_ids.ndim != 2 or input_ids.shape[0] != 1 or input_ids.shape[1] < 1:
+            raise ValueError("Block proposal currently consumes one nonempty prefix")
+        L = input_ids.shape[1]
+        cfg = self.model.config
+        if tuple(target_features.shape) != (1, L, cfg.target_hidden_size * cfg.num_target_layers):
+            raise ValueError("Target features must match the asset's ordered layers and prefix")
+        if tuple(lm_head_weight.shape) != (cfg.vocab_size, cfg.hidden_size):
+            raise ValueError("Frozen Target output head shape does not match the Draft")
+        if L + self.block_size - 1 > cfg.max_position_embeddings:
+            raise ValueError("Proposal exceeds the artifact's supported position range")
+        dev = input_ids.device
+        anchor = torch.tensor([[L - 1]])
+        # the anchor is the last known token: its block sees the L-1 tokens before it
+        hidden, _, _ = self.backbone._draft_backbone(
+            input_ids, target_features, torch.ones(1, L, device=dev), injected_anchors=anchor,
+            injected_keep_mask=torch.ones_like(anchor, dtype=torch.bool))
+        if self.algorithm == "dflash":
+            return {"token_ids": F.linear(hidden[1:], lm_head_weight).argmax(-1)[None], "algorithm": "dflash"}
+        logits = F.linear(hidden, lm_head_weight)
+        prev = input_ids[:, -1]
+        markov, head = self.model.markov_head, self.model.confidence_head
+        tokens, conf = [], []
+        for j in range(self.block_size):
+            row = logits[j:j + 1]
+            if markov is not None:
+                row = row + markov.compute_step_bias(prev).to(row.dtype)
+            if head is not None:
+                feats = hidden[j:j + 1]
+                if self.model.confidence_head_with_markov:
+                    feats = torch.cat((feats, markov.get_prev_embeddings(prev).to(feats.dtype)), -1)
+                conf.append(head(feats))
+            prev = row.argmax(-1)
+            tokens.append(prev)
+        out = {"token_ids": torch.stack(tokens, 1), "algorithm": "dspark"}
+        if conf:
+            out["draft_confidence_logits"] = torch.stack(conf, 1)
+        return out
