@@ -1,0 +1,168 @@
+"""The driver's training loop: plan -> produce -> train -> commit -> log / evaluate / checkpoint.
+
+One optimizer step has a single wall-clock budget covering supply, transfer, compute and commit
+(``optimizer_step_timeout_seconds``); when it runs out the step fails with ``TrainerStepTimeoutError`` and
+the driver terminates the trainer processes instead of waiting on a native call
+(reference: aspec/controller/loop.py:154-220, 1329-2276).  Rows for step ``s + 1`` are submitted while the
+trainers work on step ``s`` (dispatch-ahead, bounded by the ring slots).
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+from typing import Callable, Dict, List, Optional
+
+from aspec_b200.runtime.actor import ActorError, ActorTimeout
+from aspec_b200.training import checkpoint as ckpt
+
+
+class TrainerStepTimeoutError(TimeoutError):
+    pass
+
+
+class ThroughputWindow:
+    """Steady-window accounting: starts when warm-up update W completes, ends at the last optimizer
+    completion, counts only tokens committed inside (reference: docs/benchmarks/methodology.md:29-36)."""
+
+    def __init__(self, warmup_steps: int = 0, drain_steps: int = 0):
+        self.warmup, self.drain = int(warmup_steps), int(drain_steps)
+        self.records: List[tuple] = []       # (completed_step_index, t_done, tokens)
+
+    def add(self, step_index: int, tokens: int) -> None:
+        self.records.append((step_index, time.perf_counter(), int(tokens)))
+
+    def summary(self) -> dict:
+        recs = self.records
+        if len(recs) <= self.warmup + self.drain:
+            return {"valid": False, "steps": len(recs)}
+        start = recs[self.warmup - 1][1] if self.warmup > 0 else None
+        body = recs[self.warmup: len(recs) - self.drain] if self.drain else recs[self.warmup:]
+        if start is None or not body:
+            return {"valid": False, "steps": len(recs)}
+        tokens = sum(r[2] for r in body)
+        seconds = body[-1][1] - start
+        return {"valid": seconds > 0, "steps": len(body), "tokens": tokens, "seconds": seconds,
+                "tokens_per_second": tokens / seconds if seconds > 0 else None}
+
+
+def training_loop(*, controller, manager, trainers, rings, train_queues, args: Dict, layer_ids, num_steps: int,
+                  start_step: int = 0, log: Callable[[dict], None] = print, evidence=None, timeline=None,
+                  consumer_of_rank: Optional[Callable[[int], List[int]]] = None) -> dict:
+    """Runs ``num_steps`` optimizer updates.  ``trainers[r]`` are actors; ``rings[c]`` the lease rings."""
+    accumulation = int(args.get("draft_accumulation_steps", 1))
+    budget = float(args.get("optimizer_step_timeout_seconds", 1800.0))
+    save_interval = int(args.get("save_interval", 0) or 0)
+    output_dir = args.get("output_dir") or ""
+    dp = controller.dp_size
+    consumer_of_rank = consumer_of_rank or (lambda r: [r])
+    window = ThroughputWindow(int(args.get("performance_warmup_steps", 0)), int(args.get("performance_drain_steps", 0)))
+    results_by_row: Dict[str, tuple] = {}
+    submitted_plans: Dict[int, list] = {}
+    history: List[dict] = []
+    rank_of_row: Dict[str, int] = {}
+
+    def on_result(out, req) -> None:
+        # engine finished a row: account for it, then hand one descriptor to each consumer's queue
+        from aspec_b200.utils.types import TrainSample
+        controller.register_result(out)
+        results_by_row[out.row_id] = (out, req)
+        for key, (consumer, _slot, _gen) in zip(out.feature_keys, req.leases):
+            train_queues[consumer].put(TrainSample(key, out.tensor_shapes, out.document_lengths, out.packed_loss_masks,
+                                                   out.metadata, out.data_ids, out.row_id))
+
+    manager.on_result = on_result
+
+    def submit(step: int) -> bool:
+        plan = controller.plan_update(accumulation)
+        if plan is None:
+            if int(args.get("num_epochs", 1)) > controller.epoch + 1:
+                controller.next_epoch()
+                plan = controller.plan_update(accumulation)
+            if plan is None:
+                return False
+        rows = []
+        for micro in plan:
+            for rank, idxs in enumerate(micro):
+                req = controller.row_request(idxs, layer_ids)
+                rows.append((rank, req))
+                manager.submit(req, consumer_of_rank(rank))
+        submitted_plans[step] = rows
+        return True
+
+    completed = 0
+    step = start_step
+    have_next = submit(step)
+    while have_next and completed < num_steps:
+        t_step = time.perf_counter()
+        deadline = t_step + budget
+        futures = [t.call_async("train_from_queue", step, accumulation, budget) for t in trainers]
+        # dispatch-ahead: the producers work on the next update while the trainers compute this one
+        have_next = (completed + 1 < num_steps) and submit(step + 1)
+        outs = []
+        for r, fut in enumerate(futures):
+            while True:
+                manager.raise_if_failed()
+                try:
+                    outs.append(fut.get(timeout=0.25))
+                    break
+                except ActorTimeout:
+                    if time.perf_counter() > deadline:
+                        for t in trainers:
+                            t.terminate()
+                        raise TrainerStepTimeoutError(
+                            f"optimizer step {step} exceeded its {budget:.0f}s budget; trainer processes were terminated")
+        # release leases, then commit the work of this optimizer step
+        committed: List[str] = []
+        for out in outs:
+            for consumer, slot, gen in out["releases"]:
+                rings[consumer].release_acknowledged(slot, gen, _owner(results_by_row, consumer, slot, gen))
+            committed.extend(out["committed"])
+        tokens = 0
+        for rank, req in submitted_plans.pop(step):
+            res = results_by_row.pop(req.row_id, None)
+            if res is None:
+                raise RuntimeError(f"row {req.row_id} was trained on but never reported by its engine")
+            controller.release_result(res[0], participant=f"trainer{rank}")
+            tokens += sum(req.document_lengths)
+        controller.commit_optimizer_step(step, committed)
+        completed += 1
+        window.add(completed, tokens)
+        metrics = dict(outs[0]["metrics"])
+        metrics["perf/step_wall_time"] = time.perf_counter() - t_step
+        metrics["perf/input_tokens"] = tokens
+        metrics["train/step"] = step
+        history.append(metrics)
+        log(metrics)
+        if timeline:
+            timeline.event("optimizer_step", step=step, tokens=tokens)
+        next_step_id = step + 1
+        if output_dir and save_interval and next_step_id % save_interval == 0:
+            save_checkpoint(trainers, controller, output_dir, next_step_id, args)
+        step += 1
+    if output_dir and args.get("save_final_checkpoint", True) and completed and not (
+            save_interval and step % save_interval == 0):
+        save_checkpoint(trainers, controller, output_dir, step, args)
+    summary = {"completed_steps": completed, "last_step": step - 1, "window": window.summary(),
+               "ledger": controller.ledger.status(), "dropped_tail_samples": controller.dropped_tail,
+               "history": history}
+    return summary
+
+
+def _owner(results_by_row, consumer, slot, gen) -> str:
+    for row_id, (out, req) in results_by_row.items():
+        if (consumer, slot, gen) in [tuple(l) for l in req.leases]:
+            return f"row:{row_id}"
+    return "row:unknown"
+
+
+def save_checkpoint(trainers, controller, output_dir: str, step_id: int, args: Dict) -> str:
+    """Two-phase: trainers stage their shards, then the driver publishes with the committed work state."""
+    for fut in [t.call_async("save_model", output_dir, step_id) for t in trainers]:
+        fut.get(timeout=float(args.get("checkpoint_timeout_seconds", 1800.0)))
+    final = ckpt.publish(output_dir=output_dir, step_id=step_id, work_state=controller.work_state(),
+                         world_size=len(trainers))
+    keep = int(args.get("max_checkpoints", 0) or 0)
+    if keep:
+        ckpt.rotate(output_dir, keep)
+    return final

@@ -61,6 +61,13 @@ struct GemmParams {
   // Stream-K: every CTA takes an equal, contiguous share of the (tile, k-block) space.  A tile whose
   // k-range is split over CTAs is combined with fp32 atomic adds (D is fp32 and either zeroed by the
   // caller or equal to C, the in-place accumulate case).
+  // Up to kMaxMirrors extra bf16 destinations that receive the same tile (EPI_STORE, bf16): the Target's
+  // captured-layer epilogue writes the residual stream to its own buffer and straight into the ring
+  // slots of the consuming Draft ranks (peer memory mapped into this process, plain st.global over
+  // NVLink).  mirror_ld is the row stride in elements.
+  void* mirror[4];
+  long long mirror_ld[4];
+  int n_mirrors;
   int stream_k;
   int full_tiles;
   long long units_per_cta;
@@ -420,12 +427,20 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                   o.z = pack_bf16x2(v[4], v[5]);
                   o.w = pack_bf16x2(v[6], v[7]);
                   reinterpret_cast<uint4*>(drow)[i] = o;
+                  for (int m = 0; m < p.n_mirrors; ++m) {
+                    __nv_bfloat16* mrow = reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) +
+                                          (long long)row * p.mirror_ld[m] + col0 + c;
+                    reinterpret_cast<uint4*>(mrow)[i] = o;
+                  }
                 }
               } else {
                 for (int i = 0; i < 32 && i < ncol; ++i) {
                   float v = __uint_as_float(r[i]) * alpha;
                   if (crow) v += __bfloat162float(crow[i]);
                   drow[i] = __float2bfloat16(v);
+                  for (int m = 0; m < p.n_mirrors; ++m)
+                    (reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) + (long long)row * p.mirror_ld[m] + col0 + c)[i] =
+                        __float2bfloat16(v);
                 }
               }
             }
@@ -550,7 +565,8 @@ extern "C" {
 int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOperand* b0,
                  const AbOperand* a1, const AbOperand* b1, void* D, long long ldd, int d_is_fp32,
                  const void* C, float alpha, int epi, float* stats, float logit_scale, int* status,
-                 int max_ctas, int stream_k, void* stream) {
+                 int max_ctas, int stream_k, int n_mirrors, void* const* mirrors, const long long* mirror_lds,
+                 void* stream) {
   using namespace ab;
   if (M <= 0 || N <= 0 || K0 <= 0 || K1 < 0) return -10;
   if (K1 > 0 && (a1->mn_major != a0->mn_major || b1->mn_major != b0->mn_major)) return -11;
@@ -586,6 +602,16 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
   p.stats = stats;
   p.logit_scale = logit_scale;
   p.status = status;
+  p.n_mirrors = 0;
+  if (n_mirrors > 0) {
+    if (n_mirrors > 4 || epi != EPI_STORE || d_is_fp32 || stream_k) return -17;
+    for (int m = 0; m < n_mirrors; ++m) {
+      if ((reinterpret_cast<uintptr_t>(mirrors[m]) & 15) || (mirror_lds[m] & 7) || (ldd & 7)) return -17;
+      p.mirror[m] = mirrors[m];
+      p.mirror_ld[m] = mirror_lds[m];
+    }
+    p.n_mirrors = n_mirrors;
+  }
   p.stream_k = 0;
   p.full_tiles = 0;
   p.units_per_cta = 0;

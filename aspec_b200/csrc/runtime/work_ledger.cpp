@@ -12,7 +12,6 @@
 #include <map>
 #include <mutex>
 #include <set>
-#include <sstream>
 #include <string>
 #include <vector>
 
@@ -281,24 +280,30 @@ const char* ab_ledger_status(void* h) {
   }
   const bool validated = L->errors.empty() && L->resident_outputs == 0 && L->resident_bytes == 0 && incomplete == 0 &&
                          contiguous && unique_commits;
-  std::ostringstream o;
-  o << "{\"records\":" << L->records.size() << ",\"states\":{";
+  std::string o;
+  auto num = [&](long long v) { o += std::to_string(v); };
+  o += "{\"records\":"; num((long long)L->records.size());
+  o += ",\"states\":{";
   bool c = false;
-  for (auto& kv : per_state) { o << (c ? "," : "") << "\"" << kv.first << "\":" << kv.second; c = true; }
-  o << "},\"resident_outputs\":" << L->resident_outputs << ",\"resident_bytes\":" << L->resident_bytes
-    << ",\"peak_resident_outputs\":" << L->peak_outputs << ",\"peak_resident_bytes\":" << L->peak_bytes
-    << ",\"committed_steps\":[";
+  for (auto& kv : per_state) { o += (c ? "," : ""); o += "\"" + kv.first + "\":"; num(kv.second); c = true; }
+  o += "},\"resident_outputs\":"; num(L->resident_outputs);
+  o += ",\"resident_bytes\":"; num(L->resident_bytes);
+  o += ",\"peak_resident_outputs\":"; num(L->peak_outputs);
+  o += ",\"peak_resident_bytes\":"; num(L->peak_bytes);
+  o += ",\"committed_steps\":[";
   c = false;
-  for (auto& kv : L->commits) { o << (c ? "," : "") << kv.first; c = true; }
-  o << "],\"committed_work_ids\":[";
+  for (auto& kv : L->commits) { o += (c ? "," : ""); num(kv.first); c = true; }
+  o += "],\"committed_work_ids\":[";
   c = false;
-  for (auto& w : committed_work) { o << (c ? "," : "") << "\"" << json_escape(w) << "\""; c = true; }
-  o << "],\"incomplete\":" << incomplete << ",\"contiguous_steps\":" << (contiguous ? "true" : "false")
-    << ",\"unique_committed_work\":" << (unique_commits ? "true" : "false") << ",\"errors\":[";
+  for (auto& w : committed_work) { o += (c ? "," : ""); o += "\"" + json_escape(w) + "\""; c = true; }
+  o += "],\"incomplete\":"; num(incomplete);
+  o += std::string(",\"contiguous_steps\":") + (contiguous ? "true" : "false");
+  o += std::string(",\"unique_committed_work\":") + (unique_commits ? "true" : "false");
+  o += ",\"errors\":[";
   c = false;
-  for (auto& e : L->errors) { o << (c ? "," : "") << "\"" << json_escape(e) << "\""; c = true; }
-  o << "],\"validated\":" << (validated ? "true" : "false") << "}";
-  L->scratch = o.str();
+  for (auto& e : L->errors) { o += (c ? "," : ""); o += "\"" + json_escape(e) + "\""; c = true; }
+  o += std::string("],\"validated\":") + (validated ? "true" : "false") + "}";
+  L->scratch = o;
   return L->scratch.c_str();
 }
 

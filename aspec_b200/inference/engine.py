@@ -1,0 +1,183 @@
+"""Target feature engines.
+
+``InferenceEngine`` is the contract the scheduler drives (reference: aspec/inference/engine/base.py:29-91):
+``init``, ``generate``, ``health_check``, ``shutdown``, ``get_status``.  Implementations:
+
+* ``NativeTargetEngine`` - runs the in-framework Target (``models.target.dense``) prefill-only on its GPU
+  and lets the captured-layer epilogues write into the consumers' ring slots (replaces the SGLang engine,
+  aspec/inference/engine/sgl_engine.py:155-1062, and its direct sink, aspec/inference/target_prefill.py);
+* ``SyntheticEngine`` - random features of the right shape (Draft-only runs, CPU tests);
+* ``OfflineReplayEngine`` - replays materialised features from an offline store
+  (aspec/inference/engine/offline_replay_engine.py:45-240).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from aspec_b200.transport.feature_ring import RemoteRing, RingFeatureSink, feature_bytes
+from aspec_b200.utils.types import InferenceOutput, RowRequest
+
+
+class InferenceEngine:
+    name = "engine"
+
+    def init(self) -> None:
+        raise NotImplementedError
+
+    def attach_rings(self, handles: Dict[int, dict]) -> None:
+        self.rings = {int(c): RemoteRing(h) for c, h in handles.items()}
+
+    def generate(self, requests: Sequence[RowRequest]) -> List[InferenceOutput]:
+        raise NotImplementedError
+
+    def health_check(self) -> bool:
+        return True
+
+    def get_status(self) -> dict:
+        return {"name": self.name, "rows": getattr(self, "rows_done", 0), "tokens": getattr(self, "tokens_done", 0),
+                "busy_seconds": getattr(self, "busy_seconds", 0.0)}
+
+    def shutdown(self) -> None:
+        pass
+
+    close = shutdown
+
+    # -- shared helpers ---------------------------------------------------------------------------
+    def _slot_views(self, req: RowRequest):
+        n = int(req.input_ids.shape[0])
+        views = []
+        for consumer, slot, _gen in req.leases:
+            views.append(self.rings[consumer].views(slot, n))
+        return views
+
+    def _finish(self, req: RowRequest, views, layer_ids, device_flags: bool) -> InferenceOutput:
+        n = int(req.input_ids.shape[0])
+        keys = []
+        for (consumer, slot, gen), v in zip(req.leases, views):
+            ring = self.rings[consumer]
+            v["input_ids"].copy_(req.input_ids, non_blocking=True)
+            if device_flags:
+                ring.publish(slot, gen)
+            keys.append(ring.descriptor(slot, gen, n, layer_ids).to_key())
+        lay = self.rings[req.leases[0][0]].layout
+        self.rows_done = getattr(self, "rows_done", 0) + 1
+        self.tokens_done = getattr(self, "tokens_done", 0) + n
+        return InferenceOutput(req.row_id, list(req.data_ids), keys,
+                               {"input_ids": (n,), "hidden_states": (n, lay.num_layers * lay.hidden),
+                                "last_hidden_states": (n, lay.hidden)},
+                               tuple(req.document_lengths), list(req.packed_loss_masks), list(req.metadata),
+                               feature_bytes(n, lay.num_layers, lay.hidden, lay.elem, lay.store_last_hidden), self.name)
+
+
+class NativeTargetEngine(InferenceEngine):
+    def __init__(self, target_config: dict, layer_ids: Sequence[int], device: str = "cuda:0", dtype: str = "bfloat16",
+                 seed: int = 0, name: str = "target0", device_flags: bool = False, weights_path: Optional[str] = None,
+                 fail_after: Optional[int] = None):
+        from aspec_b200.models.target.dense import DenseTarget, TargetConfig
+        self.name = name
+        self.device = torch.device(device)
+        self.layer_ids = tuple(layer_ids)
+        self.device_flags = device_flags
+        self.fail_after = fail_after            # fault injection on the host: raise after N rows
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        torch.manual_seed(seed)
+        self.model = DenseTarget(TargetConfig(**target_config)).to(device=self.device, dtype=getattr(torch, dtype))
+        if weights_path:
+            self.model.load_state_dict(torch.load(weights_path, map_location=self.device), strict=True)
+        else:
+            self.model.init_random(seed)
+        self.model.eval()
+        self.rings: Dict[int, RemoteRing] = {}
+        self.busy_seconds = 0.0
+
+    def init(self) -> None:
+        pass
+
+    def lm_head(self) -> torch.Tensor:
+        return self.model.lm_head.detach()
+
+    def embedding(self) -> torch.Tensor:
+        return self.model.embed_tokens.weight.detach()
+
+    @torch.no_grad()
+    def generate(self, requests: Sequence[RowRequest]) -> List[InferenceOutput]:
+        t0 = time.perf_counter()
+        outs = []
+        for req in requests:
+            if self.fail_after is not None and getattr(self, "rows_done", 0) >= self.fail_after:
+                raise RuntimeError(f"{self.name}: injected producer failure")
+            views = self._slot_views(req)
+            sink = RingFeatureSink(views, self.layer_ids, self.model.config.hidden_size)
+            ids = req.input_ids.to(self.device, non_blocking=True)
+            self.model.prefill(ids, req.document_lengths, self.layer_ids, sink=sink)
+            outs.append(self._finish(req, views, self.layer_ids, self.device_flags))
+        if self.device.type == "cuda" and not self.device_flags:
+            torch.cuda.current_stream(self.device).synchronize()     # host-ordered readiness
+        self.busy_seconds += time.perf_counter() - t0
+        return outs
+
+
+class SyntheticEngine(InferenceEngine):
+    """Random features; deterministic per document so that runs and resumes agree."""
+
+    def __init__(self, layer_ids: Sequence[int], hidden: int, device: str = "cpu", dtype: str = "float32",
+                 name: str = "synthetic0", seed: int = 0, delay_s: float = 0.0, fail_after: Optional[int] = None):
+        self.name, self.layer_ids, self.hidden = name, tuple(layer_ids), hidden
+        self.device, self.dtype, self.seed = torch.device(device), getattr(torch, dtype), seed
+        self.delay_s, self.fail_after = delay_s, fail_after
+        self.rings = {}
+
+    def init(self) -> None:
+        pass
+
+    def generate(self, requests):
+        outs = []
+        for req in requests:
+            if self.fail_after is not None and getattr(self, "rows_done", 0) >= self.fail_after:
+                raise RuntimeError(f"{self.name}: injected producer failure")
+            if self.delay_s:
+                time.sleep(self.delay_s)
+            views = self._slot_views(req)
+            n = int(req.input_ids.shape[0])
+            g = torch.Generator().manual_seed(self.seed * 7919 + int(req.input_ids.sum()) % (2 ** 31))
+            hs = torch.randn(n, len(self.layer_ids) * self.hidden, generator=g)
+            last = torch.randn(n, self.hidden, generator=g)
+            for v in views:
+                v["hidden_states"].copy_(hs.to(v["hidden_states"].dtype))
+                if "last_hidden_states" in v:
+                    v["last_hidden_states"].copy_(last.to(v["last_hidden_states"].dtype))
+            outs.append(self._finish(req, views, self.layer_ids, device_flags=True))
+        return outs
+
+
+class OfflineReplayEngine(InferenceEngine):
+    """Replays ``samples/*.pt`` of an offline feature store into ring slots."""
+
+    def __init__(self, feature_dir: str, name: str = "offline0"):
+        from aspec_b200.offline.dataset import OfflineFeatureStore
+        self.name = name
+        self.store = OfflineFeatureStore(feature_dir)
+        self.layer_ids = tuple(self.store.binding["feature_contract"]["layer_ids"])
+        self.rings = {}
+
+    def init(self) -> None:
+        pass
+
+    def generate(self, requests):
+        outs = []
+        for req in requests:
+            views = self._slot_views(req)
+            off = 0
+            for data_id, n in zip(req.data_ids, req.document_lengths):
+                rec = self.store.load(data_id)
+                for v in views:
+                    v["hidden_states"][off:off + n].copy_(rec["hidden_states"].reshape(n, -1))
+                    if "last_hidden_states" in v:
+                        v["last_hidden_states"][off:off + n].copy_(rec["last_hidden_states"].reshape(n, -1))
+                off += n
+            outs.append(self._finish(req, views, self.layer_ids, device_flags=True))
+        return outs

@@ -1,0 +1,58 @@
+"""Creates the engine actors for the configured backend and returns the frozen Target tensors the
+trainers borrow (output head, embedding).  (reference: aspec/inference/factory.py:44-722)"""
+from __future__ import annotations
+
+import json
+from typing import Dict, List
+
+import torch
+
+from aspec_b200.runtime.actor import ProcessActor
+
+
+def target_config_from_args(flat: Dict, draft_config: dict) -> dict:
+    path = flat.get("target_model_config")
+    if path:
+        raw = json.load(open(path)) if isinstance(path, str) else dict(path)
+        return raw.get("text_config", raw)
+    # default: a Target shaped like the Draft's binding
+    return {"hidden_size": draft_config.get("target_hidden_size", draft_config["hidden_size"]),
+            "intermediate_size": draft_config.get("intermediate_size", 4 * draft_config["hidden_size"]),
+            "num_hidden_layers": draft_config.get("target_num_hidden_layers", 36),
+            "num_attention_heads": draft_config["num_attention_heads"],
+            "num_key_value_heads": draft_config["num_key_value_heads"], "head_dim": draft_config.get("head_dim"),
+            "vocab_size": draft_config["vocab_size"], "rms_norm_eps": draft_config.get("rms_norm_eps", 1e-6),
+            "rope_theta": draft_config.get("rope_theta", 1e6)}
+
+
+def create_engines(flat: Dict, draft_config: dict, layer_ids: List[int], target_devices: List[str],
+                   ring_handles: Dict[int, dict]):
+    kind = flat["inference_engine_type"]
+    hidden = int(draft_config.get("target_hidden_size", draft_config["hidden_size"]))
+    fault = flat.get("producer_fail_after")
+    if kind == "native":
+        from aspec_b200.inference.engine import NativeTargetEngine
+        tcfg = target_config_from_args(flat, draft_config)
+        engines = [ProcessActor(NativeTargetEngine, tcfg, layer_ids, dev, "bfloat16" if dev.startswith("cuda") else "float32",
+                                int(flat.get("seed", 0)), f"target{i}", bool(flat.get("device_flags", False)),
+                                flat.get("target_weights_path"), fault, name=f"target{i}")
+                   for i, dev in enumerate(target_devices)]
+        for e in engines:
+            e.wait_ready()
+            e.call("attach_rings", ring_handles, timeout=300)
+        head = engines[0].call("lm_head", timeout=300)
+        embedding = engines[0].call("embedding", timeout=300)
+        return engines, head, embedding
+    if kind == "synthetic":
+        from aspec_b200.inference.engine import SyntheticEngine
+        dev = next(iter(ring_handles.values()))["buffer"].device
+        eng = SyntheticEngine(layer_ids, hidden, str(dev), seed=int(flat.get("seed", 0)),
+                              delay_s=float(flat.get("producer_delay_seconds", 0.0)), fail_after=fault)
+        eng.attach_rings(ring_handles)
+        return [eng], None, None
+    if kind == "offline":
+        from aspec_b200.inference.engine import OfflineReplayEngine
+        eng = OfflineReplayEngine(flat["offline_feature_dir"])
+        eng.attach_rings(ring_handles)
+        return [eng], None, None
+    raise ValueError(f"unknown inference engine type {kind!r}")

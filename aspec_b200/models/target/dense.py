@@ -1,0 +1,263 @@
+"""In-framework Target: a frozen decoder-only LLM run prefill-only to produce Draft features.
+
+The reference delegates the Target to SGLang and patches its models to capture hidden states
+(aspec/inference/sglang_v0521.py:87-470, compat/patches/sglang-v0.5.21.patch:389-424); its semantic
+reference is the hook-based HF wrapper aspec/models/target/eagle3_target_model.py:120-268.  Feature
+contract reproduced here: for captured layer id ``k`` the feature is the residual-stream value *after*
+decoder layer ``k`` (``hidden + residual`` as it enters layer ``k + 1``); ``last_hidden_states`` is the
+post-final-norm hidden state; layout ``hidden_states [T, K * Dt]``.
+
+Execution is packed (THD): one flat token array plus document lengths, causal attention restricted
+to each document through the interval flash-attention kernel.  On CUDA every matrix product runs on
+the framework's tcgen05 GEMM: q/k/v are one GEMM, gate/up one GEMM whose epilogue applies SwiGLU, and
+the o_proj / down_proj GEMMs add the residual in their epilogue.  For a captured layer that epilogue
+also writes the tile into the feature sink - which may be memory of the Draft GPUs (see
+``transport.feature_ring``): capture costs no extra pass and no copy.
+"""
+from __future__ import annotations
+
+import json
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from aspec_b200.ops.attention import interval_attention_reference
+from aspec_b200.ops.norm import rmsnorm_reference
+from aspec_b200.ops.rope import qk_norm_rope_reference
+
+
+@dataclass
+class TargetConfig:
+    model_type: str = "qwen3"                 # qwen3 (q/k norm) | llama | ling_moe
+    hidden_size: int = 4096
+    intermediate_size: int = 12288
+    num_hidden_layers: int = 36
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: Optional[int] = None
+    vocab_size: int = 151936
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    max_position_embeddings: int = 40960
+    qk_norm: Optional[bool] = None
+    tie_word_embeddings: bool = False
+    # MoE (ling_moe)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    num_shared_experts: int = 0
+    moe_shared_expert_intermediate_size: int = 0
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    first_k_dense_replace: int = 0
+
+    def __post_init__(self):
+        if self.head_dim is None:
+            self.head_dim = self.hidden_size // self.num_attention_heads
+        if self.qk_norm is None:
+            self.qk_norm = self.model_type in ("qwen3", "ling_moe")
+
+    @classmethod
+    def from_file(cls, path: str) -> "TargetConfig":
+        raw = json.load(open(path))
+        raw = raw.get("text_config", raw)
+        names = {f for f in cls.__dataclass_fields__}
+        return cls(**{k: v for k, v in raw.items() if k in names})
+
+    def to_dict(self) -> dict:
+        return {k: getattr(self, k) for k in self.__dataclass_fields__}
+
+
+class FeatureSink:
+    """Where captured features go.  The default keeps them in local tensors."""
+
+    def __init__(self, n_tokens: int, layer_ids: Sequence[int], hidden: int, device, dtype):
+        self.layer_ids = list(layer_ids)
+        self.hidden = hidden
+        self.hidden_states = torch.empty(n_tokens, len(self.layer_ids) * hidden, device=device, dtype=dtype)
+        self.last_hidden_states = torch.empty(n_tokens, hidden, device=device, dtype=dtype)
+
+    def layer_views(self, layer_id: int) -> List[torch.Tensor]:
+        """Destination views ``[T, Dt]`` (row stride ``K * Dt``) for one captured layer."""
+        col = self.layer_ids.index(layer_id)
+        return [self.hidden_states[:, col * self.hidden:(col + 1) * self.hidden]]
+
+    def final_views(self) -> List[torch.Tensor]:
+        return [self.last_hidden_states]
+
+
+class _Layer(nn.Module):
+    def __init__(self, cfg: TargetConfig, layer_idx: int):
+        super().__init__()
+        d, D = cfg.head_dim, cfg.hidden_size
+        hq, hk = cfg.num_attention_heads, cfg.num_key_value_heads
+        self.cfg = cfg
+        self.qkv_proj = nn.Parameter(torch.empty((hq + 2 * hk) * d, D))
+        self.o_proj = nn.Parameter(torch.empty(D, hq * d))
+        self.input_layernorm = nn.Parameter(torch.ones(D))
+        self.post_attention_layernorm = nn.Parameter(torch.ones(D))
+        if cfg.qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(d))
+            self.k_norm = nn.Parameter(torch.ones(d))
+        self.is_moe = cfg.num_experts > 0 and layer_idx >= cfg.first_k_dense_replace
+        if self.is_moe:
+            from aspec_b200.models.target.moe import TargetMoE
+            self.mlp = TargetMoE(cfg)
+        else:
+            self.gate_up_proj = nn.Parameter(torch.empty(2 * cfg.intermediate_size, D))   # rows [gate | up]
+            self.down_proj = nn.Parameter(torch.empty(D, cfg.intermediate_size))
+        self._gate_up_tiled = None
+
+
+class DenseTarget(nn.Module):
+    """Qwen3 / Llama-shaped (optionally MoE) Target for prefill-only feature generation."""
+
+    def __init__(self, cfg: TargetConfig):
+        super().__init__()
+        self.config = cfg
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
+        self.layers = nn.ModuleList([_Layer(cfg, i) for i in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size))
+        self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size))
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.float32) / cfg.head_dim))
+        self.register_buffer("inv_freq", inv, persistent=False)
+        self.requires_grad_(False)
+
+    @torch.no_grad()
+    def init_random(self, seed: int = 0, std: float = 0.02) -> "DenseTarget":
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        for name, p in self.named_parameters():
+            if p.dim() >= 2:
+                # generate on the parameter's device in chunks to keep host memory flat
+                p.normal_(0.0, std)
+        return self
+
+    # -- pieces ---------------------------------------------------------------------------------
+    def _use_kernels(self, x: torch.Tensor) -> bool:
+        return x.is_cuda and x.dtype == torch.bfloat16 and self.config.head_dim == 128
+
+    def _tiled_gate_up(self, layer: _Layer) -> torch.Tensor:
+        """gate/up rows interleaved in blocks of 128 so one GEMM tile holds matching gate and up columns."""
+        if layer._gate_up_tiled is None:
+            I = self.config.intermediate_size
+            w = layer.gate_up_proj
+            if I % 128:
+                return None
+            layer._gate_up_tiled = torch.stack([w[:I].view(I // 128, 128, -1), w[I:].view(I // 128, 128, -1)], 1) \
+                .reshape(2 * I, -1).contiguous()
+        return layer._gate_up_tiled
+
+    def _attention(self, layer: _Layer, x, positions, intervals):
+        cfg = self.config
+        hq, hk, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        T = x.shape[0]
+        if self._use_kernels(x):
+            from aspec_b200.ops import attention_sm100 as A
+            from aspec_b200.ops import elementwise_sm100 as E
+            from aspec_b200.ops import gemm as G
+            qkv = G.gemm(x, layer.qkv_proj)
+            q = qkv[:, : hq * d].reshape(T, hq, d)
+            k = qkv[:, hq * d:(hq + hk) * d].reshape(T, hk, d)
+            v = qkv[:, (hq + hk) * d:].view(T, hk, d)
+            qn = layer.q_norm if cfg.qk_norm else None
+            kn = layer.k_norm if cfg.qk_norm else None
+            q, _ = E.qk_norm_rope_fwd(q.contiguous(), qn, positions, self.inv_freq, cfg.rms_norm_eps, 1.0)
+            k, _ = E.qk_norm_rope_fwd(k.contiguous(), kn, positions, self.inv_freq, cfg.rms_norm_eps, 1.0)
+            o, _ = A.forward(q, k, v, intervals, d ** -0.5)
+            return o.view(T, hq * d)
+        qkv = F.linear(x, layer.qkv_proj)
+        q = qkv[:, : hq * d].reshape(T, hq, d)
+        k = qkv[:, hq * d:(hq + hk) * d].reshape(T, hk, d)
+        v = qkv[:, (hq + hk) * d:].reshape(T, hk, d)
+        q = qk_norm_rope_reference(q, layer.q_norm if cfg.qk_norm else None, positions, self.inv_freq, cfg.rms_norm_eps)
+        k = qk_norm_rope_reference(k, layer.k_norm if cfg.qk_norm else None, positions, self.inv_freq, cfg.rms_norm_eps)
+        o, _ = interval_attention_reference(q, k, v, intervals, d ** -0.5)
+        return o.reshape(T, hq * d)
+
+    def _norm(self, x, w, out=None):
+        if self._use_kernels(x):
+            from aspec_b200.ops import elementwise_sm100 as E
+            y, _ = E.rmsnorm_fwd(x, w, self.config.rms_norm_eps)
+            return y
+        return rmsnorm_reference(x, w, self.config.rms_norm_eps)
+
+    def _proj_residual(self, a, w, residual, mirrors=None):
+        """``residual + a @ w.T`` with the add (and the optional mirrored stores) in the GEMM epilogue."""
+        if self._use_kernels(a):
+            from aspec_b200.ops import gemm as G
+            return G.gemm(a, w, addend=residual, mirrors=mirrors or None)
+        out = residual + F.linear(a, w)
+        for m in mirrors or ():
+            m.copy_(out)
+        return out
+
+    def _mlp(self, layer: _Layer, x, residual, mirrors):
+        if layer.is_moe:
+            out = residual + layer.mlp(x)
+            for m in mirrors or ():
+                m.copy_(out)
+            return out
+        if self._use_kernels(x):
+            from aspec_b200.ops import gemm as G
+            tiled = self._tiled_gate_up(layer)
+            if tiled is not None:
+                act = G.gemm(x, tiled, epilogue=G.EPI_SWIGLU)
+            else:
+                from aspec_b200.ops.activation import swiglu
+                act = swiglu(G.gemm(x, layer.gate_up_proj))
+            return self._proj_residual(act, layer.down_proj, residual, mirrors)
+        gu = F.linear(x, layer.gate_up_proj)
+        g, u = gu.chunk(2, -1)
+        return self._proj_residual(F.silu(g) * u, layer.down_proj, residual, mirrors)
+
+    # -- prefill ----------------------------------------------------------------------------------
+    @staticmethod
+    def causal_intervals(document_lengths: Sequence[int], device) -> torch.Tensor:
+        """Interval table of packed causal attention: token ``i`` sees ``[doc_start, i + 1)``."""
+        starts = torch.repeat_interleave(
+            torch.tensor([0] + list(torch.tensor(document_lengths).cumsum(0)[:-1].tolist())),
+            torch.tensor(document_lengths))
+        T = int(sum(document_lengths))
+        iv = torch.zeros(T, 4, dtype=torch.int32)
+        iv[:, 0] = starts.to(torch.int32)
+        iv[:, 1] = torch.arange(1, T + 1, dtype=torch.int32)
+        return iv.to(device, non_blocking=True)
+
+    @torch.no_grad()
+    def prefill(self, input_ids: torch.Tensor, document_lengths: Sequence[int], capture_layers: Sequence[int],
+                sink: Optional[FeatureSink] = None, want_logits: bool = False) -> Dict[str, torch.Tensor]:
+        """``input_ids [T]`` (packed documents).  Returns the sink's tensors (and logits when asked)."""
+        cfg = self.config
+        T = input_ids.shape[0]
+        dev = input_ids.device
+        if sum(document_lengths) != T:
+            raise ValueError("document_lengths must sum to the number of tokens")
+        x = self.embed_tokens(input_ids)
+        if sink is None:
+            sink = FeatureSink(T, capture_layers, cfg.hidden_size, dev, x.dtype)
+        pos_list = torch.cat([torch.arange(n) for n in document_lengths]).to(torch.int32)
+        positions = pos_list.to(dev, non_blocking=True)
+        intervals = self.causal_intervals(document_lengths, dev)
+        capture = set(capture_layers)
+        for i, layer in enumerate(self.layers):
+            h = self._norm(x, layer.input_layernorm)
+            a = self._attention(layer, h, positions, intervals)
+            x = self._proj_residual(a, layer.o_proj, x)
+            h = self._norm(x, layer.post_attention_layernorm)
+            x = self._mlp(layer, h, x, sink.layer_views(i) if i in capture else None)
+        final = self._norm(x, self.norm)
+        for view in sink.final_views():
+            view.copy_(final)
+        out = {"hidden_states": getattr(sink, "hidden_states", None),
+               "last_hidden_states": getattr(sink, "last_hidden_states", None), "final_hidden": final}
+        if want_logits:
+            out["logits"] = F.linear(final, self.lm_head)
+        return out
+
+    def memory_bytes(self) -> int:
+        return sum(p.numel() * p.element_size() for p in self.parameters())

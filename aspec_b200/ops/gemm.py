@@ -36,6 +36,19 @@ def _wave_efficiency(M: int, N: int) -> float:
     return waves / math.ceil(waves)
 
 
+def _mirror_ptrs(mirrors):
+    """``mirrors``: bf16 2-D tensors (possibly views of another GPU's memory) with the output's shape."""
+    if not mirrors:
+        return None
+    return (ctypes.c_void_p * len(mirrors))(*[m.data_ptr() for m in mirrors])
+
+
+def _mirror_lds(mirrors):
+    if not mirrors:
+        return None
+    return (ctypes.c_longlong * len(mirrors))(*[m.stride(0) for m in mirrors])
+
+
 class _Operand(ctypes.Structure):
     _fields_ = [("ptr", ctypes.c_void_p), ("ld", ctypes.c_longlong), ("mn_major", ctypes.c_int)]
 
@@ -71,7 +84,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
          out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
          addend: Optional[torch.Tensor] = None, alpha: float = 1.0,
          epilogue: int = EPI_STORE, stats: Optional[torch.Tensor] = None,
-         logit_scale: float = 1.0, max_ctas: int = 0, stream_k: Optional[bool] = None) -> torch.Tensor:
+         logit_scale: float = 1.0, max_ctas: int = 0, stream_k: Optional[bool] = None,
+         mirrors=None) -> torch.Tensor:
     """``alpha * (A @ B^T [+ A2 @ B2^T]) [+ addend]`` with a fused epilogue.
 
     ``stream_k=None`` picks the schedule: when whole output tiles would leave more than ~12 % of the last
@@ -89,6 +103,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     if a2 is not None:
         K2 = a2.shape[0] if a_t else a2.shape[1]
     n_out = N // 2 if epilogue == EPI_SWIGLU else N
+    if mirrors:
+        stream_k = False
     inplace_acc = addend is not None and out is not None and addend.data_ptr() == out.data_ptr()
     if stream_k is None:
         tiles = -(-M // 128) * -(-N // TILE_N)
@@ -128,6 +144,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         ctypes.c_void_p(stats.data_ptr() if stats is not None else 0),
         ctypes.c_float(logit_scale), ctypes.c_void_p(st.data_ptr()),
         ctypes.c_int(max_ctas), ctypes.c_int(1 if stream_k else 0),
+        ctypes.c_int(len(mirrors) if mirrors else 0), _mirror_ptrs(mirrors), _mirror_lds(mirrors),
         ctypes.c_void_p(torch.cuda.current_stream(a.device).cuda_stream))
     if rc != 0:
         raise RuntimeError(f"ab_gemm_bf16 refused the launch (code {rc}) for M={M} N={N} K={K}")

@@ -1,0 +1,185 @@
+"""Config -> immutable, hashed ``ExecutionPlan``.
+
+The plan is what the run is held to: workload contract (what is trained on what), execution policy (how
+many ranks in which role, which parallelism), capability decisions (which kernel / transport path each
+subsystem takes and why), and the resolved draft config.  ``plan_id`` is the SHA-256 of its canonical
+JSON; ``to_runtime_args`` flattens it for the processes (reference: aspec/planning.py:99-196, 1822-2314).
+"""
+from __future__ import annotations
+
+import dataclasses
+import hashlib
+import json
+import math
+import os
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+from aspec_b200 import __version__
+from aspec_b200.config.draft_attention import (context_shard_alignment, resolve_attention_policy, thd_contract)
+from aspec_b200.config.draft_config import (AutoDraftModelConfig, draft_model_semantics, resolve_draft_algorithm)
+from aspec_b200.config.draft_structure import resolve_ffn_policy
+from aspec_b200.config.train_config import Config, config_to_flat_args
+
+HBM_BYTES = 180 * 1024 ** 3
+
+
+@dataclass(frozen=True)
+class CapabilityDecision:
+    subsystem: str
+    choice: str
+    reason: str
+
+
+@dataclass
+class ExecutionPlan:
+    workload: Dict[str, Any]
+    policy: Dict[str, Any]
+    capabilities: List[CapabilityDecision]
+    draft_config: Dict[str, Any]
+    runtime_args: Dict[str, Any]
+    memory: Dict[str, Any] = field(default_factory=dict)
+    schema_version: str = "aspec.execution-plan/v1"
+
+    def _body(self) -> dict:
+        return {"schema_version": self.schema_version, "framework_version": __version__, "workload": self.workload,
+                "policy": self.policy, "capabilities": [dataclasses.asdict(c) for c in self.capabilities],
+                "draft_config": self.draft_config, "memory": self.memory}
+
+    @property
+    def plan_id(self) -> str:
+        return "sha256:" + hashlib.sha256(json.dumps(self._body(), sort_keys=True, default=str).encode()).hexdigest()
+
+    def to_json(self) -> str:
+        return json.dumps({"plan_id": self.plan_id, **self._body(), "runtime_args": self.runtime_args}, indent=2,
+                          sort_keys=True, default=str)
+
+    def to_runtime_args(self) -> Dict[str, Any]:
+        return {**self.runtime_args, "plan_id": self.plan_id}
+
+
+def _load_draft(flat: Dict[str, Any]) -> dict:
+    path = flat.get("draft_model_config")
+    if not path:
+        raise ValueError("model.draft_model_config is required")
+    if isinstance(path, dict):
+        raw = path
+    else:
+        if not os.path.exists(path):
+            from aspec_b200.assets import find_asset
+            path = find_asset(path)
+        raw = json.load(open(path))
+    return AutoDraftModelConfig.from_dict(raw).to_dict()
+
+
+def resolve_batch_size(flat: Dict[str, Any], dp: int) -> dict:
+    """Documents per optimizer update and the derived global quantities."""
+    mbs, acc = int(flat["micro_batch_size"]), int(flat["draft_accumulation_steps"])
+    per_update = dp * mbs * acc
+    return {"dp_size": dp, "micro_batch_size": mbs, "accumulation": acc, "documents_per_update": per_update,
+            "max_tokens_per_update": per_update * int(flat["max_seq_length"])}
+
+
+def estimate_memory(draft: dict, flat: Dict[str, Any], algorithm: str, shard: int) -> dict:
+    """Resident bytes per Draft GPU: bf16 weights + fp32 master/grad/moments (sharded by FSDP), frozen head
+    and embedding, ring slots and the largest vocabulary-sized activations.  Sized for 180 GB of HBM3e."""
+    D, V, L = draft["hidden_size"], draft["vocab_size"], draft["num_hidden_layers"]
+    I = draft.get("intermediate_size", 4 * D)
+    hq, hk = draft["num_attention_heads"], draft["num_key_value_heads"]
+    d = draft.get("head_dim") or D // hq
+    per_layer = D * (hq * d) * 2 + D * (hk * d) * 2 + 3 * D * I
+    n_tl = draft.get("num_target_layers") or draft.get("num_aux_hidden_states") or 3
+    Dt = draft.get("target_hidden_size") or D
+    trainable = L * per_layer + n_tl * Dt * D
+    if algorithm == "dspark":
+        trainable += 2 * V * int(draft.get("markov_rank", 0))
+    if algorithm in ("eagle3", "eagle4"):
+        trainable += (draft.get("draft_vocab_size") or V) * D
+    frozen = 2 * V * D
+    rows = int(flat.get("dspark_num_anchors", 512)) * int(flat.get("dspark_block_size", 7))
+    logits = 2 * rows * V * 2
+    slot = int(flat["max_seq_length"]) * (n_tl + 1) * Dt * 2 + int(flat["max_seq_length"]) * 8
+    ring = slot * int(flat.get("transport_destination_ring_slots", 1))
+    total = trainable * 2 + trainable * 16 // max(shard, 1) + frozen * 2 + logits + ring
+    return {"trainable_parameters": trainable, "frozen_parameters": frozen, "weights_bf16": trainable * 2,
+            "optimizer_fp32": trainable * 16 // max(shard, 1), "frozen_bf16": frozen * 2, "vocab_activations": logits,
+            "ring_bytes": ring, "estimated_total": total, "hbm_bytes": HBM_BYTES, "fits": total < 0.9 * HBM_BYTES}
+
+
+def compile_execution_plan(config: Config) -> ExecutionPlan:
+    flat = vars(config_to_flat_args(config)).copy()
+    draft = _load_draft(flat)
+    algorithm = resolve_draft_algorithm(draft)
+    world = int(flat["world_size"])
+    cp = int(flat["draft_context_parallel_size"])
+    u, r = int(flat["sp_ulysses_size"]), int(flat["sp_ring_size"])
+    if u * r > 1 and cp == 1:
+        cp = u * r
+        flat["draft_context_parallel_size"] = cp
+    ep, vp = int(flat["expert_parallel_size"]), int(flat["vocab_parallel_size"])
+    if world % cp:
+        raise ValueError(f"world size {world} is not divisible by context parallel size {cp}")
+    dp = world // cp
+    caps: List[CapabilityDecision] = []
+    policy = resolve_attention_policy(draft) if algorithm != "mtp" else {"layer_types": ["full_attention"]}
+    ffn = resolve_ffn_policy(draft) if algorithm != "mtp" else {"ffn_type": "dense"}
+    # ---- scope validation ----------------------------------------------------------------------
+    if flat["dflash_packing"] and algorithm not in ("dflash", "dspark", "dflash2", "eagle3", "eagle4", "mtp"):
+        raise ValueError("packing is not defined for this algorithm")
+    if algorithm in ("dflash", "dspark", "dflash2"):
+        n_anchor = int(flat["dspark_num_anchors"] if algorithm == "dspark" else flat["dflash_num_anchors"])
+        if cp > 1 and n_anchor % cp:
+            raise ValueError(f"num_anchors ({n_anchor}) must be divisible by the context-parallel size ({cp})")
+        want_layers = int(flat["dspark_num_target_layers"] if algorithm == "dspark" else flat["dflash_num_target_layers"])
+        if draft.get("num_target_layers") not in (None, want_layers) and flat.get("strict_target_layers", False):
+            raise ValueError("training.*_num_target_layers disagrees with the draft config")
+    if draft.get("mtp_conditioning") and (cp != 1 or flat["anchor_sampling_scope"] != "row"):
+        raise ValueError("MTP conditioning currently requires CP1 row anchors")
+    if ffn["ffn_type"] == "dense" and ep > 1:
+        raise ValueError("expert_parallel_size > 1 requires a MoE draft")
+    if ep > 1 and ffn.get("num_experts", 0) % ep:
+        raise ValueError("num_experts must be divisible by expert_parallel_size")
+    if vp > 1 and draft["vocab_size"] % vp:
+        raise ValueError("vocab_size must be divisible by vocab_parallel_size")
+    if ep > 1 and world % ep or vp > 1 and world % vp:
+        raise ValueError("expert / vocab parallel sizes must divide the Draft world size")
+    align = context_shard_alignment(policy) if algorithm != "mtp" else 1
+    if cp > 1 and int(flat["max_seq_length"]) // max(align, 1) < cp:
+        raise ValueError("sequence too short to give every context-parallel rank an aligned shard")
+    # ---- capability decisions ------------------------------------------------------------------
+    head_dim = draft.get("head_dim") or draft["hidden_size"] // draft["num_attention_heads"]
+    mla = draft.get("attention_mode") == "mla" or draft.get("model_type") in ("k3_dspark", "deepseek_v3")
+    caps.append(CapabilityDecision("gemm", "tcgen05_tma_persistent", "bf16 weights, sm_100a"))
+    caps.append(CapabilityDecision(
+        "attention", "dense_mask_fp32" if (mla or head_dim != 128) else "tcgen05_interval_flash",
+        "head dim 128 GQA uses the TMEM flash kernels" if not (mla or head_dim != 128)
+        else "materialised MLA / non-128 head dim runs the fp32 dense-mask path"))
+    caps.append(CapabilityDecision("vocab_head", "fused_rowstats_gemm+streaming_loss", "logits stay bf16; no fp32 [rows, V]"))
+    caps.append(CapabilityDecision("feature_transport", flat["transport_data_plane"],
+                                   "Target epilogues store into the Draft ranks' ring slots over NVLink"))
+    caps.append(CapabilityDecision("data_parallel", flat["fsdp_strategy"],
+                                   "flat fp32 gradient buffer, one SUM reduction per update"))
+    if cp > 1:
+        caps.append(CapabilityDecision("context_parallel", f"ulysses{u}xring{r}" if u * r > 1 else f"direct_cp{cp}",
+                                       f"context sharded contiguously per document, alignment {align}"))
+    if ep > 1:
+        caps.append(CapabilityDecision("expert_parallel", f"ep{ep}", "all-to-all dispatch/combine around grouped expert GEMMs"))
+    if vp > 1:
+        caps.append(CapabilityDecision("vocab_parallel", f"vp{vp}", "head rows sharded; log-sum-exp merged over peer memory"))
+    thd = thd_contract(policy) if algorithm != "mtp" else {}
+    workload = {"algorithm": algorithm, "draft_model_semantics": draft_model_semantics(draft),
+                "attention_policy": {k: policy.get(k) for k in ("layer_types", "window_semantics", "draft_block_attention")},
+                "ffn_policy": ffn, "thd_contract": thd, "max_seq_length": flat["max_seq_length"],
+                "packing": bool(flat["dflash_packing"]), "dataset": flat.get("train_data_path"),
+                "target": flat.get("target_model_path") or flat.get("target_model_config") or "shape-bound random init",
+                "engine": flat["inference_engine_type"], "context_shard_alignment": align}
+    pol = {"world_size": world, "target_gpus": int(flat["inference_num_gpus"]) if flat["inference_engine_type"] == "native" else 0,
+           "draft_gpus": world, "context_parallel": cp, "ulysses": u, "ring": r, "expert_parallel": ep,
+           "vocab_parallel": vp, "fsdp_strategy": flat["fsdp_strategy"], **resolve_batch_size(flat, dp),
+           "num_train_steps": flat.get("num_train_steps"), "seed": flat["seed"]}
+    memory = estimate_memory(draft, flat, algorithm, world if flat["fsdp_strategy"] == "FULL_SHARD" else 1)
+    if not memory["fits"]:
+        raise ValueError(f"estimated {memory['estimated_total'] / 2**30:.1f} GiB per Draft GPU exceeds 180 GB HBM3e; "
+                         "use FULL_SHARD, fewer anchors or a smaller ring")
+    flat["draft_algorithm"] = algorithm
+    return ExecutionPlan(workload, pol, caps, draft, flat, memory)

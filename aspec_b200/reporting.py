@@ -1,0 +1,49 @@
+"""``aspec --report RUN_DIR``: check that plan and evidence belong together and summarise the run
+(reference: aspec/reporting.py:93-379)."""
+from __future__ import annotations
+
+import json
+import os
+
+
+def build_run_report(run_dir: str) -> dict:
+    problems = []
+
+    def load(name):
+        p = os.path.join(run_dir, name)
+        if not os.path.isfile(p):
+            problems.append(f"missing {name}")
+            return {}
+        return json.load(open(p))
+
+    plan, ev = load("plan.json"), load("evidence.json")
+    if plan and ev and plan.get("plan_id") != ev.get("plan_id"):
+        problems.append("evidence.json was written for a different plan")
+    summary = ev.get("training_summary", {})
+    ledger = summary.get("ledger", {})
+    if ev and ev.get("state") != "completed":
+        problems.append(f"run state is {ev.get('state')!r}")
+    if ledger and not ledger.get("validated", False):
+        problems.append("work ledger is not validated (residency, incomplete work or non-contiguous steps)")
+    ckpt_root = os.path.join(run_dir, "checkpoints")
+    tracker = os.path.join(ckpt_root, "latest_checkpointed_iteration.txt")
+    latest = int(open(tracker).read()) if os.path.isfile(tracker) else None
+    return {"run_dir": os.path.abspath(run_dir), "valid": not problems, "problems": problems,
+            "plan_id": plan.get("plan_id"), "algorithm": plan.get("workload", {}).get("algorithm"),
+            "policy": plan.get("policy"), "state": ev.get("state"), "completed_steps": summary.get("completed_steps"),
+            "throughput_window": summary.get("window"), "committed_work": len(ledger.get("committed_work_ids", [])),
+            "dropped_tail_samples": summary.get("dropped_tail_samples"), "latest_checkpoint": latest,
+            "capabilities": plan.get("capabilities"), "accelerators": ev.get("accelerators")}
+
+
+def render_report(report: dict) -> str:
+    lines = [f"run        {report['run_dir']}", f"valid      {report['valid']}",
+             f"plan       {report.get('plan_id')}", f"algorithm  {report.get('algorithm')}",
+             f"state      {report.get('state')}", f"steps      {report.get('completed_steps')}",
+             f"committed  {report.get('committed_work')} documents", f"checkpoint iter {report.get('latest_checkpoint')}"]
+    w = report.get("throughput_window") or {}
+    if w.get("valid"):
+        lines.append(f"throughput {w['tokens_per_second']:.1f} input tokens/s over {w['steps']} steady updates")
+    for p in report.get("problems", []):
+        lines.append(f"PROBLEM    {p}")
+    return "\n".join(lines)

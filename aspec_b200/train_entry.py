@@ -1,0 +1,203 @@
+"""``aspec --config recipe.yaml``: load and validate the config, compile the plan, start the role
+processes and run the training loop (reference: aspec/train_entry.py:148-622).
+
+Process model on one B200 node: the driver (this process, CPU only) owns the controller, the ledger, the
+lease rings and the inference manager; each Target GPU and each Draft GPU is a child process
+(``runtime.actor.ProcessActor``).  Draft ranks allocate their feature rings and export them; Target ranks
+map them and write features directly into them.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from typing import Any, Dict, List, Optional
+
+from aspec_b200.config.draft_config import AutoDraftModelConfig, resolve_draft_algorithm
+from aspec_b200.config.train_config import config_to_flat_args, load_config, save_config
+from aspec_b200.runtime.actor import ProcessActor, make_queue
+from aspec_b200.transport.slot_ring import GenerationSlotRing
+
+RUN_ARTIFACTS = ("config.yaml", "plan.json", "evidence.json", "evaluation.json", "tracking.json",
+                 "cluster-preflight.json", "checkpoints", "runs", "traces", "scratch_draft_model")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="aspec", description="Train a speculative-decoding draft model.")
+    ap.add_argument("--config", help="recipe YAML")
+    ap.add_argument("--report", metavar="RUN_DIR", help="render the report of a finished run")
+    ap.add_argument("--report-format", default="text", choices=["text", "json"])
+    ap.add_argument("--dry-run", action="store_true", help="compile the plan and stop")
+    ap.add_argument("--print-config-only", action="store_true")
+    ap.add_argument("--preflight-only", action="store_true")
+    ap.add_argument("overrides", nargs="*", help="section.key=value")
+    return ap
+
+
+def resolve_draft_config(flat: Dict[str, Any]) -> dict:
+    path = flat.get("draft_model_config")
+    if not path:
+        raise ValueError("model.draft_model_config is required")
+    if isinstance(path, dict):
+        raw = path
+    else:
+        if not os.path.isabs(path) and not os.path.exists(path):
+            from aspec_b200.assets import find_asset
+            path = find_asset(path)
+        raw = json.load(open(path))
+    return AutoDraftModelConfig.from_dict(raw).to_dict()
+
+
+def claim_run_directory(output_dir: str) -> None:
+    """A run directory belongs to one run: refuse to reuse one that already holds evidence."""
+    os.makedirs(output_dir, exist_ok=True)
+    if os.path.exists(os.path.join(output_dir, "evidence.json")):
+        raise FileExistsError(f"{output_dir} already contains a run (evidence.json); choose a fresh output_dir")
+    for sub in ("checkpoints", "runs", "traces"):
+        os.makedirs(os.path.join(output_dir, sub), exist_ok=True)
+
+
+def _devices(flat: Dict[str, Any]):
+    import torch
+    n_draft = int(flat["training_num_gpus_per_node"]) * int(flat["training_num_nodes"])
+    n_target = int(flat["inference_num_gpus"]) if flat["inference_engine_type"] == "native" else 0
+    if torch.cuda.is_available() and not flat.get("force_cpu"):
+        have = torch.cuda.device_count()
+        if n_draft + n_target > have:
+            raise RuntimeError(f"plan needs {n_target} Target + {n_draft} Draft GPUs, {have} visible")
+        target = [f"cuda:{i}" for i in range(n_target)]
+        draft = [f"cuda:{n_target + i}" for i in range(n_draft)]
+    else:
+        target, draft = ["cpu"] * n_target, ["cpu"] * n_draft
+    return target, draft
+
+
+def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence=None, log=print,
+                              dataset: Optional[List[dict]] = None) -> dict:
+    """Starts the actors, runs the loop, tears everything down.  Returns the loop summary."""
+    from aspec_b200.controller.inference_manager import InferenceManager
+    from aspec_b200.controller.loop import training_loop
+    from aspec_b200.controller.training_controller import TrainingController
+    from aspec_b200.inference.factory import create_engines
+    from aspec_b200.training.trainer_actor import TrainerActor
+    algorithm = resolve_draft_algorithm(draft_config)
+    target_devs, draft_devs = _devices(flat)
+    world = len(draft_devs)
+    cp = max(int(flat.get("draft_context_parallel_size", 1)), 1)
+    dp = world // cp
+    args = dict(flat)
+    args.update(trainer_devices=draft_devs, run_id=flat.get("run_id") or f"run-{int(time.time())}",
+                attempt_id=str(flat.get("attempt_id", "0")))
+    cfg_obj = AutoDraftModelConfig.from_dict(draft_config)
+    layer_ids = list(getattr(cfg_obj, "target_layer_ids", None) or [])
+    if not layer_ids:
+        from aspec_b200.models.draft.dflash import build_target_layer_ids
+        layer_ids = build_target_layer_ids(int(getattr(cfg_obj, "num_target_layers", 3)),
+                                           int(getattr(cfg_obj, "target_num_hidden_layers", 36)))
+    port = int(flat.get("master_port") or 29500 + (os.getpid() % 2000))
+    queues = {r: make_queue() for r in range(world)}
+    trainers = [ProcessActor(TrainerActor, r, world, args, draft_config, queues[r], port, name=f"trainer{r}")
+                for r in range(world)]
+    engines: list = []
+    manager = None
+    try:
+        for t in trainers:
+            t.wait_ready()
+        handles = {r: trainers[r].call("ring_handle", timeout=120) for r in range(world)}
+        engines, head, embedding = create_engines(flat, draft_config, layer_ids, target_devs, handles)
+        for fut in [t.call_async("set_head", head, embedding) for t in trainers]:
+            fut.get(timeout=600)
+        start_step = 0
+        controller = TrainingController(args, dp_size=dp, consumers_per_row=cp, algorithm=algorithm)
+        n = controller.load_dataset(dataset)
+        if evidence:
+            evidence.record("dataset_admission", {"samples": n, "fingerprint": controller.dataset_fingerprint()})
+        if flat.get("load_path"):
+            # collective inside the trainer group: start it on every rank before waiting for any
+            futs = [t.call_async("load_model", flat["load_path"], bool(flat.get("continual_training"))) for t in trainers]
+            infos = [f.get(timeout=1800) for f in futs]
+            if not flat.get("continual_training") or flat.get("continue_source_cursor"):
+                controller.restore(infos[0]["work_state"])
+            start_step = infos[0]["next_step"]
+        slots = int(flat.get("transport_destination_ring_slots", 4))
+        rings = {r: GenerationSlotRing(slots) for r in range(world)}
+        manager = InferenceManager(engines, rings, on_result=lambda o, r: None,
+                                   batch_size=int(flat.get("inference_batch_size", 1)),
+                                   acquire_timeout=float(flat.get("transport_acquire_timeout_seconds", 120.0)))
+        manager.start()
+        num_steps = int(flat.get("num_train_steps") or 0) or max(n // max(dp * int(flat.get("micro_batch_size", 1))
+                                                                     * int(flat.get("draft_accumulation_steps", 1)), 1), 1)
+        consumer_of_rank = (lambda r: list(range(r * cp, (r + 1) * cp)))
+        summary = training_loop(controller=controller, manager=manager, trainers=trainers, rings=rings,
+                                train_queues=queues, args=args, layer_ids=layer_ids, num_steps=num_steps - start_step,
+                                start_step=start_step, log=log, evidence=evidence, consumer_of_rank=consumer_of_rank)
+        summary["engines"] = [e.call("get_status", timeout=30) if isinstance(e, ProcessActor) else e.get_status()
+                              for e in engines]
+        return summary
+    finally:
+        if manager is not None:
+            manager.stop()
+        for a in list(engines) + trainers:
+            if isinstance(a, ProcessActor):
+                a.shutdown(timeout=5.0)
+
+
+def main(argv=None) -> int:
+    a = build_parser().parse_args(argv)
+    if a.report:
+        from aspec_b200.reporting import build_run_report, render_report
+        report = build_run_report(a.report)
+        print(json.dumps(report, indent=2, default=str) if a.report_format == "json" else render_report(report))
+        return 0 if report.get("valid", False) else 1
+    if not a.config:
+        build_parser().error("--config is required")
+    config = load_config(a.config, a.overrides)
+    if a.print_config_only:
+        import yaml
+        print(yaml.safe_dump(config.to_dict(), sort_keys=True))
+        return 0
+    if config.experiments:
+        from aspec_b200.multi_draft import run_multi_draft_from_config
+        return run_multi_draft_from_config(config, dry_run=a.dry_run)
+    from aspec_b200.evidence import RunEvidenceRecorder
+    from aspec_b200.planning import compile_execution_plan
+    plan = compile_execution_plan(config)
+    if a.dry_run:
+        print(plan.to_json())
+        return 0
+    flat = plan.to_runtime_args()
+    claim_run_directory(flat["output_dir"])
+    save_config(config, os.path.join(flat["output_dir"], "config.yaml"))
+    with open(os.path.join(flat["output_dir"], "plan.json"), "w") as f:
+        f.write(plan.to_json())
+    evidence = RunEvidenceRecorder(plan, flat["output_dir"])
+    try:
+        from aspec_b200.preflight import run_cluster_preflight
+        pre = run_cluster_preflight(flat)
+        evidence.record("cluster_preflight", pre)
+        with open(os.path.join(flat["output_dir"], "cluster-preflight.json"), "w") as f:
+            json.dump(pre, f, indent=2)
+        if a.preflight_only:
+            evidence.complete({"preflight_only": True})
+            return 0
+        log_path = os.path.join(flat["output_dir"], "runs", "metrics.jsonl")
+
+        def log(m: dict) -> None:
+            with open(log_path, "a") as f:
+                f.write(json.dumps(m, default=float) + "\n")
+            print(f"step {m.get('train/step')}: loss {m.get('train/avg_loss', float('nan')):.4f} "
+                  f"acc {m.get('train/avg_acc', 0):.3f} tokens {m.get('perf/input_tokens')} "
+                  f"wall {m.get('perf/step_wall_time', 0):.3f}s", flush=True)
+
+        summary = train_async_no_generation(flat, plan.draft_config, evidence, log)
+        evidence.complete({k: v for k, v in summary.items() if k != "history"})
+        return 0
+    except BaseException as exc:                                  # noqa: BLE001 - recorded, then re-raised
+        evidence.fail(exc)
+        raise
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,167 @@
+"""One trainer process per Draft GPU.
+
+Counterpart of the reference's Ray ``TrainerActor`` (aspec/training/trainer_actor.py:75-245): ``init``
+joins the trainer process group, builds the Draft and its optimizer and allocates the feature ring that
+Target ranks write into; ``train_from_queue(step, num_batches)`` pops sample descriptors, reads the
+slots zero-copy, runs the micro-batches and the optimizer step, and reports metrics, the work it
+consumed and the leases it no longer needs.
+"""
+from __future__ import annotations
+
+import os
+import queue as _queue
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from aspec_b200.config.draft_config import AutoDraftModelConfig
+from aspec_b200.data.utils import unpack_loss_mask
+from aspec_b200.training import checkpoint as ckpt
+from aspec_b200.training.draft_trainer import DraftTrainer
+from aspec_b200.training.factory import build_training_model
+from aspec_b200.transport.feature_ring import FeatureDescriptor, FeatureRing, SlotLayout
+from aspec_b200.utils.types import TrainSample
+
+
+class TrainerActor:
+    def __init__(self, rank: int, world: int, args: Dict[str, Any], draft_config: Dict[str, Any], train_queue,
+                 master_port: int = 29517, group_name: str = "draft"):
+        self.rank, self.world, self.args = rank, world, dict(args)
+        self.queue = train_queue
+        dev = self.args.get("trainer_devices", ["cpu"] * world)[rank]
+        self.device = torch.device(dev)
+        self.cuda = self.device.type == "cuda"
+        if self.cuda:
+            torch.cuda.set_device(self.device)
+        self.dtype = torch.bfloat16 if self.cuda else torch.float32
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ["MASTER_PORT"] = str(master_port)
+            dist.init_process_group("nccl" if self.cuda else "gloo", rank=rank, world_size=world,
+                                    device_id=self.device if self.cuda else None)
+        torch.manual_seed(int(self.args.get("seed", 0)))
+        self.draft_config = AutoDraftModelConfig.from_dict(draft_config)
+        self.model = build_training_model(self.draft_config, self.args, self.device, self.dtype)
+        cfg = self.draft_config
+        layout = SlotLayout(int(self.args["max_seq_length"]), int(getattr(cfg, "num_target_layers", None)
+                                                                   or getattr(cfg, "num_aux_hidden_states", 3)),
+                            int(getattr(cfg, "target_hidden_size", cfg.hidden_size)),
+                            bool(self.args.get("store_last_hidden_states", True)),
+                            "bfloat16" if self.cuda else "float32")
+        self.ring = FeatureRing(int(self.args.get("transport_destination_ring_slots", 4)), layout, self.device,
+                                run_id=str(self.args.get("run_id", "run")), attempt_id=str(self.args.get("attempt_id", "0")),
+                                consumer=int(self.args.get("consumer_base", 0)) + rank)
+        self.trainer: Optional[DraftTrainer] = None
+        self.fault: Optional[dict] = self.args.get("fault_injection")      # host-side: {"kind": "raise"|"sleep", "step": k}
+        self._pending_releases: List[tuple] = []
+
+    # -- setup ------------------------------------------------------------------------------------
+    def ring_handle(self) -> dict:
+        return self.ring.export()
+
+    def set_head(self, lm_head: Optional[torch.Tensor], embedding: Optional[torch.Tensor] = None) -> None:
+        """Frozen Target output head (and embedding).  ``None`` -> deterministic random init (offline runs)."""
+        cfg = self.draft_config
+        if lm_head is None:
+            g = torch.Generator().manual_seed(1234)
+            lm_head = torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * 0.02
+        self.lm_head = lm_head.to(self.device, self.dtype)
+        draft = self.model.draft_model
+        if embedding is not None and hasattr(draft, "load_embedding"):
+            draft.load_embedding(embedding.to(self.device))
+        a = self.args
+        self.trainer = DraftTrainer(self.model, self.lm_head, lr=a.get("learning_rate", 1e-4), min_lr=a.get("min_lr", 0.0),
+                                    weight_decay=a.get("weight_decay", 0.0), max_grad_norm=a.get("max_grad_norm", 0.5),
+                                    total_steps=int(a.get("lr_total_steps") or a.get("num_train_steps") or 1000),
+                                    warmup_ratio=a.get("warmup_ratio", 0.015), decay_style=a.get("lr_decay_style", "cosine"),
+                                    accumulation=int(a.get("draft_accumulation_steps", 1)), device=self.device)
+
+    # -- data ---------------------------------------------------------------------------------------
+    def _batch(self, sample: TrainSample) -> dict:
+        views = self.ring.read(sample.feature_key, device_flags=bool(self.args.get("device_flags", False)),
+                               wait_limit_ms=float(self.args.get("transport_device_wait_limit_ms", 2000.0)))
+        lens = tuple(sample.document_lengths)
+        T = sum(lens)
+        masks = [unpack_loss_mask(m, n) for m, n in zip(sample.packed_loss_masks, lens)]
+        loss_mask = torch.cat(masks)[None]
+        batch = {"input_ids": views["input_ids"][None], "hidden_states": views["hidden_states"][None],
+                 "loss_mask": loss_mask, "_work": sample.metadata, "_key": sample.feature_key}
+        if "last_hidden_states" in views:
+            batch["last_hidden_states"] = views["last_hidden_states"][None]
+        ctx_docs = None
+        if len(lens) > 1:
+            ctx_docs = torch.cat([torch.full((n,), i, dtype=torch.long) for i, n in enumerate(lens)])[None]
+            batch["ctx_doc_ids"] = ctx_docs
+            batch["base_position_ids"] = torch.cat([torch.arange(n) for n in lens])[None]
+            batch["packed_document_lengths"] = lens
+        if hasattr(self.model, "sample_anchors"):
+            anchors, keep = self.model.sample_anchors(loss_mask, ctx_docs, lens if len(lens) > 1 else None)
+            batch["injected_anchors"], batch["injected_keep_mask"] = anchors, keep
+        return batch
+
+    def _samples(self, num_batches: int, timeout: float):
+        deadline = time.monotonic() + timeout
+        for _ in range(num_batches):
+            while True:
+                try:
+                    item = self.queue.get(timeout=0.2)
+                    break
+                except _queue.Empty:
+                    if time.monotonic() > deadline:
+                        raise TimeoutError(f"trainer {self.rank}: no sample within {timeout}s") from None
+            if item is None:
+                raise RuntimeError("train queue was closed")
+            yield item
+
+    # -- the step ---------------------------------------------------------------------------------
+    def train_from_queue(self, step: int, num_batches: int, timeout: float = 1800.0) -> dict:
+        if self.fault and int(self.fault.get("step", -1)) == step and int(self.fault.get("rank", 0)) == self.rank:
+            if self.fault.get("kind") == "sleep":
+                time.sleep(float(self.fault.get("seconds", 3600)))
+            else:
+                raise RuntimeError(f"trainer {self.rank}: injected failure at step {step}")
+        consumed, keys = [], []
+        t0 = time.perf_counter()
+
+        def batches():
+            for sample in self._samples(num_batches, timeout):
+                b = self._batch(sample)
+                consumed.extend(m["execution_id"] for m in sample.metadata)
+                keys.append(sample.feature_key)
+                yield b
+
+        self.trainer.train_update(batches())
+        metrics = self.trainer.metrics()              # one device->host read; also orders the slot reuse
+        if self.cuda:
+            self.ring.check_status()
+            from aspec_b200.ops.gemm import check_status
+            check_status(self.device)
+        releases = []
+        for k in keys:
+            d = FeatureDescriptor.from_key(k)
+            releases.append((d.consumer, d.slot, d.generation))
+        metrics["perf/step_time"] = time.perf_counter() - t0
+        return {"metrics": metrics, "committed": consumed, "releases": releases, "step": step}
+
+    # -- checkpoints --------------------------------------------------------------------------------
+    def topology(self) -> dict:
+        return ckpt.logical_training_topology({**self.args, "world_size": self.world}, self.draft_config)
+
+    def save_model(self, output_dir: str, step_id: int) -> str:
+        return ckpt.save(output_dir=output_dir, step_id=step_id, model=self.model.draft_model,
+                         optimizer=self.trainer.optimizer, draft_config=self.draft_config, topology=self.topology(),
+                         global_step=self.trainer.global_step)
+
+    def load_model(self, load_path: str, continual: bool = False) -> dict:
+        info = ckpt.load(load_path=load_path, model=self.model.draft_model, optimizer=self.trainer.optimizer,
+                         topology=self.topology(), continual_training=continual)
+        self.trainer.global_step = info["global_step"]
+        if not continual:
+            ckpt.finalize_load(info["checkpoint_dir"])
+        return {k: info[k] for k in ("next_step", "global_step", "work_state", "checkpoint_dir")}
+
+    def close(self) -> None:
+        if dist.is_available() and dist.is_initialized():
+            dist.destroy_process_group()

@@ -1,0 +1,96 @@
+"""Whole pipeline on CPU: driver + synthetic engine + 2 gloo trainer processes, checkpoint, resume, faults."""
+import json
+import os
+
+import pytest
+import torch
+
+from aspec_b200.config.train_config import Config, config_to_flat_args, load_config
+from aspec_b200.planning import compile_execution_plan
+from aspec_b200.train_entry import train_async_no_generation
+
+DRAFT = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "aspec_b200", "config", "drafts", "dspark_tiny.json")
+
+
+def _plan(tmp_path, extra=()):
+    recipe = tmp_path / "recipe.yaml"
+    recipe.write_text(f"""
+model:
+  draft_model_config: {DRAFT}
+dataset:
+  train_data_path: synthetic
+  synthetic_num_documents: 64
+  synthetic_min_length: 32
+  synthetic_max_length: 96
+inference:
+  inference_engine_type: synthetic
+training:
+  training_num_gpus_per_node: 2
+  micro_batch_size: 1
+  draft_accumulation_steps: 2
+  max_seq_length: 128
+  num_train_steps: 3
+  learning_rate: 1e-3
+  dspark_block_size: 4
+  dspark_num_anchors: 16
+  save_interval: 2
+  seed: 7
+transport:
+  destination_ring_slots: 3
+output_dir: {tmp_path / 'run'}
+""")
+    cfg = load_config(str(recipe), list(extra))
+    return compile_execution_plan(cfg)
+
+
+@pytest.mark.timeout(600)
+def test_two_trainers_train_checkpoint_and_resume(tmp_path):
+    plan = _plan(tmp_path)
+    assert plan.plan_id.startswith("sha256:") and plan.policy["dp_size"] == 2
+    flat = plan.to_runtime_args()
+    flat.update(synthetic_vocab_size=500, force_cpu=True)
+    os.makedirs(flat["output_dir"], exist_ok=True)
+    logs = []
+    summary = train_async_no_generation(flat, plan.draft_config, log=logs.append)
+    assert summary["completed_steps"] == 3 and len(logs) == 3
+    assert all(l["train/avg_loss"] == l["train/avg_loss"] for l in logs)
+    led = summary["ledger"]
+    assert led["validated"] and led["committed_steps"] == [0, 1, 2] and len(led["committed_work_ids"]) == 12
+    ck = os.path.join(flat["output_dir"], "checkpoints")
+    assert sorted(d for d in os.listdir(ck) if d.startswith("iter_")) == ["iter_0000002", "iter_0000003"]
+    ws = json.load(open(os.path.join(ck, "iter_0000002", "work_state.json")))
+    assert len(ws["committed_work_ids"]) == 8
+    # resume from iter 2: runs exactly one more step, on work that was not committed before
+    flat2 = dict(flat, load_path=os.path.join(ck, "iter_0000002"), output_dir=str(tmp_path / "run2"), save_interval=0,
+                 save_final_checkpoint=False)
+    logs2 = []
+    summary2 = train_async_no_generation(flat2, plan.draft_config, log=logs2.append)
+    assert summary2["completed_steps"] == 1 and logs2[0]["train/step"] == 2
+    assert not (set(summary2["ledger"]["committed_work_ids"]) & set(ws["committed_work_ids"]))
+    assert logs2[0]["train/avg_loss"] == pytest.approx(logs[2]["train/avg_loss"], rel=1e-5)
+
+
+@pytest.mark.timeout(300)
+def test_trainer_failure_and_producer_failure_surface(tmp_path):
+    plan = _plan(tmp_path)
+    flat = plan.to_runtime_args()
+    flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=0, save_final_checkpoint=False)
+    os.makedirs(flat["output_dir"], exist_ok=True)
+    from aspec_b200.runtime.actor import ActorError
+    with pytest.raises(ActorError, match="injected failure at step 1"):
+        train_async_no_generation(dict(flat, fault_injection={"kind": "raise", "step": 1, "rank": 1}), plan.draft_config,
+                                  log=lambda m: None)
+    with pytest.raises(RuntimeError, match="injected producer failure"):
+        train_async_no_generation(dict(flat, producer_fail_after=3), plan.draft_config, log=lambda m: None)
+
+
+@pytest.mark.timeout(300)
+def test_step_deadline_terminates_trainers(tmp_path):
+    plan = _plan(tmp_path)
+    flat = plan.to_runtime_args()
+    flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=0, save_final_checkpoint=False,
+                optimizer_step_timeout_seconds=3.0, fault_injection={"kind": "sleep", "step": 1, "rank": 0, "seconds": 120})
+    os.makedirs(flat["output_dir"], exist_ok=True)
+    from aspec_b200.controller.loop import TrainerStepTimeoutError
+    with pytest.raises(TrainerStepTimeoutError):
+        train_async_no_generation(flat, plan.draft_config, log=lambda m: None)
