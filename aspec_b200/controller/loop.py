@@ -99,19 +99,33 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
         futures = [t.call_async("train_from_queue", step, accumulation, budget) for t in trainers]
         # dispatch-ahead: the producers work on the next update while the trainers compute this one
         have_next = (completed + 1 < num_steps) and submit(step + 1)
-        outs = []
-        for r, fut in enumerate(futures):
-            while True:
-                manager.raise_if_failed()
-                try:
-                    outs.append(fut.get(timeout=0.25))
-                    break
-                except ActorTimeout:
-                    if time.perf_counter() > deadline:
+        outs = [None] * len(futures)
+        pending = set(range(len(futures)))
+        while pending:
+            # a failed trainer is reported at once (its peers may be blocked in a collective with it)
+            for r in sorted(pending):
+                if futures[r].done():
+                    try:
+                        outs[r] = futures[r].get(timeout=1.0)
+                    except ActorError:
                         for t in trainers:
                             t.terminate()
-                        raise TrainerStepTimeoutError(
-                            f"optimizer step {step} exceeded its {budget:.0f}s budget; trainer processes were terminated")
+                        raise
+                    pending.discard(r)
+            if not pending:
+                break
+            manager.raise_if_failed()
+            if time.perf_counter() > deadline:
+                for t in trainers:
+                    t.terminate()
+                raise TrainerStepTimeoutError(
+                    f"optimizer step {step} exceeded its {budget:.0f}s budget; trainer processes were terminated")
+            dead = [r for r in pending if not trainers[r].is_alive()]
+            if dead:
+                for t in trainers:
+                    t.terminate()
+                raise ActorError(f"trainer {dead[0]} exited during optimizer step {step}")
+            time.sleep(0.02)
         # release leases, then commit the work of this optimizer step
         committed: List[str] = []
         for out in outs:

@@ -85,7 +85,13 @@ class NativeTargetEngine(InferenceEngine):
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
         torch.manual_seed(seed)
-        self.model = DenseTarget(TargetConfig(**target_config)).to(device=self.device, dtype=getattr(torch, dtype))
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(getattr(torch, dtype))
+        try:
+            with torch.device(self.device):      # 8B+ parameters are created directly in device memory
+                self.model = DenseTarget(TargetConfig(**target_config))
+        finally:
+            torch.set_default_dtype(prev)
         if weights_path:
             self.model.load_state_dict(torch.load(weights_path, map_location=self.device), strict=True)
         else:

@@ -30,7 +30,7 @@ from aspec_b200.ops.attention import interval_attention
 from aspec_b200.ops.fused_params import allocate_adjacent, fused_linear
 from aspec_b200.ops.linear import Linear, linear
 from aspec_b200.ops.norm import RMSNorm
-from aspec_b200.ops.rope import qk_norm_rope
+from aspec_b200.ops.rope import RopeFrequencies, qk_norm_rope
 
 
 def build_target_layer_ids(num_target_layers: int, num_hidden_layers: int) -> List[int]:
@@ -70,7 +70,7 @@ class DFlashAttention(nn.Module):
         self.q_norm = RMSNorm(d, eps=config.rms_norm_eps)
         self.k_norm = RMSNorm(d, eps=config.rms_norm_eps)
         inv, self.rope_scaling = rope_inverse_frequencies(d, config.rope_parameters_resolved)
-        self.register_buffer("inv_freq", torch.tensor(inv, dtype=torch.float32), persistent=False)
+        self.rope_freqs = RopeFrequencies(inv)
         self.eps = config.rms_norm_eps
         self.scale = d ** -0.5
 
@@ -82,8 +82,9 @@ class DFlashAttention(nn.Module):
         kv = fused_linear(torch.cat([ctx, x], 0), [self.k_proj.weight, self.v_proj.weight])
         k = kv[:, : hk * d].reshape(T + Q, hk, d)
         v = kv[:, hk * d:].view(T + Q, hk, d)
-        q = qk_norm_rope(q, self.q_norm.weight, q_pos, self.inv_freq, self.eps, self.rope_scaling)
-        k = qk_norm_rope(k, self.k_norm.weight, kv_pos, self.inv_freq, self.eps, self.rope_scaling)
+        inv_freq = self.rope_freqs.get(x.device)
+        q = qk_norm_rope(q, self.q_norm.weight, q_pos, inv_freq, self.eps, self.rope_scaling)
+        k = qk_norm_rope(k, self.k_norm.weight, kv_pos, inv_freq, self.eps, self.rope_scaling)
         if attn_override is not None:
             o = attn_override(self, q, k, v, intervals)
         else:

@@ -27,7 +27,7 @@ import torch.nn.functional as F
 
 from aspec_b200.ops.attention import interval_attention_reference
 from aspec_b200.ops.norm import rmsnorm_reference
-from aspec_b200.ops.rope import qk_norm_rope_reference
+from aspec_b200.ops.rope import RopeFrequencies, qk_norm_rope_reference
 
 
 @dataclass
@@ -124,8 +124,8 @@ class DenseTarget(nn.Module):
         self.layers = nn.ModuleList([_Layer(cfg, i) for i in range(cfg.num_hidden_layers)])
         self.norm = nn.Parameter(torch.ones(cfg.hidden_size))
         self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size))
-        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.float32) / cfg.head_dim))
-        self.register_buffer("inv_freq", inv, persistent=False)
+        self.rope_freqs = RopeFrequencies(
+            [cfg.rope_theta ** (-(2.0 * i) / cfg.head_dim) for i in range(cfg.head_dim // 2)])
         self.requires_grad_(False)
 
     @torch.no_grad()
@@ -156,6 +156,7 @@ class DenseTarget(nn.Module):
         cfg = self.config
         hq, hk, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         T = x.shape[0]
+        inv_freq = self.rope_freqs.get(x.device)
         if self._use_kernels(x):
             from aspec_b200.ops import attention_sm100 as A
             from aspec_b200.ops import elementwise_sm100 as E
@@ -166,16 +167,16 @@ class DenseTarget(nn.Module):
             v = qkv[:, (hq + hk) * d:].view(T, hk, d)
             qn = layer.q_norm if cfg.qk_norm else None
             kn = layer.k_norm if cfg.qk_norm else None
-            q, _ = E.qk_norm_rope_fwd(q.contiguous(), qn, positions, self.inv_freq, cfg.rms_norm_eps, 1.0)
-            k, _ = E.qk_norm_rope_fwd(k.contiguous(), kn, positions, self.inv_freq, cfg.rms_norm_eps, 1.0)
+            q, _ = E.qk_norm_rope_fwd(q.contiguous(), qn, positions, inv_freq, cfg.rms_norm_eps, 1.0)
+            k, _ = E.qk_norm_rope_fwd(k.contiguous(), kn, positions, inv_freq, cfg.rms_norm_eps, 1.0)
             o, _ = A.forward(q, k, v, intervals, d ** -0.5)
             return o.view(T, hq * d)
         qkv = F.linear(x, layer.qkv_proj)
         q = qkv[:, : hq * d].reshape(T, hq, d)
         k = qkv[:, hq * d:(hq + hk) * d].reshape(T, hk, d)
         v = qkv[:, (hq + hk) * d:].reshape(T, hk, d)
-        q = qk_norm_rope_reference(q, layer.q_norm if cfg.qk_norm else None, positions, self.inv_freq, cfg.rms_norm_eps)
-        k = qk_norm_rope_reference(k, layer.k_norm if cfg.qk_norm else None, positions, self.inv_freq, cfg.rms_norm_eps)
+        q = qk_norm_rope_reference(q, layer.q_norm if cfg.qk_norm else None, positions, inv_freq, cfg.rms_norm_eps)
+        k = qk_norm_rope_reference(k, layer.k_norm if cfg.qk_norm else None, positions, inv_freq, cfg.rms_norm_eps)
         o, _ = interval_attention_reference(q, k, v, intervals, d ** -0.5)
         return o.reshape(T, hq * d)
 

@@ -12,6 +12,23 @@ from typing import Optional
 import torch
 
 
+class RopeFrequencies:
+    """Inverse frequencies kept in fp32 whatever dtype the owning module is cast to (a registered buffer
+    would be rounded to bf16 by ``module.to(torch.bfloat16)`` and shift every rotation angle)."""
+
+    def __init__(self, inv_freq):
+        self.values = [float(v) for v in inv_freq]
+        self._cache = {}
+
+    def get(self, device) -> torch.Tensor:
+        key = str(device)
+        t = self._cache.get(key)
+        if t is None:
+            t = torch.tensor(self.values, dtype=torch.float32, device=device)
+            self._cache[key] = t
+        return t
+
+
 def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, scaling: float = 1.0):
     ang = positions.float()[:, None] * inv_freq.float()[None]
     return torch.cos(ang) * scaling, torch.sin(ang) * scaling

@@ -14,7 +14,9 @@ def build_training_model(draft_config, args: Mapping[str, Any], device, dtype) -
     cfg = draft_config if hasattr(draft_config, "to_dict") else AutoDraftModelConfig.from_dict(draft_config)
     algorithm = resolve_draft_algorithm(cfg.to_dict())
     g = args.get
-    draft = AutoEagle3DraftModel.from_config(cfg).to(device=device, dtype=dtype)
+    with torch.device(device):          # allocate and initialise on the target device, not through host memory
+        draft = AutoEagle3DraftModel.from_config(cfg)
+    draft = draft.to(dtype=dtype)
     if g("gradient_checkpointing"):
         draft.gradient_checkpointing = True
     common = dict(attention_backend=g("attention_backend", "sm100_flash"),

@@ -45,6 +45,10 @@ def parse_args():
     ap.add_argument("--pool", type=int, default=0, help="distinct documents per rank (0 = accum * 2)")
     ap.add_argument("--small", action="store_true", help="tiny shapes (CPU smoke / debugging only; not a valid bench)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--mode", default="draft", choices=["draft", "online"],
+                    help="draft: Draft-only data parallel (the `value`); online: Target + Draft ranks with feature rings")
+    ap.add_argument("--targets", type=int, default=0, help="online: Target GPUs (default N // 2)")
+    ap.add_argument("--target-layers-total", type=int, default=36)
     return ap.parse_args()
 
 
@@ -108,7 +112,9 @@ def build_ours(args, device, dtype):
     cfg = DSparkConfig(num_hidden_layers=args.layers, num_target_layers=n_tl, target_layer_ids=ids,
                        target_num_hidden_layers=36, rope_theta=1e6, max_position_embeddings=40960, **dims)
     torch.manual_seed(1234)
-    draft = DSparkDraftModel(cfg).to(device=device, dtype=dtype)
+    with torch.device(device):
+        draft = DSparkDraftModel(cfg)
+    draft = draft.to(dtype=dtype)
     model = DSparkModel(draft, block_size=7, num_anchors=512 if not args.small else 64,
                         loss_decay_gamma=4.0, ce_loss_alpha=0.1, l1_loss_alpha=0.9, confidence_head_alpha=1.0)
     lm_head = (torch.randn(cfg.vocab_size, cfg.hidden_size, device=device, dtype=torch.float32) * 0.02).to(dtype)
@@ -247,6 +253,59 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_online(args) -> dict:
+    """Online training on N GPUs of this node: T Target ranks prefill and store captured layers into the
+    rings of D Draft ranks, which train.  Steady-window input tokens/s over committed work."""
+    import tempfile
+
+    import torch
+    from aspec_b200.config.draft_config import DSparkConfig
+    from aspec_b200.train_entry import train_async_no_generation
+    n = args.gpus
+    T = args.targets or max(n // 2, 1)
+    D = n - T
+    if D < 1:
+        raise SystemExit("online mode needs at least one Draft GPU")
+    small = args.small
+    dims = (dict(hidden_size=256, intermediate_size=512, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+                 vocab_size=4096, target_hidden_size=256, markov_rank=32, mask_token_id=4095) if small else
+            dict(hidden_size=4096, intermediate_size=12288, num_attention_heads=32, num_key_value_heads=8,
+                 vocab_size=151936, target_hidden_size=4096, markov_rank=256, mask_token_id=151669))
+    L = 4 if small else args.target_layers_total
+    ids = [0, 1, 3] if small else [2, 18, 33]
+    draft = DSparkConfig(num_hidden_layers=args.layers, num_target_layers=3, target_layer_ids=ids,
+                         target_num_hidden_layers=L, rope_theta=1e6, max_position_embeddings=40960, **dims).to_dict()
+    steps = args.warmup + args.steps
+    out_dir = tempfile.mkdtemp(prefix="aspec_online_")
+    flat = dict(
+        inference_engine_type="native", inference_num_gpus=T, training_num_gpus_per_node=D, training_num_nodes=1,
+        world_size=D, draft_context_parallel_size=1, micro_batch_size=1, draft_accumulation_steps=args.accum,
+        max_seq_length=args.max_len, num_train_steps=steps, learning_rate=6e-4, min_lr=6e-5, weight_decay=0.0,
+        max_grad_norm=1.0, warmup_ratio=0.04, lr_decay_style="cosine", seed=0, dspark_block_size=7,
+        dspark_num_anchors=64 if small else 512, dspark_loss_decay_gamma=4.0, dspark_ce_loss_alpha=0.1,
+        dspark_l1_loss_alpha=0.9, dspark_confidence_head_alpha=1.0, train_data_path="synthetic",
+        synthetic_num_documents=max(steps * args.accum * D * 2, 64), synthetic_min_length=min(args.min_len, args.max_len),
+        synthetic_max_length=args.max_len, synthetic_vocab_size=dims["vocab_size"] - 1024, shuffle_dataset=True,
+        length_group_size=1, transport_destination_ring_slots=max(2 * args.accum + 2, 4), inference_batch_size=1,
+        store_last_hidden_states=True, output_dir=out_dir, save_interval=0, save_final_checkpoint=False,
+        performance_warmup_steps=args.warmup, performance_drain_steps=0, optimizer_step_timeout_seconds=900.0,
+        target_model_config={"model_type": "qwen3", "hidden_size": dims["hidden_size"], "intermediate_size": dims["intermediate_size"],
+                             "num_hidden_layers": L, "num_attention_heads": dims["num_attention_heads"],
+                             "num_key_value_heads": dims["num_key_value_heads"], "head_dim": 128,
+                             "vocab_size": dims["vocab_size"], "rope_theta": 1e6},
+        force_cpu=not torch.cuda.is_available(), num_epochs=1)
+    summary = train_async_no_generation(flat, draft, log=lambda m: None)
+    w = summary["window"]
+    eng = summary.get("engines", [])
+    return {"value": w.get("tokens_per_second"), "unit": "tokens/s", "targets": T, "drafts": D,
+            "steady_steps": w.get("steps"), "steady_tokens": w.get("tokens"), "steady_seconds": w.get("seconds"),
+            "documents_per_update": args.accum * D, "ledger_validated": summary["ledger"]["validated"],
+            "vs_baseline_8gpu": (w.get("tokens_per_second") / BASELINE_8GPU) if (w.get("valid") and n == 8) else None,
+            "target_busy_seconds": [e.get("busy_seconds") for e in eng],
+            "timing": "steady window: from completion of warm-up update W to the last optimizer completion; each "
+                      "completion is observed after a device-to-host read on every Draft rank"}
+
+
 def run_reference(args):
     from baseline import reference_arm
     reference_arm.main(args)
@@ -256,5 +315,11 @@ if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.mode == "online":
+        # one driver process owns the node: under torchrun only rank 0 drives, the other ranks just exit
+        if int(os.environ.get("RANK", "0")) == 0:
+            res = run_online(a)
+            print(json.dumps({"metric": "online steady-window input tokens/s, Qwen3-8B DSpark 4K", "n_gpus": a.gpus,
+                              "higher_is_better": True, "dtype": "bf16", "impl": "ours", **res}))
     else:
         run_ours(a)
