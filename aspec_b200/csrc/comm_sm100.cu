@@ -7,6 +7,8 @@
 // context usable.
 #include "common.cuh"
 
+#include <string.h>
+
 namespace ab {
 
 // flag[0] = value, ordered after every earlier write of this GPU (release at system scope).
@@ -135,3 +137,53 @@ int ab_peer_reduce(const void* const* peer_ptrs, int n_peers, void* out, long lo
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 }  // extern "C"
+
+// Lets kernels running on `local` dereference memory of `peer` (both GPUs of this node).  IPC-mapped or
+// cudaMalloc'ed peer memory is only reachable from a kernel once the local context enabled peer access.
+// Returns 0 on success or when access was already enabled, -1 when the pair has no peer path.
+extern "C" int ab_enable_peer_access(int local, int peer) {
+  if (local == peer) return 0;
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, local, peer) != cudaSuccess || !can) return -1;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (cudaSetDevice(local) != cudaSuccess) return -2;
+  cudaError_t rc = cudaDeviceEnablePeerAccess(peer, 0);
+  if (rc == cudaErrorPeerAccessAlreadyEnabled) {
+    cudaGetLastError();   // clear the sticky-free error state
+    rc = cudaSuccess;
+  }
+  if (prev >= 0) cudaSetDevice(prev);
+  return rc == cudaSuccess ? 0 : -3;
+}
+
+// ---------------------------------------------------------------- symmetric memory -------------
+// Buffers that other processes of this node map and that kernels of other GPUs read or write.
+// They are allocated here with cudaMalloc (one allocation = one IPC handle, offset zero) and opened in
+// the importing process with the *accessing* device current and lazy peer access, so the mapping is
+// created in the context whose kernels will dereference it.
+extern "C" int ab_symm_alloc(unsigned long long bytes, void** ptr) {
+  if (!ptr || bytes == 0) return -10;
+  if (cudaMalloc(ptr, bytes) != cudaSuccess) return -5;
+  if (cudaMemset(*ptr, 0, bytes) != cudaSuccess) return -6;
+  return cudaDeviceSynchronize() == cudaSuccess ? 0 : -7;
+}
+extern "C" int ab_symm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
+extern "C" int ab_ipc_export(void* ptr, unsigned char* handle64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) return -1;
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+extern "C" int ab_ipc_import(const unsigned char* handle64, int accessing_device, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (cudaSetDevice(accessing_device) != cudaSuccess) return -2;
+  const cudaError_t rc = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (prev >= 0) cudaSetDevice(prev);
+  return rc == cudaSuccess ? 0 : -3;
+}
+extern "C" int ab_ipc_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }

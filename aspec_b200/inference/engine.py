@@ -103,11 +103,14 @@ class NativeTargetEngine(InferenceEngine):
     def init(self) -> None:
         pass
 
-    def lm_head(self) -> torch.Tensor:
-        return self.model.lm_head.detach()
+    def lm_head(self, copies: int = 1) -> list:
+        """Relayable handles (one per trainer) of the frozen output head."""
+        from aspec_b200.transport.feature_ring import export_tensor
+        return [export_tensor(self.model.lm_head.detach()) for _ in range(copies)]
 
-    def embedding(self) -> torch.Tensor:
-        return self.model.embed_tokens.weight.detach()
+    def embedding(self, copies: int = 1) -> list:
+        from aspec_b200.transport.feature_ring import export_tensor
+        return [export_tensor(self.model.embed_tokens.weight.detach()) for _ in range(copies)]
 
     @torch.no_grad()
     def generate(self, requests: Sequence[RowRequest]) -> List[InferenceOutput]:

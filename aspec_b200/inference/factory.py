@@ -37,22 +37,22 @@ def create_engines(flat: Dict, draft_config: dict, layer_ids: List[int], target_
                                 int(flat.get("seed", 0)), f"target{i}", bool(flat.get("device_flags", False)),
                                 flat.get("target_weights_path"), fault, name=f"target{i}")
                    for i, dev in enumerate(target_devices)]
-        for e in engines:
+        for i, e in enumerate(engines):
             e.wait_ready()
-            e.call("attach_rings", ring_handles, timeout=300)
-        head = engines[0].call("lm_head", timeout=300)
-        embedding = engines[0].call("embedding", timeout=300)
+            e.call("attach_rings", {c: hs[i] for c, hs in ring_handles.items()}, timeout=300)
+        n_trainers = len(ring_handles)
+        head = engines[0].call("lm_head", n_trainers, timeout=300)
+        embedding = engines[0].call("embedding", n_trainers, timeout=300)
         return engines, head, embedding
     if kind == "synthetic":
         from aspec_b200.inference.engine import SyntheticEngine
-        dev = next(iter(ring_handles.values()))["buffer"].device
-        eng = SyntheticEngine(layer_ids, hidden, str(dev), seed=int(flat.get("seed", 0)),
+        eng = SyntheticEngine(layer_ids, hidden, "cpu", seed=int(flat.get("seed", 0)),
                               delay_s=float(flat.get("producer_delay_seconds", 0.0)), fail_after=fault)
-        eng.attach_rings(ring_handles)
+        eng.attach_rings({c: hs[0] for c, hs in ring_handles.items()})
         return [eng], None, None
     if kind == "offline":
         from aspec_b200.inference.engine import OfflineReplayEngine
         eng = OfflineReplayEngine(flat["offline_feature_dir"])
-        eng.attach_rings(ring_handles)
+        eng.attach_rings({c: hs[0] for c, hs in ring_handles.items()})
         return [eng], None, None
     raise ValueError(f"unknown inference engine type {kind!r}")

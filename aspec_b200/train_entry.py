@@ -105,9 +105,11 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
     try:
         for t in trainers:
             t.wait_ready()
-        handles = {r: trainers[r].call("ring_handle", timeout=120) for r in range(world)}
+        n_producers = max(len(target_devs), 1)
+        handles = {r: trainers[r].call("ring_handle", n_producers, timeout=120) for r in range(world)}
         engines, head, embedding = create_engines(flat, draft_config, layer_ids, target_devs, handles)
-        for fut in [t.call_async("set_head", head, embedding) for t in trainers]:
+        pick = lambda v, r: v[r] if isinstance(v, list) else v
+        for fut in [t.call_async("set_head", pick(head, r), pick(embedding, r)) for r, t in enumerate(trainers)]:
             fut.get(timeout=600)
         start_step = 0
         controller = TrainingController(args, dp_size=dp, consumers_per_row=cp, algorithm=algorithm)

@@ -58,16 +58,22 @@ class TrainerActor:
         self._pending_releases: List[tuple] = []
 
     # -- setup ------------------------------------------------------------------------------------
-    def ring_handle(self) -> dict:
-        return self.ring.export()
+    def ring_handle(self, copies: int = 1) -> list:
+        """One handle per producer process that will map this ring."""
+        return [self.ring.export() for _ in range(max(int(copies), 1))]
 
     def set_head(self, lm_head: Optional[torch.Tensor], embedding: Optional[torch.Tensor] = None) -> None:
         """Frozen Target output head (and embedding).  ``None`` -> deterministic random init (offline runs)."""
+        from aspec_b200.transport.feature_ring import import_tensor
         cfg = self.draft_config
+        if isinstance(lm_head, dict):
+            lm_head = import_tensor(lm_head)
+        if isinstance(embedding, dict):
+            embedding = import_tensor(embedding)
         if lm_head is None:
             g = torch.Generator().manual_seed(1234)
             lm_head = torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * 0.02
-        self.lm_head = lm_head.to(self.device, self.dtype)
+        self.lm_head = lm_head.to(self.device, self.dtype).clone()     # own copy: the Target may live elsewhere
         draft = self.model.draft_model
         if embedding is not None and hasattr(draft, "load_embedding"):
             draft.load_embedding(embedding.to(self.device))

@@ -96,6 +96,41 @@ class FeatureDescriptor:
                 "last_hidden_states": (self.n_tokens, self.hidden)}
 
 
+def export_tensor(t: torch.Tensor) -> dict:
+    """Plain-data handle of a tensor for ONE receiving process.
+
+    CUDA: the IPC handle of the storage (``_share_cuda_``); being plain data it can be relayed by a third
+    process (the driver), which ``torch.multiprocessing``'s own tensor pickling does not allow.  Call once
+    per receiver: every export takes one reference that the receiver's import releases.
+    CPU: the tensor itself, in shared memory.
+    """
+    if not t.is_cuda:
+        return {"kind": "cpu", "tensor": t if t.is_shared() else t.share_memory_()}
+    return {"kind": "cuda", "share": tuple(t.untyped_storage()._share_cuda_()), "dtype": str(t.dtype).split(".")[1],
+            "shape": tuple(t.shape), "stride": tuple(t.stride()), "offset": t.storage_offset()}
+
+
+def ensure_peer_access(local_device, peer_device) -> None:
+    """Kernels on ``local_device`` are about to store into memory of ``peer_device``."""
+    local, peer = torch.device(local_device), torch.device(peer_device)
+    if local.type != "cuda" or peer.type != "cuda" or local.index == peer.index:
+        return
+    from aspec_b200 import _native
+    rc = _native.kernels().ab_enable_peer_access(int(local.index), int(peer.index))
+    if rc != 0:
+        raise RuntimeError(f"GPU {local.index} cannot open peer access to GPU {peer.index} (code {rc})")
+
+
+def import_tensor(meta: dict) -> torch.Tensor:
+    if meta["kind"] == "cpu":
+        return meta["tensor"]
+    storage = torch.UntypedStorage._new_shared_cuda(*meta["share"])
+    dtype = getattr(torch, meta["dtype"])
+    out = torch.empty(0, dtype=dtype, device=storage.device)
+    out.set_(storage, meta["offset"], meta["shape"], meta["stride"])
+    return out
+
+
 class _SlotViews:
     def __init__(self, buffer: torch.Tensor, flags: torch.Tensor, layout: SlotLayout, slots: int):
         self.buffer, self.flags, self.layout, self.slots = buffer, flags, layout, slots
@@ -125,19 +160,21 @@ class FeatureRing(_SlotViews):
 
     def __init__(self, slots: int, layout: SlotLayout, device, run_id: str = "run", attempt_id: str = "0",
                  consumer: int = 0):
+        from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
         device = torch.device(device)
-        buffer = torch.zeros(slots * layout.slot_bytes, dtype=torch.uint8, device=device)
-        flags = torch.zeros(slots, dtype=torch.int64, device=device)
-        if device.type == "cpu":
-            buffer.share_memory_()
-            flags.share_memory_()
+        # one allocation: [slots * slot_bytes of payload][slots int64 flag words]
+        payload = slots * layout.slot_bytes
+        self._symm = SymmetricBuffer.allocate(payload + _up(slots * 8), device)
+        raw = self._symm.tensor
+        buffer = raw[:payload]
+        flags = raw[payload:payload + slots * 8].view(torch.int64)
         super().__init__(buffer, flags, layout, slots)
         self.run_id, self.attempt_id, self.consumer = run_id, attempt_id, consumer
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
     def export(self) -> dict:
-        """Picklable handle; sending it through a ``torch.multiprocessing`` queue maps the memory in the peer."""
-        return {"buffer": self.buffer, "flags": self.flags, "layout": self.layout.to_dict(), "slots": self.slots,
+        """Handle for one producer process; it maps this ring's memory when turned into a ``RemoteRing``."""
+        return {"memory": self._symm.export(), "layout": self.layout.to_dict(), "slots": self.slots,
                 "run_id": self.run_id, "attempt_id": self.attempt_id, "consumer": self.consumer}
 
     def read(self, key: str, device_flags: bool = False, wait_limit_ms: float = 2000.0) -> Dict[str, torch.Tensor]:
@@ -173,7 +210,15 @@ class RemoteRing(_SlotViews):
     """Producer side: the consumer's ring mapped into this process."""
 
     def __init__(self, handle: dict):
-        super().__init__(handle["buffer"], handle["flags"], SlotLayout(**handle["layout"]), handle["slots"])
+        from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
+        layout = SlotLayout(**handle["layout"])
+        slots = handle["slots"]
+        # mapped with this process's GPU current: the ring then looks like local memory to torch and to
+        # the kernels, and every access crosses NVLink
+        self._symm = SymmetricBuffer.open(handle["memory"])
+        raw = self._symm.tensor
+        payload = slots * layout.slot_bytes
+        super().__init__(raw[:payload], raw[payload:payload + slots * 8].view(torch.int64), layout, slots)
         self.run_id, self.attempt_id, self.consumer = handle["run_id"], handle["attempt_id"], handle["consumer"]
 
     def descriptor(self, slot: int, generation: int, n_tokens: int, layer_ids) -> FeatureDescriptor:
