@@ -349,8 +349,8 @@ __global__ void __launch_bounds__(512) vocab_loss_kernel(const VocabLossParams p
   constexpr float L2E = 1.4426950408889634f;
 
   // pass A: l1 = sum|p-q|, c = sum p*sign(p-q), cross = sum q*s, argmax
-  float l1 = 0.f, c = 0.f, cross = 0.f, best = -INFINITY;
-  int best_i = 0x7fffffff;
+  float l1 = 0.f, c = 0.f, cross = 0.f, best = -INFINITY, tbest = -INFINITY;
+  int best_i = 0x7fffffff, tbest_i = 0x7fffffff;
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     float s[8], t[8];
     unpack8(reinterpret_cast<const uint4*>(srow)[i], s);
@@ -360,6 +360,10 @@ __global__ void __launch_bounds__(512) vocab_loss_kernel(const VocabLossParams p
       if (s[j] > best) {
         best = s[j];
         best_i = i * 8 + j;
+      }
+      if (trow && p.mode == 1 && t[j] > tbest) {
+        tbest = t[j];
+        tbest_i = i * 8 + j;
       }
       if (trow) {
         const float pp = fast_exp2((s[j] - ls) * L2E);
@@ -384,12 +388,23 @@ __global__ void __launch_bounds__(512) vocab_loss_kernel(const VocabLossParams p
   __syncthreads();
   int gidx = 0x7fffffff;
   for (int wi = 0; wi < (int)(blockDim.x >> 5); ++wi) gidx = min(gidx, iscratch[wi]);
+  int tidx = 0x7fffffff;
+  if (p.mode == 1 && trow) {   // arg-max of the teacher row (EAGLE accuracy compares the two arg-maxima)
+    const float gt = block_reduce<true>(tbest, scratch);
+    int tc = (tbest == gt) ? tbest_i : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tc = min(tc, __shfl_xor_sync(0xffffffffu, tc, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) iscratch[threadIdx.x >> 5] = tc;
+    __syncthreads();
+    for (int wi = 0; wi < (int)(blockDim.x >> 5); ++wi) tidx = min(tidx, iscratch[wi]);
+  }
 
-  const float s_label = __bfloat162float(srow[label]);
+  const float s_label = (label >= 0 && label < p.V) ? __bfloat162float(srow[label]) : 0.f;
   if (threadIdx.x == 0) {
     p.ce_out[r] = p.mode == 1 ? (ls - cross) : (ls - s_label);
     p.l1_out[r] = l1;
-    p.correct_out[r] = (gidx == (int)label) ? 1.f : 0.f;
+    p.correct_out[r] = (gidx == (p.mode == 1 && trow ? tidx : (int)label)) ? 1.f : 0.f;
   }
   if (!p.write_grad) return;
   __syncthreads();

@@ -1,0 +1,146 @@
+"""EAGLE3 draft: one decoder layer ("midlayer") fed ``cat(norm(embed), norm(hidden))``, own LM head.
+
+Architecture (reference: aspec/models/draft/llama3_eagle.py:2331-2484): ``fc: Linear(K * Dt -> D)`` turns the
+captured Target layers into the depth-0 hidden state; the attention input is the concatenation of the
+normalised token embedding and the normalised hidden state (width ``2D``); the MLP follows
+``post_attention_layernorm``; ``norm`` + ``lm_head`` (optionally over a pruned draft vocabulary with
+``t2d`` / ``d2t``) produce logits.
+
+The test-time-training recurrence is expressed over packed tokens with the interval attention kernel:
+keys of depth 0 are laid out first (``T`` rows, causal inside each document) and the keys of the later
+depths are stored token-major right after them, so that the "one diagonal key per earlier depth" of
+query ``t`` (aspec/models/draft/llama3_eagle.py:1229-1263) is the contiguous range
+``[T + t * (L - 1), T + t * (L - 1) + depth)`` - exactly the kernel's second interval.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from aspec_b200.config.draft_config import Eagle3Config
+from aspec_b200.config.rope import rope_inverse_frequencies
+from aspec_b200.models.draft.base import Eagle3DraftModel
+from aspec_b200.models.draft.dflash import DFlashMLP, _Weight
+from aspec_b200.ops.attention import interval_attention
+from aspec_b200.ops.fused_params import allocate_adjacent, fused_linear
+from aspec_b200.ops.linear import Linear
+from aspec_b200.ops.norm import RMSNorm
+from aspec_b200.ops.rope import RopeFrequencies, qk_norm_rope
+
+
+class EagleAttention(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        D, d = config.hidden_size, config.head_dim
+        self.num_heads, self.num_kv_heads, self.head_dim = config.num_attention_heads, config.num_key_value_heads, d
+        qw, kw, vw = allocate_adjacent([(self.num_heads * d, 2 * D), (self.num_kv_heads * d, 2 * D),
+                                        (self.num_kv_heads * d, 2 * D)])
+        for w in (qw, kw, vw):
+            nn.init.normal_(w, std=0.02)
+        self.q_proj, self.k_proj, self.v_proj = _Weight(qw), _Weight(kw), _Weight(vw)
+        self.o_proj = Linear(self.num_heads * d, D)
+        params = {"rope_type": "default", "rope_theta": float(config.rope_theta)}
+        scaling = getattr(config, "rope_scaling", None)
+        if scaling:
+            params.update(scaling)
+            params["rope_type"] = scaling.get("rope_type", scaling.get("type", "default"))
+            params.setdefault("original_max_position_embeddings", config.max_position_embeddings)
+        inv, self.rope_scaling = rope_inverse_frequencies(d, params)
+        self.rope_freqs = RopeFrequencies(inv)
+        self.scale = d ** -0.5
+
+    def project(self, x: torch.Tensor, positions: torch.Tensor):
+        """``x [T, 2D]`` -> rotated ``q [T, Hq, d]``, ``k [T, Hkv, d]`` and ``v [T, Hkv, d]``."""
+        T = x.shape[0]
+        hq, hk, d = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = fused_linear(x, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight])
+        q = qkv[:, : hq * d].reshape(T, hq, d)
+        k = qkv[:, hq * d:(hq + hk) * d].reshape(T, hk, d)
+        v = qkv[:, (hq + hk) * d:].reshape(T, hk, d)
+        inv = self.rope_freqs.get(x.device)
+        q = qk_norm_rope(q, None, positions, inv, 0.0, self.rope_scaling)
+        k = qk_norm_rope(k, None, positions, inv, 0.0, self.rope_scaling)
+        return q, k, v
+
+
+class EagleDecoderLayer(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.self_attn = EagleAttention(config)
+        self.mlp = DFlashMLP(config.hidden_size, config.intermediate_size)
+        self.input_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.hidden_norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+
+class LlamaForCausalLMEagle3(Eagle3DraftModel):
+    config_class = Eagle3Config
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        D, Dt = config.hidden_size, config.target_hidden_size
+        self.num_aux = int(config.num_aux_hidden_states)
+        self.fc = Linear(self.num_aux * Dt, D)
+        self.fc_norm = (nn.ModuleList([RMSNorm(Dt, eps=config.rms_norm_eps) for _ in range(self.num_aux)])
+                        if getattr(config, "fc_norm", False) else None)
+        self.embed_tokens = nn.Embedding(config.vocab_size, D)
+        self.embed_tokens.weight.requires_grad_(False)
+        self.midlayer = EagleDecoderLayer(config)
+        self.norm = RMSNorm(D, eps=config.rms_norm_eps)
+        self.lm_head = Linear(D, config.draft_vocab_size)
+        self.init_vocab_buffers(config.vocab_size, config.draft_vocab_size)
+        self.norm_output = bool(getattr(config, "norm_output", False))
+        self.gradient_checkpointing = False
+
+    # -- pieces used by the training wrapper -------------------------------------------------------
+    def project_hidden_states(self, features: torch.Tensor) -> torch.Tensor:
+        if self.fc_norm is not None:
+            parts = features.split(self.config.target_hidden_size, dim=-1)
+            features = torch.cat([n(p) for n, p in zip(self.fc_norm, parts)], -1)
+        return self.fc(features)
+
+    def embed_input_ids(self, ids: torch.Tensor) -> torch.Tensor:
+        return self.embed_tokens(ids.clamp(0, self.config.vocab_size - 1))
+
+    def backbone(self, embeds: torch.Tensor, hidden: torch.Tensor, positions: torch.Tensor, depth: int,
+                 cache: Optional[Tuple[torch.Tensor, torch.Tensor, List, List]], doc_start: torch.Tensor,
+                 ttt_length: int):
+        """One TTT depth over ``T`` packed tokens.  Returns the new hidden state and the extended cache."""
+        layer = self.midlayer
+        T = hidden.shape[0]
+        x = torch.cat([layer.input_layernorm(embeds), layer.hidden_norm(hidden)], -1)
+        q, k, v = layer.self_attn.project(x, positions + depth)
+        L1 = max(ttt_length - 1, 1)
+        dev = hidden.device
+        t = torch.arange(T, device=dev)
+        if depth == 0:
+            k0, v0, dk, dv = k, v, [], []
+        else:
+            k0, v0, dk, dv = cache
+            dk, dv = dk + [k], dv + [v]
+        if dk:
+            pad = [torch.zeros_like(k)] * (L1 - len(dk))
+            k_all = torch.cat([k0, torch.stack(dk + pad, 1).reshape(T * L1, *k.shape[1:])])
+            v_all = torch.cat([v0, torch.stack(dv + pad, 1).reshape(T * L1, *v.shape[1:])])
+        else:
+            k_all, v_all = k0, v0
+        intervals = torch.stack([doc_start, t + 1, T + t * L1, T + t * L1 + depth], -1).to(torch.int32)
+        o, _ = interval_attention(q, k_all, v_all, intervals, layer.self_attn.scale)
+        h = hidden + layer.self_attn.o_proj(o.reshape(T, -1))
+        h = h + layer.mlp(layer.post_attention_layernorm(h))
+        return h, (k0, v0, dk, dv)
+
+    def next_depth_hidden(self, hidden: torch.Tensor) -> torch.Tensor:
+        return self.norm(hidden) if self.norm_output else hidden
+
+    def get_lm_head_params(self):
+        return self.norm.weight, self.lm_head.weight, self.norm.eps
+
+    def get_lm_head_up_weight(self):
+        return None
+
+    def commit_router_load(self) -> None:
+        pass

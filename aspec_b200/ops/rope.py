@@ -78,7 +78,7 @@ class _QKNormRopeFn(torch.autograd.Function):
 def qk_norm_rope(x: torch.Tensor, norm_weight: Optional[torch.Tensor], positions: torch.Tensor,
                  inv_freq: torch.Tensor, eps: float, scaling: float = 1.0) -> torch.Tensor:
     """``x [N, H, d]`` -> normalised + rotated, same shape and dtype."""
-    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] in (64, 128, 256) and norm_weight is not None:
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] in (64, 128, 256) and x.numel():
         holder = norm_weight if isinstance(norm_weight, torch.nn.Parameter) else None
         return _QKNormRopeFn.apply(x.contiguous(), norm_weight, positions.contiguous().to(torch.int32),
                                    inv_freq.float().contiguous(), eps, scaling, holder)

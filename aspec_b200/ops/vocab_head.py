@@ -27,23 +27,25 @@ import torch.nn.functional as F
 
 
 def head_loss_reference(hidden, lm_w, labels, weight, *, prev_emb=None, markov_w2=None,
-                        teacher_hidden=None, t_index=None, a_ce=1.0, a_l1=0.0, mode=0):
+                        teacher_hidden=None, t_index=None, a_ce=1.0, a_l1=0.0, mode=0, teacher_w=None):
     """fp32 PyTorch statement of the op.  Returns (numerator, ce[R], l1[R], correct[R])."""
     logits = F.linear(hidden.float(), lm_w.float())
     if prev_emb is not None:
         logits = logits + F.linear(prev_emb.float(), markov_w2.float())
     R = logits.shape[0]
     l1 = logits.new_zeros(R)
+    tw = lm_w if teacher_w is None else teacher_w
     if mode == 1:
-        t = F.linear(teacher_hidden.float(), lm_w.float())
+        t = F.linear(teacher_hidden.float(), tw.float())
         if t_index is not None:
             t = t[t_index.long()]
         q = torch.softmax(t, -1)
         ce = torch.logsumexp(logits, -1) - (q * logits).sum(-1)
+        labels = t.argmax(-1)
     else:
         ce = F.cross_entropy(logits, labels.long(), reduction="none") if R else logits.new_zeros(0)
         if teacher_hidden is not None:
-            t = F.linear(teacher_hidden.float(), lm_w.float())
+            t = F.linear(teacher_hidden.float(), tw.float())
             if t_index is not None:
                 t = t[t_index.long()]
             l1 = (torch.softmax(logits, -1) - torch.softmax(t, -1)).abs().sum(-1)
@@ -55,14 +57,14 @@ def head_loss_reference(hidden, lm_w, labels, weight, *, prev_emb=None, markov_w
 class _HeadLossFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden, lm_w, prev_emb, markov_w2, teacher_hidden, t_index, labels, weight,
-                a_ce, a_l1, mode, w2_holder):
+                a_ce, a_l1, mode, w2_holder, teacher_w, lm_holder):
         from aspec_b200.ops import elementwise_sm100 as E
         from aspec_b200.ops import gemm as G
         R, D = hidden.shape
         V = lm_w.shape[0]
         dev = hidden.device
         nt = (V + G.TILE_N - 1) // G.TILE_N
-        need_grad = ctx.needs_input_grad[0] or ctx.needs_input_grad[2] or ctx.needs_input_grad[3]
+        need_grad = any(ctx.needs_input_grad[i] for i in (0, 1, 2, 3))
         stats = torch.empty(nt, R, 2, dtype=torch.float32, device=dev)
         logits = torch.empty(R, V, dtype=torch.bfloat16, device=dev)
         G.gemm(hidden, lm_w, a2=prev_emb, b2=markov_w2, out=logits, epilogue=G.EPI_ROWSTATS, stats=stats)
@@ -72,13 +74,15 @@ class _HeadLossFn(torch.autograd.Function):
             Tt = teacher_hidden.shape[0]
             t_stats = torch.empty(nt, Tt, 2, dtype=torch.float32, device=dev)
             t_logits = torch.empty(Tt, V, dtype=torch.bfloat16, device=dev)
-            G.gemm(teacher_hidden, lm_w, out=t_logits, epilogue=G.EPI_ROWSTATS, stats=t_stats)
+            G.gemm(teacher_hidden, lm_w if teacher_w is None else teacher_w, out=t_logits,
+                   epilogue=G.EPI_ROWSTATS, stats=t_stats)
             lse_t = E.merge_rowstats(t_stats)
         ce, l1, correct = E.vocab_loss(logits, t_logits, lse_s, lse_t, t_index, labels, weight,
                                        mode=mode, a_ce=a_ce, a_l1=a_l1, write_grad=need_grad)
         num = (weight * (a_ce * ce + a_l1 * l1)).sum()
         ctx.save_for_backward(logits if need_grad else None, hidden, lm_w, prev_emb, markov_w2)
         ctx.w2_holder = w2_holder
+        ctx.lm_holder = lm_holder
         ctx.mark_non_differentiable(ce, l1, correct)
         return num, ce, l1, correct
 
@@ -88,7 +92,17 @@ class _HeadLossFn(torch.autograd.Function):
         from aspec_b200.ops import gemm as G
         dlogits, hidden, lm_w, prev_emb, markov_w2 = ctx.saved_tensors
         scale = dnum.float().reshape(1)
-        dhidden = dprev = dw2 = None
+        dhidden = dprev = dw2 = dlm = None
+        if ctx.needs_input_grad[1]:       # trainable student head (EAGLE): dW = dlogits^T hidden
+            holder = ctx.lm_holder
+            main = getattr(holder, "main_grad", None) if holder is not None else None
+            g = G.gemm(dlogits, hidden, a_t=True, b_t=True, out_dtype=torch.float32)
+            g.mul_(scale)
+            if main is not None:
+                main.add_(g)
+                holder.main_grad_touched = True
+            else:
+                dlm = g.to(lm_w.dtype)
         if ctx.needs_input_grad[0]:
             acc = G.gemm(dlogits, lm_w, b_t=True, out_dtype=torch.float32)
             dhidden = E.cast_scale(acc, scale)
@@ -105,26 +119,29 @@ class _HeadLossFn(torch.autograd.Function):
                 holder.main_grad_touched = True
             else:
                 dw2 = g.to(markov_w2.dtype)
-        return dhidden, None, dprev, dw2, None, None, None, None, None, None, None, None
+        return dhidden, dlm, dprev, dw2, None, None, None, None, None, None, None, None, None, None
 
 
 def head_loss(hidden: torch.Tensor, lm_w: torch.Tensor, labels: torch.Tensor, weight: torch.Tensor, *,
               prev_emb: Optional[torch.Tensor] = None, markov_w2: Optional[torch.Tensor] = None,
               teacher_hidden: Optional[torch.Tensor] = None, t_index: Optional[torch.Tensor] = None,
-              a_ce: float = 1.0, a_l1: float = 0.0, mode: int = 0
+              a_ce: float = 1.0, a_l1: float = 0.0, mode: int = 0, teacher_w: Optional[torch.Tensor] = None
               ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """Weighted loss numerator plus detached per-row ``ce``, ``l1`` and ``correct``.
 
     ``hidden [R, D]``; ``lm_w [V, D]`` frozen; ``labels [R]`` int64; ``weight [R]`` fp32 (0 for rows
     that are not supervised); ``prev_emb [R, r]`` with ``markov_w2 [V, r]`` adds the Markov bias;
-    ``teacher_hidden [Tt, D]`` rows are selected per supervised row by ``t_index [R]`` (int32).
+    ``teacher_hidden [Tt, D]`` rows are selected per supervised row by ``t_index [R]`` (int32) and projected
+    with ``teacher_w`` (default ``lm_w``).  ``mode=1`` is the EAGLE soft-target cross entropy
+    ``logsumexp(z) - sum_v softmax(teacher)_v z_v``; there ``correct`` compares the two arg-maxima and
+    ``lm_w`` may be a trainable parameter.
     """
     use_kernel = (hidden.is_cuda and hidden.dtype == torch.bfloat16 and lm_w.dtype == torch.bfloat16
                   and lm_w.shape[0] % 8 == 0 and hidden.shape[1] % 8 == 0 and hidden.shape[0] > 0)
     if not use_kernel:
         return head_loss_reference(hidden, lm_w, labels, weight, prev_emb=prev_emb, markov_w2=markov_w2,
                                    teacher_hidden=teacher_hidden, t_index=t_index, a_ce=a_ce, a_l1=a_l1,
-                                   mode=mode)
+                                   mode=mode, teacher_w=teacher_w)
     if teacher_hidden is not None and t_index is None:
         t_index = torch.arange(hidden.shape[0], device=hidden.device, dtype=torch.int32)
     holder = markov_w2 if isinstance(markov_w2, torch.nn.Parameter) else None
@@ -132,4 +149,5 @@ def head_loss(hidden: torch.Tensor, lm_w: torch.Tensor, labels: torch.Tensor, we
         hidden.contiguous(), lm_w, prev_emb.contiguous() if prev_emb is not None else None, markov_w2,
         teacher_hidden.contiguous() if teacher_hidden is not None else None,
         t_index.to(torch.int32).contiguous() if t_index is not None else None,
-        labels.long().contiguous(), weight.float().contiguous(), float(a_ce), float(a_l1), int(mode), holder)
+        labels.long().contiguous(), weight.float().contiguous(), float(a_ce), float(a_l1), int(mode), holder,
+        teacher_w, lm_w if isinstance(lm_w, torch.nn.Parameter) else None)

@@ -89,7 +89,11 @@ class DraftTrainer:
         pool.setdefault("loss", []).append(torch.stack([num.detach().float(), den.float()]))
         pool.setdefault("acc_pp", []).append(torch.stack([acc_pp * count_pp.clamp(min=1.0) * (count_pp > 0), count_pp]))
         pool.setdefault("loss_pp", []).append(torch.stack([loss_pp * count_pp.clamp(min=1.0) * (count_pp > 0), count_pp]))
-        for key, (n_, d_) in comps.items():
+        for key, value in comps.items():
+            if key.startswith("_"):          # raw control statistics (e.g. Ling router counts): summed, not averaged
+                pool.setdefault("x/" + key, []).append(value.float())
+                continue
+            n_, d_ = value
             pool.setdefault("c/" + key, []).append(torch.stack([n_.float().reshape(()), d_.float().reshape(())]))
 
     # -- one optimizer update -------------------------------------------------------------
@@ -121,17 +125,29 @@ class DraftTrainer:
         opt.set_grad_scale(torch.where(den > 0, 1.0 / den.clamp(min=1e-12), torch.zeros_like(den)))
         grad_norm = opt.step()
         self.global_step += 1
+        counts = pooled.pop("x/_ling_router_counts", None)
+        if counts is not None:
+            self._update_router_bias(counts)
         for hook in self.post_step_hooks:
             hook(self)
         pooled["grad_norm"] = grad_norm
         self._last = pooled
+
+    def _update_router_bias(self, counts: torch.Tensor) -> None:
+        """Ling balancing: once per committed optimizer step, from the counts pooled over micro-batches and ranks
+        (they were already SUM-reduced with the other pooled statistics)."""
+        from aspec_b200.models.draft.ling_moe import LingMoE, update_ling_bias
+        cfg = self.draft.config
+        layers = [l.mlp for l in self.draft.layers if isinstance(getattr(l, "mlp", None), LingMoE)]
+        if layers:
+            update_ling_bias(layers, counts, cfg.moe_router_bias_update_rate, cfg.bias_zero_mean_update)
 
     def metrics(self) -> Dict[str, float]:
         """Metrics of the last update (one device->host transfer)."""
         p = self._last
         if not p:
             return {}
-        keys = sorted(k for k in p if k != "grad_norm")
+        keys = sorted(k for k in p if k != "grad_norm" and not k.startswith("x/"))
         flat = torch.cat([p[k].reshape(-1).float() for k in keys] + [p["grad_norm"].reshape(1).float()]).cpu()
         out: Dict[str, float] = {}
         off = 0
