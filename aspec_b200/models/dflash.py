@@ -103,7 +103,7 @@ class DFlashModel(nn.Module):
     # ------------------------------------------------------------------ policy --
     @property
     def uses_target_distribution(self) -> bool:
-        if getattr(self.draft_model.config, "dsa_training_stage", None) == "indexer_warmup":
+        if self._indexer_warmup_kind() is not None:
             return False
         return self.l1_loss_alpha > 0
 
@@ -247,6 +247,9 @@ class DFlashModel(nn.Module):
         if aux is not None:
             aux["layout"] = layout
             aux["keep"] = keep_flat
+            ds_flat = (doc_start if doc_start is not None else torch.zeros_like(layout.anchor)) + row_off
+            aux["query_doc_start"] = ds_flat.repeat_interleave(bs)
+            aux["query_anchor"] = (layout.anchor + row_off).repeat_interleave(bs)
         hidden = self.draft_model(ctx, embeds, ctx_pos.to(torch.int32), draft_pos.to(torch.int32),
                                   tables, aux)
         return hidden, layout, keep_flat
@@ -318,7 +321,8 @@ class DFlashModel(nn.Module):
         B, T = input_ids.shape
         dev = input_ids.device
         bs = self.block_size
-        aux: dict = {"router_logits": [], "csa_losses": [], "qsa_losses": [], "dsa_losses": []}
+        aux: dict = {"router_logits": [], "csa_losses": [], "qsa_losses": [], "dsa_losses": [],
+                     "block_size": self.block_size}
         hidden, layout, keep = self._draft_backbone(
             input_ids, hidden_states_list, loss_mask, ctx_doc_ids=ctx_doc_ids,
             base_position_ids=base_position_ids, injected_anchors=injected_anchors,
@@ -336,7 +340,7 @@ class DFlashModel(nn.Module):
         binary = weight
         decay = self._decay(dev)[None]
 
-        if self._indexer_warmup_kind() == "dsa":
+        if self._indexer_warmup_kind() is not None:
             w = binary * (decay if self.loss_objective == "decay" else 1.0)
             den = w.sum()
             num, comps = self._aux_losses(aux, w, den)

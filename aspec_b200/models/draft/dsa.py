@@ -1,0 +1,166 @@
+"""DeepSeek-style sparse attention (DSA) for DFlash-family drafts: a per-query token indexer plus
+attention over the selected context tokens, trained in three stages.
+
+Behaviour (reference: aspec/models/draft/dsa.py:51-451):
+
+* indexer (inputs detached): ``q = q_b(RMSNorm(q_a(x)))`` -> ``[Q, Hi, di]``, ``k = LayerNorm(k_proj(ctx))`` ->
+  ``[T, di]``, rotate-half RoPE on the first ``rope_dim`` dims, score ``= sum_h relu(q_h . k) * w_h`` with
+  ``w = weights_proj(x) * di^-1/2 * Hi^-1/2``;
+* ``dense``: ordinary attention, indexer untouched;
+* ``indexer_warmup``: the main attention's head-summed softmax over the eligible context (strictly before
+  the anchor, same document) is the teacher; loss = KL(teacher || softmax(score)); only the indexer trains;
+* ``sparse``: without gradient each query keeps its top-``token_budget`` context tokens, the KL is taken on
+  that set, and attention runs over the selected tokens plus the query's own block.
+
+Eligibility is read from the interval table (first interval = visible context).  Work is chunked over
+queries so that no ``[Q, T]`` fp32 tensor larger than ``dsa_workspace_bytes`` exists at once.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from aspec_b200.models.draft.dflash import DFlashAttention
+from aspec_b200.ops.attention import interval_attention
+from aspec_b200.ops.linear import Linear
+from aspec_b200.ops.norm import RMSNorm
+from aspec_b200.ops.rope import qk_norm_rope
+
+
+def _rotary(values: torch.Tensor, positions: torch.Tensor, dim: int, theta: float) -> torch.Tensor:
+    """Non-interleaved RoPE on ``values[..., :dim]`` (``values [N, H, d]``)."""
+    inv = theta ** (-torch.arange(0, dim, 2, device=values.device).float() / dim)
+    ang = positions.float()[:, None] * inv
+    cos, sin = ang.cos()[:, None], ang.sin()[:, None]
+    a, b = values[..., :dim].float().chunk(2, -1)
+    rot = torch.cat((a * cos - b * sin, a * sin + b * cos), -1).to(values.dtype)
+    return torch.cat((rot, values[..., dim:]), -1)
+
+
+class DSALightningIndexer(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.num_heads, self.head_dim = config.dsa_index_n_heads, config.dsa_index_head_dim
+        self.token_budget, self.workspace_bytes = config.dsa_token_budget, config.dsa_workspace_bytes
+        self.rope_dim, self.rope_theta = config.dsa_rope_dim, config.dsa_rope_theta
+        self.q_a_proj = Linear(config.hidden_size, config.dsa_q_lora_rank)
+        self.q_a_norm = RMSNorm(config.dsa_q_lora_rank, eps=config.rms_norm_eps)
+        self.q_b_proj = Linear(config.dsa_q_lora_rank, self.num_heads * self.head_dim)
+        self.k_proj = Linear(config.hidden_size, self.head_dim)
+        self.k_norm = nn.LayerNorm(self.head_dim, eps=config.rms_norm_eps)
+        self.weights_proj = Linear(config.hidden_size, self.num_heads)
+        self.scale = self.head_dim ** -0.5 * self.num_heads ** -0.5
+
+    def project(self, x, ctx, q_pos, ctx_pos):
+        x, ctx = x.detach(), ctx.detach()
+        q = self.q_b_proj(self.q_a_norm(self.q_a_proj(x))).view(x.shape[0], self.num_heads, self.head_dim)
+        k = self.k_norm(self.k_proj(ctx).float()).to(ctx.dtype)[:, None]
+        q = _rotary(q, q_pos, self.rope_dim, self.rope_theta)
+        k = _rotary(k, ctx_pos, self.rope_dim, self.rope_theta)[:, 0]
+        w = F.linear(x.float(), self.weights_proj.weight.float()) * self.scale
+        return q, k, w
+
+    @staticmethod
+    def scores(q, k, w):
+        """``q [n, Hi, di]``, ``k [T, di]``, ``w [n, Hi]`` -> ``[n, T]`` fp32."""
+        return (torch.einsum("nhd,td->nht", q.float(), k.float()).relu_() * w[:, :, None]).sum(1)
+
+    def chunk_rows(self, n_keys: int) -> int:
+        return max(int(self.workspace_bytes // max(n_keys * 4 * (self.num_heads + 2), 1)), 1)
+
+
+class DSAAttention(DFlashAttention):
+    def __init__(self, config, layer_idx: int):
+        super().__init__(config, layer_idx)
+        self.stage = config.dsa_training_stage
+        self.indexer = DSALightningIndexer(config)
+        self.compute_auxiliary_loss = True
+
+    # teacher: head-summed softmax of the main attention over the eligible context --------------------
+    def _teacher(self, q, k_ctx, lo, hi):
+        g = self.num_heads // self.num_kv_heads
+        kk = k_ctx.repeat_interleave(g, 1).float()
+        s = torch.einsum("nhd,thd->nht", q.float(), kk) * self.scale
+        t = torch.arange(k_ctx.shape[0], device=q.device)[None]
+        elig = (t >= lo[:, None]) & (t < hi[:, None])
+        s = s.masked_fill(~elig[:, None], float("-inf"))
+        p = torch.softmax(s, -1)
+        p = torch.where(elig[:, None], p, torch.zeros_like(p)).sum(1)
+        return p / p.sum(-1, keepdim=True).clamp_min(1e-20), elig
+
+    def forward(self, x, ctx, q_pos, kv_pos, intervals, aux=None, attn_override=None):
+        if self.stage == "dense":
+            return super().forward(x, ctx, q_pos, kv_pos, intervals, aux=aux, attn_override=attn_override)
+        Q, T = x.shape[0], ctx.shape[0]
+        d, hk = self.head_dim, self.num_kv_heads
+        from aspec_b200.ops.fused_params import fused_linear
+        frozen = self.stage == "indexer_warmup"
+        with torch.set_grad_enabled(torch.is_grad_enabled() and not frozen):
+            q = self.q_proj(x).view(Q, self.num_heads, d)
+            kv = fused_linear(torch.cat([ctx, x], 0), [self.k_proj.weight, self.v_proj.weight])
+            k = kv[:, : hk * d].reshape(T + Q, hk, d)
+            v = kv[:, hk * d:].reshape(T + Q, hk, d)
+            inv = self.rope_freqs.get(x.device)
+            q = qk_norm_rope(q, self.q_norm.weight, q_pos, inv, self.eps, self.rope_scaling)
+            k = qk_norm_rope(k, self.k_norm.weight, kv_pos, inv, self.eps, self.rope_scaling)
+        iq, ik, iw = self.indexer.project(x, ctx, q_pos, kv_pos[:T])
+        lo, hi = intervals[:, 0].long(), intervals[:, 1].long()
+        rows = self.indexer.chunk_rows(T)
+        losses = []
+        outs = []
+        budget = min(self.indexer.token_budget, T)
+        for s0 in range(0, Q, rows):
+            sl = slice(s0, min(s0 + rows, Q))
+            score = self.indexer.scores(iq[sl], ik, iw[sl])
+            with torch.no_grad():
+                teacher, elig = self._teacher(q[sl].detach(), k[:T].detach(), lo[sl], hi[sl])
+            if self.stage == "indexer_warmup":
+                logp = torch.log_softmax(score.masked_fill(~elig, float("-inf")), -1)
+                kl = (teacher * (torch.log(teacher.clamp_min(1e-20)) - logp.masked_fill(~elig, 0.0))).sum(-1)
+                losses.append(torch.where(elig.any(-1), kl, torch.zeros_like(kl)))
+                continue
+            # sparse: per-query top-k over eligible context, KL on the selected set, attention on it + own block
+            with torch.no_grad():
+                masked = score.detach().masked_fill(~elig, float("-inf"))
+                top = masked.topk(budget, -1)
+                sel, sel_ok = top.indices, torch.isfinite(top.values)
+            sel_score = score.gather(1, sel).masked_fill(~sel_ok, float("-inf"))
+            t_sel = teacher.gather(1, sel) * sel_ok
+            t_sel = t_sel / t_sel.sum(-1, keepdim=True).clamp_min(1e-20)
+            logp = torch.log_softmax(sel_score, -1).masked_fill(~sel_ok, 0.0)
+            kl = (t_sel * (torch.log(t_sel.clamp_min(1e-20)) - logp)).sum(-1)
+            losses.append(torch.where(sel_ok.any(-1), kl, torch.zeros_like(kl)))
+            outs.append(self._selected_attention(q[sl], k, v, sel, sel_ok, intervals[sl], T))
+        if aux is not None and self.compute_auxiliary_loss and losses:
+            aux.setdefault("dsa_losses", []).append(torch.cat(losses))
+        if self.stage == "indexer_warmup":
+            with torch.no_grad():
+                o, _ = interval_attention(q, k, v, intervals, self.scale)
+                return self.o_proj(o.reshape(Q, -1))
+        return self.o_proj(torch.cat(outs, 0).reshape(Q, -1))
+
+    def _selected_attention(self, q, k, v, sel, sel_ok, iv, T):
+        """Each query attends its selected context tokens and the whole of its own draft block."""
+        n = q.shape[0]
+        g = self.num_heads // self.num_kv_heads
+        b_lo, b_hi = iv[:, 2].long(), iv[:, 3].long()
+        width = int((b_hi - b_lo).max().item()) if n else 0
+        off = torch.arange(width, device=q.device)[None]
+        blk = b_lo[:, None] + off
+        blk_ok = blk < b_hi[:, None]
+        idx = torch.cat([sel, blk.clamp(max=k.shape[0] - 1)], 1)
+        ok = torch.cat([sel_ok, blk_ok], 1)
+        kk = k[idx].repeat_interleave(g, 2).float()              # [n, S, Hq, d]
+        vv = v[idx].repeat_interleave(g, 2).float()
+        s = torch.einsum("nhd,nshd->nhs", q.float(), kk) * self.scale
+        s = s.masked_fill(~ok[:, None], float("-inf"))
+        p = torch.softmax(s, -1)
+        p = torch.where(ok[:, None], p, torch.zeros_like(p))
+        return torch.einsum("nhs,nshd->nhd", p, vv).to(q.dtype)
+
+    def trainable_parameter_names(self):
+        """In ``indexer_warmup`` only the indexer learns (weights-only phase changes between stages)."""
+        return [n for n, _ in self.named_parameters() if n.startswith("indexer.")] if self.stage == "indexer_warmup" else None

@@ -122,9 +122,9 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
             k0, v0, dk, dv = cache
             dk, dv = dk + [k], dv + [v]
         if dk:
-            pad = [torch.zeros_like(k)] * (L1 - len(dk))
-            k_all = torch.cat([k0, torch.stack(dk + pad, 1).reshape(T * L1, *k.shape[1:])])
-            v_all = torch.cat([v0, torch.stack(dv + pad, 1).reshape(T * L1, *v.shape[1:])])
+            n_pad = L1 - len(dk)
+            k_all = torch.cat([k0, torch.stack(dk + [torch.zeros_like(k)] * n_pad, 1).reshape(T * L1, *k.shape[1:])])
+            v_all = torch.cat([v0, torch.stack(dv + [torch.zeros_like(v)] * n_pad, 1).reshape(T * L1, *v.shape[1:])])
         else:
             k_all, v_all = k0, v0
         intervals = torch.stack([doc_start, t + 1, T + t * L1, T + t * L1 + depth], -1).to(torch.int32)

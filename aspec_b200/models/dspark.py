@@ -60,7 +60,8 @@ class DSparkModel(DFlashModel):
         B, T = input_ids.shape
         dev = input_ids.device
         bs = self.block_size
-        aux: dict = {"router_logits": [], "csa_losses": [], "qsa_losses": [], "dsa_losses": []}
+        aux: dict = {"router_logits": [], "csa_losses": [], "qsa_losses": [], "dsa_losses": [],
+                     "block_size": self.block_size}
         hidden, layout, keep = self._draft_backbone(
             input_ids, hidden_states_list, loss_mask, ctx_doc_ids=ctx_doc_ids,
             base_position_ids=base_position_ids, injected_anchors=injected_anchors,
