@@ -32,8 +32,8 @@ def eagle4_policy(raw: Mapping) -> dict:
         raise ValueError("EAGLE4 requires efficient_lm_head_config.type=low_rank")
     rank = _posint("rank", head.get("rank"), min(raw["hidden_size"], raw["vocab_size"]))
     cands = _posint("num_candidates", head.get("num_candidates"), raw["vocab_size"])
-    teacher_k = _posint("candidate_teacher_top_k", raw.get("candidate_teacher_top_k", cands), raw["vocab_size"])
-    chunk = _posint("candidate_loss_chunk_size", raw.get("candidate_loss_chunk_size", 128))
+    teacher_k = _posint("candidate_teacher_top_k", raw.get("candidate_teacher_top_k") or cands, raw["vocab_size"])
+    chunk = _posint("candidate_loss_chunk_size", raw.get("candidate_loss_chunk_size") or 128)
     for name in ("fc_norm", "norm_output", "attn_norm", "enable_post_mlp_norm", "enable_moe", "use_rope"):
         if name in raw and not isinstance(raw[name], bool):
             raise ValueError(f"EAGLE4 {name} must be boolean")

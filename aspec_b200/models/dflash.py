@@ -112,6 +112,20 @@ class DFlashModel(nn.Module):
         return self.uses_target_distribution or bool(
             self.mtp_conditioning and self.mtp_conditioning["mode"] == "hidden")
 
+    def _prepare_draft_prefix(self, input_ids, last_hidden_states, attention_mask, draft_prefix, *packed_metadata):
+        if not self.mtp_conditioning:
+            if draft_prefix is not None:
+                raise ValueError("Unconditioned Draft does not accept an MTP prefix")
+            return None
+        if any(v is not None for v in packed_metadata):
+            raise ValueError("MTP conditioning does not accept packed or sharded documents")
+        if input_ids.shape[0] != 1:
+            raise ValueError("MTP conditioning currently requires microbatch size one")
+        if draft_prefix is None:
+            from aspec_b200.models.dmtp import training_mtp_prefix
+            return training_mtp_prefix(self.draft_model, input_ids, last_hidden_states, attention_mask)
+        return draft_prefix
+
     def _block_causal(self, layer: int) -> bool:
         spec = self._policy["draft_block_attention"] if self._policy else "bidirectional"
         if isinstance(spec, list):
@@ -190,7 +204,7 @@ class DFlashModel(nn.Module):
     def _draft_backbone(self, input_ids, hidden_states, loss_mask, *, ctx_doc_ids=None,
                         base_position_ids=None, injected_anchors=None, injected_keep_mask=None,
                         anchor_seed=None, packed_document_lengths=None, attention_mask=None,
-                        aux: Optional[dict] = None, compact: bool = True):
+                        aux: Optional[dict] = None, compact: bool = True, draft_prefix=None):
         B, T = input_ids.shape
         dev = input_ids.device
         bs = self.block_size
@@ -201,6 +215,10 @@ class DFlashModel(nn.Module):
             if keep is None:
                 raise ValueError("injected anchors need their keep mask")
         else:
+            if self.mtp_conditioning:
+                # no Target state precedes a document's first token
+                loss_mask = loss_mask.clone()
+                loss_mask[:, 0] = 0
             anchors, keep = self.sample_anchors(loss_mask, ctx_doc_ids, packed_document_lengths,
                                                 attention_mask, anchor_seed)
         self._step_counter += 1
@@ -224,6 +242,13 @@ class DFlashModel(nn.Module):
             noise[:, 0] = torch.where(keep_flat, input_ids.reshape(-1)[fa],
                                       torch.full_like(fa, self.draft_model.mask_token_id))
         embeds = self.draft_model.embed_tokens(noise).reshape(n * bs, -1).to(ctx.dtype)
+        if self.mtp_conditioning and n:
+            from aspec_b200.models.dmtp import first_candidate_embeddings
+            first = first_candidate_embeddings(self.draft_model, input_ids, anchors.to(dev), keep.to(dev), draft_prefix)
+            first = first.reshape(-1, first.shape[-1])[layout.row * layout.n_slots + layout.slot]
+            embeds = embeds.view(n, bs, -1).clone()
+            embeds[:, 1] = first.to(embeds.dtype)
+            embeds = embeds.view(n * bs, -1)
         draft_pos = (ctx_pos[fa][:, None] + j[None]).reshape(-1) if n else ctx_pos.new_zeros(0)
 
         doc_start = self._doc_start(layout, ctx_doc_ids, base_position_ids)
@@ -323,11 +348,14 @@ class DFlashModel(nn.Module):
         bs = self.block_size
         aux: dict = {"router_logits": [], "csa_losses": [], "qsa_losses": [], "dsa_losses": [],
                      "block_size": self.block_size}
+        draft_prefix = self._prepare_draft_prefix(input_ids, last_hidden_states, attention_mask, draft_prefix,
+                                                  ctx_doc_ids, base_position_ids, packed_document_lengths)
         hidden, layout, keep = self._draft_backbone(
             input_ids, hidden_states_list, loss_mask, ctx_doc_ids=ctx_doc_ids,
             base_position_ids=base_position_ids, injected_anchors=injected_anchors,
             injected_keep_mask=injected_keep_mask, anchor_seed=anchor_seed,
-            packed_document_lengths=packed_document_lengths, attention_mask=attention_mask, aux=aux)
+            packed_document_lengths=packed_document_lengths, attention_mask=attention_mask, aux=aux,
+            draft_prefix=draft_prefix)
         n = layout.n
         j = torch.arange(bs, device=dev)[None]
         label = layout.anchor[:, None] + j                                    # [n, bs]

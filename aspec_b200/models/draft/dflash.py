@@ -179,6 +179,26 @@ class DFlashDraftModel(nn.Module):
         self.final_norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
         self.gradient_checkpointing = False
         self.freeze_embedding()
+        self.mtp_fusion = self.mtp_source = None
+        conditioning = getattr(config, "mtp_conditioning", None)
+        if conditioning:
+            from aspec_b200.models.dmtp import FrozenMTPFeatures, MTPAnchorFusion
+            self.mtp_source = FrozenMTPFeatures(conditioning["native_config"])
+            if conditioning["mode"] == "hidden":
+                self.mtp_fusion = MTPAnchorFusion(config.hidden_size, dt, eps=config.rms_norm_eps)
+
+    def initialize_mtp_conditioning(self, tensors) -> None:
+        """Load the frozen MTP predictor from the Target checkpoint tensors (``mtp.*`` keys)."""
+        if self.mtp_source is not None:
+            self.mtp_source.initialize_native_weights(tensors)
+
+    def validate_mtp_binding(self, tensors, embedding=None) -> None:
+        if self.mtp_source is None:
+            return
+        if embedding is not None and not torch.equal(self.embed_tokens.weight.detach().cpu(),
+                                                     embedding.to(self.embed_tokens.weight.dtype).cpu()):
+            raise ValueError("MTP conditioning requires the Target's own frozen embedding")
+        self.mtp_source.validate_native_weights(tensors)
 
     # -- parameter policy -------------------------------------------------------
     def freeze_embedding(self) -> None:

@@ -31,12 +31,14 @@ from aspec_b200.ops.rope import RopeFrequencies, qk_norm_rope
 
 
 class EagleAttention(nn.Module):
-    def __init__(self, config):
+    def __init__(self, config, input_width: Optional[int] = None, use_rope: bool = True, window: Optional[int] = None):
         super().__init__()
         D, d = config.hidden_size, config.head_dim
+        width = input_width or 2 * D
+        self.use_rope, self.window = use_rope, window
         self.num_heads, self.num_kv_heads, self.head_dim = config.num_attention_heads, config.num_key_value_heads, d
-        qw, kw, vw = allocate_adjacent([(self.num_heads * d, 2 * D), (self.num_kv_heads * d, 2 * D),
-                                        (self.num_kv_heads * d, 2 * D)])
+        qw, kw, vw = allocate_adjacent([(self.num_heads * d, width), (self.num_kv_heads * d, width),
+                                        (self.num_kv_heads * d, width)])
         for w in (qw, kw, vw):
             nn.init.normal_(w, std=0.02)
         self.q_proj, self.k_proj, self.v_proj = _Weight(qw), _Weight(kw), _Weight(vw)
@@ -59,10 +61,11 @@ class EagleAttention(nn.Module):
         q = qkv[:, : hq * d].reshape(T, hq, d)
         k = qkv[:, hq * d:(hq + hk) * d].reshape(T, hk, d)
         v = qkv[:, (hq + hk) * d:].reshape(T, hk, d)
-        inv = self.rope_freqs.get(x.device)
-        q = qk_norm_rope(q, None, positions, inv, 0.0, self.rope_scaling)
-        k = qk_norm_rope(k, None, positions, inv, 0.0, self.rope_scaling)
-        return q, k, v
+        if self.use_rope:
+            inv = self.rope_freqs.get(x.device)
+            q = qk_norm_rope(q, None, positions, inv, 0.0, self.rope_scaling)
+            k = qk_norm_rope(k, None, positions, inv, 0.0, self.rope_scaling)
+        return q, k.contiguous(), v.contiguous()
 
 
 class EagleDecoderLayer(nn.Module):
@@ -74,9 +77,14 @@ class EagleDecoderLayer(nn.Module):
         self.hidden_norm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(config.hidden_size, eps=config.rms_norm_eps)
 
+    def attention_input(self, embeds: torch.Tensor, hidden: torch.Tensor):
+        """``(attention input, residual stream)`` of one TTT depth."""
+        return torch.cat([self.input_layernorm(embeds), self.hidden_norm(hidden)], -1), hidden
+
 
 class LlamaForCausalLMEagle3(Eagle3DraftModel):
     config_class = Eagle3Config
+    decoder_layer_class = EagleDecoderLayer
 
     def __init__(self, config):
         super().__init__()
@@ -88,7 +96,7 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
                         if getattr(config, "fc_norm", False) else None)
         self.embed_tokens = nn.Embedding(config.vocab_size, D)
         self.embed_tokens.weight.requires_grad_(False)
-        self.midlayer = EagleDecoderLayer(config)
+        self.midlayer = self.decoder_layer_class(config)
         self.norm = RMSNorm(D, eps=config.rms_norm_eps)
         self.lm_head = Linear(D, config.draft_vocab_size)
         self.init_vocab_buffers(config.vocab_size, config.draft_vocab_size)
@@ -111,7 +119,7 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
         """One TTT depth over ``T`` packed tokens.  Returns the new hidden state and the extended cache."""
         layer = self.midlayer
         T = hidden.shape[0]
-        x = torch.cat([layer.input_layernorm(embeds), layer.hidden_norm(hidden)], -1)
+        x, residual = layer.attention_input(embeds, hidden)
         q, k, v = layer.self_attn.project(x, positions + depth)
         L1 = max(ttt_length - 1, 1)
         dev = hidden.device
@@ -127,11 +135,16 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
             v_all = torch.cat([v0, torch.stack(dv + [torch.zeros_like(v)] * n_pad, 1).reshape(T * L1, *v.shape[1:])])
         else:
             k_all, v_all = k0, v0
-        intervals = torch.stack([doc_start, t + 1, T + t * L1, T + t * L1 + depth], -1).to(torch.int32)
+        window = getattr(layer.self_attn, "window", None)
+        lo = doc_start if window is None else torch.maximum(doc_start, t + 1 - window)
+        intervals = torch.stack([lo, t + 1, T + t * L1, T + t * L1 + depth], -1).to(torch.int32)
         o, _ = interval_attention(q, k_all, v_all, intervals, layer.self_attn.scale)
-        h = hidden + layer.self_attn.o_proj(o.reshape(T, -1))
-        h = h + layer.mlp(layer.post_attention_layernorm(h))
+        h = residual + layer.self_attn.o_proj(o.reshape(T, -1))
+        h = h + self._mlp(layer, layer.post_attention_layernorm(h), depth)
         return h, (k0, v0, dk, dv)
+
+    def _mlp(self, layer, x: torch.Tensor, depth: int) -> torch.Tensor:
+        return layer.mlp(x)
 
     def next_depth_hidden(self, hidden: torch.Tensor) -> torch.Tensor:
         return self.norm(hidden) if self.norm_output else hidden

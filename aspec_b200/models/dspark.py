@@ -62,11 +62,14 @@ class DSparkModel(DFlashModel):
         bs = self.block_size
         aux: dict = {"router_logits": [], "csa_losses": [], "qsa_losses": [], "dsa_losses": [],
                      "block_size": self.block_size}
+        draft_prefix = self._prepare_draft_prefix(input_ids, last_hidden_states, attention_mask, draft_prefix,
+                                                  ctx_doc_ids, base_position_ids, packed_document_lengths)
         hidden, layout, keep = self._draft_backbone(
             input_ids, hidden_states_list, loss_mask, ctx_doc_ids=ctx_doc_ids,
             base_position_ids=base_position_ids, injected_anchors=injected_anchors,
             injected_keep_mask=injected_keep_mask, anchor_seed=anchor_seed,
-            packed_document_lengths=packed_document_lengths, attention_mask=attention_mask, aux=aux)
+            packed_document_lengths=packed_document_lengths, attention_mask=attention_mask, aux=aux,
+            draft_prefix=draft_prefix)
         n = layout.n
         j = torch.arange(bs, device=dev)[None]
         label = layout.anchor[:, None] + j + 1                                   # [n, bs]
@@ -136,7 +139,13 @@ class DSparkModel(DFlashModel):
             if accept is not None:
                 s = self.prediction_start
                 stats = F.pad(acceptance_statistics(accept.view(n, bs)[:, s:], eval_mask[:, s:]), (s, 0))
-                comps.update(acceptance_components(stats))
+                obs = acceptance_components(stats)
+                if self.mtp_conditioning:
+                    # the visible first candidate is not a prediction: report the suffix only
+                    obs = {("suffix_tau_probabilistic" if k == "tau_probabilistic"
+                            else f"suffix_accept_rate@{int(k.split('@')[1]) - s}"): v for k, v in obs.items()
+                           if k == "tau_probabilistic" or int(k.split('@')[1]) >= s}
+                comps.update(obs)
             correct = correct.view(n, bs) * (eval_mask > 0.5)
             accuracy = correct.sum() / eval_mask.sum().clamp(min=1e-6)
             count_pp = eval_mask.sum(0)

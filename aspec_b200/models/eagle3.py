@@ -146,6 +146,8 @@ class Eagle3Model(nn.Module):
         doc_end = torch.where(last, t + 1, torch.full_like(t, T)).flip(0).cummin(0).values.flip(0)
         positions = (base_position_ids.reshape(-1).to(dev) if base_position_ids is not None else t - doc_start).to(torch.int32)
         mask = mask * valid
+        if hasattr(draft, "set_valid_rows"):
+            draft.set_valid_rows(lambda depth: (t + depth + 1 < doc_end) & valid)
 
         target = LazyTarget(teacher, lm_head_weight, getattr(draft, "t2d", None) if draft.vocab_pruned else None)
         hidden = draft.project_hidden_states(feats)

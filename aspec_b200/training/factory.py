@@ -49,6 +49,7 @@ def build_training_model(draft_config, args: Mapping[str, Any], device, dtype) -
                            lk_eta=g("lk_eta", 3.0), ploss_weights=g("ploss_weights"))
     if algorithm == "eagle4":
         from aspec_b200.models.eagle4 import Eagle4TrainingModel
+        draft.configure_training_stage()
         return Eagle4TrainingModel(draft, length=g("ttt_length", 7), loss_type=g("loss_type", "forward_kl"),
                                    lk_eta=g("lk_eta", 3.0), ploss_weights=g("ploss_weights"))
     if algorithm == "mtp":
