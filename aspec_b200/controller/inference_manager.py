@@ -36,6 +36,7 @@ class InferenceManager:
         self.submitted = 0
         self.completed = 0
         self._engine_load = [0] * len(self.engines)
+        self.dead_consumers: set = set()          # fenced readers: never leased again, pending waits are abandoned
 
     def start(self) -> None:
         self._thread.start()
@@ -116,6 +117,9 @@ class InferenceManager:
                     for c in consumers:
                         deadline = time.monotonic() + self.acquire_timeout
                         while True:
+                            if c in self.dead_consumers:
+                                lease = None
+                                break
                             try:
                                 lease = self.rings[c].acquire(f"row:{request.row_id}", timeout=0.05)
                                 break
@@ -127,9 +131,11 @@ class InferenceManager:
                                 if time.monotonic() > deadline or self._stop.is_set():
                                     raise TimeoutError(
                                         f"no free ring slot on consumer {c} within {self.acquire_timeout}s") from None
-                        leases.append((c, lease.slot_id, lease.generation))
+                        if lease is not None:
+                            leases.append((c, lease.slot_id, lease.generation))
                     request.leases = leases
-                    batch.append(request)
+                    if leases:
+                        batch.append(request)
                 if len(batch) >= self.batch_size or item == "idle":
                     flush()
                 self._collect(block=False)

@@ -110,4 +110,34 @@ long long ab_expand_loss_mask(const long long* runs, int n_runs, unsigned char* 
   return cursor;
 }
 
+// Assistant-span loss mask on token ids: after every occurrence of `header` (plus `skip_after` tokens) mark
+// tokens as supervised until `end` begins (or to the end of the sequence when no terminator follows).
+// Returns the start of the last assistant span (0 when none).
+long long ab_assistant_loss_mask(const long long* ids, long long n, const long long* header, int header_len,
+                                 const long long* end, int end_len, int skip_after, unsigned char* out) {
+  for (long long k = 0; k < n; ++k) out[k] = 0;
+  if (header_len <= 0) return 0;
+  long long i = 0, last_start = 0;
+  while (i <= n - header_len) {
+    bool match = true;
+    for (int k = 0; k < header_len; ++k)
+      if (ids[i + k] != header[k]) { match = false; break; }
+    if (!match) { ++i; continue; }
+    long long j = i + header_len + skip_after;
+    last_start = j;
+    bool found = false;
+    while (end_len > 0 && j <= n - end_len) {
+      bool e = true;
+      for (int k = 0; k < end_len; ++k)
+        if (ids[j + k] != end[k]) { e = false; break; }
+      if (e) { found = true; break; }
+      out[j] = 1;
+      ++j;
+    }
+    if (!found) for (long long k = std::max<long long>(j, 0); k < n; ++k) out[k] = 1;
+    i = j + std::max(end_len, 1);
+  }
+  return last_start;
+}
+
 }  // extern "C"

@@ -28,7 +28,26 @@ class InferenceEngine:
         raise NotImplementedError
 
     def attach_rings(self, handles: Dict[int, dict]) -> None:
+        """``handles[c]`` maps consumer ``c``'s ring; an optional ``"layer_ids"`` entry names the subset of this
+        engine's captured layers that the consumer wants (several Drafts sharing one Target)."""
         self.rings = {int(c): RemoteRing(h) for c, h in handles.items()}
+        self.consumer_layers = {int(c): tuple(h["layer_ids"]) for c, h in handles.items() if h.get("layer_ids")}
+
+    def _layers_of(self, consumer: int):
+        return getattr(self, "consumer_layers", {}).get(consumer, tuple(self.layer_ids))
+
+    def _copy_features(self, req: RowRequest, views, hidden_states, last_hidden_states, row_slice=slice(None)) -> None:
+        """Copy union-layout features ``[n, K * D]`` into every reader's slot, selecting its layer columns."""
+        D = hidden_states.shape[-1] // len(self.layer_ids)
+        for (consumer, _s, _g), v in zip(req.leases, views):
+            layers = self._layers_of(consumer)
+            src = hidden_states
+            if tuple(layers) != tuple(self.layer_ids):
+                cols = torch.cat([torch.arange(self.layer_ids.index(l) * D, (self.layer_ids.index(l) + 1) * D) for l in layers])
+                src = hidden_states[:, cols]
+            v["hidden_states"][row_slice].copy_(src.to(v["hidden_states"].dtype))
+            if "last_hidden_states" in v and last_hidden_states is not None:
+                v["last_hidden_states"][row_slice].copy_(last_hidden_states.to(v["last_hidden_states"].dtype))
 
     def generate(self, requests: Sequence[RowRequest]) -> List[InferenceOutput]:
         raise NotImplementedError
@@ -61,7 +80,7 @@ class InferenceEngine:
             v["input_ids"].copy_(req.input_ids, non_blocking=True)
             if device_flags:
                 ring.publish(slot, gen)
-            keys.append(ring.descriptor(slot, gen, n, layer_ids).to_key())
+            keys.append(ring.descriptor(slot, gen, n, self._layers_of(consumer)).to_key())
         lay = self.rings[req.leases[0][0]].layout
         self.rows_done = getattr(self, "rows_done", 0) + 1
         self.tokens_done = getattr(self, "tokens_done", 0) + n
@@ -120,7 +139,8 @@ class NativeTargetEngine(InferenceEngine):
             if self.fail_after is not None and getattr(self, "rows_done", 0) >= self.fail_after:
                 raise RuntimeError(f"{self.name}: injected producer failure")
             views = self._slot_views(req)
-            sink = RingFeatureSink(views, self.layer_ids, self.model.config.hidden_size)
+            sink = RingFeatureSink(views, self.layer_ids, self.model.config.hidden_size,
+                                   [self._layers_of(c) for c, _s, _g in req.leases])
             ids = req.input_ids.to(self.device, non_blocking=True)
             self.model.prefill(ids, req.document_lengths, self.layer_ids, sink=sink)
             outs.append(self._finish(req, views, self.layer_ids, self.device_flags))
@@ -155,10 +175,7 @@ class SyntheticEngine(InferenceEngine):
             g = torch.Generator().manual_seed(self.seed * 7919 + int(req.input_ids.sum()) % (2 ** 31))
             hs = torch.randn(n, len(self.layer_ids) * self.hidden, generator=g)
             last = torch.randn(n, self.hidden, generator=g)
-            for v in views:
-                v["hidden_states"].copy_(hs.to(v["hidden_states"].dtype))
-                if "last_hidden_states" in v:
-                    v["last_hidden_states"].copy_(last.to(v["last_hidden_states"].dtype))
+            self._copy_features(req, views, hs, last)
             outs.append(self._finish(req, views, self.layer_ids, device_flags=True))
         return outs
 
@@ -170,7 +187,7 @@ class OfflineReplayEngine(InferenceEngine):
         from aspec_b200.offline.dataset import OfflineFeatureStore
         self.name = name
         self.store = OfflineFeatureStore(feature_dir)
-        self.layer_ids = tuple(self.store.binding["feature_contract"]["layer_ids"])
+        self.layer_ids = tuple(self.store.binding["feature_contract"]["aux_hidden_state_layers"])
         self.rings = {}
 
     def init(self) -> None:
@@ -183,10 +200,9 @@ class OfflineReplayEngine(InferenceEngine):
             off = 0
             for data_id, n in zip(req.data_ids, req.document_lengths):
                 rec = self.store.load(data_id)
-                for v in views:
-                    v["hidden_states"][off:off + n].copy_(rec["hidden_states"].reshape(n, -1))
-                    if "last_hidden_states" in v:
-                        v["last_hidden_states"][off:off + n].copy_(rec["last_hidden_states"].reshape(n, -1))
+                last = rec.get("last_hidden_states")
+                self._copy_features(req, views, rec["hidden_states"].reshape(n, -1),
+                                    None if last is None else last.reshape(n, -1), slice(off, off + n))
                 off += n
             outs.append(self._finish(req, views, self.layer_ids, device_flags=True))
         return outs

@@ -1,0 +1,247 @@
+"""Several Drafts trained from one Target pool ("shared Target, multi-Draft").
+
+``experiments[]`` in the recipe lists Drafts that differ in their model config and hyper-parameters but consume the
+same document stream.  Each gets a child execution plan, its own trainer group, optimizer, ledger and checkpoints
+under ``<output_dir>/experiments/<name>``; the Target pool runs once per row and its epilogues store into every
+experiment's ring slot, each reader keeping only the captured layers it asked for
+(reference: aspec/multi_draft.py:51-835; fan-out semantics in aspec/controller/shared_source.py:313-409).
+
+One experiment failing or being cancelled fences its readers; its siblings continue.
+"""
+from __future__ import annotations
+
+import copy
+import dataclasses
+import json
+import os
+import threading
+import time
+from typing import Any, Dict, List, Optional
+
+from aspec_b200.config.draft_config import AutoDraftModelConfig, resolve_draft_algorithm
+from aspec_b200.config.train_config import Config, _apply, _merge, validate_config
+from aspec_b200.feature_contract import build_target_feature_contract, shared_feature_union
+from aspec_b200.planning import ExecutionPlan, compile_execution_plan
+
+# what every experiment must share so that all of them plan identical rows
+_SHARED_ROW_KEYS = ("train_data_path", "max_seq_length", "micro_batch_size", "draft_accumulation_steps", "dflash_packing",
+                    "seed", "dataset_seed", "num_epochs", "draft_context_parallel_size", "world_size",
+                    "synthetic_num_documents", "synthetic_min_length", "synthetic_max_length", "synthetic_vocab_size")
+
+
+@dataclasses.dataclass
+class MultiDraftPlan:
+    names: List[str]
+    plans: Dict[str, ExecutionPlan]
+    union: Dict[str, Any]                    # shared feature contract + per-reader views
+    consumer_offsets: Dict[str, int]
+    schema_version: str = "aspec.multi-draft-plan/v1"
+
+    def to_json(self) -> str:
+        return json.dumps({"schema_version": self.schema_version, "experiments": self.names,
+                           "consumer_offsets": self.consumer_offsets, "shared_feature_contract": self.union["contract"],
+                           "reader_views": self.union["views"],
+                           "plans": {n: json.loads(p.to_json()) for n, p in self.plans.items()}}, indent=2, default=str)
+
+
+def _layer_ids(draft: dict) -> List[int]:
+    cfg = AutoDraftModelConfig.from_dict(draft)
+    ids = list(getattr(cfg, "target_layer_ids", None) or [])
+    if not ids:
+        from aspec_b200.models.draft.dflash import build_target_layer_ids
+        ids = build_target_layer_ids(int(getattr(cfg, "num_target_layers", 3)), int(getattr(cfg, "target_num_hidden_layers", 36)))
+    return ids
+
+
+def _contract(draft: dict) -> dict:
+    algorithm = resolve_draft_algorithm(draft)
+    return build_target_feature_contract(
+        drafter_family=algorithm, target_hidden_size=int(draft.get("target_hidden_size", draft["hidden_size"])),
+        target_num_hidden_layers=int(draft.get("target_num_hidden_layers", 36)), aux_hidden_state_layers=_layer_ids(draft),
+        store_last_hidden_states=algorithm != "mtp")
+
+
+def child_config(config: Config, experiment: Dict[str, Any]) -> Config:
+    """Base recipe ⊕ the experiment's overrides, rooted at its own output directory."""
+    tree = config.to_dict()
+    tree["experiments"] = []
+    overrides = {k: v for k, v in experiment.items() if k != "name"}
+    tree = _merge(tree, copy.deepcopy(overrides))
+    tree["output_dir"] = os.path.join(config.output_dir, "experiments", experiment["name"])
+    child = Config()
+    _apply(child, tree, "")
+    validate_config(child)
+    return child
+
+
+def compile_multi_draft_plan(config: Config) -> MultiDraftPlan:
+    if len(config.experiments) < 2:
+        raise ValueError("a shared-Target run needs at least two experiments")
+    plans, names = {}, []
+    for exp in config.experiments:
+        names.append(exp["name"])
+        plans[exp["name"]] = compile_execution_plan(child_config(config, exp))
+    first = plans[names[0]].runtime_args
+    for n in names[1:]:
+        for key in _SHARED_ROW_KEYS:
+            if plans[n].runtime_args.get(key) != first.get(key):
+                raise ValueError(f"experiments that share a Target must agree on {key}: "
+                                 f"{names[0]}={first.get(key)!r}, {n}={plans[n].runtime_args.get(key)!r}")
+    union = shared_feature_union([_contract(plans[n].draft_config) for n in names])
+    offsets, at = {}, 0
+    for n in names:
+        offsets[n] = at
+        at += int(plans[n].runtime_args["world_size"])
+    return MultiDraftPlan(names, plans, union, offsets)
+
+
+def _common_samples(controllers: Dict[str, Any], dataset: Optional[List[dict]]) -> List[dict]:
+    """Admit a document only if every experiment admits it, so that all of them see the same stream."""
+    admitted = None
+    for c in controllers.values():
+        c.load_dataset(dataset)
+        ids = {s["data_id"] for s in c.samples}
+        admitted = ids if admitted is None else admitted & ids
+    any_c = next(iter(controllers.values()))
+    return [s for s in any_c.samples if s["data_id"] in admitted]
+
+
+def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = None, log=print,
+                    cancel: Optional[Dict[str, threading.Event]] = None) -> Dict[str, Any]:
+    from aspec_b200.controller.inference_manager import InferenceManager
+    from aspec_b200.controller.loop import training_loop
+    from aspec_b200.controller.shared_source import SharedSourceState
+    from aspec_b200.controller.training_controller import TrainingController
+    from aspec_b200.inference.factory import create_engines
+    from aspec_b200.runtime.actor import ProcessActor, make_queue
+    from aspec_b200.train_entry import _devices, claim_run_directory
+    from aspec_b200.training.trainer_actor import TrainerActor
+    from aspec_b200.transport.slot_ring import GenerationSlotRing
+
+    names = plan.names
+    base = plan.plans[names[0]].to_runtime_args()
+    target_devs, _ = _devices(base)
+    union_layers = plan.union["contract"]["aux_hidden_state_layers"]
+    groups: Dict[str, dict] = {}
+    engines: list = []
+    manager = None
+    results: Dict[str, Any] = {}
+    try:
+        # ---- one trainer group per experiment --------------------------------------------------------
+        next_dev = 0
+        for n in names:
+            flat = plan.plans[n].to_runtime_args()
+            claim_run_directory(flat["output_dir"])
+            with open(os.path.join(flat["output_dir"], "plan.json"), "w") as f:
+                f.write(plan.plans[n].to_json())
+            world = int(flat["world_size"])
+            devs = flat.get("trainer_devices")
+            if not devs:
+                total = sum(int(plan.plans[m].runtime_args["world_size"]) for m in names)
+                _, pool = _devices({**flat, "training_num_gpus_per_node": total, "training_num_nodes": 1})
+                devs = pool[next_dev:next_dev + world]
+                next_dev += world
+            args = dict(flat, trainer_devices=devs, run_id=flat.get("run_id") or f"run-{int(time.time())}-{n}",
+                        attempt_id=str(flat.get("attempt_id", "0")))
+            port = int(flat.get("master_port") or 29500 + (os.getpid() % 2000)) + 17 * (names.index(n) + 1)
+            queues = {r: make_queue() for r in range(world)}
+            trainers = [ProcessActor(TrainerActor, r, world, args, plan.plans[n].draft_config, queues[r], port,
+                                     name=f"{n}-trainer{r}") for r in range(world)]
+            groups[n] = dict(flat=flat, args=args, world=world, queues=queues, trainers=trainers,
+                             layer_ids=_layer_ids(plan.plans[n].draft_config))
+        for g in groups.values():
+            for t in g["trainers"]:
+                t.wait_ready()
+        # ---- one engine pool: every reader's ring, tagged with the layers it keeps ---------------------
+        n_producers = max(len(target_devs), 1)
+        handles: Dict[int, list] = {}
+        for n in names:
+            g = groups[n]
+            for r, t in enumerate(g["trainers"]):
+                hs = t.call("ring_handle", n_producers, timeout=120)
+                for h in hs:
+                    h["layer_ids"] = list(g["layer_ids"])
+                handles[plan.consumer_offsets[n] + r] = hs
+        union_draft = dict(plan.plans[names[0]].draft_config, target_layer_ids=list(union_layers),
+                           num_target_layers=len(union_layers))
+        engines, head, embedding = create_engines(base, union_draft, list(union_layers), target_devs, handles)
+        pick = lambda v, i: v[i] if isinstance(v, list) else v
+        for n in names:
+            g = groups[n]
+            futs = [t.call_async("set_head", pick(head, plan.consumer_offsets[n] + r), pick(embedding, plan.consumer_offsets[n] + r))
+                    for r, t in enumerate(g["trainers"])]
+            for f in futs:
+                f.get(timeout=600)
+        # ---- shared stream --------------------------------------------------------------------------------
+        slots = int(base.get("transport_destination_ring_slots", 4))
+        all_rings: Dict[int, GenerationSlotRing] = {}
+        controllers = {}
+        for n in names:
+            g = groups[n]
+            cp = max(int(g["flat"].get("draft_context_parallel_size", 1)), 1)
+            g["cp"], g["dp"] = cp, g["world"] // cp
+            g["rings"] = {r: GenerationSlotRing(slots) for r in range(g["world"])}
+            for r, ring in g["rings"].items():
+                all_rings[plan.consumer_offsets[n] + r] = ring
+            controllers[n] = TrainingController(g["args"], dp_size=g["dp"], consumers_per_row=cp,
+                                                algorithm=resolve_draft_algorithm(plan.plans[n].draft_config))
+        common = _common_samples(controllers, dataset)
+        for c in controllers.values():
+            c.load_dataset(common)
+        manager = InferenceManager(engines, all_rings, on_result=lambda o, r: None,
+                                   batch_size=int(base.get("inference_batch_size", 1)),
+                                   acquire_timeout=float(base.get("transport_acquire_timeout_seconds", 120.0)))
+        shared = SharedSourceState(manager, names, plan.consumer_offsets)
+        manager.start()
+
+        def run_one(n: str) -> None:
+            g = groups[n]
+            c = controllers[n]
+            steps = int(g["flat"].get("num_train_steps") or 0) or max(
+                len(c.samples) // max(g["dp"] * int(g["flat"].get("micro_batch_size", 1))
+                                      * int(g["flat"].get("draft_accumulation_steps", 1)), 1), 1)
+            cp = g["cp"]
+            try:
+                results[n] = training_loop(controller=c, manager=shared.proxy(n), trainers=g["trainers"], rings=g["rings"],
+                                           train_queues=g["queues"], args=g["args"], layer_ids=g["layer_ids"], num_steps=steps,
+                                           log=lambda m, n=n: log({"experiment": n, **m}),
+                                           consumer_of_rank=lambda r: list(range(r * cp, (r + 1) * cp)))
+            except BaseException as exc:                       # noqa: BLE001 - one experiment must not stop the others
+                results[n] = {"failed": f"{type(exc).__name__}: {exc}"}
+                shared.fence(n, results[n]["failed"])
+                for t in g["trainers"]:
+                    t.terminate()
+
+        threads = {n: threading.Thread(target=run_one, args=(n,), name=f"experiment-{n}", daemon=True) for n in names}
+        for t in threads.values():
+            t.start()
+        while any(t.is_alive() for t in threads.values()):
+            for n, ev in (cancel or {}).items():
+                if ev.is_set() and n in shared.live:
+                    shared.fence(n, "cancelled")
+                    for t in groups[n]["trainers"]:
+                        t.terminate()
+            time.sleep(0.05)
+        results["shared_source"] = shared.status()
+        return results
+    finally:
+        if manager is not None:
+            manager.stop()
+        for a in list(engines) + [t for g in groups.values() for t in g["trainers"]]:
+            if isinstance(a, ProcessActor):
+                a.shutdown(timeout=5.0)
+
+
+def run_multi_draft_from_config(config: Config, dry_run: bool = False) -> int:
+    plan = compile_multi_draft_plan(config)
+    if dry_run:
+        print(plan.to_json())
+        return 0
+    os.makedirs(config.output_dir, exist_ok=True)
+    with open(os.path.join(config.output_dir, "multi-draft-plan.json"), "w") as f:
+        f.write(plan.to_json())
+    results = run_multi_draft(plan, log=lambda m: print(json.dumps(m, default=float), flush=True))
+    with open(os.path.join(config.output_dir, "multi-draft-summary.json"), "w") as f:
+        json.dump({k: ({kk: vv for kk, vv in v.items() if kk != "history"} if isinstance(v, dict) else v)
+                   for k, v in results.items()}, f, indent=2, default=str)
+    return 0 if all("failed" not in v for k, v in results.items() if k != "shared_source") else 1

@@ -241,16 +241,22 @@ class RemoteRing(_SlotViews):
 class RingFeatureSink:
     """``models.target.dense.FeatureSink`` protocol over one or several remote slots (multi-reader fan-out)."""
 
-    def __init__(self, slot_views, layer_ids, hidden: int):
+    def __init__(self, slot_views, layer_ids, hidden: int, reader_layer_ids=None):
         self.slot_views = list(slot_views)       # one dict of views per reader
-        self.layer_ids = list(layer_ids)
+        self.layer_ids = list(layer_ids)         # every layer the Target captures (union over readers)
+        # readers of a shared Target may each want a subset of the captured layers, in their own column order
+        self.reader_layer_ids = [list(r) for r in reader_layer_ids] if reader_layer_ids else [self.layer_ids] * len(self.slot_views)
         self.hidden = hidden
         self.hidden_states = self.slot_views[0]["hidden_states"]
         self.last_hidden_states = self.slot_views[0].get("last_hidden_states")
 
     def layer_views(self, layer_id: int):
-        col = self.layer_ids.index(layer_id)
-        return [v["hidden_states"][:, col * self.hidden:(col + 1) * self.hidden] for v in self.slot_views]
+        out = []
+        for v, layers in zip(self.slot_views, self.reader_layer_ids):
+            if layer_id in layers:
+                col = layers.index(layer_id)
+                out.append(v["hidden_states"][:, col * self.hidden:(col + 1) * self.hidden])
+        return out
 
     def final_views(self):
         return [v["last_hidden_states"] for v in self.slot_views if "last_hidden_states" in v]

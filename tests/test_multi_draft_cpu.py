@@ -1,0 +1,85 @@
+"""Two Drafts share one (synthetic) Target on CPU: identical row stream, per-reader layer subsets, independent
+ledgers and checkpoints, and fencing of a failed experiment while its sibling finishes
+(reference: tests/test_multi_draft.py, tests/test_shared_source.py)."""
+import os
+
+import pytest
+
+from aspec_b200.config.train_config import load_config
+from aspec_b200.multi_draft import compile_multi_draft_plan, run_multi_draft
+
+HERE = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DSPARK = os.path.join(HERE, "aspec_b200", "config", "drafts", "dspark_tiny.json")
+DFLASH = os.path.join(HERE, "aspec_b200", "config", "drafts", "dflash_tiny.json")
+
+
+def _plan(tmp_path, second_extra=""):
+    recipe = tmp_path / "recipe.yaml"
+    recipe.write_text(f"""
+model:
+  draft_model_config: {DSPARK}
+dataset:
+  train_data_path: synthetic
+  synthetic_num_documents: 48
+  synthetic_min_length: 32
+  synthetic_max_length: 96
+inference:
+  inference_engine_type: synthetic
+training:
+  training_num_gpus_per_node: 1
+  micro_batch_size: 1
+  draft_accumulation_steps: 2
+  max_seq_length: 128
+  num_train_steps: 3
+  learning_rate: 1e-3
+  dspark_block_size: 4
+  dspark_num_anchors: 16
+  dflash_block_size: 4
+  dflash_num_anchors: 16
+  save_interval: 0
+  seed: 7
+transport:
+  destination_ring_slots: 3
+experiments:
+  - name: spark
+  - name: flash
+    model:
+      draft_model_config: {DFLASH}
+{second_extra}
+output_dir: {tmp_path / 'run'}
+""")
+    plan = compile_multi_draft_plan(load_config(str(recipe)))
+    for p in plan.plans.values():
+        p.runtime_args.update(synthetic_vocab_size=500, force_cpu=True)
+    return plan
+
+
+@pytest.mark.timeout(600)
+def test_two_experiments_share_one_target_stream(tmp_path):
+    plan = _plan(tmp_path)
+    assert plan.union["contract"]["aux_hidden_state_layers"] == sorted(set(plan.union["contract"]["aux_hidden_state_layers"]))
+    assert [v["layer_columns"] for v in plan.union["views"]][1] != [v["layer_columns"] for v in plan.union["views"]][0]
+    logs = []
+    out = run_multi_draft(plan, log=logs.append)
+    assert out["spark"]["completed_steps"] == 3 and out["flash"]["completed_steps"] == 3
+    # one Target pass per row, not one per experiment
+    assert out["shared_source"]["rows_shared"] == 3 * 2              # 3 updates x 2 micro-batches, shared by both
+    assert out["spark"]["ledger"]["committed_work_ids"] == out["flash"]["ledger"]["committed_work_ids"]
+    assert {l["experiment"] for l in logs} == {"spark", "flash"}
+    for name in ("spark", "flash"):
+        assert os.path.isdir(os.path.join(tmp_path, "run", "experiments", name, "checkpoints"))
+
+
+@pytest.mark.timeout(600)
+def test_failed_experiment_is_fenced_and_sibling_finishes(tmp_path):
+    plan = _plan(tmp_path)
+    plan.plans["flash"].runtime_args["fault_injection"] = {"kind": "raise", "step": 1, "rank": 0}
+    out = run_multi_draft(plan, log=lambda m: None)
+    assert "failed" in out["flash"]
+    assert out["spark"]["completed_steps"] == 3
+    assert "flash" in out["shared_source"]["fenced"]
+
+
+def test_experiments_must_agree_on_the_row_stream(tmp_path):
+    with pytest.raises(ValueError, match="must agree on max_seq_length"):
+        _plan(tmp_path, second_extra="    training:\n      max_seq_length: 64\n")
