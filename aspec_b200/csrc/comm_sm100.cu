@@ -90,6 +90,89 @@ __global__ void peer_reduce_f32_kernel(PeerPtrsF peers, int n_peers, float* __re
   }
 }
 
+
+// ---- sharded optimizer over peer memory ("reduce-scatter + norm" and "AdamW + all-gather" without a library
+// collective).  Every rank owns the element range [lo, lo + n) of the flat parameter space.
+//
+// Phase 1: shard[i] = sum_r peer_grad[r][lo + i]   (p loads over NVLink, one local store) and the shard's
+//          sum of squares / non-finite flag go to ctrl[0] / ctrl[1] (block-reduced, one atomic per block).
+__global__ void shard_reduce_sumsq_kernel(PeerPtrsF peers, int n_peers, long long lo, float* __restrict__ shard,
+                                          long long n, float* __restrict__ ctrl) {
+  float ss = 0.f;
+  int bad = 0;
+  const long long nv = n >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0, 0, 0, 0);
+    for (int r = 0; r < n_peers; ++r) {
+      const float4 v = *reinterpret_cast<const float4*>(peers.p[r] + lo + 4 * i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(shard)[i] = acc;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    bad |= !(isfinite(acc.x) && isfinite(acc.y) && isfinite(acc.z) && isfinite(acc.w));
+  }
+  __shared__ float red[32];
+  __shared__ int red_bad;
+  if (threadIdx.x == 0) red_bad = 0;
+  __syncthreads();
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  if (bad) atomicOr(&red_bad, 1);
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) {
+      atomicAdd(&ctrl[0], v);
+      if (red_bad) atomicAdd(&ctrl[1], 1.f);
+    }
+  }
+}
+
+struct PeerPtrsW {
+  __nv_bfloat16* p[8];
+};
+// Phase 2: AdamW on the owned shard (fp32 master / moments are shard-sized) and the new bf16 weights stored into
+//          EVERY rank's replica of the flat parameter buffer - the parameter all-gather is the epilogue's store.
+//          ctrl as in the replicated optimizer: [0] global sum of squares, [1] non-finite flag, [2] pre-scale.
+__global__ void shard_adamw_scatter_kernel(float* __restrict__ master, const float* __restrict__ grad,
+                                           float* __restrict__ m, float* __restrict__ v, PeerPtrsW params,
+                                           int n_peers, long long lo, long long n, const float* __restrict__ ctrl,
+                                           float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                                           float bc2, float max_norm) {
+  if (ctrl[1] > 0.f || !isfinite(ctrl[0])) return;
+  const float pre = ctrl[2];
+  const float norm = pre * sqrtf(ctrl[0]);
+  float coef = pre;
+  if (max_norm > 0.f) coef *= fminf(1.f, max_norm / (norm + 1e-6f));
+  const long long nv = n >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 g4 = reinterpret_cast<const float4*>(grad)[i];
+    float4 w4 = reinterpret_cast<float4*>(master)[i];
+    float4 m4 = reinterpret_cast<float4*>(m)[i];
+    float4 v4 = reinterpret_cast<float4*>(v)[i];
+    const float g[4] = {g4.x * coef, g4.y * coef, g4.z * coef, g4.w * coef};
+    float w[4] = {w4.x, w4.y, w4.z, w4.w};
+    float mm[4] = {m4.x, m4.y, m4.z, m4.w};
+    float vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      mm[j] = beta1 * mm[j] + (1.f - beta1) * g[j];
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * g[j] * g[j];
+      w[j] = w[j] * (1.f - lr * wd) - lr * (mm[j] / bc1) / (sqrtf(vv[j] / bc2) + eps);
+    }
+    reinterpret_cast<float4*>(master)[i] = make_float4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<float4*>(m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    uint2 packed;
+    packed.x = pack_bf16x2(w[0], w[1]);
+    packed.y = pack_bf16x2(w[2], w[3]);
+    for (int r = 0; r < n_peers; ++r) *reinterpret_cast<uint2*>(params.p[r] + lo + 4 * i) = packed;
+  }
+}
+
 }  // namespace ab
 
 extern "C" {
@@ -134,6 +217,32 @@ int ab_peer_reduce(const void* const* peer_ptrs, int n_peers, void* out, long lo
     peer_reduce_bf16_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         pp, n_peers, reinterpret_cast<__nv_bfloat16*>(out), n, scale);
   }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Shard element ranges must start and end on multiples of 4 elements (16-byte fp32 vectors, 8-byte bf16 stores).
+int ab_shard_reduce_sumsq(const void* const* peer_grads, int n_peers, long long lo, float* shard, long long n,
+                          float* ctrl, void* stream) {
+  if (n_peers < 1 || n_peers > 8 || n < 0 || (n & 3) || (lo & 3)) return -10;
+  if (n == 0) return 0;
+  PeerPtrsF pp;
+  for (int i = 0; i < n_peers; ++i) pp.p[i] = reinterpret_cast<const float*>(peer_grads[i]);
+  long long grid = ((n >> 2) + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  shard_reduce_sumsq_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pp, n_peers, lo, shard, n, ctrl);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+int ab_shard_adamw_scatter(float* master, const float* grad, float* m, float* v, void* const* peer_params, int n_peers,
+                           long long lo, long long n, const float* ctrl, float lr, float beta1, float beta2, float eps,
+                           float wd, float bc1, float bc2, float max_norm, void* stream) {
+  if (n_peers < 1 || n_peers > 8 || n < 0 || (n & 3) || (lo & 3)) return -10;
+  if (n == 0) return 0;
+  PeerPtrsW pp;
+  for (int i = 0; i < n_peers; ++i) pp.p[i] = reinterpret_cast<__nv_bfloat16*>(peer_params[i]);
+  long long grid = ((n >> 2) + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  shard_adamw_scatter_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      master, grad, m, v, pp, n_peers, lo, n, ctrl, lr, beta1, beta2, eps, wd, bc1, bc2, max_norm);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 }  // extern "C"

@@ -1,0 +1,53 @@
+"""Python face of the peer-memory communication kernels (``csrc/comm_sm100.cu``).
+
+All functions take *lists of tensors that live on (or are mapped into) the launching GPU's address space*: a
+tensor opened through ``parallel.symmetric_memory.SymmetricBuffer.open`` is peer HBM that looks local, so the same
+call works for one process emulating several ranks on one GPU (tests) and for real multi-GPU peers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Sequence
+
+import torch
+
+from aspec_b200 import _native
+
+
+def _stream(t: torch.Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ptrs(tensors: Sequence[torch.Tensor]):
+    arr = (C.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    return arr
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} refused the launch (code {rc})")
+
+
+def peer_reduce(peers: Sequence[torch.Tensor], out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """``out = scale * sum(peers)`` (bf16 or fp32; element count a multiple of 8 / 4)."""
+    _check(_native.kernels().ab_peer_reduce(_ptrs(peers), len(peers), C.c_void_p(out.data_ptr()), C.c_longlong(out.numel()),
+                                            C.c_float(scale), int(out.dtype == torch.float32), _stream(out)), "ab_peer_reduce")
+    return out
+
+
+def shard_reduce_sumsq(peer_grads: Sequence[torch.Tensor], lo: int, shard: torch.Tensor, ctrl: torch.Tensor) -> None:
+    """``shard = sum_r peer_grads[r][lo : lo + len(shard)]``; ``ctrl[0] += sum(shard^2)``, ``ctrl[1] += non-finite``."""
+    _check(_native.kernels().ab_shard_reduce_sumsq(_ptrs(peer_grads), len(peer_grads), C.c_longlong(lo),
+                                                   C.c_void_p(shard.data_ptr()), C.c_longlong(shard.numel()),
+                                                   C.c_void_p(ctrl.data_ptr()), _stream(shard)), "ab_shard_reduce_sumsq")
+
+
+def shard_adamw_scatter(master, grad, m, v, peer_params: Sequence[torch.Tensor], lo: int, ctrl, *, lr, beta1, beta2, eps,
+                        wd, step, max_norm) -> None:
+    """AdamW on the owned shard; the new bf16 weights are stored into every replica ``peer_params[r][lo : lo + n]``."""
+    f = C.c_float
+    _check(_native.kernels().ab_shard_adamw_scatter(
+        C.c_void_p(master.data_ptr()), C.c_void_p(grad.data_ptr()), C.c_void_p(m.data_ptr()), C.c_void_p(v.data_ptr()),
+        _ptrs(peer_params), len(peer_params), C.c_longlong(lo), C.c_longlong(master.numel()), C.c_void_p(ctrl.data_ptr()),
+        f(lr), f(beta1), f(beta2), f(eps), f(wd), f(1.0 - beta1 ** step), f(1.0 - beta2 ** step), f(max_norm),
+        _stream(master)), "ab_shard_adamw_scatter")

@@ -38,17 +38,26 @@ class DraftTrainer:
                  min_lr: float = 6e-5, weight_decay: float = 0.0, max_grad_norm: float = 1.0,
                  total_steps: int = 1000, warmup_ratio: float = 0.04, decay_style: str = "cosine",
                  accumulation: int = 1, dp_group: Optional[dist.ProcessGroup] = None,
-                 device: Optional[torch.device] = None, betas=(0.9, 0.999)):
+                 device: Optional[torch.device] = None, betas=(0.9, 0.999), fsdp_strategy: str = "REPLICATE"):
         self.model = model
         self.draft = model.draft_model
         self.lm_head_weight = lm_head_weight
         self.accumulation = int(accumulation)
         self.dp_group = dp_group
         self.device = device or next(model.parameters()).device
-        self.optimizer = BF16Optimizer(self.draft, lr=lr, weight_decay=weight_decay,
-                                       max_grad_norm=max_grad_norm, total_steps=total_steps,
-                                       warmup_ratio=warmup_ratio, decay_style=decay_style, min_lr=min_lr,
-                                       betas=betas)
+        self.sharded = (fsdp_strategy == "FULL_SHARD" and dist.is_available() and dist.is_initialized()
+                        and dist.get_world_size(dp_group) > 1)
+        if self.sharded:
+            # gradients, masters and moments sharded over the data-parallel ranks; reduction and update over peer memory
+            from aspec_b200.training.sharded_optimizer import ShardedBF16Optimizer
+            self.optimizer = ShardedBF16Optimizer(self.draft, lr=lr, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
+                                                  total_steps=total_steps, warmup_ratio=warmup_ratio, decay_style=decay_style,
+                                                  min_lr=min_lr, betas=betas, group=dp_group)
+        else:
+            self.optimizer = BF16Optimizer(self.draft, lr=lr, weight_decay=weight_decay,
+                                           max_grad_norm=max_grad_norm, total_steps=total_steps,
+                                           warmup_ratio=warmup_ratio, decay_style=decay_style, min_lr=min_lr,
+                                           betas=betas)
         self.global_step = 0
         self._pool: Dict[str, List[torch.Tensor]] = {}
         self._last: Dict[str, torch.Tensor] = {}
@@ -120,7 +129,8 @@ class DraftTrainer:
                 m = pooled[k].numel()
                 pooled[k] = flat[off:off + m].view_as(pooled[k])
                 off += m
-            dist.all_reduce(opt.flat_grad, group=self.dp_group)
+            if not self.sharded:            # the sharded optimizer reduces its own shard from the peers' buffers
+                dist.all_reduce(opt.flat_grad, group=self.dp_group)
         den = pooled["loss"][1]
         opt.set_grad_scale(torch.where(den > 0, 1.0 / den.clamp(min=1e-12), torch.zeros_like(den)))
         grad_norm = opt.step()

@@ -82,7 +82,8 @@ class TrainerActor:
                                     weight_decay=a.get("weight_decay", 0.0), max_grad_norm=a.get("max_grad_norm", 0.5),
                                     total_steps=int(a.get("lr_total_steps") or a.get("num_train_steps") or 1000),
                                     warmup_ratio=a.get("warmup_ratio", 0.015), decay_style=a.get("lr_decay_style", "cosine"),
-                                    accumulation=int(a.get("draft_accumulation_steps", 1)), device=self.device)
+                                    accumulation=int(a.get("draft_accumulation_steps", 1)), device=self.device,
+                                    fsdp_strategy=str(a.get("fsdp_strategy", "REPLICATE")))
 
     # -- data ---------------------------------------------------------------------------------------
     def _batch(self, sample: TrainSample) -> dict:

@@ -94,3 +94,25 @@ def test_step_deadline_terminates_trainers(tmp_path):
     from aspec_b200.controller.loop import TrainerStepTimeoutError
     with pytest.raises(TrainerStepTimeoutError):
         train_async_no_generation(flat, plan.draft_config, log=lambda m: None)
+
+
+@pytest.mark.timeout(600)
+def test_full_shard_matches_replicate(tmp_path):
+    """Same recipe under REPLICATE and FULL_SHARD: identical losses, and the sharded run's checkpoint resumes."""
+    losses = {}
+    for strategy in ("REPLICATE", "FULL_SHARD"):
+        plan = _plan(tmp_path / strategy if (tmp_path / strategy).mkdir() is None else tmp_path, [f"training.fsdp_strategy={strategy}"])
+        flat = plan.to_runtime_args()
+        flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=2, save_final_checkpoint=False)
+        os.makedirs(flat["output_dir"], exist_ok=True)
+        logs = []
+        train_async_no_generation(flat, plan.draft_config, log=logs.append)
+        losses[strategy] = [l["train/avg_loss"] for l in logs]
+        if strategy == "FULL_SHARD":
+            ck = os.path.join(flat["output_dir"], "checkpoints", "iter_0000002")
+            logs2 = []
+            train_async_no_generation(dict(flat, load_path=ck, output_dir=str(tmp_path / "resumed"), save_interval=0),
+                                      plan.draft_config, log=logs2.append)
+            assert logs2[0]["train/step"] == 2
+            assert logs2[0]["train/avg_loss"] == pytest.approx(logs[2]["train/avg_loss"], rel=1e-5)
+    assert losses["FULL_SHARD"] == pytest.approx(losses["REPLICATE"], rel=1e-5)
