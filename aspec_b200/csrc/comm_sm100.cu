@@ -173,6 +173,43 @@ __global__ void shard_adamw_scatter_kernel(float* __restrict__ master, const flo
   }
 }
 
+// ---- vocabulary-parallel merges over peer memory -----------------------------------------------------------
+// out[i] = log sum_r exp(lse_r[i])   (each rank's partial log-sum-exp over its vocabulary shard)
+__global__ void peer_lse_merge_kernel(PeerPtrsF peers, int n_peers, float* __restrict__ out, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float v[8];
+    float m = -INFINITY;
+    for (int r = 0; r < n_peers; ++r) {
+      v[r] = peers.p[r][i];
+      m = fmaxf(m, v[r]);
+    }
+    float s = 0.f;
+    for (int r = 0; r < n_peers; ++r)
+      if (v[r] > -INFINITY) s += __expf(v[r] - m);
+    out[i] = m + __logf(s);
+  }
+}
+struct PeerPtrsI {
+  const int* p[8];
+};
+// Per row: the arg-max over all shards (largest value, smallest global column on ties) compared with the label.
+__global__ void peer_argmax_merge_kernel(PeerPtrsF vals, PeerPtrsI idxs, int n_peers, const long long* __restrict__ labels,
+                                         float* __restrict__ correct, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int r = 0; r < n_peers; ++r) {
+      const float v = vals.p[r][i];
+      const int a = idxs.p[r][i];
+      if (v > best || (v == best && a < arg)) {
+        best = v;
+        arg = a;
+      }
+    }
+    correct[i] = (long long)arg == labels[i] ? 1.f : 0.f;
+  }
+}
+
 }  // namespace ab
 
 extern "C" {
@@ -243,6 +280,30 @@ int ab_shard_adamw_scatter(float* master, const float* grad, float* m, float* v,
   if (grid > 148 * 8) grid = 148 * 8;
   shard_adamw_scatter_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       master, grad, m, v, pp, n_peers, lo, n, ctrl, lr, beta1, beta2, eps, wd, bc1, bc2, max_norm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int ab_peer_lse_merge(const void* const* peer_lse, int n_peers, float* out, long long n, void* stream) {
+  if (n_peers < 1 || n_peers > 8 || n <= 0) return n == 0 ? 0 : -10;
+  PeerPtrsF pp;
+  for (int i = 0; i < n_peers; ++i) pp.p[i] = reinterpret_cast<const float*>(peer_lse[i]);
+  long long grid = (n + 255) / 256;
+  if (grid > 148 * 4) grid = 148 * 4;
+  peer_lse_merge_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pp, n_peers, out, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+int ab_peer_argmax_merge(const void* const* peer_vals, const void* const* peer_idxs, int n_peers, const long long* labels,
+                         float* correct, long long n, void* stream) {
+  if (n_peers < 1 || n_peers > 8 || n <= 0) return n == 0 ? 0 : -10;
+  PeerPtrsF pv;
+  PeerPtrsI pi;
+  for (int i = 0; i < n_peers; ++i) {
+    pv.p[i] = reinterpret_cast<const float*>(peer_vals[i]);
+    pi.p[i] = reinterpret_cast<const int*>(peer_idxs[i]);
+  }
+  long long grid = (n + 255) / 256;
+  if (grid > 148 * 4) grid = 148 * 4;
+  peer_argmax_merge_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pv, pi, n_peers, labels, correct, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 }  // extern "C"

@@ -332,6 +332,16 @@ struct VocabLossParams {
   int mode;
   float a_ce, a_l1;
   int write_grad;
+  // vocabulary shards (all null / 0 for the unsharded head):
+  //   partial == 1: statistics pass over this rank's columns only; lse_s / lse_t are the GLOBAL normalisers;
+  //                 ce_out = -s[label] when the label's column is local else 0, l1_out = partial sum|p - q|,
+  //                 c_io = partial sum p*sign(p - q), best_val / best_idx = local arg-max (global column index).
+  //   partial == 2: gradient pass only; c_io holds the sum of all ranks' partials.
+  int partial;
+  long long vocab_offset;       // global index of local column 0
+  float* c_io;                  // [R]
+  float* best_val_out;          // [R]
+  int* best_idx_out;            // [R]
 };
 
 __global__ void __launch_bounds__(512) vocab_loss_kernel(const VocabLossParams p) {
@@ -343,14 +353,16 @@ __global__ void __launch_bounds__(512) vocab_loss_kernel(const VocabLossParams p
   const __nv_bfloat16* trow = p.teacher ? p.teacher + (size_t)ti * p.ld_t : nullptr;
   const float ls = p.lse_s[r];
   const float lt = trow ? p.lse_t[ti] : 0.f;
-  const long long label = p.labels[r];
+  const long long label = p.labels[r] - p.vocab_offset;   // local column of the label (may be out of range)
   const float wgt = p.weight[r];
   const int nv = p.V >> 3;  // V % 8 == 0 is required by the launcher
   constexpr float L2E = 1.4426950408889634f;
-
-  // pass A: l1 = sum|p-q|, c = sum p*sign(p-q), cross = sum q*s, argmax
   float l1 = 0.f, c = 0.f, cross = 0.f, best = -INFINITY, tbest = -INFINITY;
   int best_i = 0x7fffffff, tbest_i = 0x7fffffff;
+  if (p.partial == 2) {
+    c = p.c_io[r];
+  } else {
+  // pass A: l1 = sum|p-q|, c = sum p*sign(p-q), cross = sum q*s, argmax
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     float s[8], t[8];
     unpack8(reinterpret_cast<const uint4*>(srow)[i], s);
@@ -402,10 +414,19 @@ __global__ void __launch_bounds__(512) vocab_loss_kernel(const VocabLossParams p
 
   const float s_label = (label >= 0 && label < p.V) ? __bfloat162float(srow[label]) : 0.f;
   if (threadIdx.x == 0) {
-    p.ce_out[r] = p.mode == 1 ? (ls - cross) : (ls - s_label);
-    p.l1_out[r] = l1;
-    p.correct_out[r] = (gidx == (p.mode == 1 && trow ? tidx : (int)label)) ? 1.f : 0.f;
+    if (p.partial == 1) {
+      p.ce_out[r] = -s_label;
+      p.l1_out[r] = l1;
+      p.c_io[r] = c;
+      p.best_val_out[r] = gbest;
+      p.best_idx_out[r] = (int)p.vocab_offset + gidx;
+    } else {
+      p.ce_out[r] = p.mode == 1 ? (ls - cross) : (ls - s_label);
+      p.l1_out[r] = l1;
+      p.correct_out[r] = (gidx == (p.mode == 1 && trow ? tidx : (int)label)) ? 1.f : 0.f;
+    }
   }
+  }  // statistics pass
   if (!p.write_grad) return;
   __syncthreads();
   // pass B: gradient
@@ -634,6 +655,46 @@ int ab_vocab_loss(void* logits, const void* teacher, const float* lse_s, const f
   p.a_ce = a_ce;
   p.a_l1 = a_l1;
   p.write_grad = write_grad;
+  p.partial = 0;
+  p.vocab_offset = 0;
+  p.c_io = nullptr;
+  p.best_val_out = nullptr;
+  p.best_idx_out = nullptr;
+  vocab_loss_kernel<<<R, 512, 0, STREAM>>>(p);
+  return LAUNCH_OK;
+}
+// Vocabulary-sharded form of the same kernel (mode 0).  phase 1 = statistics over the local columns, phase 2 =
+// gradient with the globally summed `c`.  `lse_s` / `lse_t` are the normalisers over the FULL vocabulary.
+int ab_vocab_loss_shard(void* logits, const void* teacher, const float* lse_s, const float* lse_t,
+                        const int* t_index, const long long* labels, const float* weight, float* ce_part,
+                        float* l1_part, float* c_io, float* best_val, int* best_idx, long long ld,
+                        long long ld_t, int R, int V_local, long long vocab_offset, float a_ce, float a_l1,
+                        int phase, void* stream) {
+  if ((V_local & 7) || (ld & 7) || (ld_t & 7) || (phase != 1 && phase != 2)) return -10;
+  if (R <= 0) return 0;
+  VocabLossParams p;
+  p.logits = (__nv_bfloat16*)logits;
+  p.teacher = (const __nv_bfloat16*)teacher;
+  p.lse_s = lse_s;
+  p.lse_t = lse_t;
+  p.t_index = t_index;
+  p.labels = labels;
+  p.weight = weight;
+  p.ce_out = ce_part;
+  p.l1_out = l1_part;
+  p.correct_out = nullptr;
+  p.ld = ld;
+  p.ld_t = ld_t;
+  p.V = V_local;
+  p.mode = 0;
+  p.a_ce = a_ce;
+  p.a_l1 = a_l1;
+  p.write_grad = phase == 2;
+  p.partial = phase;
+  p.vocab_offset = vocab_offset;
+  p.c_io = c_io;
+  p.best_val_out = best_val;
+  p.best_idx_out = best_idx;
   vocab_loss_kernel<<<R, 512, 0, STREAM>>>(p);
   return LAUNCH_OK;
 }

@@ -65,9 +65,12 @@ struct GemmParams {
   // captured-layer epilogue writes the residual stream to its own buffer and straight into the ring
   // slots of the consuming Draft ranks (peer memory mapped into this process, plain st.global over
   // NVLink).  mirror_ld is the row stride in elements.
-  void* mirror[4];
-  long long mirror_ld[4];
+  void* mirror[8];
+  long long mirror_ld[8];
   int n_mirrors;
+  // mirror_cols > 0: scatter instead of broadcast - output columns [m * mirror_cols, (m + 1) * mirror_cols) go ONLY
+  // to mirror[m], at column (col % mirror_cols); D itself is not written (sequence<->head all-to-all in the epilogue).
+  int mirror_cols;
   int stream_k;
   int full_tiles;
   long long units_per_cta;
@@ -399,6 +402,27 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                   drow[i] = __uint_as_float(r[i]) * alpha + (crow ? crow[i] : 0.f);
               }
             } else {
+              if (p.mirror_cols > 0) {
+                // scatter: this 32-column chunk belongs to exactly one destination
+                const int gcol = col0 + c;
+                const int dst = gcol / p.mirror_cols;
+                __nv_bfloat16* mrow = reinterpret_cast<__nv_bfloat16*>(p.mirror[dst]) +
+                                      (long long)row * p.mirror_ld[dst] + (gcol - dst * p.mirror_cols);
+                if (ncol >= 32) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    uint4 o;
+                    o.x = pack_bf16x2(__uint_as_float(r[8 * i]) * alpha, __uint_as_float(r[8 * i + 1]) * alpha);
+                    o.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * alpha, __uint_as_float(r[8 * i + 3]) * alpha);
+                    o.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * alpha, __uint_as_float(r[8 * i + 5]) * alpha);
+                    o.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * alpha, __uint_as_float(r[8 * i + 7]) * alpha);
+                    reinterpret_cast<uint4*>(mrow)[i] = o;
+                  }
+                } else {
+                  for (int i = 0; i < ncol; ++i) mrow[i] = __float2bfloat16(__uint_as_float(r[i]) * alpha);
+                }
+                continue;
+              }
               __nv_bfloat16* drow =
                   reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)row * p.ldd + col0 + c;
               const __nv_bfloat16* crow =
@@ -566,6 +590,7 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
                  const AbOperand* a1, const AbOperand* b1, void* D, long long ldd, int d_is_fp32,
                  const void* C, float alpha, int epi, float* stats, float logit_scale, int* status,
                  int max_ctas, int stream_k, int n_mirrors, void* const* mirrors, const long long* mirror_lds,
+                 int mirror_cols,
                  void* stream) {
   using namespace ab;
   if (M <= 0 || N <= 0 || K0 <= 0 || K1 < 0) return -10;
@@ -603,14 +628,18 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
   p.logit_scale = logit_scale;
   p.status = status;
   p.n_mirrors = 0;
+  p.mirror_cols = 0;
   if (n_mirrors > 0) {
-    if (n_mirrors > 4 || epi != EPI_STORE || d_is_fp32 || stream_k) return -17;
+    if (n_mirrors > 8 || epi != EPI_STORE || d_is_fp32 || stream_k) return -17;
+    // scatter mode: whole 32-column chunks per destination, all of N covered, no addend
+    if (mirror_cols < 0 || (mirror_cols > 0 && ((mirror_cols & 31) || (long long)mirror_cols * n_mirrors < N || C))) return -17;
     for (int m = 0; m < n_mirrors; ++m) {
       if ((reinterpret_cast<uintptr_t>(mirrors[m]) & 15) || (mirror_lds[m] & 7) || (ldd & 7)) return -17;
       p.mirror[m] = mirrors[m];
       p.mirror_ld[m] = mirror_lds[m];
     }
     p.n_mirrors = n_mirrors;
+    p.mirror_cols = mirror_cols;
   }
   p.stream_k = 0;
   p.full_tiles = 0;

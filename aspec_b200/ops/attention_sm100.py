@@ -37,14 +37,18 @@ def _rows_view(t: torch.Tensor) -> Tuple[torch.Tensor, int]:
     return t, t.stride(0)
 
 
-def forward(q, k, v, intervals, scale) -> Tuple[torch.Tensor, torch.Tensor]:
+def forward(q, k, v, intervals, scale, out=None, lse=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``q`` may be another GPU's memory mapped here (TMA loads it over NVLink) and ``out`` / ``lse`` may be slots
+    in the query owner's memory: that is how context-parallel partial attention moves its data."""
     Q, hq, d = q.shape
     tk, hkv = k.shape[0], k.shape[1]
     q = q.contiguous()
     k, k_ld = _rows_view(k)
     v, v_ld = _rows_view(v)
-    out = torch.empty_like(q)
-    lse = torch.empty(hq, Q, dtype=torch.float32, device=q.device)
+    out = torch.empty_like(q) if out is None else out
+    lse = torch.empty(hq, Q, dtype=torch.float32, device=q.device) if lse is None else lse
+    if not (out.is_contiguous() and lse.is_contiguous() and out.shape == q.shape and lse.shape == (hq, Q)):
+        raise ValueError("out / lse destinations must be contiguous [Q, H, d] / [H, Q]")
     st = status_word(q.device)
     rc = _native.kernels().ab_attn_fwd(
         _c.c_void_p(q.data_ptr()), _c.c_void_p(k.data_ptr()), _c.c_void_p(v.data_ptr()),
@@ -56,13 +60,15 @@ def forward(q, k, v, intervals, scale) -> Tuple[torch.Tensor, torch.Tensor]:
     return out, lse
 
 
-def backward(q, k, v, intervals, out, lse, dout, scale):
+def backward(q, k, v, intervals, out, lse, dout, scale, dq=None):
     Q, hq, d = q.shape
     tk, hkv = k.shape[0], k.shape[1]
     lib = _native.kernels()
     k, k_ld = _rows_view(k)
     v, v_ld = _rows_view(v)
-    dq = torch.empty_like(q)
+    dq = torch.empty_like(q) if dq is None else dq
+    if not (dq.is_contiguous() and dq.shape == q.shape):
+        raise ValueError("dq destination must be contiguous [Q, H, d]")
     dk = torch.empty(tk, hkv, d, dtype=q.dtype, device=q.device)
     dv = torch.empty(tk, hkv, d, dtype=q.dtype, device=q.device)
     delta = torch.empty(hq, Q, dtype=torch.float32, device=q.device)

@@ -51,3 +51,19 @@ def shard_adamw_scatter(master, grad, m, v, peer_params: Sequence[torch.Tensor],
         _ptrs(peer_params), len(peer_params), C.c_longlong(lo), C.c_longlong(master.numel()), C.c_void_p(ctrl.data_ptr()),
         f(lr), f(beta1), f(beta2), f(eps), f(wd), f(1.0 - beta1 ** step), f(1.0 - beta2 ** step), f(max_norm),
         _stream(master)), "ab_shard_adamw_scatter")
+
+
+def peer_lse_merge(peer_lse: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """``out[i] = logsumexp_r peer_lse[r][i]`` (fp32)."""
+    _check(_native.kernels().ab_peer_lse_merge(_ptrs(peer_lse), len(peer_lse), C.c_void_p(out.data_ptr()),
+                                               C.c_longlong(out.numel()), _stream(out)), "ab_peer_lse_merge")
+    return out
+
+
+def peer_argmax_merge(peer_vals: Sequence[torch.Tensor], peer_idxs: Sequence[torch.Tensor], labels: torch.Tensor,
+                      correct: torch.Tensor) -> torch.Tensor:
+    """``correct[i] = (argmax over all shards == labels[i])``; ``peer_idxs`` hold global column indices (int32)."""
+    _check(_native.kernels().ab_peer_argmax_merge(_ptrs(peer_vals), _ptrs(peer_idxs), len(peer_vals),
+                                                  C.c_void_p(labels.data_ptr()), C.c_void_p(correct.data_ptr()),
+                                                  C.c_longlong(correct.numel()), _stream(correct)), "ab_peer_argmax_merge")
+    return correct

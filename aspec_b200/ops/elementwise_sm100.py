@@ -101,6 +101,18 @@ def vocab_loss(logits, teacher, lse_s, lse_t, t_index, labels, weight, *, mode: 
     return ce, l1, correct
 
 
+def vocab_loss_shard(logits, teacher, lse_s, lse_t, t_index, labels, weight, ce_part, l1_part, c_io, best_val, best_idx, *,
+                     vocab_offset: int, a_ce: float, a_l1: float, phase: int) -> None:
+    """Vocabulary-sharded loss: ``phase=1`` writes this shard's statistics, ``phase=2`` turns ``logits`` into the
+    gradient using the globally summed ``c_io``.  ``lse_s`` / ``lse_t`` are normalisers over the full vocabulary."""
+    R, V = logits.shape
+    _check(_native.kernels().ab_vocab_loss_shard(
+        _p(logits), _p(teacher), _p(lse_s), _p(lse_t), _p(t_index), _p(labels), _p(weight), _p(ce_part), _p(l1_part),
+        _p(c_io), _p(best_val), _p(best_idx), _c.c_longlong(logits.stride(0)),
+        _c.c_longlong(teacher.stride(0) if teacher is not None else 0), R, V, _c.c_longlong(vocab_offset),
+        _c.c_float(a_ce), _c.c_float(a_l1), int(phase), _stream(logits)), "ab_vocab_loss_shard")
+
+
 def sumsq(g: torch.Tensor, out: torch.Tensor) -> None:
     _check(_native.kernels().ab_sumsq(_p(g), _c.c_longlong(g.numel()), _p(out), _stream(g)), "ab_sumsq")
 

@@ -85,8 +85,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
          addend: Optional[torch.Tensor] = None, alpha: float = 1.0,
          epilogue: int = EPI_STORE, stats: Optional[torch.Tensor] = None,
          logit_scale: float = 1.0, max_ctas: int = 0, stream_k: Optional[bool] = None,
-         mirrors=None) -> torch.Tensor:
+         mirrors=None, scatter_cols: int = 0) -> torch.Tensor:
     """``alpha * (A @ B^T [+ A2 @ B2^T]) [+ addend]`` with a fused epilogue.
+
+    ``mirrors``: extra bf16 destinations (up to 8, possibly views of other GPUs' memory) that receive every output
+    tile straight from the epilogue.  With ``scatter_cols > 0`` the output is scattered instead: columns
+    ``[m * scatter_cols, (m + 1) * scatter_cols)`` go only to ``mirrors[m]`` (its own column origin at 0) and no
+    local result is written - the sequence-to-head all-to-all of Ulysses attention done by the GEMM's stores.
 
     ``stream_k=None`` picks the schedule: when whole output tiles would leave more than ~12 % of the last
     wave of CTAs idle (for example 448 tiles on 148 SMs), the (tile, k-block) space is divided evenly
@@ -123,6 +128,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
             out = torch.zeros((M, N), dtype=torch.float32, device=a.device)
         elif not inplace_acc:
             out.zero_()
+    if scatter_cols:
+        if not mirrors or scatter_cols % 32 or scatter_cols * len(mirrors) < N or addend is not None:
+            raise ValueError("scatter needs mirrors covering all columns in multiples of 32 and no addend")
+        out = mirrors[0]                       # placeholder for the descriptor; never written in scatter mode
     if out is None:
         out = torch.empty((M, n_out), dtype=out_dtype, device=a.device)
     if out.stride(1) != 1:
@@ -145,9 +154,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         ctypes.c_float(logit_scale), ctypes.c_void_p(st.data_ptr()),
         ctypes.c_int(max_ctas), ctypes.c_int(1 if stream_k else 0),
         ctypes.c_int(len(mirrors) if mirrors else 0), _mirror_ptrs(mirrors), _mirror_lds(mirrors),
+        ctypes.c_int(int(scatter_cols)),
         ctypes.c_void_p(torch.cuda.current_stream(a.device).cuda_stream))
     if rc != 0:
         raise RuntimeError(f"ab_gemm_bf16 refused the launch (code {rc}) for M={M} N={N} K={K}")
+    if scatter_cols:
+        return None
     if workspace_for is not None:
         from aspec_b200.ops import elementwise_sm100 as E
         cast = E.cast_scale(out)

@@ -1,0 +1,131 @@
+"""Ulysses sequence<->head exchange done by the GEMMs around attention (no all-to-all collective).
+
+Sequence-parallel attention (reference: aspec/models/ops/eagle_thd.py:32-54 ``_SequenceHeads`` and the yunchang
+``SeqAllToAll4D`` calls in aspec/models/draft/llama3_eagle.py:2078-2148) needs, per layer, an all-to-all that turns
+"my rows, all heads" into "all rows, my heads" for Q, K, V and the inverse for the attention output.  Here:
+
+* sequence -> heads: the QKV projection's epilogue scatters each column block (one rank's heads) into that rank's
+  receive buffer at this rank's row range - the GEMM's own stores are the all-to-all (``scatter_cols`` epilogue);
+* heads -> sequence: the output projection reads its K-dimension from ``p`` sources - head group ``g`` of this rank's
+  rows lives in rank ``g``'s attention output, loaded by TMA over NVLink (two sources per launch, accumulated).
+
+The backward pass uses the same two primitives with the roles swapped.  Weight layout: the fused QKV weight's rows
+are grouped per rank ``[q heads of g | k heads of g | v heads of g]`` so that a rank's columns are contiguous.
+Phases are separate methods so that several ranks can be emulated in one process.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
+
+
+def _up(n: int, a: int = 256) -> int:
+    return -(-n // a) * a
+
+
+def group_qkv_rows(wq, wk, wv, world: int, head_dim: int) -> torch.Tensor:
+    """Reorder ``[Hq*d | Hk*d | Hk*d, D]`` projection rows into per-rank column groups."""
+    hq, hk = wq.shape[0] // head_dim // world, wk.shape[0] // head_dim // world
+    parts = []
+    for g in range(world):
+        parts += [wq[g * hq * head_dim:(g + 1) * hq * head_dim], wk[g * hk * head_dim:(g + 1) * hk * head_dim],
+                  wv[g * hk * head_dim:(g + 1) * hk * head_dim]]
+    return torch.cat(parts, 0).contiguous()
+
+
+class UlyssesWorkspace:
+    def __init__(self, world: int, rows_per_rank: int, qkv_cols: int, out_cols: int, device=None,
+                 buffer: Optional[SymmetricBuffer] = None):
+        """``qkv_cols`` = one rank's share of the QKV columns, ``out_cols`` = one rank's share of the attention output."""
+        self.world, self.rows, self.qkv_cols, self.out_cols = world, rows_per_rank, qkv_cols, out_cols
+        total = world * rows_per_rank
+        sizes = [("qkv", total * qkv_cols * 2), ("attn", total * out_cols * 2), ("dqkv", total * qkv_cols * 2),
+                 ("dattn", total * out_cols * 2)]
+        self._off, off = {}, 0
+        for name, n in sizes:
+            self._off[name] = (off, n)
+            off += _up(n)
+        self.buffer = buffer if buffer is not None else SymmetricBuffer.allocate(off, device)
+        raw = self.buffer.tensor
+        v = lambda name, cols: raw[self._off[name][0]: self._off[name][0] + self._off[name][1]].view(torch.bfloat16).view(total, cols)
+        self.qkv, self.dqkv = v("qkv", qkv_cols), v("dqkv", qkv_cols)           # all rows, my heads
+        self.attn, self.dattn = v("attn", out_cols), v("dattn", out_cols)
+
+    def export(self) -> dict:
+        return {"memory": self.buffer.export(), "world": self.world, "rows": self.rows, "qkv_cols": self.qkv_cols,
+                "out_cols": self.out_cols}
+
+    @classmethod
+    def open(cls, meta: dict) -> "UlyssesWorkspace":
+        return cls(meta["world"], meta["rows"], meta["qkv_cols"], meta["out_cols"], buffer=SymmetricBuffer.open(meta["memory"]))
+
+
+def _multi_source(sources_a: Sequence[torch.Tensor], sources_b: Sequence[torch.Tensor], a_t=False, b_t=False,
+                  out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``sum_g A_g @ B_g^T`` two sources per launch (the GEMM's dual K range), later launches accumulate."""
+    from aspec_b200.ops import gemm as G
+    out = None
+    for i in range(0, len(sources_a), 2):
+        a2 = sources_a[i + 1] if i + 1 < len(sources_a) else None
+        b2 = sources_b[i + 1] if i + 1 < len(sources_b) else None
+        out = G.gemm(sources_a[i], sources_b[i], a_t=a_t, b_t=b_t, a2=a2, b2=b2, out=out, addend=out,
+                     out_dtype=out_dtype, stream_k=False)
+    return out
+
+
+class UlyssesExchange:
+    def __init__(self, rank: int, world: int, workspaces: Sequence[UlyssesWorkspace], barrier: Optional[Callable[[], None]] = None):
+        self.rank, self.world, self.ws = rank, world, list(workspaces)
+        self.mine = self.ws[rank]
+        self.barrier = barrier or (lambda: None)
+
+    def _rows(self, r: int) -> slice:
+        return slice(r * self.mine.rows, (r + 1) * self.mine.rows)
+
+    # -- forward ------------------------------------------------------------------------------------------
+    def project_scatter(self, x: torch.Tensor, w_grouped: torch.Tensor) -> None:
+        """``x [T_loc, D] @ W^T`` with each rank's column block stored into that rank's ``qkv`` rows of this rank."""
+        from aspec_b200.ops import gemm as G
+        dests = [w.qkv[self._rows(self.rank)] for w in self.ws]
+        G.gemm(x, w_grouped, mirrors=dests, scatter_cols=self.mine.qkv_cols)
+
+    def received_qkv(self) -> torch.Tensor:
+        return self.mine.qkv                      # [T_tot, my columns]
+
+    def publish_attention(self, attn: torch.Tensor) -> None:
+        self.mine.attn.copy_(attn.reshape(self.mine.attn.shape))
+
+    def output_projection(self, w_o: torch.Tensor) -> torch.Tensor:
+        """``out[T_loc, D] = sum_g attn_g[my rows] @ W_o[:, cols_g]^T`` with ``attn_g`` read from rank ``g``."""
+        c = self.mine.out_cols
+        return _multi_source([w.attn[self._rows(self.rank)] for w in self.ws],
+                             [w_o[:, g * c:(g + 1) * c] for g in range(self.world)])
+
+    # -- backward -----------------------------------------------------------------------------------------
+    def output_projection_backward(self, dout: torch.Tensor, w_o: torch.Tensor):
+        """``d attn_g[my rows] = dout @ W_o[:, cols_g]`` scattered to rank ``g``; returns ``dW_o`` (fp32)."""
+        from aspec_b200.ops import gemm as G
+        dests = [w.dattn[self._rows(self.rank)] for w in self.ws]
+        G.gemm(dout, w_o, b_t=True, mirrors=dests, scatter_cols=self.mine.out_cols)
+        c = self.mine.out_cols
+        parts = [G.gemm(dout, w.attn[self._rows(self.rank)], a_t=True, b_t=True, out_dtype=torch.float32, stream_k=False)
+                 for w in self.ws]
+        return torch.cat(parts, 1)                # [D, Hq*d] columns grouped by rank, as W_o's
+
+    def received_dattn(self) -> torch.Tensor:
+        return self.mine.dattn
+
+    def publish_dqkv(self, dqkv: torch.Tensor) -> None:
+        self.mine.dqkv.copy_(dqkv.reshape(self.mine.dqkv.shape))
+
+    def projection_backward(self, x: torch.Tensor, w_grouped: torch.Tensor):
+        """``dx = sum_g dqkv_g[my rows] @ W_g`` and ``dW_g = dqkv_g[my rows]^T @ x`` with ``dqkv_g`` read from rank ``g``."""
+        from aspec_b200.ops import gemm as G
+        c = self.mine.qkv_cols
+        srcs = [w.dqkv[self._rows(self.rank)] for w in self.ws]
+        dx = _multi_source(srcs, [w_grouped[g * c:(g + 1) * c] for g in range(self.world)], b_t=True)
+        dw = torch.cat([G.gemm(s, x, a_t=True, b_t=True, out_dtype=torch.float32, stream_k=False) for s in srcs], 0)
+        return dx, dw
