@@ -214,7 +214,7 @@ def vocab_parallel_head_loss(head: VocabParallelHead, hidden, lm_w_shard, labels
     holder = markov_w2 if isinstance(markov_w2, torch.nn.Parameter) else None
     return _VocabParallelLossFn.apply(
         head, hidden.contiguous(), lm_w_shard, prev_emb.contiguous() if prev_emb is not None else None,
-        w2_shard.detach().contiguous() if w2_shard is not None else None,
+        w2_shard.contiguous() if w2_shard is not None else None,
         teacher_hidden.contiguous() if teacher_hidden is not None else None,
         t_index.to(torch.int32).contiguous() if t_index is not None else None, labels.long().contiguous(),
         weight.float().contiguous(), float(a_ce), float(a_l1), holder)

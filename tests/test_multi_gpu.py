@@ -1,0 +1,162 @@
+"""Real two-GPU runs of the peer-memory layers (one process per GPU, NCCL for the barriers only): FULL_SHARD
+optimizer, vocabulary-parallel head, direct context-parallel attention, Ulysses projections.  Skipped when fewer
+than two GPUs are visible.  NVLS is off and the kernels use plain peer loads / stores."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, rtol, atol):
+    return bool(torch.allclose(a.float(), b.float(), rtol=rtol, atol=atol))
+
+
+def _worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    res = {}
+    from aspec_b200.parallel.group import exchange_workspaces, make_barrier
+    barrier = make_barrier(dev)
+    bf = torch.bfloat16
+    try:
+        # ---- FULL_SHARD optimizer against the replicated one -------------------------------------------------
+        from aspec_b200.training.optimizer import BF16Optimizer
+        from aspec_b200.training.sharded_optimizer import ShardedBF16Optimizer
+        torch.manual_seed(0)
+        make = lambda: torch.nn.Sequential(torch.nn.Linear(256, 512, bias=False), torch.nn.Linear(512, 128, bias=False)).to(dev, bf)
+        m_s, m_r = make(), make()
+        m_r.load_state_dict(m_s.state_dict())
+        opt_s = ShardedBF16Optimizer(m_s, lr=1e-2, weight_decay=0.01, max_grad_norm=0.5, total_steps=100)
+        opt_r = BF16Optimizer(m_r, lr=1e-2, weight_decay=0.01, max_grad_norm=0.5, total_steps=100)
+        for step in range(3):
+            for ps, pr in zip(m_s.parameters(), m_r.parameters()):
+                g = torch.Generator(device=dev).manual_seed(1000 * step + 10 * rank + ps.numel() % 7)
+                grad = torch.randn(ps.shape, device=dev, generator=g)
+                ps.main_grad.add_(grad)
+                pr.main_grad.add_(grad)
+            dist.all_reduce(opt_r.flat_grad)
+            n_s, n_r = opt_s.step(), opt_r.step()
+        res["fsdp_params"] = all(_close(a, b, 0, 1e-2) for a, b in zip(m_s.parameters(), m_r.parameters()))
+        res["fsdp_norm"] = _close(n_s, n_r, 1e-4, 1e-6)
+        res["fsdp_state_bytes"] = int(opt_s.shard_master.numel() * 12)
+        res["repl_state_bytes"] = int(opt_r.flat_master.numel() * 12)
+        opt_s.close()
+
+        # ---- vocabulary-parallel head ------------------------------------------------------------------------
+        from aspec_b200.ops.vocab_head import head_loss
+        from aspec_b200.parallel.vocab_parallel import VocabParallelHead, VocabShardWorkspace, vocab_parallel_head_loss
+        torch.manual_seed(1)
+        R, Tt, D, V, rk = 384, 128, 256, 8192, 32
+        hidden = (torch.randn(R, D, device=dev) * 0.5).to(bf)
+        W = (torch.randn(V, D, device=dev) * 0.05).to(bf)
+        W2 = torch.nn.Parameter((torch.randn(V, rk, device=dev) * 0.05).to(bf))
+        prev = (torch.randn(R, rk, device=dev) * 0.5).to(bf)
+        teacher = (torch.randn(Tt, D, device=dev) * 0.5).to(bf)
+        t_index = torch.randint(0, Tt, (R,), device=dev, dtype=torch.int32)
+        labels = torch.randint(0, V, (R,), device=dev)
+        weight = torch.rand(R, device=dev)
+        for t in (hidden, W, W2.data, prev, teacher, t_index, labels, weight):
+            dist.broadcast(t, 0)
+        h1, p1 = hidden.clone().requires_grad_(True), prev.clone().requires_grad_(True)
+        w2_ref = W2.detach().clone().requires_grad_(True)
+        num1, ce1, l11, _ = head_loss(h1, W, labels, weight, prev_emb=p1, markov_w2=w2_ref, teacher_hidden=teacher,
+                                      t_index=t_index, a_ce=0.1, a_l1=0.9)
+        num1.backward()
+        ws = exchange_workspaces(VocabShardWorkspace(R, Tt, D, rk, world, device=dev), VocabShardWorkspace.open)
+        head = VocabParallelHead(rank, world, V, ws, barrier)
+        h2, p2 = hidden.clone().requires_grad_(True), prev.clone().requires_grad_(True)
+        num2, ce2, l12, _ = vocab_parallel_head_loss(head, h2, head.shard_rows(W).contiguous(), labels, weight, prev_emb=p2,
+                                                     markov_w2=W2, teacher_hidden=teacher, t_index=t_index, a_ce=0.1, a_l1=0.9)
+        num2.backward()
+        gmax = h1.grad.float().abs().max().item()
+        res["vp_loss"] = _close(num2, num1, 2e-3, 1e-3) and _close(ce2, ce1, 2e-3, 2e-3) and _close(l12, l11, 2e-3, 2e-3)
+        res["vp_dhidden"] = _close(h2.grad, h1.grad, 5e-2, 4e-3 * gmax)
+        res["vp_dprev"] = _close(p2.grad, p1.grad, 5e-2, 4e-3 * p1.grad.float().abs().max().item())
+        sl = slice(head.offset, head.offset + head.shard)
+        res["vp_dw2"] = _close(W2.grad[sl], w2_ref.grad[sl], 5e-2, 4e-3 * w2_ref.grad.float().abs().max().item())
+
+        # ---- direct context-parallel attention ----------------------------------------------------------------
+        from aspec_b200.ops import attention_sm100 as K
+        from aspec_b200.ops.attention import build_block_intervals
+        from aspec_b200.parallel.context import context_shard_bounds
+        from aspec_b200.parallel.context_parallel import CPWorkspace, DirectCPAttention, direct_cp_attention, local_intervals
+        torch.manual_seed(2)
+        T, A, bs, H, Hk, d = 1024, 64, 4, 8, 2, 128
+        Q = A * bs
+        anchors = torch.sort(torch.randint(8, T - bs, (A,), device=dev)).values
+        q = (torch.randn(Q, H, d, device=dev) * 0.5).to(bf)
+        k = (torch.randn(T + Q, Hk, d, device=dev) * 0.5).to(bf)
+        v = (torch.randn(T + Q, Hk, d, device=dev) * 0.5).to(bf)
+        dout = (torch.randn(Q, H, d, device=dev) * 0.5).to(bf)
+        for t in (anchors, q, k, v, dout):
+            dist.broadcast(t, 0)
+        iv = build_block_intervals(anchors, torch.ones(A, dtype=torch.bool, device=dev), ctx_len=T, block_size=bs)
+        scale = d ** -0.5
+        o_ref, l_ref = K.forward(q, k, v, iv, scale)
+        dq_ref, dk_ref, dv_ref = K.backward(q, k, v, iv, o_ref, l_ref, dout, scale)
+        ql = Q // world
+        s, e = context_shard_bounds(T, rank, world, 1)
+        cws = exchange_workspaces(CPWorkspace(world, ql, H, d, device=dev), CPWorkspace.open)
+        cp = DirectCPAttention(rank, world, cws, barrier)
+        k_loc = torch.cat([k[s:e], k[T + rank * ql: T + (rank + 1) * ql]]).clone().requires_grad_(True)
+        v_loc = torch.cat([v[s:e], v[T + rank * ql: T + (rank + 1) * ql]]).clone().requires_grad_(True)
+        q_loc = q[rank * ql:(rank + 1) * ql].clone().requires_grad_(True)
+        tables = [local_intervals(iv[o * ql:(o + 1) * ql], s, e, T, own=(o == rank), query_start=rank * ql) for o in range(world)]
+        out, lse = direct_cp_attention(cp, q_loc, k_loc, v_loc, tables, [ql] * world, scale)
+        out.backward(dout[rank * ql:(rank + 1) * ql])
+        tol = dict(rtol=5e-2, atol=3e-2)
+        res["cp_out"] = _close(out, o_ref[rank * ql:(rank + 1) * ql], 2e-2, 2e-2)
+        res["cp_dq"] = _close(q_loc.grad, dq_ref[rank * ql:(rank + 1) * ql], **tol)
+        res["cp_dk"] = _close(k_loc.grad[: e - s], dk_ref[s:e], **tol) and _close(v_loc.grad[: e - s], dv_ref[s:e], **tol)
+
+        # ---- Ulysses projections ----------------------------------------------------------------------------------
+        from aspec_b200.parallel.ulysses import UlyssesExchange, UlyssesWorkspace, group_qkv_rows
+        torch.manual_seed(3)
+        T_loc, D2, hq, hk, d2 = 256, 512, 8, 2, 64
+        wq, wk, wv = [(torch.randn(n * d2, D2, device=dev) * 0.05).to(bf) for n in (hq, hk, hk)]
+        wo = (torch.randn(D2, hq * d2, device=dev) * 0.05).to(bf)
+        xs = [(torch.randn(T_loc, D2, device=dev) * 0.5).to(bf) for _ in range(world)]
+        for t in [wq, wk, wv, wo] + xs:
+            dist.broadcast(t, 0)
+        wg = group_qkv_rows(wq, wk, wv, world, d2)
+        qc, oc = (hq + 2 * hk) * d2 // world, hq * d2 // world
+        uws = exchange_workspaces(UlyssesWorkspace(world, T_loc, qc, oc, device=dev), UlyssesWorkspace.open)
+        ex = UlyssesExchange(rank, world, uws, barrier)
+        ex.project_scatter(xs[rank], wg)
+        barrier()
+        want = torch.cat(xs).float() @ wg[rank * qc:(rank + 1) * qc].float().T
+        res["ulysses_scatter"] = _close(ex.received_qkv(), want, 2e-2, 3e-2)
+        attn_all = [(torch.sin(torch.arange(world * T_loc * oc, device=dev).float() * (g + 1) * 0.37).view(world * T_loc, oc) * 0.5).to(bf)
+                    for g in range(world)]
+        ex.publish_attention(attn_all[rank])
+        barrier()
+        got = ex.output_projection(wo)
+        want = torch.cat(attn_all, 1).float()[rank * T_loc:(rank + 1) * T_loc] @ wo.float().T
+        res["ulysses_oproj"] = _close(got, want, 2e-2, 5e-2)
+        barrier()
+        torch.cuda.synchronize()
+    except Exception as exc:                                     # noqa: BLE001 - reported to the parent
+        import traceback
+        res["error"] = f"{type(exc).__name__}: {exc}\n{traceback.format_exc()[-1500:]}"
+    torch.save(res, f"{out_path}.{rank}")
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(900)
+def test_peer_memory_layers_on_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = str(tmp_path / "res")
+    mp.spawn(_worker, args=(2, 29700 + os.getpid() % 500, out), nprocs=2, join=True)
+    for rank in range(2):
+        res = torch.load(f"{out}.{rank}")
+        assert "error" not in res, res.get("error")
+        bad = [k for k, v in res.items() if isinstance(v, bool) and not v]
+        assert not bad, (rank, bad, res)
+        assert res["fsdp_state_bytes"] * 2 <= res["repl_state_bytes"] + 12 * 16

