@@ -46,6 +46,7 @@ class DatasetConfig:
     train_data_path: Optional[str] = ""
     # synthetic source (train_data_path: "synthetic")
     synthetic_num_documents: int = 4096
+    synthetic_vocab_size: Optional[int] = None      # default: the draft's vocabulary minus its reserved tail
     synthetic_min_length: int = 256
     synthetic_max_length: int = 4096
     synthetic_length_distribution: str = "log_uniform"

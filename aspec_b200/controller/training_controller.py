@@ -51,7 +51,7 @@ class TrainingController:
         if samples is None:
             path = a.get("train_data_path") or "synthetic"
             if path == "synthetic":
-                spec = SyntheticSpec(vocab_size=int(a.get("synthetic_vocab_size", 32000)),
+                spec = SyntheticSpec(vocab_size=int(a.get("synthetic_vocab_size") or 32000),
                                      min_len=int(a.get("synthetic_min_length", 256)),
                                      max_len=min(int(a.get("synthetic_max_length", 4096)), int(a["max_seq_length"])),
                                      length_distribution=a.get("synthetic_length_distribution", "log_uniform"),

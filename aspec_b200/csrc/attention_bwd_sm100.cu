@@ -232,6 +232,7 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       a0 = iv.x; a1 = iv.y; b0 = iv.z; b1 = iv.w;
       lse2 = p.lse[(size_t)head * p.q_total + pos] * kLog2e;
       delta = p.delta[(size_t)head * p.q_total + pos];
+      if (!(lse2 > -INFINITY)) lse2 = 0.f;      // a row without any visible key: every score is masked to -inf below
     }
     bool alive = true;
     for (int j = 0; j < n_tiles && alive; ++j) {
@@ -241,21 +242,35 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       tc_fence_after();
       const int k0 = tile_index(j) * BN;
       const uint32_t ds_addr = tmem + lane_base + 384 + (j & 1) * 64;
+      // visible columns of this tile for my row, tile-local: [la, ha) U [lb, hb); a tile that every row of the warp
+      // sees completely needs no per-element test
+      const int la = max(a0 - k0, 0), ha = min(a1 - k0, BN);
+      const int lb = max(b0 - k0, 0), hb = min(b1 - k0, BN);
+      const uint32_t wa = (row_ok && ha > la) ? static_cast<uint32_t>(ha - la) : 0u;
+      const uint32_t wb = (row_ok && hb > lb) ? static_cast<uint32_t>(hb - lb) : 0u;
+      const bool warp_full = __all_sync(0xffffffffu, wa == BN || wb == BN);
+      const float neg_lse = -lse2, neg_ds = -delta * p.scale;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t s[32], dp[32], pk[16];
         tmem_ld_32x32(tmem + lane_base + c, s);
         tmem_ld_32x32(tmem + lane_base + 128 + c, dp);
         tmem_ld_wait();
+        if (!warp_full) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t col = static_cast<uint32_t>(c + i);
+            const bool vis = (col - static_cast<uint32_t>(la) < wa) | (col - static_cast<uint32_t>(lb) < wb);
+            s[i] = vis ? s[i] : 0xff800000u;        // exp2(-inf) = 0 -> dS = 0
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float e[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int kk = k0 + c + i + u;
-            const bool vis = row_ok && visible(kk, a0, a1, b0, b1);
-            const float pr = vis ? fast_exp2(__uint_as_float(s[i + u]) * p.scale_log2 - lse2) : 0.f;
-            e[u] = pr * (__uint_as_float(dp[i + u]) - delta) * p.scale;
+            const float pr = fast_exp2(fmaf(__uint_as_float(s[i + u]), p.scale_log2, neg_lse));
+            e[u] = pr * fmaf(__uint_as_float(dp[i + u]), p.scale, neg_ds);
           }
           pk[i / 2] = pack_bf16x2(e[0], e[1]);
         }
@@ -334,6 +349,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* n_list = reinterpret_cast<int*>(tmem_slot + 2);
+  int* tile_cnt = reinterpret_cast<int*>(tmem_slot + 3);   // [2] running count of query rows that see the whole key tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.group, pm = BM / G;
@@ -342,6 +358,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
 
   if (threadIdx.x == 0) {
     *abort_word = 0;
+    tile_cnt[0] = tile_cnt[1] = 0;
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
     mbar_init(st_full, 1);
@@ -441,6 +458,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
     const int t = qd * 32 + lane;          // key row of the tile == TMEM lane
     const int kk = k0 + t;
     bool alive = true;
+    int prev_cnt[2] = {0, 0};
     for (int i = 0; i < n && alive; ++i) {
       // Row metadata of query tile i (thread t fetches query row t) into shared memory.
       uint8_t* mb = meta + (i & 1) * 128 * 24;
@@ -450,19 +468,32 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       {
         const int pos = list[i] * pm + t / G;
         const int head = kvh * G + t % G;
-        int4 iv = make_int4(0, 0, 0, 0);
+        // per query row: interval starts and widths for the unsigned-compare visibility test, -lse (log2) and
+        // -delta * scale; a query tile whose every row sees this whole key tile needs no per-element test
+        uint4 iv = make_uint4(0u, 0u, 0u, 0u);
         float l2 = 0.f, dl = 0.f;
+        bool covers = false;
         if (pos < p.q_total) {
-          iv = reinterpret_cast<const int4*>(p.intervals)[pos];
+          const int4 raw = reinterpret_cast<const int4*>(p.intervals)[pos];
+          iv = make_uint4((uint32_t)raw.x, raw.y > raw.x ? (uint32_t)(raw.y - raw.x) : 0u, (uint32_t)raw.z,
+                          raw.w > raw.z ? (uint32_t)(raw.w - raw.z) : 0u);
           l2 = p.lse[(size_t)head * p.q_total + pos] * kLog2e;
+          if (!(l2 > -INFINITY)) l2 = 0.f;
           dl = p.delta[(size_t)head * p.q_total + pos];
+          covers = (raw.x <= k0 && raw.y >= k0 + BN) || (raw.z <= k0 && raw.w >= k0 + BN);
         }
-        m_iv[t] = iv;
-        m_lse[t] = l2;
-        m_delta[t] = dl;
+        reinterpret_cast<uint4*>(m_iv)[t] = iv;
+        m_lse[t] = -l2;
+        m_delta[t] = -dl * p.scale;
+        if (covers) atomicAdd(&tile_cnt[i & 1], 1);
       }
       mbar_arrive(meta_bar);
       if (!mbar_wait(meta_bar, i & 1, abort_word)) { alive = false; break; }
+      // the counter only grows; it is next touched at tile i + 2, after every thread has passed the barrier of
+      // tile i + 1, hence after this read
+      const int seen = *reinterpret_cast<volatile int*>(&tile_cnt[i & 1]);
+      const bool all_full = (seen - prev_cnt[i & 1]) == 128;
+      prev_cnt[i & 1] = seen;
       if (!mbar_wait(st_full, i & 1, abort_word)) { alive = false; break; }
       tc_fence_after();
 #pragma unroll 1
@@ -471,20 +502,29 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         tmem_ld_32x32(tmem + lane_base + c, s);
         tmem_ld_32x32(tmem + lane_base + 128 + c, dp);
         tmem_ld_wait();
+        if (!all_full) {
 #pragma unroll
-        for (int r = 0; r < 32; r += 2) {
-          float pv[2], dsv[2];
+          for (int r = 0; r < 32; ++r) {
+            const uint4 iv = reinterpret_cast<const uint4*>(m_iv)[c + r];
+            const bool vis = ((uint32_t)kk - iv.x < iv.y) | ((uint32_t)kk - iv.z < iv.w);
+            s[r] = vis ? s[r] : 0xff800000u;
+          }
+        }
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int4 iv = m_iv[c + r + u];
-            const bool vis = visible(kk, iv.x, iv.y, iv.z, iv.w);
-            const float pr =
-                vis ? fast_exp2(__uint_as_float(s[r + u]) * p.scale_log2 - m_lse[c + r + u]) : 0.f;
-            pv[u] = pr;
-            dsv[u] = pr * (__uint_as_float(dp[r + u]) - m_delta[c + r + u]) * p.scale;
+        for (int r = 0; r < 32; r += 4) {
+          const float4 nl = *reinterpret_cast<const float4*>(m_lse + c + r);
+          const float4 nd = *reinterpret_cast<const float4*>(m_delta + c + r);
+          const float nls[4] = {nl.x, nl.y, nl.z, nl.w}, nds[4] = {nd.x, nd.y, nd.z, nd.w};
+          float pv[4], dsv[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            pv[u] = fast_exp2(fmaf(__uint_as_float(s[r + u]), p.scale_log2, nls[u]));
+            dsv[u] = pv[u] * fmaf(__uint_as_float(dp[r + u]), p.scale, nds[u]);
           }
           pp[r / 2] = pack_bf16x2(pv[0], pv[1]);
+          pp[r / 2 + 1] = pack_bf16x2(pv[2], pv[3]);
           ds[r / 2] = pack_bf16x2(dsv[0], dsv[1]);
+          ds[r / 2 + 1] = pack_bf16x2(dsv[2], dsv[3]);
         }
         // P^T over the S^T columns already consumed, dS^T over the dP^T columns already consumed
         asm volatile(

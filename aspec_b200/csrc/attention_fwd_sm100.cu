@@ -8,16 +8,20 @@
 // (row = position * G + head-in-group), so every K/V tile that is staged in
 // shared memory serves all of them.  Head dimension 128 (qk and v).
 //
-//   warp 0      TMA producer: Q once, then K/V tiles (2 stages)
+//   warp 0      TMA producer: Q once, then one K and one V buffer, refilled as soon
+//               as the MMA that read them has completed
 //   warp 1      tcgen05.mma issuer:  S = Q K^T  (128 x 128 x 128),  O += P V
-//   warps 2..5  softmax: tcgen05.ld S -> mask -> online softmax (exp2 domain)
-//               -> P as bf16 back into TMEM (A operand of the PV MMA), and the
-//               conditional rescale of the O accumulator, which stays in TMEM
+//   warps 2..5  softmax: one tcgen05.ld pass brings the row's 128 scores into
+//               registers; max, exp2 and the row sum run on them; P goes back as bf16
+//               into the first 64 columns of the S region (A operand of the PV MMA);
+//               O stays in TMEM and is rescaled lazily
 //
-// S_{j+1} is issued before P_j V_j so the softmax of tile j+1 overlaps the PV
-// MMA of tile j; P is double-buffered for the same reason.
+// Two CTAs are resident per SM (96 KB shared memory, 256 TMEM columns each): while one
+// CTA's softmax warps work, the other CTA's MMAs keep the tensor core busy, and two
+// warps per scheduler hide each other's dependent-issue latency.  Tiles that every row
+// of a warp sees completely take a path without any per-element masking.
 //
-// TMEM columns: S [0,128)  O [128,256)  P0 [256,320)  P1 [320,384)   (512 allocated)
+// TMEM columns: S / P [0,128)   O [128,256)
 // Every wait is bounded; a timeout sets status[0] and the CTA drains and exits.
 #include "common.cuh"
 
@@ -27,15 +31,15 @@ namespace attn {
 static constexpr int BM = 128;   // query rows per CTA (positions x heads-in-group)
 static constexpr int BN = 128;   // keys per tile
 static constexpr int HD = 128;   // head dim
-static constexpr int kStages = 2;
 static constexpr int kThreads = 192;
 static constexpr int kQBytes = BM * HD * 2;       // 32 KB (two 64-column swizzled chunks)
 static constexpr int kKVBytes = BN * HD * 2;      // 32 KB each for K and V
 static constexpr int kChunk = BM * 128;           // bytes of one 64-column chunk (128 rows x 128 B)
-static constexpr int kSmemBytes = kQBytes + kStages * 2 * kKVBytes + 1024 + 256;
-static constexpr uint32_t kColS = 0, kColO = 128, kColP = 256;
+static constexpr int kSmemBytes = kQBytes + 2 * kKVBytes + 1024 + 256;
+static constexpr uint32_t kColS = 0, kColO = 128, kTmemCols = 256;
 static constexpr float kLog2e = 1.4426950408889634f;
 static constexpr float kRescaleThreshold = 8.0f;  // log2 domain: lazy rescale when max grows > 2^8
+static constexpr uint32_t kNegInf = 0xff800000u;
 
 struct FwdParams {
   const int* intervals;   // [Qtot, 4]
@@ -49,20 +53,23 @@ struct alignas(64) FwdMaps {
   CUtensorMap q, k, v;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
-  uint8_t* sKV = smem + kQBytes;  // stage s: K at sKV + s*2*kKVBytes, V right after
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kStages * 2 * kKVBytes);
-  uint64_t* q_full = bars;            // 1
-  uint64_t* kv_full = bars + 1;       // kStages
-  uint64_t* kv_empty = bars + 3;      // kStages
-  uint64_t* s_full = bars + 5;        // 1
-  uint64_t* p_full = bars + 6;        // 1   (4 arrivals: one per softmax warp)
-  uint64_t* o_full = bars + 7;        // 1
+  uint8_t* sK = smem + kQBytes;
+  uint8_t* sV = sK + kKVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kKVBytes);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 2;
+  uint64_t* v_full = bars + 3;
+  uint64_t* v_empty = bars + 4;
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;        // 4 arrivals: one per softmax warp
+  uint64_t* o_full = bars + 7;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* range = reinterpret_cast<int*>(tmem_slot + 2);  // [4] c_lo, c_hi, b_lo, b_hi (tile units)
@@ -76,10 +83,10 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
   if (threadIdx.x == 0) {
     *abort_word = 0;
     mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
-    }
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
     mbar_init(p_full, 4);
     mbar_init(o_full, 1);
@@ -91,7 +98,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
     tma_prefetch_desc(&maps.v);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -139,55 +146,48 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
       tma_load_3d(sQ, &maps.q, q_full, 0, kvh * G, q0);
       tma_load_3d(sQ + kChunk, &maps.q, q_full, 64, kvh * G, q0);
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j % kStages;
-        const uint32_t ph = (j / kStages) & 1;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1u, abort_word)) break;
-        uint8_t* sK = sKV + st * 2 * kKVBytes;
-        uint8_t* sV = sK + kKVBytes;
+        const uint32_t ph = j & 1;
         const int k0 = tile_index(j) * BN;
-        mbar_arrive_expect_tx(&kv_full[st], 2 * kKVBytes);
-        tma_load_3d(sK, &maps.k, &kv_full[st], 0, kvh, k0);
-        tma_load_3d(sK + kChunk, &maps.k, &kv_full[st], 64, kvh, k0);
-        tma_load_3d(sV, &maps.v, &kv_full[st], 0, kvh, k0);
-        tma_load_3d(sV + kChunk, &maps.v, &kv_full[st], 64, kvh, k0);
+        if (!mbar_wait(k_empty, ph ^ 1u, abort_word)) break;        // S_{j-1} has read the K buffer
+        mbar_arrive_expect_tx(k_full, kKVBytes);
+        tma_load_3d(sK, &maps.k, k_full, 0, kvh, k0);
+        tma_load_3d(sK + kChunk, &maps.k, k_full, 64, kvh, k0);
+        if (!mbar_wait(v_empty, ph ^ 1u, abort_word)) break;        // P_{j-1} V_{j-1} has read the V buffer
+        mbar_arrive_expect_tx(v_full, kKVBytes);
+        tma_load_3d(sV, &maps.v, v_full, 0, kvh, k0);
+        tma_load_3d(sV + kChunk, &maps.v, v_full, 64, kvh, k0);
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(BM, BN, 0, 0);   // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = make_idesc_bf16(BM, HD, 0, 1);   // P (TMEM)   x V (MN-major)
-      const uint32_t q_addr = smem_u32(sQ);
-      auto issue_s = [&](int j) {
-        const uint32_t k_addr = smem_u32(sKV + (j % kStages) * 2 * kKVBytes);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      bool alive = mbar_wait(q_full, 0, abort_word);
+      for (int j = 0; j < n_tiles && alive; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(k_full, ph, abort_word)) break;
+        tc_fence_after();
+        // S_j overwrites the region P_{j-1} lives in: the tensor core executes in issue order, so it runs
+        // after P_{j-1} V_{j-1} has consumed P.
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * kChunk + (k & 3) * 32;
           tc_mma_ss(tmem + kColS, make_smem_desc(q_addr + off, 16, 1024),
                     make_smem_desc(k_addr + off, 16, 1024), idesc_s, k ? 1u : 0u);
         }
+        tc_commit(k_empty);
         tc_commit(s_full);
-      };
-      bool alive = mbar_wait(q_full, 0, abort_word) && mbar_wait(&kv_full[0], 0, abort_word);
-      if (alive) {
+        if (!mbar_wait(v_full, ph, abort_word)) break;
+        if (!mbar_wait(p_full, ph, abort_word)) break;
         tc_fence_after();
-        issue_s(0);
-      }
-      for (int j = 0; j < n_tiles && alive; ++j) {
-        if (j + 1 < n_tiles) {
-          if (!mbar_wait(&kv_full[(j + 1) % kStages], ((j + 1) / kStages) & 1, abort_word)) break;
-        }
-        if (!mbar_wait(p_full, j & 1, abort_word)) break;
-        tc_fence_after();
-        if (j + 1 < n_tiles) issue_s(j + 1);
-        const uint32_t v_addr = smem_u32(sKV + (j % kStages) * 2 * kKVBytes + kKVBytes);
-        const uint32_t p_col = tmem + kColP + (j & 1) * 64;
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
           // V is MN-major: 64-wide dv chunks are kChunk apart, 16 keys = 2048 B.
-          tc_mma_ts(tmem + kColO, p_col + k * 8, make_smem_desc(v_addr + k * 2048, kChunk, 1024),
+          tc_mma_ts(tmem + kColO, tmem + kColS + k * 8, make_smem_desc(v_addr + k * 2048, kChunk, 1024),
                     idesc_o, (j | k) ? 1u : 0u);
         }
-        tc_commit(&kv_empty[j % kStages]);
+        tc_commit(v_empty);
         tc_commit(o_full);
       }
     }
@@ -195,36 +195,56 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
     // ------------------------------------------------------- softmax --------
     const int q = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    const float sc = p.scale_log2;
     float m_used = -INFINITY, l_sum = 0.f;
     bool alive = true;
     for (int j = 0; j < n_tiles && alive; ++j) {
       if (!mbar_wait(s_full, j & 1, abort_word)) { alive = false; break; }
       tc_fence_after();
       const int k0 = tile_index(j) * BN;
-      // visibility class of this tile for my row
-      const int la = max(a0, k0), ha = min(a1, k0 + BN);
-      const int lb = max(b0, k0), hb = min(b1, k0 + BN);
+      // visible columns of this tile for my row, tile-local: [la, ha) U [lb, hb)
+      const int la = max(a0 - k0, 0), ha = min(a1 - k0, BN);
+      const int lb = max(b0 - k0, 0), hb = min(b1 - k0, BN);
       const bool none = (ha <= la) && (hb <= lb);
-      const bool full = (la == k0 && ha == k0 + BN) || (lb == k0 && hb == k0 + BN);
-      // pass 1: row max
-      float rmax = -INFINITY;
-      if (!__all_sync(0xffffffffu, none)) {
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem + lane_base + kColS + c, r);
-          tmem_ld_wait();
-          if (!none) {
+      const bool full = (la == 0 && ha == BN) || (lb == 0 && hb == BN);
+      const bool warp_full = __all_sync(0xffffffffu, full);
+      const bool warp_none = __all_sync(0xffffffffu, none);
+      const uint32_t wa = ha > la ? static_cast<uint32_t>(ha - la) : 0u;
+      const uint32_t wb = hb > lb ? static_cast<uint32_t>(hb - lb) : 0u;
+      // 64 score columns (two 32-column loads in flight) -> registers; masked unless the whole warp sees the tile
+      auto load_half = [&](int h, uint32_t (&r)[2][32]) {
+        tmem_ld_32x32(tmem + lane_base + kColS + h * 64, r[0]);
+        tmem_ld_32x32(tmem + lane_base + kColS + h * 64 + 32, r[1]);
+        tmem_ld_wait();
+        if (!warp_full) {
+          // branch-free visibility: column c is visible iff (c - la) <u (ha - la) or (c - lb) <u (hb - lb)
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const int kk = k0 + c + i;
-              const bool vis = full || (kk >= la && kk < ha) || (kk >= lb && kk < hb);
-              if (vis) rmax = fmaxf(rmax, __uint_as_float(r[i]));
+              const uint32_t col = static_cast<uint32_t>(h * 64 + c * 32 + i);
+              const bool vis = (col - static_cast<uint32_t>(la) < wa) | (col - static_cast<uint32_t>(lb) < wb);
+              r[c][i] = vis ? r[c][i] : kNegInf;
             }
+        }
+      };
+      // pass 1: row max, four independent chains
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (!warp_none) {
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[2][32];
+          load_half(h, r);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            mx[0] = fmaxf(mx[0], __uint_as_float(r[0][i]));
+            mx[1] = fmaxf(mx[1], __uint_as_float(r[0][i + 1]));
+            mx[2] = fmaxf(mx[2], __uint_as_float(r[1][i]));
+            mx[3] = fmaxf(mx[3], __uint_as_float(r[1][i + 1]));
           }
         }
       }
-      rmax *= p.scale_log2;   // scale > 0; -inf stays -inf
+      const float rmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;   // scale > 0; -inf stays -inf
       const float m_cand = fmaxf(m_used, rmax);
       const bool need = (m_cand > m_used) && (m_used == -INFINITY || m_cand - m_used > kRescaleThreshold);
       const float alpha = need ? (m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_cand)) : 1.f;
@@ -232,53 +252,44 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
         m_used = m_cand;
         l_sum *= alpha;
       }
-      // pass 2: P = exp2(s - m_used) -> TMEM (bf16 pairs), row sum
-      const uint32_t p_addr = tmem + lane_base + kColP + (j & 1) * 64;
-      float rsum = 0.f;
+      // s_full of tile j implies P_{j-1} V_{j-1} has completed: O may be rescaled now
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 64) {
-        uint32_t packed[32];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem + lane_base + kColS + c + h * 32, r);
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem + lane_base + kColO + c, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float e[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int kk = k0 + c + h * 32 + i + u;
-              const bool vis = !none && (full || (kk >= la && kk < ha) || (kk >= lb && kk < hb));
-              e[u] = vis ? fast_exp2(__uint_as_float(r[i + u]) * p.scale_log2 - m_used) : 0.f;
-            }
-            // sum what the MMA will see (bf16-rounded) so the normaliser matches the numerator
-            const uint32_t pk = pack_bf16x2(e[0], e[1]);
-            const __nv_bfloat162 pb = *reinterpret_cast<const __nv_bfloat162*>(&pk);
-            rsum += __low2float(pb) + __high2float(pb);
-            packed[h * 16 + i / 2] = pk;
-          }
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(tmem + lane_base + kColO + c, o);
         }
-        // O must not be rescaled, and P_j not overwritten... P buffer j&1 was last read by PV_{j-2},
-        // which completed before o_full of tile j-1 was observed in the previous iteration.
-        tmem_st_32x32(p_addr + c / 2, packed);
       }
-      l_sum += rsum;
-      if (j > 0) {
-        if (!mbar_wait(o_full, (j - 1) & 1, abort_word)) { alive = false; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, need)) {
+      // pass 2: P = exp2(s * scale - m) as bf16 pairs over the score columns already consumed
+      // (64 scores -> 32 words: half h goes to columns [32 h, 32 h + 32) of the S region)
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;   // a row that has seen no key yet: exp2(-inf) = 0
+      float sm[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-          for (int c = 0; c < HD; c += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32(tmem + lane_base + kColO + c, r);
-            tmem_ld_wait();
+      for (int h = 0; h < 2; ++h) {
+        uint32_t packed[32];
+        if (!warp_none) {
+          uint32_t r[2][32];
+          load_half(h, r);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tmem + lane_base + kColO + c, r);
-          }
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float e0 = fast_exp2(fmaf(__uint_as_float(r[c][i]), sc, neg_m));
+              const float e1 = fast_exp2(fmaf(__uint_as_float(r[c][i + 1]), sc, neg_m));
+              sm[c * 2 + ((i >> 1) & 1)] += e0 + e1;
+              packed[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
+            }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) packed[i] = 0u;
         }
+        tmem_st_32x32(tmem + lane_base + kColS + h * 32, packed);
       }
+      l_sum += (sm[0] + sm[1]) + (sm[2] + sm[3]);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -295,24 +306,24 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
       __nv_bfloat16* orow = p.out + ((size_t)(row_ok ? my_pos : 0) * p.hq + head) * HD;
 #pragma unroll 1
       for (int c = 0; c < HD; c += 32) {
-        uint32_t r[32];
+        uint32_t o[32];
         if (n_tiles > 0) {
-          tmem_ld_32x32(tmem + lane_base + kColO + c, r);
+          tmem_ld_32x32(tmem + lane_base + kColO + c, o);
           tmem_ld_wait();
         }
         if (row_ok) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            uint4 o;
+            uint4 w;
             if (n_tiles > 0 && l_sum > 0.f) {
-              o.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * inv, __uint_as_float(r[8 * i + 1]) * inv);
-              o.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * inv, __uint_as_float(r[8 * i + 3]) * inv);
-              o.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * inv, __uint_as_float(r[8 * i + 5]) * inv);
-              o.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * inv, __uint_as_float(r[8 * i + 7]) * inv);
+              w.x = pack_bf16x2(__uint_as_float(o[8 * i + 0]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+              w.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+              w.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+              w.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
             } else {
-              o = make_uint4(0, 0, 0, 0);
+              w = make_uint4(0, 0, 0, 0);
             }
-            reinterpret_cast<uint4*>(orow + c)[i] = o;
+            reinterpret_cast<uint4*>(orow + c)[i] = w;
           }
         }
       }
@@ -330,7 +341,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, kTmemCols);
   }
 }
 

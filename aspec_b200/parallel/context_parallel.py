@@ -130,11 +130,27 @@ class DirectCPAttention:
             if n == 0:
                 continue
             q, out, dout, lse = self._views(self.ws[o], n)
+            if o != self.rank:
+                # the dK/dV kernel re-reads the query-side tiles once per key tile: fetch the peer's rows into local
+                # memory once (peer memory is not cached in this GPU's L2) and run the kernels on the copies
+                q, out, dout, lse = (self._fetch(t) for t in (q, out, dout, lse))
             _dq, dk_o, dv_o = K.backward(q, k_local, v_local, tables[o], out, lse, dout, scale,
                                          dq=self.ws[o].part_dq[self.rank, :n])
             dk += dk_o
             dv += dv_o
         return dk.to(k_local.dtype), dv.to(v_local.dtype)
+
+    @staticmethod
+    def _fetch(peer: torch.Tensor) -> torch.Tensor:
+        import ctypes as C
+        from aspec_b200 import _native
+        local = torch.empty(peer.shape, dtype=peer.dtype, device=peer.device)
+        nbytes = peer.numel() * peer.element_size()
+        rc = _native.kernels().ab_copy_bytes(C.c_void_p(peer.data_ptr()), C.c_void_p(local.data_ptr()), C.c_longlong(nbytes),
+                                             C.c_void_p(torch.cuda.current_stream(peer.device).cuda_stream))
+        if rc != 0:                       # sizes that are not multiples of 16 bytes take the generic copy
+            local.copy_(peer)
+        return local
 
     def reduce_grad(self) -> torch.Tensor:
         from aspec_b200.ops import comm
