@@ -27,7 +27,7 @@ int make_map_rows_heads(CUtensorMap* map, const void* base, long long rows, int 
 static constexpr int BM = 128;
 static constexpr int BN = 128;
 static constexpr int HD = 128;
-static constexpr int kThreads = 192;
+static constexpr int kThreads = 320;   // TMA warp, MMA warp, two warpgroups that split every score tile by columns
 static constexpr int kTile = 128 * HD * 2;   // 32 KB: one 128 x 128 bf16 tile (two swizzled chunks)
 static constexpr int kChunk = 128 * 128;     // bytes per 64-column chunk
 static constexpr float kLog2e = 1.4426950408889634f;
@@ -135,7 +135,7 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(sp_full, 1);
-    mbar_init(ds_full, 4);
+    mbar_init(ds_full, 8);
     mbar_init(&dq_done[0], 1);
     mbar_init(&dq_done[1], 1);
     fence_barrier_init();
@@ -219,7 +219,10 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       }
     }
   } else {
+    // warps 2..9: TMEM lane quadrant warp % 4 (two warps per quadrant); the first four take score columns
+    // [0, 64), the other four [64, 128) - no row reduction is needed in the backward pass
     const int qd = warp & 3;
+    const int cbeg = ((warp - 2) >> 2) * 64;
     const uint32_t lane_base = static_cast<uint32_t>(qd * 32) << 16;
     const int t = qd * 32 + lane;
     const int pos = q0 + t / G;
@@ -251,7 +254,7 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       const bool warp_full = __all_sync(0xffffffffu, wa == BN || wb == BN);
       const float neg_lse = -lse2, neg_ds = -delta * p.scale;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = cbeg; c < cbeg + 64; c += 32) {
         uint32_t s[32], dp[32], pk[16];
         tmem_ld_32x32(tmem + lane_base + c, s);
         tmem_ld_32x32(tmem + lane_base + 128 + c, dp);
@@ -294,7 +297,7 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       tc_fence_after();
       __nv_bfloat16* row = p.dq + ((size_t)(row_ok ? pos : 0) * p.hq + head) * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
+      for (int c = cbeg; c < cbeg + 64; c += 32) {
         uint32_t r[32];
         if (n_tiles > 0) { tmem_ld_32x32(tmem + lane_base + 256 + c, r); tmem_ld_wait(); }
         if (row_ok) {
@@ -362,7 +365,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
     mbar_init(st_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(acc_done, 1);
     mbar_init(meta_bar, 128);
     fence_barrier_init();
@@ -441,19 +444,25 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         if (!mbar_wait(pds_full, i & 1, abort_word)) break;
         tc_fence_after();
 #pragma unroll
+        // Each warpgroup wrote its 64 query columns as 32 packed columns over scores IT had consumed:
+        // query columns [0, 64) live at packed columns [0, 32), query columns [64, 128) at [64, 96).
         for (int k = 0; k < BM / 16; ++k)   // reduction over the 128 query rows of the tile
-          tc_mma_ts(tmem + 256, tmem + 0 + k * 8, make_smem_desc(do_addr + k * 2048, kChunk, 1024),
+          tc_mma_ts(tmem + 256, tmem + 0 + (k >> 2) * 64 + (k & 3) * 8, make_smem_desc(do_addr + k * 2048, kChunk, 1024),
                     idesc_acc, (i | k) ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < BM / 16; ++k)
-          tc_mma_ts(tmem + 384, tmem + 128 + k * 8, make_smem_desc(q_addr + k * 2048, kChunk, 1024),
+          tc_mma_ts(tmem + 384, tmem + 128 + (k >> 2) * 64 + (k & 3) * 8, make_smem_desc(q_addr + k * 2048, kChunk, 1024),
                     idesc_acc, (i | k) ? 1u : 0u);
         tc_commit(&qdo_empty[st]);
         tc_commit(acc_done);
       }
     }
   } else {
+    // warps 2..9: TMEM lane quadrant warp % 4; the first four take query columns [0, 64) of every tile and stage
+    // the tile's row metadata, the other four take columns [64, 128)
     const int qd = warp & 3;
+    const int wg = (warp - 2) >> 2;
+    const int cbeg = wg * 64;
     const uint32_t lane_base = static_cast<uint32_t>(qd * 32) << 16;
     const int t = qd * 32 + lane;          // key row of the tile == TMEM lane
     const int kk = k0 + t;
@@ -465,7 +474,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       int4* m_iv = reinterpret_cast<int4*>(mb);
       float* m_lse = reinterpret_cast<float*>(mb + 128 * 16);
       float* m_delta = m_lse + 128;
-      {
+      if (wg == 0) {
         const int pos = list[i] * pm + t / G;
         const int head = kvh * G + t % G;
         // per query row: interval starts and widths for the unsigned-compare visibility test, -lse (log2) and
@@ -486,8 +495,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         m_lse[t] = -l2;
         m_delta[t] = -dl * p.scale;
         if (covers) atomicAdd(&tile_cnt[i & 1], 1);
+        mbar_arrive(meta_bar);
       }
-      mbar_arrive(meta_bar);
       if (!mbar_wait(meta_bar, i & 1, abort_word)) { alive = false; break; }
       // the counter only grows; it is next touched at tile i + 2, after every thread has passed the barrier of
       // tile i + 1, hence after this read
@@ -497,7 +506,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       if (!mbar_wait(st_full, i & 1, abort_word)) { alive = false; break; }
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < BM; c += 32) {
+      for (int c = cbeg; c < cbeg + 64; c += 32) {
         uint32_t s[32], dp[32], pp[16], ds[16];
         tmem_ld_32x32(tmem + lane_base + c, s);
         tmem_ld_32x32(tmem + lane_base + 128 + c, dp);
@@ -530,14 +539,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         asm volatile(
             "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
             "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-            ::"r"(tmem + lane_base + c / 2), "r"(pp[0]), "r"(pp[1]), "r"(pp[2]), "r"(pp[3]), "r"(pp[4]),
+            ::"r"(tmem + lane_base + cbeg + (c - cbeg) / 2), "r"(pp[0]), "r"(pp[1]), "r"(pp[2]), "r"(pp[3]), "r"(pp[4]),
             "r"(pp[5]), "r"(pp[6]), "r"(pp[7]), "r"(pp[8]), "r"(pp[9]), "r"(pp[10]), "r"(pp[11]),
             "r"(pp[12]), "r"(pp[13]), "r"(pp[14]), "r"(pp[15])
             : "memory");
         asm volatile(
             "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
             "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-            ::"r"(tmem + lane_base + 128 + c / 2), "r"(ds[0]), "r"(ds[1]), "r"(ds[2]), "r"(ds[3]),
+            ::"r"(tmem + lane_base + 128 + cbeg + (c - cbeg) / 2), "r"(ds[0]), "r"(ds[1]), "r"(ds[2]), "r"(ds[3]),
             "r"(ds[4]), "r"(ds[5]), "r"(ds[6]), "r"(ds[7]), "r"(ds[8]), "r"(ds[9]), "r"(ds[10]),
             "r"(ds[11]), "r"(ds[12]), "r"(ds[13]), "r"(ds[14]), "r"(ds[15])
             : "memory");
@@ -558,7 +567,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         __nv_bfloat16* row = half ? dkrow : dvrow;
         const uint32_t col0 = half ? 384 : 256;
 #pragma unroll 1
-        for (int c = 0; c < HD; c += 32) {
+        for (int c = cbeg; c < cbeg + 64; c += 32) {
           uint32_t r[32];
           if (n > 0) { tmem_ld_32x32(tmem + lane_base + col0 + c, r); tmem_ld_wait(); }
           if (row_ok) {
