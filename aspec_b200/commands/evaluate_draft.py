@@ -1,0 +1,105 @@
+"""``evaluate``: acceptance statistics of an exported Draft on held-out documents, without a serving engine.
+
+For every document a set of evaluation anchors is drawn deterministically; at each anchor the Draft proposes one
+block through ``BlockDraftConsumer`` exactly as a speculative decoder would, and the proposal is verified greedily
+against the document's own continuation (the tokens a Target that generated the document would accept).  Reports
+per-position acceptance, the mean accepted length tau and the share of fully accepted blocks
+(reference: aspec/commands/evaluate_draft.py, which drives a serving engine's decode loop for the same statistics).
+Target features come from the in-framework Target (random-init unless weights are given) or an offline feature
+dataset (``--features``)."""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+
+def evaluate(consumer, lm_head, documents, features_of, *, anchors_per_doc: int = 16, seed: int = 0) -> dict:
+    import torch
+    bs = consumer.block_size
+    accepted_at = torch.zeros(bs - 1)
+    proposals = 0
+    lengths = []
+    g = torch.Generator().manual_seed(seed)
+    for doc in documents:
+        ids = doc["input_ids"].reshape(1, -1)
+        T = ids.shape[1]
+        if T < bs + 2:
+            continue
+        feats = features_of(doc)
+        picks = torch.randperm(T - bs - 1, generator=g)[:anchors_per_doc] + 1
+        for a in picks.tolist():
+            out = consumer.propose(ids[:, : a + 1].to(feats.device), feats[:, : a + 1], lm_head_weight=lm_head)
+            prop = out["token_ids"].reshape(-1)[: bs - 1].cpu()
+            truth = ids[0, a + 1: a + bs]
+            ok = (prop[: truth.numel()] == truth).long().cumprod(0)
+            accepted_at[: ok.numel()] += ok.float()
+            lengths.append(int(ok.sum()))
+            proposals += 1
+    if not proposals:
+        return {"proposals": 0}
+    rate = (accepted_at / proposals).tolist()
+    return {"proposals": proposals, "accept_rate_at": rate, "tau": 1.0 + sum(lengths) / proposals,
+            "mean_accepted_draft_tokens": sum(lengths) / proposals,
+            "fully_accepted_share": sum(1 for n in lengths if n == bs - 1) / proposals}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="aspec-b200 evaluate", description=__doc__)
+    ap.add_argument("--asset-dir", required=True, help="directory written by `aspec-b200 export --format aspec`")
+    ap.add_argument("--data", required=True, help="held-out conversations or pre-tokenised .jsonl")
+    ap.add_argument("--features", help="offline feature dataset directory (else the in-framework Target computes them)")
+    ap.add_argument("--target-weights")
+    ap.add_argument("--tokenizer")
+    ap.add_argument("--chat-template", default="qwen")
+    ap.add_argument("--max-seq-length", type=int, default=4096)
+    ap.add_argument("--block-size", type=int, default=7)
+    ap.add_argument("--anchors-per-doc", type=int, default=16)
+    ap.add_argument("--max-docs", type=int, default=256)
+    ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--output")
+    a = ap.parse_args(argv)
+    import torch
+    from aspec_b200.data.dataset import load_training_samples
+    from aspec_b200.draft_artifact import BlockDraftConsumer, load_native_draft
+    dev = torch.device(a.device if torch.cuda.is_available() else "cpu")
+    dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    draft, manifest = load_native_draft(a.asset_dir, device=dev, dtype=dtype)
+    consumer = BlockDraftConsumer(draft, block_size=a.block_size)
+    cfg = draft.config
+    docs = load_training_samples(a.data, {"tokenizer_path": a.tokenizer, "chat_template": a.chat_template,
+                                          "max_seq_length": a.max_seq_length})[: a.max_docs]
+    if a.features:
+        from aspec_b200.offline.dataset import OfflineFeatureStore
+        store = OfflineFeatureStore(a.features)
+        lm_head = torch.load(f"{a.features}/lm_head.pt", map_location=dev).to(dtype) if False else None
+        features_of = lambda d: store.load(d["data_id"])["hidden_states"][None].to(dev, dtype)
+    else:
+        from aspec_b200.inference.factory import target_config_from_args
+        from aspec_b200.models.target.dense import DenseTarget, TargetConfig
+        tcfg = target_config_from_args({"target_model_config": None}, cfg.to_dict())
+        torch.set_default_dtype(dtype)
+        with torch.device(dev):
+            target = DenseTarget(TargetConfig(**tcfg))
+        torch.set_default_dtype(torch.float32)
+        if a.target_weights:
+            target.load_state_dict(torch.load(a.target_weights, map_location=dev), strict=True)
+        else:
+            target.init_random(0)
+        target.eval()
+        layers = list(cfg.target_layer_ids or draft.target_layer_ids)
+        lm_head = target.lm_head.detach()
+        features_of = lambda d: target.prefill(d["input_ids"].reshape(-1).to(dev), [int(d["input_ids"].numel())], layers)["hidden_states"][None]
+    if lm_head is None:
+        raise ValueError("an offline feature dataset does not carry the Target output head; pass --target-weights instead")
+    res = evaluate(consumer, lm_head, docs, features_of, anchors_per_doc=a.anchors_per_doc)
+    res.update(asset=a.asset_dir, algorithm=manifest.get("algorithm"), documents=len(docs), block_size=a.block_size)
+    text = json.dumps(res, indent=2)
+    if a.output:
+        open(a.output, "w").write(text + "\n")
+    print(text)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -152,6 +152,35 @@ class TrainerActor:
         metrics["perf/step_time"] = time.perf_counter() - t0
         return {"metrics": metrics, "committed": consumed, "releases": releases, "step": step}
 
+    # -- evaluation -------------------------------------------------------------------------------
+    def eval_from_queue(self, num_batches: int, cache_key: str = "", timeout: float = 1800.0) -> dict:
+        """Held-out pass over ``num_batches`` ring samples.  With ``cache_key`` the batches are kept in host memory
+        under that identity, so later passes (``eval_from_cache``) need no Target."""
+        keys, kept = [], []
+
+        def batches():
+            for sample in self._samples(num_batches, timeout):
+                b = self._batch(sample)
+                keys.append(sample.feature_key)
+                if cache_key:
+                    kept.append({k: (v.detach().to("cpu", copy=True) if torch.is_tensor(v) else v) for k, v in b.items()})
+                yield b
+
+        metrics = self.trainer.eval_update(batches())
+        if cache_key:
+            self._eval_cache = {"key": cache_key, "batches": kept}
+        releases = []
+        for k in keys:
+            d = FeatureDescriptor.from_key(k)
+            releases.append((d.consumer, d.slot, d.generation))
+        return {"metrics": metrics, "releases": releases, "cached": len(kept)}
+
+    def eval_from_cache(self, cache_key: str) -> dict:
+        cache = getattr(self, "_eval_cache", None)
+        if not cache or cache["key"] != cache_key:
+            return {"metrics": {}, "miss": True}
+        return {"metrics": self.trainer.eval_update(iter(cache["batches"])), "miss": False}
+
     # -- checkpoints --------------------------------------------------------------------------------
     def topology(self) -> dict:
         return ckpt.logical_training_topology({**self.args, "world_size": self.world}, self.draft_config)
