@@ -38,3 +38,13 @@ def swiglu(gu: torch.Tensor, clamp: float = 0.0) -> torch.Tensor:
         out = _SwiGLUFn.apply(gu.reshape(-1, gu.shape[-1]).contiguous(), float(clamp))
         return out.view(*lead, gu.shape[-1] // 2)
     return swiglu_reference(gu, clamp)
+
+
+def swiglu_backward(gu: torch.Tensor, dact: torch.Tensor, clamp: float = 0.0) -> torch.Tensor:
+    """``d gu [..., 2I]`` from ``d act [..., I]`` (explicit backward for code that manages its own graph)."""
+    if gu.is_cuda and gu.dtype == torch.bfloat16 and gu.shape[-1] % 16 == 0 and gu.numel():
+        from aspec_b200.ops import elementwise_sm100 as E
+        return E.swiglu_bwd(gu.reshape(-1, gu.shape[-1]).contiguous(), dact.reshape(-1, dact.shape[-1]).contiguous(), float(clamp)).view(gu.shape)
+    g = gu.detach().clone().requires_grad_(True)
+    swiglu_reference(g, clamp).backward(dact.to(gu.dtype))
+    return g.grad

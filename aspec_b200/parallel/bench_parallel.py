@@ -257,12 +257,47 @@ def case_ulysses(rank, world, dev, timer, barrier):
             "flops_per_rank": flops, "nvlink_bytes_per_rank": nv, "roofline_ms": floor, "achieved_over_roofline": floor / t_f}
 
 
-CASES = {"fsdp": case_fsdp, "vocab": case_vocab, "cp": case_cp, "ulysses": case_ulysses}
+def case_moe(rank, world, dev, timer, barrier):
+    from aspec_b200.models.draft.moe import ExpertBank
+    from aspec_b200.parallel.expert_parallel import (EPWorkspace, FusedExpertParallel, dispatch_combine, exchange_counts,
+                                                     fused_dispatch_combine)
+    from aspec_b200.parallel.group import exchange_workspaces
+    bf = torch.bfloat16
+    E, D, I, N, k = 64, 2048, 1024, 3584, 4               # Ling-flash-like block: 3584 supervised rows, top-4 of 64
+    bank = ExpertBank(E, D, I, ep_rank=rank, ep_size=world).to(dev, bf)
+    torch.manual_seed(rank)
+    x = (torch.randn(N, D, device=dev) * 0.5).to(bf)
+    sel = torch.randint(0, E, (N * k,), device=dev)
+    order = torch.argsort(sel, stable=True)
+    xs = x.repeat_interleave(k, 0)[order].contiguous()
+    se = sel[order]
+    dy = (torch.randn(N * k, D, device=dev) * 0.1).to(bf)
+    ws = exchange_workspaces(EPWorkspace(N * k, D, device=dev), EPWorkspace.open)
+    ep = FusedExpertParallel(rank, world, E, ws, barrier)
+
+    def fused():
+        a = xs.clone().requires_grad_(True)
+        fused_dispatch_combine(ep, bank, a, se).backward(dy)
+
+    def library():
+        a = xs.clone().requires_grad_(True)
+        dispatch_combine(bank, a, se).backward(dy)
+
+    t_f, t_l = timer(fused), timer(library)
+    rows_remote = N * k * (world - 1) / world
+    flops = 3 * 2.0 * N * k * D * 3 * I                     # fwd + dgrad + wgrad of the two GEMMs (gate/up is 2I wide)
+    nv = rows_remote * D * 2 * 4                            # x, y, dy, dx rows that belong to remote experts
+    floor = max(flops / (_peak() * 1e9), nv / (NVLINK_GBS * 1e6))
+    return {"case": "moe_expert_parallel_fwd_bwd", "rows": N * k, "experts": E, "fused_ms": t_f, "nccl_all_to_all_ms": t_l,
+            "flops_per_rank": flops, "nvlink_bytes_per_rank": nv, "roofline_ms": floor, "achieved_over_roofline": floor / t_f}
+
+
+CASES = {"moe": case_moe, "fsdp": case_fsdp, "vocab": case_vocab, "cp": case_cp, "ulysses": case_ulysses}
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--cases", default="fsdp,vocab,cp,ulysses")
+    ap.add_argument("--cases", default="fsdp,vocab,cp,ulysses,moe")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))

@@ -45,3 +45,147 @@ def dispatch_combine(bank, x_sorted: torch.Tensor, sorted_expert: torch.Tensor, 
     back = torch.empty_like(y)
     back[order] = y
     return _AllToAll.apply(back, send_splits, recv_splits, group)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Fused dispatch / combine over peer memory
+# ---------------------------------------------------------------------------------------------------------------
+class EPWorkspace:
+    """Peer-visible buffers of one rank: its expert-sorted tokens (``x``), the rows returned by the experts (``y``) and
+    the same pair for the backward pass (``dy`` sent to the experts, ``dx`` returned)."""
+
+    def __init__(self, max_rows: int, hidden: int, device=None, buffer=None):
+        from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
+        self.max_rows, self.hidden = max_rows, hidden
+        n = max_rows * hidden * 2
+        n = -(-n // 256) * 256
+        self.buffer = buffer if buffer is not None else SymmetricBuffer.allocate(4 * n, device)
+        raw = self.buffer.tensor
+        view = lambda i: raw[i * n: i * n + max_rows * hidden * 2].view(torch.bfloat16).view(max_rows, hidden)
+        self.x, self.y, self.dy, self.dx = view(0), view(1), view(2), view(3)
+
+    def export(self) -> dict:
+        return {"memory": self.buffer.export(), "max_rows": self.max_rows, "hidden": self.hidden}
+
+    @classmethod
+    def open(cls, meta: dict) -> "EPWorkspace":
+        from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
+        return cls(meta["max_rows"], meta["hidden"], buffer=SymmetricBuffer.open(meta["memory"]))
+
+
+class FusedExpertParallel:
+    """Expert-parallel MoE whose all-to-alls are the expert GEMMs' own memory traffic.
+
+    Every rank sorts its routed tokens by global expert into its peer-visible ``x``.  The owner of expert ``e`` then
+    runs, per source rank ``s``, the gate/up GEMM with its A operand read by TMA straight from ``x_s`` (the dispatch)
+    and the down GEMM with its output stored straight into ``y_s`` (the combine): no staging copy, no collective,
+    and the transfer overlaps the math tile by tile inside the GEMM pipelines.  Only the ``[ranks, experts]`` count
+    matrix is exchanged beforehand (the same host-side split sizes the all-to-all baseline needs).
+    The backward pass mirrors it: ``dy`` rows are pulled from the source, ``dx`` rows are pushed back, weight gradients
+    stay local.  Phases are separate methods so several ranks can be emulated in one process.
+    """
+
+    def __init__(self, rank: int, world: int, num_experts: int, workspaces, barrier=None):
+        if num_experts % world:
+            raise ValueError("num_experts must be divisible by the expert-parallel size")
+        self.rank, self.world, self.E = rank, world, num_experts
+        self.local = num_experts // world
+        self.ws = list(workspaces)
+        self.mine = self.ws[rank]
+        self.barrier = barrier or (lambda: None)
+
+    # -- forward ------------------------------------------------------------------------------------------
+    def publish(self, x_sorted: torch.Tensor) -> None:
+        self._n = x_sorted.shape[0]
+        self.mine.x[: self._n].copy_(x_sorted)
+
+    def run_experts(self, count_matrix, gate_up: torch.Tensor, down: torch.Tensor, clamp: float = 0.0) -> None:
+        """``count_matrix[s][e]``: rows rank ``s`` routed to global expert ``e`` (host ints).  ``gate_up [E_local, 2I, D]``,
+        ``down [E_local, D, I]``.  Keeps the activations needed by the backward pass."""
+        from aspec_b200.ops import gemm as G
+        from aspec_b200.ops.activation import swiglu
+        self._counts = [list(map(int, row)) for row in count_matrix]
+        self._saved = []
+        for s in range(self.world):
+            offs = [0]
+            for c in self._counts[s]:
+                offs.append(offs[-1] + c)
+            for le in range(self.local):
+                e = self.rank * self.local + le
+                n, o = self._counts[s][e], offs[e]
+                if n == 0:
+                    continue
+                xs = self.ws[s].x[o:o + n]                               # peer rows: the GEMM's TMA loads are the dispatch
+                gu = G.gemm(xs, gate_up[le])
+                act = swiglu(gu.detach(), clamp)
+                G.gemm(act, down[le], out=self.ws[s].y[o:o + n])       # epilogue stores are the combine
+                self._saved.append((s, le, o, n, gu, act))
+
+    def collect(self) -> torch.Tensor:
+        return self.mine.y[: self._n]
+
+    # -- backward -----------------------------------------------------------------------------------------
+    def publish_grad(self, dy_sorted: torch.Tensor) -> None:
+        self.mine.dy[: self._n].copy_(dy_sorted)
+
+    def run_experts_backward(self, gate_up: torch.Tensor, down: torch.Tensor, clamp: float = 0.0):
+        """Returns ``(d gate_up, d down)`` of the local experts (fp32); pushes ``dx`` rows back to their sources."""
+        from aspec_b200.ops import gemm as G
+        from aspec_b200.ops.activation import swiglu_backward
+        d_gu = torch.zeros(gate_up.shape, dtype=torch.float32, device=gate_up.device)
+        d_dn = torch.zeros(down.shape, dtype=torch.float32, device=down.device)
+        for s, le, o, n, gu, act in self._saved:
+            dys = self.ws[s].dy[o:o + n]                                 # pulled from the source rank
+            d_act = G.gemm(dys, down[le], b_t=True)                      # [n, I]
+            G.gemm(dys, act, a_t=True, b_t=True, out=d_dn[le], addend=d_dn[le], out_dtype=torch.float32)
+            d_gu_rows = swiglu_backward(gu, d_act, clamp)                # [n, 2I]
+            xs = self.ws[s].x[o:o + n]
+            G.gemm(d_gu_rows, xs, a_t=True, b_t=True, out=d_gu[le], addend=d_gu[le], out_dtype=torch.float32)
+            G.gemm(d_gu_rows, gate_up[le], b_t=True, out=self.ws[s].dx[o:o + n])   # pushed back to the source
+        self._saved = []
+        return d_gu, d_dn
+
+    def collect_grad(self) -> torch.Tensor:
+        return self.mine.dx[: self._n]
+
+
+class _FusedEPFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ep: FusedExpertParallel, x_sorted, gate_up, down, count_matrix, clamp):
+        ep.publish(x_sorted)
+        ep.barrier()
+        ep.run_experts(count_matrix, gate_up, down, clamp)
+        ep.barrier()
+        y = ep.collect().clone()
+        ctx.ep, ctx.clamp = ep, clamp
+        ctx.save_for_backward(gate_up, down)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        ep = ctx.ep
+        gate_up, down = ctx.saved_tensors
+        ep.publish_grad(dy.contiguous())
+        ep.barrier()
+        d_gu, d_dn = ep.run_experts_backward(gate_up, down, ctx.clamp)
+        ep.barrier()
+        dx = ep.collect_grad().clone()
+        ep.barrier()                      # the next layer may overwrite x / dy only after every expert owner has read them
+        return None, dx, d_gu.to(gate_up.dtype), d_dn.to(down.dtype), None, None
+
+
+def exchange_counts(sorted_expert: torch.Tensor, num_experts: int, group=None):
+    """``[ranks][experts]`` routed-row counts of every rank (one small all-gather and one host read)."""
+    counts = torch.bincount(sorted_expert, minlength=num_experts)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return [counts.tolist()]
+    allc = [torch.empty_like(counts) for _ in range(world)]
+    dist.all_gather(allc, counts, group=group)
+    return torch.stack(allc).tolist()
+
+
+def fused_dispatch_combine(ep: FusedExpertParallel, bank, x_sorted: torch.Tensor, sorted_expert: torch.Tensor, group=None):
+    """Drop-in for ``dispatch_combine`` on CUDA bf16: same inputs, the expert bank's stacked weights are used directly."""
+    counts = exchange_counts(sorted_expert, bank.num_experts, group)
+    return _FusedEPFn.apply(ep, x_sorted.contiguous(), bank.gate_up_proj, bank.down_proj, counts, float(bank.clamp))

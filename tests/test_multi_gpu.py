@@ -140,6 +140,39 @@ def _worker(rank, world, port, out_path):
         want = torch.cat(attn_all, 1).float()[rank * T_loc:(rank + 1) * T_loc] @ wo.float().T
         res["ulysses_oproj"] = _close(got, want, 2e-2, 5e-2)
         barrier()
+
+        # ---- expert parallelism: fused peer-memory dispatch / combine against the NCCL all-to-all path ------------
+        from aspec_b200.models.draft.moe import ExpertBank
+        from aspec_b200.parallel.expert_parallel import (EPWorkspace, FusedExpertParallel, dispatch_combine,
+                                                         fused_dispatch_combine)
+        torch.manual_seed(4)
+        E, D3, I3, N3, k3 = 8, 256, 128, 512, 2
+        full_gu = (torch.randn(E, 2 * I3, D3, device=dev) * 0.05).to(bf)
+        full_dn = (torch.randn(E, D3, I3, device=dev) * 0.05).to(bf)
+        dist.broadcast(full_gu, 0)
+        dist.broadcast(full_dn, 0)
+        loc = E // world
+        outs = {}
+        torch.manual_seed(100 + rank)
+        x3 = (torch.randn(N3, D3, device=dev) * 0.5).to(bf)
+        sel = torch.randint(0, E, (N3 * k3,), device=dev)
+        order = torch.argsort(sel, stable=True)
+        dy3 = (torch.randn(N3 * k3, D3, device=dev) * 0.1).to(bf)
+        ews = exchange_workspaces(EPWorkspace(N3 * k3, D3, device=dev), EPWorkspace.open)
+        ep = FusedExpertParallel(rank, world, E, ews, barrier)
+        for name in ("nccl", "fused"):
+            bank = ExpertBank(E, D3, I3, ep_rank=rank, ep_size=world).to(dev, bf)
+            bank.gate_up_proj.data.copy_(full_gu[rank * loc:(rank + 1) * loc])
+            bank.down_proj.data.copy_(full_dn[rank * loc:(rank + 1) * loc])
+            xs3 = x3.repeat_interleave(k3, 0)[order].contiguous().requires_grad_(True)
+            y3 = (dispatch_combine(bank, xs3, sel[order]) if name == "nccl" else fused_dispatch_combine(ep, bank, xs3, sel[order]))
+            y3.backward(dy3)
+            outs[name] = (y3.detach().float(), xs3.grad.float(), bank.gate_up_proj.grad.float(), bank.down_proj.grad.float())
+        tolf = lambda a, b: _close(a, b, 5e-2, 3e-2 * max(b.abs().max().item(), 1e-3))
+        res["ep_forward"] = tolf(outs["fused"][0], outs["nccl"][0])
+        res["ep_dx"] = tolf(outs["fused"][1], outs["nccl"][1])
+        res["ep_dw"] = tolf(outs["fused"][2], outs["nccl"][2]) and tolf(outs["fused"][3], outs["nccl"][3])
+        barrier()
         torch.cuda.synchronize()
     except Exception as exc:                                     # noqa: BLE001 - reported to the parent
         import traceback
