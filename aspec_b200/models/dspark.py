@@ -110,11 +110,17 @@ class DSparkModel(DFlashModel):
 
         markov = self.draft_model.markov_head
         prev_emb = markov.get_prev_embeddings(prev_ids.reshape(-1)).to(hidden.dtype) if markov is not None else None
-        num_ce_l1, ce, l1, correct = head_loss(
-            hidden, lm_head_weight, target_ids.reshape(-1), w.reshape(-1),
-            prev_emb=prev_emb, markov_w2=markov.markov_w2.weight if markov is not None else None,
-            teacher_hidden=teacher_hidden, t_index=t_index, a_ce=self.ce_loss_alpha,
-            a_l1=self.l1_loss_alpha if teacher_hidden is not None else 0.0)
+        head_kw = dict(prev_emb=prev_emb, markov_w2=markov.markov_w2.weight if markov is not None else None,
+                       teacher_hidden=teacher_hidden, t_index=t_index, a_ce=self.ce_loss_alpha,
+                       a_l1=self.l1_loss_alpha if teacher_hidden is not None else 0.0)
+        vp = getattr(self, "vocab_parallel", None)
+        if vp is not None and hidden.is_cuda:
+            # ``lm_head_weight`` is this rank's row shard of the Target head; statistics merge over the peers' memory
+            from aspec_b200.parallel.vocab_parallel import vocab_parallel_head_loss
+            num_ce_l1, ce, l1, correct = vocab_parallel_head_loss(vp, hidden, lm_head_weight, target_ids.reshape(-1),
+                                                                  w.reshape(-1), **head_kw)
+        else:
+            num_ce_l1, ce, l1, correct = head_loss(hidden, lm_head_weight, target_ids.reshape(-1), w.reshape(-1), **head_kw)
         wf = w.reshape(-1)
         ce_num = (ce * wf).sum()
         l1_num = (l1 * wf).sum() if teacher_hidden is not None else ce_num.new_zeros(())

@@ -192,7 +192,9 @@ class _VocabParallelLossFn(torch.autograd.Function):
         dw2 = None
         if prev_emb is not None and ctx.needs_input_grad[4]:
             g = G.gemm(head.dlogits, prev_emb, a_t=True, b_t=True, out_dtype=torch.float32)
-            g.mul_(scale)
+            # every rank of the group back-propagates the same rows, and the data-parallel reduction then sums the
+            # group's (otherwise identical) gradients: shard-only gradients are pre-multiplied so both scale alike
+            g.mul_(scale * float(head.world))
             holder = ctx.w2_holder
             main = getattr(holder, "main_grad", None) if holder is not None else None
             if main is not None:

@@ -85,7 +85,9 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
     algorithm = resolve_draft_algorithm(draft_config)
     target_devs, draft_devs = _devices(flat)
     world = len(draft_devs)
-    cp = max(int(flat.get("draft_context_parallel_size", 1)), 1)
+    # ranks that must see the same rows: a context-parallel group shares a row's shards, a vocabulary-parallel group
+    # shares its supervised rows
+    cp = max(int(flat.get("draft_context_parallel_size", 1)), 1) * max(int(flat.get("vocab_parallel_size", 1) or 1), 1)
     dp = world // cp
     args = dict(flat)
     args.update(trainer_devices=draft_devs, run_id=flat.get("run_id") or f"run-{int(time.time())}",

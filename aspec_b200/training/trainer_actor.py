@@ -74,6 +74,23 @@ class TrainerActor:
             g = torch.Generator().manual_seed(1234)
             lm_head = torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * 0.02
         self.lm_head = lm_head.to(self.device, self.dtype).clone()     # own copy: the Target may live elsewhere
+        vp = int(self.args.get("vocab_parallel_size", 1) or 1)
+        if vp > 1 and self.cuda and hasattr(self.model, "prediction_start"):
+            # ranks [g * vp, (g + 1) * vp) train on the same rows; each keeps 1 / vp of the head's rows
+            from aspec_b200.parallel.group import exchange_workspaces, make_barrier
+            from aspec_b200.parallel.vocab_parallel import VocabParallelHead, VocabShardWorkspace
+            if self.world % vp:
+                raise ValueError("vocab_parallel_size must divide the Draft world size")
+            ranks = [list(range(g * vp, (g + 1) * vp)) for g in range(self.world // vp)]
+            groups = [dist.new_group(r) for r in ranks]
+            mine = groups[self.rank // vp]
+            rows = int(self.args.get("dspark_num_anchors", self.args.get("dflash_num_anchors", 512))) * int(self.model.block_size)
+            ws = exchange_workspaces(VocabShardWorkspace(rows, int(self.args["max_seq_length"]) + int(self.model.block_size) + 2,
+                                                         cfg.hidden_size, int(getattr(cfg, "markov_rank", 0) or 8), vp,
+                                                         device=self.device), VocabShardWorkspace.open, group=mine)
+            head = VocabParallelHead(self.rank % vp, vp, cfg.vocab_size, ws, make_barrier(self.device, mine))
+            self.model.vocab_parallel = head
+            self.lm_head = head.shard_rows(self.lm_head).contiguous()
         draft = self.model.draft_model
         if embedding is not None and hasattr(draft, "load_embedding"):
             draft.load_embedding(embedding.to(self.device))

@@ -79,7 +79,8 @@ def _worker(rank, world, port, out_path):
         res["vp_dhidden"] = _close(h2.grad, h1.grad, 5e-2, 4e-3 * gmax)
         res["vp_dprev"] = _close(p2.grad, p1.grad, 5e-2, 4e-3 * p1.grad.float().abs().max().item())
         sl = slice(head.offset, head.offset + head.shard)
-        res["vp_dw2"] = _close(W2.grad[sl], w2_ref.grad[sl], 5e-2, 4e-3 * w2_ref.grad.float().abs().max().item())
+        # shard-only gradients carry the group size (the data-parallel sum then treats them like replicated ones)
+        res["vp_dw2"] = _close(W2.grad[sl].float() / world, w2_ref.grad[sl], 5e-2, 4e-3 * w2_ref.grad.float().abs().max().item())
 
         # ---- direct context-parallel attention ----------------------------------------------------------------
         from aspec_b200.ops import attention_sm100 as K
