@@ -22,6 +22,8 @@
 //                  columns per half; D -> silu(gate) * up in bf16
 //
 // All waits are bounded (common.cuh); a timeout is reported in status[0].
+#include <cstdio>
+#include <cstdlib>
 #include "common.cuh"
 
 #include <stdio.h>
@@ -527,6 +529,19 @@ static int make_map_bf16(CUtensorMap* map, const void* base, long long rows, lon
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // First call on a thread that has no current context yet (for example an autograd worker whose first device
+    // work is this launch): bind the primary context of the operand's device and encode again.
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, base) == cudaSuccess && at.device >= 0) cudaSetDevice(at.device);
+    cudaFree(nullptr);
+    r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS && getenv("AB_DEBUG"))
+    fprintf(stderr, "cuTensorMapEncodeTiled failed: CUresult %d base %p rows %lld cols %lld ld %lld box %d x %d\n",
+            (int)r, base, rows, cols, ld, box_cols, box_rows);
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 

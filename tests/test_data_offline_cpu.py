@@ -1,0 +1,171 @@
+"""Data pipeline, offline feature store, feature contract, topology study, trackers and small runtime modules on CPU
+(reference: tests/test_data_*.py, tests/test_offline_dataset.py, tests/test_feature_contract.py, tests/test_topology.py)."""
+import json
+import os
+import signal
+
+import pytest
+import torch
+
+from aspec_b200.data.dataset import load_training_samples
+from aspec_b200.data.loss_mask import compute_assistant_loss_mask
+from aspec_b200.data.parse import create_parser
+from aspec_b200.data.preprocessing import generate_vocab_mapping
+from aspec_b200.data.template import TEMPLATE_REGISTRY
+from aspec_b200.data.utils import unpack_loss_mask
+from aspec_b200.feature_contract import (FeatureContractError, FeatureContractRuntime, build_target_feature_contract,
+                                         shared_feature_union, validate_feature_contract)
+from aspec_b200.offline.dataset import OfflineFeatureStore
+from aspec_b200.offline.generate import materialize, target_binding
+
+
+class Tok:
+    """Special tokens are single ids; every other character is one id."""
+    specials = ["<|im_start|>", "<|im_end|>", "<think>", "</think>"]
+    eos_token_id = 1001
+
+    def encode(self, text, add_special_tokens=False):
+        out, i = [], 0
+        while i < len(text):
+            for k, s in enumerate(self.specials):
+                if text.startswith(s, i):
+                    out.append(1000 + k)
+                    i += len(s)
+                    break
+            else:
+                out.append(ord(text[i]) % 1000)
+                i += 1
+        return out
+
+    def get_vocab(self):
+        return {s: 1000 + k for k, s in enumerate(self.specials)}
+
+    def apply_chat_template(self, messages, tools=None, tokenize=True, add_generation_prompt=False, **kw):
+        text = "".join(f"<|im_start|>{m['role']}\n{m['content']}<|im_end|>\n" for m in messages)
+        if add_generation_prompt:
+            text += "<|im_start|>assistant\n"
+        return self.encode(text)
+
+
+CONV = [{"from": "human", "value": "hi"}, {"from": "gpt", "value": "<think>hm</think>\n\nhello"},
+        {"role": "user", "content": "more"}, {"role": "assistant", "content": "sure", "reasoning_content": "think2"}]
+
+
+def test_thinking_parser_drops_history_reasoning_and_masks_the_last_turn():
+    parser = create_parser(Tok(), TEMPLATE_REGISTRY.get("qwen3-thinking"))
+    text = parser.format(CONV, last_turn_only=True)
+    assert "hm" not in text and "<think>\nthink2\n</think>\n\nsure" in text
+    ids, mask = parser.parse(CONV, 512, last_turn_only=True)
+    supervised = "<think>\nthink2\n</think>\n\nsure<|im_end|>\n"
+    assert int(mask.sum()) == len(Tok().encode(supervised)) and len(ids) == len(mask)
+    assert int(mask[: len(ids) - int(mask.sum())].sum()) == 0              # everything before the last reply is unsupervised
+
+
+def test_dataset_loader_cache_renderer_and_vocab_mapping(tmp_path):
+    path = tmp_path / "c.jsonl"
+    path.write_text("\n".join(json.dumps({"conversations": CONV}) for _ in range(3)))
+    args = {"max_seq_length": 512, "chat_template": "qwen", "cache_dir": str(tmp_path)}
+    rep = {}
+    samples = load_training_samples(str(path), args, tokenizer=Tok(), report=rep)
+    assert len(samples) == 3 and rep["cache"] == "miss" and rep["last_turn_only"] == 3
+    rep2 = {}
+    again = load_training_samples(str(path), args, tokenizer=Tok(), report=rep2)
+    assert rep2["cache"] == "hit" and torch.equal(again[0]["input_ids"], samples[0]["input_ids"])
+    rendered = load_training_samples(str(path), {"max_seq_length": 512, "renderer": "kimi_k3"}, tokenizer=Tok())
+    mask = unpack_loss_mask(rendered[0]["packed_loss_mask"], rendered[0]["input_ids"].numel())
+    assert int(mask.sum()) == 12 + 5                                        # both replies, each with its end-of-turn token
+    d2t, t2d = generate_vocab_mapping(samples, 2000, 16)
+    assert d2t.shape == (16,) and int(t2d.sum()) == 16
+    pre = tmp_path / "pre.jsonl"
+    pre.write_text(json.dumps({"input_ids": [1, 2, 3, 4], "loss_mask": [0, 0, 1, 1]}) + "\n")
+    assert load_training_samples(str(pre), {"max_seq_length": 8})[0]["packed_loss_mask"] == "2,2"
+
+
+def test_native_assistant_span_scan():
+    mask, last = compute_assistant_loss_mask(torch.tensor([5, 1, 2, 7, 7, 9, 1, 2, 8, 8]), [1, 2], [9])
+    assert mask.tolist() == [0, 0, 0, 1, 1, 0, 0, 0, 1, 1] and last == 8
+    only_last, _ = compute_assistant_loss_mask(torch.tensor([5, 1, 2, 7, 7, 9, 1, 2, 8, 8]), [1, 2], [9], last_turn_only=True)
+    assert only_last.tolist() == [0] * 8 + [1, 1]
+
+
+def test_feature_contract_identity_validation_and_union():
+    kw = dict(drafter_family="dspark", target_hidden_size=32, target_num_hidden_layers=8, store_last_hidden_states=True)
+    a = build_target_feature_contract(aux_hidden_state_layers=[1, 3, 5], **kw)
+    validate_feature_contract(a)
+    tampered = dict(a, target_hidden_size=64)
+    with pytest.raises(FeatureContractError, match="identity mismatch"):
+        validate_feature_contract(tampered)
+    with pytest.raises(FeatureContractError):
+        build_target_feature_contract(aux_hidden_state_layers=[1, 9], **kw)
+    rt = FeatureContractRuntime(a, role="consumer", participant="t")
+    good = {"input_ids": torch.zeros(7, dtype=torch.long), "hidden_states": torch.zeros(7, 96, dtype=torch.bfloat16),
+            "last_hidden_states": torch.zeros(7, 32, dtype=torch.bfloat16)}
+    rt.validate_payload(good)
+    with pytest.raises(FeatureContractError, match="width"):
+        rt.validate_payload({**good, "hidden_states": torch.zeros(7, 64, dtype=torch.bfloat16)})
+    b = build_target_feature_contract(aux_hidden_state_layers=[3, 7], **{**kw, "store_last_hidden_states": False})
+    union = shared_feature_union([a, b])
+    assert union["contract"]["aux_hidden_state_layers"] == [1, 3, 5, 7]
+    assert union["views"][1]["layer_columns"] == [1, 3] and not union["views"][1]["last_hidden_states"]
+
+
+def test_offline_store_round_trip_hash_check_and_resume(tmp_path):
+    dc = dict(target_hidden_size=32, target_num_hidden_layers=8, target_layer_ids=[1, 3, 5])
+    binding = target_binding({"model": "toy"}, dc, "dspark", True)
+    docs = [{"data_id": i, "input_ids": torch.randint(0, 50, (10 + i,)), "loss_mask": torch.ones(10 + i)} for i in range(3)]
+    feats = lambda ids: (torch.randn(len(ids), 96), torch.randn(len(ids), 32))
+    out = str(tmp_path / "off")
+    materialize(out, docs[:2], feats, binding)
+    store = OfflineFeatureStore(out)
+    assert len(store) == 2 and store.load("1")["hidden_states"].shape == (11, 96)
+    assert next(store.samples())["packed_loss_mask"] == "0,10"
+    materialize(out, docs, feats, binding, resume=True)                     # appends only the missing document
+    assert len(OfflineFeatureStore(out)) == 3
+    with pytest.raises(FeatureContractError):
+        OfflineFeatureStore(out).validate_consumer("sha-of-another-contract")
+    victim = os.path.join(out, store.rows()[0]["file"])
+    with open(victim, "ab") as f:
+        f.write(b"x")
+    with pytest.raises(ValueError, match="manifest hash"):
+        OfflineFeatureStore(out).load("0")
+    with pytest.raises(FileExistsError):
+        OfflineFeatureStore(out, create=True, binding=binding)
+
+
+def test_topology_prediction_and_legal_splits():
+    from aspec_b200.topology import legal_splits, predict
+    assert legal_splits(8, cp=2) == [(2, 6), (4, 4), (6, 2)]
+    assert predict(48000, 90000, 5, 3) == (240000, "target")
+    assert predict(48000, 90000, 6, 2)[1] == "draft"
+
+
+def test_trackers_locality_identity_and_termination(tmp_path):
+    from aspec_b200.locality import apportion
+    from aspec_b200.runtime_control import TerminationRequested, deferred_termination, install_termination_handlers, restore_handlers
+    from aspec_b200.runtime_identity import runtime_identity, verify_runtime_identity
+    from aspec_b200.utils.env import forwarded_environment, recorded_environment
+    from aspec_b200.utils.logging import Trackers
+    t = Trackers(str(tmp_path), "wandb,nosuch")
+    t.log({"train/avg_loss": 1.5, "note": "x"}, 3)
+    t.close()
+    tracking = json.load(open(tmp_path / "tracking.json"))
+    assert tracking["active"][0] == "jsonl" and "nosuch" in tracking["unavailable"]
+    assert json.loads(open(tmp_path / "runs" / "metrics.jsonl").read())["train/avg_loss"] == 1.5
+    assert apportion(10, {"a": 3, "b": 1, "c": 0}) == {"a": 7, "b": 3, "c": 0}
+    ident = runtime_identity()
+    verify_runtime_identity(ident)
+    with pytest.raises(ValueError):
+        verify_runtime_identity({**ident, "sha256": "0" * 64})
+    env = forwarded_environment({"ASPEC_X": "1", "CUDA_VISIBLE_DEVICES": "3", "RANDOM": "z", "NCCL_DEBUG": "INFO"})
+    assert env == {"ASPEC_X": "1", "NCCL_DEBUG": "INFO"}
+    assert recorded_environment({"ASPEC_API_TOKEN": "secret"})["ASPEC_API_TOKEN"] == "***"
+    prev = install_termination_handlers((signal.SIGUSR1,))
+    try:
+        with pytest.raises(TerminationRequested):
+            with deferred_termination():
+                os.kill(os.getpid(), signal.SIGUSR1)
+                reached = True                                              # delivery is deferred to the end of the block
+            raise AssertionError("termination was swallowed")
+        assert reached
+    finally:
+        restore_handlers(prev)
