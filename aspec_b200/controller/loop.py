@@ -137,7 +137,8 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
             res = results_by_row.pop(req.row_id, None)
             if res is None:
                 raise RuntimeError(f"row {req.row_id} was trained on but never reported by its engine")
-            controller.release_result(res[0], participant=f"trainer{rank}")
+            for consumer in consumer_of_rank(rank):          # every reader of the row releases its own lease
+                controller.release_result(res[0], participant=f"trainer{consumer}")
             tokens += sum(req.document_lengths)
         controller.commit_optimizer_step(step, committed)
         completed += 1

@@ -269,6 +269,10 @@ class DFlashModel(nn.Module):
                     layout.anchor + row_off, keep_flat, ctx_len=B * T, block_size=bs,
                     doc_start=ds + row_off, context_window=cw, query_window=qw, causal=causal)
             tables.append(cache[key])
+        cp = self.context_parallel
+        if cp is not None and cp.size > 1:
+            return self._context_parallel_backbone(cp, hidden_states, B, T, layout, keep_flat, embeds, ctx_pos, draft_pos,
+                                                   tables, aux)
         if aux is not None:
             aux["layout"] = layout
             aux["keep"] = keep_flat
@@ -278,6 +282,33 @@ class DFlashModel(nn.Module):
         hidden = self.draft_model(ctx, embeds, ctx_pos.to(torch.int32), draft_pos.to(torch.int32),
                                   tables, aux)
         return hidden, layout, keep_flat
+
+    def _context_parallel_backbone(self, cp, hidden_states, B, T, layout, keep_flat, embeds, ctx_pos, draft_pos, tables, aux):
+        """This rank's share of the backbone: its context rows, its blocks; attention exchanges with the other owners."""
+        from aspec_b200.parallel.context_parallel import local_intervals
+        if any(k not in ("full_attention", "sliding_attention") for k in (self._policy or {}).get("layer_types", [])):
+            raise NotImplementedError("context parallelism is wired for dense and sliding-window layers")
+        bs, n, total = self.block_size, layout.n, B * T
+        s, e = cp.context_bounds(total)
+        lo, hi = cp.block_bounds(n)
+        wdtype = self.draft_model.context_proj.weight.dtype
+        ctx_local = self.draft_model.extract_context_feature(hidden_states.reshape(total, -1)[s:e].to(wdtype))
+        q_lo, q_hi = lo * bs, hi * bs
+        owners = [cp.block_bounds(n, o) for o in range(cp.size)]
+        counts = [(b - a) * bs for a, b in owners]
+        per_layer, cache = [], {}
+        for t in tables:
+            key = id(t)
+            if key not in cache:
+                cache[key] = {"cp": cp, "counts": counts,
+                              "tables": [local_intervals(t[a * bs:b * bs], s, e, total, own=(o == cp.rank), query_start=q_lo)
+                                         for o, (a, b) in enumerate(owners)]}
+            per_layer.append(cache[key])
+        hidden = self.draft_model(ctx_local, embeds[q_lo:q_hi], ctx_pos[s:e].to(torch.int32),
+                                  draft_pos[q_lo:q_hi].to(torch.int32), per_layer, aux)
+        local = BlockLayout(layout.row[lo:hi], layout.anchor[lo:hi], layout.slot[lo:hi], layout.n_rows, layout.seq_len,
+                            layout.n_slots)
+        return hidden, local, keep_flat[lo:hi]
 
     # -------------------------------------------------------------- aux losses --
     def _aux_losses(self, aux: dict, weights: torch.Tensor, denominator: torch.Tensor):

@@ -85,7 +85,11 @@ class DFlashAttention(nn.Module):
         inv_freq = self.rope_freqs.get(x.device)
         q = qk_norm_rope(q, self.q_norm.weight, q_pos, inv_freq, self.eps, self.rope_scaling)
         k = qk_norm_rope(k, self.k_norm.weight, kv_pos, inv_freq, self.eps, self.rope_scaling)
-        if attn_override is not None:
+        if isinstance(intervals, dict):
+            # context parallel: k / v are this rank's context shard + own draft rows; the runtime exchanges queries and
+            # partial results with the other owners
+            o = intervals["cp"].attention(self.layer_idx, q, k, v, intervals["tables"], intervals["counts"], self.scale)
+        elif attn_override is not None:
             o = attn_override(self, q, k, v, intervals)
         else:
             o, _ = interval_attention(q, k, v, intervals, self.scale)

@@ -45,6 +45,17 @@ class TrainerActor:
         self.draft_config = AutoDraftModelConfig.from_dict(draft_config)
         self.model = build_training_model(self.draft_config, self.args, self.device, self.dtype)
         cfg = self.draft_config
+        self.cp_size = max(int(self.args.get("draft_context_parallel_size", 1) or 1), 1)
+        if self.cp_size > 1 and hasattr(self.model, "context_parallel") and world > 1:
+            # ranks [g * cp, (g + 1) * cp) share every row: each projects its context shard and carries its own blocks
+            from aspec_b200.parallel.cp_runtime import ContextParallel, attach
+            if world % self.cp_size:
+                raise ValueError("draft_context_parallel_size must divide the Draft world size")
+            groups = [dist.new_group(list(range(g * self.cp_size, (g + 1) * self.cp_size))) for g in range(world // self.cp_size)]
+            per_rank = -(-int(self.model.num_anchors) // self.cp_size) * int(self.model.block_size)
+            attach(self.model, ContextParallel(groups[rank // self.cp_size], num_layers=int(cfg.num_hidden_layers),
+                                               max_queries=per_rank, heads=int(cfg.num_attention_heads),
+                                               head_dim=int(cfg.head_dim), device=self.device))
         layout = SlotLayout(int(self.args["max_seq_length"]), int(getattr(cfg, "num_target_layers", None)
                                                                    or getattr(cfg, "num_aux_hidden_states", 3)),
                             int(getattr(cfg, "target_hidden_size", cfg.hidden_size)),
@@ -121,7 +132,12 @@ class TrainerActor:
             batch["base_position_ids"] = torch.cat([torch.arange(n) for n in lens])[None]
             batch["packed_document_lengths"] = lens
         if hasattr(self.model, "sample_anchors"):
-            anchors, keep = self.model.sample_anchors(loss_mask, ctx_docs, lens if len(lens) > 1 else None)
+            seed = None
+            if getattr(self, "cp_size", 1) > 1:
+                # every rank of a context-parallel group must draw the same anchors for the row
+                import zlib
+                seed = zlib.crc32(str(sample.row_id).encode()) ^ int(self.args.get("seed", 0))
+            anchors, keep = self.model.sample_anchors(loss_mask, ctx_docs, lens if len(lens) > 1 else None, anchor_seed=seed)
             batch["injected_anchors"], batch["injected_keep_mask"] = anchors, keep
         return batch
 

@@ -1,0 +1,73 @@
+"""Context-parallel wiring on CPU: two gloo ranks, each with half of the context rows and half of the blocks, must
+reproduce the single-rank loss terms and (summed over ranks) the single-rank gradients."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from aspec_b200.config.draft_config import DSparkConfig
+from aspec_b200.models.draft.dspark import DSparkDraftModel
+from aspec_b200.models.dspark import DSparkModel
+from aspec_b200.ops.anchors import sample_anchor_positions
+
+CFG = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+           vocab_size=256, num_target_layers=3, target_hidden_size=64, target_num_hidden_layers=8, markov_rank=16,
+           mask_token_id=255, layer_types=["full_attention", "sliding_attention"], sliding_window=24)
+
+
+def _inputs():
+    g = torch.Generator().manual_seed(5)
+    T = 96
+    ids = torch.randint(0, 250, (1, T), generator=g)
+    feats = torch.randn(1, T, 192, generator=g)
+    last = torch.randn(1, T, 64, generator=g)
+    mask = torch.ones(1, T)
+    mask[:, :12] = 0
+    head = torch.randn(256, 64, generator=g) * 0.1
+    anchors, keep = sample_anchor_positions(T, mask, 12, 4, generator=torch.Generator().manual_seed(9))
+    return ids, feats, mask, head, last, anchors, keep
+
+
+def _model():
+    torch.manual_seed(0)
+    return DSparkModel(DSparkDraftModel(DSparkConfig(**CFG)), block_size=4, num_anchors=12)
+
+
+def _run(model):
+    ids, feats, mask, head, last, anchors, keep = _inputs()
+    out = model(ids, feats, mask, head, last_hidden_states=last, injected_anchors=anchors, injected_keep_mask=keep)
+    num, den = out[6]
+    num.backward()
+    grads = {n: p.grad.clone() for n, p in model.draft_model.named_parameters() if p.grad is not None}
+    return num.detach(), den.detach(), grads
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from aspec_b200.parallel.cp_runtime import ContextParallel, attach
+    model = _model()
+    attach(model, ContextParallel(num_layers=2, max_queries=24, heads=4, head_dim=16))
+    num, den, grads = _run(model)
+    stats = torch.stack([num, den])
+    dist.all_reduce(stats)
+    for g in grads.values():
+        dist.all_reduce(g)
+    if rank == 0:
+        torch.save({"stats": stats, "grads": grads}, out)
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_cp2_matches_single_rank(tmp_path):
+    out = str(tmp_path / "cp.pt")
+    mp.spawn(_worker, args=(2, 29900 + os.getpid() % 500, out), nprocs=2, join=True)
+    got = torch.load(out)
+    num, den, grads = _run(_model())
+    assert torch.allclose(got["stats"][1], den)
+    assert torch.allclose(got["stats"][0], num, rtol=1e-4, atol=1e-5)
+    assert set(got["grads"]) == set(grads)
+    for name, g in grads.items():
+        assert torch.allclose(got["grads"][name], g, rtol=2e-3, atol=2e-5), name

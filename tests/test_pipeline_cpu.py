@@ -116,3 +116,19 @@ def test_full_shard_matches_replicate(tmp_path):
             assert logs2[0]["train/step"] == 2
             assert logs2[0]["train/avg_loss"] == pytest.approx(logs[2]["train/avg_loss"], rel=1e-5)
     assert losses["FULL_SHARD"] == pytest.approx(losses["REPLICATE"], rel=1e-5)
+
+
+@pytest.mark.timeout(600)
+def test_context_parallel_trainers_share_rows(tmp_path):
+    """Two trainers forming one context-parallel group: every row goes to both, each takes half of the context and
+    half of the blocks, and the work ledger sees two consumers per row."""
+    plan = _plan(tmp_path, ["training.draft_context_parallel_size=2", "training.dspark_num_anchors=16"])
+    assert plan.policy["dp_size"] == 1 and plan.policy["context_parallel"] == 2
+    flat = plan.to_runtime_args()
+    flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=0, save_final_checkpoint=False)
+    os.makedirs(flat["output_dir"], exist_ok=True)
+    logs = []
+    summary = train_async_no_generation(flat, plan.draft_config, log=logs.append)
+    assert summary["completed_steps"] == 3
+    assert all(l["train/avg_loss"] == l["train/avg_loss"] and l["train/avg_loss"] > 0 for l in logs)
+    assert summary["ledger"]["validated"] and len(summary["ledger"]["committed_work_ids"]) == 6
