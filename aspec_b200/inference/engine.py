@@ -135,14 +135,21 @@ class NativeTargetEngine(InferenceEngine):
     def generate(self, requests: Sequence[RowRequest]) -> List[InferenceOutput]:
         t0 = time.perf_counter()
         outs = []
+        if self.fail_after is not None and getattr(self, "rows_done", 0) + len(requests) > self.fail_after:
+            raise RuntimeError(f"{self.name}: injected producer failure")
+        # all requests of the call run as ONE packed prefill (bigger GEMMs); each request's rows go to its own slots
+        all_views, segments, off = [], [], 0
         for req in requests:
-            if self.fail_after is not None and getattr(self, "rows_done", 0) >= self.fail_after:
-                raise RuntimeError(f"{self.name}: injected producer failure")
             views = self._slot_views(req)
-            sink = RingFeatureSink(views, self.layer_ids, self.model.config.hidden_size,
-                                   [self._layers_of(c) for c, _s, _g in req.leases])
-            ids = req.input_ids.to(self.device, non_blocking=True)
-            self.model.prefill(ids, req.document_lengths, self.layer_ids, sink=sink)
+            n = int(req.input_ids.shape[0])
+            segments.append((off, off + n, RingFeatureSink(views, self.layer_ids, self.model.config.hidden_size,
+                                                           [self._layers_of(c) for c, _s, _g in req.leases])))
+            all_views.append(views)
+            off += n
+        ids = torch.cat([req.input_ids.reshape(-1) for req in requests]).to(self.device, non_blocking=True)
+        lengths = [n for req in requests for n in req.document_lengths]
+        self.model.prefill(ids, lengths, self.layer_ids, sink=segments if len(requests) > 1 else segments[0][2])
+        for req, views in zip(requests, all_views):
             outs.append(self._finish(req, views, self.layer_ids, self.device_flags))
         if self.device.type == "cuda" and not self.device_flags:
             torch.cuda.current_stream(self.device).synchronize()     # host-ordered readiness

@@ -188,7 +188,16 @@ class DenseTarget(nn.Module):
         return rmsnorm_reference(x, w, self.config.rms_norm_eps)
 
     def _proj_residual(self, a, w, residual, mirrors=None):
-        """``residual + a @ w.T`` with the add (and the optional mirrored stores) in the GEMM epilogue."""
+        """``residual + a @ w.T`` with the add (and the optional mirrored stores) in the GEMM epilogue.
+
+        ``mirrors`` is a list of destination views of the whole output, or a list of ``(row_start, row_end, views)``
+        segments when several requests were batched into one prefill: then the product runs once per segment so that
+        each request's rows go to its own destinations."""
+        if mirrors and isinstance(mirrors[0], tuple):
+            out = torch.empty_like(residual)
+            for r0, r1, views in mirrors:
+                out[r0:r1] = self._proj_residual(a[r0:r1], w, residual[r0:r1], views)
+            return out
         if self._use_kernels(a):
             from aspec_b200.ops import gemm as G
             return G.gemm(a, w, addend=residual, mirrors=mirrors or None)
@@ -201,7 +210,11 @@ class DenseTarget(nn.Module):
         if layer.is_moe:
             out = residual + layer.mlp(x)
             for m in mirrors or ():
-                m.copy_(out)
+                if isinstance(m, tuple):
+                    for view in m[2]:
+                        view.copy_(out[m[0]:m[1]])
+                else:
+                    m.copy_(out)
             return out
         if self._use_kernels(x):
             from aspec_b200.ops import gemm as G
@@ -231,14 +244,18 @@ class DenseTarget(nn.Module):
 
     @torch.no_grad()
     def prefill(self, input_ids: torch.Tensor, document_lengths: Sequence[int], capture_layers: Sequence[int],
-                sink: Optional[FeatureSink] = None, want_logits: bool = False) -> Dict[str, torch.Tensor]:
-        """``input_ids [T]`` (packed documents).  Returns the sink's tensors (and logits when asked)."""
+                sink=None, want_logits: bool = False) -> Dict[str, torch.Tensor]:
+        """``input_ids [T]`` (packed documents).  Returns the sink's tensors (and logits when asked).
+
+        ``sink`` may be a list of ``(row_start, row_end, sink)`` segments: several requests batched into one pass (larger
+        GEMMs), each with its own destinations."""
         cfg = self.config
         T = input_ids.shape[0]
         dev = input_ids.device
         if sum(document_lengths) != T:
             raise ValueError("document_lengths must sum to the number of tokens")
         x = self.embed_tokens(input_ids)
+        segments = sink if isinstance(sink, list) else None
         if sink is None:
             sink = FeatureSink(T, capture_layers, cfg.hidden_size, dev, x.dtype)
         pos_list = torch.cat([torch.arange(n) for n in document_lengths]).to(torch.int32)
@@ -250,8 +267,19 @@ class DenseTarget(nn.Module):
             a = self._attention(layer, h, positions, intervals)
             x = self._proj_residual(a, layer.o_proj, x)
             h = self._norm(x, layer.post_attention_layernorm)
-            x = self._mlp(layer, h, x, sink.layer_views(i) if i in capture else None)
+            if i not in capture:
+                mirrors = None
+            elif segments is not None:
+                mirrors = [(r0, r1, sk.layer_views(i)) for r0, r1, sk in segments]
+            else:
+                mirrors = sink.layer_views(i)
+            x = self._mlp(layer, h, x, mirrors)
         final = self._norm(x, self.norm)
+        if segments is not None:
+            for r0, r1, sk in segments:
+                for view in sk.final_views():
+                    view.copy_(final[r0:r1])
+            return {"final_hidden": final}
         for view in sink.final_views():
             view.copy_(final)
         out = {"hidden_states": getattr(sink, "hidden_states", None),

@@ -49,6 +49,8 @@ def parse_args():
                     help="draft: Draft-only data parallel (the `value`); online: Target + Draft ranks with feature rings")
     ap.add_argument("--targets", type=int, default=0, help="online: Target GPUs (default N // 2)")
     ap.add_argument("--target-layers-total", type=int, default=36)
+    ap.add_argument("--target-batch", type=int, default=4, help="online: documents packed into one Target prefill")
+    ap.add_argument("--fsdp", action="store_true", help="draft mode: FULL_SHARD optimizer over peer memory instead of REPLICATE")
     return ap.parse_args()
 
 
@@ -165,7 +167,7 @@ def run_ours(args):
     total_updates = args.steps * 2 + args.warmup * 2 + 8
     trainer = DraftTrainer(model, lm_head, lr=6e-4, min_lr=6e-5, weight_decay=0.0, max_grad_norm=1.0,
                            total_steps=max(total_updates, 32), warmup_ratio=0.04, accumulation=args.accum,
-                           device=device)
+                           device=device, fsdp_strategy="FULL_SHARD" if args.fsdp else "REPLICATE")
     n_docs = args.pool or args.accum * 2
     pool = make_pool(args, cfg, model, rank, n_docs, pin=cuda)
     resident = [trainer.to_device(b) for b in pool]
@@ -243,7 +245,7 @@ def run_ours(args):
             "config": {"model": f"Qwen3-8B-shaped DSpark draft, {args.layers} layer(s), {args.target_layers} captured layers, vocab {cfg.vocab_size}",
                        "global_batch": args.accum * world, "seq_len": args.max_len,
                        "doc_lengths": f"log-uniform [{args.min_len},{args.max_len}]",
-                       "parallelism": f"dp{world}", "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,
+                       "parallelism": f"dp{world}" + ("+full_shard" if args.fsdp else ""), "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,
                        "block_size": model.block_size,
                        "l2_policy": "inputs larger than L2 (1.2 GB lm_head + per-document features stream from HBM every micro-batch)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours",
@@ -286,7 +288,8 @@ def run_online(args) -> dict:
         dspark_l1_loss_alpha=0.9, dspark_confidence_head_alpha=1.0, train_data_path="synthetic",
         synthetic_num_documents=max(steps * args.accum * D * 2, 64), synthetic_min_length=min(args.min_len, args.max_len),
         synthetic_max_length=args.max_len, synthetic_vocab_size=dims["vocab_size"] - 1024, shuffle_dataset=True,
-        length_group_size=1, transport_destination_ring_slots=max(2 * args.accum + 2, 4), inference_batch_size=1,
+        length_group_size=1, transport_destination_ring_slots=max(2 * args.accum + 2, 4),
+        inference_batch_size=max(args.target_batch, 1),
         store_last_hidden_states=True, output_dir=out_dir, save_interval=0, save_final_checkpoint=False,
         performance_warmup_steps=args.warmup, performance_drain_steps=0, optimizer_step_timeout_seconds=900.0,
         target_model_config={"model_type": "qwen3", "hidden_size": dims["hidden_size"], "intermediate_size": dims["intermediate_size"],
