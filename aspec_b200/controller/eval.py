@@ -52,6 +52,8 @@ class EvalRunner:
 
             def on_result(out, req):
                 from aspec_b200.utils.types import TrainSample
+                if not str(out.row_id).startswith("eval-"):
+                    return prev(out, req)              # a dispatched-ahead training row finished during the evaluation
                 results[out.row_id] = (out, req)
                 for key, (consumer, _s, _g) in zip(out.feature_keys, req.leases):
                     self.queues[consumer].put(TrainSample(key, out.tensor_shapes, out.document_lengths, out.packed_loss_masks,
@@ -59,16 +61,22 @@ class EvalRunner:
 
             self.manager.on_result = on_result
             try:
-                futs = [t.call_async("eval_from_queue", len(rows), self.identity) for t in self.trainers]
+                for f in [t.call_async("eval_begin", self.identity) for t in self.trainers]:
+                    f.get(timeout=600)
+                # one row per rank at a time: the trainers hand each lease back right away, so the evaluation fits in the
+                # ring slots that the dispatched-ahead training rows leave free
                 for micro in rows:
+                    futs = [t.call_async("eval_step", 1) for t in self.trainers]
                     for rank, idx in enumerate(micro):
                         req = self.controller.row_request([idx], self.layer_ids)
                         req.row_id = "eval-" + req.row_id
                         self.manager.submit(req, self.consumer_of_rank(rank))
-                outs = [f.get(timeout=3600) for f in futs]
-                for o in outs:
-                    for consumer, slot, gen in o["releases"]:
-                        self.rings[consumer].release_acknowledged(slot, gen, "eval")
+                    for f in futs:
+                        for consumer, slot, gen in f.get(timeout=3600)["releases"]:
+                            owner = next((f"row:{rid}" for rid, (_o, rq) in results.items()
+                                          if (consumer, slot, gen) in [tuple(l) for l in rq.leases]), "row:unknown")
+                            self.rings[consumer].release_acknowledged(slot, gen, owner)
+                outs = [f.get(timeout=3600) for f in [t.call_async("eval_end") for t in self.trainers]]
                 self.cached = all(o.get("cached", 0) == len(rows) for o in outs)
             finally:
                 self.manager.on_result = prev

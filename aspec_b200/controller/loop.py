@@ -48,7 +48,8 @@ class ThroughputWindow:
 
 def training_loop(*, controller, manager, trainers, rings, train_queues, args: Dict, layer_ids, num_steps: int,
                   start_step: int = 0, log: Callable[[dict], None] = print, evidence=None, timeline=None,
-                  consumer_of_rank: Optional[Callable[[int], List[int]]] = None) -> dict:
+                  consumer_of_rank: Optional[Callable[[int], List[int]]] = None,
+                  on_step: Optional[Callable[[int, dict], None]] = None) -> dict:
     """Runs ``num_steps`` optimizer updates.  ``trainers[r]`` are actors; ``rings[c]`` the lease rings."""
     accumulation = int(args.get("draft_accumulation_steps", 1))
     budget = float(args.get("optimizer_step_timeout_seconds", 1800.0))
@@ -154,6 +155,8 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
         next_step_id = step + 1
         if output_dir and save_interval and next_step_id % save_interval == 0:
             save_checkpoint(trainers, controller, output_dir, next_step_id, args)
+        if on_step is not None:
+            on_step(next_step_id, metrics)          # held-out evaluation, trackers
         step += 1
     if output_dir and args.get("save_final_checkpoint", True) and completed and not (
             save_interval and step % save_interval == 0):

@@ -134,9 +134,30 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
         num_steps = int(flat.get("num_train_steps") or 0) or max(n // max(dp * int(flat.get("micro_batch_size", 1))
                                                                      * int(flat.get("draft_accumulation_steps", 1)), 1), 1)
         consumer_of_rank = (lambda r: list(range(r * cp, (r + 1) * cp)))
+        on_step = None
+        eval_history: list = []
+        if flat.get("eval_data_path") and int(flat.get("eval_interval") or 0) > 0:
+            from aspec_b200.controller.eval import EvalRunner
+            eval_args = dict(args, train_data_path=flat["eval_data_path"], shuffle_dataset=False,
+                             synthetic_num_documents=int(flat.get("eval_num_documents") or 32),
+                             dataset_seed=int(flat.get("seed", 0)) + 1)
+            eval_controller = TrainingController(eval_args, dp_size=dp, consumers_per_row=cp, algorithm=algorithm)
+            eval_controller.load_dataset(None)
+            runner = EvalRunner(controller=eval_controller, manager=manager, trainers=trainers, rings=rings, train_queues=queues,
+                                args=args, layer_ids=layer_ids, consumer_of_rank=consumer_of_rank)
+            interval = int(flat["eval_interval"])
+
+            def on_step(next_step: int, metrics: dict) -> None:
+                if next_step % interval == 0:
+                    m = runner.run(next_step)
+                    eval_history.append({"step": next_step, **m})
+                    log({"train/step": next_step - 1, **m})
         summary = training_loop(controller=controller, manager=manager, trainers=trainers, rings=rings,
                                 train_queues=queues, args=args, layer_ids=layer_ids, num_steps=num_steps - start_step,
-                                start_step=start_step, log=log, evidence=evidence, consumer_of_rank=consumer_of_rank)
+                                start_step=start_step, log=log, evidence=evidence, consumer_of_rank=consumer_of_rank,
+                                on_step=on_step)
+        if eval_history:
+            summary["evaluation"] = eval_history
         summary["engines"] = [e.call("get_status", timeout=30) if isinstance(e, ProcessActor) else e.get_status()
                               for e in engines]
         return summary

@@ -152,41 +152,54 @@ class DraftTrainer:
         if layers:
             update_ling_bias(layers, counts, cfg.moe_router_bias_update_rate, cfg.bias_zero_mean_update)
 
+    # -- held-out evaluation: same forward and pooling as training, no gradients, no optimizer step ---------------
+    # (reference: aspec/controller/eval.py:42-357, aspec/training/trainer.py:387-533)
+    def eval_begin(self) -> dict:
+        return {"pool": {}, "n": 0}
+
     @torch.no_grad()
-    def eval_update(self, batches: Iterable[dict]) -> Dict[str, float]:
-        """Held-out pass: same forward and pooling as training, no gradients, no optimizer step.  Metrics come back
-        under ``eval/`` (reference: aspec/controller/eval.py:42-357, aspec/training/trainer.py:387-533)."""
+    def eval_add(self, state: dict, batch: dict) -> None:
         was_training = self.model.training
         self.model.eval()
-        saved_pool, saved_last = self._pool, self._last
-        self._pool = {}
+        saved = self._pool
+        self._pool = state["pool"]
         try:
-            n = 0
-            for batch in batches:
-                self._forward_backward(self.to_device(batch))
-                n += 1
-            if n == 0:
-                return {}
-            pooled = {k: torch.stack(v).sum(0) for k, v in self._pool.items()}
-            world = dist.get_world_size(self.dp_group) if (dist.is_available() and dist.is_initialized()) else 1
-            if world > 1:
-                keys = sorted(pooled)
-                flat = torch.cat([pooled[k].reshape(-1) for k in keys])
-                dist.all_reduce(flat, group=self.dp_group)
-                off = 0
-                for k in keys:
-                    m = pooled[k].numel()
-                    pooled[k] = flat[off:off + m].view_as(pooled[k])
-                    off += m
-            pooled["grad_norm"] = torch.zeros((), device=self.device)
-            self._last = pooled
-            out = {("eval/" + k[len("train/"):] if k.startswith("train/") else k): v for k, v in self.metrics().items()}
-            for drop in ("eval/grad_norm", "eval/lr", "eval/global_step"):
-                out.pop(drop, None)
-            return out
+            self._forward_backward(self.to_device(batch))
+            state["n"] += 1
         finally:
-            self._pool, self._last = saved_pool, saved_last
+            self._pool = saved
             self.model.train(was_training)
+
+    def eval_end(self, state: dict) -> Dict[str, float]:
+        if state["n"] == 0:
+            return {}
+        pooled = {k: torch.stack(v).sum(0) for k, v in state["pool"].items()}
+        world = dist.get_world_size(self.dp_group) if (dist.is_available() and dist.is_initialized()) else 1
+        if world > 1:
+            keys = sorted(pooled)
+            flat = torch.cat([pooled[k].reshape(-1) for k in keys])
+            dist.all_reduce(flat, group=self.dp_group)
+            off = 0
+            for k in keys:
+                m = pooled[k].numel()
+                pooled[k] = flat[off:off + m].view_as(pooled[k])
+                off += m
+        pooled["grad_norm"] = torch.zeros((), device=self.device)
+        saved_last = self._last
+        self._last = pooled
+        try:
+            out = {("eval/" + k[len("train/"):] if k.startswith("train/") else k): v for k, v in self.metrics().items()}
+        finally:
+            self._last = saved_last
+        for drop in ("eval/grad_norm", "eval/lr", "eval/global_step"):
+            out.pop(drop, None)
+        return out
+
+    def eval_update(self, batches: Iterable[dict]) -> Dict[str, float]:
+        state = self.eval_begin()
+        for b in batches:
+            self.eval_add(state, b)
+        return self.eval_end(state)
 
     def metrics(self) -> Dict[str, float]:
         """Metrics of the last update (one device->host transfer)."""

@@ -141,18 +141,30 @@ class TrainerActor:
             batch["injected_anchors"], batch["injected_keep_mask"] = anchors, keep
         return batch
 
-    def _samples(self, num_batches: int, timeout: float):
+    def _samples(self, num_batches: int, timeout: float, evaluation: bool = False):
+        """Training and held-out samples share the queue (rows whose id starts with ``eval-`` are held-out); a sample
+        of the other kind that arrives first is set aside and served to the next reader of its kind."""
         deadline = time.monotonic() + timeout
+        stash = self.__dict__.setdefault("_stash", [])
         for _ in range(num_batches):
-            while True:
-                try:
-                    item = self.queue.get(timeout=0.2)
+            item = None
+            for i, held in enumerate(stash):
+                if str(held.row_id).startswith("eval-") == evaluation:
+                    item = stash.pop(i)
                     break
+            while item is None:
+                try:
+                    got = self.queue.get(timeout=0.2)
                 except _queue.Empty:
                     if time.monotonic() > deadline:
                         raise TimeoutError(f"trainer {self.rank}: no sample within {timeout}s") from None
-            if item is None:
-                raise RuntimeError("train queue was closed")
+                    continue
+                if got is None:
+                    raise RuntimeError("train queue was closed")
+                if str(got.row_id).startswith("eval-") == evaluation:
+                    item = got
+                else:
+                    stash.append(got)
             yield item
 
     # -- the step ---------------------------------------------------------------------------------
@@ -186,33 +198,44 @@ class TrainerActor:
         return {"metrics": metrics, "committed": consumed, "releases": releases, "step": step}
 
     # -- evaluation -------------------------------------------------------------------------------
-    def eval_from_queue(self, num_batches: int, cache_key: str = "", timeout: float = 1800.0) -> dict:
-        """Held-out pass over ``num_batches`` ring samples.  With ``cache_key`` the batches are kept in host memory
-        under that identity, so later passes (``eval_from_cache``) need no Target."""
-        keys, kept = [], []
+    def eval_begin(self, cache_key: str = "") -> None:
+        self._eval = {"key": cache_key, "kept": [], "state": self.trainer.eval_begin()}
 
-        def batches():
-            for sample in self._samples(num_batches, timeout):
-                b = self._batch(sample)
-                keys.append(sample.feature_key)
-                if cache_key:
-                    kept.append({k: (v.detach().to("cpu", copy=True) if torch.is_tensor(v) else v) for k, v in b.items()})
-                yield b
-
-        metrics = self.trainer.eval_update(batches())
-        if cache_key:
-            self._eval_cache = {"key": cache_key, "batches": kept}
+    def eval_step(self, num_batches: int, timeout: float = 1800.0) -> dict:
+        """Held-out forward over ``num_batches`` ring samples; the leases are returned at once so that a small ring
+        suffices.  With a cache key the batches are kept in host memory for later passes."""
+        keys = []
+        ev = self._eval
+        for sample in self._samples(num_batches, timeout, evaluation=True):
+            b = self._batch(sample)
+            keys.append(sample.feature_key)
+            if ev["key"]:
+                ev["kept"].append({k: (v.detach().to("cpu", copy=True) if torch.is_tensor(v) else v) for k, v in b.items()})
+            self.trainer.eval_add(ev["state"], b)
+        if self.cuda:
+            torch.cuda.synchronize(self.device)            # the slots are reusable once the forward has read them
         releases = []
         for k in keys:
             d = FeatureDescriptor.from_key(k)
             releases.append((d.consumer, d.slot, d.generation))
-        return {"metrics": metrics, "releases": releases, "cached": len(kept)}
+        return {"releases": releases}
+
+    def eval_end(self) -> dict:
+        ev = self._eval
+        metrics = self.trainer.eval_end(ev["state"])
+        if ev["key"]:
+            self._eval_cache = {"key": ev["key"], "batches": ev["kept"]}
+        self._eval = None
+        return {"metrics": metrics, "cached": len(ev["kept"])}
 
     def eval_from_cache(self, cache_key: str) -> dict:
         cache = getattr(self, "_eval_cache", None)
         if not cache or cache["key"] != cache_key:
             return {"metrics": {}, "miss": True}
-        return {"metrics": self.trainer.eval_update(iter(cache["batches"])), "miss": False}
+        state = self.trainer.eval_begin()
+        for b in cache["batches"]:
+            self.trainer.eval_add(state, b)
+        return {"metrics": self.trainer.eval_end(state), "miss": False}
 
     # -- checkpoints --------------------------------------------------------------------------------
     def topology(self) -> dict:
