@@ -220,3 +220,43 @@ def vocab_parallel_head_loss(head: VocabParallelHead, hidden, lm_w_shard, labels
         teacher_hidden.contiguous() if teacher_hidden is not None else None,
         t_index.to(torch.int32).contiguous() if t_index is not None else None, labels.long().contiguous(),
         weight.float().contiguous(), float(a_ce), float(a_l1), holder)
+
+
+def vocab_parallel_head_loss_reference(hidden, lm_w_shard, labels, weight, *, vocab_offset: int, group=None, prev_emb=None,
+                                       markov_w2_shard=None, teacher_hidden=None, t_index=None, a_ce=1.0, a_l1=0.0):
+    """Reference-math statement of the sharded head on any backend (fp32, differentiable collectives): every rank holds
+    rows ``[vocab_offset, vocab_offset + V/p)`` of the head; normalisers are merged with an all-gather of the partial
+    log-sum-exps, the CE target logit and the L1 partial sums with all-reduces.  Returns ``(numerator, ce, l1)`` like
+    ``ops.vocab_head.head_loss_reference`` (the numerator is this rank's share: sum the ranks' numerators, or
+    all-reduce gradients, exactly as for the kernel path)."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    from aspec_b200.parallel.cp_runtime import _AllGatherStack
+
+    def global_lse(local_logits):
+        part = torch.logsumexp(local_logits, -1)
+        return torch.logsumexp(_AllGatherStack.apply(part, group), 0)
+
+    def all_sum(x):
+        return _AllGatherStack.apply(x, group).sum(0)
+
+    logits = F.linear(hidden.float(), lm_w_shard.float())
+    if prev_emb is not None:
+        logits = logits + F.linear(prev_emb.float(), markov_w2_shard.float())
+    lse = global_lse(logits)
+    local = labels.long() - vocab_offset
+    mine = (local >= 0) & (local < logits.shape[1])
+    picked = logits.gather(1, local.clamp(0, logits.shape[1] - 1)[:, None])[:, 0]
+    ce = lse - all_sum(torch.where(mine, picked, torch.zeros_like(picked)))
+    l1 = torch.zeros_like(ce)
+    if teacher_hidden is not None:
+        t = F.linear(teacher_hidden.float(), lm_w_shard.float())
+        if t_index is not None:
+            t = t[t_index.long()]
+        q = torch.exp(t - global_lse(t)[:, None])
+        p = torch.exp(logits - lse[:, None])
+        l1 = all_sum((p - q).abs().sum(-1))
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    num = (weight.float() * (a_ce * ce + a_l1 * l1)).sum() / world       # every rank holds the same rows
+    return num, ce.detach(), l1.detach()
