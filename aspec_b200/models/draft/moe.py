@@ -40,6 +40,10 @@ class ExpertBank(nn.Module):
 
     def forward(self, x_sorted: torch.Tensor, counts: List[int]) -> torch.Tensor:
         """``x_sorted [N, D]`` grouped by local expert, ``counts[e]`` rows each -> ``[N, D]``."""
+        if (x_sorted.is_cuda and x_sorted.dtype == torch.bfloat16 and self.gate_up_proj.dtype == torch.bfloat16 and x_sorted.shape[0]
+                and x_sorted.shape[1] % 64 == 0 and self.intermediate_size % 64 == 0):
+            from aspec_b200.ops.grouped_gemm import grouped_experts
+            return grouped_experts(x_sorted, self.gate_up_proj, self.down_proj, counts, self.clamp)
         outs = []
         off = 0
         for e, n in enumerate(counts):

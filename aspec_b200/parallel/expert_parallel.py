@@ -61,6 +61,8 @@ class EPWorkspace:
         n = -(-n // 256) * 256
         self.buffer = buffer if buffer is not None else SymmetricBuffer.allocate(4 * n, device)
         raw = self.buffer.tensor
+        if buffer is None:
+            raw.zero_()          # rows past a run's end are read (and masked or multiplied by zero): keep them finite
         view = lambda i: raw[i * n: i * n + max_rows * hidden * 2].view(torch.bfloat16).view(max_rows, hidden)
         self.x, self.y, self.dy, self.dx = view(0), view(1), view(2), view(3)
 
@@ -79,7 +81,8 @@ class FusedExpertParallel:
     Every rank sorts its routed tokens by global expert into its peer-visible ``x``.  The owner of expert ``e`` then
     runs, per source rank ``s``, the gate/up GEMM with its A operand read by TMA straight from ``x_s`` (the dispatch)
     and the down GEMM with its output stored straight into ``y_s`` (the combine): no staging copy, no collective,
-    and the transfer overlaps the math tile by tile inside the GEMM pipelines.  Only the ``[ranks, experts]`` count
+    and the transfer overlaps the math tile by tile inside the GEMM pipelines.  All (source, expert) pairs of a
+    phase run as one grouped launch (``ops/grouped_gemm.py``).  Only the ``[ranks, experts]`` count
     matrix is exchanged beforehand (the same host-side split sizes the all-to-all baseline needs).
     The backward pass mirrors it: ``dy`` rows are pulled from the source, ``dx`` rows are pushed back, weight gradients
     stay local.  Phases are separate methods so several ranks can be emulated in one process.
@@ -99,27 +102,36 @@ class FusedExpertParallel:
         self._n = x_sorted.shape[0]
         self.mine.x[: self._n].copy_(x_sorted)
 
+    def _problems(self, count_matrix):
+        """Runs of rows this rank's experts own, as parallel arrays: source rank, local expert, row offset in the
+        source's sorted buffer, row count, row offset in this rank's padded staging layout."""
+        import numpy as np
+        from aspec_b200.ops.grouped_gemm import padded_offsets
+        counts = np.asarray(count_matrix, dtype=np.int64)                    # [ranks, experts]
+        offs = np.cumsum(counts, 1) - counts
+        mine = slice(self.rank * self.local, (self.rank + 1) * self.local)
+        src = np.repeat(np.arange(self.world), self.local)
+        le = np.tile(np.arange(self.local), self.world)
+        rows = counts[:, mine].reshape(-1)
+        row0 = offs[:, mine].reshape(-1)
+        pstart, ptotal = padded_offsets(rows)
+        return src, le, row0, rows, pstart, ptotal
+
     def run_experts(self, count_matrix, gate_up: torch.Tensor, down: torch.Tensor, clamp: float = 0.0) -> None:
         """``count_matrix[s][e]``: rows rank ``s`` routed to global expert ``e`` (host ints).  ``gate_up [E_local, 2I, D]``,
-        ``down [E_local, D, I]``.  Keeps the activations needed by the backward pass."""
-        from aspec_b200.ops import gemm as G
+        ``down [E_local, D, I]``.  Two grouped launches: the gate/up GEMM reads its A rows by TMA straight from every
+        source rank's ``x`` (the dispatch), the down GEMM stores its rows straight into every source rank's ``y``
+        (the combine).  Keeps the activations needed by the backward pass."""
+        import numpy as np
         from aspec_b200.ops.activation import swiglu
-        self._counts = [list(map(int, row)) for row in count_matrix]
-        self._saved = []
-        for s in range(self.world):
-            offs = [0]
-            for c in self._counts[s]:
-                offs.append(offs[-1] + c)
-            for le in range(self.local):
-                e = self.rank * self.local + le
-                n, o = self._counts[s][e], offs[e]
-                if n == 0:
-                    continue
-                xs = self.ws[s].x[o:o + n]                               # peer rows: the GEMM's TMA loads are the dispatch
-                gu = G.gemm(xs, gate_up[le])
-                act = swiglu(gu.detach(), clamp)
-                G.gemm(act, down[le], out=self.ws[s].y[o:o + n])       # epilogue stores are the combine
-                self._saved.append((s, le, o, n, gu, act))
+        from aspec_b200.ops.grouped_gemm import rows_gemm
+        src, le, row0, rows, pstart, ptotal = self._problems(count_matrix)
+        zeros = np.zeros_like(src)
+        gu = torch.zeros(ptotal, gate_up.shape[1], dtype=gate_up.dtype, device=gate_up.device)
+        rows_gemm([w.x for w in self.ws], gate_up, [gu], src=src, a_row=row0, rows=rows, expert=le, dst=zeros, out_row=pstart)
+        act = swiglu(gu, clamp)
+        rows_gemm([act], down, [w.y for w in self.ws], src=zeros, a_row=pstart, rows=rows, expert=le, dst=src, out_row=row0)
+        self._saved = (src, le, row0, rows, pstart, ptotal, gu, act)
 
     def collect(self) -> torch.Tensor:
         return self.mine.y[: self._n]
@@ -129,20 +141,25 @@ class FusedExpertParallel:
         self.mine.dy[: self._n].copy_(dy_sorted)
 
     def run_experts_backward(self, gate_up: torch.Tensor, down: torch.Tensor, clamp: float = 0.0):
-        """Returns ``(d gate_up, d down)`` of the local experts (fp32); pushes ``dx`` rows back to their sources."""
-        from aspec_b200.ops import gemm as G
+        """Returns ``(d gate_up, d down)`` of the local experts (fp32); pushes ``dx`` rows back to their sources.
+        Five grouped launches: ``dy`` rows are pulled from the sources, weight gradients reduce over every source's rows
+        inside one accumulator per output tile, ``dx`` rows are stored into the sources' buffers."""
+        import numpy as np
         from aspec_b200.ops.activation import swiglu_backward
-        d_gu = torch.zeros(gate_up.shape, dtype=torch.float32, device=gate_up.device)
-        d_dn = torch.zeros(down.shape, dtype=torch.float32, device=down.device)
-        for s, le, o, n, gu, act in self._saved:
-            dys = self.ws[s].dy[o:o + n]                                 # pulled from the source rank
-            d_act = G.gemm(dys, down[le], b_t=True)                      # [n, I]
-            G.gemm(dys, act, a_t=True, b_t=True, out=d_dn[le], addend=d_dn[le], out_dtype=torch.float32)
-            d_gu_rows = swiglu_backward(gu, d_act, clamp)                # [n, 2I]
-            xs = self.ws[s].x[o:o + n]
-            G.gemm(d_gu_rows, xs, a_t=True, b_t=True, out=d_gu[le], addend=d_gu[le], out_dtype=torch.float32)
-            G.gemm(d_gu_rows, gate_up[le], b_t=True, out=self.ws[s].dx[o:o + n])   # pushed back to the source
-        self._saved = []
+        from aspec_b200.ops.grouped_gemm import rows_gemm, wgrad_gemm
+        src, le, row0, rows, pstart, ptotal, gu, act = self._saved
+        zeros = np.zeros_like(src)
+        dys, xs = [w.dy for w in self.ws], [w.x for w in self.ws]
+        d_act = torch.zeros(ptotal, down.shape[2], dtype=down.dtype, device=down.device)
+        rows_gemm(dys, down, [d_act], src=src, a_row=row0, rows=rows, expert=le, dst=zeros, out_row=pstart, b_t=True)
+        d_gu_rows = swiglu_backward(gu, d_act, clamp)                              # zero padding rows stay zero
+        d_dn = torch.empty(down.shape, dtype=torch.float32, device=down.device)
+        wgrad_gemm(dys, [act], d_dn, expert=le, a_src=src, a_row=row0, b_src=zeros, b_row=pstart, rows=rows)
+        d_gu = torch.empty(gate_up.shape, dtype=torch.float32, device=gate_up.device)
+        wgrad_gemm([d_gu_rows], xs, d_gu, expert=le, a_src=zeros, a_row=pstart, b_src=src, b_row=row0, rows=rows)
+        rows_gemm([d_gu_rows], gate_up, [w.dx for w in self.ws], src=zeros, a_row=pstart, rows=rows, expert=le, dst=src,
+                  out_row=row0, b_t=True)
+        self._saved = None
         return d_gu, d_dn
 
     def collect_grad(self) -> torch.Tensor:
