@@ -2,7 +2,7 @@
 
 Each case launches its kernel a few times on inputs larger than the 126 MB L2 but well under a few GB, so
 that ``ncu --set full -k regex:<kernel> -c 1..3`` finishes in about a minute.  Cases: ``gemm``, ``gemm_head``,
-``attn_fwd``, ``attn_bwd``, ``vocab_loss``, ``rmsnorm``.
+``attn_fwd``, ``attn_bwd``, ``vocab_loss``, ``rmsnorm``, ``grouped_experts``.
 """
 from __future__ import annotations
 
@@ -55,6 +55,16 @@ def case_attn_bwd():
     do = torch.randn_like(out)
     for _ in range(2):
         A.backward(q, k, v, iv, out, lse, do, 128 ** -0.5)
+
+
+def case_grouped_experts():
+    from aspec_b200.ops.grouped_gemm import grouped_experts
+    E, D, I, N = 64, 2048, 1024, 32768
+    g = torch.Generator().manual_seed(0)
+    counts = torch.bincount(torch.randint(0, E, (N,), generator=g), minlength=E).tolist()
+    x, gu, dn = _bf16(N, D, scale=1.0), _bf16(E, 2 * I, D), _bf16(E, D, I)
+    for _ in range(3):
+        grouped_experts(x, gu, dn, counts)
 
 
 def case_vocab_loss():

@@ -104,6 +104,7 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
                 for r in range(world)]
     engines: list = []
     manager = None
+    failed = False
     try:
         for t in trainers:
             t.wait_ready()
@@ -161,12 +162,23 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
         summary["engines"] = [e.call("get_status", timeout=30) if isinstance(e, ProcessActor) else e.get_status()
                               for e in engines]
         return summary
+    except BaseException:
+        failed = True
+        raise
     finally:
+        # Ownership fence: engine processes store into rings that live in the trainers' memory, so engines are
+        # stopped and observed dead before any trainer (the owner of that memory) is allowed to exit.
+        from aspec_b200.owner_fence import SourceFence
         if manager is not None:
             manager.stop()
-        for a in list(engines) + trainers:
-            if isinstance(a, ProcessActor):
-                a.shutdown(timeout=5.0)
+        fence = SourceFence(grace_seconds=5.0, hold_seconds=float(flat.get("fence_hold_seconds", 60.0)),
+                            log=lambda msg: print(msg, flush=True))
+        for e in engines:
+            if isinstance(e, ProcessActor):
+                fence.add_accessor(e)
+        for t in trainers:
+            fence.add_owner(t)
+        fence.close(failed=failed)
 
 
 def main(argv=None) -> int:
