@@ -34,6 +34,8 @@ class DatasetConfig:
     eval_data_path: Optional[str] = None
     eval_interval: int = 50
     eval_cache_idle_timeout_seconds: float = 300.0
+    eval_decode_anchors_per_doc: int = 0          # > 0: block proposals of the live Draft on the held-out rows (tau) at every evaluation
+    eval_num_documents: int = 32                  # rows of the synthetic held-out split
     eval_micro_batch_size: Optional[int] = None
     eval_prompt_key: Optional[str] = None
     last_turn_loss_only: Any = "auto"

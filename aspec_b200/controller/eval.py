@@ -22,12 +22,13 @@ def eval_cache_identity(fingerprint: str, contract_id: str, args: Dict[str, Any]
 class EvalRunner:
     def __init__(self, *, controller, manager, trainers, rings, train_queues, args: Dict[str, Any], layer_ids,
                  contract_id: str = "", consumer_of_rank: Optional[Callable[[int], List[int]]] = None, metric: str = "eval/avg_loss",
-                 higher_is_better: bool = False):
+                 higher_is_better: bool = False, decode_anchors_per_doc: int = 0):
         self.controller, self.manager, self.trainers, self.rings, self.queues = controller, manager, trainers, rings, train_queues
         self.args, self.layer_ids = args, layer_ids
         self.consumer_of_rank = consumer_of_rank or (lambda r: [r])
         self.identity = eval_cache_identity(controller.dataset_fingerprint(), contract_id, args)
         self.metric, self.higher = metric, higher_is_better
+        self.decode_anchors = int(decode_anchors_per_doc)
         self.cached = False
         self.history: List[dict] = []
         self.best: Optional[dict] = None
@@ -81,6 +82,12 @@ class EvalRunner:
             finally:
                 self.manager.on_result = prev
         metrics = dict(outs[0]["metrics"])
+        if self.decode_anchors > 0 and self.cached:
+            # train-with-decode: block proposals of the live weights on the cached held-out rows (rank 0's share)
+            dec = self.trainers[0].call("decode_from_cache", self.identity, self.decode_anchors, timeout=3600).get("decode")
+            if dec and dec.get("proposals"):
+                metrics.update({"eval/decode_tau": dec["tau"], "eval/decode_fully_accepted": dec["fully_accepted_share"],
+                                "eval/decode_proposals": dec["proposals"]})
         record = {"step": step, "seconds": round(time.perf_counter() - t0, 3), "from_cache": bool(self.cached and self.history),
                   "metrics": metrics, "checkpoint": checkpoint}
         self.history.append(record)

@@ -73,6 +73,27 @@ class BlockDraftConsumer:
         self.backbone = DFlashModel(draft_model, block_size=block_size, num_anchors=1)
 
     @torch.no_grad()
+    def update_weights_from_disk(self, asset_dir) -> dict:
+        """Hot reload: validate a newer export of the same architecture and copy its tensors into the live modules in
+        place, so compiled graphs, buffers and references held by a decode loop stay valid (the reference asks its
+        serving engine for the same thing, aspec/inference/engine/sgl_engine_decode.py:39-424)."""
+        from safetensors.torch import load_file
+        asset_dir = Path(asset_dir)
+        manifest = validate_native_asset(asset_dir)
+        if manifest["algorithm"] != self.algorithm:
+            raise ValueError("the new asset was trained with a different algorithm")
+        tensors = load_file(str(asset_dir / "model.safetensors"))
+        state = self.model.state_dict()
+        if set(tensors) != set(state):
+            raise ValueError("the new asset's tensor names differ from the loaded Draft")
+        for name, t in tensors.items():
+            if tuple(t.shape) != tuple(state[name].shape):
+                raise ValueError(f"shape of {name} changed: {tuple(state[name].shape)} -> {tuple(t.shape)}")
+        for name, t in tensors.items():
+            state[name].copy_(t.to(state[name].device, state[name].dtype))
+        return manifest
+
+    @torch.no_grad()
     def propose(self, input_ids, target_features, *, lm_head_weight) -> dict:
         if input_ids.ndim != 2 or input_ids.shape[0] != 1 or input_ids.shape[1] < 1:
             raise ValueError("Block proposal currently consumes one nonempty prefix")

@@ -145,7 +145,8 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
             eval_controller = TrainingController(eval_args, dp_size=dp, consumers_per_row=cp, algorithm=algorithm)
             eval_controller.load_dataset(None)
             runner = EvalRunner(controller=eval_controller, manager=manager, trainers=trainers, rings=rings, train_queues=queues,
-                                args=args, layer_ids=layer_ids, consumer_of_rank=consumer_of_rank)
+                                args=args, layer_ids=layer_ids, consumer_of_rank=consumer_of_rank,
+                                decode_anchors_per_doc=int(flat.get("eval_decode_anchors_per_doc") or 0))
             interval = int(flat["eval_interval"])
 
             def on_step(next_step: int, metrics: dict) -> None:

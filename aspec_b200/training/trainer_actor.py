@@ -237,6 +237,42 @@ class TrainerActor:
             self.trainer.eval_add(state, b)
         return {"metrics": self.trainer.eval_end(state), "miss": False}
 
+    def decode_from_cache(self, cache_key: str, anchors_per_doc: int = 8, max_docs: int = 64) -> dict:
+        """Train-with-decode: block proposals of the live Draft weights (no export, no reload) on the cached held-out
+        rows, verified greedily against each document's continuation - mean accepted length tau during training
+        (the reference drives a serving engine's speculative decode from the trainer for the same number,
+        aspec/inference/engine/sgl_engine_decode.py:39-424)."""
+        cache = getattr(self, "_eval_cache", None)
+        if not cache or cache["key"] != cache_key:
+            return {"miss": True}
+        from aspec_b200.commands.evaluate_draft import evaluate
+        from aspec_b200.draft_artifact import BlockDraftConsumer
+        draft = self.model.draft_model
+        was_training = draft.training
+        if getattr(self.model, "vocab_parallel", None) is not None:
+            return {"unsupported": "the output head is sharded over a vocabulary-parallel group"}
+        try:
+            consumer = BlockDraftConsumer(draft, block_size=int(self.model.block_size))
+        except ValueError as exc:
+            return {"unsupported": str(exc)}
+        docs = []
+        for b in cache["batches"]:
+            ids, feats = b["input_ids"][0], b["hidden_states"][0]
+            lens = b.get("packed_document_lengths") or (ids.numel(),)
+            off = 0
+            for n in lens:
+                docs.append({"input_ids": ids[off:off + n], "features": feats[off:off + n]})
+                off += n
+        docs = docs[:max_docs]
+        dtype = next(draft.parameters()).dtype
+        try:
+            res = evaluate(consumer, self.lm_head, docs,
+                           lambda d: d["features"][None].to(self.device, dtype), anchors_per_doc=anchors_per_doc,
+                           seed=int(self.args.get("seed", 0)))
+        finally:
+            draft.train(was_training)
+        return {"decode": res, "miss": False}
+
     # -- checkpoints --------------------------------------------------------------------------------
     def topology(self) -> dict:
         return ckpt.logical_training_topology({**self.args, "world_size": self.world}, self.draft_config)

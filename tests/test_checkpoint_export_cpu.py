@@ -93,6 +93,20 @@ def test_train_resume_export_propose(tmp_path):
     ids = torch.randint(0, 120, (1, 20))
     res = consumer.propose(ids, torch.randn(1, 20, 96), lm_head_weight=head)
     assert res["token_ids"].shape == (1, 4) and res["draft_confidence_logits"].shape == (1, 4)
+    # hot reload: the same modules, new values; a proposal afterwards equals one from a freshly loaded consumer
+    params_before = {n: p.data_ptr() for n, p in consumer.model.named_parameters()}
+    with torch.no_grad():
+        for p in consumer.model.parameters():
+            p.add_(0.5)
+    drifted = consumer.propose(ids, torch.randn(1, 20, 96, generator=torch.Generator().manual_seed(5)), lm_head_weight=head)
+    consumer.update_weights_from_disk(native)
+    assert {n: p.data_ptr() for n, p in consumer.model.named_parameters()} == params_before
+    feats = torch.randn(1, 20, 96, generator=torch.Generator().manual_seed(5))
+    fresh = BlockDraftConsumer(load_native_draft(native)[0], block_size=4).propose(ids, feats, lm_head_weight=head)
+    again = consumer.propose(ids, feats, lm_head_weight=head)
+    assert torch.equal(again["token_ids"], fresh["token_ids"])
+    assert torch.allclose(again["draft_confidence_logits"], fresh["draft_confidence_logits"])
+    del drifted
     cfgp = native / "config.json"
     cfgp.write_text(cfgp.read_text() + " ")
     with pytest.raises(ValueError):

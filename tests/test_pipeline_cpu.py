@@ -138,12 +138,15 @@ def test_context_parallel_trainers_share_rows(tmp_path):
 def test_held_out_evaluation_runs_and_replays_from_the_trainer_cache(tmp_path):
     plan = _plan(tmp_path, ["dataset.eval_data_path=synthetic", "dataset.eval_interval=1"])
     flat = plan.to_runtime_args()
-    flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=0, save_final_checkpoint=False, eval_num_documents=8)
+    flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=0, save_final_checkpoint=False, eval_num_documents=8,
+                eval_decode_anchors_per_doc=2)
     os.makedirs(flat["output_dir"], exist_ok=True)
     logs = []
     summary = train_async_no_generation(flat, plan.draft_config, log=logs.append)
     evals = summary["evaluation"]
     assert [e["step"] for e in evals] == [1, 2, 3] and all(e["eval/avg_loss"] > 0 for e in evals)
+    # train-with-decode: proposals of the live weights on the cached rows, at every evaluation
+    assert all(e["eval/decode_proposals"] > 0 and 1.0 <= e["eval/decode_tau"] <= 7.0 for e in evals)
     record = json.load(open(os.path.join(flat["output_dir"], "evaluation.json")))
     assert [h["from_cache"] for h in record["history"]] == [False, True, True]      # the Target served the eval split once
     assert record["best"]["metric"] == "eval/avg_loss"
