@@ -41,7 +41,8 @@ static constexpr int kThreads = 192;   // warp0 TMA, warp1 MMA, warps 2..5 epilo
 static constexpr int kATileBytes = BM * BK * 2;
 static constexpr int kBTileBytes = BN * BK * 2;
 static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+static constexpr int kStoreStageBytes = 4 * 32 * 256;  // per epilogue warp: 32 rows x 128 bf16 columns, for row-contiguous stores
+static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kStoreStageBytes;
 
 enum { EPI_STORE = 0, EPI_ROWSTATS = 1, EPI_SWIGLU = 2 };
 
@@ -361,8 +362,72 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
         }
       } else {
         const float alpha = p.alpha;
+        // Tiles that also go to other destinations (peer memory over NVLink) are transposed through shared memory so
+        // that every store instruction writes two whole 256-byte row segments instead of 32 scattered 16-byte pieces:
+        // a link carries full sectors only when a warp's stores are contiguous.
+        const bool staged = p.n_mirrors > 0 && !p.d_is_fp32 && !partial && col0 + BN <= p.N;
+        if (staged) {
+          uint8_t* stg = smem + kStages * kStageBytes + 256 + q * (32 * 256);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+            for (int cc = 0; cc < 4; ++cc) {
+              uint32_t r[32];
+              const int c = half * 128 + cc * 32;
+              tmem_ld_32x32(t_row + c, r);
+              tmem_ld_wait();
+              const __nv_bfloat16* crow =
+                  (p.C && row_ok) ? reinterpret_cast<const __nv_bfloat16*>(p.C) + (long long)row * p.ldd + col0 + c : nullptr;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * i + j]) * alpha;
+                if (crow) {
+                  const uint4 cv = reinterpret_cast<const uint4*>(crow)[i];
+                  const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&cv);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 f = __bfloat1622float2(c2[j]);
+                    v[2 * j] += f.x;
+                    v[2 * j + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+                const int chunk = cc * 4 + i;  // 16-byte piece of this lane's 256-byte row segment, XOR-swizzled
+                *reinterpret_cast<uint4*>(stg + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+              }
+            }
+            __syncwarp();
+#pragma unroll 1
+            for (int r2 = 0; r2 < 16; ++r2) {
+              const int rr = 2 * r2 + (lane >> 4);
+              const int ch = lane & 15;
+              const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((ch ^ (rr & 15)) << 4));
+              const int grow = mt * BM + q * 32 + rr;
+              if (grow < p.M) {
+                const int gcol = col0 + half * 128 + ch * 8;
+                if (p.mirror_cols > 0) {
+                  const int dst = gcol / p.mirror_cols;
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[dst]) +
+                                            (long long)grow * p.mirror_ld[dst] + (gcol - dst * p.mirror_cols)) = o;
+                } else {
+                  *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)grow * p.ldd + gcol) = o;
+                  for (int m = 0; m < p.n_mirrors; ++m)
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.mirror[m]) +
+                                              (long long)grow * p.mirror_ld[m] + gcol) = o;
+                }
+              }
+            }
+            __syncwarp();
+          }
+        }
+#pragma unroll 1
+        for (int c = staged ? BN : 0; c < BN; c += 32) {
           uint32_t r[32];
           tmem_ld_32x32(t_row + c, r);
           tmem_ld_wait();

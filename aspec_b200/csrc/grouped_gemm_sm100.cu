@@ -40,7 +40,8 @@ static constexpr int kThreads = 192;  // warp0 TMA, warp1 MMA, warps 2..5 epilog
 static constexpr int kATileBytes = BM * BK * 2;
 static constexpr int kBTileBytes = BN * BK * 2;
 static constexpr int kStageBytes = kATileBytes + kBTileBytes;
-static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+static constexpr int kStoreStageBytes = 4 * 32 * 256;  // per epilogue warp: 32 rows x 128 bf16 columns
+static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kStoreStageBytes;
 static constexpr int kMaxMaps = 12;
 
 struct alignas(16) GTile {
@@ -198,8 +199,46 @@ grouped_gemm_kernel(const __grid_constant__ GMaps maps, const GParams p) {
       // a tile without segments (an expert that received no rows) stores zeros
       const bool has = tile.nseg > 0;
       auto val = [&](uint32_t bits) { return has ? __uint_as_float(bits) * alpha : 0.f; };
+      // Full-width bf16 tiles (the destination may be a peer GPU's memory) are transposed through shared memory so that
+      // each store instruction writes two whole 256-byte row segments.
+      const bool staged = !p.d_is_fp32 && tile.cols == BN && (tile.ldd & 7) == 0 &&
+                          (reinterpret_cast<uintptr_t>(tile.d) & 15) == 0;
+      if (staged) {
+        uint8_t* stg = smem + kStages * kStageBytes + 256 + q * (32 * 256);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + half * 128 + cc * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 o;
+              o.x = pack_bf16x2(val(r[8 * i]), val(r[8 * i + 1]));
+              o.y = pack_bf16x2(val(r[8 * i + 2]), val(r[8 * i + 3]));
+              o.z = pack_bf16x2(val(r[8 * i + 4]), val(r[8 * i + 5]));
+              o.w = pack_bf16x2(val(r[8 * i + 6]), val(r[8 * i + 7]));
+              const int chunk = cc * 4 + i;
+              *reinterpret_cast<uint4*>(stg + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
+            }
+          }
+          __syncwarp();
+#pragma unroll 1
+          for (int r2 = 0; r2 < 16; ++r2) {
+            const int rr = 2 * r2 + (lane >> 4);
+            const int ch = lane & 15;
+            const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((ch ^ (rr & 15)) << 4));
+            const int trow = q * 32 + rr;
+            if (trow < tile.rows)
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(tile.d) + (long long)trow * tile.ldd +
+                                        half * 128 + ch * 8) = o;
+          }
+          __syncwarp();
+        }
+      }
+#pragma unroll 1
+      for (int c = staged ? BN : 0; c < BN; c += 32) {
         const int ncol = tile.cols - c;
         if (ncol <= 0) break;               // uniform over the CTA
         uint32_t r[32];

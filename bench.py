@@ -128,9 +128,25 @@ def make_pool(args, cfg, model, rank, n_docs, pin):
     import torch
     from aspec_b200.data.synthetic import SyntheticSpec, make_document, synthetic_features
     spec = SyntheticSpec(vocab_size=cfg.vocab_size - 1024, min_len=min(args.min_len, args.max_len), max_len=args.max_len, seed=17)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rows = list(range(n_docs))
+    if world > 1:
+        # Data-parallel ranks draw from one global stream that is dealt the way the training controller deals it
+        # (controller/training_controller.py, length_group_size): documents are sorted by length inside a group and
+        # consecutive ones go to different ranks, so every micro-step has similar lengths on all ranks and no rank
+        # waits for another's longer documents.  The micro-step order is then shuffled identically on every rank.
+        import random
+        total = n_docs * world
+        lengths = [make_document(spec, r)["seq_len"] for r in range(total)]
+        group = 32 * world
+        order = []
+        for c in range(0, total, group):
+            order += sorted(range(c, min(c + group, total)), key=lambda j: -lengths[j])
+        steps = list(range(n_docs))
+        random.Random(5).shuffle(steps)
+        rows = [order[m * world + (rank if m % 2 == 0 else world - 1 - rank)] for m in steps]      # serpentine
     pool = []
-    for i in range(n_docs):
-        row = rank * 100003 + i
+    for row in rows:
         doc = make_document(spec, row)
         T = doc["seq_len"]
         feats = synthetic_features(T, cfg.num_target_layers, cfg.target_hidden_size, row, pin=pin)
@@ -245,7 +261,8 @@ def run_ours(args):
             "config": {"model": f"Qwen3-8B-shaped DSpark draft, {args.layers} layer(s), {args.target_layers} captured layers, vocab {cfg.vocab_size}",
                        "global_batch": args.accum * world, "seq_len": args.max_len,
                        "doc_lengths": f"log-uniform [{args.min_len},{args.max_len}]",
-                       "parallelism": f"dp{world}" + ("+full_shard" if args.fsdp else ""), "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,
+                       "parallelism": f"dp{world}" + ("+full_shard" if args.fsdp else ""),
+                       "dp_balance": "length-grouped deal across ranks (group 32)" if world > 1 else "n/a", "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,
                        "block_size": model.block_size,
                        "l2_policy": "inputs larger than L2 (1.2 GB lm_head + per-document features stream from HBM every micro-batch)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours",

@@ -100,3 +100,38 @@ def test_gemm_stream_k(M, N, K):
     assert (out32 - ref).abs().max().item() < tol
     assert (out16.float() - ref).abs().max().item() < tol + 0.05
     assert (acc - 1 - ref).abs().max().item() < tol
+
+
+@pytest.mark.parametrize("M,N", [(300, 768), (257, 600)])
+def test_gemm_mirrored_stores_match_the_primary_output(M, N):
+    """Broadcast mirrors (with a residual addend): whole tiles take the shared-memory transposed store path, the
+    ragged last column tile the per-thread path; rows past M are never written."""
+    from aspec_b200.ops import gemm as G
+    K = 192
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    mirrors = [torch.full((M + 5, N + 8), 9.0, device="cuda", dtype=torch.bfloat16)[:M, :N] for _ in range(3)]
+    G.gemm(a, b, out=out, addend=res, mirrors=mirrors)
+    G.check_status("cuda")
+    ref = a.float() @ b.float().t() + res.float()
+    assert torch.allclose(out.float(), ref, atol=0.15, rtol=0.02)
+    for m in mirrors:
+        assert torch.equal(m, out)
+        base = m._base if m._base is not None else m
+        assert torch.all(base[M:] == 9.0) and torch.all(base[:, N:] == 9.0)
+
+
+def test_gemm_scatter_epilogue_splits_columns_over_destinations():
+    from aspec_b200.ops import gemm as G
+    M, K, per, n_dst = 200, 128, 256, 3
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(per * n_dst, K, device="cuda") * 0.5).bfloat16()
+    dsts = [torch.full((M + 3, per), 5.0, device="cuda", dtype=torch.bfloat16) for _ in range(n_dst)]
+    G.gemm(a, b, mirrors=[d[:M] for d in dsts], scatter_cols=per)
+    G.check_status("cuda")
+    ref = (a.float() @ b.float().t())
+    for i, d in enumerate(dsts):
+        assert torch.allclose(d[:M].float(), ref[:, i * per:(i + 1) * per], atol=0.1, rtol=0.02)
+        assert torch.all(d[M:] == 5.0)
