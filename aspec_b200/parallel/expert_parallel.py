@@ -78,10 +78,10 @@ class EPWorkspace:
 class FusedExpertParallel:
     """Expert-parallel MoE whose all-to-alls are the expert GEMMs' own memory traffic.
 
-    Every rank sorts its routed tokens by global expert into its peer-visible ``x``.  The owner of expert ``e`` then
-    runs, per source rank ``s``, the gate/up GEMM with its A operand read by TMA straight from ``x_s`` (the dispatch)
-    and the down GEMM with its output stored straight into ``y_s`` (the combine): no staging copy, no collective,
-    and the transfer overlaps the math tile by tile inside the GEMM pipelines.  All (source, expert) pairs of a
+    Every rank sorts its routed tokens by global expert into its peer-visible ``x``.  The owner of expert ``e`` pulls
+    the rows bound for it from every source's ``x`` once (the dispatch: each row crosses NVLink exactly once, no
+    split-size negotiation beyond the count matrix, no collective) and its down GEMM stores its output straight into
+    the source's ``y`` (the combine: the transfer is the epilogue's own stores, tile by tile).  All (source, expert) pairs of a
     phase run as one grouped launch (``ops/grouped_gemm.py``).  Only the ``[ranks, experts]`` count
     matrix is exchanged beforehand (the same host-side split sizes the all-to-all baseline needs).
     The backward pass mirrors it: ``dy`` rows are pulled from the source, ``dx`` rows are pushed back, weight gradients
@@ -103,8 +103,9 @@ class FusedExpertParallel:
         self.mine.x[: self._n].copy_(x_sorted)
 
     def _problems(self, count_matrix):
-        """Runs of rows this rank's experts own, as parallel arrays: source rank, local expert, row offset in the
-        source's sorted buffer, row count, row offset in this rank's padded staging layout."""
+        """Runs of rows this rank's experts own, as parallel arrays: source rank, local expert, row offset inside the
+        source's run for this rank, row count, row offset in this rank's padded staging layout; plus every source's
+        ``(first row, row count)`` of that run in its sorted buffer (this rank's experts are adjacent there)."""
         import numpy as np
         from aspec_b200.ops.grouped_gemm import padded_offsets
         counts = np.asarray(count_matrix, dtype=np.int64)                    # [ranks, experts]
@@ -113,25 +114,50 @@ class FusedExpertParallel:
         src = np.repeat(np.arange(self.world), self.local)
         le = np.tile(np.arange(self.local), self.world)
         rows = counts[:, mine].reshape(-1)
-        row0 = offs[:, mine].reshape(-1)
+        span0 = offs[:, self.rank * self.local]
+        span = counts[:, mine].sum(1)
+        row0 = (offs[:, mine] - span0[:, None]).reshape(-1)
         pstart, ptotal = padded_offsets(rows)
-        return src, le, row0, rows, pstart, ptotal
+        return src, le, row0, rows, pstart, ptotal, span0, span
+
+    def _pull(self, bufs, span0, span):
+        """Bring every source's rows for this rank's experts into local memory, once: a GEMM re-reads its A rows for
+        every column tile, and peer memory is not cached in this GPU's L2, so reading them in place would cross NVLink
+        once per column tile.  The rank's own rows are used where they are."""
+        import ctypes as C
+        from aspec_b200 import _native
+        out = []
+        for s, buf in enumerate(bufs):
+            view = buf[int(span0[s]): int(span0[s] + span[s])]
+            if s == self.rank or view.shape[0] == 0:
+                out.append(view if view.shape[0] else buf[:1])
+                continue
+            local = torch.empty(view.shape, dtype=view.dtype, device=view.device)
+            rc = _native.kernels().ab_copy_bytes(C.c_void_p(view.data_ptr()), C.c_void_p(local.data_ptr()),
+                                                 C.c_longlong(view.numel() * view.element_size()),
+                                                 C.c_void_p(torch.cuda.current_stream(view.device).cuda_stream))
+            if rc != 0:
+                raise RuntimeError(f"ab_copy_bytes refused the peer copy (code {rc})")
+            out.append(local)
+        return out
 
     def run_experts(self, count_matrix, gate_up: torch.Tensor, down: torch.Tensor, clamp: float = 0.0) -> None:
         """``count_matrix[s][e]``: rows rank ``s`` routed to global expert ``e`` (host ints).  ``gate_up [E_local, 2I, D]``,
-        ``down [E_local, D, I]``.  Two grouped launches: the gate/up GEMM reads its A rows by TMA straight from every
-        source rank's ``x`` (the dispatch), the down GEMM stores its rows straight into every source rank's ``y``
-        (the combine).  Keeps the activations needed by the backward pass."""
+        ``down [E_local, D, I]``.  The dispatch is one pull of each source's rows; the gate/up GEMM is one grouped
+        launch over all (source, expert) pairs; the down GEMM, again one grouped launch, stores its rows straight into
+        every source rank's ``y`` (the combine).  Keeps the activations needed by the backward pass."""
         import numpy as np
         from aspec_b200.ops.activation import swiglu
         from aspec_b200.ops.grouped_gemm import rows_gemm
-        src, le, row0, rows, pstart, ptotal = self._problems(count_matrix)
+        src, le, row0, rows, pstart, ptotal, span0, span = self._problems(count_matrix)
         zeros = np.zeros_like(src)
+        xs = self._pull([w.x for w in self.ws], span0, span)
         gu = torch.zeros(ptotal, gate_up.shape[1], dtype=gate_up.dtype, device=gate_up.device)
-        rows_gemm([w.x for w in self.ws], gate_up, [gu], src=src, a_row=row0, rows=rows, expert=le, dst=zeros, out_row=pstart)
+        rows_gemm(xs, gate_up, [gu], src=src, a_row=row0, rows=rows, expert=le, dst=zeros, out_row=pstart)
         act = swiglu(gu, clamp)
-        rows_gemm([act], down, [w.y for w in self.ws], src=zeros, a_row=pstart, rows=rows, expert=le, dst=src, out_row=row0)
-        self._saved = (src, le, row0, rows, pstart, ptotal, gu, act)
+        rows_gemm([act], down, [w.y for w in self.ws], src=zeros, a_row=pstart, rows=rows, expert=le, dst=src,
+                  out_row=row0 + span0[src])
+        self._saved = (src, le, row0, rows, pstart, ptotal, span0, span, xs, gu, act)
 
     def collect(self) -> torch.Tensor:
         return self.mine.y[: self._n]
@@ -142,14 +168,14 @@ class FusedExpertParallel:
 
     def run_experts_backward(self, gate_up: torch.Tensor, down: torch.Tensor, clamp: float = 0.0):
         """Returns ``(d gate_up, d down)`` of the local experts (fp32); pushes ``dx`` rows back to their sources.
-        Five grouped launches: ``dy`` rows are pulled from the sources, weight gradients reduce over every source's rows
+        ``dy`` rows are pulled once; five grouped launches follow: weight gradients reduce over every source's rows
         inside one accumulator per output tile, ``dx`` rows are stored into the sources' buffers."""
         import numpy as np
         from aspec_b200.ops.activation import swiglu_backward
         from aspec_b200.ops.grouped_gemm import rows_gemm, wgrad_gemm
-        src, le, row0, rows, pstart, ptotal, gu, act = self._saved
+        src, le, row0, rows, pstart, ptotal, span0, span, xs, gu, act = self._saved
         zeros = np.zeros_like(src)
-        dys, xs = [w.dy for w in self.ws], [w.x for w in self.ws]
+        dys = self._pull([w.dy for w in self.ws], span0, span)
         d_act = torch.zeros(ptotal, down.shape[2], dtype=down.dtype, device=down.device)
         rows_gemm(dys, down, [d_act], src=src, a_row=row0, rows=rows, expert=le, dst=zeros, out_row=pstart, b_t=True)
         d_gu_rows = swiglu_backward(gu, d_act, clamp)                              # zero padding rows stay zero
@@ -158,7 +184,7 @@ class FusedExpertParallel:
         d_gu = torch.empty(gate_up.shape, dtype=torch.float32, device=gate_up.device)
         wgrad_gemm([d_gu_rows], xs, d_gu, expert=le, a_src=zeros, a_row=pstart, b_src=src, b_row=row0, rows=rows)
         rows_gemm([d_gu_rows], gate_up, [w.dx for w in self.ws], src=zeros, a_row=pstart, rows=rows, expert=le, dst=src,
-                  out_row=row0, b_t=True)
+                  out_row=row0 + span0[src], b_t=True)
         self._saved = None
         return d_gu, d_dn
 

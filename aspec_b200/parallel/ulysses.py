@@ -85,6 +85,26 @@ class UlyssesExchange:
     def _rows(self, r: int) -> slice:
         return slice(r * self.mine.rows, (r + 1) * self.mine.rows)
 
+    def _pull(self, views: Sequence[torch.Tensor]) -> list:
+        """Local copies of the peers' row blocks (this rank's own block is used in place).  The consuming GEMMs re-read
+        their A rows once per column tile and peer memory is not cached in this GPU's L2, so each block crosses NVLink
+        once here instead of once per tile there."""
+        import ctypes as C
+        from aspec_b200 import _native
+        out = []
+        for g, v in enumerate(views):
+            if g == self.rank:
+                out.append(v)
+                continue
+            local = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+            rc = _native.kernels().ab_copy_bytes(C.c_void_p(v.data_ptr()), C.c_void_p(local.data_ptr()),
+                                                 C.c_longlong(v.numel() * v.element_size()),
+                                                 C.c_void_p(torch.cuda.current_stream(v.device).cuda_stream))
+            if rc != 0:
+                raise RuntimeError(f"ab_copy_bytes refused the peer copy (code {rc})")
+            out.append(local)
+        return out
+
     # -- forward ------------------------------------------------------------------------------------------
     def project_scatter(self, x: torch.Tensor, w_grouped: torch.Tensor) -> None:
         """``x [T_loc, D] @ W^T`` with each rank's column block stored into that rank's ``qkv`` rows of this rank."""
@@ -101,8 +121,8 @@ class UlyssesExchange:
     def output_projection(self, w_o: torch.Tensor) -> torch.Tensor:
         """``out[T_loc, D] = sum_g attn_g[my rows] @ W_o[:, cols_g]^T`` with ``attn_g`` read from rank ``g``."""
         c = self.mine.out_cols
-        return _multi_source([w.attn[self._rows(self.rank)] for w in self.ws],
-                             [w_o[:, g * c:(g + 1) * c] for g in range(self.world)])
+        self._attn_rows = self._pull([w.attn[self._rows(self.rank)] for w in self.ws])
+        return _multi_source(self._attn_rows, [w_o[:, g * c:(g + 1) * c] for g in range(self.world)])
 
     # -- backward -----------------------------------------------------------------------------------------
     def output_projection_backward(self, dout: torch.Tensor, w_o: torch.Tensor):
@@ -111,8 +131,9 @@ class UlyssesExchange:
         dests = [w.dattn[self._rows(self.rank)] for w in self.ws]
         G.gemm(dout, w_o, b_t=True, mirrors=dests, scatter_cols=self.mine.out_cols)
         c = self.mine.out_cols
-        parts = [G.gemm(dout, w.attn[self._rows(self.rank)], a_t=True, b_t=True, out_dtype=torch.float32, stream_k=False)
-                 for w in self.ws]
+        attn_rows = getattr(self, "_attn_rows", None) or self._pull([w.attn[self._rows(self.rank)] for w in self.ws])
+        self._attn_rows = None
+        parts = [G.gemm(dout, a, a_t=True, b_t=True, out_dtype=torch.float32, stream_k=False) for a in attn_rows]
         return torch.cat(parts, 1)                # [D, Hq*d] columns grouped by rank, as W_o's
 
     def received_dattn(self) -> torch.Tensor:
@@ -125,7 +146,7 @@ class UlyssesExchange:
         """``dx = sum_g dqkv_g[my rows] @ W_g`` and ``dW_g = dqkv_g[my rows]^T @ x`` with ``dqkv_g`` read from rank ``g``."""
         from aspec_b200.ops import gemm as G
         c = self.mine.qkv_cols
-        srcs = [w.dqkv[self._rows(self.rank)] for w in self.ws]
+        srcs = self._pull([w.dqkv[self._rows(self.rank)] for w in self.ws])
         dx = _multi_source(srcs, [w_grouped[g * c:(g + 1) * c] for g in range(self.world)], b_t=True)
         dw = torch.cat([G.gemm(s, x, a_t=True, b_t=True, out_dtype=torch.float32, stream_k=False) for s in srcs], 0)
         return dx, dw
