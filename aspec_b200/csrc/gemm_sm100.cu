@@ -101,28 +101,29 @@ struct Work {
   long long cur;
   int in_tail;
 };
-__device__ __forceinline__ Work work_begin(const GemmParams& p) {
+// `unit` / `units`: index and number of schedulers walking the tile space (CTAs, or CTA pairs).
+__device__ __forceinline__ Work work_begin(int unit) {
   Work w;
-  w.cur = blockIdx.x;
+  w.cur = unit;
   w.in_tail = 0;
   return w;
 }
-__device__ __forceinline__ bool next_work(const GemmParams& p, int total_tiles, int k_blocks, Work& w,
-                                          int& tile, int& kb0, int& kb1) {
+__device__ __forceinline__ bool next_work(const GemmParams& p, int total_tiles, int k_blocks, Work& w, int unit,
+                                          int units, int& tile, int& kb0, int& kb1) {
   const int full_tiles = p.stream_k ? p.full_tiles : total_tiles;
   if (!w.in_tail) {
     if (w.cur < full_tiles) {
       tile = (int)w.cur;
       kb0 = 0;
       kb1 = k_blocks;
-      w.cur += gridDim.x;
+      w.cur += units;
       return true;
     }
     if (!p.stream_k) return false;
     w.in_tail = 1;
-    w.cur = (long long)blockIdx.x * p.units_per_cta;
+    w.cur = (long long)unit * p.units_per_cta;
   }
-  long long end = ((long long)blockIdx.x + 1) * p.units_per_cta;
+  long long end = ((long long)unit + 1) * p.units_per_cta;
   const long long total = (long long)(total_tiles - full_tiles) * k_blocks;
   if (end > total) end = total;
   if (w.cur >= end) return false;
@@ -136,19 +137,32 @@ __device__ __forceinline__ bool next_work(const GemmParams& p, int total_tiles, 
   return true;
 }
 
-template <int A_MN, int B_MN, int EPI>
+// PAIR = 1: two CTAs of a cluster share every 256 x 256 output tile (tcgen05 cta_group::2).  Each stages its own
+// 128 rows of A and its own 128-column half of B (32 KB per k-block instead of 48 KB, six stages instead of four),
+// the even CTA issues the 256-row MMAs, each CTA keeps and drains its own 128 accumulator rows.  Barriers: tile
+// loads of both CTAs report their bytes to the even CTA's full barrier; the MMA thread commits to the empty and
+// accumulator-full barriers of both CTAs; the epilogue warps of both CTAs arrive on the even CTA's accumulator-empty
+// barrier.  No load requests cluster multicast.
+template <int A_MN, int B_MN, int EPI, int PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
+  constexpr int NS = PAIR ? 6 : kStages;                       // pipeline stages
+  constexpr int BN_LOAD = PAIR ? BN / 2 : BN;                  // B rows (output columns) staged by this CTA
+  constexpr int STAGE = kATileBytes + BN_LOAD * BK * 2;        // bytes per stage in this CTA
+  static_assert(NS * STAGE == kStages * kStageBytes, "both layouts fill the same shared-memory budget");
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128-byte swizzle atom (8 rows x 128 B).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  uint64_t* full_bar = bars;                       // [kStages]
-  uint64_t* empty_bar = bars + kStages;            // [kStages]
-  uint64_t* acc_full = bars + 2 * kStages;         // [kAccBufs]
-  uint64_t* acc_empty = bars + 2 * kStages + kAccBufs;  // [kAccBufs]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 2 * kAccBufs);
+  uint64_t* full_bar = bars;                  // [NS]
+  uint64_t* empty_bar = bars + NS;            // [NS]
+  uint64_t* acc_full = bars + 2 * NS;         // [kAccBufs]
+  uint64_t* acc_empty = bars + 2 * NS + kAccBufs;  // [kAccBufs]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NS + 2 * kAccBufs);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -158,24 +172,30 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
 
   if (threadIdx.x == 0) {
     *abort_word = 0;
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < NS; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < kAccBufs; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // one arrive per epilogue warp
+      mbar_init(&acc_empty[b], PAIR ? 8 : 4);  // one arrive per epilogue warp (of both CTAs of a pair)
     }
     fence_barrier_init();
     tma_prefetch_desc(&maps.a0);
     tma_prefetch_desc(&maps.b0);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the other CTA's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -185,58 +205,80 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       bool alive = true;
-      Work cursor = work_begin(p);
+      Work cursor = work_begin(unit);
       int tile, kb0, kb1;
-      while (alive && next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
+      while (alive && next_work(p, total_tiles, k_blocks, cursor, unit, units, tile, kb0, kb1)) {
         int mt, nt;
         tile_coords(tile, p.m_tiles, mt, nt);
+        const int row0 = (PAIR ? mt * 2 + (int)cta_rank : mt) * BM;       // this CTA's rows of A
+        const int col0 = nt * BN + (PAIR ? (int)cta_rank * BN_LOAD : 0);  // this CTA's rows of B
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word)) { alive = false; break; }
           const bool second = kb >= p.k_blocks0;
           const CUtensorMap* ma = second ? &maps.a1 : &maps.a0;
           const CUtensorMap* mb = second ? &maps.b1 : &maps.b0;
           const int k0 = (second ? kb - p.k_blocks0 : kb) * BK;
-          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sa = smem + stage * STAGE;
           uint8_t* sb = sa + kATileBytes;
-          mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
-          if (A_MN) {
-            // global A^T is [K, M] row-major: box = 64 (m) x 64 (k rows)
+          if (PAIR) {
+            // both CTAs' bytes are counted on the even CTA's barrier, which alone expects them
+            const uint32_t bar0 = mapa_u32(smem_u32(&full_bar[stage]), 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * STAGE);
+            if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(sa + j * (BK * 128), ma, &full_bar[stage], mt * BM + j * 64, k0);
-          } else {
-            tma_load_2d(sa, ma, &full_bar[stage], k0, mt * BM);
-          }
-          if (B_MN) {
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_2d_pair(sa + j * (BK * 128), ma, bar0, row0 + j * 64, k0);
+            } else {
+              tma_load_2d_pair(sa, ma, bar0, k0, row0);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (BK * 128), mb, &full_bar[stage], nt * BN + j * 64, k0);
+              for (int j = 0; j < BN_LOAD / 64; ++j)
+                tma_load_2d_pair(sb + j * (BK * 128), mb, bar0, col0 + j * 64, k0);
+            } else {
+              tma_load_2d_pair(sb, mb, bar0, k0, col0);
+            }
           } else {
-            tma_load_2d(sb, mb, &full_bar[stage], k0, nt * BN);
+            mbar_arrive_expect_tx(&full_bar[stage], STAGE);
+            if (A_MN) {
+              // global A^T is [K, M] row-major: box = 64 (m) x 64 (k rows)
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_2d(sa + j * (BK * 128), ma, &full_bar[stage], row0 + j * 64, k0);
+            } else {
+              tma_load_2d(sa, ma, &full_bar[stage], k0, row0);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * (BK * 128), mb, &full_bar[stage], col0 + j * 64, k0);
+            } else {
+              tma_load_2d(sb, mb, &full_bar[stage], k0, col0);
+            }
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == NS) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer -----------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(PAIR ? 2 * BM : BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool alive = true;
-      Work cursor = work_begin(p);
+      Work cursor = work_begin(unit);
       int tile, kb0, kb1;
-      while (alive && next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
+      while (alive && next_work(p, total_tiles, k_blocks, cursor, unit, units, tile, kb0, kb1)) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1u, abort_word)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_word)) { alive = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+          const uint32_t sa = smem_u32(smem + stage * STAGE);
           const uint32_t sb = sa + kATileBytes;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -246,12 +288,28 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
                                      : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
                                      : make_smem_desc(sb + k * 32, 16, 1024);
-            tc_mma_ss(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            if (PAIR)
+              tc_mma_ss_pair(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            else
+              tc_mma_ss(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
-          tc_commit(&empty_bar[stage]);  // frees the smem stage when the MMAs retire
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          // frees the smem stage (in both CTAs of a pair) when the MMAs retire
+          if (PAIR) {
+            tc_commit_pair(smem_u32(&empty_bar[stage]));
+            tc_commit_pair(mapa_u32(smem_u32(&empty_bar[stage]), 1));
+          } else {
+            tc_commit(&empty_bar[stage]);
+          }
+          if (++stage == NS) { stage = 0; phase ^= 1u; }
         }
-        if (alive) tc_commit(&acc_full[acc]);
+        if (alive) {
+          if (PAIR) {
+            tc_commit_pair(smem_u32(&acc_full[acc]));
+            tc_commit_pair(mapa_u32(smem_u32(&acc_full[acc]), 1));
+          } else {
+            tc_commit(&acc_full[acc]);
+          }
+        }
         if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
       }
     }
@@ -260,11 +318,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    Work cursor = work_begin(p);
+    Work cursor = work_begin(unit);
     int tile, kb0, kb1;
-    while (next_work(p, total_tiles, k_blocks, cursor, tile, kb0, kb1)) {
+    while (next_work(p, total_tiles, k_blocks, cursor, unit, units, tile, kb0, kb1)) {
       int mt, nt;
       tile_coords(tile, p.m_tiles, mt, nt);
+      if (PAIR) mt = mt * 2 + (int)cta_rank;   // this CTA's 128 rows of the pair's 256
       const bool partial = p.stream_k && !(kb0 == 0 && kb1 == k_blocks);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_word)) break;
       tc_fence_after();
@@ -541,7 +600,12 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
       // Accumulator buffer drained: hand it back to the MMA warp.
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) {
+        if (PAIR)
+          mbar_arrive_cluster(mapa_u32(smem_u32(&acc_empty[acc]), 0));
+        else
+          mbar_arrive(&acc_empty[acc]);
+      }
       if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
   }
@@ -555,9 +619,14 @@ gemm_bf16_kernel(const __grid_constant__ GemmMaps maps, const GemmParams p) {
   }
   tc_fence_before();
   __syncthreads();
+  // a pair leaves together: the even CTA's MMAs read the odd CTA's shared memory, and both signal each other's barriers
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (PAIR)
+      tmem_dealloc_pair(tmem_base, kTmemCols);
+    else
+      tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -620,9 +689,9 @@ static int num_sms() {
   return g_num_sms;
 }
 
-template <int A_MN, int B_MN, int EPI>
+template <int A_MN, int B_MN, int EPI, int PAIR>
 static int launch(const GemmMaps& maps, const GemmParams& p, int max_ctas, cudaStream_t stream) {
-  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI>;
+  auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI, PAIR>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
@@ -630,23 +699,41 @@ static int launch(const GemmMaps& maps, const GemmParams& p, int max_ctas, cudaS
       return -3;
     attr_set = true;
   }
-  int grid = p.m_tiles * p.n_tiles;
+  // scheduling units: CTAs, or CTA pairs (p.m_tiles then counts 256-row tiles)
+  int units = p.m_tiles * p.n_tiles;
   int cap = max_ctas > 0 ? max_ctas : num_sms();
-  if (grid > cap) grid = cap;
-  if (grid <= 0) return 0;
+  if (PAIR) cap /= 2;
+  if (cap < 1) cap = 1;
+  if (units > cap) units = cap;
+  if (units <= 0) return 0;
   GemmParams q = p;
   if (q.stream_k) {
     const int tiles = p.m_tiles * p.n_tiles;
     const int kb = p.k_blocks0 + p.k_blocks1;
-    grid = cap;
-    if ((long long)tiles * kb < grid) grid = (int)((long long)tiles * kb);
-    q.full_tiles = (tiles / grid) * grid;
+    units = cap;
+    if ((long long)tiles * kb < units) units = (int)((long long)tiles * kb);
+    q.full_tiles = (tiles / units) * units;
     const long long tail_units = (long long)(tiles - q.full_tiles) * kb;
-    q.units_per_cta = (tail_units + grid - 1) / grid;
+    q.units_per_cta = (tail_units + units - 1) / units;
     if (tail_units == 0) q.stream_k = 0;
   }
-  kern<<<grid, kThreads, kSmemBytes, stream>>>(maps, q);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  if (!PAIR) {
+    kern<<<units, kThreads, kSmemBytes, stream>>>(maps, q);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * units, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, maps, q) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace ab
@@ -670,7 +757,7 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
                  const AbOperand* a1, const AbOperand* b1, void* D, long long ldd, int d_is_fp32,
                  const void* C, float alpha, int epi, float* stats, float logit_scale, int* status,
                  int max_ctas, int stream_k, int n_mirrors, void* const* mirrors, const long long* mirror_lds,
-                 int mirror_cols,
+                 int mirror_cols, int cta_pair,
                  void* stream) {
   using namespace ab;
   if (M <= 0 || N <= 0 || K0 <= 0 || K1 < 0) return -10;
@@ -683,11 +770,12 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
     return make_map_bf16(m, o->ptr, mn_extent, k_extent, o->ld, BK, tile_mn);
   };
   int rc;
+  const int b_box = cta_pair ? BN / 2 : BN;   // a CTA of a pair stages half of the tile's B rows
   if ((rc = mk(&maps.a0, a0, M, K0, BM))) return rc;
-  if ((rc = mk(&maps.b0, b0, N, K0, BN))) return rc;
+  if ((rc = mk(&maps.b0, b0, N, K0, b_box))) return rc;
   if (K1 > 0) {
     if ((rc = mk(&maps.a1, a1, M, K1, BM))) return rc;
-    if ((rc = mk(&maps.b1, b1, N, K1, BN))) return rc;
+    if ((rc = mk(&maps.b1, b1, N, K1, b_box))) return rc;
   } else {
     maps.a1 = maps.a0;
     maps.b1 = maps.b0;
@@ -697,7 +785,7 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
   p.N = N;
   p.k_blocks0 = (K0 + BK - 1) / BK;
   p.k_blocks1 = K1 > 0 ? (K1 + BK - 1) / BK : 0;
-  p.m_tiles = (M + BM - 1) / BM;
+  p.m_tiles = cta_pair ? (M + 2 * BM - 1) / (2 * BM) : (M + BM - 1) / BM;
   p.n_tiles = (N + BN - 1) / BN;
   p.D = D;
   p.ldd = ldd;
@@ -731,19 +819,24 @@ int ab_gemm_bf16(int M, int N, int K0, int K1, const AbOperand* a0, const AbOper
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int amn = a0->mn_major, bmn = b0->mn_major;
-#define AB_DISPATCH(EPI)                                                         \
-  if (!amn && !bmn) return launch<0, 0, EPI>(maps, p, max_ctas, s);              \
-  if (!amn && bmn) return launch<0, 1, EPI>(maps, p, max_ctas, s);               \
-  if (amn && !bmn) return launch<1, 0, EPI>(maps, p, max_ctas, s);               \
-  return launch<1, 1, EPI>(maps, p, max_ctas, s);
-  if (epi == EPI_STORE) { AB_DISPATCH(EPI_STORE) }
+#define AB_DISPATCH(EPI, PAIR)                                                         \
+  if (!amn && !bmn) return launch<0, 0, EPI, PAIR>(maps, p, max_ctas, s);              \
+  if (!amn && bmn) return launch<0, 1, EPI, PAIR>(maps, p, max_ctas, s);               \
+  if (amn && !bmn) return launch<1, 0, EPI, PAIR>(maps, p, max_ctas, s);               \
+  return launch<1, 1, EPI, PAIR>(maps, p, max_ctas, s);
+  if (epi == EPI_STORE) {
+    if (cta_pair) { AB_DISPATCH(EPI_STORE, 1) }
+    AB_DISPATCH(EPI_STORE, 0)
+  }
   if (epi == EPI_ROWSTATS) {
     if (amn || bmn || d_is_fp32) return -13;
-    return launch<0, 0, EPI_ROWSTATS>(maps, p, max_ctas, s);
+    if (cta_pair) return launch<0, 0, EPI_ROWSTATS, 1>(maps, p, max_ctas, s);
+    return launch<0, 0, EPI_ROWSTATS, 0>(maps, p, max_ctas, s);
   }
   if (epi == EPI_SWIGLU) {
     if (amn || bmn || d_is_fp32 || (N & 1)) return -13;
-    return launch<0, 0, EPI_SWIGLU>(maps, p, max_ctas, s);
+    if (cta_pair) return launch<0, 0, EPI_SWIGLU, 1>(maps, p, max_ctas, s);
+    return launch<0, 0, EPI_SWIGLU, 0>(maps, p, max_ctas, s);
   }
 #undef AB_DISPATCH
   return -14;

@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional
 
 import torch
@@ -28,11 +29,13 @@ TILE_N = 256
 
 
 NUM_SMS = 148
+# CTA-pair (cta_group::2) kernels by default; AB_GEMM_PAIR=0/1 overrides
+PAIR_DEFAULT = os.environ.get("AB_GEMM_PAIR", "1") == "1"
 
 
-def _wave_efficiency(M: int, N: int) -> float:
-    tiles = -(-M // 128) * -(-N // TILE_N)
-    waves = tiles / NUM_SMS
+def _wave_efficiency(M: int, N: int, pair: bool = False) -> float:
+    tiles = -(-M // (256 if pair else 128)) * -(-N // TILE_N)
+    waves = tiles / (NUM_SMS // 2 if pair else NUM_SMS)
     return waves / math.ceil(waves)
 
 
@@ -85,7 +88,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
          addend: Optional[torch.Tensor] = None, alpha: float = 1.0,
          epilogue: int = EPI_STORE, stats: Optional[torch.Tensor] = None,
          logit_scale: float = 1.0, max_ctas: int = 0, stream_k: Optional[bool] = None,
-         mirrors=None, scatter_cols: int = 0) -> torch.Tensor:
+         mirrors=None, scatter_cols: int = 0, cta_pair: Optional[bool] = None) -> torch.Tensor:
     """``alpha * (A @ B^T [+ A2 @ B2^T]) [+ addend]`` with a fused epilogue.
 
     ``mirrors``: extra bf16 destinations (up to 8, possibly views of other GPUs' memory) that receive every output
@@ -93,11 +96,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
     ``[m * scatter_cols, (m + 1) * scatter_cols)`` go only to ``mirrors[m]`` (its own column origin at 0) and no
     local result is written - the sequence-to-head all-to-all of Ulysses attention done by the GEMM's stores.
 
+    ``cta_pair``: run every 256 x 256 output tile on two CTAs of a cluster (``tcgen05`` ``cta_group::2``: each CTA
+    stages half of B, one thread issues 256-row MMAs for both).  ``None`` takes the module default ``PAIR_DEFAULT``.
+
     ``stream_k=None`` picks the schedule: when whole output tiles would leave more than ~12 % of the last
     wave of CTAs idle (for example 448 tiles on 148 SMs), the (tile, k-block) space is divided evenly
     over the CTAs instead and split tiles are combined with fp32 reductions.  A bf16 result then goes
     through an fp32 workspace and one cast pass.
     """
+    if cta_pair is None:
+        cta_pair = PAIR_DEFAULT
     M = a.shape[1] if a_t else a.shape[0]
     K = a.shape[0] if a_t else a.shape[1]
     N = b.shape[1] if b_t else b.shape[0]
@@ -112,10 +120,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         stream_k = False
     inplace_acc = addend is not None and out is not None and addend.data_ptr() == out.data_ptr()
     if stream_k is None:
-        tiles = -(-M // 128) * -(-N // TILE_N)
+        tiles = -(-M // (256 if cta_pair else 128)) * -(-N // TILE_N)
+        units = NUM_SMS // 2 if cta_pair else NUM_SMS
         stream_k = (epilogue == EPI_STORE and (addend is None or inplace_acc)
-                    and ((_wave_efficiency(M, N) < 0.88 and (K + K2) >= 8192)
-                         or (tiles < NUM_SMS // 2 and (K + K2) >= 16384)))
+                    and ((_wave_efficiency(M, N, cta_pair) < 0.88 and (K + K2) >= 8192)
+                         or (tiles < units // 2 and (K + K2) >= 16384)))
     workspace_for = None
     if stream_k:
         if epilogue != EPI_STORE or not (addend is None or inplace_acc):
@@ -154,7 +163,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_t: bool = False, b_t: bool = Fal
         ctypes.c_float(logit_scale), ctypes.c_void_p(st.data_ptr()),
         ctypes.c_int(max_ctas), ctypes.c_int(1 if stream_k else 0),
         ctypes.c_int(len(mirrors) if mirrors else 0), _mirror_ptrs(mirrors), _mirror_lds(mirrors),
-        ctypes.c_int(int(scatter_cols)),
+        ctypes.c_int(int(scatter_cols)), ctypes.c_int(1 if cta_pair else 0),
         ctypes.c_void_p(torch.cuda.current_stream(a.device).cuda_stream))
     if rc != 0:
         raise RuntimeError(f"ab_gemm_bf16 refused the launch (code {rc}) for M={M} N={N} K={K}")

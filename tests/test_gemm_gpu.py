@@ -135,3 +135,17 @@ def test_gemm_scatter_epilogue_splits_columns_over_destinations():
     for i, d in enumerate(dsts):
         assert torch.allclose(d[:M].float(), ref[:, i * per:(i + 1) * per], atol=0.1, rtol=0.02)
         assert torch.all(d[M:] == 5.0)
+
+
+@pytest.mark.parametrize("pair", [False, True])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, True)])
+def test_gemm_single_cta_and_cta_pair_kernels_agree(pair, a_t, b_t):
+    """Both schedules of the kernel (one CTA per 128 x 256 tile; a cluster pair per 256 x 256 tile with
+    ``cta_group::2`` MMAs) against the fp32 product, on a shape with ragged edges in M, N and K."""
+    from aspec_b200.ops import gemm as G
+    M, N, K = 392, 776, 328
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    out = G.gemm(a.t().contiguous() if a_t else a, b.t().contiguous() if b_t else b, a_t=a_t, b_t=b_t, cta_pair=pair)
+    G.check_status("cuda")
+    assert torch.allclose(out.float(), _ref(a, b), atol=0.2, rtol=0.02)
