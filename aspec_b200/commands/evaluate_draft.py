@@ -72,7 +72,9 @@ def main(argv=None) -> int:
     if a.features:
         from aspec_b200.offline.dataset import OfflineFeatureStore
         store = OfflineFeatureStore(a.features)
-        lm_head = torch.load(f"{a.features}/lm_head.pt", map_location=dev).to(dtype) if False else None
+        import os
+        head_path = os.path.join(a.features, "lm_head.pt")      # optional: written next to the features by the generator
+        lm_head = torch.load(head_path, map_location=dev).to(dtype) if os.path.exists(head_path) else None
         features_of = lambda d: store.load(d["data_id"])["hidden_states"][None].to(dev, dtype)
     else:
         from aspec_b200.inference.factory import target_config_from_args
@@ -91,7 +93,7 @@ def main(argv=None) -> int:
         lm_head = target.lm_head.detach()
         features_of = lambda d: target.prefill(d["input_ids"].reshape(-1).to(dev), [int(d["input_ids"].numel())], layers)["hidden_states"][None]
     if lm_head is None:
-        raise ValueError("an offline feature dataset does not carry the Target output head; pass --target-weights instead")
+        raise ValueError("this offline feature dataset has no lm_head.pt; compute features with the in-framework Target instead (omit --features)")
     res = evaluate(consumer, lm_head, docs, features_of, anchors_per_doc=a.anchors_per_doc)
     res.update(asset=a.asset_dir, algorithm=manifest.get("algorithm"), documents=len(docs), block_size=a.block_size)
     text = json.dumps(res, indent=2)

@@ -25,8 +25,11 @@ def target_binding(target_identity: Dict, draft_config: Dict, family: str, store
 
 
 def materialize(output_dir: str, documents: Iterable[dict], features: Callable[[torch.Tensor], tuple], binding: dict,
-                *, split: str = "train", resume: bool = False, progress: Optional[Callable[[int], None]] = None) -> OfflineFeatureStore:
-    """``documents`` yield ``{"data_id", "input_ids", "loss_mask"}``; ``features(ids)`` returns the contract's tensors."""
+                *, split: str = "train", resume: bool = False, progress: Optional[Callable[[int], None]] = None,
+                lm_head: Optional[torch.Tensor] = None) -> OfflineFeatureStore:
+    """``documents`` yield ``{"data_id", "input_ids", "loss_mask"}``; ``features(ids)`` returns the contract's tensors.
+    ``lm_head`` (the Target's frozen output head) is saved beside the features as ``lm_head.pt`` so that decode
+    evaluation can run from the dataset alone."""
     store = (OfflineFeatureStore(output_dir, allow_incomplete=True) if resume
              else OfflineFeatureStore(output_dir, create=True, binding=binding, last_hidden_states_prenorm=False))
     if resume and store.binding["feature_contract"]["contract_id"] != binding["feature_contract"]["contract_id"]:
@@ -46,5 +49,8 @@ def materialize(output_dir: str, documents: Iterable[dict], features: Callable[[
         store.append(split, data_id, rec)
         if progress:
             progress(n + 1)
+    if lm_head is not None:
+        import os
+        torch.save(lm_head.detach().to(torch.bfloat16).cpu(), os.path.join(output_dir, "lm_head.pt"))
     store.mark_complete()
     return store
