@@ -142,6 +142,41 @@ def _worker(rank, world, port, out_path):
         res["ulysses_oproj"] = _close(got, want, 2e-2, 5e-2)
         barrier()
 
+        # ---- Ulysses self-attention block (autograd) against the same module on one GPU over the whole sequence ----
+        from aspec_b200.models.target.dense import DenseTarget
+        from aspec_b200.parallel.ulysses_attention import UlyssesSelfAttention
+        torch.manual_seed(5)
+        T5, D5, hq5, hk5, d5 = 256, 512, 8, 2, 128
+        ref_attn = UlyssesSelfAttention(D5, hq5, hk5, d5).to(dev, bf)
+        for prm in ref_attn.parameters():
+            dist.broadcast(prm.data, 0)
+        x_all = (torch.randn(world * T5, D5, device=dev) * 0.5).to(bf)
+        dy_all = (torch.randn(world * T5, D5, device=dev) * 0.1).to(bf)
+        dist.broadcast(x_all, 0)
+        dist.broadcast(dy_all, 0)
+        iv5 = DenseTarget.causal_intervals([300, world * T5 - 300], dev)
+        xr = x_all.clone().requires_grad_(True)
+        ref_attn(xr, iv5).backward(dy_all)
+        qc5, oc5 = (hq5 + 2 * hk5) * d5 // world, hq5 * d5 // world
+        uws5 = exchange_workspaces(UlyssesWorkspace(world, T5, qc5, oc5, device=dev), UlyssesWorkspace.open)
+        par = UlyssesSelfAttention(D5, hq5, hk5, d5, exchange=UlyssesExchange(rank, world, uws5, barrier)).to(dev, bf)
+        par.load_state_dict(ref_attn.state_dict())
+        rows = slice(rank * T5, (rank + 1) * T5)
+        xp = x_all[rows].clone().requires_grad_(True)
+        yp = par(xp, iv5)
+        yp.backward(dy_all[rows])
+        with torch.no_grad():
+            yr = ref_attn(x_all, iv5)[rows]
+        res["ulysses_block_forward"] = _close(yp, yr, 3e-2, 2e-2)
+        res["ulysses_block_dx"] = _close(xp.grad, xr.grad[rows], 5e-2, 2e-2)
+        ok = True
+        for (n, pp), (_, pr) in zip(par.named_parameters(), ref_attn.named_parameters()):
+            g = pp.grad.float().clone()
+            dist.all_reduce(g)                      # every rank contributed its own rows
+            ok = ok and _close(g, pr.grad, 5e-2, 3e-2 * max(pr.grad.abs().max().item(), 1e-3))
+        res["ulysses_block_dw"] = ok
+        barrier()
+
         # ---- expert parallelism: fused peer-memory dispatch / combine against the NCCL all-to-all path ------------
         from aspec_b200.models.draft.moe import ExpertBank
         from aspec_b200.parallel.expert_parallel import (EPWorkspace, FusedExpertParallel, dispatch_combine,
