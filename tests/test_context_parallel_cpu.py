@@ -71,3 +71,24 @@ def test_cp2_matches_single_rank(tmp_path):
     assert set(got["grads"]) == set(grads)
     for name, g in grads.items():
         assert torch.allclose(got["grads"][name], g, rtol=2e-3, atol=2e-5), name
+
+
+def test_ulysses_attention_module_without_an_exchange_is_plain_gqa_attention():
+    """The sequence-parallel block's single-GPU path (its own test reference on GPUs) against an explicit softmax."""
+    import torch
+    from aspec_b200.models.target.dense import DenseTarget
+    from aspec_b200.parallel.ulysses_attention import UlyssesSelfAttention
+    torch.manual_seed(0)
+    m = UlyssesSelfAttention(32, 4, 2, 8)
+    x = torch.randn(12, 32)
+    iv = DenseTarget.causal_intervals([7, 5], "cpu")
+    y = m(x, iv)
+    q = (x @ m.q_proj.T).view(12, 4, 8)
+    k = (x @ m.k_proj.T).view(12, 2, 8).repeat_interleave(2, 1)
+    v = (x @ m.v_proj.T).view(12, 2, 8).repeat_interleave(2, 1)
+    doc = torch.tensor([0] * 7 + [1] * 5)
+    mask = (doc[:, None] == doc[None, :]) & (torch.arange(12)[:, None] >= torch.arange(12)[None, :])
+    s = torch.einsum("qhd,khd->hqk", q, k) * 8 ** -0.5
+    p = torch.softmax(s.masked_fill(~mask, float("-inf")), -1)
+    want = torch.einsum("hqk,khd->qhd", p, v).reshape(12, 32) @ m.o_proj.T
+    assert torch.allclose(y, want, atol=1e-5)
