@@ -16,6 +16,7 @@ COMMANDS = {
     "prepare-target-data": "aspec_b200.commands.prepare_target_dataset",
     "select-answers": "aspec_b200.commands.prepare_selected_answers",
     "convert-data": "aspec_b200.commands.convert_pretokenized_jsonl",
+    "build-workload": "aspec_b200.commands.build_workload",
     "build": "aspec_b200.build",
     "topology": "aspec_b200.topology",
 }

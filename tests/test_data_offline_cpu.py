@@ -169,3 +169,21 @@ def test_trackers_locality_identity_and_termination(tmp_path):
         assert reached
     finally:
         restore_handlers(prev)
+
+
+def test_workload_builders_are_deterministic_and_load_as_training_samples(tmp_path):
+    import json
+    from aspec_b200.commands.build_workload import build_fixed, build_mixed
+    from aspec_b200.data.dataset import load_training_samples
+    a = build_fixed(str(tmp_path / "a.jsonl"), sequence_length=64, rows=5, seed=3, min_token_id=10, max_token_id=500, prompt_tokens=16)
+    b = build_fixed(str(tmp_path / "b.jsonl"), sequence_length=64, rows=5, seed=3, min_token_id=10, max_token_id=500, prompt_tokens=16)
+    assert a["sha256"] == b["sha256"] and a["rows"] == 5
+    rows = [json.loads(l) for l in open(tmp_path / "a.jsonl")]
+    assert all(len(r["input_ids"]) == 64 and r["loss_tokens"] == 48 and 10 <= min(r["input_ids"]) and max(r["input_ids"]) < 500 for r in rows)
+    m = build_mixed(str(tmp_path / "a.jsonl"), str(tmp_path / "m.jsonl"), lengths=[16, 40, 64], repetitions=2)
+    assert m["rows"] == 6
+    mixed = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    assert [r["seq_len"] for r in mixed] == [16, 40, 64, 16, 40, 64]
+    assert mixed[1]["input_ids"] == rows[1]["input_ids"][:40] and mixed[1]["loss_tokens"] == 24 and mixed[0]["loss_tokens"] == 0
+    samples = load_training_samples(str(tmp_path / "m.jsonl"), {"max_seq_length": 64})
+    assert len(samples) >= 4                                            # rows without supervised tokens may be dropped
