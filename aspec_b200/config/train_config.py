@@ -100,6 +100,8 @@ class LoggingConfig:
 @dataclass
 class ClusterConfig:
     mode: str = "single_node"
+    nodes: Optional[List[dict]] = None          # [{name, gpus}]: the machines of a static cluster; default: this machine
+    node_name: Optional[str] = None             # which entry of ``nodes`` this process runs on
     shared_root: Optional[str] = None
     storage_mode: str = "shared"
     file_transfer_timeout_seconds: float = 600.0

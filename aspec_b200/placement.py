@@ -80,8 +80,13 @@ def _get(args, key: str, default=None):
     return args.get(key, default) if isinstance(args, dict) else getattr(args, key, default)
 
 
+def _role_nodes(args, role: str) -> List[str]:
+    """``training_nodes`` / ``inference_nodes``, or the reference's spelling ``training_node_ips`` / ``inference_node_ips``."""
+    return _as_list(_get(args, f"{role}_nodes") or _get(args, f"{role}_node_ips"), f"{role}_nodes")
+
+
 def has_custom_fields(args) -> bool:
-    return bool(_as_list(_get(args, "training_nodes"), "training_nodes") or _as_list(_get(args, "inference_nodes"), "inference_nodes"))
+    return bool(_role_nodes(args, "training") or _role_nodes(args, "inference"))
 
 
 def create_placement(args, nodes: Sequence[Node], roles: Optional[Set[str]] = None) -> Placement:
@@ -120,14 +125,13 @@ def create_placement(args, nodes: Sequence[Node], roles: Optional[Set[str]] = No
     if n_train <= 0:
         raise ValueError("Training placement requires a positive GPU count")
     if colocate:
-        pool = _packed(_select(nodes, _as_list(_get(args, "training_nodes"), "training_nodes"))) if strategy == "custom" else _packed(nodes)
+        pool = _packed(_select(nodes, _role_nodes(args, "training"))) if strategy == "custom" else _packed(nodes)
         if n_train > len(pool):
             raise ValueError(f"colocated roles need {n_train} GPUs, {len(pool)} offered")
         return Placement(training=pool[:n_train], inference=pool[:n_train], strategy=strategy)
 
     if strategy == "custom":
-        t_names = _as_list(_get(args, "training_nodes"), "training_nodes")
-        i_names = _as_list(_get(args, "inference_nodes"), "inference_nodes")
+        t_names, i_names = _role_nodes(args, "training"), _role_nodes(args, "inference")
         if not t_names or (n_inf > 0 and not i_names):
             raise ValueError("custom placement needs training_nodes and inference_nodes")
         both = set(t_names) & set(i_names)

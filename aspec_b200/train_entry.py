@@ -60,15 +60,25 @@ def claim_run_directory(output_dir: str) -> None:
 
 
 def _devices(flat: Dict[str, Any]):
+    """Device strings of the Target and Draft roles on this node, from the placement policy (``placement_strategy``,
+    ``colocate``, ``training_nodes`` / ``inference_nodes``, ``cluster_nodes``)."""
     import torch
+    from aspec_b200.placement import cluster_from_args, create_placement
     n_draft = int(flat["training_num_gpus_per_node"]) * int(flat["training_num_nodes"])
     n_target = int(flat["inference_num_gpus"]) if flat["inference_engine_type"] == "native" else 0
     if torch.cuda.is_available() and not flat.get("force_cpu"):
         have = torch.cuda.device_count()
-        if n_draft + n_target > have:
+        nodes = cluster_from_args(flat, have)
+        args = dict(flat, inference_num_gpus=n_target)
+        roles = None if n_target > 0 else {"training"}
+        if roles is None and not flat.get("colocate") and len(nodes) == 1 and n_draft + n_target > have:
             raise RuntimeError(f"plan needs {n_target} Target + {n_draft} Draft GPUs, {have} visible")
-        target = [f"cuda:{i}" for i in range(n_target)]
-        draft = [f"cuda:{n_target + i}" for i in range(n_draft)]
+        placement = create_placement(args, nodes, roles)
+        here = str(flat.get("cluster_node_name") or nodes[0].name)
+        target, draft = placement.devices_on(here, "inference"), placement.devices_on(here, "training")
+        if len(target) != n_target or len(draft) != n_draft:
+            raise RuntimeError(f"placement puts {len(target)} Target + {len(draft)} Draft roles on node {here}; this runtime "
+                               f"launches one node and the plan needs {n_target} + {n_draft} there")
     else:
         target, draft = ["cpu"] * n_target, ["cpu"] * n_draft
     return target, draft
