@@ -50,6 +50,9 @@ def parse_args():
     ap.add_argument("--targets", type=int, default=0, help="online: Target GPUs (default N // 2)")
     ap.add_argument("--target-layers-total", type=int, default=36)
     ap.add_argument("--target-batch", type=int, default=4, help="online: documents packed into one Target prefill")
+    ap.add_argument("--length-group", type=int, default=32,
+                    help="online: the controller's length_group_size (documents of similar length go to different Draft ranks "
+                         "in the same micro-step; 1 disables the grouping)")
     ap.add_argument("--fsdp", action="store_true", help="draft mode: FULL_SHARD optimizer over peer memory instead of REPLICATE")
     return ap.parse_args()
 
@@ -305,7 +308,7 @@ def run_online(args) -> dict:
         dspark_l1_loss_alpha=0.9, dspark_confidence_head_alpha=1.0, train_data_path="synthetic",
         synthetic_num_documents=max(steps * args.accum * D * 2, 64), synthetic_min_length=min(args.min_len, args.max_len),
         synthetic_max_length=args.max_len, synthetic_vocab_size=dims["vocab_size"] - 1024, shuffle_dataset=True,
-        length_group_size=1, transport_destination_ring_slots=max(2 * args.accum + 2, 4),
+        length_group_size=max(args.length_group, 1), transport_destination_ring_slots=max(2 * args.accum + 2, 4),
         inference_batch_size=max(args.target_batch, 1),
         store_last_hidden_states=True, output_dir=out_dir, save_interval=0, save_final_checkpoint=False,
         performance_warmup_steps=args.warmup, performance_drain_steps=0, optimizer_step_timeout_seconds=900.0,
