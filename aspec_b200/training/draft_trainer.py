@@ -75,6 +75,25 @@ class DraftTrainer:
                 out[k] = v
         return out
 
+    def _stage(self, batch):
+        """``(device batch, event or None)``: host tensors are copied on a side stream so that the copy of micro-batch
+        ``i + 1`` overlaps the compute of micro-batch ``i``; the event marks the end of the copies."""
+        if batch is None:
+            return None
+        if self.device.type != "cuda" or self.h2d_bytes(batch) == 0:
+            return self.to_device(batch), None
+        if getattr(self, "_copy_stream", None) is None:
+            self._copy_stream = torch.cuda.Stream(self.device)
+        compute = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self._copy_stream):
+            out = self.to_device(batch)
+            for k, v in out.items():
+                if torch.is_tensor(v) and v.is_cuda and v is not batch.get(k):
+                    v.record_stream(compute)              # allocated on the copy stream, consumed on the compute stream
+            ready = torch.cuda.Event()
+            ready.record(self._copy_stream)
+        return out, ready
+
     @staticmethod
     def h2d_bytes(batch: dict) -> int:
         return sum(v.numel() * v.element_size() for k, v in batch.items()
@@ -111,8 +130,14 @@ class DraftTrainer:
         self.model.train()
         self._pool = {}
         n = 0
-        for batch in batches:
-            self._forward_backward(self.to_device(batch))
+        it = iter(batches)
+        staged = self._stage(next(it, None))
+        while staged is not None:
+            batch, ready = staged
+            staged = self._stage(next(it, None))          # the next micro-batch's copies run under this one's compute
+            if ready is not None:
+                torch.cuda.current_stream(self.device).wait_event(ready)
+            self._forward_backward(batch)
             n += 1
         if n == 0:
             raise ValueError("train_update needs at least one micro-batch")
