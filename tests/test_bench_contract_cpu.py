@@ -1,0 +1,39 @@
+"""The benchmark entry point's output contract, on CPU with tiny shapes (not a valid measurement, only the format)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REQUIRED = {"metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline",
+            "dtype", "data", "config", "e2e", "gpu_launches", "clocks"}
+
+
+def _run(cmd, env=None):
+    out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600, env={**os.environ, **(env or {})})
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1, out.stdout[-2000:]
+    return json.loads(lines[0])
+
+
+@pytest.mark.timeout(600)
+def test_single_process_line_has_every_key_and_an_end_to_end_number():
+    res = _run([sys.executable, "bench.py", "--small", "--steps", "2", "--warmup", "1"], {"CUDA_VISIBLE_DEVICES": ""})
+    assert REQUIRED <= set(res)
+    assert res["n_gpus"] == 1 and res["steps"] == 2 and res["warmup"] == 1 and res["higher_is_better"] is True
+    assert res["value"] > 0 and res["ms_per_step"] > 0
+    e2e = res["e2e"]
+    assert e2e["value"] > 0 and e2e["h2d_bytes_per_step"] >= 0 and e2e["d2h_bytes_per_step"] > 0
+    assert res["config"]["parallelism"] == "dp1" and "l2_policy" in res["config"]
+
+
+@pytest.mark.timeout(900)
+def test_two_ranks_under_torchrun_print_one_line_with_the_aggregate():
+    res = _run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                "--master-port", str(29600 + os.getpid() % 300), "bench.py", "--gpus", "2", "--small", "--steps", "1", "--warmup", "1",
+                "--no-e2e"], {"CUDA_VISIBLE_DEVICES": ""})
+    assert res["n_gpus"] == 2 and res["config"]["parallelism"] == "dp2" and res["config"]["global_batch"] == 32
+    assert res["vs_baseline"] is None and "length-grouped" in res["config"]["dp_balance"]
