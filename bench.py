@@ -131,26 +131,16 @@ def make_pool(args, cfg, model, rank, n_docs, pin):
     import torch
     from aspec_b200.data.synthetic import SyntheticSpec, make_document, synthetic_features
     spec = SyntheticSpec(vocab_size=cfg.vocab_size - 1024, min_len=min(args.min_len, args.max_len), max_len=args.max_len, seed=17)
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rows = list(range(n_docs))
-    if world > 1:
-        # Data-parallel ranks draw from one global stream that is dealt the way the training controller deals it
-        # (controller/training_controller.py, length_group_size): documents are sorted by length inside a group and
-        # consecutive ones go to different ranks, so every micro-step has similar lengths on all ranks and no rank
-        # waits for another's longer documents.  The micro-step order is then shuffled identically on every rank.
-        import random
-        total = n_docs * world
-        lengths = [make_document(spec, r)["seq_len"] for r in range(total)]
-        group = 32 * world
-        order = []
-        for c in range(0, total, group):
-            order += sorted(range(c, min(c + group, total)), key=lambda j: -lengths[j])
-        steps = list(range(n_docs))
-        random.Random(5).shuffle(steps)
-        rows = [order[m * world + (rank if m % 2 == 0 else world - 1 - rank)] for m in steps]      # serpentine
     pool = []
-    for row in rows:
-        doc = make_document(spec, row)
+    for i in range(n_docs):
+        # Weak scaling: rank r's document i has the LENGTH of the 1-GPU run's document i (so per-GPU work is the same
+        # at every N and micro-steps are balanced across ranks, which is what the training controller's length-grouped
+        # deal approximates on real data) but its own token ids and features.
+        doc = make_document(spec, i)
+        row = rank * 100003 + i
+        if rank > 0:
+            g = torch.Generator().manual_seed(row)
+            doc["input_ids"] = torch.randint(0, spec.vocab_size, (doc["seq_len"],), generator=g, dtype=torch.int64)
         T = doc["seq_len"]
         feats = synthetic_features(T, cfg.num_target_layers, cfg.target_hidden_size, row, pin=pin)
         lm = doc["loss_mask"][None]
@@ -265,7 +255,7 @@ def run_ours(args):
                        "global_batch": args.accum * world, "seq_len": args.max_len,
                        "doc_lengths": f"log-uniform [{args.min_len},{args.max_len}]",
                        "parallelism": f"dp{world}" + ("+full_shard" if args.fsdp else ""),
-                       "dp_balance": "length-grouped deal across ranks (group 32)" if world > 1 else "n/a", "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,
+                       "dp_balance": "every rank draws documents with the length sequence of the 1-GPU run (own token ids and features)" if world > 1 else "n/a", "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,
                        "block_size": model.block_size,
                        "l2_policy": "inputs larger than L2 (1.2 GB lm_head + per-document features stream from HBM every micro-batch)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours",

@@ -36,4 +36,4 @@ def test_two_ranks_under_torchrun_print_one_line_with_the_aggregate():
                 "--master-port", str(29600 + os.getpid() % 300), "bench.py", "--gpus", "2", "--small", "--steps", "1", "--warmup", "1",
                 "--no-e2e"], {"CUDA_VISIBLE_DEVICES": ""})
     assert res["n_gpus"] == 2 and res["config"]["parallelism"] == "dp2" and res["config"]["global_batch"] == 32
-    assert res["vs_baseline"] is None and "length-grouped" in res["config"]["dp_balance"]
+    assert res["vs_baseline"] is None and "length sequence of the 1-GPU run" in res["config"]["dp_balance"]
