@@ -260,7 +260,8 @@ class InferenceConfig:
     inference_num_gpus: int = 1
     inference_num_gpus_per_engine: int = 1
     inference_num_gpus_per_node: int = 8
-    inference_batch_size: int = 8
+    inference_batch_size: int = 8               # rows per Target call (upper bound when inference_batch_tokens is set)
+    inference_batch_tokens: int = 0             # > 0: send a batch once it holds this many tokens
     inference_buffer_threshold: int = 32
     inference_node_ips: Optional[List[str]] = None
     max_sample_pool_size: int = 64

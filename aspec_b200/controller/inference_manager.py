@@ -21,11 +21,15 @@ from aspec_b200.utils.types import InferenceOutput, RowRequest
 
 class InferenceManager:
     def __init__(self, engines: Sequence, rings: Dict[int, GenerationSlotRing], on_result: Callable[[InferenceOutput, RowRequest], None],
-                 batch_size: int = 1, acquire_timeout: float = 120.0, max_inflight_per_engine: int = 2):
+                 batch_size: int = 1, acquire_timeout: float = 120.0, max_inflight_per_engine: int = 2,
+                 batch_tokens: int = 0):
         self.engines = list(engines)
         self.rings = rings
         self.on_result = on_result
         self.batch_size = max(int(batch_size), 1)
+        # > 0: a batch is sent once it holds this many tokens (or ``batch_size`` rows, whichever comes first), so that
+        # batches of short documents still give the Target full-width GEMMs
+        self.batch_tokens = max(int(batch_tokens), 0)
         self.acquire_timeout = acquire_timeout
         self.max_inflight = max_inflight_per_engine
         self._todo: "queue.Queue" = queue.Queue()
@@ -136,7 +140,9 @@ class InferenceManager:
                     request.leases = leases
                     if leases:
                         batch.append(request)
-                if len(batch) >= self.batch_size or item == "idle":
+                full = len(batch) >= self.batch_size or (self.batch_tokens > 0 and batch
+                                                         and sum(sum(r.document_lengths) for r in batch) >= self.batch_tokens)
+                if full or item == "idle":
                     flush()
                 self._collect(block=False)
             if not self._stop.is_set():

@@ -140,6 +140,7 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
         rings = {r: GenerationSlotRing(slots) for r in range(world)}
         manager = InferenceManager(engines, rings, on_result=lambda o, r: None,
                                    batch_size=int(flat.get("inference_batch_size", 1)),
+                                   batch_tokens=int(flat.get("inference_batch_tokens", 0) or 0),
                                    acquire_timeout=float(flat.get("transport_acquire_timeout_seconds", 120.0)))
         manager.start()
         num_steps = int(flat.get("num_train_steps") or 0) or max(n // max(dp * int(flat.get("micro_batch_size", 1))

@@ -299,7 +299,8 @@ def run_online(args) -> dict:
         synthetic_num_documents=max(steps * args.accum * D * 2, 64), synthetic_min_length=min(args.min_len, args.max_len),
         synthetic_max_length=args.max_len, synthetic_vocab_size=dims["vocab_size"] - 1024, shuffle_dataset=True,
         length_group_size=max(args.length_group, 1), transport_destination_ring_slots=max(2 * args.accum + 2, 4),
-        inference_batch_size=max(args.target_batch, 1),
+        # batches are cut by tokens (about --target-batch average documents), so short documents still fill the GEMMs
+        inference_batch_size=max(args.target_batch, 1) * 8, inference_batch_tokens=max(args.target_batch, 1) * 2048,
         store_last_hidden_states=True, output_dir=out_dir, save_interval=0, save_final_checkpoint=False,
         performance_warmup_steps=args.warmup, performance_drain_steps=0, optimizer_step_timeout_seconds=900.0,
         target_model_config={"model_type": "qwen3", "hidden_size": dims["hidden_size"], "intermediate_size": dims["intermediate_size"],

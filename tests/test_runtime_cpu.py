@@ -184,3 +184,41 @@ def test_feature_ring_descriptor_and_stale_rejection():
     wrong = FeatureDescriptor("r1", "0", 4, 1, 5, 10, (2, 18, 33), 16, "float32")
     with pytest.raises(RuntimeError):
         ring.read(wrong.to_key())
+
+
+def test_inference_manager_cuts_batches_by_tokens():
+    """With a token budget, short rows are grouped until the budget is reached; long rows go out alone; the row cap
+    still bounds a batch."""
+    import time
+    import torch
+    from aspec_b200.controller.inference_manager import InferenceManager
+    from aspec_b200.transport.slot_ring import GenerationSlotRing
+    from aspec_b200.utils.types import InferenceOutput, RowRequest
+
+    class Engine:
+        def __init__(self):
+            self.batches = []
+
+        def generate(self, requests):
+            self.batches.append([sum(r.document_lengths) for r in requests])
+            return [InferenceOutput(r.row_id, r.data_ids, [f"k{r.row_id}"], {}, r.document_lengths, r.packed_loss_masks, r.metadata, 0)
+                    for r in requests]
+
+    eng = Engine()
+    done = []
+    mgr = InferenceManager([eng], {0: GenerationSlotRing(64)}, on_result=lambda out, req: done.append(out.row_id),
+                           batch_size=6, batch_tokens=1000)
+    lengths = [300, 300, 300, 300, 2000, 100, 100, 100, 100, 100, 100, 100]
+    for i, n in enumerate(lengths):                       # queued before the worker starts, so batching is deterministic
+        mgr.submit(RowRequest(str(i), [str(i)], torch.zeros(n, dtype=torch.int64), (n,), [str(n)], [{}]), [0])
+    mgr.start()
+    deadline = time.monotonic() + 20
+    while len(done) < len(lengths) and time.monotonic() < deadline:
+        time.sleep(0.01)
+    mgr.stop()
+    mgr.raise_if_failed()
+    assert len(done) == len(lengths)
+    assert eng.batches[0] == [300, 300, 300, 300]          # 1200 >= 1000 tokens
+    assert eng.batches[1] == [2000]                        # a long row alone
+    assert eng.batches[2] == [100] * 6                     # the row cap
+    assert sum(len(b) for b in eng.batches) == len(lengths)
