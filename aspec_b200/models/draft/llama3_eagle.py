@@ -118,12 +118,27 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
                  ttt_length: int):
         """One TTT depth over ``T`` packed tokens.  Returns the new hidden state and the extended cache."""
         layer = self.midlayer
-        T = hidden.shape[0]
         x, residual = layer.attention_input(embeds, hidden)
-        q, k, v = layer.self_attn.project(x, positions + depth)
+        ex = getattr(self, "ulysses", None)
+        if ex is not None:
+            # Sequence parallel: ``embeds`` / ``hidden`` are this rank's rows, ``positions`` / ``doc_start`` describe ALL
+            # rows of the packed sequence; the exchange moves QKV to head owners and attention outputs back.
+            attn_out, cache = self._ulysses_attention(layer, x, positions, depth, cache, doc_start, ttt_length, ex)
+            h = residual + attn_out
+        else:
+            q, k, v = layer.self_attn.project(x, positions + depth)
+            o, cache = self._attend(layer.self_attn, q, k, v, depth, cache, doc_start, ttt_length)
+            h = residual + layer.self_attn.o_proj(o.reshape(o.shape[0], -1))
+        h = h + self._mlp(layer, layer.post_attention_layernorm(h), depth)
+        return h, cache
+
+    @staticmethod
+    def _attend(attn, q, k, v, depth: int, cache, doc_start: torch.Tensor, ttt_length: int):
+        """Attention of one TTT depth over ``T`` rows: causal keys of depth 0 plus the row's own keys of depths
+        ``1..depth``.  Returns the output ``[T, H, d]`` and the extended cache ``(k0, v0, [k_1..], [v_1..])``."""
+        T = q.shape[0]
         L1 = max(ttt_length - 1, 1)
-        dev = hidden.device
-        t = torch.arange(T, device=dev)
+        t = torch.arange(T, device=q.device)
         if depth == 0:
             k0, v0, dk, dv = k, v, [], []
         else:
@@ -135,13 +150,39 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
             v_all = torch.cat([v0, torch.stack(dv + [torch.zeros_like(v)] * n_pad, 1).reshape(T * L1, *v.shape[1:])])
         else:
             k_all, v_all = k0, v0
-        window = getattr(layer.self_attn, "window", None)
+        window = getattr(attn, "window", None)
         lo = doc_start if window is None else torch.maximum(doc_start, t + 1 - window)
         intervals = torch.stack([lo, t + 1, T + t * L1, T + t * L1 + depth], -1).to(torch.int32)
-        o, _ = interval_attention(q, k_all, v_all, intervals, layer.self_attn.scale)
-        h = residual + layer.self_attn.o_proj(o.reshape(T, -1))
-        h = h + self._mlp(layer, layer.post_attention_layernorm(h), depth)
-        return h, (k0, v0, dk, dv)
+        o, _ = interval_attention(q, k_all, v_all, intervals, attn.scale)
+        return o, (k0, v0, dk, dv)
+
+    def _ulysses_attention(self, layer, x, positions_all, depth: int, cache, doc_start_all, ttt_length: int, ex):
+        from aspec_b200.parallel.ulysses import group_qkv_rows
+        from aspec_b200.parallel.ulysses_attention import ulysses_block
+        sa = layer.self_attn
+        p = ex.world
+        if sa.num_heads % p or sa.num_kv_heads % p:
+            raise ValueError("attention head counts must be divisible by the sequence-parallel size")
+        hq, hk, d = sa.num_heads // p, sa.num_kv_heads // p, sa.head_dim
+        w_grouped = group_qkv_rows(sa.q_proj.weight, sa.k_proj.weight, sa.v_proj.weight, p, d)
+        state = {}
+
+        def core(qkv: torch.Tensor) -> torch.Tensor:            # all rows, this rank's heads
+            T = qkv.shape[0]
+            q = qkv[:, : hq * d].reshape(T, hq, d)
+            k = qkv[:, hq * d:(hq + hk) * d].reshape(T, hk, d)
+            v = qkv[:, (hq + hk) * d:].reshape(T, hk, d)
+            if sa.use_rope:
+                inv = sa.rope_freqs.get(qkv.device)
+                pos = positions_all + depth
+                q = qk_norm_rope(q.contiguous(), None, pos, inv, 0.0, sa.rope_scaling)
+                k = qk_norm_rope(k.contiguous(), None, pos, inv, 0.0, sa.rope_scaling)
+            o, state["cache"] = self._attend(sa, q, k.contiguous(), v.contiguous(), depth, cache, doc_start_all, ttt_length)
+            return o.reshape(T, hq * d)
+
+        ex.set_rows(x.shape[0])
+        out = ulysses_block(x, w_grouped, sa.o_proj.weight, ex, core)
+        return out, state["cache"]
 
     def _mlp(self, layer, x: torch.Tensor, depth: int) -> torch.Tensor:
         return layer.mlp(x)

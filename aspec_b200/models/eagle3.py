@@ -121,6 +121,23 @@ class Eagle3Model(nn.Module):
         if last_hidden_states is None:
             raise ValueError("EAGLE3 training needs the Target's last_hidden_states")
         draft = self.draft_model
+        sp = getattr(self, "sequence_parallel", None)          # (rank, size, process group) of an Ulysses group
+        if sp is not None:
+            # every rank of the group receives the whole row; it pads it to a multiple of the group size, keeps its own
+            # slice of the token-wise work and meets the others inside the attention exchange
+            if input_ids.shape[0] != 1:
+                raise ValueError("sequence-parallel EAGLE training takes one packed row per micro-batch")
+            pad = (-input_ids.shape[1]) % sp[1]
+            if ctx_doc_ids is None:
+                ctx_doc_ids = torch.zeros_like(input_ids)
+            if pad:
+                def padded(x, value):
+                    return None if x is None else torch.cat([x, x.new_full((1, pad, *x.shape[2:]), value)], 1)
+                feats_in = hidden_states_list if torch.is_tensor(hidden_states_list) else torch.cat(list(hidden_states_list), -1)
+                input_ids, loss_mask = padded(input_ids, 0), padded(loss_mask, 0)
+                hidden_states_list, last_hidden_states = padded(feats_in, 0), padded(last_hidden_states, 0)
+                ctx_doc_ids, base_position_ids = padded(ctx_doc_ids, -1), padded(base_position_ids, 0)
+                attention_mask = padded(attention_mask, 0)
         B, T0 = input_ids.shape
         dev = input_ids.device
         ids = input_ids.reshape(-1)
@@ -146,11 +163,19 @@ class Eagle3Model(nn.Module):
         doc_end = torch.where(last, t + 1, torch.full_like(t, T)).flip(0).cummin(0).values.flip(0)
         positions = (base_position_ids.reshape(-1).to(dev) if base_position_ids is not None else t - doc_start).to(torch.int32)
         mask = mask * valid
-        if hasattr(draft, "set_valid_rows"):
+        if hasattr(draft, "set_valid_rows") and sp is None:
             draft.set_valid_rows(lambda depth: (t + depth + 1 < doc_end) & valid)
 
+        if sp is not None:
+            sp_rank, sp_size, sp_group = sp
+            T_loc = T // sp_size
+            sl = slice(sp_rank * T_loc, (sp_rank + 1) * T_loc)
+            if hasattr(draft, "set_valid_rows"):
+                draft.set_valid_rows(lambda depth: ((t + depth + 1 < doc_end) & valid)[sl])
+        else:
+            sl = slice(0, T)
         target = LazyTarget(teacher, lm_head_weight, getattr(draft, "t2d", None) if draft.vocab_pruned else None)
-        hidden = draft.project_hidden_states(feats)
+        hidden = draft.project_hidden_states(feats[sl])
         cache = None
         numerator = hidden.new_zeros((), dtype=torch.float32)
         loss_pp, acc_pp, count_pp = [], [], []
@@ -159,8 +184,9 @@ class Eagle3Model(nn.Module):
             step_ids, _ = shift_within_documents(ids, doc_end, 1 + i)
             step_mask, inside = shift_within_documents(mask, doc_end, i)
             teacher_i, _ = shift_within_documents(teacher, doc_end, 1 + i)
+            step_ids, step_mask, teacher_i = step_ids[sl], step_mask[sl], teacher_i[sl]
             embeds = draft.embed_input_ids(step_ids).to(hidden.dtype)
-            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+            if self.gradient_checkpointing and self.training and torch.is_grad_enabled() and sp is None:
                 from torch.utils.checkpoint import checkpoint
                 hidden, cache = checkpoint(draft.backbone, embeds, hidden, positions, i, cache, doc_start, self.length,
                                            use_reentrant=False)
@@ -173,13 +199,20 @@ class Eagle3Model(nn.Module):
             else:
                 loss_sum = hidden.sum() * 0.0
                 correct = alpha_sum = loss_sum.detach()
+            total_loss = loss_sum.detach()
+            if sp is not None:
+                # the depth's supervised rows are spread over the group: normalise by the row's count, report the row's sums
+                import torch.distributed as dist
+                pooled = torch.stack([total_loss.float(), correct.float(), count.float(), alpha_sum.float()])
+                dist.all_reduce(pooled, group=sp_group)
+                total_loss, correct, count, alpha_sum = pooled.unbind(0)
             numerator = numerator + self.ploss_weights[i] * loss_sum / count.clamp(min=1.0)
-            loss_pp.append((loss_sum / count.clamp(min=1.0)).detach())
+            loss_pp.append(total_loss / count.clamp(min=1.0))
             acc_pp.append((correct / count.clamp(min=1.0)).detach())
             count_pp.append(count.detach())
             alphas.append((alpha_sum / count.clamp(min=1.0)).detach())
             hidden = draft.next_depth_hidden(hidden)
-        denominator = torch.ones((), device=dev)
+        denominator = torch.ones((), device=dev) / (sp[1] if sp is not None else 1)
         loss_pp, acc_pp, count_pp = torch.stack(loss_pp), torch.stack(acc_pp), torch.stack(count_pp)
         accuracy = (acc_pp * count_pp).sum() / count_pp.sum().clamp(min=1.0)
         comps = {}

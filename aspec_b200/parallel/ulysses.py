@@ -41,6 +41,7 @@ class UlyssesWorkspace:
                  buffer: Optional[SymmetricBuffer] = None):
         """``qkv_cols`` = one rank's share of the QKV columns, ``out_cols`` = one rank's share of the attention output."""
         self.world, self.rows, self.qkv_cols, self.out_cols = world, rows_per_rank, qkv_cols, out_cols
+        self.capacity = rows_per_rank
         total = world * rows_per_rank
         sizes = [("qkv", total * qkv_cols * 2), ("attn", total * out_cols * 2), ("dqkv", total * qkv_cols * 2),
                  ("dattn", total * out_cols * 2)]
@@ -54,8 +55,20 @@ class UlyssesWorkspace:
         self.qkv, self.dqkv = v("qkv", qkv_cols), v("dqkv", qkv_cols)           # all rows, my heads
         self.attn, self.dattn = v("attn", out_cols), v("dattn", out_cols)
 
+    def resize(self, rows: int) -> None:
+        """Use the first ``world * rows`` rows of every buffer (``rows`` up to the allocated capacity)."""
+        if rows > self.capacity:
+            raise ValueError(f"{rows} rows per rank exceed the workspace's capacity of {self.capacity}")
+        if rows == self.rows:
+            return
+        raw, total = self.buffer.tensor, self.world * rows
+        v = lambda name, cols: raw[self._off[name][0]: self._off[name][0] + total * cols * 2].view(torch.bfloat16).view(total, cols)
+        self.rows = rows
+        self.qkv, self.dqkv = v("qkv", self.qkv_cols), v("dqkv", self.qkv_cols)
+        self.attn, self.dattn = v("attn", self.out_cols), v("dattn", self.out_cols)
+
     def export(self) -> dict:
-        return {"memory": self.buffer.export(), "world": self.world, "rows": self.rows, "qkv_cols": self.qkv_cols,
+        return {"memory": self.buffer.export(), "world": self.world, "rows": self.capacity, "qkv_cols": self.qkv_cols,
                 "out_cols": self.out_cols}
 
     @classmethod
@@ -81,6 +94,11 @@ class UlyssesExchange:
         self.rank, self.world, self.ws = rank, world, list(workspaces)
         self.mine = self.ws[rank]
         self.barrier = barrier or (lambda: None)
+
+    def set_rows(self, rows: int) -> None:
+        """Rows per rank of the next exchange (all ranks of the group must agree)."""
+        for w in self.ws:
+            w.resize(int(rows))
 
     def _rows(self, r: int) -> slice:
         return slice(r * self.mine.rows, (r + 1) * self.mine.rows)

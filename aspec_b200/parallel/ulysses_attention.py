@@ -44,7 +44,9 @@ class _UlyssesBlockFn(torch.autograd.Function):
         d_wo = ex.output_projection_backward(dout.contiguous(), w_o)      # scatters d attn to the head owners
         ex.barrier()
         d_attn = ex.received_dattn().clone()
-        torch.autograd.backward(attn, d_attn.reshape(attn.shape))         # fills qkv.grad and the core's own parameters
+        # fills qkv.grad and the core's own parameters; the graph is retained because cores of later blocks may share
+        # sub-graphs with this one (EAGLE's depth-0 keys and values are reused by every later depth)
+        torch.autograd.backward(attn, d_attn.reshape(attn.shape), retain_graph=True)
         ex.publish_dqkv(qkv.grad)
         ex.barrier()
         dx, d_wg = ex.projection_backward(x, w_grouped)

@@ -177,6 +177,60 @@ def _worker(rank, world, port, out_path):
         res["ulysses_block_dw"] = ok
         barrier()
 
+        # ---- EAGLE3 training wrapper, sequence parallel over the Ulysses block, against one GPU over the whole row ----
+        from aspec_b200.config.draft_config import AutoDraftModelConfig
+        from aspec_b200.training.factory import build_training_model
+        raw6 = dict(architectures=["LlamaForCausalLMEagle3"], model_type="llama", hidden_size=256, intermediate_size=512,
+                    num_attention_heads=4, num_key_value_heads=2, head_dim=128, vocab_size=512, draft_vocab_size=512,
+                    target_hidden_size=256, num_aux_hidden_states=3, rope_theta=10000.0, max_position_embeddings=2048)
+        args6 = dict(ttt_length=3, seed=0)
+        torch.manual_seed(6)
+        ref6 = build_training_model(AutoDraftModelConfig.from_dict(raw6), args6, dev, bf)
+        par6 = build_training_model(AutoDraftModelConfig.from_dict(raw6), args6, dev, bf)
+        for prm in ref6.parameters():
+            dist.broadcast(prm.data, 0)
+        par6.load_state_dict(ref6.state_dict())
+        T6 = 301                                                        # odd on purpose: the row is padded to the group size
+        g6 = torch.Generator(device="cpu").manual_seed(66)
+        batch6 = dict(input_ids=torch.randint(0, 500, (1, T6), generator=g6).to(dev),
+                      hidden_states_list=(torch.randn(1, T6, 768, generator=g6) * 0.5).to(dev, bf),
+                      loss_mask=torch.cat([torch.zeros(1, 40), torch.ones(1, T6 - 40)], 1).to(dev),
+                      lm_head_weight=(torch.randn(512, 256, generator=g6) * 0.05).to(dev, bf),
+                      last_hidden_states=(torch.randn(1, T6, 256, generator=g6) * 0.5).to(dev, bf),
+                      ctx_doc_ids=torch.cat([torch.zeros(1, 120), torch.ones(1, T6 - 120)], 1).long().to(dev))
+        ref6.train()
+        par6.train()
+        out_r = ref6(**batch6)
+        out_r[6][0].backward()
+        d6 = par6.draft_model
+        sa6 = d6.midlayer.self_attn
+        rows6 = -(-T6 // world)
+        qc6 = (sa6.num_heads + 2 * sa6.num_kv_heads) * sa6.head_dim // world
+        oc6 = sa6.num_heads * sa6.head_dim // world
+        uws6 = exchange_workspaces(UlyssesWorkspace(world, rows6 + 8, qc6, oc6, device=dev), UlyssesWorkspace.open)
+        d6.ulysses = UlyssesExchange(rank, world, uws6, barrier)
+        par6.sequence_parallel = (rank, world, None)
+        out_p = par6(**batch6)
+        out_p[6][0].backward()
+        num6 = out_p[6][0].detach().float().clone()
+        den6 = out_p[6][1].detach().float().clone()
+        dist.all_reduce(num6)
+        dist.all_reduce(den6)
+        res["sp_eagle_loss"] = _close(num6 / den6, out_r[6][0].detach().float() / out_r[6][1].float(), 2e-2, 2e-2)
+        res["sp_eagle_counts"] = bool(torch.equal(out_p[4], out_r[4]))
+        ok6, worst6 = True, ""
+        for (n, pp), (_, pr) in zip(par6.draft_model.named_parameters(), ref6.draft_model.named_parameters()):
+            if pr.grad is None:
+                continue
+            g = (pp.grad if pp.grad is not None else torch.zeros_like(pr)).float().clone()
+            dist.all_reduce(g)
+            if not _close(g, pr.grad, 8e-2, 4e-2 * max(pr.grad.float().abs().max().item(), 1e-3)):
+                ok6, worst6 = False, n
+        res["sp_eagle_grads"] = ok6
+        if not ok6:
+            res["sp_eagle_worst"] = worst6
+        barrier()
+
         # ---- expert parallelism: fused peer-memory dispatch / combine against the NCCL all-to-all path ------------
         from aspec_b200.models.draft.moe import ExpertBank
         from aspec_b200.parallel.expert_parallel import (EPWorkspace, FusedExpertParallel, dispatch_combine,
