@@ -31,8 +31,12 @@ def _adjacent(params: Sequence[torch.Tensor]) -> bool:
     if any(not p.is_contiguous() for p in params):
         return False
     esz = params[0].element_size()
+    storage = params[0].untyped_storage().data_ptr()
     for a, b in zip(params[:-1], params[1:]):
         if a.data_ptr() + a.numel() * esz != b.data_ptr() or a.dtype != b.dtype:
+            return False
+        # separately allocated tensors can be neighbours in the allocator's block by chance: the fused view needs one storage
+        if b.untyped_storage().data_ptr() != storage:
             return False
     return True
 
