@@ -136,21 +136,27 @@ class UlyssesExchange:
     def publish_attention(self, attn: torch.Tensor) -> None:
         self.mine.attn.copy_(attn.reshape(self.mine.attn.shape))
 
-    def output_projection(self, w_o: torch.Tensor) -> torch.Tensor:
-        """``out[T_loc, D] = sum_g attn_g[my rows] @ W_o[:, cols_g]^T`` with ``attn_g`` read from rank ``g``."""
+    def output_projection(self, w_o: torch.Tensor, return_rows: bool = False):
+        """``out[T_loc, D] = sum_g attn_g[my rows] @ W_o[:, cols_g]^T`` with ``attn_g`` read from rank ``g``.  With
+        ``return_rows`` also returns the pulled row blocks: the backward pass needs exactly these (the peers' buffers
+        are overwritten by the next exchange)."""
         c = self.mine.out_cols
-        self._attn_rows = self._pull([w.attn[self._rows(self.rank)] for w in self.ws])
-        return _multi_source(self._attn_rows, [w_o[:, g * c:(g + 1) * c] for g in range(self.world)])
+        rows = self._pull([w.attn[self._rows(self.rank)] for w in self.ws])
+        if rows[self.rank].data_ptr() == self.mine.attn[self._rows(self.rank)].data_ptr():
+            rows[self.rank] = rows[self.rank].clone() if return_rows else rows[self.rank]
+        out = _multi_source(rows, [w_o[:, g * c:(g + 1) * c] for g in range(self.world)])
+        return (out, rows) if return_rows else out
 
     # -- backward -----------------------------------------------------------------------------------------
-    def output_projection_backward(self, dout: torch.Tensor, w_o: torch.Tensor):
-        """``d attn_g[my rows] = dout @ W_o[:, cols_g]`` scattered to rank ``g``; returns ``dW_o`` (fp32)."""
+    def output_projection_backward(self, dout: torch.Tensor, w_o: torch.Tensor, attn_rows=None):
+        """``d attn_g[my rows] = dout @ W_o[:, cols_g]`` scattered to rank ``g``; returns ``dW_o`` (fp32).  ``attn_rows``:
+        the blocks ``output_projection`` returned; without them the peers' buffers are read again (only valid when no
+        other exchange ran in between)."""
         from aspec_b200.ops import gemm as G
         dests = [w.dattn[self._rows(self.rank)] for w in self.ws]
         G.gemm(dout, w_o, b_t=True, mirrors=dests, scatter_cols=self.mine.out_cols)
-        c = self.mine.out_cols
-        attn_rows = getattr(self, "_attn_rows", None) or self._pull([w.attn[self._rows(self.rank)] for w in self.ws])
-        self._attn_rows = None
+        if attn_rows is None:
+            attn_rows = self._pull([w.attn[self._rows(self.rank)] for w in self.ws])
         parts = [G.gemm(dout, a, a_t=True, b_t=True, out_dtype=torch.float32, stream_k=False) for a in attn_rows]
         return torch.cat(parts, 1)                # [D, Hq*d] columns grouped by rank, as W_o's
 

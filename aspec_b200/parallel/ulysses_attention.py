@@ -29,10 +29,10 @@ class _UlyssesBlockFn(torch.autograd.Function):
             attn = core(qkv)                                              # [T_tot, my head columns]
         ex.publish_attention(attn.detach())
         ex.barrier()
-        out = ex.output_projection(w_o)
+        out, attn_rows = ex.output_projection(w_o, return_rows=True)
         ex.barrier()                                                      # peers have read this rank's attention rows
         ctx.ex = ex
-        ctx.graph = (qkv, attn)
+        ctx.graph = (qkv, attn, attn_rows)
         ctx.save_for_backward(x, w_grouped, w_o)
         return out
 
@@ -40,8 +40,9 @@ class _UlyssesBlockFn(torch.autograd.Function):
     def backward(ctx, dout):
         ex = ctx.ex
         x, w_grouped, w_o = ctx.saved_tensors
-        qkv, attn = ctx.graph
-        d_wo = ex.output_projection_backward(dout.contiguous(), w_o)      # scatters d attn to the head owners
+        qkv, attn, attn_rows = ctx.graph
+        ex.set_rows(x.shape[0])
+        d_wo = ex.output_projection_backward(dout.contiguous(), w_o, attn_rows)   # scatters d attn to the head owners
         ex.barrier()
         d_attn = ex.received_dattn().clone()
         # fills qkv.grad and the core's own parameters; the graph is retained because cores of later blocks may share
