@@ -81,6 +81,7 @@ class Eagle3Model(nn.Module):
         self.block_size = self.length          # per-position metrics have one slot per depth
 
     uses_target_distribution = True
+    supports_sequence_parallel = True       # ``sequence_parallel = (rank, size, group)`` + ``draft_model.ulysses``
 
     # -- per-depth loss ---------------------------------------------------------------------------
     def _depth_loss(self, hidden, rows, teacher_rows, target: LazyTarget):

@@ -97,7 +97,11 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
     world = len(draft_devs)
     # ranks that must see the same rows: a context-parallel group shares a row's shards, a vocabulary-parallel group
     # shares its supervised rows
-    cp = max(int(flat.get("draft_context_parallel_size", 1)), 1) * max(int(flat.get("vocab_parallel_size", 1) or 1), 1)
+    usp = max(int(flat.get("sp_ulysses_size", 1) or 1), 1) * max(int(flat.get("sp_ring_size", 1) or 1), 1)
+    cp = max(int(flat.get("draft_context_parallel_size", 1)), 1)
+    if algorithm in ("eagle3", "eagle4"):
+        cp = max(cp, usp)                  # the planner folds the sequence-parallel degree into the context-parallel size
+    cp *= max(int(flat.get("vocab_parallel_size", 1) or 1), 1)
     dp = world // cp
     args = dict(flat)
     args.update(trainer_devices=draft_devs, run_id=flat.get("run_id") or f"run-{int(time.time())}",

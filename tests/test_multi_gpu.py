@@ -283,3 +283,64 @@ def test_peer_memory_layers_on_two_gpus(tmp_path):
         bad = [k for k, v in res.items() if isinstance(v, bool) and not v]
         assert not bad, (rank, bad, res)
         assert res["fsdp_state_bytes"] * 2 <= res["repl_state_bytes"] + 12 * 16
+
+
+def _eagle_recipe(tmp_path, name, gpus, extra=""):
+    import json
+    draft = tmp_path / "eagle3_small.json"
+    draft.write_text(json.dumps(dict(
+        architectures=["LlamaForCausalLMEagle3"], model_type="llama", hidden_size=256, intermediate_size=512,
+        num_attention_heads=4, num_key_value_heads=2, head_dim=128, vocab_size=512, draft_vocab_size=512, target_hidden_size=256,
+        target_num_hidden_layers=8, num_aux_hidden_states=3, rope_theta=10000.0, max_position_embeddings=2048)))
+    recipe = tmp_path / f"{name}.yaml"
+    recipe.write_text(f"""
+model:
+  draft_model_config: {draft}
+dataset:
+  train_data_path: synthetic
+  synthetic_num_documents: 32
+  synthetic_min_length: 200
+  synthetic_max_length: 420
+  shuffle_dataset: false
+inference:
+  inference_engine_type: synthetic
+training:
+  training_num_gpus_per_node: {gpus}
+  micro_batch_size: 1
+  draft_accumulation_steps: 2
+  max_seq_length: 512
+  num_train_steps: 3
+  learning_rate: 1e-3
+  ttt_length: 3
+  save_interval: 0
+  save_final_checkpoint: false
+  seed: 11
+{extra}
+transport:
+  destination_ring_slots: 4
+output_dir: {tmp_path / name}
+""")
+    from aspec_b200.config.train_config import load_config
+    from aspec_b200.planning import compile_execution_plan
+    return compile_execution_plan(load_config(str(recipe), []))
+
+
+@pytest.mark.timeout(900)
+def test_sequence_parallel_eagle3_pipeline_matches_one_gpu(tmp_path):
+    """The whole pipeline (driver, synthetic engine, trainer processes): EAGLE3 with ``sp_ulysses_size: 2`` on two GPUs
+    trains on the same rows as one GPU and reports the same losses."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from aspec_b200.train_entry import train_async_no_generation
+    losses = {}
+    for name, gpus, extra in (("one", 1, ""), ("sp2", 2, "  sp_ulysses_size: 2")):
+        plan = _eagle_recipe(tmp_path, name, gpus, extra)
+        flat = plan.to_runtime_args()
+        flat.update(synthetic_vocab_size=500)
+        os.makedirs(flat["output_dir"], exist_ok=True)
+        logs = []
+        summary = train_async_no_generation(flat, plan.draft_config, log=logs.append)
+        assert summary["completed_steps"] == 3 and summary["ledger"]["validated"]
+        losses[name] = [l["train/avg_loss"] for l in logs]
+    assert losses["one"][0] == pytest.approx(losses["sp2"][0], rel=3e-2)
+    assert losses["one"][-1] == pytest.approx(losses["sp2"][-1], rel=6e-2)
