@@ -18,6 +18,7 @@ from __future__ import annotations
 from typing import Callable, List, Optional, Sequence
 
 import torch
+import torch.distributed as dist
 
 from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
 
@@ -173,4 +174,69 @@ class UlyssesExchange:
         srcs = self._pull([w.dqkv[self._rows(self.rank)] for w in self.ws])
         dx = _multi_source(srcs, [w_grouped[g * c:(g + 1) * c] for g in range(self.world)], b_t=True)
         dw = torch.cat([G.gemm(s, x, a_t=True, b_t=True, out_dtype=torch.float32, stream_k=False) for s in srcs], 0)
+        return dx, dw
+
+
+class CollectiveUlyssesExchange:
+    """The exchange's phase interface over ``torch.distributed`` collectives (any backend, any device): the reference
+    statement of ``UlyssesExchange`` for CPU / gloo tests of the sequence-parallel model paths.  Every phase that moves
+    data is one all-gather followed by a slice (gloo has no all-to-all)."""
+
+    def __init__(self, rank: int, world: int, group=None):
+        self.rank, self.world, self.group = rank, world, group
+        self.rows = 0
+        self.barrier = lambda: None
+
+    def set_rows(self, rows: int) -> None:
+        self.rows = int(rows)
+
+    def _rows(self, r: int) -> slice:
+        return slice(r * self.rows, (r + 1) * self.rows)
+
+    def _gather(self, x: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(x) for _ in range(self.world)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.stack(parts)
+
+    def _cols(self, full: torch.Tensor, width: int) -> torch.Tensor:
+        """``full [world, rows, world * width]`` gathered from all sources -> this rank's column block of every source."""
+        return torch.cat([full[s][:, self.rank * width:(self.rank + 1) * width] for s in range(self.world)], 0)
+
+    def project_scatter(self, x: torch.Tensor, w_grouped: torch.Tensor) -> None:
+        self.rows = x.shape[0]
+        self._qkv = self._cols(self._gather(x @ w_grouped.T), w_grouped.shape[0] // self.world)
+
+    def received_qkv(self) -> torch.Tensor:
+        return self._qkv
+
+    def publish_attention(self, attn: torch.Tensor) -> None:
+        self._attn = attn.reshape(self.world * self.rows, -1)
+
+    def output_projection(self, w_o: torch.Tensor, return_rows: bool = False):
+        full = self._gather(self._attn)                                   # [world, T_tot, out_cols]
+        c = full.shape[-1]
+        rows = [full[g][self._rows(self.rank)] for g in range(self.world)]
+        out = sum(rows[g] @ w_o[:, g * c:(g + 1) * c].T for g in range(self.world))
+        return (out, rows) if return_rows else out
+
+    def output_projection_backward(self, dout: torch.Tensor, w_o: torch.Tensor, attn_rows=None):
+        c = w_o.shape[1] // self.world
+        self._dattn = self._cols(self._gather(dout @ w_o), c)
+        if attn_rows is None:
+            full = self._gather(self._attn)
+            attn_rows = [full[g][self._rows(self.rank)] for g in range(self.world)]
+        return torch.cat([dout.float().T @ a.float() for a in attn_rows], 1)
+
+    def received_dattn(self) -> torch.Tensor:
+        return self._dattn
+
+    def publish_dqkv(self, dqkv: torch.Tensor) -> None:
+        self._dqkv = dqkv.reshape(self.world * self.rows, -1)
+
+    def projection_backward(self, x: torch.Tensor, w_grouped: torch.Tensor):
+        full = self._gather(self._dqkv)
+        c = full.shape[-1]
+        srcs = [full[g][self._rows(self.rank)] for g in range(self.world)]
+        dx = sum(srcs[g] @ w_grouped[g * c:(g + 1) * c] for g in range(self.world))
+        dw = torch.cat([s.float().T @ x.float() for s in srcs], 0)
         return dx, dw

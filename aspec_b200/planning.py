@@ -155,6 +155,14 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
         "head dim 128 GQA uses the TMEM flash kernels" if not (mla or head_dim != 128)
         else "materialised MLA / non-128 head dim runs the fp32 dense-mask path"))
     caps.append(CapabilityDecision("vocab_head", "fused_rowstats_gemm+streaming_loss", "logits stay bf16; no fp32 [rows, V]"))
+    # a trainer holds the slots of all micro-batches of an update until its optimizer step commits, and the next
+    # update's rows are dispatched meanwhile: fewer slots than that deadlock the producer against the consumer
+    need_slots = int(flat["draft_accumulation_steps"]) * int(flat["micro_batch_size"]) + 1
+    if int(flat.get("transport_destination_ring_slots", 1) or 1) < need_slots:
+        caps.append(CapabilityDecision("feature_ring", f"destination_ring_slots raised to {need_slots}",
+                                       f"configured {flat.get('transport_destination_ring_slots')}: one update keeps "
+                                       f"{need_slots - 1} slots leased until its optimizer step commits"))
+        flat["transport_destination_ring_slots"] = need_slots
     caps.append(CapabilityDecision("feature_transport", flat["transport_data_plane"],
                                    "Target epilogues store into the Draft ranks' ring slots over NVLink"))
     caps.append(CapabilityDecision("data_parallel", flat["fsdp_strategy"],

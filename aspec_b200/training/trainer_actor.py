@@ -58,10 +58,8 @@ class TrainerActor:
                                                head_dim=int(cfg.head_dim), device=self.device))
         # the reference splits a sequence-parallel group into Ulysses x ring; here the whole group exchanges heads
         self.sp_size = max(int(self.args.get("sp_ulysses_size", 1) or 1), 1) * max(int(self.args.get("sp_ring_size", 1) or 1), 1)
-        if self.sp_size > 1 and self.cuda and world > 1 and getattr(self.model, "supports_sequence_parallel", False):
+        if self.sp_size > 1 and world > 1 and getattr(self.model, "supports_sequence_parallel", False):
             # ranks [g * sp, (g + 1) * sp) share every row: each keeps a slice of the tokens, attention heads are exchanged
-            from aspec_b200.parallel.group import exchange_workspaces, make_barrier
-            from aspec_b200.parallel.ulysses import UlyssesExchange, UlyssesWorkspace
             if world % self.sp_size:
                 raise ValueError("sp_ulysses_size must divide the Draft world size")
             heads, kv_heads, hd = int(cfg.num_attention_heads), int(cfg.num_key_value_heads), int(cfg.head_dim)
@@ -69,11 +67,18 @@ class TrainerActor:
                 raise ValueError("sp_ulysses_size must divide the attention head counts")
             groups = [dist.new_group(list(range(g * self.sp_size, (g + 1) * self.sp_size))) for g in range(world // self.sp_size)]
             mine = groups[rank // self.sp_size]
-            rows = -(-int(self.args["max_seq_length"]) // self.sp_size) + 8
-            ws = exchange_workspaces(UlyssesWorkspace(self.sp_size, rows, (heads + 2 * kv_heads) * hd // self.sp_size,
-                                                      heads * hd // self.sp_size, device=self.device),
-                                     UlyssesWorkspace.open, group=mine)
-            self.model.draft_model.ulysses = UlyssesExchange(rank % self.sp_size, self.sp_size, ws, make_barrier(self.device, mine))
+            if self.cuda:
+                from aspec_b200.parallel.group import exchange_workspaces, make_barrier
+                from aspec_b200.parallel.ulysses import UlyssesExchange, UlyssesWorkspace
+                rows = -(-int(self.args["max_seq_length"]) // self.sp_size) + 8
+                ws = exchange_workspaces(UlyssesWorkspace(self.sp_size, rows, (heads + 2 * kv_heads) * hd // self.sp_size,
+                                                          heads * hd // self.sp_size, device=self.device),
+                                         UlyssesWorkspace.open, group=mine)
+                exchange = UlyssesExchange(rank % self.sp_size, self.sp_size, ws, make_barrier(self.device, mine))
+            else:
+                from aspec_b200.parallel.ulysses import CollectiveUlyssesExchange
+                exchange = CollectiveUlyssesExchange(rank % self.sp_size, self.sp_size, mine)
+            self.model.draft_model.ulysses = exchange
             self.model.sequence_parallel = (rank % self.sp_size, self.sp_size, mine)
         layout = SlotLayout(int(self.args["max_seq_length"]), int(getattr(cfg, "num_target_layers", None)
                                                                    or getattr(cfg, "num_aux_hidden_states", 3)),

@@ -151,3 +151,52 @@ def test_held_out_evaluation_runs_and_replays_from_the_trainer_cache(tmp_path):
     assert [h["from_cache"] for h in record["history"]] == [False, True, True]      # the Target served the eval split once
     assert record["best"]["metric"] == "eval/avg_loss"
     assert summary["completed_steps"] == 3 and summary["ledger"]["validated"]
+
+
+@pytest.mark.timeout(900)
+def test_sequence_parallel_eagle3_pipeline_on_two_gloo_ranks(tmp_path):
+    """EAGLE3 with ``sp_ulysses_size: 2``: two CPU trainer ranks share every row and report the loss of a one-rank run."""
+    draft = tmp_path / "eagle3_tiny.json"
+    draft.write_text(json.dumps(dict(
+        architectures=["LlamaForCausalLMEagle3"], model_type="llama", hidden_size=32, intermediate_size=64, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=8, vocab_size=512, draft_vocab_size=512, target_hidden_size=32, target_num_hidden_layers=4,
+        num_aux_hidden_states=3, rope_theta=10000.0, max_position_embeddings=256)))
+    losses = {}
+    for name, gpus, extra in (("one", 1, ""), ("sp2", 2, "  sp_ulysses_size: 2")):
+        recipe = tmp_path / f"{name}.yaml"
+        recipe.write_text(f"""
+model:
+  draft_model_config: {draft}
+dataset:
+  train_data_path: synthetic
+  synthetic_num_documents: 16
+  synthetic_min_length: 40
+  synthetic_max_length: 90
+  shuffle_dataset: false
+inference:
+  inference_engine_type: synthetic
+training:
+  training_num_gpus_per_node: {gpus}
+  micro_batch_size: 1
+  draft_accumulation_steps: 2
+  max_seq_length: 128
+  num_train_steps: 2
+  learning_rate: 1e-3
+  ttt_length: 3
+  save_interval: 0
+  save_final_checkpoint: false
+  seed: 3
+{extra}
+transport:
+  destination_ring_slots: 4
+output_dir: {tmp_path / name}
+""")
+        plan = compile_execution_plan(load_config(str(recipe), []))
+        flat = plan.to_runtime_args()
+        flat.update(synthetic_vocab_size=500, force_cpu=True)
+        os.makedirs(flat["output_dir"], exist_ok=True)
+        logs = []
+        summary = train_async_no_generation(flat, plan.draft_config, log=logs.append)
+        assert summary["completed_steps"] == 2 and summary["ledger"]["validated"]
+        losses[name] = [l["train/avg_loss"] for l in logs]
+    assert losses["sp2"] == pytest.approx(losses["one"], rel=1e-3)
