@@ -23,14 +23,14 @@ def main(argv=None) -> int:
     ap.add_argument("--resume", action="store_true")
     a = ap.parse_args(argv)
     import torch
-    from aspec_b200.assets import find_asset
+    from aspec_b200.assets import find_asset, load_draft_config
     from aspec_b200.config.draft_config import AutoDraftModelConfig, resolve_draft_algorithm
     from aspec_b200.data.dataset import load_training_samples
     from aspec_b200.inference.factory import target_config_from_args
     from aspec_b200.models.target.dense import DenseTarget, TargetConfig
     from aspec_b200.multi_draft import _layer_ids
     from aspec_b200.offline.generate import materialize, target_binding
-    draft = json.load(open(find_asset(a.draft_config)))
+    draft = load_draft_config(a.draft_config)
     algorithm = resolve_draft_algorithm(draft)
     layers = _layer_ids(draft)
     tcfg = (TargetConfig.from_file(a.target_config).to_dict() if a.target_config

@@ -62,14 +62,8 @@ def _load_draft(flat: Dict[str, Any]) -> dict:
     path = flat.get("draft_model_config")
     if not path:
         raise ValueError("model.draft_model_config is required")
-    if isinstance(path, dict):
-        raw = path
-    else:
-        if not os.path.exists(path):
-            from aspec_b200.assets import find_asset
-            path = find_asset(path)
-        raw = json.load(open(path))
-    return AutoDraftModelConfig.from_dict(raw).to_dict()
+    from aspec_b200.assets import load_draft_config
+    return AutoDraftModelConfig.from_dict(load_draft_config(path)).to_dict()
 
 
 def resolve_batch_size(flat: Dict[str, Any], dp: int) -> dict:

@@ -14,7 +14,9 @@ from aspec_b200.planning import compile_execution_plan
 
 ROOT = os.path.dirname(os.path.abspath(aspec_b200.__file__))
 RECIPES = sorted(glob.glob(os.path.join(ROOT, "recipes", "*.yaml")))
-DRAFTS = sorted(glob.glob(os.path.join(ROOT, "config", "drafts", "*.json")))
+from aspec_b200.assets import draft_catalog, load_draft_config
+
+DRAFTS = sorted(draft_catalog())
 
 
 @pytest.mark.parametrize("path", RECIPES, ids=[os.path.basename(p) for p in RECIPES])
@@ -31,9 +33,19 @@ def test_recipe_loads_and_plans(path):
     assert resolve_draft_algorithm(plan.draft_config) in ("dspark", "dflash", "dflash2", "eagle3", "eagle4", "mtp")
 
 
-@pytest.mark.parametrize("path", DRAFTS, ids=[os.path.basename(p) for p in DRAFTS])
+def test_the_catalog_covers_every_family():
+    names = set(DRAFTS)
+    assert len(names) >= 37
+    for want in ("dspark_qwen3_8b_5layer", "dflash_base", "dflash2_qwen3_8b_swa", "eagle3_qwen3_8b_pruned", "eagle4_qwen3_8b_candidate",
+                 "qwen3_5_9b_mtp", "dspark_qwen3_5_9b_dmtp", "dspark_ling3_flash_csa_sparse", "dspark_ling3_flash_qsa_indexer",
+                 "dspark_qwen3_8b_dsa_sparse", "dspark_ling31_flash_mla_moe", "eagle3_qwen3_8b_mla", "dspark_qwen3_8_27b"):
+        assert want in names, want
+    assert load_draft_config("eagle3_qwen3_8b.json") == load_draft_config("eagle3_qwen3_8b")
+
+
+@pytest.mark.parametrize("path", DRAFTS)
 def test_bundled_draft_config_builds(path):
-    raw = json.load(open(path))
+    raw = load_draft_config(path)
     cfg = AutoDraftModelConfig.from_dict(raw)
     with torch.device("meta"):
         model = AutoEagle3DraftModel.from_config(cfg)
