@@ -1,16 +1,24 @@
-"""EAGLE4 MoE feed-forward: sigmoid router with a loss-free load-balancing bias, packed routed experts
-(``sparse_swiglu`` as ``w13 | w2``, or ``nemotron_latent_relu2`` running ReLU^2 experts in a latent width between two
-dense projections) and optional shared experts (reference: aspec/models/draft/eagle4_moe.py:38-213).
+"""Mixture-of-experts feed-forward of the EAGLE4 Draft.
 
-Routing: ``scores = sigmoid(W x)`` in fp32; the bias only selects (optionally group-limited by the sum of each
-group's top-2), the un-biased scores weight the selected experts, renormalised and scaled.  ``down`` projections
-start at zero so that a freshly added routed bank is a no-op.  The load observed on valid query rows is committed
-to the router once per optimizer step and moves the bias by ``rate * sign(mean - load)``.
+Two expert layouts share one module (parameter names follow the reference's checkpoints,
+aspec/models/draft/eagle4_moe.py:38-213, so its weights load unchanged):
+
+* ``sparse_swiglu``: ``experts.w13_weight [E, 2I, D]`` (gate rows, then up rows) and ``experts.w2_weight [E, D, I]``;
+  on CUDA in bf16 the whole bank runs as grouped tcgen05 launches (``ops/grouped_gemm.py``);
+* ``nemotron_latent_relu2``: the tokens are projected to a latent width, every expert is ``down(relu(up(x))^2)`` in
+  that width, and the sum is projected back.
+
+Routing is sigmoid scoring with a selection-only bias: ``sigmoid(W x) + bias`` picks the experts (optionally only
+inside the ``topk_group`` groups whose two best biased scores sum highest), the unbiased scores of the picked experts
+are the mixing weights (renormalised, then scaled).  The bias is the loss-free balancer: once per optimizer step it
+moves by ``rate * sign(mean load - load)`` with the load counted on valid query rows.  ``down`` projections start at
+zero, so a freshly initialised routed bank adds nothing to the residual stream.
 """
 from __future__ import annotations
 
 import re
 from collections import defaultdict
+from typing import Callable, Dict, List, Tuple
 
 import torch
 import torch.distributed as dist
@@ -20,152 +28,193 @@ import torch.nn.functional as F
 from aspec_b200.ops.linear import Linear, linear
 
 LATENT_MOE = "nemotron_latent_relu2"
-_PACKED = re.compile(r"(.*\.experts)\.(up_proj|down_proj)")
-_PER_EXPERT = re.compile(r"(.*\.experts)\.(\d+)\.(up_proj|down_proj)\.weight")
+
+_ACTIVATIONS: Dict[str, Callable[[torch.Tensor], torch.Tensor]] = {
+    "silu": F.silu, "gelu": F.gelu, "relu": F.relu, "relu2": lambda t: F.relu(t).square()}
 
 
-def _activation(name: str):
-    if name == "relu2":
-        return lambda x: F.relu(x).square()
-    return {"silu": F.silu, "gelu": F.gelu, "relu": F.relu}[name]
+def select_experts(scores: torch.Tensor, bias: torch.Tensor, top_k: int, n_group: int, topk_group: int) -> torch.Tensor:
+    """Indices ``[N, top_k]`` of the experts with the highest biased scores, restricted to the best groups."""
+    ranked = scores + bias
+    if n_group > 1:
+        per_group = ranked.view(ranked.shape[0], n_group, -1)
+        group_value = per_group.topk(2, dim=-1).values.sum(-1)                    # two best members speak for a group
+        chosen = group_value.topk(topk_group, dim=-1).indices
+        allowed = torch.zeros_like(group_value, dtype=torch.bool).scatter_(1, chosen, True)
+        ranked = per_group.masked_fill(~allowed[..., None], float("-inf")).flatten(1)
+    return ranked.topk(top_k, dim=-1).indices
 
 
 class Eagle4Router(nn.Module):
+    """Scoring matrix, the balancing bias (kept in fp32 whatever the module is cast to) and the load counter."""
+
     def __init__(self, config):
         super().__init__()
-        n = config.n_routed_experts
-        self.weight = nn.Parameter(torch.empty(n, config.hidden_size).normal_(std=getattr(config, "initializer_range", 0.02)))
-        self.register_buffer("e_score_correction_bias", torch.zeros(n))
-        self.register_buffer("load", torch.zeros(n, dtype=torch.long), persistent=False)
-        self.update_rate = getattr(config, "expert_bias_update_rate", getattr(config, "moe_router_bias_update_rate", 1e-3))
+        experts = int(config.n_routed_experts)
+        std = getattr(config, "initializer_range", 0.02)
+        self.weight = nn.Parameter(torch.randn(experts, config.hidden_size) * std)
+        self.register_buffer("e_score_correction_bias", torch.zeros(experts))
+        self.register_buffer("load", torch.zeros(experts, dtype=torch.long), persistent=False)
+        rate = getattr(config, "expert_bias_update_rate", None)
+        self.update_rate = rate if rate is not None else getattr(config, "moe_router_bias_update_rate", 1e-3)
 
     def _apply(self, fn, recurse=True):
-        bias = self.e_score_correction_bias
+        # steps of 1e-3 vanish in bf16 once the bias is a few tenths: carry the fp32 values across any cast
+        exact = self.e_score_correction_bias.detach().float().clone()
         super()._apply(fn, recurse)
-        # bf16 cannot represent 1e-3 steps once |bias| passes 0.25, so the bias keeps fp32 through casts
-        self.e_score_correction_bias = bias.to(device=self.e_score_correction_bias.device, dtype=torch.float32)
+        self.e_score_correction_bias = exact.to(self.e_score_correction_bias.device)
         return self
+
+    def scores(self, x: torch.Tensor) -> torch.Tensor:
+        return torch.sigmoid(x.float() @ self.weight.float().t())
 
     @torch.no_grad()
     def update_bias(self, *, apply_update: bool = True, group=None) -> torch.Tensor:
-        """Once per optimizer step; returns max / mean expert load."""
-        load = self.load.float()
+        """Fold the committed load into the bias (once per optimizer step).  Returns max load / mean load."""
+        counts = self.load.to(torch.float32)
         if dist.is_available() and dist.is_initialized():
-            dist.all_reduce(load, group=group)
+            dist.all_reduce(counts, group=group)
         self.load.zero_()
-        if apply_update and float(load.sum()) > 0:
-            self.e_score_correction_bias.add_(self.update_rate * (load.mean() - load).sign())
-        return load.max() / load.mean().clamp_min(1.0)
+        mean = counts.mean()
+        if apply_update and counts.sum().item() > 0:
+            self.e_score_correction_bias += self.update_rate * torch.sign(mean - counts)
+        return counts.max() / mean.clamp_min(1.0)
 
 
 class SharedExpert(nn.Module):
-    def __init__(self, hidden_size, intermediate_size, act, gated):
+    """Always-on expert: gated (``act(gate) * up``) for the SwiGLU layout, plain ``act(up)`` for the latent layout."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, act, gated: bool):
         super().__init__()
-        if gated:
-            self.gate_proj = Linear(hidden_size, intermediate_size)
+        self.act = act
         self.up_proj = Linear(hidden_size, intermediate_size)
         self.down_proj = Linear(intermediate_size, hidden_size)
-        self.act = act
+        if gated:
+            self.gate_proj = Linear(hidden_size, intermediate_size)
 
-    def forward(self, x):
-        h = self.up_proj(x)
-        return self.down_proj(self.act(self.gate_proj(x)) * h if hasattr(self, "gate_proj") else self.act(h))
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        inner = self.up_proj(x)
+        inner = self.act(self.gate_proj(x)) * inner if hasattr(self, "gate_proj") else self.act(inner)
+        return self.down_proj(inner)
 
 
 class Eagle4MoE(nn.Module):
     def __init__(self, config):
         super().__init__()
+        hidden, inter, experts = config.hidden_size, config.moe_intermediate_size, int(config.n_routed_experts)
+        std = getattr(config, "initializer_range", 0.02)
         self.latent = getattr(config, "moe_architecture", "sparse_swiglu") == LATENT_MOE
-        self.top_k = config.num_experts_per_tok
+        self.hidden_act = config.hidden_act
+        self.act = _ACTIVATIONS[config.hidden_act]
+        self.top_k = int(config.num_experts_per_tok)
         self.n_group = getattr(config, "n_group", None) or 1
         self.topk_group = getattr(config, "topk_group", None) or self.n_group
         self.norm_topk_prob = getattr(config, "norm_topk_prob", True)
         self.routed_scaling_factor = getattr(config, "routed_scaling_factor", 1.0)
-        self.act = _activation(config.hidden_act)
-        n, D, inter = config.n_routed_experts, config.hidden_size, config.moe_intermediate_size
-        width = config.moe_latent_size if self.latent else D
         self.gate = Eagle4Router(config)
-        up = torch.empty(n, inter if self.latent else 2 * inter, width).normal_(std=getattr(config, "initializer_range", 0.02))
+        expert_width = config.moe_latent_size if self.latent else hidden
+        first_rows = inter if self.latent else 2 * inter
         self.expert_names = ("up_proj", "down_proj") if self.latent else ("w13_weight", "w2_weight")
-        self.experts = nn.ParameterDict({self.expert_names[0]: nn.Parameter(up),
-                                         self.expert_names[1]: nn.Parameter(torch.zeros(n, width, inter))})
+        self.experts = nn.ParameterDict({
+            self.expert_names[0]: nn.Parameter(torch.randn(experts, first_rows, expert_width) * std),
+            self.expert_names[1]: nn.Parameter(torch.zeros(experts, expert_width, inter))})
         if self.latent:
-            self.fc1_latent_proj = Linear(D, width)
-            self.fc2_latent_proj = Linear(width, D)
-        n_shared = getattr(config, "n_shared_experts", None) or 0
-        shared_inter = config.moe_shared_expert_intermediate_size if self.latent else inter
-        self.shared_experts = SharedExpert(D, shared_inter * n_shared, self.act, gated=not self.latent) if n_shared else None
-        self.query_mask = None
+            self.fc1_latent_proj = Linear(hidden, expert_width)
+            self.fc2_latent_proj = Linear(expert_width, hidden)
+        shared = getattr(config, "n_shared_experts", None) or 0
+        self.shared_experts = None
+        if shared:
+            shared_inter = (config.moe_shared_expert_intermediate_size if self.latent else inter) * shared
+            self.shared_experts = SharedExpert(hidden, shared_inter, self.act, gated=not self.latent)
+        self.query_mask = None          # set by the training wrapper: rows that count for the load statistics
         self.last_load = None
 
-    def route(self, x):
-        scores = F.linear(x.float(), self.gate.weight.float()).sigmoid()
-        biased = scores + self.gate.e_score_correction_bias
-        if self.n_group > 1:
-            groups = biased.unflatten(-1, (self.n_group, -1))
-            best = groups.topk(2, -1).values.sum(-1).topk(self.topk_group, -1).indices
-            dropped = torch.ones_like(groups[..., 0], dtype=torch.bool).scatter_(1, best, False)
-            biased = groups.masked_fill(dropped[..., None], float("-inf")).flatten(1)
-        idx = biased.topk(self.top_k, -1).indices
-        w = scores.gather(1, idx)
+    # -- routing ----------------------------------------------------------------------------------------------------
+    def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        scores = self.gate.scores(x)
+        picked = select_experts(scores, self.gate.e_score_correction_bias, self.top_k, self.n_group, self.topk_group)
+        mix = torch.gather(scores, 1, picked)
         if self.norm_topk_prob:
-            w = w / w.sum(-1, keepdim=True)
-        return idx, w * self.routed_scaling_factor
+            mix = mix / mix.sum(-1, keepdim=True)
+        return picked, mix * self.routed_scaling_factor
 
-    def forward(self, hidden_states):
+    def _record_load(self, picked: torch.Tensor) -> None:
+        if not (self.training and any(p.requires_grad for p in self.parameters())):
+            return
+        per_row = torch.ones_like(picked)
+        if self.query_mask is not None:
+            per_row = self.query_mask.reshape(-1, 1).to(picked.dtype).expand_as(picked)
+        self.last_load = picked.new_zeros(self.gate.weight.shape[0]).scatter_add_(0, picked.reshape(-1), per_row.reshape(-1))
+
+    # -- experts ----------------------------------------------------------------------------------------------------
+    def _bank(self, rows: torch.Tensor, counts: List[int]) -> torch.Tensor:
+        """``rows`` sorted by expert (``counts[e]`` each) -> expert outputs in the same order."""
+        first, second = (self.experts[name] for name in self.expert_names)
+        swiglu_kernel = (not self.latent and self.hidden_act == "silu" and rows.is_cuda and rows.dtype == torch.bfloat16
+                         and first.dtype == torch.bfloat16 and rows.shape[0] > 0 and rows.shape[1] % 64 == 0
+                         and second.shape[2] % 64 == 0)
+        if swiglu_kernel:
+            from aspec_b200.ops.grouped_gemm import grouped_experts
+            return grouped_experts(rows, first, second, counts)
+        pieces, start = [], 0
+        for e, n in enumerate(counts):
+            if n:
+                inner = linear(rows[start:start + n], first[e].to(rows.dtype))
+                if self.latent:
+                    inner = self.act(inner)
+                else:
+                    gate, value = inner.chunk(2, dim=-1)
+                    inner = self.act(gate) * value
+                pieces.append(linear(inner.contiguous(), second[e].to(rows.dtype)))
+            start += n
+        anchor = (first.sum() + second.sum()).to(rows.dtype) * 0.0          # experts without rows still get (zero) grads
+        return (torch.cat(pieces, 0) if pieces else rows.new_zeros(0, second.shape[1])) + anchor
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
         x = hidden_states.reshape(-1, hidden_states.shape[-1])
-        idx, weights = self.route(x)
-        n_exp = self.gate.weight.shape[0]
-        if self.training and any(p.requires_grad for p in self.parameters()):
-            mask = self.query_mask
-            lw = torch.ones_like(idx) if mask is None else mask.reshape(-1, 1).expand_as(idx).to(idx.dtype)
-            self.last_load = idx.new_zeros(n_exp).scatter_add_(0, idx.flatten(), lw.flatten())
-        order = idx.flatten().argsort()
-        tokens = order // self.top_k
-        counts = torch.bincount(idx.flatten(), minlength=n_exp).tolist()
-        h = self.fc1_latent_proj(x) if self.latent else x
-        up, down = (self.experts[name] for name in self.expert_names)
-        rows = h[tokens]
-        outs, off = [], 0
-        for e, c in enumerate(counts):
-            if c == 0:
-                continue
-            inner = linear(rows[off:off + c], up[e].to(rows.dtype))
-            if self.latent:
-                inner = self.act(inner)
-            else:
-                g, v = inner.chunk(2, -1)
-                inner = self.act(g) * v
-            outs.append(linear(inner.contiguous(), down[e].to(rows.dtype)))
-            off += c
-        out = torch.cat(outs, 0) * weights.flatten()[order, None].to(rows.dtype)
-        out = h.new_zeros(h.shape).index_add_(0, tokens, out) + 0.0 * (up.sum() + down.sum()).to(h.dtype)
-        if self.latent:
-            out = self.fc2_latent_proj(out)
+        picked, mix = self.route(x)
+        self._record_load(picked)
+        flat = picked.reshape(-1)
+        by_expert = torch.argsort(flat)
+        token_of = by_expert // self.top_k
+        counts = torch.bincount(flat, minlength=self.gate.weight.shape[0]).tolist()
+        inner_x = self.fc1_latent_proj(x) if self.latent else x
+        produced = self._bank(inner_x[token_of], counts)
+        produced = produced * mix.reshape(-1)[by_expert].unsqueeze(-1).to(produced.dtype)
+        routed = torch.zeros_like(inner_x).index_add_(0, token_of, produced)
+        out = self.fc2_latent_proj(routed) if self.latent else routed
         if self.shared_experts is not None:
             out = out + self.shared_experts(x)
-        return out.view_as(hidden_states)
+        return out.reshape(hidden_states.shape)
+
+
+# -- checkpoint layouts of the latent experts --------------------------------------------------------------------------
+_STACKED = re.compile(r"(?P<bank>.*\.experts)\.(?P<proj>up_proj|down_proj)")
+_SINGLE = re.compile(r"(?P<bank>.*\.experts)\.(?P<index>\d+)\.(?P<proj>up_proj|down_proj)\.weight")
 
 
 def split_latent_experts(tensors: dict) -> dict:
-    """Packed latent experts -> one key per expert (the layout the serving loader reads)."""
-    out = {}
-    for key, value in tensors.items():
-        m = _PACKED.fullmatch(key)
-        if m:
-            out.update({f"{m[1]}.{i}.{m[2]}.weight": w.clone() for i, w in enumerate(value)})
-        else:
-            out[key] = value
-    return out
+    """``...experts.up_proj [E, ...]`` -> ``...experts.<e>.up_proj.weight`` (one tensor per expert, as serving loaders read them)."""
+    result = {}
+    for name, tensor in tensors.items():
+        hit = _STACKED.fullmatch(name)
+        if hit is None:
+            result[name] = tensor
+            continue
+        for index, one in enumerate(tensor.unbind(0)):
+            result[f"{hit['bank']}.{index}.{hit['proj']}.weight"] = one.clone()
+    return result
 
 
 def stack_latent_experts(tensors: dict) -> dict:
-    out, groups = {}, defaultdict(dict)
-    for key, value in tensors.items():
-        m = _PER_EXPERT.fullmatch(key)
-        if m:
-            groups[f"{m[1]}.{m[3]}"][int(m[2])] = value
+    """Inverse of ``split_latent_experts``."""
+    result, banks = {}, defaultdict(dict)
+    for name, tensor in tensors.items():
+        hit = _SINGLE.fullmatch(name)
+        if hit is None:
+            result[name] = tensor
         else:
-            out[key] = value
-    out.update({k: torch.stack([g[i] for i in sorted(g)]) for k, g in groups.items()})
-    return out
+            banks[f"{hit['bank']}.{hit['proj']}"][int(hit["index"])] = tensor
+    for name, members in banks.items():
+        result[name] = torch.stack([members[i] for i in sorted(members)])
+    return result
