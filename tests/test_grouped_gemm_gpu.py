@@ -85,3 +85,31 @@ def test_grouped_experts_match_the_per_expert_loop_forward_and_backward():
     assert torch.allclose(x.grad.float(), xr.grad, atol=0.03, rtol=0.05)
     assert torch.allclose(gu.grad.float(), gur.grad, atol=0.15, rtol=0.05)
     assert torch.allclose(dn.grad.float(), dnr.grad, atol=0.15, rtol=0.05)
+
+
+def test_eagle4_swiglu_moe_runs_on_the_grouped_kernels_and_matches_fp32():
+    """The EAGLE4 mixture-of-experts block: bf16 on the GPU (grouped launches) against the same module in fp32 on the CPU."""
+    from types import SimpleNamespace
+    from aspec_b200.models.draft.eagle4_moe import Eagle4MoE
+    cfg = SimpleNamespace(hidden_size=128, moe_intermediate_size=64, n_routed_experts=8, num_experts_per_tok=2, hidden_act="silu",
+                          n_group=2, topk_group=1, norm_topk_prob=True, routed_scaling_factor=1.5, n_shared_experts=1,
+                          moe_architecture="sparse_swiglu", initializer_range=0.05)
+    torch.manual_seed(0)
+    ref = Eagle4MoE(cfg)
+    with torch.no_grad():
+        ref.experts["w2_weight"].normal_(std=0.05)              # the bank starts as a no-op: give it something to compute
+    gpu = Eagle4MoE(cfg)
+    gpu.load_state_dict(ref.state_dict())
+    gpu = gpu.to("cuda", torch.bfloat16)
+    x = torch.randn(300, 128) * 0.5
+    xg = x.to("cuda", torch.bfloat16).requires_grad_(True)
+    xr = x.bfloat16().float().requires_grad_(True)
+    yg = gpu(xg)
+    yr = ref(xr)
+    dy = torch.randn(300, 128) * 0.1
+    yg.backward(dy.to("cuda", torch.bfloat16))
+    yr.backward(dy.bfloat16().float())
+    assert torch.allclose(yg.float().cpu(), yr, atol=0.05, rtol=0.05)
+    assert torch.allclose(xg.grad.float().cpu(), xr.grad, atol=0.05, rtol=0.1)
+    w13_g, w13_r = gpu.experts["w13_weight"].grad.float().cpu(), ref.experts["w13_weight"].grad
+    assert torch.allclose(w13_g, w13_r, atol=0.05 * max(w13_r.abs().max().item(), 1e-3) + 0.02, rtol=0.1)
