@@ -77,16 +77,45 @@ class UlyssesWorkspace:
         return cls(meta["world"], meta["rows"], meta["qkv_cols"], meta["out_cols"], buffer=SymmetricBuffer.open(meta["memory"]))
 
 
-def _multi_source(sources_a: Sequence[torch.Tensor], sources_b: Sequence[torch.Tensor], a_t=False, b_t=False,
-                  out_dtype=torch.bfloat16) -> torch.Tensor:
-    """``sum_g A_g @ B_g^T`` two sources per launch (the GEMM's dual K range), later launches accumulate."""
+def _multi_source(sources_a: Sequence[torch.Tensor], b_full: torch.Tensor, width: int, b_t: bool = False) -> torch.Tensor:
+    """``sum_g A_g @ B_g^T`` where ``A_g [M, width]`` are separate buffers and ``B_g`` is slice ``g`` of ``b_full`` along
+    the reduction index (columns ``[g * width, (g + 1) * width)`` of ``[N, world * width]``, or rows of
+    ``[world * width, N]`` when ``b_t``).  Two sources run as one dual-source launch of the dense kernel; more run as ONE
+    grouped launch whose output tiles each reduce over ``world`` K segments inside their accumulator."""
     from aspec_b200.ops import gemm as G
-    out = None
-    for i in range(0, len(sources_a), 2):
-        a2 = sources_a[i + 1] if i + 1 < len(sources_a) else None
-        b2 = sources_b[i + 1] if i + 1 < len(sources_b) else None
-        out = G.gemm(sources_a[i], sources_b[i], a_t=a_t, b_t=b_t, a2=a2, b2=b2, out=out, addend=out,
-                     out_dtype=out_dtype, stream_k=False)
+    world = len(sources_a)
+    piece = (lambda g: b_full[g * width:(g + 1) * width]) if b_t else (lambda g: b_full[:, g * width:(g + 1) * width])
+    if world <= 2:
+        a2, b2 = (sources_a[1], piece(1)) if world == 2 else (None, None)
+        return G.gemm(sources_a[0], piece(0), b_t=b_t, a2=a2, b2=b2, stream_k=False)
+    import numpy as np
+    from aspec_b200.ops import grouped_gemm as GG
+    M = sources_a[0].shape[0]
+    N = b_full.shape[1] if b_t else b_full.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=b_full.device)
+    m_tiles, n_tiles = -(-M // GG.BM), -(-N // GG.BN)
+    total = m_tiles * n_tiles
+    nt, mt = np.divmod(np.arange(total), m_tiles)
+    tiles = np.zeros(total, dtype=GG._TILE)
+    tiles["d"] = np.uint64(out.data_ptr()) + ((mt * GG.BM * out.stride(0) + nt * GG.BN) * 2).astype(np.uint64)
+    tiles["ldd"] = out.stride(0)
+    tiles["rows"] = np.minimum(GG.BM, M - mt * GG.BM)
+    tiles["cols"] = np.minimum(GG.BN, N - nt * GG.BN)
+    tiles["seg0"] = np.arange(total) * world
+    tiles["nseg"] = world
+    segs = np.zeros(total * world, dtype=GG._SEG)
+    g = np.tile(np.arange(world), total)
+    segs["a_map"] = g
+    segs["a_mn"] = np.repeat(mt * GG.BM, world)
+    segs["b_map"] = world
+    segs["b_mn"] = np.repeat(nt * GG.BN, world)
+    segs["b_k"] = g * width
+    segs["k_blocks"] = -(-width // GG.BK)
+    # a last partial k-block reads past the segment in B, but A's columns past ``width`` are the TMA zero fill
+    if width % 8:
+        raise ValueError("the per-rank reduction width must be a multiple of 8 elements (TMA alignment)")
+    operands = [(GG._as_2d(a), 0) for a in sources_a] + [(GG._as_2d(b_full), 1)]
+    GG._launch(operands, tiles, segs, False, b_t, False, 1.0, b_full.device)
     return out
 
 
@@ -145,7 +174,7 @@ class UlyssesExchange:
         rows = self._pull([w.attn[self._rows(self.rank)] for w in self.ws])
         if rows[self.rank].data_ptr() == self.mine.attn[self._rows(self.rank)].data_ptr():
             rows[self.rank] = rows[self.rank].clone() if return_rows else rows[self.rank]
-        out = _multi_source(rows, [w_o[:, g * c:(g + 1) * c] for g in range(self.world)])
+        out = _multi_source(rows, w_o, c)
         return (out, rows) if return_rows else out
 
     # -- backward -----------------------------------------------------------------------------------------
@@ -172,7 +201,7 @@ class UlyssesExchange:
         from aspec_b200.ops import gemm as G
         c = self.mine.qkv_cols
         srcs = self._pull([w.dqkv[self._rows(self.rank)] for w in self.ws])
-        dx = _multi_source(srcs, [w_grouped[g * c:(g + 1) * c] for g in range(self.world)], b_t=True)
+        dx = _multi_source(srcs, w_grouped, c, b_t=True)
         dw = torch.cat([G.gemm(s, x, a_t=True, b_t=True, out_dtype=torch.float32, stream_k=False) for s in srcs], 0)
         return dx, dw
 

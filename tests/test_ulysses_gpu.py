@@ -5,11 +5,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_projection_scatter_and_multi_source_output_projection():
+@pytest.mark.parametrize("world", [2, 4])
+def test_projection_scatter_and_multi_source_output_projection(world):
     from aspec_b200.parallel.ulysses import UlyssesExchange, UlyssesWorkspace, group_qkv_rows
     dev = torch.device("cuda:0")
     torch.manual_seed(0)
-    world, T_loc, D, hq, hk, d = 2, 192, 256, 4, 2, 64
+    T_loc, D, hq, hk, d = 192, 256, 8, 4, 64        # four ranks reduce over four sources in one grouped launch
     bf = torch.bfloat16
     wq, wk, wv = [(torch.randn(n * d, D, device=dev) * 0.05).to(bf) for n in (hq, hk, hk)]
     wo = (torch.randn(D, hq * d, device=dev) * 0.05).to(bf)
