@@ -83,6 +83,7 @@ class DirectCPAttention:
         self.rank, self.world, self.ws = rank, world, list(workspaces)
         self.mine = self.ws[rank]
         self.barrier = barrier or (lambda: None)
+        self.concurrent_owners = True
 
     def _views(self, w: CPWorkspace, n: int):
         H = w.heads
@@ -97,14 +98,41 @@ class DirectCPAttention:
         """``tables[o]`` / ``counts[o]``: owner ``o``'s queries against THIS rank's keys."""
         from aspec_b200.ops import attention_sm100 as K
         self._saved = (k_local, v_local, list(tables), list(counts), scale)
-        for o in range(self.world):
+
+        def one(o: int) -> None:
             n = counts[o]
             if n == 0:
-                continue
+                return
             w = self.ws[o]
             H = w.heads
             K.forward(w.q[:n], k_local, v_local, tables[o], scale, out=w.part_o[self.rank, :n],
                       lse=w.part_lse[self.rank, : H * n].view(H, n))
+
+        self._per_owner(one)
+
+    def _per_owner(self, fn: Callable[[int], object]) -> list:
+        """Run ``fn(owner)`` for every owner, each on its own CUDA stream: the owners' launches are independent (their
+        queries and outputs differ, the keys are shared), and run one after another every launch would pay its own
+        tail wave.  The calling stream waits for all of them; tensors returned by ``fn`` are handed over to it."""
+        dev = self.mine.q.device
+        if dev.type != "cuda" or self.world == 1 or not self.concurrent_owners:
+            return [fn(o) for o in range(self.world)]
+        cur = torch.cuda.current_stream(dev)
+        if not hasattr(self, "_streams"):
+            self._streams = [torch.cuda.Stream(dev) for _ in range(self.world)]
+        start = cur.record_event()
+        results = []
+        for o, side in enumerate(self._streams):
+            side.wait_event(start)
+            with torch.cuda.stream(side):
+                res = fn(o)
+            for t in (res if isinstance(res, (tuple, list)) else (res,)):
+                if torch.is_tensor(t):
+                    t.record_stream(cur)
+            results.append(res)
+        for side in self._streams:
+            cur.wait_stream(side)
+        return results
 
     def merge(self) -> Tuple[torch.Tensor, torch.Tensor]:
         n, w = self._nq, self.mine
@@ -123,12 +151,10 @@ class DirectCPAttention:
     def grad_partials(self) -> Tuple[torch.Tensor, torch.Tensor]:
         from aspec_b200.ops import attention_sm100 as K
         k_local, v_local, tables, counts, scale = self._saved
-        dk = torch.zeros_like(k_local, dtype=torch.float32)
-        dv = torch.zeros_like(v_local, dtype=torch.float32)
-        for o in range(self.world):
+        def one(o: int):
             n = counts[o]
             if n == 0:
-                continue
+                return None
             q, out, dout, lse = self._views(self.ws[o], n)
             if o != self.rank:
                 # the dK/dV kernel re-reads the query-side tiles once per key tile: fetch the peer's rows into local
@@ -136,8 +162,14 @@ class DirectCPAttention:
                 q, out, dout, lse = (self._fetch(t) for t in (q, out, dout, lse))
             _dq, dk_o, dv_o = K.backward(q, k_local, v_local, tables[o], out, lse, dout, scale,
                                          dq=self.ws[o].part_dq[self.rank, :n])
-            dk += dk_o
-            dv += dv_o
+            return dk_o, dv_o
+
+        dk = torch.zeros_like(k_local, dtype=torch.float32)
+        dv = torch.zeros_like(v_local, dtype=torch.float32)
+        for res in self._per_owner(one):
+            if res is not None:
+                dk += res[0]
+                dv += res[1]
         return dk.to(k_local.dtype), dv.to(v_local.dtype)
 
     @staticmethod
