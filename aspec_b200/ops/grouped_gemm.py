@@ -71,6 +71,77 @@ def _launch(operands, tiles: np.ndarray, segs: np.ndarray, a_mn: bool, b_mn: boo
         raise RuntimeError(f"ab_grouped_gemm_bf16 refused the launch (code {rc})")
 
 
+NATIVE_PLANNER = True          # tables from the C++ runtime (csrc/runtime/grouped_plan.cpp); False: the array-library statement
+
+
+def _i64(v) -> np.ndarray:
+    return np.ascontiguousarray(v, dtype=np.int64)
+
+
+def _ptr(a: np.ndarray):
+    return ctypes.c_void_p(a.ctypes.data)
+
+
+def _plan_rows_native(src, a_row, rows, expert, dst, out_row, base, ldd, esize, N, K, b_map, b_t):
+    lib = _native.runtime()
+    lib.ab_plan_rows_count.restype = ctypes.c_int64
+    lib.ab_plan_rows_gemm.restype = ctypes.c_int64
+    src, a_row, rows, expert, dst, out_row, ldd = (_i64(v) for v in (src, a_row, rows, expert, dst, out_row, ldd))
+    base = np.ascontiguousarray(base, dtype=np.uint64)
+    total = int(lib.ab_plan_rows_count(ctypes.c_int(len(rows)), _ptr(rows), ctypes.c_int64(N)))
+    tiles, segs = np.empty(total, dtype=_TILE), np.empty(total, dtype=_SEG)
+    lib.ab_plan_rows_gemm(ctypes.c_int(len(rows)), _ptr(src), _ptr(a_row), _ptr(rows), _ptr(expert), _ptr(dst), _ptr(out_row),
+                          _ptr(base), _ptr(ldd), ctypes.c_int(esize), ctypes.c_int64(N), ctypes.c_int64(K), ctypes.c_int(b_map),
+                          ctypes.c_int(int(b_t)), _ptr(tiles), _ptr(segs))
+    return tiles, segs
+
+
+def _plan_rows_numpy(src, a_row, rows, expert, dst, out_row, base, ldd, esize, N, K, b_map, b_t):
+    m_tiles = -(-rows // BM)
+    n_tiles = -(-N // BN)
+    per = m_tiles * n_tiles
+    total = int(per.sum())
+    prob = np.repeat(np.arange(len(rows)), per)
+    within = np.arange(total) - np.repeat(np.cumsum(per) - per, per)
+    nt = within // m_tiles[prob]                      # n-tile major inside a problem: CTAs in flight share B
+    mt = within - nt * m_tiles[prob]
+    tiles = np.zeros(total, dtype=_TILE)
+    row0 = out_row[prob] + mt * BM
+    tiles["d"] = base[dst[prob]] + ((row0 * ldd[dst[prob]] + nt * BN) * esize).astype(np.uint64)
+    tiles["ldd"] = ldd[dst[prob]]
+    tiles["rows"] = np.minimum(BM, rows[prob] - mt * BM)
+    tiles["cols"] = np.minimum(BN, N - nt * BN)
+    tiles["seg0"] = np.arange(total)
+    tiles["nseg"] = 1
+    segs = np.zeros(total, dtype=_SEG)
+    segs["a_map"] = src[prob]
+    segs["a_mn"] = a_row[prob] + mt * BM
+    segs["a_k"] = 0
+    segs["b_map"] = b_map
+    if b_t:
+        segs["b_mn"] = nt * BN
+        segs["b_k"] = expert[prob] * K
+    else:
+        segs["b_mn"] = expert[prob] * N + nt * BN
+        segs["b_k"] = 0
+    segs["k_blocks"] = -(-K // BK)
+    return tiles, segs
+
+
+def _plan_wgrad_native(expert, a_src, a_row, b_src, b_row, rows, E, Ma, Nb, out, esize, b_map0):
+    lib = _native.runtime()
+    lib.ab_plan_wgrad_gemm.restype = ctypes.c_int64
+    expert, a_src, a_row, b_src, b_row, rows = (_i64(v) for v in (expert, a_src, a_row, b_src, b_row, rows))
+    per = -(-Ma // BM) * -(-Nb // BN)
+    n_seg = len(rows) * per
+    tiles, segs = np.empty(E * per, dtype=_TILE), np.empty(n_seg, dtype=_SEG)
+    lib.ab_plan_wgrad_gemm(ctypes.c_int(len(rows)), _ptr(expert), _ptr(a_src), _ptr(a_row), _ptr(b_src), _ptr(b_row), _ptr(rows),
+                           ctypes.c_int(E), ctypes.c_int64(Ma), ctypes.c_int64(Nb), ctypes.c_uint64(out.data_ptr()),
+                           ctypes.c_int64(out.stride(0)), ctypes.c_int64(out.stride(1)), ctypes.c_int(esize), ctypes.c_int(b_map0),
+                           _ptr(tiles), _ptr(segs))
+    return tiles, segs
+
+
 def rows_gemm(a_bufs: List[torch.Tensor], weights: torch.Tensor, out_bufs: List[torch.Tensor], *, src, a_row, rows,
               expert, dst, out_row, b_t: bool = False, alpha: float = 1.0) -> None:
     """For every problem ``i``: ``out_bufs[dst[i]][out_row[i] : out_row[i] + rows[i]] = a_bufs[src[i]][a_row[i] : ...] @ W_i``.
@@ -102,52 +173,14 @@ def rows_gemm(a_bufs: List[torch.Tensor], weights: torch.Tensor, out_bufs: List[
             raise ValueError("output buffers must share a dtype, have unit inner stride and at least N columns")
     base = np.array([o.data_ptr() for o in out_bufs], dtype=np.uint64)
     ldd = np.array([o.stride(0) for o in out_bufs], dtype=np.int64)
-    m_tiles = -(-rows // BM)
-    n_tiles = -(-N // BN)
-    per = m_tiles * n_tiles
-    total = int(per.sum())
-    prob = np.repeat(np.arange(len(rows)), per)
-    within = np.arange(total) - np.repeat(np.cumsum(per) - per, per)
-    nt = within // m_tiles[prob]                      # n-tile major inside a problem: CTAs in flight share B
-    mt = within - nt * m_tiles[prob]
-    tiles = np.zeros(total, dtype=_TILE)
-    row0 = out_row[prob] + mt * BM
-    tiles["d"] = base[dst[prob]] + ((row0 * ldd[dst[prob]] + nt * BN) * esize).astype(np.uint64)
-    tiles["ldd"] = ldd[dst[prob]]
-    tiles["rows"] = np.minimum(BM, rows[prob] - mt * BM)
-    tiles["cols"] = np.minimum(BN, N - nt * BN)
-    tiles["seg0"] = np.arange(total)
-    tiles["nseg"] = 1
-    segs = np.zeros(total, dtype=_SEG)
-    segs["a_map"] = src[prob]
-    segs["a_mn"] = a_row[prob] + mt * BM
-    segs["a_k"] = 0
-    segs["b_map"] = b_map
-    if b_t:
-        segs["b_mn"] = nt * BN
-        segs["b_k"] = expert[prob] * K
-    else:
-        segs["b_mn"] = expert[prob] * N + nt * BN
-        segs["b_k"] = 0
-    segs["k_blocks"] = -(-K // BK)
+    plan = _plan_rows_native if NATIVE_PLANNER else _plan_rows_numpy
+    tiles, segs = plan(src, a_row, rows, expert, dst, out_row, base, ldd, esize, N, K, b_map, b_t)
     if b_t and K % BK and E > 1:
         raise ValueError("a transposed stacked weight needs its reduction extent to be a multiple of 64")
     _launch(operands, tiles, segs, False, b_t, out_dtype == torch.float32, alpha, a_bufs[0].device)
 
 
-def wgrad_gemm(a_bufs: List[torch.Tensor], b_bufs: List[torch.Tensor], out: torch.Tensor, *, expert, a_src, a_row, b_src,
-               b_row, rows, alpha: float = 1.0) -> None:
-    """``out[e] = sum over runs i with expert[i] == e of  A_i^T @ B_i`` with ``A_i = a_bufs[a_src[i]][a_row[i] : + rows[i]]``
-    (``[rows, Ma]``) and ``B_i`` likewise (``[rows, Nb]``); ``out`` is ``[E, Ma, Nb]`` fp32 or bf16 and is fully written
-    (experts without rows get zeros)."""
-    expert, a_src, a_row, b_src, b_row, rows = (np.asarray(v, dtype=np.int64) for v in (expert, a_src, a_row, b_src, b_row, rows))
-    E, Ma, Nb = out.shape
-    keep = rows > 0
-    expert, a_src, a_row, b_src, b_row, rows = (v[keep] for v in (expert, a_src, a_row, b_src, b_row, rows))
-    order = np.argsort(expert, kind="stable")
-    expert, a_src, a_row, b_src, b_row, rows = (v[order] for v in (expert, a_src, a_row, b_src, b_row, rows))
-    a_bufs, b_bufs = [_as_2d(a) for a in a_bufs], [_as_2d(b) for b in b_bufs]
-    operands = [(a, 0) for a in a_bufs] + [(b, 1) for b in b_bufs]
+def _plan_wgrad_numpy(expert, a_src, a_row, b_src, b_row, rows, E, Ma, Nb, out, esize, b_map0):
     runs_per_expert = np.bincount(expert, minlength=E)
     run0 = np.cumsum(runs_per_expert) - runs_per_expert
     m_tiles, n_tiles = -(-Ma // BM), -(-Nb // BN)
@@ -157,7 +190,6 @@ def wgrad_gemm(a_bufs: List[torch.Tensor], b_bufs: List[torch.Tensor], out: torc
     within = np.arange(total) - e_of * per
     nt = within // m_tiles
     mt = within - nt * m_tiles
-    esize = 4 if out.dtype == torch.float32 else 2
     tiles = np.zeros(total, dtype=_TILE)
     tiles["d"] = np.uint64(out.data_ptr()) + ((e_of * out.stride(0) + mt * BM * out.stride(1) + nt * BN) * esize).astype(np.uint64)
     tiles["ldd"] = out.stride(1)
@@ -174,10 +206,31 @@ def wgrad_gemm(a_bufs: List[torch.Tensor], b_bufs: List[torch.Tensor], out: torc
     segs["a_map"] = a_src[run]
     segs["a_mn"] = mt[tile_of] * BM
     segs["a_k"] = a_row[run]
-    segs["b_map"] = len(a_bufs) + b_src[run]
+    segs["b_map"] = b_map0 + b_src[run]
     segs["b_mn"] = nt[tile_of] * BN
     segs["b_k"] = b_row[run]
     segs["k_blocks"] = -(-rows[run] // BK)
+    return tiles, segs
+
+
+def wgrad_gemm(a_bufs: List[torch.Tensor], b_bufs: List[torch.Tensor], out: torch.Tensor, *, expert, a_src, a_row, b_src,
+               b_row, rows, alpha: float = 1.0) -> None:
+    """``out[e] = sum over runs i with expert[i] == e of  A_i^T @ B_i`` with ``A_i = a_bufs[a_src[i]][a_row[i] : + rows[i]]``
+    (``[rows, Ma]``) and ``B_i`` likewise (``[rows, Nb]``); ``out`` is ``[E, Ma, Nb]`` fp32 or bf16 and is fully written
+    (experts without rows get zeros)."""
+    expert, a_src, a_row, b_src, b_row, rows = (np.asarray(v, dtype=np.int64) for v in (expert, a_src, a_row, b_src, b_row, rows))
+    E, Ma, Nb = out.shape
+    keep = rows > 0
+    expert, a_src, a_row, b_src, b_row, rows = (v[keep] for v in (expert, a_src, a_row, b_src, b_row, rows))
+    order = np.argsort(expert, kind="stable")
+    expert, a_src, a_row, b_src, b_row, rows = (v[order] for v in (expert, a_src, a_row, b_src, b_row, rows))
+    a_bufs, b_bufs = [_as_2d(a) for a in a_bufs], [_as_2d(b) for b in b_bufs]
+    operands = [(a, 0) for a in a_bufs] + [(b, 1) for b in b_bufs]
+    esize = 4 if out.dtype == torch.float32 else 2
+    if NATIVE_PLANNER:
+        tiles, segs = _plan_wgrad_native(expert, a_src, a_row, b_src, b_row, rows, E, Ma, Nb, out, esize, len(a_bufs))
+    else:
+        tiles, segs = _plan_wgrad_numpy(expert, a_src, a_row, b_src, b_row, rows, E, Ma, Nb, out, esize, len(a_bufs))
     if out.stride(2) != 1:
         raise ValueError("output must have unit inner stride")
     _launch(operands, tiles, segs, True, True, out.dtype == torch.float32, alpha, out.device)

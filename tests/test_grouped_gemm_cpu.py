@@ -86,3 +86,42 @@ def test_wgrad_plan_reduces_over_sources_with_a_padded_operand(monkeypatch):
                  b_src=[0] * len(runs), b_row=pstart, rows=[n for _, _, n in runs])
     assert torch.equal(out[1], torch.zeros(Ma, Nb))             # an expert without rows is zero-filled, not skipped
     assert torch.allclose(out, ref, atol=1e-2, rtol=1e-3)
+
+
+def test_native_planner_writes_the_same_tables_as_the_array_statement(monkeypatch):
+    """The C++ planner (runtime library) against the numpy planner, table for table."""
+    rng = np.random.default_rng(0)
+    captured = {}
+
+    def capture(key):
+        def fake(operands, tiles, segs, *rest, **kw):
+            captured[key] = (tiles.copy(), segs.copy())
+        return fake
+
+    E, N, K = 7, 600, 200
+    a_bufs = [torch.zeros(4000, K).bfloat16(), torch.zeros(3000, K).bfloat16()]
+    outs = [torch.zeros(5000, N).bfloat16(), torch.zeros(5000, N + 8).bfloat16()]
+    n = 40
+    rows = rng.integers(0, 300, n)
+    rows[::7] = 0
+    args = dict(src=rng.integers(0, 2, n), a_row=rng.integers(0, 2000, n), rows=rows, expert=rng.integers(0, E, n),
+                dst=rng.integers(0, 2, n), out_row=rng.integers(0, 3000, n))
+    for b_t in (False, True):
+        w = torch.zeros((E, K if b_t else N, N if b_t else K)).bfloat16() if not b_t else torch.zeros(E, 192, N).bfloat16()
+        bufs = a_bufs if not b_t else [torch.zeros(4000, 192).bfloat16(), torch.zeros(3000, 192).bfloat16()]
+        for native in (True, False):
+            monkeypatch.setattr(G, "NATIVE_PLANNER", native)
+            monkeypatch.setattr(G, "_launch", capture(native))
+            G.rows_gemm(bufs, w, outs, b_t=b_t, **args)
+        for a, b in zip(captured[True], captured[False]):
+            assert a.dtype == b.dtype and a.tobytes() == b.tobytes()
+    out = torch.zeros(E, 300, 520)
+    runs = 25
+    wargs = dict(expert=rng.integers(0, E, runs), a_src=rng.integers(0, 2, runs), a_row=rng.integers(0, 2000, runs),
+                 b_src=np.zeros(runs, dtype=np.int64), b_row=rng.integers(0, 30, runs) * 64, rows=rng.integers(0, 200, runs))
+    for native in (True, False):
+        monkeypatch.setattr(G, "NATIVE_PLANNER", native)
+        monkeypatch.setattr(G, "_launch", capture(native))
+        G.wgrad_gemm([torch.zeros(4000, 300).bfloat16(), torch.zeros(3000, 300).bfloat16()], [torch.zeros(4000, 520).bfloat16()], out, **wargs)
+    for a, b in zip(captured[True], captured[False]):
+        assert a.tobytes() == b.tobytes()
