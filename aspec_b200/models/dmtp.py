@@ -66,82 +66,100 @@ class FrozenMTPFeatures(MTPPredictor):
         return self.predict_embeddings(hidden.detach(), embeds.detach(), positions, intervals).detach()
 
 
-def training_mtp_prefix(draft, input_ids, last_hidden_states, attention_mask=None) -> MTPPrefix:
-    policy = draft.config.mtp_conditioning
-    if policy["mode"] == "token":
-        return MTPPrefix()
-    if last_hidden_states is None or last_hidden_states.shape[:2] != input_ids.shape:
-        raise ValueError("MTP hidden conditioning requires aligned post-norm Target final states")
-    if input_ids.shape[0] != 1:
-        raise ValueError("MTP conditioning currently requires microbatch size one")
+def _document_length(input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor]) -> int:
+    """Tokens of the (single, right-padded) document in the row."""
     total = input_ids.shape[1]
-    length = total
-    if attention_mask is not None:
-        if attention_mask.shape != input_ids.shape:
-            raise ValueError("MTP attention mask must align with input token IDs")
-        length = int(attention_mask.sum())
-        if not attention_mask[:, :length].bool().all() or attention_mask[:, length:].bool().any():
-            raise ValueError("MTP conditioning requires right-padded complete documents")
+    if attention_mask is None:
+        return total
+    if attention_mask.shape != input_ids.shape:
+        raise ValueError(f"attention mask {tuple(attention_mask.shape)} does not cover the ids {tuple(input_ids.shape)}")
+    live = attention_mask[0].bool()
+    n = int(live.sum())
+    if not bool(live[:n].all()) or bool(live[n:].any()):
+        raise ValueError("the MTP prefix needs one contiguous document followed by padding only")
+    return n
+
+
+def training_mtp_prefix(draft, input_ids, last_hidden_states, attention_mask=None) -> MTPPrefix:
+    """What the training wrapper hands to the block model: nothing in ``token`` mode (the first candidate is teacher
+    forced), the frozen predictor's post-norm states ``[1, T-1, Dt]`` in ``hidden`` mode."""
+    if draft.config.mtp_conditioning["mode"] != "hidden":
+        return MTPPrefix()
+    rows, total = input_ids.shape
+    if rows != 1:
+        raise ValueError("MTP-conditioned training takes one row per micro-batch")
+    if last_hidden_states is None or tuple(last_hidden_states.shape[:2]) != (rows, total):
+        raise ValueError("hidden-mode conditioning needs the Target's final (post-norm) state of every token")
+    n = _document_length(input_ids, attention_mask)
     width = draft.config.target_hidden_size
-    if length < 2:
-        return MTPPrefix(last_hidden_states.new_zeros((1, max(total - 1, 0), width)))
-    dev = input_ids.device
-    pos = torch.arange(length - 1, device=dev, dtype=torch.int32)
-    wdtype = draft.mtp_source.fc.weight.dtype
-    hidden = draft.mtp_source(last_hidden_states[0, :length - 1].to(wdtype),
-                              draft.embed_tokens(input_ids[0, 1:length]).to(wdtype), pos,
-                              causal_intervals(torch.zeros(length - 1, dtype=torch.long, device=dev)))
-    hidden = torch.nn.functional.pad(hidden, (0, 0, 0, total - length))
-    return MTPPrefix(hidden.detach()[None])
+    if n < 2:                                              # nothing to predict from
+        return MTPPrefix(last_hidden_states.new_zeros(1, max(total - 1, 0), width))
+    source = draft.mtp_source
+    dtype = source.fc.weight.dtype
+    steps = n - 1                                          # row i: Target state of token i and token i+1 -> token i+2
+    device = input_ids.device
+    states = source(last_hidden_states[0, :steps].to(dtype), draft.embed_tokens(input_ids[0, 1:n]).to(dtype),
+                    torch.arange(steps, device=device, dtype=torch.int32),
+                    causal_intervals(torch.zeros(steps, dtype=torch.long, device=device)))
+    padded = states.new_zeros(total - 1, states.shape[-1])
+    padded[:steps] = states
+    return MTPPrefix(padded.detach().unsqueeze(0))
 
 
 def first_candidate_embeddings(draft, input_ids, anchors, keep, prefix: MTPPrefix) -> torch.Tensor:
-    """``[B, S, D]`` embedding of ``T1`` per anchor, fused with the MTP state in ``hidden`` mode."""
+    """``[B, S, D]``: the embedding of every anchor's first candidate ``T1`` (fused with the predictor's state in
+    ``hidden`` mode).  ``T1`` is ``x[a+1]`` when ``prefix.first_candidate_ids`` is ``None`` (training), else the given
+    proposals (drafting); dropped anchors get the mask token."""
     if not isinstance(prefix, MTPPrefix):
-        raise ValueError("MTP conditioning requires an explicit derived prefix")
-    T = input_ids.shape[1]
-    if ((anchors < 1) | (anchors + 1 >= T))[keep].any():
-        raise ValueError("MTP anchors need a previous Target state and an in-bounds T1")
-    if prefix.first_candidate_ids is None:
-        ids = input_ids.gather(1, (anchors + 1).clamp(max=T - 1))
-    else:
-        ids = prefix.first_candidate_ids
-        if ids.shape != anchors.shape or ids.dtype != torch.long:
-            raise ValueError("MTP proposal IDs must be int64 with the anchor shape")
-    ids = torch.where(keep, ids, torch.full_like(ids, draft.mask_token_id))
-    first = draft.embed_tokens(ids)
-    if draft.config.mtp_conditioning["mode"] == "hidden":
-        hidden = prefix.prediction_hidden
-        expected = (input_ids.shape[0], T - 1, draft.config.target_hidden_size)
-        if hidden is None or tuple(hidden.shape) != expected:
-            raise ValueError(f"MTP prediction hidden must have shape {expected}")
-        index = (anchors - 1).clamp_min(0).unsqueeze(-1).expand(-1, -1, hidden.shape[-1])
-        selected = hidden.gather(1, index)
-        selected = torch.where(keep.unsqueeze(-1), selected, torch.zeros_like(selected))
-        first = draft.mtp_fusion(first.to(draft.mtp_fusion.proj.weight.dtype), selected)
-    elif prefix.prediction_hidden is not None:
-        raise ValueError("Token-only conditioning does not consume MTP hidden features")
-    return first
+        raise ValueError("pass the MTPPrefix derived for this row (training_mtp_prefix or a proposal-time prefix)")
+    mode = draft.config.mtp_conditioning["mode"]
+    batch, length = input_ids.shape
+    live = anchors[keep]
+    if live.numel() and (int(live.min()) < 1 or int(live.max()) + 1 >= length):
+        raise ValueError("every kept anchor needs a token before it (the predictor's input) and one after it (T1)")
+    proposals = prefix.first_candidate_ids
+    if proposals is None:
+        proposals = torch.gather(input_ids, 1, torch.clamp(anchors + 1, max=length - 1))
+    elif proposals.dtype != torch.long or proposals.shape != anchors.shape:
+        raise ValueError("first_candidate_ids must be an int64 tensor shaped like the anchors")
+    proposals = proposals.masked_fill(~keep, draft.mask_token_id)
+    embedded = draft.embed_tokens(proposals)
+    states = prefix.prediction_hidden
+    if mode != "hidden":
+        if states is not None:
+            raise ValueError("token-mode conditioning takes no predictor states")
+        return embedded
+    want = (batch, length - 1, draft.config.target_hidden_size)
+    if states is None or tuple(states.shape) != want:
+        raise ValueError(f"hidden-mode conditioning expects predictor states of shape {want}")
+    rows = torch.clamp(anchors - 1, min=0)                                  # state a-1 predicts x[a+1]
+    picked = torch.gather(states, 1, rows[..., None].expand(*rows.shape, states.shape[-1]))
+    picked = picked * keep[..., None].to(picked.dtype)
+    fusion = draft.mtp_fusion
+    return fusion(embedded.to(fusion.proj.weight.dtype), picked)
 
 
 def condition_noise_embeddings(draft, embeddings, input_ids, anchors, keep, prefix, block_size):
-    """Replace block position 1 of ``embeddings [B, S * block, D]`` with the (fused) ``T1`` embedding."""
+    """Put the (fused) ``T1`` embedding into slot 1 of every block of ``embeddings [B, S * block, D]``."""
     first = first_candidate_embeddings(draft, input_ids, anchors, keep, prefix)
-    blocks = embeddings.reshape(input_ids.shape[0], anchors.shape[1], block_size, -1)
-    return torch.cat((blocks[:, :, :1], first.unsqueeze(2).to(blocks.dtype), blocks[:, :, 2:]), 2).flatten(1, 2)
+    blocks = embeddings.view(input_ids.shape[0], anchors.shape[1], block_size, embeddings.shape[-1]).clone()
+    blocks[:, :, 1] = first.to(blocks.dtype)
+    return blocks.view(input_ids.shape[0], -1, embeddings.shape[-1])
 
 
 @torch.no_grad()
 def frozen_mtp_predictions(mtp, input_ids, final_hidden_states):
-    """Causal single-document predictor pass: output row ``a-1`` predicts the unverified ``x[a+1]``."""
-    if mtp.training or any(p.requires_grad for p in mtp.parameters()):
-        raise ValueError("The native MTP feature producer must be frozen and in eval mode")
-    if (input_ids.ndim != 2 or input_ids.shape[0] != 1 or input_ids.shape[1] < 2
-            or final_hidden_states.shape[:2] != input_ids.shape):
-        raise ValueError("MTP feature extraction requires one complete unpadded document")
-    n = input_ids.shape[1] - 1
-    dev = input_ids.device
-    pos = torch.arange(n, device=dev, dtype=torch.int32)
-    out = mtp.predict(final_hidden_states[0, :-1].detach(), input_ids[0, 1:], pos,
-                      causal_intervals(torch.zeros(n, dtype=torch.long, device=dev)))
-    return out.detach()[None]
+    """Predictor states ``[1, T-1, Dt]`` of one whole document (proposal time): row ``a-1`` is the state that predicts
+    ``x[a+1]``.  The predictor must be frozen and in eval mode."""
+    trainable = [n for n, p in mtp.named_parameters() if p.requires_grad]
+    if mtp.training or trainable:
+        raise ValueError("the native MTP predictor is a frozen feature producer: call .eval() and freeze it first")
+    one_document = input_ids.ndim == 2 and input_ids.shape[0] == 1 and input_ids.shape[1] >= 2
+    if not one_document or tuple(final_hidden_states.shape[:2]) != tuple(input_ids.shape):
+        raise ValueError("expected one unpadded document of at least two tokens with a final state per token")
+    steps = input_ids.shape[1] - 1
+    device = input_ids.device
+    states = mtp.predict(final_hidden_states[0, :steps].detach(), input_ids[0, 1:],
+                         torch.arange(steps, device=device, dtype=torch.int32),
+                         causal_intervals(torch.zeros(steps, dtype=torch.long, device=device)))
+    return states.detach().unsqueeze(0)
