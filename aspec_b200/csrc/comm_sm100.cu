@@ -173,6 +173,47 @@ __global__ void shard_adamw_scatter_kernel(float* __restrict__ master, const flo
   }
 }
 
+// ---- merge of attention partials over disjoint key sets (direct context parallelism) -------------------------
+// One warp per (query row, head): lse = log sum_r exp(lse_r), out = sum_r exp(lse_r - lse) * O_r.  Parts whose lse is
+// not finite saw no key for the row; a row that no part saw gets zeros and `empty_lse`.
+__global__ void attn_merge_partials_kernel(const __nv_bfloat16* __restrict__ part_o, long long part_stride_o,
+                                           const float* __restrict__ part_lse, long long part_stride_lse, int n_parts,
+                                           int n_rows, int heads, int head_dim, __nv_bfloat16* __restrict__ out,
+                                           float* __restrict__ lse_out, float empty_lse) {
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= (long long)n_rows * heads) return;
+  const int row = (int)(warp / heads), h = (int)(warp - (long long)row * heads);
+  float l[8], m = -INFINITY;
+  for (int r = 0; r < n_parts; ++r) {
+    l[r] = part_lse[r * part_stride_lse + (long long)h * n_rows + row];
+    if (isfinite(l[r])) m = fmaxf(m, l[r]);
+  }
+  const bool any = m > -INFINITY;
+  float s = 0.f;
+  for (int r = 0; r < n_parts; ++r)
+    if (any && isfinite(l[r])) s += __expf(l[r] - m);
+  const float lse = any ? m + __logf(s) : empty_lse;
+  const long long base = ((long long)row * heads + h) * head_dim;
+  for (int e = lane * 4; e < head_dim; e += 128) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < n_parts; ++r) {
+      if (!any || !isfinite(l[r])) continue;
+      const float w = __expf(l[r] - lse);
+      const uint2 raw = *reinterpret_cast<const uint2*>(part_o + r * part_stride_o + base + e);
+      const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 a = __bfloat1622float2(v[0]), b = __bfloat1622float2(v[1]);
+      acc[0] += w * a.x;
+      acc[1] += w * a.y;
+      acc[2] += w * b.x;
+      acc[3] += w * b.y;
+    }
+    __nv_bfloat162 o[2] = {__floats2bfloat162_rn(acc[0], acc[1]), __floats2bfloat162_rn(acc[2], acc[3])};
+    *reinterpret_cast<uint2*>(out + base + e) = *reinterpret_cast<uint2*>(o);
+  }
+  if (lane == 0) lse_out[(long long)h * n_rows + row] = lse;
+}
+
 // ---- vocabulary-parallel merges over peer memory -----------------------------------------------------------
 // out[i] = log sum_r exp(lse_r[i])   (each rank's partial log-sum-exp over its vocabulary shard)
 __global__ void peer_lse_merge_kernel(PeerPtrsF peers, int n_peers, float* __restrict__ out, long long n) {
@@ -290,6 +331,21 @@ int ab_peer_lse_merge(const void* const* peer_lse, int n_peers, float* out, long
   long long grid = (n + 255) / 256;
   if (grid > 148 * 4) grid = 148 * 4;
   peer_lse_merge_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pp, n_peers, out, n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+// out[n_rows, heads, head_dim] (bf16) and lse_out[heads, n_rows] from `n_parts` partial results laid out with the
+// given strides (elements) between parts.  head_dim must be a multiple of 4 and all row bases 8-byte aligned.
+int ab_attn_merge_partials(const void* part_o, long long part_stride_o, const float* part_lse, long long part_stride_lse,
+                           int n_parts, int n_rows, int heads, int head_dim, void* out, float* lse_out, float empty_lse,
+                           void* stream) {
+  if (n_parts < 1 || n_parts > 8 || (head_dim & 3)) return -10;
+  if (n_rows <= 0) return 0;
+  const long long warps = (long long)n_rows * heads;
+  const int block = 256;
+  const long long grid = (warps * 32 + block - 1) / block;
+  attn_merge_partials_kernel<<<(unsigned)grid, block, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(part_o), part_stride_o, part_lse, part_stride_lse, n_parts, n_rows, heads, head_dim,
+      reinterpret_cast<__nv_bfloat16*>(out), lse_out, empty_lse);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 int ab_peer_argmax_merge(const void* const* peer_vals, const void* const* peer_idxs, int n_peers, const long long* labels,

@@ -67,3 +67,15 @@ def peer_argmax_merge(peer_vals: Sequence[torch.Tensor], peer_idxs: Sequence[tor
                                                   C.c_void_p(labels.data_ptr()), C.c_void_p(correct.data_ptr()),
                                                   C.c_longlong(correct.numel()), _stream(correct)), "ab_peer_argmax_merge")
     return correct
+
+
+def attn_merge_partials(part_o: torch.Tensor, part_lse: torch.Tensor, n_rows: int, out: torch.Tensor, lse_out: torch.Tensor) -> None:
+    """``part_o [P, R_max, H, d]`` (bf16) and ``part_lse [P, H * R_max]`` (fp32, each part holding ``[H, n_rows]`` in its
+    first ``H * n_rows`` entries) -> ``out [n_rows, H, d]``, ``lse_out [H, n_rows]``: the exact merge of attention
+    partials over disjoint key sets in one kernel (``ops.attention.merge_partials`` is the fp32 statement)."""
+    P, _, H, d = part_o.shape
+    rc = _native.kernels().ab_attn_merge_partials(
+        C.c_void_p(part_o.data_ptr()), C.c_longlong(part_o.stride(0)), C.c_void_p(part_lse.data_ptr()),
+        C.c_longlong(part_lse.stride(0)), C.c_int(P), C.c_int(n_rows), C.c_int(H), C.c_int(d),
+        C.c_void_p(out.data_ptr()), C.c_void_p(lse_out.data_ptr()), C.c_float(float("-inf")), _stream(part_o))
+    _check(rc, "ab_attn_merge_partials")

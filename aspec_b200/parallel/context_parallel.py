@@ -137,12 +137,15 @@ class DirectCPAttention:
     def merge(self) -> Tuple[torch.Tensor, torch.Tensor]:
         n, w = self._nq, self.mine
         H = w.heads
-        outs = w.part_o[:, :n]
-        lses = w.part_lse[:, : H * n].view(self.world, H, n)
-        out, lse = merge_partials(outs, lses)
-        w.out[:n].copy_(out)
-        w.lse[: H * n].view(H, n).copy_(lse)
-        return out, lse
+        out, lse = w.out[:n], w.lse[: H * n].view(H, n)
+        if w.part_o.is_cuda and w.head_dim % 4 == 0:
+            from aspec_b200.ops import comm
+            comm.attn_merge_partials(w.part_o, w.part_lse, n, out, lse)     # one kernel, straight into the workspace
+            return out.clone(), lse.clone()                                 # the workspace is reused by the next call
+        merged, merged_lse = merge_partials(w.part_o[:, :n], w.part_lse[:, : H * n].view(self.world, H, n))
+        out.copy_(merged)
+        lse.copy_(merged_lse)
+        return merged, merged_lse
 
     # -- backward -----------------------------------------------------------------------------------------
     def publish_grad(self, dout: torch.Tensor) -> None:
