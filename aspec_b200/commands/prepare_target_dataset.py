@@ -23,8 +23,8 @@ def main(argv=None) -> int:
     ap.add_argument("--resume", action="store_true")
     a = ap.parse_args(argv)
     import torch
-    from aspec_b200.assets import find_asset, load_draft_config
-    from aspec_b200.config.draft_config import AutoDraftModelConfig, resolve_draft_algorithm
+    from aspec_b200.assets import load_draft_config
+    from aspec_b200.config.draft_config import resolve_draft_algorithm
     from aspec_b200.data.dataset import load_training_samples
     from aspec_b200.inference.factory import target_config_from_args
     from aspec_b200.models.target.dense import DenseTarget, TargetConfig

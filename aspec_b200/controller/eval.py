@@ -9,7 +9,7 @@ import hashlib
 import json
 import os
 import time
-from typing import Any, Callable, Dict, List, Optional, Sequence
+from typing import Any, Callable, Dict, List, Optional
 
 
 def eval_cache_identity(fingerprint: str, contract_id: str, args: Dict[str, Any]) -> str:

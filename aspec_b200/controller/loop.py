@@ -8,12 +8,10 @@ trainers work on step ``s`` (dispatch-ahead, bounded by the ring slots).
 """
 from __future__ import annotations
 
-import json
-import os
 import time
 from typing import Callable, Dict, List, Optional
 
-from aspec_b200.runtime.actor import ActorError, ActorTimeout
+from aspec_b200.runtime.actor import ActorError
 from aspec_b200.training import checkpoint as ckpt
 
 

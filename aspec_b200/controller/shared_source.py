@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import copy
 import threading
-from typing import Callable, Dict, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Sequence, Tuple
 
 from aspec_b200.utils.types import InferenceOutput, RowRequest
 

@@ -1,7 +1,7 @@
 """Renderer protocol (reference: aspec/data/renderers/base.py:27-70)."""
 from __future__ import annotations
 
-from typing import Any, List, Optional, Protocol, Tuple, runtime_checkable
+from typing import List, Optional, Protocol, Tuple, runtime_checkable
 
 import torch
 

@@ -5,7 +5,6 @@ from __future__ import annotations
 import json
 from typing import Dict, List
 
-import torch
 
 from aspec_b200.runtime.actor import ProcessActor
 

@@ -18,7 +18,7 @@ is a CPU tensor the compaction needs no device synchronisation.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn

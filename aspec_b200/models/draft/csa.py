@@ -19,7 +19,6 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from aspec_b200.models.draft.dflash import DFlashAttention
 from aspec_b200.models.draft.sparse_common import (build_group_layout, eligible_groups, gathered_attention, kl_rows,

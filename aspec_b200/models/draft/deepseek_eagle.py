@@ -1,7 +1,6 @@
 """EAGLE3 draft with DeepSeek multi-head latent attention (reference: aspec/models/draft/deepseek_eagle.py:89-575)."""
 from __future__ import annotations
 
-import torch
 import torch.nn as nn
 
 from aspec_b200.config.draft_config import DeepseekEagleConfig

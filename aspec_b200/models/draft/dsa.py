@@ -17,7 +17,6 @@ queries so that no ``[Q, T]`` fp32 tensor larger than ``dsa_workspace_bytes`` ex
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 import torch.nn as nn

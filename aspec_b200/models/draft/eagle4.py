@@ -9,7 +9,6 @@ distribution, starting from a randomised truncated SVD of the exact head.
 from __future__ import annotations
 
 import torch
-import torch.nn as nn
 
 from aspec_b200.config.draft_attention import resolve_attention_policy
 from aspec_b200.config.draft_config import Eagle4Config

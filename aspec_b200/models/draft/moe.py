@@ -11,7 +11,7 @@ one GEMM over its contiguous slice (tcgen05 GEMM on CUDA).  With expert parallel
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import List, Optional
 
 import torch
 import torch.nn as nn

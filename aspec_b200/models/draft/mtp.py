@@ -14,7 +14,6 @@ from typing import Dict
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from aspec_b200.config.draft_config import NativeMTPConfig
 from aspec_b200.models.draft.base import Eagle3DraftModel

@@ -17,8 +17,7 @@ also writes the tile into the feature sink - which may be memory of the Draft GP
 from __future__ import annotations
 
 import json
-import math
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 import torch

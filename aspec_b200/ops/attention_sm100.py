@@ -2,7 +2,6 @@
 from __future__ import annotations
 
 import ctypes as _c
-import math
 from typing import Tuple
 
 import torch

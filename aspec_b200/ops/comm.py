@@ -7,7 +7,7 @@ call works for one process emulating several ranks on one GPU (tests) and for re
 from __future__ import annotations
 
 import ctypes as C
-from typing import List, Sequence
+from typing import Sequence
 
 import torch
 

@@ -14,11 +14,11 @@ Key layout on rank ``r``: ``[context rows owned by r | draft rows of r's own que
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence, Tuple
+from typing import Callable, Optional, Sequence, Tuple
 
 import torch
 
-from aspec_b200.ops.attention import MASK_VALUE, merge_partials
+from aspec_b200.ops.attention import merge_partials
 from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
 
 

@@ -15,7 +15,7 @@ Phases are separate methods so that several ranks can be emulated in one process
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence
+from typing import Callable, Optional, Sequence
 
 import torch
 import torch.distributed as dist

@@ -20,7 +20,7 @@ tiny stream-ordered collective in real runs.
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence
+from typing import Callable, Optional, Sequence
 
 import torch
 

@@ -17,7 +17,7 @@ The result is what the launcher needs: per role the ordered ``(node, gpu)`` pair
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, Iterable, List, Optional, Sequence, Set, Tuple
+from typing import Iterable, List, Optional, Sequence, Set, Tuple
 
 
 @dataclass(frozen=True)

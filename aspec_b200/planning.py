@@ -10,10 +10,8 @@ from __future__ import annotations
 import dataclasses
 import hashlib
 import json
-import math
-import os
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List
 
 from aspec_b200 import __version__
 from aspec_b200.config.draft_attention import (context_shard_alignment, resolve_attention_policy, thd_contract)

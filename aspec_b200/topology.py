@@ -21,7 +21,7 @@ import math
 import os
 import statistics
 import sys
-from typing import Any, Dict, List, Mapping, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence
 
 TOPOLOGY_STUDY_SCHEMA_VERSION = "aspec.topology-study/v1"
 

@@ -16,7 +16,7 @@ import time
 from typing import Any, Dict, List, Optional
 
 from aspec_b200.config.draft_config import AutoDraftModelConfig, resolve_draft_algorithm
-from aspec_b200.config.train_config import config_to_flat_args, load_config, save_config
+from aspec_b200.config.train_config import load_config, save_config
 from aspec_b200.runtime.actor import ProcessActor, make_queue
 from aspec_b200.transport.slot_ring import GenerationSlotRing
 

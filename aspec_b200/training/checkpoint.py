@@ -26,7 +26,7 @@ import random
 import shutil
 import time
 import warnings
-from typing import Any, Dict, Mapping, Optional
+from typing import Any, Mapping, Optional
 
 import torch
 import torch.distributed as dist

@@ -16,7 +16,6 @@ performs the single device->host read of an update.
 """
 from __future__ import annotations
 
-import time
 from typing import Dict, Iterable, List, Optional
 
 import torch
