@@ -154,6 +154,17 @@ def make_pool(args, cfg, model, rank, n_docs, pin):
             for k in ("input_ids", "loss_mask", "injected_anchors"):
                 batch[k] = batch[k].pin_memory()
         pool.append(batch)
+    # One update takes ``accum`` consecutive documents of the pool.  Deal the documents to the updates by length
+    # (serpentine over the sorted list) so that every update carries about the same number of tokens and the metric does
+    # not depend on which updates fall into the timed window.
+    groups = max(len(pool) // max(args.accum, 1), 1)
+    if groups > 1 and len(pool) % groups == 0:
+        order = sorted(range(len(pool)), key=lambda i: -pool[i]["seq_len"])
+        buckets = [[] for _ in range(groups)]
+        for j, i in enumerate(order):
+            g = j % groups
+            buckets[g if (j // groups) % 2 == 0 else groups - 1 - g].append(i)
+        pool = [pool[i] for b in buckets for i in b]
     return pool
 
 
