@@ -73,3 +73,31 @@ def iter_documents(spec: SyntheticSpec, start: int = 0, count: Optional[int] = N
 
 def mean_length(spec: SyntheticSpec, rows: int = 2048) -> float:
     return float(np.mean([document_length(spec, r) for r in range(rows)]))
+
+
+def benchmark_documents(spec: SyntheticSpec, n_docs: int, per_update: int, rank: int = 0) -> list:
+    """The benchmark's document pool, identical in shape for every arm and rank.
+
+    Document ``i`` has the length of row ``i`` of ``spec`` on every rank (so per-GPU work does not depend on the number of
+    GPUs); ranks above 0 draw their own token ids.  The documents are then dealt to the updates (``per_update``
+    consecutive pool entries each) by length, serpentine over the sorted list, so that every update carries about the
+    same number of tokens.  Each entry is ``make_document``'s dictionary plus ``"row"`` (a per-rank seed for features).
+    """
+    docs = []
+    for i in range(n_docs):
+        doc = make_document(spec, i)
+        row = rank * 100003 + i
+        if rank > 0:
+            g = torch.Generator().manual_seed(row)
+            doc["input_ids"] = torch.randint(0, spec.vocab_size, (doc["seq_len"],), generator=g, dtype=torch.int64)
+        doc["row"] = row
+        docs.append(doc)
+    groups = max(n_docs // max(per_update, 1), 1)
+    if groups > 1 and n_docs % groups == 0:
+        order = sorted(range(n_docs), key=lambda i: -docs[i]["seq_len"])
+        buckets = [[] for _ in range(groups)]
+        for j, i in enumerate(order):
+            g = j % groups
+            buckets[g if (j // groups) % 2 == 0 else groups - 1 - g].append(i)
+        docs = [docs[i] for b in buckets for i in b]
+    return docs

@@ -82,15 +82,13 @@ def _run(args):
 
     # same synthetic documents as the other arm (host tensors only; no model / kernel code is shared)
     sys.path.insert(0, os.path.dirname(HERE))
-    from aspec_b200.data.synthetic import SyntheticSpec, make_document, synthetic_features
+    from aspec_b200.data.synthetic import SyntheticSpec, benchmark_documents, synthetic_features
     spec = SyntheticSpec(vocab_size=cfg.vocab_size - 1024, min_len=min(args.min_len, args.max_len),
                          max_len=args.max_len, seed=17)
     n_docs = args.pool or args.accum * 2
     pool = []
-    for i in range(n_docs):
-        row = rank * 100003 + i
-        doc = make_document(spec, row)
-        feats = synthetic_features(doc["seq_len"], n_tl, cfg.target_hidden_size, row, pin=cuda)
+    for doc in benchmark_documents(spec, n_docs, args.accum, rank):
+        feats = synthetic_features(doc["seq_len"], n_tl, cfg.target_hidden_size, doc["row"], pin=cuda)
         pool.append({"input_ids": doc["input_ids"][None], "loss_mask": doc["loss_mask"][None],
                      "hidden_states": feats["hidden_states"][None], "last_hidden_states": feats["last_hidden_states"][None],
                      "seq_len": doc["seq_len"]})

@@ -129,23 +129,17 @@ def build_ours(args, device, dtype):
 def make_pool(args, cfg, model, rank, n_docs, pin):
     """Host-side documents with features and pre-sampled anchors (the collator's job)."""
     import torch
-    from aspec_b200.data.synthetic import SyntheticSpec, make_document, synthetic_features
+    from aspec_b200.data.synthetic import SyntheticSpec, benchmark_documents, synthetic_features
     spec = SyntheticSpec(vocab_size=cfg.vocab_size - 1024, min_len=min(args.min_len, args.max_len), max_len=args.max_len, seed=17)
+    from aspec_b200.ops.anchors import sample_anchor_positions
     pool = []
-    for i in range(n_docs):
-        # Weak scaling: rank r's document i has the LENGTH of the 1-GPU run's document i (so per-GPU work is the same
-        # at every N and micro-steps are balanced across ranks, which is what the training controller's length-grouped
-        # deal approximates on real data) but its own token ids and features.
-        doc = make_document(spec, i)
-        row = rank * 100003 + i
-        if rank > 0:
-            g = torch.Generator().manual_seed(row)
-            doc["input_ids"] = torch.randint(0, spec.vocab_size, (doc["seq_len"],), generator=g, dtype=torch.int64)
-        T = doc["seq_len"]
+    # every rank gets documents with the 1-GPU run's lengths (own token ids and features), dealt to the updates so that
+    # each update carries about the same number of tokens: see ``benchmark_documents``
+    for doc in benchmark_documents(spec, n_docs, args.accum, rank):
+        row, T = doc["row"], doc["seq_len"]
         feats = synthetic_features(T, cfg.num_target_layers, cfg.target_hidden_size, row, pin=pin)
         lm = doc["loss_mask"][None]
         g = torch.Generator().manual_seed(row)
-        from aspec_b200.ops.anchors import sample_anchor_positions
         anchors, keep = sample_anchor_positions(T, lm, model.num_anchors, model.block_size, generator=g)
         batch = {"input_ids": doc["input_ids"][None], "loss_mask": lm,
                  "hidden_states": feats["hidden_states"][None], "last_hidden_states": feats["last_hidden_states"][None],
@@ -154,17 +148,6 @@ def make_pool(args, cfg, model, rank, n_docs, pin):
             for k in ("input_ids", "loss_mask", "injected_anchors"):
                 batch[k] = batch[k].pin_memory()
         pool.append(batch)
-    # One update takes ``accum`` consecutive documents of the pool.  Deal the documents to the updates by length
-    # (serpentine over the sorted list) so that every update carries about the same number of tokens and the metric does
-    # not depend on which updates fall into the timed window.
-    groups = max(len(pool) // max(args.accum, 1), 1)
-    if groups > 1 and len(pool) % groups == 0:
-        order = sorted(range(len(pool)), key=lambda i: -pool[i]["seq_len"])
-        buckets = [[] for _ in range(groups)]
-        for j, i in enumerate(order):
-            g = j % groups
-            buckets[g if (j // groups) % 2 == 0 else groups - 1 - g].append(i)
-        pool = [pool[i] for b in buckets for i in b]
     return pool
 
 
