@@ -38,7 +38,7 @@ def select_experts(scores: torch.Tensor, bias: torch.Tensor, top_k: int, n_group
     ranked = scores + bias
     if n_group > 1:
         per_group = ranked.view(ranked.shape[0], n_group, -1)
-        group_value = per_group.topk(2, dim=-1).values.sum(-1)                    # two best members speak for a group
+        group_value = per_group.topk(min(2, per_group.shape[-1]), dim=-1).values.sum(-1)   # two best members speak for a group
         chosen = group_value.topk(topk_group, dim=-1).indices
         allowed = torch.zeros_like(group_value, dtype=torch.bool).scatter_(1, chosen, True)
         ranked = per_group.masked_fill(~allowed[..., None], float("-inf")).flatten(1)

@@ -31,19 +31,16 @@ class LingGate(nn.Module):
         return self
 
     def forward(self, hidden: torch.Tensor):
-        logits = F.linear(hidden.reshape(-1, hidden.shape[-1]).float(), self.weight.float())
-        scores = logits.sigmoid()
-        pick = scores + self.expert_bias if self.bias_enabled else scores
-        per = scores.shape[-1] // self.groups
-        group_scores = pick.view(-1, self.groups, per).topk(min(2, per), -1).values.sum(-1)
-        keep = group_scores.topk(self.group_topk, -1, sorted=False).indices
-        gmask = torch.zeros_like(group_scores, dtype=torch.bool).scatter_(1, keep, True)
-        smask = gmask[:, :, None].expand(-1, -1, per).reshape_as(scores)
-        selected = pick.masked_fill(~smask, float("-inf")).topk(self.top_k, -1).indices
-        w = scores.gather(1, selected)
-        if self.top_k > 1:                       # top-1 keeps its raw sigmoid score
-            w = w / (w.sum(-1, keepdim=True) + 1e-20)
-        return selected, w * self.scale, logits
+        """``(selected [N, k], mixing weights [N, k], router logits [N, E])`` in fp32."""
+        from aspec_b200.models.draft.eagle4_moe import select_experts
+        logits = hidden.reshape(-1, hidden.shape[-1]).float() @ self.weight.float().t()
+        scores = torch.sigmoid(logits)
+        bias = self.expert_bias if self.bias_enabled else torch.zeros_like(self.expert_bias)
+        selected = select_experts(scores, bias, self.top_k, self.groups, self.group_topk)
+        mix = torch.gather(scores, 1, selected)
+        if self.top_k > 1:                       # a single expert keeps its raw sigmoid score
+            mix = mix / (mix.sum(-1, keepdim=True) + 1e-20)
+        return selected, mix * self.scale, logits
 
 
 class LingMoE(nn.Module):
