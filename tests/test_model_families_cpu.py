@@ -141,3 +141,28 @@ def test_mtp_conditioned_blocks(mode, arch):
     assert ("mtp_fusion.proj.weight" in grads) == (mode == "hidden")
     if arch == "DSparkDraftModel":
         assert "suffix_tau_probabilistic" in out[5]
+
+
+@pytest.mark.parametrize("ffn", ["ling_moe", "qwen3_moe"])
+def test_dspark_with_mixture_of_experts_feed_forward_trains(ffn):
+    """DSpark over the two MoE feed-forwards: experts and routers receive gradients, router statistics are reported,
+    and (Ling) the balancing bias moves once per committed step."""
+    extra = dict(ffn_type=ffn, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32)
+    if ffn == "ling_moe":
+        extra.update(num_shared_experts=1, moe_shared_expert_intermediate_size=32, n_group=2, topk_group=1, routed_scaling_factor=2.5,
+                     moe_router_enable_expert_bias=True, router_z_loss_coef=1e-3, expert_swiglu_limit_list=[0, 0],
+                     share_expert_swiglu_limit_list=[0, 0])
+    raw = dict(architectures=["DSparkDraftModel"], markov_rank=8, head_dim=16, target_layer_ids=[1, 3, 5], rope_theta=10000.0,
+               max_position_embeddings=512, **DFLASH, **extra)
+    model, out, grads = _step(raw)
+    assert any(".experts." in n for n in grads) and any(".gate." in n for n in grads)
+    if ffn == "ling_moe":
+        from aspec_b200.models.draft.ling_moe import LingMoE, update_ling_bias
+        assert {"router_z_loss", "router_max_load", "_ling_router_counts"} <= set(out[5])
+        layers = [m for m in model.draft_model.modules() if isinstance(m, LingMoE)]
+        counts = out[5]["_ling_router_counts"]
+        assert counts.shape == (len(layers), 8) and float(counts.sum()) > 0
+        before = [l.gate.expert_bias.clone() for l in layers]
+        update_ling_bias(layers, counts.clone(), update_rate=1e-3)
+        assert any(not torch.equal(b, l.gate.expert_bias) for b, l in zip(before, layers))
+        assert all(l.gate.expert_bias.dtype == torch.float32 for l in layers)
