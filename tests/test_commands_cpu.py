@@ -1,0 +1,145 @@
+"""Command-line entry points end to end on the CPU: environment check, the bounded quick start (plan, train, resume,
+report, export), acceptance evaluation of the exported asset with live and with stored Target features, and the
+corpus preparation commands."""
+import json
+
+import pytest
+import torch
+
+
+def _pretokenized(path, n=6, length=48, vocab=500, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    with open(path, "w") as f:
+        for i in range(n):
+            ids = torch.randint(0, vocab, (length + i,), generator=g).tolist()
+            f.write(json.dumps({"data_id": f"doc-{i}", "input_ids": ids,
+                                "loss_mask": [0] * 8 + [1] * (len(ids) - 8)}) + "\n")
+    return str(path)
+
+
+def test_doctor_reports_every_check(capsys):
+    from aspec_b200.commands import doctor
+    rc = doctor.main(["--json"])
+    report = json.loads(capsys.readouterr().out)
+    names = {c["name"] for c in report["checks"]}
+    assert {"torch", "nvcc"} <= names and report["gpu_requested"] is False
+    assert rc in (0, 1) and all(isinstance(c["ok"], bool) for c in report["checks"])
+
+
+@pytest.fixture(scope="module")
+def quickstart_run(tmp_path_factory):
+    from aspec_b200.commands import quickstart
+    out = tmp_path_factory.mktemp("quickstart") / "run"
+    assert quickstart.main(["tiny", "--output", str(out), "--steps", "2"]) == 0
+    return out
+
+
+def test_quickstart_trains_resumes_and_exports(quickstart_run):
+    acceptance = json.loads((quickstart_run / "acceptance.json").read_text())
+    assert acceptance["status"] == "passed"
+    stages = {s["stage"]: s for s in acceptance["stages"]}
+    assert stages["train first half"]["rc"] == 0 and stages["resume second half"]["rc"] == 0
+    assert stages["report"]["valid"] is True
+    asset = quickstart_run / "stage-2" / "asset"
+    assert (asset / "model.safetensors").exists() and (asset / "export_manifest.json").exists()
+
+
+def test_quickstart_plan_only_starts_nothing(tmp_path, capsys):
+    from aspec_b200.commands import quickstart
+    out = tmp_path / "planned"
+    assert quickstart.main(["tiny", "--output", str(out), "--plan"]) == 0
+    assert "plan" in capsys.readouterr().out.lower()
+    assert not (out / "stage-1" / "checkpoints").exists()
+
+
+def test_report_on_quickstart_stage(quickstart_run, capsys):
+    from aspec_b200 import train_entry
+    rc = train_entry.main(["--report", str(quickstart_run / "stage-2"), "--report-format", "json"])
+    report = json.loads(capsys.readouterr().out)
+    assert rc == 0 and isinstance(report, dict) and report
+
+
+def test_evaluate_exported_asset_with_live_target(quickstart_run, tmp_path, capsys):
+    from aspec_b200.commands import evaluate_draft
+    data = _pretokenized(tmp_path / "held.jsonl")
+    out = tmp_path / "eval.json"
+    rc = evaluate_draft.main(["--asset-dir", str(quickstart_run / "stage-2" / "asset"), "--data", data,
+                              "--block-size", "4", "--anchors-per-doc", "3", "--device", "cpu", "--output", str(out)])
+    capsys.readouterr()
+    result = json.loads(out.read_text())
+    assert rc == 0 and result["proposals"] == 18 and result["documents"] == 6
+    assert len(result["accept_rate_at"]) == 3 and 1.0 <= result["tau"] <= 4.0
+    rates = result["accept_rate_at"]
+    assert all(0.0 <= r <= 1.0 for r in rates) and rates == sorted(rates, reverse=True)
+
+
+def test_prepare_target_data_then_evaluate_from_store(quickstart_run, tmp_path, capsys):
+    from aspec_b200.commands import evaluate_draft, prepare_target_dataset
+    from aspec_b200.offline.dataset import OfflineFeatureStore
+    asset = quickstart_run / "stage-2" / "asset"
+    data = _pretokenized(tmp_path / "held.jsonl", n=4)
+    store_dir = tmp_path / "features"
+    rc = prepare_target_dataset.main(["--input", data, "--output-dir", str(store_dir), "--draft-config",
+                                      str(asset / "config.json"), "--device", "cpu"])
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and summary["samples"] == 4
+    store = OfflineFeatureStore(str(store_dir))
+    one = store.load("doc-0")
+    assert one["hidden_states"].shape[0] == 48
+    # a second call with --resume adds nothing and keeps the contract
+    rc = prepare_target_dataset.main(["--input", data, "--output-dir", str(store_dir), "--draft-config",
+                                      str(asset / "config.json"), "--device", "cpu", "--resume"])
+    again = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rc == 0 and again["samples"] == 4 and again["contract_id"] == summary["contract_id"]
+
+
+def test_prepare_data_split_is_stable_and_deduplicated(tmp_path, capsys):
+    from aspec_b200.commands import prepare_quality_dataset
+    rows = [{"conversations": [{"role": "user", "content": f"question {i}"}, {"role": "assistant", "content": f"answer {i}"}]}
+            for i in range(200)]
+    rows += rows[:10]                                                            # duplicates
+    rows.append({"conversations": [{"role": "user", "content": "no answer"}]})   # too short
+    src = tmp_path / "corpus.jsonl"
+    src.write_text("".join(json.dumps(r) + "\n" for r in rows))
+    for name in ("a", "b"):
+        assert prepare_quality_dataset.main(["--input", str(src), "--output-dir", str(tmp_path / name),
+                                             "--eval-fraction", "0.1", "--seed", "3"]) == 0
+    capsys.readouterr()
+    a, b = (json.loads((tmp_path / n / "manifest.json").read_text()) for n in ("a", "b"))
+    assert a["duplicates"] == 10 and a["too_short"] == 1 and a["train"]["rows"] + a["eval"]["rows"] == 200
+    assert 5 <= a["eval"]["rows"] <= 40
+    assert a["train"]["sha256"] == b["train"]["sha256"] and a["eval"]["sha256"] == b["eval"]["sha256"]
+    # growing the corpus never moves an old row to the other side
+    grown = tmp_path / "grown.jsonl"
+    grown.write_text(src.read_text() + json.dumps({"conversations": [{"role": "user", "content": "new"},
+                                                                     {"role": "assistant", "content": "row"}]}) + "\n")
+    assert prepare_quality_dataset.main(["--input", str(grown), "--output-dir", str(tmp_path / "c"),
+                                         "--eval-fraction", "0.1", "--seed", "3"]) == 0
+    capsys.readouterr()
+    old_eval = set((tmp_path / "a" / "eval.jsonl").read_text().splitlines())
+    new_eval = set((tmp_path / "c" / "eval.jsonl").read_text().splitlines())
+    assert old_eval <= new_eval and len(new_eval - old_eval) <= 1
+
+
+def test_select_answers_rules(tmp_path, capsys):
+    from aspec_b200.commands import prepare_selected_answers
+    rows = [{"id": 1, "prompt": [{"role": "user", "content": "q"}],
+             "candidates": [{"content": "long answer text", "score": 0.9}, {"content": "short", "score": 0.4}]},
+            {"id": 2, "prompt": [{"role": "user", "content": "q2"}], "candidates": [{"content": "weak", "score": 0.1}]},
+            {"id": 3, "prompt": [{"role": "user", "content": "q3"}], "candidates": []}]
+    src = tmp_path / "cands.jsonl"
+    src.write_text("".join(json.dumps(r) + "\n" for r in rows))
+
+    def run(*extra):
+        out = tmp_path / "out.jsonl"
+        assert prepare_selected_answers.main(["--input", str(src), "--output", str(out), *extra]) == 0
+        stats = json.loads(capsys.readouterr().out)
+        return stats, [json.loads(line) for line in out.read_text().splitlines()]
+
+    stats, kept = run()
+    assert stats == {"output": str(tmp_path / "out.jsonl"), "kept": 2, "dropped": 1, "rule": "best_score"}
+    assert kept[0]["conversations"][-1] == {"role": "assistant", "content": "long answer text"}
+    stats, kept = run("--rule", "shortest")
+    assert kept[0]["conversations"][-1]["content"] == "short"
+    stats, kept = run("--min-score", "0.5")
+    assert stats["kept"] == 1 and stats["dropped"] == 2 and kept[0]["id"] == 1
