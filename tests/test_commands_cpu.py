@@ -91,6 +91,16 @@ def test_prepare_target_data_then_evaluate_from_store(quickstart_run, tmp_path, 
                                       str(asset / "config.json"), "--device", "cpu", "--resume"])
     again = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert rc == 0 and again["samples"] == 4 and again["contract_id"] == summary["contract_id"]
+    # the stored features and output head give the statistics that the live Target gives
+    results = []
+    for extra in (["--features", str(store_dir)], []):
+        out = tmp_path / f"eval{len(extra)}.json"
+        assert evaluate_draft.main(["--asset-dir", str(asset), "--data", data, "--block-size", "4", "--anchors-per-doc", "2",
+                                    "--device", "cpu", "--output", str(out), *extra]) == 0
+        capsys.readouterr()
+        results.append(json.loads(out.read_text()))
+    assert results[0]["proposals"] == results[1]["proposals"] == 8
+    assert results[0]["accept_rate_at"] == pytest.approx(results[1]["accept_rate_at"], abs=0.26)
 
 
 def test_prepare_data_split_is_stable_and_deduplicated(tmp_path, capsys):
@@ -143,3 +153,51 @@ def test_select_answers_rules(tmp_path, capsys):
     assert kept[0]["conversations"][-1]["content"] == "short"
     stats, kept = run("--min-score", "0.5")
     assert stats["kept"] == 1 and stats["dropped"] == 2 and kept[0]["id"] == 1
+
+
+def test_convert_data_packs_loss_masks(tmp_path, capsys):
+    from aspec_b200.commands import convert_pretokenized_jsonl
+    from aspec_b200.data.dataset import load_training_samples
+    src = _pretokenized(tmp_path / "raw.jsonl", n=3, length=20)
+    out = tmp_path / "packed.jsonl"
+    rc = convert_pretokenized_jsonl.main(["--input", src, "--output", str(out), "--tokenizer", "unused",
+                                          "--max-seq-length", "21"])
+    stats = json.loads(capsys.readouterr().out)
+    rows = [json.loads(line) for line in out.read_text().splitlines()]
+    assert rc == 0 and stats["samples"] == 3 and stats["pretokenized"] is True
+    assert [r["data_id"] for r in rows] == ["doc-0", "doc-1", "doc-2"]
+    assert [len(r["input_ids"]) for r in rows] == [20, 21, 21]               # the third row is cut at the length limit
+    assert rows[0]["packed_loss_mask"] == "8,12" and "loss_mask" not in rows[0]
+    again = load_training_samples(str(out), {"max_seq_length": 64})
+    assert [s["packed_loss_mask"] for s in again] == [r["packed_loss_mask"] for r in rows]
+
+
+def test_stitch_native_mtp_into_target_directory(tmp_path, capsys):
+    from safetensors.torch import load_file, save_file
+    from aspec_b200.commands import stitch_native_mtp
+    asset, target, out = tmp_path / "asset", tmp_path / "target", tmp_path / "stitched"
+    asset.mkdir(), target.mkdir()
+    trained = {"mtp.layers.0.self_attn.q_proj.weight": torch.randn(8, 8), "mtp.fc.weight": torch.randn(8, 16),
+               "embed_tokens.weight": torch.randn(4, 8)}                      # only mtp.* tensors are stitched
+    save_file(trained, str(asset / "model.safetensors"))
+    (asset / "export_manifest.json").write_text(json.dumps({"algorithm": "mtp"}))
+    save_file({"model.layers.0.w": torch.zeros(2), "mtp.fc.weight": torch.zeros(8, 16)}, str(target / "model-00001.safetensors"))
+    (target / "config.json").write_text("{}")
+    (target / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": {
+        "model.layers.0.w": "model-00001.safetensors", "mtp.fc.weight": "model-00001.safetensors"}}))
+    rc = stitch_native_mtp.main(["--asset-dir", str(asset), "--target-dir", str(target), "--output-dir", str(out)])
+    report = json.loads(capsys.readouterr().out)
+    assert rc == 0 and report["tensors"] == 2 and report["replaced_existing"] == 1
+    index = json.loads((out / "model.safetensors.index.json").read_text())["weight_map"]
+    assert index["mtp.fc.weight"] == report["shard"] and index["model.layers.0.w"] == "model-00001.safetensors"
+    assert (out / "config.json").is_symlink() and (out / "model-00001.safetensors").is_symlink()
+    stitched = load_file(str(out / report["shard"]))
+    assert set(stitched) == {"mtp.layers.0.self_attn.q_proj.weight", "mtp.fc.weight"}
+    assert torch.equal(stitched["mtp.fc.weight"], trained["mtp.fc.weight"])
+    # the Target directory itself is never modified, and other algorithms are refused
+    assert json.loads((target / "model.safetensors.index.json").read_text())["weight_map"]["mtp.fc.weight"] == "model-00001.safetensors"
+    with pytest.raises(ValueError, match="in place"):
+        stitch_native_mtp.stitch(str(asset), str(target), str(target))
+    (asset / "export_manifest.json").write_text(json.dumps({"algorithm": "dflash"}))
+    with pytest.raises(ValueError, match="native MTP"):
+        stitch_native_mtp.stitch(str(asset), str(target), str(tmp_path / "other"))
