@@ -51,7 +51,13 @@ def create_engines(flat: Dict, draft_config: dict, layer_ids: List[int], target_
         return [eng], None, None
     if kind == "offline":
         from aspec_b200.inference.engine import OfflineReplayEngine
+        import os
         eng = OfflineReplayEngine(flat["offline_feature_dir"])
+        stored = eng.store.binding["feature_contract"]
+        if list(stored["aux_hidden_state_layers"]) != [int(i) for i in layer_ids] or int(stored["target_hidden_size"]) != hidden:
+            raise ValueError(f"offline features hold layers {stored['aux_hidden_state_layers']} of width {stored['target_hidden_size']}; "
+                             f"this Draft needs layers {list(layer_ids)} of width {hidden}")
         eng.attach_rings({c: hs[0] for c, hs in ring_handles.items()})
-        return [eng], None, None
+        head_file = os.path.join(flat["offline_feature_dir"], "lm_head.pt")      # written by prepare-target-data
+        return [eng], ({"file": head_file} if os.path.isfile(head_file) else None), None
     raise ValueError(f"unknown inference engine type {kind!r}")

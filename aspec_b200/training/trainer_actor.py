@@ -98,10 +98,15 @@ class TrainerActor:
         return [self.ring.export() for _ in range(max(int(copies), 1))]
 
     def set_head(self, lm_head: Optional[torch.Tensor], embedding: Optional[torch.Tensor] = None) -> None:
-        """Frozen Target output head (and embedding).  ``None`` -> deterministic random init (offline runs)."""
+        """Frozen Target output head (and embedding): a tensor, a relayable handle, ``{"file": path}`` (a head stored
+        beside offline features) or ``None`` -> deterministic random init (feature stores without a head)."""
         from aspec_b200.transport.feature_ring import import_tensor
         cfg = self.draft_config
-        if isinstance(lm_head, dict):
+        if isinstance(lm_head, dict) and "file" in lm_head:
+            lm_head = torch.load(lm_head["file"], map_location="cpu")
+            if tuple(lm_head.shape) != (cfg.vocab_size, getattr(cfg, "target_hidden_size", None) or cfg.hidden_size):
+                raise ValueError(f"stored Target head {tuple(lm_head.shape)} does not fit the Draft configuration")
+        elif isinstance(lm_head, dict):
             lm_head = import_tensor(lm_head)
         if isinstance(embedding, dict):
             embedding = import_tensor(embedding)

@@ -201,3 +201,45 @@ def test_stitch_native_mtp_into_target_directory(tmp_path, capsys):
     (asset / "export_manifest.json").write_text(json.dumps({"algorithm": "dflash"}))
     with pytest.raises(ValueError, match="native MTP"):
         stitch_native_mtp.stitch(str(asset), str(target), str(tmp_path / "other"))
+
+
+@pytest.mark.timeout(600)
+def test_offline_training_from_prepared_features(tmp_path, capsys):
+    """prepare-target-data -> training with the offline replay engine: the stored head is the one trained against, and
+    a store made for other Target layers is refused before any step runs."""
+    from aspec_b200 import train_entry
+    from aspec_b200.commands import prepare_target_dataset
+    data = _pretokenized(tmp_path / "docs.jsonl", n=16, length=40)
+    feats = tmp_path / "feats"
+    assert prepare_target_dataset.main(["--input", data, "--output-dir", str(feats), "--draft-config", "dspark_tiny.json",
+                                        "--device", "cpu"]) == 0
+    assert (feats / "lm_head.pt").exists()
+    recipe = tmp_path / "recipe.yaml"
+    recipe.write_text(f"""
+model:
+  draft_model_config: dspark_tiny.json
+dataset:
+  train_data_path: {data}
+inference:
+  inference_engine_type: offline
+  offline:
+    feature_dir: {feats}
+training:
+  training_num_gpus_per_node: 1
+  micro_batch_size: 1
+  draft_accumulation_steps: 2
+  max_seq_length: 128
+  num_train_steps: 2
+  learning_rate: 1e-3
+  dspark_block_size: 4
+  dspark_num_anchors: 16
+output_dir: {tmp_path / 'run'}
+""")
+    capsys.readouterr()
+    assert train_entry.main(["--config", str(recipe)]) == 0
+    evidence = json.loads((tmp_path / "run" / "evidence.json").read_text())
+    assert evidence["state"] == "completed" and evidence["training_summary"]["completed_steps"] == 2
+    assert evidence["training_summary"]["ledger"]["validated"]
+    with pytest.raises(ValueError, match="offline features hold layers"):
+        train_entry.main(["--config", str(recipe), "model.draft_model_config=dflash_tiny.json",
+                          f"output_dir={tmp_path / 'other'}"])
