@@ -141,10 +141,14 @@ def interval_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, interv
                        scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Differentiable interval attention: tcgen05 kernels on CUDA, fp32 reference on CPU."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else float(scale)
+    from aspec_b200.ops.observed import note
     if q.is_cuda:
         from aspec_b200.ops import attention_sm100 as K
         if K.supported(q, k, v):
+            note("attention", "tcgen05_interval_flash")
             return _IntervalAttentionFn.apply(q.contiguous(), k.contiguous(), v.contiguous(),
                                               intervals.contiguous(), scale)
+        note("attention", "dense_mask_fp32")
         return K.unsupported_shape_fallback(q, k, v, intervals, scale)
+    note("attention", "reference_fp32_cpu")
     return interval_attention_reference(q, k, v, intervals, scale)

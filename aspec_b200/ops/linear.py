@@ -14,6 +14,8 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
+from aspec_b200.ops.observed import note
+
 
 def _kernel_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
@@ -56,8 +58,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             x2d = x2d.contiguous()
         if x2d.shape[0] == 0:
             return x.new_zeros(*lead, w.shape[0])
+        note("gemm", "tcgen05_tma_persistent")
         y = _LinearFn.apply(x2d, w, w if isinstance(w, torch.nn.Parameter) else None)
         return y.view(*lead, w.shape[0])
+    note("gemm", "torch")
     return F.linear(x, w, bias)
 
 

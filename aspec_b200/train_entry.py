@@ -169,6 +169,14 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
                                 on_step=on_step)
         if eval_history:
             summary["evaluation"] = eval_history
+        # what rank 0 really launched, beside the plan's capability decisions
+        summary["capabilities_observed"] = trainers[0].call("observed_capabilities", timeout=60)
+        if evidence:
+            for subsystem, counts in summary["capabilities_observed"].items():
+                evidence.observe_capability(subsystem, counts)
+        traces = [f.get(timeout=300) for f in [t.call_async("flush_debug") for t in trainers]]
+        if any(traces):
+            summary["trace_files"] = sorted(p for files in traces for p in files)
         summary["engines"] = [e.call("get_status", timeout=30) if isinstance(e, ProcessActor) else e.get_status()
                               for e in engines]
         return summary

@@ -61,6 +61,7 @@ class DraftTrainer:
         self._pool: Dict[str, List[torch.Tensor]] = {}
         self._last: Dict[str, torch.Tensor] = {}
         self.post_step_hooks = []
+        self.pre_step_hooks: list = []
         self._copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
 
     # -- host -> device -------------------------------------------------------------
@@ -155,6 +156,8 @@ class DraftTrainer:
                 off += m
             if not self.sharded:            # the sharded optimizer reduces its own shard from the peers' buffers
                 dist.all_reduce(opt.flat_grad, group=self.dp_group)
+        for hook in self.pre_step_hooks:     # debug dumps read the accumulated (not yet scaled) gradients here
+            hook(self)
         den = pooled["loss"][1]
         opt.set_grad_scale(torch.where(den > 0, 1.0 / den.clamp(min=1e-12), torch.zeros_like(den)))
         grad_norm = opt.step()

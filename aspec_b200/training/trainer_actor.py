@@ -91,6 +91,33 @@ class TrainerActor:
         self.trainer: Optional[DraftTrainer] = None
         self.fault: Optional[dict] = self.args.get("fault_injection")      # host-side: {"kind": "raise"|"sleep", "step": k}
         self._pending_releases: List[tuple] = []
+        self._debug_instruments()
+
+    def _debug_instruments(self) -> None:
+        """Profiler window, memory snapshot, step dumps and the JSONL timeline, all off unless the ``debug`` /
+        ``logging`` sections ask for them.  Their files go under the run directory (``traces/``, ``dumps/``,
+        ``timeline/``) unless a directory is configured."""
+        from aspec_b200.utils.profiling import StepProfiler
+        from aspec_b200.utils.timeline import Timeline
+        a, out = self.args, str(self.args.get("output_dir") or ".")
+        start, end = int(a.get("profile_step_start") or 0), int(a.get("profile_step_end") or 0)
+        window = bool(a.get("use_pytorch_profiler")) and end > start
+        mem_step = a.get("memory_snapshot_num_steps") if a.get("record_memory_history") else None
+        trace_dir = a.get("profile_dir_name") if a.get("profile_dir_name") not in (None, "", "/tmp/aspec_profiles") else os.path.join(out, "traces")
+        self.profiler = (StepProfiler(trace_dir, start if window else None, end if window else None,
+                                      int(mem_step) if mem_step is not None else None, rank=self.rank)
+                         if window or mem_step is not None else None)
+        self.dump_dir = a.get("save_debug_train_data")
+        if self.dump_dir in (True, "true", "1"):
+            self.dump_dir = out
+        self.timeline = Timeline((a.get("timeline_output_dir") or os.path.join(out, "timeline")) if a.get("timeline_enabled") else None,
+                                 role="trainer", rank=self.rank, run_id=str(a.get("timeline_run_id") or a.get("run_id", "")),
+                                 flush_every=int(a.get("timeline_flush_every") or 128), enabled=bool(a.get("timeline_enabled")))
+
+    def observed_capabilities(self) -> dict:
+        """Counts of the implementations that this process really ran, per subsystem."""
+        from aspec_b200.ops.observed import snapshot
+        return snapshot()
 
     # -- setup ------------------------------------------------------------------------------------
     def ring_handle(self, copies: int = 1) -> list:
@@ -206,15 +233,43 @@ class TrainerActor:
         consumed, keys = [], []
         t0 = time.perf_counter()
 
+        dumping = bool(self.dump_dir) and step < int(self.args.get("max_dump_steps") or 0)
+        first_batch: dict = {}
+
         def batches():
             for sample in self._samples(num_batches, timeout):
-                b = self._batch(sample)
+                with self.timeline.span("batch_ready", step=step, rows=len(sample.metadata)):
+                    b = self._batch(sample)
+                if dumping and not first_batch:
+                    first_batch.update(b)
                 consumed.extend(m["execution_id"] for m in sample.metadata)
                 keys.append(sample.feature_key)
                 yield b
 
-        self.trainer.train_update(batches())
-        metrics = self.trainer.metrics()              # one device->host read; also orders the slot reuse
+        grad_norms: dict = {}
+
+        def capture_grad_norms(trainer) -> None:          # accumulated over the update, before the 1 / denominator scale
+            for name, p in trainer.draft.named_parameters():
+                g = getattr(p, "main_grad", None)
+                g = p.grad if g is None else g
+                if g is not None:
+                    grad_norms[name] = float(g.float().norm())
+
+        if self.profiler is not None:
+            self.profiler.step(step)
+        if dumping:
+            self.trainer.pre_step_hooks.append(capture_grad_norms)
+        try:
+            with self.timeline.span("train_update", step=step, micro_batches=num_batches):
+                self.trainer.train_update(batches())
+                metrics = self.trainer.metrics()      # one device->host read; also orders the slot reuse
+        finally:
+            if dumping:
+                self.trainer.pre_step_hooks.remove(capture_grad_norms)
+        if dumping:
+            from aspec_b200.utils.train_dump import dump_step
+            dump_step(str(self.dump_dir), step, self.rank, batch=first_batch, outputs=dict(metrics), model=self.model,
+                      grad_norms=grad_norms)
         if self.cuda:
             self.ring.check_status()
             from aspec_b200.ops.gemm import check_status
@@ -319,6 +374,14 @@ class TrainerActor:
             ckpt.finalize_load(info["checkpoint_dir"])
         return {k: info[k] for k in ("next_step", "global_step", "work_state", "checkpoint_dir")}
 
+    def flush_debug(self) -> list:
+        """Finish an open profiler window and flush the timeline; returns the trace files written so far."""
+        if self.profiler is not None:
+            self.profiler.close()
+        self.timeline.close()
+        return list(self.profiler.written) if self.profiler is not None else []
+
     def close(self) -> None:
+        self.flush_debug()
         if dist.is_available() and dist.is_initialized():
             dist.destroy_process_group()

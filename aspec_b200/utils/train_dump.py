@@ -20,7 +20,10 @@ def _cpu(value: Any) -> Any:
 
 
 def dump_step(run_dir: str, step: int, rank: int, *, batch: Optional[Dict[str, Any]] = None, outputs: Any = None,
-              model: Optional[torch.nn.Module] = None, max_tensor_elems: int = 1 << 22) -> str:
+              model: Optional[torch.nn.Module] = None, max_tensor_elems: int = 1 << 22,
+              grad_norms: Optional[Dict[str, float]] = None) -> str:
+    """``grad_norms`` overrides the norms read from ``model`` (a trainer whose optimizer step clears the gradients
+    captures them before the step)."""
     os.makedirs(os.path.join(run_dir, "dumps"), exist_ok=True)
     record: Dict[str, Any] = {"step": step, "rank": rank}
     if batch is not None:
@@ -35,7 +38,7 @@ def dump_step(run_dir: str, step: int, rank: int, *, batch: Optional[Dict[str, A
             g = getattr(p, "main_grad", None) if getattr(p, "main_grad_touched", False) else p.grad
             if g is not None:
                 grads[name] = float(g.float().norm())
-        record["grad_norms"] = grads
+        record["grad_norms"] = grads if grad_norms is None else dict(grad_norms)
         record["param_norms"] = {n: float(p.detach().float().norm()) for n, p in model.named_parameters()}
     path = os.path.join(run_dir, "dumps", f"step-{step}-rank{rank}.pt")
     torch.save(record, path)

@@ -243,3 +243,30 @@ output_dir: {tmp_path / 'run'}
     with pytest.raises(ValueError, match="offline features hold layers"):
         train_entry.main(["--config", str(recipe), "model.draft_model_config=dflash_tiny.json",
                           f"output_dir={tmp_path / 'other'}"])
+
+
+@pytest.mark.timeout(600)
+def test_debug_instruments_and_observed_capabilities(tmp_path, capsys):
+    """A run with the profiler window, step dumps and the timeline switched on writes all three under the run
+    directory, and the evidence names the implementations that really ran."""
+    from aspec_b200 import train_entry
+    run = tmp_path / "run"
+    overrides = ["output_dir=" + str(run), "training.num_train_steps=3", "debug.use_pytorch_profiler=true",
+                 "debug.profile_step_start=1", "debug.profile_step_end=2", "debug.save_debug_train_data=true",
+                 "debug.max_dump_steps=2", "debug.timeline_enabled=true"]
+    from aspec_b200.assets import find_asset
+    assert train_entry.main(["--config", find_asset("quickstart_tiny.yaml"), *overrides]) == 0
+    capsys.readouterr()
+    evidence = json.loads((run / "evidence.json").read_text())
+    assert evidence["state"] == "completed"
+    observed = evidence["capabilities_observed"]
+    assert set(observed["attention"]) == {"reference_fp32_cpu"} and observed["attention"]["reference_fp32_cpu"] > 0
+    assert set(observed["gemm"]) == {"torch"}
+    assert [p.name for p in (run / "traces").glob("trace-*.json")] == ["trace-steps1-2-rank0.json"]
+    assert sorted(p.name for p in (run / "dumps").iterdir()) == ["step-0-rank0.pt", "step-1-rank0.pt"]
+    dump = torch.load(run / "dumps" / "step-1-rank0.pt", weights_only=False)
+    assert "input_ids" in dump["batch"] and dump["grad_norms"] and "loss" in " ".join(dump["outputs"])
+    rows = [json.loads(line) for f in (run / "timeline").glob("timeline-trainer-0-*.jsonl") for line in f.read_text().splitlines()]
+    updates = [r for r in rows if r["name"] == "train_update"]
+    assert [r["step"] for r in updates] == [0, 1, 2] and all(r["duration_ns"] > 0 for r in updates)
+    assert any(r["name"] == "batch_ready" for r in rows)
