@@ -37,7 +37,8 @@ class DraftTrainer:
                  min_lr: float = 6e-5, weight_decay: float = 0.0, max_grad_norm: float = 1.0,
                  total_steps: int = 1000, warmup_ratio: float = 0.04, decay_style: str = "cosine",
                  accumulation: int = 1, dp_group: Optional[dist.ProcessGroup] = None,
-                 device: Optional[torch.device] = None, betas=(0.9, 0.999), fsdp_strategy: str = "REPLICATE"):
+                 device: Optional[torch.device] = None, betas=(0.9, 0.999), fsdp_strategy: str = "REPLICATE",
+                 wsd_decay_steps: Optional[int] = None, wsd_decay_style: Optional[str] = None):
         self.model = model
         self.draft = model.draft_model
         self.lm_head_weight = lm_head_weight
@@ -51,12 +52,13 @@ class DraftTrainer:
             from aspec_b200.training.sharded_optimizer import ShardedBF16Optimizer
             self.optimizer = ShardedBF16Optimizer(self.draft, lr=lr, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
                                                   total_steps=total_steps, warmup_ratio=warmup_ratio, decay_style=decay_style,
-                                                  min_lr=min_lr, betas=betas, group=dp_group)
+                                                  min_lr=min_lr, betas=betas, group=dp_group,
+                                                  wsd_decay_steps=wsd_decay_steps, wsd_decay_style=wsd_decay_style)
         else:
             self.optimizer = BF16Optimizer(self.draft, lr=lr, weight_decay=weight_decay,
                                            max_grad_norm=max_grad_norm, total_steps=total_steps,
                                            warmup_ratio=warmup_ratio, decay_style=decay_style, min_lr=min_lr,
-                                           betas=betas)
+                                           betas=betas, wsd_decay_steps=wsd_decay_steps, wsd_decay_style=wsd_decay_style)
         self.global_step = 0
         self._pool: Dict[str, List[torch.Tensor]] = {}
         self._last: Dict[str, torch.Tensor] = {}

@@ -44,6 +44,8 @@ class TrainerActor:
         torch.manual_seed(int(self.args.get("seed", 0)))
         self.draft_config = AutoDraftModelConfig.from_dict(draft_config)
         self.model = build_training_model(self.draft_config, self.args, self.device, self.dtype)
+        if self.args.get("initial_draft_model_path") and not self.args.get("load_path"):
+            self._load_initial_weights(str(self.args["initial_draft_model_path"]))
         cfg = self.draft_config
         self.cp_size = max(int(self.args.get("draft_context_parallel_size", 1) or 1), 1)
         if self.cp_size > 1 and hasattr(self.model, "context_parallel") and world > 1:
@@ -92,6 +94,25 @@ class TrainerActor:
         self.fault: Optional[dict] = self.args.get("fault_injection")      # host-side: {"kind": "raise"|"sleep", "step": k}
         self._pending_releases: List[tuple] = []
         self._debug_instruments()
+
+    @torch.no_grad()
+    def _load_initial_weights(self, asset_dir: str) -> None:
+        """Start from an exported Draft (``model.initial_draft_model_path``): its tensors are copied into the freshly
+        built modules in place, before the optimizer takes its fp32 masters from them.  The asset must hold exactly
+        this architecture's tensors; a resume (``load_path``) takes precedence over it
+        (reference: aspec/training/checkpoint.py:772-858)."""
+        from safetensors.torch import load_file
+        from aspec_b200.draft_artifact import validate_native_asset
+        validate_native_asset(asset_dir)
+        tensors = load_file(os.path.join(asset_dir, "model.safetensors"))
+        draft = self.model.draft_model
+        own = draft.state_dict()
+        wrong = sorted(k for k in tensors if k in own and tuple(tensors[k].shape) != tuple(own[k].shape))
+        if set(tensors) != set(own) or wrong:
+            missing, extra = sorted(set(own) - set(tensors)), sorted(set(tensors) - set(own))
+            raise ValueError(f"initial Draft asset {asset_dir} does not fit this Draft configuration: missing {missing[:4]}, "
+                             f"unexpected {extra[:4]}, shape mismatch {wrong[:4]}")
+        draft.load_state_dict({k: v.to(self.device) for k, v in tensors.items()}, strict=True)
 
     def _debug_instruments(self) -> None:
         """Profiler window, memory snapshot, step dumps and the JSONL timeline, all off unless the ``debug`` /
@@ -162,9 +183,15 @@ class TrainerActor:
         if embedding is not None and hasattr(draft, "load_embedding"):
             draft.load_embedding(embedding.to(self.device))
         a = self.args
+        total = int(a.get("lr_total_steps") or a.get("num_train_steps") or 1000)
+        wsd = {}
+        if a.get("lr_decay_style") == "WSD":     # warm-up, stable, then a final decay over ``ratio`` of the schedule
+            ratio = float(a.get("wsd_decay_ratio") if a.get("wsd_decay_ratio") is not None else a.get("lr_wsd_decay_ratio", 0.2))
+            wsd = {"wsd_decay_steps": min(max(int(round(total * ratio)), 1), total),
+                   "wsd_decay_style": a.get("wsd_decay_style") or a.get("lr_wsd_decay_style") or "cosine"}
         self.trainer = DraftTrainer(self.model, self.lm_head, lr=a.get("learning_rate", 1e-4), min_lr=a.get("min_lr", 0.0),
                                     weight_decay=a.get("weight_decay", 0.0), max_grad_norm=a.get("max_grad_norm", 0.5),
-                                    total_steps=int(a.get("lr_total_steps") or a.get("num_train_steps") or 1000),
+                                    total_steps=total, **wsd,
                                     warmup_ratio=a.get("warmup_ratio", 0.015), decay_style=a.get("lr_decay_style", "cosine"),
                                     accumulation=int(a.get("draft_accumulation_steps", 1)), device=self.device,
                                     fsdp_strategy=str(a.get("fsdp_strategy", "REPLICATE")))

@@ -270,3 +270,34 @@ def test_debug_instruments_and_observed_capabilities(tmp_path, capsys):
     updates = [r for r in rows if r["name"] == "train_update"]
     assert [r["step"] for r in updates] == [0, 1, 2] and all(r["duration_ns"] > 0 for r in updates)
     assert any(r["name"] == "batch_ready" for r in rows)
+
+
+@pytest.mark.timeout(600)
+def test_initial_weights_from_an_exported_asset_and_wsd_schedule(quickstart_run, tmp_path, capsys):
+    """A run that starts from the quick start's exported Draft holds exactly that Draft's weights (checked with a zero
+    learning rate), a warm-up / stable / decay schedule reports the expected rates, and an asset of another
+    architecture is refused."""
+    from pathlib import Path
+    from safetensors.torch import load_file
+    from aspec_b200 import train_entry
+    from aspec_b200.assets import find_asset
+    from aspec_b200.commands.convert_to_hf import convert_checkpoint
+    asset = quickstart_run / "stage-2" / "asset"
+    recipe = find_asset("quickstart_tiny.yaml")
+    frozen = tmp_path / "frozen"
+    assert train_entry.main(["--config", recipe, f"output_dir={frozen}", "training.num_train_steps=1", "training.learning_rate=0.0",
+                             "training.min_lr=0.0", "training.save_final_checkpoint=true",
+                             f"model.initial_draft_model_path={asset}"]) == 0
+    convert_checkpoint(input_dir=Path(frozen / "checkpoints" / "iter_0000001"), output_dir=Path(tmp_path / "again"),
+                       artifact_format="aspec")
+    before, after = load_file(str(asset / "model.safetensors")), load_file(str(tmp_path / "again" / "model.safetensors"))
+    assert set(before) == set(after) and all(torch.equal(before[k], after[k]) for k in before)
+    capsys.readouterr()
+    assert train_entry.main(["--config", recipe, f"output_dir={tmp_path / 'wsd'}", "training.num_train_steps=4",
+                             "training.lr_decay_style=WSD", "training.lr_wsd_decay_ratio=0.5", "training.lr_wsd_decay_style=linear",
+                             "training.warmup_ratio=0.25", "training.learning_rate=1e-3", "training.min_lr=0.0"]) == 0
+    summary = json.loads((tmp_path / "wsd" / "evidence.json").read_text())["training_summary"]
+    assert summary["completed_steps"] == 4
+    with pytest.raises(Exception, match="does not fit this Draft configuration"):
+        train_entry.main(["--config", recipe, f"output_dir={tmp_path / 'bad'}", "model.draft_model_config=dflash_tiny.json",
+                          f"model.initial_draft_model_path={asset}"])
