@@ -190,10 +190,10 @@ class SyntheticEngine(InferenceEngine):
 class OfflineReplayEngine(InferenceEngine):
     """Replays ``samples/*.pt`` of an offline feature store into ring slots."""
 
-    def __init__(self, feature_dir: str, name: str = "offline0"):
+    def __init__(self, feature_dir: str, name: str = "offline0", require_complete: bool = True):
         from aspec_b200.offline.dataset import OfflineFeatureStore
         self.name = name
-        self.store = OfflineFeatureStore(feature_dir)
+        self.store = OfflineFeatureStore(feature_dir, allow_incomplete=not require_complete)
         self.layer_ids = tuple(self.store.binding["feature_contract"]["aux_hidden_state_layers"])
         self.rings = {}
 

@@ -52,7 +52,7 @@ def create_engines(flat: Dict, draft_config: dict, layer_ids: List[int], target_
     if kind == "offline":
         from aspec_b200.inference.engine import OfflineReplayEngine
         import os
-        eng = OfflineReplayEngine(flat["offline_feature_dir"])
+        eng = OfflineReplayEngine(flat["offline_feature_dir"], require_complete=bool(flat.get("offline_require_complete", True)))
         stored = eng.store.binding["feature_contract"]
         if list(stored["aux_hidden_state_layers"]) != [int(i) for i in layer_ids] or int(stored["target_hidden_size"]) != hidden:
             raise ValueError(f"offline features hold layers {stored['aux_hidden_state_layers']} of width {stored['target_hidden_size']}; "

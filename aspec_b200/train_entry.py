@@ -237,16 +237,22 @@ def main(argv=None) -> int:
         if a.preflight_only:
             evidence.complete({"preflight_only": True})
             return 0
-        log_path = os.path.join(flat["output_dir"], "runs", "metrics.jsonl")
+        from aspec_b200.utils.logging import Trackers
+        wanted = [name for name, key in (("tensorboard", "use_tensorboard"), ("wandb", "use_wandb")) if flat.get(key)]
+        trackers = Trackers(flat["output_dir"], ",".join(wanted) or "none", project=flat.get("wandb_project") or "aspec-b200",
+                            run_name=flat.get("wandb_run_id"), config=config.to_dict(),
+                            wandb_mode=flat.get("wandb_mode") or "offline")
 
         def log(m: dict) -> None:
-            with open(log_path, "a") as f:
-                f.write(json.dumps(m, default=float) + "\n")
+            trackers.log(m, int(m.get("train/step") or 0))
             print(f"step {m.get('train/step')}: loss {m.get('train/avg_loss', float('nan')):.4f} "
                   f"acc {m.get('train/avg_acc', 0):.3f} tokens {m.get('perf/input_tokens')} "
                   f"wall {m.get('perf/step_wall_time', 0):.3f}s", flush=True)
 
-        summary = train_async_no_generation(flat, plan.draft_config, evidence, log)
+        try:
+            summary = train_async_no_generation(flat, plan.draft_config, evidence, log)
+        finally:
+            trackers.close()
         evidence.complete({k: v for k, v in summary.items() if k != "history"})
         return 0
     except BaseException as exc:                                  # noqa: BLE001 - recorded, then re-raised

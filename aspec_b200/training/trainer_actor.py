@@ -39,8 +39,11 @@ class TrainerActor:
         if world > 1:
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
             os.environ["MASTER_PORT"] = str(master_port)
+            # a collective that a lost rank never joins ends with an error after this long instead of waiting forever
+            from datetime import timedelta
             dist.init_process_group("nccl" if self.cuda else "gloo", rank=rank, world_size=world,
-                                    device_id=self.device if self.cuda else None)
+                                    device_id=self.device if self.cuda else None,
+                                    timeout=timedelta(minutes=float(self.args.get("distributed_timeout_minutes") or 10)))
         torch.manual_seed(int(self.args.get("seed", 0)))
         self.draft_config = AutoDraftModelConfig.from_dict(draft_config)
         self.model = build_training_model(self.draft_config, self.args, self.device, self.dtype)

@@ -266,6 +266,9 @@ def test_debug_instruments_and_observed_capabilities(tmp_path, capsys):
     assert sorted(p.name for p in (run / "dumps").iterdir()) == ["step-0-rank0.pt", "step-1-rank0.pt"]
     dump = torch.load(run / "dumps" / "step-1-rank0.pt", weights_only=False)
     assert "input_ids" in dump["batch"] and dump["grad_norms"] and "loss" in " ".join(dump["outputs"])
+    metrics = [json.loads(line) for line in (run / "runs" / "metrics.jsonl").read_text().splitlines()]
+    assert [m["step"] for m in metrics] == [0, 1, 2] and all("train/avg_loss" in m for m in metrics)
+    assert json.loads((run / "tracking.json").read_text())["active"] == ["jsonl"]
     rows = [json.loads(line) for f in (run / "timeline").glob("timeline-trainer-0-*.jsonl") for line in f.read_text().splitlines()]
     updates = [r for r in rows if r["name"] == "train_update"]
     assert [r["step"] for r in updates] == [0, 1, 2] and all(r["duration_ns"] > 0 for r in updates)
