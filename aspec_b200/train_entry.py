@@ -254,10 +254,15 @@ def main(argv=None) -> int:
         finally:
             trackers.close()
         evidence.complete({k: v for k, v in summary.items() if k != "history"})
-        return 0
     except BaseException as exc:                                  # noqa: BLE001 - recorded, then re-raised
         evidence.fail(exc)
         raise
+    if flat.get("performance_measurement_required") and not (summary.get("window") or {}).get("valid"):
+        # the run itself is complete and recorded; what is refused is calling it a throughput measurement
+        raise ValueError("debug.performance_measurement_required: the run has no valid steady throughput window "
+                         "(needs more optimizer steps than performance_warmup_steps + performance_drain_steps, "
+                         "and at least one warm-up step)")
+    return 0
 
 
 if __name__ == "__main__":

@@ -304,3 +304,20 @@ def test_initial_weights_from_an_exported_asset_and_wsd_schedule(quickstart_run,
     with pytest.raises(Exception, match="does not fit this Draft configuration"):
         train_entry.main(["--config", recipe, f"output_dir={tmp_path / 'bad'}", "model.draft_model_config=dflash_tiny.json",
                           f"model.initial_draft_model_path={asset}"])
+
+
+@pytest.mark.timeout(600)
+def test_required_throughput_measurement(tmp_path, capsys):
+    from aspec_b200 import train_entry
+    from aspec_b200.assets import find_asset
+    recipe = find_asset("quickstart_tiny.yaml")
+    with pytest.raises(ValueError, match="no valid steady throughput window"):
+        train_entry.main(["--config", recipe, f"output_dir={tmp_path / 'short'}", "training.num_train_steps=2",
+                          "debug.performance_measurement_required=true", "debug.performance_warmup_steps=2"])
+    assert json.loads((tmp_path / "short" / "evidence.json").read_text())["state"] == "completed"
+    assert train_entry.main(["--config", recipe, f"output_dir={tmp_path / 'long'}", "training.num_train_steps=4",
+                             "debug.performance_measurement_required=true", "debug.performance_warmup_steps=1",
+                             "debug.performance_drain_steps=1"]) == 0
+    window = json.loads((tmp_path / "long" / "evidence.json").read_text())["training_summary"]["window"]
+    assert window["valid"] and window["steps"] == 2 and window["tokens_per_second"] > 0
+    capsys.readouterr()
