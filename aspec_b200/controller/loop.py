@@ -72,11 +72,15 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
 
     manager.on_result = on_result
 
+    epoch_boundaries: set = set()
+    last_saved = None
+
     def submit(step: int) -> bool:
         plan = controller.plan_update(accumulation)
         if plan is None:
             if int(args.get("num_epochs", 1)) > controller.epoch + 1:
                 controller.next_epoch()
+                epoch_boundaries.add(step)          # update ``step`` opens an epoch: ``step`` updates complete the last one
                 plan = controller.plan_update(accumulation)
             if plan is None:
                 return False
@@ -151,13 +155,14 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
         if timeline:
             timeline.event("optimizer_step", step=step, tokens=tokens)
         next_step_id = step + 1
-        if output_dir and save_interval and next_step_id % save_interval == 0:
+        if output_dir and ((save_interval and next_step_id % save_interval == 0)
+                           or (args.get("save_per_epoch") and next_step_id in epoch_boundaries)):
             save_checkpoint(trainers, controller, output_dir, next_step_id, args)
+            last_saved = next_step_id
         if on_step is not None:
             on_step(next_step_id, metrics)          # held-out evaluation, trackers
         step += 1
-    if output_dir and args.get("save_final_checkpoint", True) and completed and not (
-            save_interval and step % save_interval == 0):
+    if output_dir and args.get("save_final_checkpoint", True) and completed and last_saved != step:
         save_checkpoint(trainers, controller, output_dir, step, args)
     summary = {"completed_steps": completed, "last_step": step - 1, "window": window.summary(),
                "ledger": controller.ledger.status(), "dropped_tail_samples": controller.dropped_tail,

@@ -200,3 +200,18 @@ output_dir: {tmp_path / name}
         assert summary["completed_steps"] == 2 and summary["ledger"]["validated"]
         losses[name] = [l["train/avg_loss"] for l in logs]
     assert losses["sp2"] == pytest.approx(losses["one"], rel=1e-3)
+
+
+@pytest.mark.timeout(600)
+def test_checkpoint_at_every_epoch_end(tmp_path):
+    """Eight documents, four per update: an epoch is two updates.  With ``save_per_epoch`` and no interval the run keeps a
+    checkpoint where each epoch closed, and the final one is not written twice."""
+    plan = _plan(tmp_path, ["dataset.synthetic_num_documents=8", "training.num_train_steps=5", "training.num_epochs=3",
+                            "training.save_interval=0", "training.save_per_epoch=true", "training.max_checkpoints=10"])
+    flat = plan.to_runtime_args()
+    flat.update(synthetic_vocab_size=500, force_cpu=True)
+    os.makedirs(flat["output_dir"], exist_ok=True)
+    summary = train_async_no_generation(flat, plan.draft_config, log=lambda m: None)
+    assert summary["completed_steps"] == 5
+    ck = os.path.join(flat["output_dir"], "checkpoints")
+    assert sorted(d for d in os.listdir(ck) if d.startswith("iter_")) == ["iter_0000002", "iter_0000004", "iter_0000005"]
