@@ -163,10 +163,17 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
                     m = runner.run(next_step)
                     eval_history.append({"step": next_step, **m})
                     log({"train/step": next_step - 1, **m})
-        summary = training_loop(controller=controller, manager=manager, trainers=trainers, rings=rings,
-                                train_queues=queues, args=args, layer_ids=layer_ids, num_steps=num_steps - start_step,
-                                start_step=start_step, log=log, evidence=evidence, consumer_of_rank=consumer_of_rank,
-                                on_step=on_step)
+        from aspec_b200.utils.timeline import Timeline
+        timeline = Timeline((flat.get("timeline_output_dir") or os.path.join(str(flat.get("output_dir") or "."), "timeline"))
+                            if flat.get("timeline_enabled") else None, role="driver", run_id=str(flat.get("timeline_run_id") or ""),
+                            flush_every=int(flat.get("timeline_flush_every") or 128), enabled=bool(flat.get("timeline_enabled")))
+        try:
+            summary = training_loop(controller=controller, manager=manager, trainers=trainers, rings=rings,
+                                    train_queues=queues, args=args, layer_ids=layer_ids, num_steps=num_steps - start_step,
+                                    start_step=start_step, log=log, evidence=evidence, consumer_of_rank=consumer_of_rank,
+                                    on_step=on_step, timeline=timeline)
+        finally:
+            timeline.close()
         if eval_history:
             summary["evaluation"] = eval_history
         # what rank 0 really launched, beside the plan's capability decisions

@@ -273,6 +273,8 @@ def test_debug_instruments_and_observed_capabilities(tmp_path, capsys):
     updates = [r for r in rows if r["name"] == "train_update"]
     assert [r["step"] for r in updates] == [0, 1, 2] and all(r["duration_ns"] > 0 for r in updates)
     assert any(r["name"] == "batch_ready" for r in rows)
+    driver = [json.loads(line) for f in (run / "timeline").glob("timeline-driver-0-*.jsonl") for line in f.read_text().splitlines()]
+    assert [r["step"] for r in driver if r["name"] == "optimizer_step"] == [0, 1, 2]
 
 
 @pytest.mark.timeout(600)
