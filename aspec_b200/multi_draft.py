@@ -240,7 +240,29 @@ def run_multi_draft_from_config(config: Config, dry_run: bool = False) -> int:
     os.makedirs(config.output_dir, exist_ok=True)
     with open(os.path.join(config.output_dir, "multi-draft-plan.json"), "w") as f:
         f.write(plan.to_json())
-    results = run_multi_draft(plan, log=lambda m: print(json.dumps(m, default=float), flush=True))
+    from aspec_b200.utils.logging import Trackers
+    trackers: Dict[str, Trackers] = {}
+
+    def log(m: dict) -> None:
+        """One metrics writer per experiment, under that experiment's own run directory."""
+        print(json.dumps(m, default=float), flush=True)
+        name = m.get("experiment")
+        if name not in plan.plans:
+            return
+        if name not in trackers:
+            flat = plan.plans[name].to_runtime_args()
+            wanted = [t for t, key in (("tensorboard", "use_tensorboard"), ("wandb", "use_wandb")) if flat.get(key)]
+            os.makedirs(flat["output_dir"], exist_ok=True)
+            trackers[name] = Trackers(flat["output_dir"], ",".join(wanted) or "none",
+                                      project=flat.get("wandb_project") or "aspec-b200", run_name=f"{flat.get('wandb_run_id') or 'run'}-{name}",
+                                      wandb_mode=flat.get("wandb_mode") or "offline")
+        trackers[name].log({k: v for k, v in m.items() if k != "experiment"}, int(m.get("train/step") or 0))
+
+    try:
+        results = run_multi_draft(plan, log=log)
+    finally:
+        for t in trackers.values():
+            t.close()
     with open(os.path.join(config.output_dir, "multi-draft-summary.json"), "w") as f:
         json.dump({k: ({kk: vv for kk, vv in v.items() if kk != "history"} if isinstance(v, dict) else v)
                    for k, v in results.items()}, f, indent=2, default=str)

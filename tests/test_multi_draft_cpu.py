@@ -83,3 +83,21 @@ def test_failed_experiment_is_fenced_and_sibling_finishes(tmp_path):
 def test_experiments_must_agree_on_the_row_stream(tmp_path):
     with pytest.raises(ValueError, match="must agree on max_seq_length"):
         _plan(tmp_path, second_extra="    training:\n      max_seq_length: 64\n")
+
+
+@pytest.mark.timeout(600)
+def test_multi_draft_from_the_command_line_writes_per_experiment_metrics(tmp_path, capsys):
+    import json
+    from aspec_b200 import train_entry
+    _plan(tmp_path)                                   # writes recipe.yaml
+    recipe = tmp_path / "recipe.yaml"
+    assert train_entry.main(["--config", str(recipe), "dataset.synthetic_vocab_size=500"]) == 0
+    capsys.readouterr()
+    run = tmp_path / "run"
+    summary = json.loads((run / "multi-draft-summary.json").read_text())
+    assert summary["spark"]["completed_steps"] == 3 and summary["flash"]["completed_steps"] == 3
+    assert json.loads((run / "multi-draft-plan.json").read_text())["experiments"] == ["spark", "flash"]
+    for name in ("spark", "flash"):
+        rows = [json.loads(line) for line in (run / "experiments" / name / "runs" / "metrics.jsonl").read_text().splitlines()]
+        assert [r["step"] for r in rows] == [0, 1, 2] and all("experiment" not in r for r in rows)
+        assert json.loads((run / "experiments" / name / "tracking.json").read_text())["active"] == ["jsonl"]
