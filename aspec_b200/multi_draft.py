@@ -255,7 +255,8 @@ def run_multi_draft_from_config(config: Config, dry_run: bool = False) -> int:
             os.makedirs(flat["output_dir"], exist_ok=True)
             trackers[name] = Trackers(flat["output_dir"], ",".join(wanted) or "none",
                                       project=flat.get("wandb_project") or "aspec-b200", run_name=f"{flat.get('wandb_run_id') or 'run'}-{name}",
-                                      wandb_mode=flat.get("wandb_mode") or "offline")
+                                      wandb_mode=flat.get("wandb_mode") or "offline", wandb_group=flat.get("wandb_group"),
+                            wandb_team=flat.get("wandb_team"), wandb_dir=flat.get("wandb_dir"))
         trackers[name].log({k: v for k, v in m.items() if k != "experiment"}, int(m.get("train/step") or 0))
 
     try:

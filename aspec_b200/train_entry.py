@@ -248,7 +248,8 @@ def main(argv=None) -> int:
         wanted = [name for name, key in (("tensorboard", "use_tensorboard"), ("wandb", "use_wandb")) if flat.get(key)]
         trackers = Trackers(flat["output_dir"], ",".join(wanted) or "none", project=flat.get("wandb_project") or "aspec-b200",
                             run_name=flat.get("wandb_run_id"), config=config.to_dict(),
-                            wandb_mode=flat.get("wandb_mode") or "offline")
+                            wandb_mode=flat.get("wandb_mode") or "offline", wandb_group=flat.get("wandb_group"),
+                            wandb_team=flat.get("wandb_team"), wandb_dir=flat.get("wandb_dir"))
 
         def log(m: dict) -> None:
             trackers.log(m, int(m.get("train/step") or 0))

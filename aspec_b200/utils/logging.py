@@ -69,9 +69,11 @@ class TensorBoardTracker:
 class WandbTracker:
     name = "wandb"
 
-    def __init__(self, run_dir: str, project: str, run_name: Optional[str], config: Optional[dict], mode: str = "offline"):
+    def __init__(self, run_dir: str, project: str, run_name: Optional[str], config: Optional[dict], mode: str = "offline",
+                 group: Optional[str] = None, team: Optional[str] = None, directory: Optional[str] = None):
         import wandb                                                 # optional dependency
-        self.run = wandb.init(project=project, name=run_name, dir=run_dir, config=config or {}, mode=mode, reinit=True)
+        self.run = wandb.init(project=project, name=run_name, dir=directory or run_dir, config=config or {}, mode=mode,
+                              group=group, entity=team, reinit=True)
 
     def log(self, metrics: Dict[str, Any], step: int) -> None:
         self.run.log({k: v for k, v in metrics.items() if isinstance(v, (int, float))}, step=step)
@@ -85,7 +87,8 @@ class Trackers:
     comma-separated list; the JSONL sink is always on."""
 
     def __init__(self, run_dir: str, report_to: str = "none", *, project: str = "aspec-b200", run_name: Optional[str] = None,
-                 config: Optional[dict] = None, wandb_mode: str = "offline"):
+                 config: Optional[dict] = None, wandb_mode: str = "offline", wandb_group: Optional[str] = None,
+                 wandb_team: Optional[str] = None, wandb_dir: Optional[str] = None):
         self.run_dir = run_dir
         self.active: List[Any] = [JsonlTracker(run_dir)]
         self.unavailable: Dict[str, str] = {}
@@ -95,7 +98,7 @@ class Trackers:
                 if name == "tensorboard":
                     self.active.append(TensorBoardTracker(run_dir))
                 elif name == "wandb":
-                    self.active.append(WandbTracker(run_dir, project, run_name, config, wandb_mode))
+                    self.active.append(WandbTracker(run_dir, project, run_name, config, wandb_mode, wandb_group, wandb_team, wandb_dir))
                 else:
                     self.unavailable[name] = "unknown tracker"
             except Exception as exc:                                 # noqa: BLE001 - a tracker never stops a run
