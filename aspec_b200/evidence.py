@@ -69,7 +69,8 @@ class RunEvidenceRecorder:
         self.doc["sections"][section] = payload
         self._write()
 
-    def observe_capability(self, subsystem: str, observed: str) -> None:
+    def observe_capability(self, subsystem: str, observed: Any) -> None:
+        """What really ran for ``subsystem``: an implementation name, or ``{implementation: launches}``."""
         self.doc.setdefault("capabilities_observed", {})[subsystem] = observed
         self._write()
 
