@@ -25,6 +25,13 @@ def build_run_report(run_dir: str) -> dict:
         problems.append(f"run state is {ev.get('state')!r}")
     if ledger and not ledger.get("validated", False):
         problems.append("work ledger is not validated (residency, incomplete work or non-contiguous steps)")
+    # a GPU run that launched something else than the plan chose (a fallback) is reported, not hidden
+    observed = ev.get("capabilities_observed") or {}
+    if (ev.get("accelerators") or {}).get("cuda"):
+        for decision in plan.get("capabilities") or []:
+            ran = observed.get(decision.get("subsystem"))
+            if isinstance(ran, dict) and ran and decision.get("choice") not in ran:
+                problems.append(f"plan chose {decision['choice']} for {decision['subsystem']}, the run launched {sorted(ran)}")
     ckpt_root = os.path.join(run_dir, "checkpoints")
     tracker = os.path.join(ckpt_root, "latest_checkpointed_iteration.txt")
     latest = int(open(tracker).read()) if os.path.isfile(tracker) else None
@@ -33,7 +40,8 @@ def build_run_report(run_dir: str) -> dict:
             "policy": plan.get("policy"), "state": ev.get("state"), "completed_steps": summary.get("completed_steps"),
             "throughput_window": summary.get("window"), "committed_work": len(ledger.get("committed_work_ids", [])),
             "dropped_tail_samples": summary.get("dropped_tail_samples"), "latest_checkpoint": latest,
-            "capabilities": plan.get("capabilities"), "accelerators": ev.get("accelerators")}
+            "capabilities": plan.get("capabilities"), "capabilities_observed": observed or None,
+            "accelerators": ev.get("accelerators")}
 
 
 def render_report(report: dict) -> str:

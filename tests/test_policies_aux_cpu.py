@@ -135,6 +135,19 @@ def test_run_report_flags_every_inconsistency(tmp_path):
         (run / "evidence.json").write_text(json.dumps({**good, **change}))
         bad = build_run_report(str(run))
         assert not bad["valid"] and any(needle in p for p in bad["problems"]) and "PROBLEM" in render_report(bad)
+    # a GPU run whose dispatcher launched another implementation than the plan chose is flagged; a CPU run is not
+    planned = {**plan, "capabilities": [{"subsystem": "attention", "choice": "tcgen05_interval_flash", "reason": ""}]}
+    (run / "plan.json").write_text(json.dumps(planned))
+    fallback = {**good, "capabilities_observed": {"attention": {"dense_mask_fp32": 12}}}
+    (run / "evidence.json").write_text(json.dumps(fallback))
+    assert build_run_report(str(run))["valid"]
+    (run / "evidence.json").write_text(json.dumps({**fallback, "accelerators": {"cuda": True}}))
+    flagged = build_run_report(str(run))
+    assert not flagged["valid"] and "the run launched ['dense_mask_fp32']" in flagged["problems"][0]
+    (run / "evidence.json").write_text(json.dumps({**fallback, "accelerators": {"cuda": True}, "capabilities_observed": {
+        "attention": {"tcgen05_interval_flash": 40, "dense_mask_fp32": 2}}}))
+    assert build_run_report(str(run))["valid"]
+    (run / "plan.json").write_text(json.dumps(plan))
     unvalidated = json.loads(json.dumps(good))
     unvalidated["training_summary"]["ledger"]["validated"] = False
     (run / "evidence.json").write_text(json.dumps(unvalidated))
