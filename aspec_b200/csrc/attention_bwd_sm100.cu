@@ -645,13 +645,12 @@ extern "C" int ab_attn_bwd(const void* q, const void* k, const void* v, const in
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   p.status = status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem) != cudaSuccess)
-      return -3;
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_done{0};
+  if (!once_per_device(attr_done, [&] {
+        return cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem) == cudaSuccess &&
+               cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem) == cudaSuccess;
+      }))
+    return -3;
   attn_bwd_dq_kernel<<<dim3(n_qtiles, hkv), kThreads, kDqSmem, stream>>>(maps, p);
   attn_bwd_dkv_kernel<<<dim3(n_ktiles, hkv), kThreads, kDkvSmem, stream>>>(maps, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

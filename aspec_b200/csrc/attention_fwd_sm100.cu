@@ -418,13 +418,12 @@ extern "C" int ab_attn_fwd(const void* q, const void* k, const void* v, const in
   p.tk = tk;
   p.scale_log2 = scale * kLog2e;
   p.status = status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-        cudaSuccess)
-      return -3;
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_done{0};
+  if (!once_per_device(attr_done, [&] {
+        return cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
+               cudaSuccess;
+      }))
+    return -3;
   dim3 grid((q_total + pm - 1) / pm, hkv);
   attn_fwd_kernel<<<grid, kThreads, kSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(maps, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

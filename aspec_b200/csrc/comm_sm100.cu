@@ -142,6 +142,11 @@ __global__ void shard_adamw_scatter_kernel(float* __restrict__ master, const flo
                                            float lr, float beta1, float beta2, float eps, float wd, float bc1,
                                            float bc2, float max_norm) {
   if (ctrl[1] > 0.f || !isfinite(ctrl[0])) return;
+  if (bc1 <= 0.f) {   // device-side step counter: ctrl[4] = applied updates including this one
+    const float t = fmaxf(ctrl[4], 1.f);
+    bc1 = 1.f - powf(beta1, t);
+    bc2 = 1.f - powf(beta2, t);
+  }
   const float pre = ctrl[2];
   const float norm = pre * sqrtf(ctrl[0]);
   float coef = pre;

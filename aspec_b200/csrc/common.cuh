@@ -13,6 +13,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace ab {
 
 // ---------------------------------------------------------------- status ----
@@ -343,6 +345,21 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+
+// ------------------------------------------------------- host: per-device set-up ----
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the current device only, so a launcher has to
+// ask once per device, not once per process.  `done` is a bit per device ordinal; setting the attribute twice
+// (two host threads racing on the same device) is harmless.
+template <typename SetFn>
+static inline bool once_per_device(std::atomic<unsigned long long>& done, SetFn set) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (done.load(std::memory_order_acquire) & bit) return true;
+  if (!set()) return false;
+  done.fetch_or(bit, std::memory_order_release);
+  return true;
 }
 
 }  // namespace ab

@@ -488,6 +488,8 @@ __global__ void sumsq_kernel(const float* __restrict__ g, long long n, float* __
 //   ctrl[0] = sum of squares of all gradients (already reduced over ranks)
 //   ctrl[1] = non-finite count (> 0 => skip the step entirely)
 //   ctrl[2] = gradient pre-scale (loss-denominator normalisation), applied before clipping
+//   ctrl[4] = number of APPLIED updates including this one (device-side step counter: a skipped update does not
+//             advance Adam's bias correction); read when the host passes bc1 <= 0, else bc1 / bc2 are used as given
 // clip coefficient = min(1, max_norm / (pre_scale * sqrt(ctrl[0]) + 1e-6)).
 __global__ void adamw_kernel(float* __restrict__ master, const float* __restrict__ grad,
                              float* __restrict__ m, float* __restrict__ v,
@@ -495,6 +497,11 @@ __global__ void adamw_kernel(float* __restrict__ master, const float* __restrict
                              const float* __restrict__ ctrl, float lr, float beta1, float beta2,
                              float eps, float wd, float bc1, float bc2, float max_norm) {
   if (ctrl[1] > 0.f || !isfinite(ctrl[0])) return;
+  if (bc1 <= 0.f) {
+    const float t = fmaxf(ctrl[4], 1.f);
+    bc1 = 1.f - powf(beta1, t);
+    bc2 = 1.f - powf(beta2, t);
+  }
   const float pre = ctrl[2];
   const float norm = pre * sqrtf(ctrl[0]);
   float coef = pre;

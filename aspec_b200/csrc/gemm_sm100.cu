@@ -692,13 +692,11 @@ static int num_sms() {
 template <int A_MN, int B_MN, int EPI, int PAIR>
 static int launch(const GemmMaps& maps, const GemmParams& p, int max_ctas, cudaStream_t stream) {
   auto kern = gemm_bf16_kernel<A_MN, B_MN, EPI, PAIR>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-        cudaSuccess)
-      return -3;
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_done{0};   // one per template instantiation, one bit per device
+  if (!once_per_device(attr_done, [&] {
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess;
+      }))
+    return -3;
   // scheduling units: CTAs, or CTA pairs (p.m_tiles then counts 256-row tiles)
   int units = p.m_tiles * p.n_tiles;
   int cap = max_ctas > 0 ? max_ctas : num_sms();

@@ -340,11 +340,11 @@ static int encode(CUtensorMap* map, const void* base, long long rows, long long 
 template <int A_MN, int B_MN>
 static int launch(const GMaps& maps, const GParams& p, int max_ctas, cudaStream_t stream) {
   auto kern = grouped_gemm_kernel<A_MN, B_MN>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return -3;
-    attr_set = true;
-  }
+  static std::atomic<unsigned long long> attr_done{0};   // one per template instantiation, one bit per device
+  if (!once_per_device(attr_done, [&] {
+        return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess;
+      }))
+    return -3;
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

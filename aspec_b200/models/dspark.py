@@ -110,10 +110,15 @@ class DSparkModel(DFlashModel):
 
         markov = self.draft_model.markov_head
         prev_emb = markov.get_prev_embeddings(prev_ids.reshape(-1)).to(hidden.dtype) if markov is not None else None
+        sampled = self.l1_sampling_enabled and teacher_hidden is not None
         head_kw = dict(prev_emb=prev_emb, markov_w2=markov.markov_w2.weight if markov is not None else None,
-                       teacher_hidden=teacher_hidden, t_index=t_index, a_ce=self.ce_loss_alpha,
-                       a_l1=self.l1_loss_alpha if teacher_hidden is not None else 0.0)
+                       teacher_hidden=None if sampled else teacher_hidden, t_index=None if sampled else t_index,
+                       a_ce=self.ce_loss_alpha,
+                       a_l1=self.l1_loss_alpha if (teacher_hidden is not None and not sampled) else 0.0)
         vp = getattr(self, "vocab_parallel", None)
+        if vp is not None and sampled:
+            raise NotImplementedError("dspark_l1_* sampling transforms need the whole vocabulary on one rank; "
+                                      "run with training.vocab_parallel_size=1")
         if vp is not None and hidden.is_cuda:
             # ``lm_head_weight`` is this rank's row shard of the Target head; statistics merge over the peers' memory
             from aspec_b200.parallel.vocab_parallel import vocab_parallel_head_loss
@@ -122,6 +127,15 @@ class DSparkModel(DFlashModel):
         else:
             num_ce_l1, ce, l1, correct = head_loss(hidden, lm_head_weight, target_ids.reshape(-1), w.reshape(-1), **head_kw)
         wf = w.reshape(-1)
+        if sampled:
+            # L1 on the distributions a sampler would draw from (temperature / top-p / top-k): row-chunked logits
+            from aspec_b200.ops.loss_sampling import sampled_l1
+            rows = teacher_hidden[t_index.long()] if t_index is not None else teacher_hidden
+            l1_live = sampled_l1(hidden, lm_head_weight, rows.to(hidden.dtype), prev_emb=prev_emb,
+                                 markov_w2=head_kw["markov_w2"], target_sampling=self.l1_sampling[0],
+                                 draft_sampling=self.l1_sampling[1])
+            num_ce_l1 = num_ce_l1 + self.l1_loss_alpha * (l1_live * wf).sum()
+            l1 = l1_live.detach()
         ce_num = (ce * wf).sum()
         l1_num = (l1 * wf).sum() if teacher_hidden is not None else ce_num.new_zeros(())
         conf_num = ce_num.new_zeros(())

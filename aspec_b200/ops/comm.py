@@ -44,12 +44,14 @@ def shard_reduce_sumsq(peer_grads: Sequence[torch.Tensor], lo: int, shard: torch
 
 def shard_adamw_scatter(master, grad, m, v, peer_params: Sequence[torch.Tensor], lo: int, ctrl, *, lr, beta1, beta2, eps,
                         wd, step, max_norm) -> None:
-    """AdamW on the owned shard; the new bf16 weights are stored into every replica ``peer_params[r][lo : lo + n]``."""
+    """AdamW on the owned shard; the new bf16 weights are stored into every replica ``peer_params[r][lo : lo + n]``.
+    ``step=None`` takes the bias-correction step from ``ctrl[4]`` (applied updates, counted on the device)."""
     f = C.c_float
     _check(_native.kernels().ab_shard_adamw_scatter(
         C.c_void_p(master.data_ptr()), C.c_void_p(grad.data_ptr()), C.c_void_p(m.data_ptr()), C.c_void_p(v.data_ptr()),
         _ptrs(peer_params), len(peer_params), C.c_longlong(lo), C.c_longlong(master.numel()), C.c_void_p(ctrl.data_ptr()),
-        f(lr), f(beta1), f(beta2), f(eps), f(wd), f(1.0 - beta1 ** step), f(1.0 - beta2 ** step), f(max_norm),
+        f(lr), f(beta1), f(beta2), f(eps), f(wd), f(0.0 if step is None else 1.0 - beta1 ** step),
+        f(0.0 if step is None else 1.0 - beta2 ** step), f(max_norm),
         _stream(master)), "ab_shard_adamw_scatter")
 
 

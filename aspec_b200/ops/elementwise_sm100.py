@@ -118,8 +118,9 @@ def sumsq(g: torch.Tensor, out: torch.Tensor) -> None:
 
 
 def adamw(master, grad, m, v, param, ctrl, *, lr, beta1, beta2, eps, wd, step, max_norm) -> None:
-    bc1 = 1.0 - beta1 ** step
-    bc2 = 1.0 - beta2 ** step
+    """``step=None``: the kernel takes the bias-correction step from ``ctrl[4]`` (applied updates, kept on the device)."""
+    bc1 = 0.0 if step is None else 1.0 - beta1 ** step
+    bc2 = 0.0 if step is None else 1.0 - beta2 ** step
     f = _c.c_float
     _check(_native.kernels().ab_adamw(_p(master), _p(grad), _p(m), _p(v), _p(param),
                                       _c.c_longlong(master.numel()), _p(ctrl), f(lr), f(beta1), f(beta2),

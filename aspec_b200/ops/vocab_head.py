@@ -138,6 +138,11 @@ def head_loss(hidden: torch.Tensor, lm_w: torch.Tensor, labels: torch.Tensor, we
     """
     use_kernel = (hidden.is_cuda and hidden.dtype == torch.bfloat16 and lm_w.dtype == torch.bfloat16
                   and lm_w.shape[0] % 8 == 0 and hidden.shape[1] % 8 == 0 and hidden.shape[0] > 0)
+    if (not use_kernel and hidden.is_cuda and hidden.dtype == torch.bfloat16 and lm_w.dtype == torch.bfloat16
+            and hidden.shape[0] > 0):
+        # on a GPU the fused head is the only bf16 path: refuse the shape rather than run the fp32 statement silently
+        raise ValueError(f"vocabulary head kernel needs vocab and hidden sizes that are multiples of 8, got "
+                         f"{tuple(lm_w.shape)}; pad the head (and mask the padded logits) or run in fp32")
     if not use_kernel:
         return head_loss_reference(hidden, lm_w, labels, weight, prev_emb=prev_emb, markov_w2=markov_w2,
                                    teacher_hidden=teacher_hidden, t_index=t_index, a_ce=a_ce, a_l1=a_l1,

@@ -27,7 +27,38 @@ def _align(n: int, a: int = 8) -> int:
     return -(-n // a) * a
 
 
-class BF16Optimizer:
+class _AppliedSteps:
+    """Adam's step counter lives on the device and advances only when an update is applied: an update skipped for
+    non-finite gradients changes neither parameters, moments nor the bias-correction step, as with a fused AdamW
+    driven by ``found_inf`` (reference: aspec/training/optimizer.py:123-135).  Reading ``step_count`` or
+    ``skipped_steps`` on the host is a device-to-host read, done at checkpoint / metrics time only."""
+
+    def _init_steps(self, device) -> None:
+        self._applied = torch.zeros((), dtype=torch.float32, device=device)
+        self.attempted_steps = 0
+
+    def _advance_steps(self, ctrl: torch.Tensor) -> None:
+        """``ctrl[0:2]`` hold the agreed norm / non-finite flag; writes this update's step index to ``ctrl[4]``."""
+        self.attempted_steps += 1
+        ok = ((ctrl[1] <= 0) & torch.isfinite(ctrl[0])).to(torch.float32)
+        self._applied += ok
+        ctrl[4] = self._applied
+
+    @property
+    def step_count(self) -> int:
+        return int(round(float(self._applied)))
+
+    @step_count.setter
+    def step_count(self, value: int) -> None:
+        self._applied.fill_(float(value))
+        self.attempted_steps = max(self.attempted_steps, int(value))
+
+    @property
+    def skipped_steps(self) -> int:
+        return self.attempted_steps - self.step_count
+
+
+class BF16Optimizer(_AppliedSteps):
     def __init__(self, model: torch.nn.Module, lr: float, weight_decay: float = 0.0,
                  max_grad_norm: float = 0.5, total_steps: int = 800_000, warmup_ratio: float = 0.015,
                  decay_style: str = "cosine", min_lr: float = 0.0, wsd_decay_steps=None,
@@ -67,15 +98,14 @@ class BF16Optimizer:
                 p.main_grad = self.flat_grad[o:o + n].view(p.shape)
                 p.main_grad_touched = False
                 p.grad = None
-        self.step_count = 0
-        self._ctrl = torch.zeros(4, dtype=torch.float32, device=dev)
+        self._init_steps(dev)
+        self._ctrl = torch.zeros(8, dtype=torch.float32, device=dev)
         self._grad_scale = torch.ones((), dtype=torch.float32, device=dev)
         self.use_kernel = dev.type == "cuda" and dtype == torch.bfloat16
         self.scheduler = LRSchedulerWithWarmup(
             self, max_lr=lr, total_steps=total_steps, warmup_steps=int(warmup_ratio * total_steps),
             decay_style=decay_style, min_lr=min_lr, wsd_decay_steps=wsd_decay_steps,
             wsd_decay_style=wsd_decay_style)
-        self.skipped_steps = 0
 
     # -- gradient plumbing --------------------------------------------------------
     def fold_autograd_grads(self) -> None:
@@ -119,13 +149,13 @@ class BF16Optimizer:
             dist.all_reduce(flag, op=dist.ReduceOp.MAX)
             ctrl[1] = flag[0]
         ctrl[2] = self._grad_scale
-        self.step_count += 1
+        self._advance_steps(ctrl)
         b1, b2 = self.betas
         if self.use_kernel:
             from aspec_b200.ops import elementwise_sm100 as E
             E.adamw(self.flat_master, self.flat_grad, self.exp_avg, self.exp_avg_sq, self.flat_param, ctrl,
                     lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, wd=self.weight_decay,
-                    step=self.step_count, max_norm=self.max_grad_norm)
+                    step=None, max_norm=self.max_grad_norm)
         else:
             self._step_reference(ctrl, b1, b2)
         grad_norm = ctrl[2] * torch.sqrt(ctrl[0])
@@ -139,7 +169,6 @@ class BF16Optimizer:
     def _step_reference(self, ctrl, b1, b2) -> None:
         bad = bool(ctrl[1] > 0) or not bool(torch.isfinite(ctrl[0]))
         if bad:
-            self.skipped_steps += 1
             return
         pre = ctrl[2]
         norm = pre * torch.sqrt(ctrl[0])
@@ -149,8 +178,9 @@ class BF16Optimizer:
         g = self.flat_grad * coef
         self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
         self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
-        bc1 = 1 - b1 ** self.step_count
-        bc2 = 1 - b2 ** self.step_count
+        step = self.step_count
+        bc1 = 1 - b1 ** step
+        bc2 = 1 - b2 ** step
         self.flat_master.mul_(1 - self.lr * self.weight_decay)
         self.flat_master.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + self.eps, value=-self.lr)
         self.flat_param.copy_(self.flat_master)

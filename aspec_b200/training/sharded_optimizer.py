@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
 from aspec_b200.training.lr_scheduler import LRSchedulerWithWarmup
-from aspec_b200.training.optimizer import _align
+from aspec_b200.training.optimizer import _AppliedSteps, _align
 
 
 def shard_bounds(numel: int, rank: int, world: int, align: int = 8):
@@ -35,7 +35,7 @@ def shard_bounds(numel: int, rank: int, world: int, align: int = 8):
     return lo, min(lo + per, numel)
 
 
-class ShardedBF16Optimizer:
+class ShardedBF16Optimizer(_AppliedSteps):
     def __init__(self, model: torch.nn.Module, lr: float, weight_decay: float = 0.0, max_grad_norm: float = 0.5,
                  total_steps: int = 800_000, warmup_ratio: float = 0.015, decay_style: str = "cosine", min_lr: float = 0.0,
                  wsd_decay_steps=None, wsd_decay_style=None, betas=(0.9, 0.999), eps: float = 1e-8,
@@ -84,13 +84,12 @@ class ShardedBF16Optimizer:
         self._opened: List[SymmetricBuffer] = []
         if self.world > 1 and self.use_kernel:
             self._exchange_handles(dtype)
-        self.step_count = 0
-        self._ctrl = torch.zeros(4, dtype=torch.float32, device=dev)
+        self._init_steps(dev)
+        self._ctrl = torch.zeros(8, dtype=torch.float32, device=dev)
         self._grad_scale = torch.ones((), dtype=torch.float32, device=dev)
         self.scheduler = LRSchedulerWithWarmup(self, max_lr=lr, total_steps=total_steps, warmup_steps=int(warmup_ratio * total_steps),
                                                decay_style=decay_style, min_lr=min_lr, wsd_decay_steps=wsd_decay_steps,
                                                wsd_decay_style=wsd_decay_style)
-        self.skipped_steps = 0
 
     def _exchange_handles(self, dtype) -> None:
         """Every rank maps every other rank's parameter and gradient replica (one IPC export per importer)."""
@@ -137,16 +136,16 @@ class ShardedBF16Optimizer:
         ctrl = self._ctrl
         ctrl.zero_()
         b1, b2 = self.betas
-        self.step_count += 1
         if self.use_kernel:
             from aspec_b200.ops import comm
             self._barrier(ctrl[3:4])                                   # all replicas hold their final gradients
             comm.shard_reduce_sumsq(self._peer_grads, self.lo, self.shard_grad, ctrl)
             self._barrier(ctrl[0:2])                                   # global norm; also: every peer finished reading
             ctrl[2] = self._grad_scale
+            self._advance_steps(ctrl)
             comm.shard_adamw_scatter(self.shard_master, self.shard_grad, self.exp_avg, self.exp_avg_sq, self._peer_params,
                                      self.lo, ctrl, lr=self.lr, beta1=b1, beta2=b2, eps=self.eps, wd=self.weight_decay,
-                                     step=self.step_count, max_norm=self.max_grad_norm)
+                                     step=None, max_norm=self.max_grad_norm)
             self.flat_grad.zero_()
             self._barrier(ctrl[3:4])                                   # all parameter stores have landed
         else:
@@ -166,6 +165,7 @@ class ShardedBF16Optimizer:
         ctrl[1] = (~torch.isfinite(g)).any().float()
         self._barrier(ctrl[0:2])
         ctrl[2] = self._grad_scale
+        self._advance_steps(ctrl)
         if not (bool(ctrl[1] > 0) or not bool(torch.isfinite(ctrl[0]))):
             coef = ctrl[2]
             if self.max_grad_norm > 0:
@@ -173,11 +173,10 @@ class ShardedBF16Optimizer:
             g = g * coef
             self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
             self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
-            bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+            step = self.step_count
+            bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
             self.shard_master.mul_(1 - self.lr * self.weight_decay)
             self.shard_master.addcdiv_(self.exp_avg / bc1, (self.exp_avg_sq / bc2).sqrt() + self.eps, value=-self.lr)
-        else:
-            self.skipped_steps += 1
         mine = self.shard_master.to(self.flat_param.dtype)
         if self.world > 1:
             per = shard_bounds(self.numel, 0, self.world)[1]

@@ -9,10 +9,15 @@ reduction across ranks, clip, AdamW.  Documents follow the benchmark config: len
 micro-batch.  Features are synthetic (random bf16 captured layers) and weights random-init.
 
 * ``value``: tokens/s with the documents' features resident on the GPU (the reference's Draft-only
-  methodology), device-timed with CUDA events, max over ranks.
+  methodology), device-timed with CUDA events, max over ranks.  Anchors are sampled inside the timed region
+  (on the host, from the host copy of the loss mask, as the data pipeline does).
 * ``e2e.value``: the same metric through ``DraftTrainer.train_update`` fed from pinned host memory,
   every step including the host->device copy of its inputs and a device->host read of its metrics.
-* ``--impl reference`` runs the unmodified reference package from ``baseline/_ref``.
+* for N >= 2 the gradient exchange and optimizer run over peer memory (sharded reduce + AdamW + parameter
+  scatter kernels); ``--baseline`` keeps the NCCL all-reduce + replicated AdamW.
+* for N >= 2 rank 0 afterwards runs the online split (N/2 Target + N/2 Draft GPUs, steady window of at least
+  32 updates) as a child process and reports it under ``online``; ``--no-online`` skips it.
+* ``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` and prints the same keys.
 """
 from __future__ import annotations
 
@@ -53,8 +58,17 @@ def parse_args():
     ap.add_argument("--length-group", type=int, default=32,
                     help="online: the controller's length_group_size (documents of similar length go to different Draft ranks "
                          "in the same micro-step; 1 disables the grouping)")
-    ap.add_argument("--fsdp", action="store_true", help="draft mode: FULL_SHARD optimizer over peer memory instead of REPLICATE")
+    ap.add_argument("--fsdp", action="store_true", help="(kept for old command lines: the peer-memory sharded step is the default for N >= 2)")
+    ap.add_argument("--baseline", action="store_true",
+                    help="draft mode, N >= 2: NCCL all-reduce of the flat gradient + replicated AdamW instead of the peer-memory sharded step")
+    ap.add_argument("--no-online", action="store_true", help="N >= 2: do not append the online Target + Draft run")
+    ap.add_argument("--online-steps", type=int, default=56, help="measured updates of the appended online run (window >= 32 updates)")
+    ap.add_argument("--online-warmup", type=int, default=8)
+    ap.add_argument("--online-timeout", type=float, default=900.0, help="seconds before the appended online run is abandoned")
     return ap.parse_args()
+
+
+METRIC = "Draft input tokens/s, Qwen3-8B DSpark 4K (Draft-only, resident features)"
 
 
 class ClockSampler:
@@ -127,11 +141,10 @@ def build_ours(args, device, dtype):
 
 
 def make_pool(args, cfg, model, rank, n_docs, pin):
-    """Host-side documents with features and pre-sampled anchors (the collator's job)."""
+    """Host-side documents with features.  ``host_loss_mask`` stays on the host for the anchor sampler."""
     import torch
     from aspec_b200.data.synthetic import SyntheticSpec, benchmark_documents, synthetic_features
     spec = SyntheticSpec(vocab_size=cfg.vocab_size - 1024, min_len=min(args.min_len, args.max_len), max_len=args.max_len, seed=17)
-    from aspec_b200.ops.anchors import sample_anchor_positions
     pool = []
     # every rank gets documents with the 1-GPU run's lengths (own token ids and features), dealt to the updates so that
     # each update carries about the same number of tokens: see ``benchmark_documents``
@@ -139,13 +152,11 @@ def make_pool(args, cfg, model, rank, n_docs, pin):
         row, T = doc["row"], doc["seq_len"]
         feats = synthetic_features(T, cfg.num_target_layers, cfg.target_hidden_size, row, pin=pin)
         lm = doc["loss_mask"][None]
-        g = torch.Generator().manual_seed(row)
-        anchors, keep = sample_anchor_positions(T, lm, model.num_anchors, model.block_size, generator=g)
         batch = {"input_ids": doc["input_ids"][None], "loss_mask": lm,
                  "hidden_states": feats["hidden_states"][None], "last_hidden_states": feats["last_hidden_states"][None],
-                 "injected_anchors": anchors, "injected_keep_mask": keep, "seq_len": T}
+                 "seq_len": T, "host_loss_mask": lm}
         if pin and torch.cuda.is_available():
-            for k in ("input_ids", "loss_mask", "injected_anchors"):
+            for k in ("input_ids", "loss_mask"):
                 batch[k] = batch[k].pin_memory()
         pool.append(batch)
     return pool
@@ -165,20 +176,32 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl" if cuda else "gloo", device_id=device if cuda else None)
     from aspec_b200 import _native
+    from aspec_b200.ops.anchors import sample_anchor_positions
     from aspec_b200.training.draft_trainer import DraftTrainer
     cfg, model, lm_head = build_ours(args, device, dtype)
     total_updates = args.steps * 2 + args.warmup * 2 + 8
+    sharded = world > 1 and not args.baseline
     trainer = DraftTrainer(model, lm_head, lr=6e-4, min_lr=6e-5, weight_decay=0.0, max_grad_norm=1.0,
                            total_steps=max(total_updates, 32), warmup_ratio=0.04, accumulation=args.accum,
-                           device=device, fsdp_strategy="FULL_SHARD" if args.fsdp else "REPLICATE")
+                           device=device, fsdp_strategy="FULL_SHARD" if sharded else "REPLICATE")
     n_docs = args.pool or args.accum * 2
     pool = make_pool(args, cfg, model, rank, n_docs, pin=cuda)
-    resident = [trainer.to_device(b) for b in pool]
+    resident = [dict(trainer.to_device(b), host_loss_mask=b["host_loss_mask"]) for b in pool]
     if cuda:
         torch.cuda.synchronize()
+    sampler_rng = torch.Generator().manual_seed(1000 + rank)
 
     def batches_for(step, source):
-        return [source[(step * args.accum + i) % n_docs] for i in range(args.accum)]
+        """The step's micro-batches, each with anchors drawn now: the sampler's cost is inside the timed region."""
+        out = []
+        for i in range(args.accum):
+            b = dict(source[(step * args.accum + i) % n_docs])
+            lm = b.pop("host_loss_mask")
+            anchors, keep = sample_anchor_positions(b["seq_len"], lm, model.num_anchors, model.block_size,
+                                                    generator=sampler_rng)
+            b["injected_anchors"], b["injected_keep_mask"] = anchors, keep
+            out.append(b)
+        return out
 
     def tokens_for(step):
         return sum(pool[(step * args.accum + i) % n_docs]["seq_len"] for i in range(args.accum))
@@ -237,10 +260,15 @@ def run_ours(args):
         e2e = {"value": toks2 / (ms2 / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": 4 * (3 * 2 * model.block_size + 2 + 2 * 12 + 1),
                "ms_per_step": ms2 / args.steps, "loss": last.get("train/avg_loss")}
+    collective = ("none (1 GPU)" if world == 1 else
+                  "NCCL all-reduce of the flat fp32 gradient + replicated AdamW" if args.baseline else
+                  "peer-memory sharded step: shard_reduce_sumsq (peer loads) + shard_adamw_scatter (peer stores); "
+                  "NCCL only for three scalar all-reduces per update")
+    line = None
     if rank == 0:
         base = BASELINE_1GPU if world == 1 else None
         line = {
-            "metric": "Draft input tokens/s, Qwen3-8B DSpark 4K (Draft-only, resident features)",
+            "metric": METRIC,
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / base) if base else None, "dtype": "bf16" if cuda else "fp32",
@@ -248,15 +276,56 @@ def run_ours(args):
             "config": {"model": f"Qwen3-8B-shaped DSpark draft, {args.layers} layer(s), {args.target_layers} captured layers, vocab {cfg.vocab_size}",
                        "global_batch": args.accum * world, "seq_len": args.max_len,
                        "doc_lengths": f"log-uniform [{args.min_len},{args.max_len}]",
-                       "parallelism": f"dp{world}" + ("+full_shard" if args.fsdp else ""),
+                       "parallelism": f"dp{world}" + ("+sharded_optimizer" if sharded else ""),
+                       "collective": collective,
+                       "anchors_sampled": "inside the timed region, every micro-batch",
                        "dp_balance": "every rank draws documents with the length sequence of the 1-GPU run (own token ids and features)" if world > 1 else "n/a", "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,
                        "block_size": model.block_size,
                        "l2_policy": "inputs larger than L2 (1.2 GB lm_head + per-document features stream from HBM every micro-batch)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "ours",
         }
-        print(json.dumps(line))
+    # release this rank's GPU before the online run takes the node
+    close = getattr(trainer.optimizer, "close", None)
+    if world > 1:
+        dist.barrier()
+    if close:
+        close()
+    del trainer, model, lm_head, resident, pool
+    if cuda:
+        torch.cuda.empty_cache()
     if world > 1:
         dist.destroy_process_group()
+    if rank == 0:
+        if world > 1 and cuda and not args.no_online and not args.small:
+            line["online"] = online_child(args)
+        print(json.dumps(line), flush=True)
+
+
+def online_child(args) -> dict:
+    """Run ``--mode online`` on the node's N GPUs in a child process (this process keeps only its CUDA context)."""
+    time.sleep(3.0)                         # the other ranks are exiting and releasing their GPUs
+    env = {k: v for k, v in os.environ.items()
+           if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "ROLE_NAME",
+                        "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_RUN_ID", "TORCHELASTIC_RESTART_COUNT",
+                        "TORCHELASTIC_MAX_RESTARTS", "TORCHELASTIC_USE_AGENT_STORE", "TORCH_NCCL_ASYNC_ERROR_HANDLING",
+                        "GROUP_WORLD_SIZE", "ROLE_WORLD_SIZE", "TORCHELASTIC_ERROR_FILE")}
+    cmd = [sys.executable, os.path.abspath(__file__), "--mode", "online", "--gpus", str(args.gpus),
+           "--steps", str(args.online_steps), "--warmup", str(args.online_warmup), "--accum", str(args.accum),
+           "--layers", str(args.layers), "--min-len", str(args.min_len), "--max-len", str(args.max_len)]
+    t0 = time.perf_counter()
+    try:
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=args.online_timeout, cwd=ROOT)
+    except subprocess.TimeoutExpired:
+        return {"error": f"online run did not finish within {args.online_timeout:.0f} s"}
+    for ln in reversed(res.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            try:
+                out = json.loads(ln)
+                out["wall_seconds_incl_startup"] = time.perf_counter() - t0
+                return out
+            except json.JSONDecodeError:
+                continue
+    return {"error": f"online run exited {res.returncode}", "stderr_tail": res.stderr[-600:]}
 
 
 def run_online(args) -> dict:

@@ -171,6 +171,73 @@ def test_flat_optimizer_matches_torch_adamw_and_skips_nonfinite():
     for a, b in zip(model.parameters(), before):
         assert torch.equal(a, b)
     assert opt.skipped_steps == 1
+    # a skipped update does not advance Adam's bias-correction step: the next applied update is step 4 on both sides
+    assert opt.step_count == 3
+    model(x).pow(2).sum().backward()
+    ref(x).pow(2).sum().backward()
+    torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+    opt.step()
+    ropt.step(); ropt.zero_grad()
+    assert opt.step_count == 4 and opt.skipped_steps == 1
+    for a, b in zip(model.parameters(), ref.parameters()):
+        assert torch.allclose(a, b, atol=1e-5)
     state = opt.state_dict()
+    assert state["step"] == 4
     assert set(state["master"]) == {"0.weight", "0.bias", "1.weight", "1.bias"}
     opt.load_state_dict(state)
+    assert opt.step_count == 4
+
+
+def test_sampling_logits_support_and_l1():
+    """Temperature / top-k / top-p restrict the support the way a sampler would; default is the identity."""
+    import torch
+    from aspec_b200.ops.loss_sampling import l1_between, sampling_logits
+    torch.manual_seed(0)
+    z = torch.randn(5, 50)
+    assert sampling_logits(z) is z
+    k = sampling_logits(z, (1.0, 1.0, 7))
+    assert (torch.isfinite(k).sum(-1) == 7).all()
+    assert torch.equal(torch.isfinite(k), z >= z.topk(7, -1).values[:, -1:])
+    t = sampling_logits(z, (0.5, 1.0, -1))
+    assert torch.allclose(t, (z - z.amax(-1, keepdim=True)) / 0.5)
+    p = sampling_logits(z, (1.0, 0.6, -1))
+    pr = z.softmax(-1)
+    for r in range(5):
+        order = pr[r].argsort(descending=True, stable=True)
+        before = pr[r][order].cumsum(0) - pr[r][order]
+        keep = set(order[before <= 0.6].tolist())
+        assert set(torch.isfinite(p[r]).nonzero().flatten().tolist()) == keep
+    # identical distributions on identical supports are at distance 0; disjoint supports at distance 2
+    assert torch.allclose(l1_between(z, z, (1.0, 0.5, 10), (1.0, 0.5, 10)), torch.zeros(5), atol=1e-6)
+    a = torch.full((1, 4), -10.0); a[0, 0] = 10
+    b = torch.full((1, 4), -10.0); b[0, 3] = 10
+    assert abs(float(l1_between(a, b, (1.0, 1.0, 1), (1.0, 1.0, 1))) - 2.0) < 1e-5
+
+
+def test_dspark_l1_sampling_changes_the_loss_and_trains():
+    import torch
+    from aspec_b200.config.draft_config import DSparkConfig
+    from aspec_b200.models.draft.dspark import DSparkDraftModel
+    from aspec_b200.models.dspark import DSparkModel
+    torch.manual_seed(0)
+    cfg = DSparkConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=2,
+                       num_key_value_heads=1, head_dim=32, vocab_size=128, num_target_layers=2, target_hidden_size=64,
+                       target_num_hidden_layers=4, markov_rank=8, mask_token_id=127)
+    draft = DSparkDraftModel(cfg)
+    head = torch.randn(128, 64) * 0.3
+    T = 48
+    ids = torch.randint(0, 120, (1, T))
+    lm = torch.ones(1, T)
+    hs, last = torch.randn(1, T, 128), torch.randn(1, T, 64)
+    out = {}
+    for name, samp in (("plain", (1.0, 1.0, -1)), ("topk", (0.7, 0.9, 16))):
+        model = DSparkModel(draft, block_size=4, num_anchors=8, l1_target_sampling=samp, l1_draft_sampling=samp,
+                            deterministic_anchor_sampling=True)
+        res = model(ids, hs, lm, head, last_hidden_states=last)
+        num = res[6][0]
+        draft.zero_grad()
+        num.backward()
+        g = draft.layers[0].mlp.down_proj.weight.grad
+        assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
+        out[name] = float(res[5]["l1_loss"][0])
+    assert out["plain"] != out["topk"]
