@@ -156,8 +156,7 @@ def kernels() -> "_CountingLibrary":
         if _kernels is None:
             if not _KERNEL_LIB.exists():
                 raise RuntimeError(
-                    f"{_KERNEL_LIB} is missing: run `python -c 'import __graft_entry__ as g; g.build()'`"
-                    " or `python -m aspec_b200.build` first")
+                    f"{_KERNEL_LIB} is missing: run `python -m aspec_b200.build` first")
             _kernels = _CountingLibrary(ctypes.CDLL(str(_KERNEL_LIB)))
         return _kernels
 

@@ -4,7 +4,7 @@ low-rank candidate-retrieval head trained in a second stage (reference: aspec/mo
 
 Stages: ``draft`` trains everything but the candidate head; ``candidate_head`` freezes the draft body (kept in eval
 mode) and trains ``efficient_lm_head_down_proj`` / ``efficient_lm_head`` to reproduce the frozen draft's top-k
-distribution, starting from a randomised truncated SVD of the exact head.
+distribution, starting from the rank-r truncation of the exact head (``models/draft/candidate_head.py``).
 """
 from __future__ import annotations
 
@@ -13,13 +13,12 @@ import torch
 from aspec_b200.config.draft_attention import resolve_attention_policy
 from aspec_b200.config.draft_config import Eagle4Config
 from aspec_b200.config.eagle4 import eagle4_policy
+from aspec_b200.models.draft.candidate_head import CANDIDATE_MODULES, low_rank_factors, shortlist_logits, stage_trains
 from aspec_b200.models.draft.eagle4_moe import Eagle4MoE, split_latent_experts, stack_latent_experts
 from aspec_b200.models.draft.keymap import to_export_keys, to_internal_keys
 from aspec_b200.models.draft.llama3_eagle import EagleAttention, EagleDecoderLayer, LlamaForCausalLMEagle3
 from aspec_b200.ops.linear import Linear
 from aspec_b200.ops.norm import RMSNorm
-
-_CANDIDATE_PREFIXES = ("efficient_lm_head.", "efficient_lm_head_down_proj.")
 
 
 class Eagle4DecoderLayer(EagleDecoderLayer):
@@ -83,62 +82,86 @@ class Eagle4DraftModel(LlamaForCausalLMEagle3):
 
     # -- stages ---------------------------------------------------------------------------------------
     @property
+    def stage(self) -> str:
+        return self.eagle4_policy["stage"]
+
+    @property
     def candidate_stage(self) -> bool:
-        return self.eagle4_policy["stage"] == "candidate_head"
+        return self.stage == "candidate_head"
 
     @property
     def preserve_loaded_embedding(self) -> bool:
+        # the candidate stage distils a finished Draft: its embedding must stay the one it was trained with
         return self.candidate_stage
 
+    def _frozen_body(self):
+        """Sub-modules that stay in inference mode while only the candidate head trains."""
+        return [m for name, m in self.named_children() if name not in CANDIDATE_MODULES]
+
     def configure_training_stage(self) -> None:
-        for name, p in self.named_parameters():
-            cand = name.startswith(_CANDIDATE_PREFIXES)
-            p.requires_grad_(cand if self.candidate_stage else not cand)
+        """Mark what the configured stage updates; the embedding is the Target's and never trains, and a post-MLP norm
+        that ``norm_output`` bypasses would be a trainable leaf nothing reaches."""
+        stage = self.stage
+        for name, param in self.named_parameters():
+            param.requires_grad_(stage_trains(name, stage))
         self.embed_tokens.weight.requires_grad_(False)
-        if self.norm_output and hasattr(self.midlayer, "post_mlp_layernorm"):
-            self.midlayer.post_mlp_layernorm.requires_grad_(False)
+        bypassed = getattr(self.midlayer, "post_mlp_layernorm", None) if self.norm_output else None
+        if bypassed is not None:
+            bypassed.requires_grad_(False)
         self.train(self.training)
 
     def train(self, mode: bool = True):
         super().train(mode)
-        if hasattr(self, "eagle4_policy") and self.candidate_stage:
-            for name, module in self.named_children():
-                if name not in ("efficient_lm_head", "efficient_lm_head_down_proj"):
-                    module.eval()
+        # called by nn.Module.__init__ paths before the policy exists
+        if getattr(self, "eagle4_policy", None) is not None and self.candidate_stage:
+            for module in self._frozen_body():
+                module.train(False)
         return self
 
     def validate_target_binding(self, target_embedding: torch.Tensor) -> None:
-        if self.candidate_stage:
-            actual = self.embed_tokens.weight.detach()
-            if actual.shape != target_embedding.shape or not torch.equal(actual.cpu(), target_embedding.to(actual.dtype).cpu()):
-                raise ValueError("Candidate training requires the pretrained Draft's same frozen Target embedding")
+        if not self.candidate_stage:
+            return
+        mine = self.embed_tokens.weight.detach().cpu()
+        theirs = target_embedding.detach().to(mine.dtype).cpu()
+        if mine.shape != theirs.shape or not torch.equal(mine, theirs):
+            raise ValueError("the candidate stage distils a pretrained Draft and needs the Target embedding that Draft was "
+                             "trained with; the loaded embedding differs")
 
     @torch.no_grad()
     def initialize_candidate_head(self, *, device=None) -> None:
-        if int(self.candidate_head_steps) != 0:
-            raise ValueError("Refusing to overwrite a trained candidate head with SVD")
-        weight = self.lm_head.weight.detach().to(device=device, dtype=torch.float32)
-        rank = self.eagle4_policy["rank"]
-        u, s, v = torch.svd_lowrank(weight, q=min(rank + 16, *weight.shape), niter=2)
-        self.efficient_lm_head_down_proj.weight.copy_(v[:, :rank].T)
-        self.efficient_lm_head.weight.copy_(u[:, :rank] * s[:rank])
+        """Start the two projections from the rank-r truncation of the exact head (once: never over trained weights)."""
+        if int(self.candidate_head_steps) > 0:
+            raise ValueError(f"the candidate head has already taken {int(self.candidate_head_steps)} update(s); "
+                             "re-initialising it from the exact head would discard them")
+        down, up = low_rank_factors(self.lm_head.weight.detach().to(device=device), self.eagle4_policy["rank"])
+        self.efficient_lm_head_down_proj.weight.copy_(down.to(self.efficient_lm_head_down_proj.weight))
+        self.efficient_lm_head.weight.copy_(up.to(self.efficient_lm_head.weight))
 
     def candidate_scores(self, hidden):
-        return self.efficient_lm_head(self.efficient_lm_head_down_proj(hidden))
+        latent = self.efficient_lm_head_down_proj(hidden)
+        return self.efficient_lm_head(latent)
 
     @torch.no_grad()
     def score_candidates(self, hidden):
-        """Exact draft logits on the retrieved shortlist (evaluation helper, not a serving path)."""
-        ids = self.candidate_scores(hidden).topk(self.eagle4_policy["num_candidates"], -1).indices
-        return ids, torch.matmul(self.lm_head.weight[ids], hidden.unsqueeze(-1)).squeeze(-1)
+        """``(ids, exact logits)`` of the retrieved shortlist (an evaluation helper, not the serving path)."""
+        k = self.eagle4_policy["num_candidates"]
+        ids = torch.topk(self.candidate_scores(hidden), k, dim=-1).indices
+        return ids, shortlist_logits(self.lm_head.weight, hidden, ids)
 
     def commit_router_load(self) -> None:
+        """Fold the last forward's expert load into the router's running count (draft stage, training mode only)."""
+        if not self.training or self.candidate_stage:
+            return
         mlp = self.midlayer.mlp
-        if self.training and not self.candidate_stage and isinstance(mlp, Eagle4MoE) and mlp.last_load is not None:
-            mlp.gate.load.add_(mlp.last_load)
+        load = getattr(mlp, "last_load", None) if isinstance(mlp, Eagle4MoE) else None
+        if load is not None:
+            mlp.gate.load += load
 
+    # -- serving layout: per-expert latent tensors, exported key names ----------------------------------
     def state_dict_from_serving(self, tensors: dict) -> dict:
-        return to_internal_keys(stack_latent_experts(tensors), self.state_dict().keys())
+        stacked = stack_latent_experts(tensors)
+        return to_internal_keys(stacked, self.state_dict().keys())
 
     def state_dict_for_serving(self) -> dict:
-        return split_latent_experts(to_export_keys(self.state_dict()))
+        exported = to_export_keys(self.state_dict())
+        return split_latent_experts(exported)

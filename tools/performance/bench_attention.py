@@ -3,7 +3,7 @@ tools/performance/benchmark_cudnn_gqa.py:19-85): 12 packed documents ``[4096] * 
 anchors per document, block 7 -> Q ``[43008, 32, 128]``, K/V ``[174080, 8, 128]`` bf16.  Published on an SM100 GPU:
 18.12 ms forward + backward (4.47 + 12.93) for cuDNN forward + the joint-GQA CuTe-DSL backward.
 
-``python -m aspec_b200.ops.bench_attention [--iters N] [--small]`` prints one JSON line: forward / backward ms
+``python -m tools.performance.bench_attention [--iters N] [--small]`` prints one JSON line: forward / backward ms
 (CUDA events, L2 flushed between iterations) and the algorithmic FLOP rate.
 """
 from __future__ import annotations

@@ -1,4 +1,4 @@
-"""``python -m aspec_b200.ops.bench_grouped``: SwiGLU expert bank forward + backward, grouped launches against the
+"""``python -m tools.performance.bench_grouped``: SwiGLU expert bank forward + backward, grouped launches against the
 per-expert loop of dense GEMMs (both on the tcgen05 kernels of this package).  CUDA events, L2 flushed between
 iterations; prints one JSON line with times and the fraction of the measured GEMM peak."""
 from __future__ import annotations

@@ -3,7 +3,7 @@
 Run with one process per GPU::
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        -m aspec_b200.parallel.bench_parallel [--cases fsdp,vocab,cp,ulysses] [--iters 20]
+        -m tools.performance.bench_parallel [--cases fsdp,vocab,cp,ulysses] [--iters 20]
 
 Every case is timed with CUDA events on the launching stream after warm-up, a barrier and a synchronize on both
 sides; the reported time is the maximum over ranks.  Between iterations a buffer larger than L2 is written.  Rank 0

@@ -3,7 +3,7 @@
 Run::
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port P \
-        -m aspec_b200.parallel.bench_transport [--tokens 8192] [--iters 10]
+        -m tools.performance.bench_transport [--tokens 8192] [--iters 10]
 
 Rank 0 plays a Target layer's down projection with its residual add, ``x[T, D] = act[T, I] @ W[D, I]^T + x`` - the GEMM
 whose output is a captured layer - and rank 1 owns the destination (a Draft ring slot: a peer-visible buffer).  Timed
@@ -41,7 +41,7 @@ def main() -> None:
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from aspec_b200.ops import gemm as G
-    from aspec_b200.parallel.bench_parallel import NVLINK_GBS, Timer, _peak
+    from tools.performance.bench_parallel import NVLINK_GBS, Timer, _peak
     from aspec_b200.parallel.group import exchange_workspaces
     from aspec_b200.parallel.symmetric_memory import SymmetricBuffer
     T, D, I = a.tokens, a.hidden, a.intermediate

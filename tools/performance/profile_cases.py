@@ -1,7 +1,10 @@
-"""Small single-kernel workloads for profiler captures: ``python -m aspec_b200.ops.profile_cases CASE``.
+"""Small single-kernel workloads for profiler captures: ``python -m tools.performance.profile_cases CASE``.
 
 Each case launches its kernel a few times on inputs larger than the 126 MB L2 but well under a few GB, so
-that ``ncu --set full -k regex:<kernel> -c 1..3`` finishes in about a minute.  Cases: ``gemm``, ``gemm_head``,
+that ``ncu --set full --clock-control none -k regex:<kernel> -c 1..3`` finishes in about a minute.  The flag
+``--clock-control none`` matters on shared GPUs: without it the profiler locks the clocks and a killed capture can
+leave them locked for the next user.  Capture one kernel on these small cases only, after the same command line has
+run to completion without the profiler.  Cases: ``gemm``, ``gemm_head``,
 ``attn_fwd``, ``attn_bwd``, ``vocab_loss``, ``rmsnorm``, ``grouped_experts``.
 """
 from __future__ import annotations
