@@ -21,7 +21,7 @@ import torch
 import torch.nn as nn
 
 from aspec_b200.models.draft.dflash import DFlashAttention
-from aspec_b200.models.draft.sparse_common import (build_group_layout, eligible_groups, gathered_attention, kl_rows,
+from aspec_b200.models.draft.sparse_common import (build_group_layout, eligible_groups, indexed_attention, kl_rows,
                                                    masked_log_softmax, own_block_index, rotary)
 from aspec_b200.ops.fused_params import fused_linear
 from aspec_b200.ops.norm import RMSNorm
@@ -160,6 +160,9 @@ class CSAAttention(DFlashAttention):
         vals = torch.cat([v, cval.to(v.dtype)], 0)
         per_row = (width + blk.shape[1] + G) * self.num_kv_heads * self.head_dim * 2 * 4
         rows = max(int(self.workspace_bytes // max(per_row, 1)), 1)
+        from aspec_b200.ops.sparse_attention import _kernel_ok
+        if _kernel_ok(q, keys, vals):
+            rows = max(Q, 1)            # the kernel gathers tile by tile: no per-row workspace to bound
         comp = (k.shape[0] + torch.arange(G, device=q.device))[None]
         outs = []
         for s0 in range(0, Q, rows):
@@ -168,7 +171,7 @@ class CSAAttention(DFlashAttention):
             raw_ok = raw < hi[sl, None]
             idx = torch.cat([raw.clamp(max=T - 1), blk[sl], comp.expand(raw.shape[0], -1)], 1)
             ok = torch.cat([raw_ok, blk_ok[sl], visible[sl]], 1)
-            outs.append(gathered_attention(q[sl], keys[idx], vals[idx], ok, self.scale))
+            outs.append(indexed_attention(q[sl], keys, vals, idx, ok, self.scale))
         return torch.cat(outs, 0) if outs else q.new_zeros(q.shape)
 
     def trainable_parameter_names(self):

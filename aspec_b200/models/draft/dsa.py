@@ -56,7 +56,9 @@ class DSALightningIndexer(nn.Module):
     def project(self, x, ctx, q_pos, ctx_pos):
         x, ctx = x.detach(), ctx.detach()
         q = self.q_b_proj(self.q_a_norm(self.q_a_proj(x))).view(x.shape[0], self.num_heads, self.head_dim)
-        k = self.k_norm(self.k_proj(ctx).float()).to(ctx.dtype)[:, None]
+        kn = self.k_norm                     # statistics in fp32 whatever the module's parameter dtype
+        k = F.layer_norm(self.k_proj(ctx).float(), kn.normalized_shape, kn.weight.float(), kn.bias.float(),
+                         kn.eps).to(ctx.dtype)[:, None]
         q = _rotary(q, q_pos, self.rope_dim, self.rope_theta)
         k = _rotary(k, ctx_pos, self.rope_dim, self.rope_theta)[:, 0]
         w = F.linear(x.float(), self.weights_proj.weight.float()) * self.scale
@@ -107,6 +109,9 @@ class DSAAttention(DFlashAttention):
             k = qk_norm_rope(k, self.k_norm.weight, kv_pos, inv, self.eps, self.rope_scaling)
         iq, ik, iw = self.indexer.project(x, ctx, q_pos, kv_pos[:T])
         lo, hi = intervals[:, 0].long(), intervals[:, 1].long()
+        from aspec_b200.ops import sparse_attention as SA
+        if self.stage == "sparse" and SA._kernel_ok(q, k, v):
+            return self.o_proj(self._sparse_stage_kernels(q, k, v, iq, ik, iw, intervals, T, aux).reshape(Q, -1))
         rows = self.indexer.chunk_rows(T)
         losses = []
         outs = []
@@ -140,6 +145,62 @@ class DSAAttention(DFlashAttention):
                 o, _ = interval_attention(q, k, v, intervals, self.scale)
                 return self.o_proj(o.reshape(Q, -1))
         return self.o_proj(torch.cat(outs, 0).reshape(Q, -1))
+
+    def _sparse_stage_kernels(self, q, k, v, iq, ik, iw, intervals, T, aux):
+        """The sparse stage on a GPU: indexer scores (tcgen05 GEMM with the ReLU / weight / head-sum epilogue), radix
+        top-k and attention over the selected rows are kernels; nothing of size ``Q x T x heads`` is materialised.
+        The KL between the main attention's and the indexer's distributions is taken on the selected set only, so
+        its pieces - the selected indexer scores (with gradient) and the attention logits at the selected keys - are
+        small gathers, chunked over queries; the per-head normaliser of the main attention over ALL eligible keys
+        comes from one forward of the interval kernel."""
+        from aspec_b200.ops import sparse_attention as SA
+        from aspec_b200.models.draft.sparse_common import indexed_attention, own_block_index
+        Q = q.shape[0]
+        lo, hi = intervals[:, 0].contiguous(), intervals[:, 1].contiguous()
+        budget = min(self.indexer.token_budget, T)
+        rows = max(int(self.indexer.workspace_bytes // max(T * 4 * 2, 1)), 1)
+        picks = []
+        for s0 in range(0, Q, rows):
+            sl = slice(s0, min(s0 + rows, Q))
+            score = SA.indexer_scores(iq[sl].detach(), ik.detach(), iw[sl].detach(), lo[sl], hi[sl])
+            picks.append(SA.topk_select(score, lo[sl], hi[sl], budget))
+            del score
+        sel = torch.cat(picks) if picks else torch.zeros(0, budget, dtype=torch.int32, device=q.device)
+        if aux is not None and self.compute_auxiliary_loss:
+            aux.setdefault("dsa_losses", []).append(self._selected_set_kl(q, k, iq, ik, iw, sel, intervals, T))
+        blk, blk_ok = own_block_index(intervals, k.shape[0])
+        idx = torch.cat([sel.long().clamp_min(0), blk], 1)
+        ok = torch.cat([sel >= 0, blk_ok], 1)
+        return indexed_attention(q, k, v, idx, ok, self.scale)
+
+    def _selected_set_kl(self, q, k, iq, ik, iw, sel, intervals, T):
+        """``KL(teacher || indexer)`` per query over its selected keys.  teacher(s) is proportional to the sum over heads
+        of the main attention's probability of key ``s`` under the softmax over the whole eligible context."""
+        Q, S = sel.shape
+        g = self.num_heads // self.num_kv_heads
+        with torch.no_grad():
+            ctx_only = torch.stack([intervals[:, 0], intervals[:, 1], torch.zeros_like(intervals[:, 0]),
+                                    torch.zeros_like(intervals[:, 0])], 1).to(torch.int32).contiguous()
+            _, lse = interval_attention(q.detach(), k[:T].detach(), k[:T].detach(), ctx_only, self.scale)   # [Hq, Q]
+        per_row = S * (self.num_kv_heads * self.head_dim * 2 + self.num_heads * 4 * 2 + self.indexer.num_heads * 4 * 2)
+        rows = max(int(self.indexer.workspace_bytes // max(per_row, 1)), 1)
+        out = []
+        for s0 in range(0, Q, rows):
+            sl = slice(s0, min(s0 + rows, Q))
+            s_idx = sel[sl].long().clamp_min(0)
+            ok = sel[sl] >= 0
+            sel_score = (torch.einsum("nhd,nsd->nhs", iq[sl].float(), ik[s_idx].float()).relu() * iw[sl][:, :, None]).sum(1)
+            with torch.no_grad():
+                kk = k[:T][s_idx].float().repeat_interleave(g, 2)                       # [c, S, Hq, d]
+                logit = torch.einsum("nhd,nshd->nhs", q[sl].float(), kk) * self.scale
+                l = lse[:, sl].t()
+                l = torch.where(torch.isfinite(l), l, torch.zeros_like(l))
+                t_sel = (torch.exp(logit - l[:, :, None]) * ok[:, None]).sum(1)
+                t_sel = t_sel / t_sel.sum(-1, keepdim=True).clamp_min(1e-20)
+            logp = torch.log_softmax(sel_score.masked_fill(~ok, float("-inf")), -1).masked_fill(~ok, 0.0)
+            kl = (t_sel * (torch.log(t_sel.clamp_min(1e-20)) - logp)).sum(-1)
+            out.append(torch.where(ok.any(-1), kl, torch.zeros_like(kl)))
+        return torch.cat(out) if out else q.new_zeros(0, dtype=torch.float32)
 
     def _selected_attention(self, q, k, v, sel, sel_ok, iv, T):
         """Each query attends its selected context tokens and the whole of its own draft block."""

@@ -19,7 +19,7 @@ import torch
 import torch.nn as nn
 
 from aspec_b200.models.draft.dflash import DFlashAttention
-from aspec_b200.models.draft.sparse_common import (build_group_layout, eligible_groups, gathered_attention, kl_rows,
+from aspec_b200.models.draft.sparse_common import (build_group_layout, eligible_groups, indexed_attention, kl_rows,
                                                    masked_log_softmax, own_block_index, rotary)
 from aspec_b200.ops.attention import interval_attention
 from aspec_b200.ops.fused_params import fused_linear
@@ -146,7 +146,7 @@ class QSAAttention(DFlashAttention):
         blk, blk_ok = own_block_index(intervals, k.shape[0])
         idx = torch.cat([torch.cat([tok, tail.clamp(max=T - 1)], 1).repeat_interleave(block, 0), blk], 1)
         ok = torch.cat([torch.cat([tok_ok, tail_ok], 1).repeat_interleave(block, 0), blk_ok], 1)
-        return gathered_attention(q, k[idx], v[idx], ok, self.scale)
+        return indexed_attention(q, k, v, idx, ok, self.scale)
 
     def trainable_parameter_names(self):
         return [n for n, _ in self.named_parameters() if n.startswith("indexer.")] if self.stage == "indexer_warmup" else None

@@ -93,6 +93,19 @@ def gathered_attention(q, keys, values, ok, scale):
     return torch.einsum("nhs,nshd->nhd", p, vv).to(q.dtype)
 
 
+def indexed_attention(q, keys, values, idx, ok, scale):
+    """Attention of ``q [n, H, d]`` over the key rows ``idx [n, S]`` of ``keys / values [Tk, Hk, d]`` where ``ok``.
+
+    On a GPU (bf16, head dim 128) this is the selected-key kernel: rows are gathered tile by tile inside the kernel
+    and nothing of size ``n x S x Hk x d`` is materialised.  Elsewhere it is the gathered fp32 statement above."""
+    from aspec_b200.ops import sparse_attention as SA
+    if SA._kernel_ok(q, keys, values):
+        sel = torch.where(ok, idx, torch.full_like(idx, -1)).to(torch.int32)
+        out, _ = SA.selected_attention(q, keys, values, sel, scale)
+        return out
+    return gathered_attention(q, keys[idx], values[idx], ok, scale)
+
+
 def own_block_index(iv: torch.Tensor, n_keys: int):
     b_lo, b_hi = iv[:, 2].long(), iv[:, 3].long()
     width = int((b_hi - b_lo).max().item()) if iv.shape[0] else 0

@@ -129,7 +129,8 @@ class _SelectedAttentionFn(torch.autograd.Function):
         dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
         dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
         st = status_word(q.device)
-        rc = _native.kernels().ab_sel_attn_bwd(_p(q), _p(k), _p(v), _p(sel), _p(out), _p(lse), _p(dout.contiguous()), _p(dq),
+        dout = dout.contiguous()            # named: a temporary's memory could be reused before the launch
+        rc = _native.kernels().ab_sel_attn_bwd(_p(q), _p(k), _p(v), _p(sel), _p(out), _p(lse), _p(dout), _p(dq),
                                                _p(dk), _p(dv), n, k.shape[0], sel.shape[1], hq, k.shape[1], d,
                                                _c.c_longlong(k.stride(0)), _c.c_longlong(v.stride(0)), _c.c_float(ctx.scale),
                                                _p(st), _stream(q))
@@ -173,9 +174,12 @@ def indexer_scores(qi: torch.Tensor, ki: torch.Tensor, w: torch.Tensor, lo: torc
         ki = ki.contiguous()
     out = torch.full((n, T), float("-inf"), dtype=torch.float32, device=qi.device)
     st = status_word(qi.device)
-    rc = _native.kernels().ab_indexer_scores(_p(qi), _p(ki), _p(w.float().contiguous()), _p(lo.to(torch.int32).contiguous()),
-                                             _p(hi.to(torch.int32).contiguous()), _p(out), _c.c_longlong(out.stride(0)), n, T, H, d,
-                                             _c.c_longlong(ki.stride(0)), _p(st), _stream(qi))
+    # converted copies are held in names until after the launch: a temporary freed between two conversions would hand
+    # the same block to the next one
+    w32, lo32, hi32 = w.float().contiguous(), lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
+    rc = _native.kernels().ab_indexer_scores(_p(qi), _p(ki), _p(w32), _p(lo32), _p(hi32), _p(out),
+                                             _c.c_longlong(out.stride(0)), n, T, H, d, _c.c_longlong(ki.stride(0)), _p(st),
+                                             _stream(qi))
     if rc != 0:
         raise RuntimeError(f"ab_indexer_scores refused the launch (code {rc})")
     return out
@@ -191,8 +195,9 @@ def topk_select(scores: torch.Tensor, lo: torch.Tensor, hi: torch.Tensor, k: int
     note("topk", "radix_select")
     n, T = scores.shape
     out = torch.empty(n, k, dtype=torch.int32, device=scores.device)
-    rc = _native.kernels().ab_topk_select(_p(scores), _c.c_longlong(scores.stride(0)), _p(lo.to(torch.int32).contiguous()),
-                                          _p(hi.to(torch.int32).contiguous()), n, T, k, _p(out), _stream(scores))
+    lo32, hi32 = lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
+    rc = _native.kernels().ab_topk_select(_p(scores), _c.c_longlong(scores.stride(0)), _p(lo32), _p(hi32), n, T, k, _p(out),
+                                          _stream(scores))
     if rc != 0:
         raise RuntimeError(f"ab_topk_select refused the launch (code {rc})")
     return out

@@ -44,15 +44,19 @@ def test_forward_matches_reference(n_ctx, n_blocks, bs, hq, hkv, causal, window,
     assert (lse[fin] - ref_lse[fin]).abs().max().item() < 2e-2
 
 
-@pytest.mark.parametrize("n_ctx,n_blocks,bs,hq,hkv,causal", [
-    (200, 9, 7, 4, 1, False),
-    (1000, 64, 7, 8, 2, False),
-    (517, 33, 4, 2, 2, True),
+@pytest.mark.parametrize("n_ctx,n_blocks,bs,hq,hkv,causal,window,docs", [
+    (200, 9, 7, 4, 1, False, None, 1),
+    (1000, 64, 7, 8, 2, False, None, 1),
+    (517, 33, 4, 2, 2, True, None, 1),
+    (2048, 128, 7, 8, 2, False, 300, 1),       # context window
+    (1536, 96, 7, 8, 2, False, None, 3),       # several packed documents
+    (1500, 90, 7, 8, 2, True, 256, 3),         # window + causal inside the block + documents
+    (4096, 512, 7, 32, 8, False, None, 1),     # the production head layout: 32 / 8 heads, 4 K context, 3584 queries
 ])
-def test_backward_matches_reference(n_ctx, n_blocks, bs, hq, hkv, causal):
+def test_backward_matches_reference(n_ctx, n_blocks, bs, hq, hkv, causal, window, docs):
     from aspec_b200.ops.attention import interval_attention, interval_attention_reference
     from aspec_b200.ops.gemm import check_status
-    q, k, v, iv = _case(n_ctx, n_blocks, bs, hq, hkv, seed=7 + n_ctx, causal=causal)
+    q, k, v, iv = _case(n_ctx, n_blocks, bs, hq, hkv, seed=7 + n_ctx, causal=causal, window=window, docs=docs)
     scale = 128 ** -0.5
     q.requires_grad_(); k.requires_grad_(); v.requires_grad_()
     out, _ = interval_attention(q, k, v, iv, scale)

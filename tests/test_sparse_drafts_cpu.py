@@ -75,3 +75,69 @@ def test_mla_dspark_trains():
                   last_hidden_states=torch.randn(1, 48, 64))
     out[6][0].backward()
     assert model.layers[0].self_attn.kv_b_proj.weight.grad.abs().sum() > 0
+
+
+def test_dsa_kernel_path_statement_matches_the_chunked_path(monkeypatch):
+    """The GPU sparse stage (scores kernel -> top-k kernel -> selected-key kernel, KL on the selected set) is driven
+    here through its fp32 statements: loss terms must equal the original chunked formulation."""
+    from aspec_b200.ops import sparse_attention as SA
+    kind = dict(KINDS["dsa"], dsa_token_budget=6)        # a budget that really prunes
+    outs = {}
+    for name in ("chunked", "kernel_path"):
+        if name == "kernel_path":
+            calls = {"n": 0}
+
+            def first_true(q, keys, values):
+                calls["n"] += 1
+                return calls["n"] == 1           # only the stage dispatch in DSAAttention.forward takes the new path
+
+            monkeypatch.setattr(SA, "_kernel_ok", first_true)
+        torch.manual_seed(0)
+        cfg = DSparkConfig(**BASE, **kind, dsa_training_stage="sparse")
+        model = DSparkDraftModel(cfg)
+        wrapper = DSparkModel(model, block_size=4, num_anchors=8)
+        torch.manual_seed(1)
+        ids = torch.randint(0, 250, (1, 48))
+        hs, last = torch.randn(1, 48, 192), torch.randn(1, 48, 64)
+        mask = torch.ones(1, 48)
+        mask[:, :10] = 0
+        out = wrapper(ids, hs, mask, torch.randn(256, 64) * 0.1, last_hidden_states=last, anchor_seed=7)
+        out[6][0].backward()
+        outs[name] = (dict(out[5]), {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None})
+    a, b = outs["chunked"], outs["kernel_path"]
+    for key in ("ce_loss", "dsa_indexer_loss"):
+        assert torch.allclose(a[0][key][0], b[0][key][0], rtol=1e-4, atol=1e-5), key
+    assert set(a[1]) == set(b[1])
+    for n in a[1]:
+        assert torch.allclose(a[1][n], b[1][n], rtol=2e-3, atol=2e-5), n
+
+
+def test_selected_attention_and_selection_oracles():
+    from aspec_b200.ops.attention import interval_attention_reference
+    from aspec_b200.ops.sparse_attention import (indexer_scores_reference, selected_attention_reference,
+                                                 topk_select_reference)
+    torch.manual_seed(3)
+    n, hq, hkv, d, T = 6, 4, 2, 16, 30
+    q, k, v = torch.randn(n, hq, d), torch.randn(T, hkv, d), torch.randn(T, hkv, d)
+    lo = torch.tensor([0, 0, 3, 5, 10, 7])
+    hi = torch.tensor([10, 30, 3, 25, 11, 29])
+    # a list that names every key of [lo, hi) once (plus empty slots) is interval attention
+    sel = torch.full((n, T + 2), -1)
+    for i in range(n):
+        r = torch.arange(lo[i], hi[i])
+        sel[i, 1:1 + r.numel()] = r[torch.randperm(r.numel())]
+    out, lse = selected_attention_reference(q, k, v, sel, 0.25)
+    iv = torch.stack([lo, hi, torch.zeros_like(lo), torch.zeros_like(lo)], 1)
+    want, want_lse = interval_attention_reference(q, k, v, iv, 0.25)
+    assert torch.allclose(out, want, atol=1e-5) and torch.allclose(lse[:, [0, 1, 3, 4, 5]], want_lse[:, [0, 1, 3, 4, 5]], atol=1e-5)
+    assert (out[2] == 0).all() and torch.isinf(lse[:, 2]).all()
+    qi, ki, w = torch.randn(n, 4, 8), torch.randn(T, 8), torch.rand(n, 4)
+    sc = indexer_scores_reference(qi, ki, w, lo, hi)
+    top = topk_select_reference(sc, lo, hi, 5)
+    for i in range(n):
+        got = [t for t in top[i].tolist() if t >= 0]
+        assert got == sorted(got) and len(got) == min(5, int(hi[i] - lo[i]))
+        if got:
+            worst = sc[i, got].min()
+            rest = [t for t in range(int(lo[i]), int(hi[i])) if t not in got]
+            assert all(sc[i, t] <= worst for t in rest)
