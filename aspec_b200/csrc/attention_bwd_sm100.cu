@@ -16,6 +16,12 @@
 // Shared-memory tiles are used under two descriptor views: [rows, 64] K-major
 // when the tile is the left/right operand of a d-reduction, and MN-major when
 // the same bytes are the right operand of a row-reduction.
+//
+// Both main kernels are templates on the query/key head dimension HDQK: 128, or 192 for materialised-MLA heads
+// (values stay 128 wide).  At 192 a dQ / dK accumulator would need 192 of the 512 tensor-memory columns next to S,
+// dP and the other accumulators, so the grid gets a third dimension: pass 0 produces columns [0, 128) (and dV),
+// pass 1 columns [128, 192); each pass recomputes S and dP.  The wider Q / K tiles also leave room for only one
+// K/V (or Q/dO) stage in shared memory.
 #include "common.cuh"
 
 namespace ab {
@@ -23,6 +29,8 @@ namespace attn {
 
 int make_map_rows_heads(CUtensorMap* map, const void* base, long long rows, int heads, long long ld,
                         int box_heads, int box_rows);
+int make_map_rows_heads_d(CUtensorMap* map, const void* base, long long rows, int heads, long long ld,
+                          int box_heads, int box_rows, int hd);
 
 static constexpr int BM = 128;
 static constexpr int BN = 128;
@@ -32,13 +40,21 @@ static constexpr int kTile = 128 * HD * 2;   // 32 KB: one 128 x 128 bf16 tile (
 static constexpr int kChunk = 128 * 128;     // bytes per 64-column chunk
 static constexpr float kLog2e = 1.4426950408889634f;
 
+template <int HDQK> struct BwdCfg {
+  static constexpr int kQKTile = 128 * HDQK * 2;                 // a Q or K tile: HDQK / 64 chunks
+  static constexpr int kStages = HDQK == 128 ? 2 : 1;
+  static constexpr int kPasses = (HDQK + 127) / 128;             // passes over the qk head dim for dQ / dK
+  static constexpr int kDqSmem = kQKTile + kTile + kStages * (kQKTile + kTile) + 1024 + 256;
+  static constexpr int kDkvSmem = kQKTile + kTile + kStages * (kQKTile + kTile) + 2 * 128 * 24 + 4096 * 4 + 1024 + 256;
+};
+
 struct BwdParams {
   const int* intervals;       // [Qtot, 4]
   const float* lse;           // [Hq, Qtot] natural log
   const float* delta;         // [Hq, Qtot]
   const int* tile_ranges;     // [n_qtiles, 4]  (c_lo, c_hi, b_lo, b_hi) in key index units
-  __nv_bfloat16* dq;          // [Qtot, Hq, HD]
-  __nv_bfloat16* dk;          // [Tk, Hkv, HD]
+  __nv_bfloat16* dq;          // [Qtot, Hq, HDQK]
+  __nv_bfloat16* dk;          // [Tk, Hkv, HDQK]
   __nv_bfloat16* dv;          // [Tk, Hkv, HD]
   int q_total, hq, hkv, group, tk, n_qtiles;
   float scale, scale_log2;
@@ -103,17 +119,21 @@ __device__ __forceinline__ bool visible(int kk, int a0, int a1, int b0, int b1) 
 
 // -------------------------------------------------------------------- dQ ----
 // TMEM: S [0,128)  dP [128,256)  dQ [256,384)  dS0 [384,448)  dS1 [448,512)
-static constexpr int kDqSmem = 2 * kTile /*Q,dO*/ + 2 * 2 * kTile /*K,V x2 stages*/ + 1024 + 256;
-
+template <int HDQK>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
+  constexpr int kQKTile = BwdCfg<HDQK>::kQKTile, kStages = BwdCfg<HDQK>::kStages;
+  constexpr int kStage = kQKTile + kTile;          // one K/V stage: K (HDQK wide) then V
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
-  uint8_t* sdO = smem + kTile;
-  uint8_t* sKV = smem + 2 * kTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + 4 * kTile);
+  uint8_t* sdO = smem + kQKTile;
+  uint8_t* sKV = sdO + kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kStages * kStage);
+  // this CTA's columns of dQ: [dcol0, dcol0 + ncols) of the HDQK-wide head
+  const int dcol0 = blockIdx.z * 128;
+  const int ncols = HDQK - dcol0 < 128 ? HDQK - dcol0 : 128;
   uint64_t* q_full = bars;        // Q and dO
   uint64_t* kv_full = bars + 1;   // [2]
   uint64_t* kv_empty = bars + 3;  // [2]
@@ -161,20 +181,20 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
 
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
-      mbar_arrive_expect_tx(q_full, 2 * kTile);
-      tma_load_3d(sQ, &maps.q, q_full, 0, kvh * G, q0);
-      tma_load_3d(sQ + kChunk, &maps.q, q_full, 64, kvh * G, q0);
+      mbar_arrive_expect_tx(q_full, kQKTile + kTile);
+#pragma unroll
+      for (int c = 0; c < HDQK / 64; ++c) tma_load_3d(sQ + c * kChunk, &maps.q, q_full, 64 * c, kvh * G, q0);
       tma_load_3d(sdO, &maps.dout, q_full, 0, kvh * G, q0);
       tma_load_3d(sdO + kChunk, &maps.dout, q_full, 64, kvh * G, q0);
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_word)) break;
-        uint8_t* sK = sKV + st * 2 * kTile;
-        uint8_t* sV = sK + kTile;
+        const int st = j % kStages;
+        if (!mbar_wait(&kv_empty[st], ((j / kStages) & 1) ^ 1u, abort_word)) break;
+        uint8_t* sK = sKV + st * kStage;
+        uint8_t* sV = sK + kQKTile;
         const int k0 = tile_index(j) * BN;
-        mbar_arrive_expect_tx(&kv_full[st], 2 * kTile);
-        tma_load_3d(sK, &maps.k, &kv_full[st], 0, kvh, k0);
-        tma_load_3d(sK + kChunk, &maps.k, &kv_full[st], 64, kvh, k0);
+        mbar_arrive_expect_tx(&kv_full[st], kStage);
+#pragma unroll
+        for (int c = 0; c < HDQK / 64; ++c) tma_load_3d(sK + c * kChunk, &maps.k, &kv_full[st], 64 * c, kvh, k0);
         tma_load_3d(sV, &maps.v, &kv_full[st], 0, kvh, k0);
         tma_load_3d(sV + kChunk, &maps.v, &kv_full[st], 64, kvh, k0);
       }
@@ -182,13 +202,13 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(BM, BN, 0, 0);   // both K-major (d-reduction)
-      constexpr uint32_t idesc_dq = make_idesc_bf16(BM, HD, 0, 1);   // dS (TMEM) x K (MN-major view)
+      const uint32_t idesc_dq = make_idesc_bf16(BM, ncols, 0, 1);    // dS (TMEM) x K (MN-major view), this pass's columns
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
       auto issue_s_dp = [&](int j) {
-        const uint32_t k_addr = smem_u32(sKV + (j & 1) * 2 * kTile);
-        const uint32_t v_addr = k_addr + kTile;
+        const uint32_t k_addr = smem_u32(sKV + (j % kStages) * kStage);
+        const uint32_t v_addr = k_addr + kQKTile;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
+        for (int k = 0; k < HDQK / 16; ++k) {
           const uint32_t off = (k >> 2) * kChunk + (k & 3) * 32;
           tc_mma_ss(tmem + 0, make_smem_desc(q_addr + off, 16, 1024),
                     make_smem_desc(k_addr + off, 16, 1024), idesc_kk, k ? 1u : 0u);
@@ -201,21 +221,42 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         }
         tc_commit(sp_full);
       };
-      bool alive = mbar_wait(q_full, 0, abort_word) && mbar_wait(&kv_full[0], 0, abort_word);
-      if (alive) { tc_fence_after(); issue_s_dp(0); }
-      for (int j = 0; j < n_tiles && alive; ++j) {
-        if (j + 1 < n_tiles && !mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_word)) break;
-        if (!mbar_wait(ds_full, j & 1, abort_word)) break;
-        tc_fence_after();
-        if (j + 1 < n_tiles) issue_s_dp(j + 1);
-        const uint32_t k_addr = smem_u32(sKV + (j & 1) * 2 * kTile);
-        const uint32_t ds_col = tmem + 384 + (j & 1) * 64;
+      bool alive = mbar_wait(q_full, 0, abort_word);
+      if (kStages == 2) {
+        // S / dP of tile j + 1 are issued before dQ of tile j: the other K/V stage is already in shared memory
+        alive = alive && mbar_wait(&kv_full[0], 0, abort_word);
+        if (alive) { tc_fence_after(); issue_s_dp(0); }
+        for (int j = 0; j < n_tiles && alive; ++j) {
+          if (j + 1 < n_tiles && !mbar_wait(&kv_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_word)) break;
+          if (!mbar_wait(ds_full, j & 1, abort_word)) break;
+          tc_fence_after();
+          if (j + 1 < n_tiles) issue_s_dp(j + 1);
+          const uint32_t k_addr = smem_u32(sKV + (j & 1) * kStage);
+          const uint32_t ds_col = tmem + 384 + (j & 1) * 64;
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          tc_mma_ts(tmem + 256, ds_col + k * 8, make_smem_desc(k_addr + k * 2048, kChunk, 1024), idesc_dq,
-                    (j | k) ? 1u : 0u);
-        tc_commit(&kv_empty[j & 1]);
-        tc_commit(&dq_done[j & 1]);
+          for (int k = 0; k < BN / 16; ++k)
+            tc_mma_ts(tmem + 256, ds_col + k * 8, make_smem_desc(k_addr + k * 2048, kChunk, 1024), idesc_dq,
+                      (j | k) ? 1u : 0u);
+          tc_commit(&kv_empty[j & 1]);
+          tc_commit(&dq_done[j & 1]);
+        }
+      } else {
+        // one K/V stage: the K tile is also the dQ MMA's operand, so a tile is finished before the next is loaded
+        for (int j = 0; j < n_tiles && alive; ++j) {
+          if (!mbar_wait(&kv_full[0], j & 1, abort_word)) break;
+          tc_fence_after();
+          issue_s_dp(j);
+          if (!mbar_wait(ds_full, j & 1, abort_word)) break;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(sKV) + (dcol0 / 64) * kChunk;   // this pass's 64-column chunks of K
+          const uint32_t ds_col = tmem + 384 + (j & 1) * 64;
+#pragma unroll
+          for (int k = 0; k < BN / 16; ++k)
+            tc_mma_ts(tmem + 256, ds_col + k * 8, make_smem_desc(k_addr + k * 2048, kChunk, 1024), idesc_dq,
+                      (j | k) ? 1u : 0u);
+          tc_commit(&kv_empty[0]);
+          tc_commit(&dq_done[j & 1]);
+        }
       }
     }
   } else {
@@ -295,9 +336,9 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       alive = mbar_wait(&dq_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_word);
     if (alive) {
       tc_fence_after();
-      __nv_bfloat16* row = p.dq + ((size_t)(row_ok ? pos : 0) * p.hq + head) * HD;
+      __nv_bfloat16* row = p.dq + ((size_t)(row_ok ? pos : 0) * p.hq + head) * HDQK + dcol0;
 #pragma unroll 1
-      for (int c = cbeg; c < cbeg + 64; c += 32) {
+      for (int c = cbeg; c < cbeg + 64 && c < ncols; c += 32) {
         uint32_t r[32];
         if (n_tiles > 0) { tmem_ld_32x32(tmem + lane_base + 256 + c, r); tmem_ld_wait(); }
         if (row_ok) {
@@ -328,18 +369,23 @@ attn_bwd_dq_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
 // ------------------------------------------------------------------ dK/dV ---
 // TMEM: S^T / P^T [0,128)   dP^T / dS^T [128,256)   dV [256,384)   dK [384,512)
 static constexpr int kListCap = 4096;
-static constexpr int kDkvSmem = 2 * kTile /*K,V*/ + 2 * 2 * kTile /*Q,dO x2 stages*/ +
-                                2 * 128 * 24 /*row metadata x2*/ + kListCap * 4 + 1024 + 256;
 
+template <int HDQK>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
+  constexpr int kQKTile = BwdCfg<HDQK>::kQKTile, kStages = BwdCfg<HDQK>::kStages;
+  constexpr int kStage = kQKTile + kTile;     // one Q/dO stage: Q (HDQK wide) then dO
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sK = smem;
-  uint8_t* sV = smem + kTile;
-  uint8_t* sQdO = smem + 2 * kTile;           // stage s: Q at +s*2*kTile, dO right after
-  uint8_t* meta = sQdO + 4 * kTile;           // stage s: int4 iv[128]; float lse2[128]; float delta[128]
+  uint8_t* sV = smem + kQKTile;
+  uint8_t* sQdO = sV + kTile;                 // stage s: Q at +s*kStage, dO right after
+  uint8_t* meta = sQdO + kStages * kStage;    // buffer b: int4 iv[128]; float lse2[128]; float delta[128]
+  // this CTA's columns of dK: [dcol0, dcol0 + ncols); dV belongs to pass 0
+  const int dcol0 = blockIdx.z * 128;
+  const int ncols = HDQK - dcol0 < 128 ? HDQK - dcol0 : 128;
+  const bool with_dv = blockIdx.z == 0;
   int* list = reinterpret_cast<int*>(meta + 2 * 128 * 24);
   uint64_t* bars = reinterpret_cast<uint64_t*>(list + kListCap);
   uint64_t* kv_full = bars;         // 1
@@ -398,20 +444,20 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
 
   if (warp == 0) {
     if (lane == 0 && n > 0) {
-      mbar_arrive_expect_tx(kv_full, 2 * kTile);
-      tma_load_3d(sK, &maps.k, kv_full, 0, kvh, k0);
-      tma_load_3d(sK + kChunk, &maps.k, kv_full, 64, kvh, k0);
+      mbar_arrive_expect_tx(kv_full, kQKTile + kTile);
+#pragma unroll
+      for (int c = 0; c < HDQK / 64; ++c) tma_load_3d(sK + c * kChunk, &maps.k, kv_full, 64 * c, kvh, k0);
       tma_load_3d(sV, &maps.v, kv_full, 0, kvh, k0);
       tma_load_3d(sV + kChunk, &maps.v, kv_full, 64, kvh, k0);
       for (int i = 0; i < n; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(&qdo_empty[st], ((i >> 1) & 1) ^ 1u, abort_word)) break;
-        uint8_t* sQ = sQdO + st * 2 * kTile;
-        uint8_t* sdO = sQ + kTile;
+        const int st = i % kStages;
+        if (!mbar_wait(&qdo_empty[st], ((i / kStages) & 1) ^ 1u, abort_word)) break;
+        uint8_t* sQ = sQdO + st * kStage;
+        uint8_t* sdO = sQ + kQKTile;
         const int q0 = list[i] * pm;
-        mbar_arrive_expect_tx(&qdo_full[st], 2 * kTile);
-        tma_load_3d(sQ, &maps.q, &qdo_full[st], 0, kvh * G, q0);
-        tma_load_3d(sQ + kChunk, &maps.q, &qdo_full[st], 64, kvh * G, q0);
+        mbar_arrive_expect_tx(&qdo_full[st], kStage);
+#pragma unroll
+        for (int c = 0; c < HDQK / 64; ++c) tma_load_3d(sQ + c * kChunk, &maps.q, &qdo_full[st], 64 * c, kvh * G, q0);
         tma_load_3d(sdO, &maps.dout, &qdo_full[st], 0, kvh * G, q0);
         tma_load_3d(sdO + kChunk, &maps.dout, &qdo_full[st], 64, kvh * G, q0);
       }
@@ -419,17 +465,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
   } else if (warp == 1) {
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(BN, BM, 0, 0);   // K/V (K-major) x Q/dO (K-major)
-      constexpr uint32_t idesc_acc = make_idesc_bf16(BN, HD, 0, 1);  // P^T/dS^T (TMEM) x dO/Q (MN-major)
+      constexpr uint32_t idesc_dv = make_idesc_bf16(BN, HD, 0, 1);   // P^T (TMEM) x dO (MN-major)
+      const uint32_t idesc_dk = make_idesc_bf16(BN, ncols, 0, 1);    // dS^T (TMEM) x Q (MN-major), this pass's columns
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       bool alive = mbar_wait(kv_full, 0, abort_word);
       for (int i = 0; i < n && alive; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(&qdo_full[st], (i >> 1) & 1, abort_word)) break;
+        const int st = i % kStages;
+        if (!mbar_wait(&qdo_full[st], (i / kStages) & 1, abort_word)) break;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQdO + st * 2 * kTile);
-        const uint32_t do_addr = q_addr + kTile;
+        const uint32_t q_addr = smem_u32(sQdO + st * kStage);
+        const uint32_t do_addr = q_addr + kQKTile;
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
+        for (int k = 0; k < HDQK / 16; ++k) {
           const uint32_t off = (k >> 2) * kChunk + (k & 3) * 32;
           tc_mma_ss(tmem + 0, make_smem_desc(k_addr + off, 16, 1024),
                     make_smem_desc(q_addr + off, 16, 1024), idesc_kk, k ? 1u : 0u);
@@ -447,12 +494,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
         // Each warpgroup wrote its 64 query columns as 32 packed columns over scores IT had consumed:
         // query columns [0, 64) live at packed columns [0, 32), query columns [64, 128) at [64, 96).
         for (int k = 0; k < BM / 16; ++k)   // reduction over the 128 query rows of the tile
-          tc_mma_ts(tmem + 256, tmem + 0 + (k >> 2) * 64 + (k & 3) * 8, make_smem_desc(do_addr + k * 2048, kChunk, 1024),
-                    idesc_acc, (i | k) ? 1u : 0u);
+          if (with_dv)
+            tc_mma_ts(tmem + 256, tmem + 0 + (k >> 2) * 64 + (k & 3) * 8, make_smem_desc(do_addr + k * 2048, kChunk, 1024),
+                      idesc_dv, (i | k) ? 1u : 0u);
+        const uint32_t qd_addr = q_addr + (dcol0 / 64) * kChunk;   // this pass's 64-column chunks of Q
 #pragma unroll
         for (int k = 0; k < BM / 16; ++k)
-          tc_mma_ts(tmem + 384, tmem + 128 + (k >> 2) * 64 + (k & 3) * 8, make_smem_desc(q_addr + k * 2048, kChunk, 1024),
-                    idesc_acc, (i | k) ? 1u : 0u);
+          tc_mma_ts(tmem + 384, tmem + 128 + (k >> 2) * 64 + (k & 3) * 8, make_smem_desc(qd_addr + k * 2048, kChunk, 1024),
+                    idesc_dk, (i | k) ? 1u : 0u);
         tc_commit(&qdo_empty[st]);
         tc_commit(acc_done);
       }
@@ -561,13 +610,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
       tc_fence_after();
       const bool row_ok = kk < p.tk;
       __nv_bfloat16* dvrow = p.dv + ((size_t)(row_ok ? kk : 0) * p.hkv + kvh) * HD;
-      __nv_bfloat16* dkrow = p.dk + ((size_t)(row_ok ? kk : 0) * p.hkv + kvh) * HD;
+      __nv_bfloat16* dkrow = p.dk + ((size_t)(row_ok ? kk : 0) * p.hkv + kvh) * HDQK + dcol0;
 #pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      for (int half = with_dv ? 0 : 1; half < 2; ++half) {
         __nv_bfloat16* row = half ? dkrow : dvrow;
         const uint32_t col0 = half ? 384 : 256;
+        const int width = half ? ncols : HD;
 #pragma unroll 1
-        for (int c = cbeg; c < cbeg + 64; c += 32) {
+        for (int c = cbeg; c < cbeg + 64 && c < width; c += 32) {
           uint32_t r[32];
           if (n > 0) { tmem_ld_32x32(tmem + lane_base + col0 + c, r); tmem_ld_wait(); }
           if (row_ok) {
@@ -599,8 +649,26 @@ attn_bwd_dkv_kernel(const __grid_constant__ BwdMaps maps, const BwdParams p) {
 }  // namespace attn
 }  // namespace ab
 
-// dq [Qtot,Hq,128], dk/dv [Tk,Hkv,128] contiguous bf16.  Scratch supplied by the caller and filled
-// here: delta [Hq,Qtot] fp32 and ranges [ceil(Qtot / (128 / G)), 4] int32.
+template <int HDQK>
+static int launch_bwd_main(const ab::attn::BwdMaps& maps, const ab::attn::BwdParams& p, int n_qtiles, int n_ktiles,
+                           cudaStream_t stream) {
+  using namespace ab;
+  using namespace ab::attn;
+  using Cfg = BwdCfg<HDQK>;
+  static std::atomic<unsigned long long> attr_done{0};
+  if (!once_per_device(attr_done, [&] {
+        return cudaFuncSetAttribute(attn_bwd_dq_kernel<HDQK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kDqSmem) == cudaSuccess &&
+               cudaFuncSetAttribute(attn_bwd_dkv_kernel<HDQK>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kDkvSmem) == cudaSuccess;
+      }))
+    return -3;
+  attn_bwd_dq_kernel<HDQK><<<dim3(n_qtiles, p.hkv, Cfg::kPasses), kThreads, Cfg::kDqSmem, stream>>>(maps, p);
+  attn_bwd_dkv_kernel<HDQK><<<dim3(n_ktiles, p.hkv, Cfg::kPasses), kThreads, Cfg::kDkvSmem, stream>>>(maps, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// `head_dim` is the query/key head dimension (128, or 192 for materialised-MLA heads); values, out and dout are 128
+// wide.  dq [Qtot,Hq,head_dim], dk [Tk,Hkv,head_dim], dv [Tk,Hkv,128] contiguous bf16.  Scratch supplied by the caller
+// and filled here: delta [Hq,Qtot] fp32 and ranges [ceil(Qtot / (128 / G)), 4] int32.
 extern "C" int ab_attn_bwd(const void* q, const void* k, const void* v, const int* intervals,
                            const void* out, const float* lse, const void* dout, float* delta,
                            int* ranges, void* dq,
@@ -609,7 +677,7 @@ extern "C" int ab_attn_bwd(const void* q, const void* k, const void* v, const in
   using namespace ab;
   using namespace ab::attn;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  if (head_dim != HD || hq % hkv) return -10;
+  if ((head_dim != HD && head_dim != 192) || hq % hkv) return -10;
   const int G = hq / hkv;
   if (G > 16 || (BM % G)) return -11;
   if (q_total <= 0 || tk <= 0) return 0;
@@ -624,9 +692,9 @@ extern "C" int ab_attn_bwd(const void* q, const void* k, const void* v, const in
       intervals, ranges, q_total, hq, pm, n_qtiles);
   BwdMaps maps;
   int rc;
-  if ((rc = make_map_rows_heads(&maps.q, q, q_total, hq, (long long)hq * HD, G, pm))) return rc;
+  if ((rc = make_map_rows_heads_d(&maps.q, q, q_total, hq, (long long)hq * head_dim, G, pm, head_dim))) return rc;
   if ((rc = make_map_rows_heads(&maps.dout, dout, q_total, hq, (long long)hq * HD, G, pm))) return rc;
-  if ((rc = make_map_rows_heads(&maps.k, k, tk, hkv, k_ld, 1, BN))) return rc;
+  if ((rc = make_map_rows_heads_d(&maps.k, k, tk, hkv, k_ld, 1, BN, head_dim))) return rc;
   if ((rc = make_map_rows_heads(&maps.v, v, tk, hkv, v_ld, 1, BN))) return rc;
   BwdParams p;
   p.intervals = intervals;
@@ -645,15 +713,8 @@ extern "C" int ab_attn_bwd(const void* q, const void* k, const void* v, const in
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   p.status = status;
-  static std::atomic<unsigned long long> attr_done{0};
-  if (!once_per_device(attr_done, [&] {
-        return cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem) == cudaSuccess &&
-               cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem) == cudaSuccess;
-      }))
-    return -3;
-  attn_bwd_dq_kernel<<<dim3(n_qtiles, hkv), kThreads, kDqSmem, stream>>>(maps, p);
-  attn_bwd_dkv_kernel<<<dim3(n_ktiles, hkv), kThreads, kDkvSmem, stream>>>(maps, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return head_dim == HD ? launch_bwd_main<128>(maps, p, n_qtiles, n_ktiles, stream)
+                        : launch_bwd_main<192>(maps, p, n_qtiles, n_ktiles, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -6,7 +6,9 @@
 // One CTA owns 128 query rows of one key/value head.  The G = Hq / Hkv query
 // heads that share that key/value head are folded into the row dimension
 // (row = position * G + head-in-group), so every K/V tile that is staged in
-// shared memory serves all of them.  Head dimension 128 (qk and v).
+// shared memory serves all of them.  Value head dimension 128; query/key head dimension 128, or 192 for
+// materialised-MLA heads (128 "nope" + 64 rotary dims): the kernel is a template on it, the 192 variant stages three
+// 64-column chunks of Q and K and runs one CTA per SM.
 //
 //   warp 0      TMA producer: Q once, then one K and one V buffer, refilled as soon
 //               as the MMA that read them has completed
@@ -30,12 +32,16 @@ namespace attn {
 
 static constexpr int BM = 128;   // query rows per CTA (positions x heads-in-group)
 static constexpr int BN = 128;   // keys per tile
-static constexpr int HD = 128;   // head dim
+static constexpr int HD = 128;   // value head dim (and the query/key head dim of ordinary heads)
 static constexpr int kThreads = 192;
-static constexpr int kQBytes = BM * HD * 2;       // 32 KB (two 64-column swizzled chunks)
-static constexpr int kKVBytes = BN * HD * 2;      // 32 KB each for K and V
+static constexpr int kKVBytes = BN * HD * 2;      // 32 KB: the V tile (and the K tile at head dim 128)
 static constexpr int kChunk = BM * 128;           // bytes of one 64-column chunk (128 rows x 128 B)
-static constexpr int kSmemBytes = kQBytes + 2 * kKVBytes + 1024 + 256;
+// Q and K tiles are HDQK / 64 chunks each
+template <int HDQK> struct FwdSmem {
+  static constexpr int kQBytes = BM * HDQK * 2;
+  static constexpr int kKBytes = BN * HDQK * 2;
+  static constexpr int kBytes = kQBytes + kKBytes + kKVBytes + 1024 + 256;
+};
 static constexpr uint32_t kColS = 0, kColO = 128, kTmemCols = 256;
 static constexpr float kLog2e = 1.4426950408889634f;
 static constexpr float kRescaleThreshold = 8.0f;  // log2 domain: lazy rescale when max grows > 2^8
@@ -53,14 +59,16 @@ struct alignas(64) FwdMaps {
   CUtensorMap q, k, v;
 };
 
+template <int HDQK>
 __global__ void __launch_bounds__(kThreads, 2)
 attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
+  constexpr int kQBytes = FwdSmem<HDQK>::kQBytes, kKBytes = FwdSmem<HDQK>::kKBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = smem + kQBytes;
-  uint8_t* sV = sK + kKVBytes;
+  uint8_t* sV = sK + kKBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kKVBytes);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;
@@ -143,15 +151,15 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
       mbar_arrive_expect_tx(q_full, kQBytes);
-      tma_load_3d(sQ, &maps.q, q_full, 0, kvh * G, q0);
-      tma_load_3d(sQ + kChunk, &maps.q, q_full, 64, kvh * G, q0);
+#pragma unroll
+      for (int c = 0; c < HDQK / 64; ++c) tma_load_3d(sQ + c * kChunk, &maps.q, q_full, 64 * c, kvh * G, q0);
       for (int j = 0; j < n_tiles; ++j) {
         const uint32_t ph = j & 1;
         const int k0 = tile_index(j) * BN;
         if (!mbar_wait(k_empty, ph ^ 1u, abort_word)) break;        // S_{j-1} has read the K buffer
-        mbar_arrive_expect_tx(k_full, kKVBytes);
-        tma_load_3d(sK, &maps.k, k_full, 0, kvh, k0);
-        tma_load_3d(sK + kChunk, &maps.k, k_full, 64, kvh, k0);
+        mbar_arrive_expect_tx(k_full, kKBytes);
+#pragma unroll
+        for (int c = 0; c < HDQK / 64; ++c) tma_load_3d(sK + c * kChunk, &maps.k, k_full, 64 * c, kvh, k0);
         if (!mbar_wait(v_empty, ph ^ 1u, abort_word)) break;        // P_{j-1} V_{j-1} has read the V buffer
         mbar_arrive_expect_tx(v_full, kKVBytes);
         tma_load_3d(sV, &maps.v, v_full, 0, kvh, k0);
@@ -171,7 +179,7 @@ attn_fwd_kernel(const __grid_constant__ FwdMaps maps, const FwdParams p) {
         // S_j overwrites the region P_{j-1} lives in: the tensor core executes in issue order, so it runs
         // after P_{j-1} V_{j-1} has consumed P.
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
+        for (int k = 0; k < HDQK / 16; ++k) {
           const uint32_t off = (k >> 2) * kChunk + (k & 3) * 32;
           tc_mma_ss(tmem + kColS, make_smem_desc(q_addr + off, 16, 1024),
                     make_smem_desc(k_addr + off, 16, 1024), idesc_s, k ? 1u : 0u);
@@ -362,13 +370,13 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [rows, heads, 128] bf16 with row stride `ld` elements; box = 64 x box_heads x box_rows.
-int make_map_rows_heads(CUtensorMap* map, const void* base, long long rows, int heads, long long ld,
-                        int box_heads, int box_rows) {
+// [rows, heads, hd] bf16 with row stride `ld` elements; box = 64 x box_heads x box_rows.
+int make_map_rows_heads_d(CUtensorMap* map, const void* base, long long rows, int heads, long long ld,
+                          int box_heads, int box_rows, int hd) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -1;
-  cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)rows};
-  cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)ld * 2};
+  cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)rows};
+  cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)ld * 2};
   cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
@@ -385,16 +393,34 @@ int make_map_rows_heads(CUtensorMap* map, const void* base, long long rows, int 
   }
   return r == CUDA_SUCCESS ? 0 : -2;
 }
+int make_map_rows_heads(CUtensorMap* map, const void* base, long long rows, int heads, long long ld,
+                        int box_heads, int box_rows) {
+  return make_map_rows_heads_d(map, base, rows, heads, ld, box_heads, box_rows, HD);
+}
+
+template <int HDQK>
+static int launch_fwd(const FwdMaps& maps, const FwdParams& p, dim3 grid, cudaStream_t stream) {
+  static std::atomic<unsigned long long> attr_done{0};
+  if (!once_per_device(attr_done, [&] {
+        return cudaFuncSetAttribute(attn_fwd_kernel<HDQK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    FwdSmem<HDQK>::kBytes) == cudaSuccess;
+      }))
+    return -3;
+  attn_fwd_kernel<HDQK><<<grid, kThreads, FwdSmem<HDQK>::kBytes, stream>>>(maps, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
 
 }  // namespace attn
 }  // namespace ab
 
+// `head_dim` is the query/key head dimension: 128, or 192 for materialised-MLA heads; values and the output are
+// always 128 wide.  q [Qtot, Hq, head_dim] contiguous; k [Tk, Hkv, head_dim] / v [Tk, Hkv, 128] with row strides.
 extern "C" int ab_attn_fwd(const void* q, const void* k, const void* v, const int* intervals, void* out,
                            float* lse, int q_total, int tk, int hq, int hkv, int head_dim,
                            long long k_ld, long long v_ld, float scale, int* status, void* stream) {
   using namespace ab;
   using namespace ab::attn;
-  if (head_dim != HD || hq % hkv) return -10;
+  if ((head_dim != HD && head_dim != 192) || hq % hkv) return -10;
   const int G = hq / hkv;
   if (G > 16 || (BM % G)) return -11;
   if (q_total <= 0) return 0;
@@ -404,8 +430,8 @@ extern "C" int ab_attn_fwd(const void* q, const void* k, const void* v, const in
   FwdMaps maps;
   const int pm = BM / G;
   int rc;
-  if ((rc = make_map_rows_heads(&maps.q, q, q_total, hq, (long long)hq * HD, G, pm))) return rc;
-  if ((rc = make_map_rows_heads(&maps.k, k, tk, hkv, k_ld, 1, BN))) return rc;
+  if ((rc = make_map_rows_heads_d(&maps.q, q, q_total, hq, (long long)hq * head_dim, G, pm, head_dim))) return rc;
+  if ((rc = make_map_rows_heads_d(&maps.k, k, tk, hkv, k_ld, 1, BN, head_dim))) return rc;
   if ((rc = make_map_rows_heads(&maps.v, v, tk, hkv, v_ld, 1, BN))) return rc;
   FwdParams p;
   p.intervals = intervals;
@@ -418,13 +444,7 @@ extern "C" int ab_attn_fwd(const void* q, const void* k, const void* v, const in
   p.tk = tk;
   p.scale_log2 = scale * kLog2e;
   p.status = status;
-  static std::atomic<unsigned long long> attr_done{0};
-  if (!once_per_device(attr_done, [&] {
-        return cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
-               cudaSuccess;
-      }))
-    return -3;
   dim3 grid((q_total + pm - 1) / pm, hkv);
-  attn_fwd_kernel<<<grid, kThreads, kSmemBytes, reinterpret_cast<cudaStream_t>(stream)>>>(maps, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return head_dim == HD ? launch_fwd<128>(maps, p, grid, s) : launch_fwd<192>(maps, p, grid, s);
 }

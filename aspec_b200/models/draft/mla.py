@@ -5,8 +5,8 @@ from a shared latent (``kv_a_proj_with_mqa -> RMSNorm -> kv_b_proj``) plus one r
 The latent is expanded before attention ("materialised"), so the layout is MHA with
 ``qk_nope + qk_rope`` query/key width and a separate value width
 (reference: aspec/models/draft/dspark.py:176-484, aspec/models/draft/deepseek_eagle.py:89-575,
-aspec/config/draft_attention.py:21-67).  The 192/128 head shape is outside the tcgen05 attention kernels'
-coverage and runs the fp32 dense-mask path.
+aspec/config/draft_attention.py:21-67).  The (192, 128) head shape of the shipped MLA configurations runs the
+interval attention kernels (their 192-wide query/key instantiation); other widths take the bounded fp32 statement.
 """
 from __future__ import annotations
 

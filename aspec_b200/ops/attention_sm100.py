@@ -10,22 +10,34 @@ from aspec_b200 import _native
 from aspec_b200.ops.gemm import status_word
 
 HEAD_DIM = 128
+QK_HEAD_DIMS = (128, 192)          # 192 = materialised-MLA heads (128 "nope" + 64 rotary dims)
 
 
 def supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
-    """The tcgen05 kernels cover bf16, head dim 128 for q/k/v and group size Hq/Hkv in {1,2,4,8,16}."""
+    """The tcgen05 kernels cover bf16, value head dim 128, query/key head dim 128 or 192, and group size Hq/Hkv in
+    {1,2,4,8,16}."""
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
         return False
-    if q.shape[-1] != HEAD_DIM or k.shape[-1] != HEAD_DIM or v.shape[-1] != HEAD_DIM:
+    if q.shape[-1] not in QK_HEAD_DIMS or k.shape[-1] != q.shape[-1] or v.shape[-1] != HEAD_DIM:
         return False
     hq, hkv = q.shape[1], k.shape[1]
     return hq % hkv == 0 and (hq // hkv) in (1, 2, 4, 8, 16)
 
 
+# A dense fp32 score matrix of this many elements (heads x queries x keys) is the most the fallback will allocate.
+DENSE_FALLBACK_MAX_SCORES = 1 << 28
+
+
 def unsupported_shape_fallback(q, k, v, intervals, scale):
-    """Shapes outside the kernel's coverage (e.g. MLA 192/128 heads) run the dense-mask statement in
-    fp32 on the device.  This is a correctness path for small auxiliary configurations only."""
+    """Shapes outside the kernels' coverage (odd head dims of small auxiliary configurations) run the dense-mask
+    statement in fp32 on the device.  It materialises ``heads x queries x keys`` scores, so it refuses problems above
+    ``DENSE_FALLBACK_MAX_SCORES`` elements instead of trying to allocate them."""
     from aspec_b200.ops.attention import interval_attention_reference
+    scores = q.shape[0] * q.shape[1] * k.shape[0]
+    if scores > DENSE_FALLBACK_MAX_SCORES:
+        raise ValueError(
+            f"attention with head dims ({q.shape[-1]}, {v.shape[-1]}) has no kernel and its dense fallback would need "
+            f"{scores} fp32 scores (limit {DENSE_FALLBACK_MAX_SCORES}); supported: bf16, value dim 128, query/key dim 128 or 192")
     return interval_attention_reference(q, k, v, intervals, scale)
 
 
@@ -44,10 +56,10 @@ def forward(q, k, v, intervals, scale, out=None, lse=None) -> Tuple[torch.Tensor
     q = q.contiguous()
     k, k_ld = _rows_view(k)
     v, v_ld = _rows_view(v)
-    out = torch.empty_like(q) if out is None else out
+    out = torch.empty(Q, hq, HEAD_DIM, dtype=q.dtype, device=q.device) if out is None else out
     lse = torch.empty(hq, Q, dtype=torch.float32, device=q.device) if lse is None else lse
-    if not (out.is_contiguous() and lse.is_contiguous() and out.shape == q.shape and lse.shape == (hq, Q)):
-        raise ValueError("out / lse destinations must be contiguous [Q, H, d] / [H, Q]")
+    if not (out.is_contiguous() and lse.is_contiguous() and out.shape == (Q, hq, HEAD_DIM) and lse.shape == (hq, Q)):
+        raise ValueError("out / lse destinations must be contiguous [Q, H, 128] / [H, Q]")
     st = status_word(q.device)
     rc = _native.kernels().ab_attn_fwd(
         _c.c_void_p(q.data_ptr()), _c.c_void_p(k.data_ptr()), _c.c_void_p(v.data_ptr()),
@@ -69,7 +81,7 @@ def backward(q, k, v, intervals, out, lse, dout, scale, dq=None):
     if not (dq.is_contiguous() and dq.shape == q.shape):
         raise ValueError("dq destination must be contiguous [Q, H, d]")
     dk = torch.empty(tk, hkv, d, dtype=q.dtype, device=q.device)
-    dv = torch.empty(tk, hkv, d, dtype=q.dtype, device=q.device)
+    dv = torch.empty(tk, hkv, HEAD_DIM, dtype=q.dtype, device=q.device)
     delta = torch.empty(hq, Q, dtype=torch.float32, device=q.device)
     pm = 128 // (hq // hkv)
     ranges = torch.empty((Q + pm - 1) // pm, 4, dtype=torch.int32, device=q.device)

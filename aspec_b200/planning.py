@@ -142,10 +142,17 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
     head_dim = draft.get("head_dim") or draft["hidden_size"] // draft["num_attention_heads"]
     mla = draft.get("attention_mode") == "mla" or draft.get("model_type") in ("k3_dspark", "deepseek_v3")
     caps.append(CapabilityDecision("gemm", "tcgen05_tma_persistent", "bf16 weights, sm_100a"))
+    if mla:
+        qk_dim = int(draft.get("qk_nope_head_dim") or 0) + int(draft.get("qk_rope_head_dim") or 0)
+        v_dim = int(draft.get("v_head_dim") or 0)
+    else:
+        qk_dim = v_dim = int(head_dim)
+    kernel_heads = v_dim == 128 and qk_dim in (128, 192)
     caps.append(CapabilityDecision(
-        "attention", "dense_mask_fp32" if (mla or head_dim != 128) else "tcgen05_interval_flash",
-        "head dim 128 GQA uses the TMEM flash kernels" if not (mla or head_dim != 128)
-        else "materialised MLA / non-128 head dim runs the fp32 dense-mask path"))
+        "attention", "tcgen05_interval_flash" if kernel_heads else "dense_mask_fp32",
+        f"query/key head dim {qk_dim}, value head dim {v_dim}: the TMEM flash kernels cover (128, 128) and the "
+        f"materialised-MLA shape (192, 128)" if kernel_heads else
+        f"head dims ({qk_dim}, {v_dim}) have no kernel: fp32 dense-mask statement, refused above a bounded score size"))
     caps.append(CapabilityDecision("vocab_head", "fused_rowstats_gemm+streaming_loss", "logits stay bf16; no fp32 [rows, V]"))
     # a trainer holds the slots of all micro-batches of an update until its optimizer step commits, and the next
     # update's rows are dispatched meanwhile: fewer slots than that deadlock the producer against the consumer
