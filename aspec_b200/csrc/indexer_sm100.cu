@@ -8,7 +8,8 @@
 // reduction, and the 128 lanes write 128 consecutive keys of a score row (coalesced).  [n*H, T] logits never exist.
 //   warp 0      TMA producer: the tile's 128 (query, head) rows once, then key tiles through a 3-stage ring
 //   warp 1      tcgen05.mma issuer, two 128-column accumulators so that the epilogue of tile j runs under tile j+1
-//   warps 2..5  epilogue
+//   warps 2..9  epilogue: two warpgroups, each takes half of the accumulator's columns (whole queries when H <= 64), so
+//               two warps per scheduler hide each other's tensor-memory load latency
 //
 // ab_topk_select: one CTA per score row; an 8-bit-per-pass radix select over the order-preserving integer image of
 // the floats finds the k-th largest value, then one ordered pass writes the selected key indices in ascending order
@@ -23,7 +24,7 @@ namespace idx {
 static constexpr int BM = 128;   // keys per tile
 static constexpr int BN = 128;   // (query, head) pairs per tile
 static constexpr int kStages = 3;
-static constexpr int kThreads = 192;
+static constexpr int kThreads = 320;   // TMA warp, MMA warp, two epilogue warpgroups
 
 struct alignas(64) IdxMaps {
   CUtensorMap q, k;
@@ -82,6 +83,9 @@ template <int H>
 __global__ void __launch_bounds__(kThreads, 1)
 indexer_scores_kernel(const __grid_constant__ IdxMaps maps, const IdxParams p) {
   constexpr int NQ = BN / H;   // queries per tile
+  constexpr int kSplit = H <= 64 ? 2 : 1;      // epilogue warpgroups that share an accumulator
+  constexpr int kCols = BN / kSplit;           // accumulator columns per epilogue thread
+  constexpr int NQL = kCols / H;               // queries per epilogue thread
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
@@ -107,7 +111,7 @@ indexer_scores_kernel(const __grid_constant__ IdxMaps maps, const IdxParams p) {
     *abort_word = 0;
     mbar_init(q_full, 1);
     for (int s = 0; s < kStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4 * kSplit); }
     fence_barrier_init();
     tma_prefetch_desc(&maps.q);
     tma_prefetch_desc(&maps.k);
@@ -177,25 +181,33 @@ indexer_scores_kernel(const __grid_constant__ IdxMaps maps, const IdxParams p) {
         tc_commit(&acc_full[acc]);
       }
     }
-  } else {
+  } else if (((warp - 2) >> 2) < kSplit) {
     const int qd = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int cbeg = half * kCols;
     const uint32_t lane_base = static_cast<uint32_t>(qd * 32) << 16;
     const int r = qd * 32 + lane;            // key row of the tile
     for (int j = 0; j < n_tiles; ++j) {
       const int acc = j & 1;
       if (!mbar_wait(&acc_full[acc], (j >> 1) & 1, abort_word)) break;
       tc_fence_after();
-      float sum[NQ];
+      float sum[NQL];
 #pragma unroll
-      for (int i = 0; i < NQ; ++i) sum[i] = 0.f;
+      for (int i = 0; i < NQL; ++i) sum[i] = 0.f;
 #pragma unroll
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = 0; c < kCols; c += 32) {
         uint32_t s[32];
-        tmem_ld_32x32(tmem + lane_base + acc * BN + c, s);
+        tmem_ld_32x32(tmem + lane_base + acc * BN + cbeg + c, s);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          sum[(c + i) / H] = fmaf(fmaxf(__uint_as_float(s[i]), 0.f), sW[c + i], sum[(c + i) / H]);
+        for (int i = 0; i < 32; i += 4) {
+          const float4 w4 = *reinterpret_cast<const float4*>(sW + cbeg + c + i);   // same address in every lane: broadcast
+          float& dst = sum[(c + i) / H];
+          dst = fmaf(fmaxf(__uint_as_float(s[i + 0]), 0.f), w4.x, dst);
+          dst = fmaf(fmaxf(__uint_as_float(s[i + 1]), 0.f), w4.y, dst);
+          dst = fmaf(fmaxf(__uint_as_float(s[i + 2]), 0.f), w4.z, dst);
+          dst = fmaf(fmaxf(__uint_as_float(s[i + 3]), 0.f), w4.w, dst);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -203,10 +215,11 @@ indexer_scores_kernel(const __grid_constant__ IdxMaps maps, const IdxParams p) {
       const int key = (t0 + j) * BM + r;
       if (key < p.T) {
 #pragma unroll
-        for (int i = 0; i < NQ; ++i) {
-          const int q = q0 + i;
+        for (int i = 0; i < NQL; ++i) {
+          const int ql = half * NQL + i;
+          const int q = q0 + ql;
           if (q < p.n) {
-            const bool vis = key >= sLo[i] && key < sHi[i];
+            const bool vis = key >= sLo[ql] && key < sHi[ql];
             p.out[(size_t)q * p.ld_out + key] = vis ? sum[i] : -INFINITY;
           }
         }

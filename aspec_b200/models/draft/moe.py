@@ -37,6 +37,40 @@ class ExpertBank(nn.Module):
         self.down_proj = nn.Parameter(torch.empty(self.local_experts, hidden_size, intermediate_size))
         nn.init.normal_(self.gate_up_proj, std=0.02)
         nn.init.normal_(self.down_proj, std=0.02)
+        self.ep_group = None          # process group of the ranks that together hold all experts
+        self.fused_ep = None          # parallel.expert_parallel.FusedExpertParallel when peer memory is set up
+        self._register_state_dict_hook(ExpertBank._full_bank_state)
+
+    # -- expert parallelism: each rank keeps ``E / ep`` experts; state dicts always show the whole bank ------------
+    @torch.no_grad()
+    def shard_(self, ep_rank: int, ep_size: int, group=None) -> "ExpertBank":
+        """Keep only this rank's experts of a bank that was built whole (every rank built it from the same seed or
+        loaded the same weights).  Checkpoints stay topology-independent: ``state_dict`` gathers the bank over
+        ``group`` and ``load_state_dict`` slices a whole bank down to the local experts."""
+        if self.ep_size != 1:
+            raise ValueError("the bank is already sharded")
+        if self.num_experts % ep_size:
+            raise ValueError("num_experts must be divisible by the expert-parallel size")
+        local = self.num_experts // ep_size
+        first = ep_rank * local
+        for name in ("gate_up_proj", "down_proj"):
+            full = getattr(self, name)
+            part = nn.Parameter(full.detach()[first:first + local].clone(), requires_grad=full.requires_grad)
+            part.expert_parallel = True          # the optimizer reduces these over expert replicas only
+            setattr(self, name, part)
+        self.ep_rank, self.ep_size, self.local_experts, self.first_expert, self.ep_group = ep_rank, ep_size, local, first, group
+        return self
+
+    @staticmethod
+    def _full_bank_state(module, state_dict, prefix, local_metadata):
+        if module.ep_size > 1 and module.ep_group is not None:
+            import torch.distributed as dist
+            for name in ("gate_up_proj", "down_proj"):
+                part = state_dict[prefix + name]
+                pieces = [torch.empty_like(part) for _ in range(module.ep_size)]
+                dist.all_gather(pieces, part.contiguous(), group=module.ep_group)
+                state_dict[prefix + name] = torch.cat(pieces, 0)
+        return state_dict
 
     def forward(self, x_sorted: torch.Tensor, counts: List[int]) -> torch.Tensor:
         """``x_sorted [N, D]`` grouped by local expert, ``counts[e]`` rows each -> ``[N, D]``."""
@@ -71,6 +105,12 @@ class ExpertBank(nn.Module):
                 state_dict.pop(k)
             state_dict[f"{prefix}gate_up_proj"] = torch.stack(gu)
             state_dict[f"{prefix}down_proj"] = torch.stack(dn)
+        if self.ep_size > 1:
+            # a whole bank (any checkpoint) is cut down to this rank's experts
+            for name in ("gate_up_proj", "down_proj"):
+                t = state_dict.get(prefix + name)
+                if t is not None and t.shape[0] == self.num_experts:
+                    state_dict[prefix + name] = t[self.first_expert:self.first_expert + self.local_experts]
         super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
 
@@ -84,8 +124,14 @@ def route_and_run(bank: ExpertBank, hidden: torch.Tensor, selected: torch.Tensor
     sorted_expert = flat_expert[order]
     x_sorted = hidden[token_of]
     if bank.ep_size > 1:
-        from aspec_b200.parallel.expert_parallel import dispatch_combine
-        y_sorted = dispatch_combine(bank, x_sorted, sorted_expert, ep_group)
+        group = ep_group if ep_group is not None else bank.ep_group
+        if bank.fused_ep is not None and x_sorted.is_cuda:
+            # dispatch and combine are the grouped expert GEMMs' own loads and stores over peer memory
+            from aspec_b200.parallel.expert_parallel import fused_dispatch_combine
+            y_sorted = fused_dispatch_combine(bank.fused_ep, bank, x_sorted, sorted_expert, group)
+        else:
+            from aspec_b200.parallel.expert_parallel import dispatch_combine
+            y_sorted = dispatch_combine(bank, x_sorted, sorted_expert, group)
     else:
         counts = torch.bincount(sorted_expert, minlength=bank.num_experts).tolist()
         y_sorted = bank(x_sorted, counts)

@@ -131,6 +131,8 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
         raise ValueError("expert_parallel_size > 1 requires a MoE draft")
     if ep > 1 and ffn.get("num_experts", 0) % ep:
         raise ValueError("num_experts must be divisible by expert_parallel_size")
+    if ep > 1 and str(flat["fsdp_strategy"]).upper() == "FULL_SHARD":
+        raise ValueError("expert parallelism shards the experts itself: use training.fsdp_strategy=REPLICATE with it")
     if vp > 1 and draft["vocab_size"] % vp:
         raise ValueError("vocab_size must be divisible by vocab_parallel_size")
     if ep > 1 and world % ep or vp > 1 and world % vp:
@@ -170,7 +172,10 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
         caps.append(CapabilityDecision("context_parallel", f"ulysses{u}xring{r}" if u * r > 1 else f"direct_cp{cp}",
                                        f"context sharded contiguously per document, alignment {align}"))
     if ep > 1:
-        caps.append(CapabilityDecision("expert_parallel", f"ep{ep}", "all-to-all dispatch/combine around grouped expert GEMMs"))
+        caps.append(CapabilityDecision("expert_parallel", f"ep{ep}",
+                                       "each rank of a group keeps E / ep experts of every MoE layer; dispatch / combine run "
+                                       "inside the grouped expert GEMMs over peer memory; expert gradients are reduced over "
+                                       "replicas only; checkpoints hold whole banks"))
     if vp > 1:
         caps.append(CapabilityDecision("vocab_parallel", f"vp{vp}", "head rows sharded; log-sum-exp merged over peer memory"))
     thd = thd_contract(policy) if algorithm != "mtp" else {}

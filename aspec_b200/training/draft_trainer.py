@@ -60,6 +60,7 @@ class DraftTrainer:
                                            warmup_ratio=warmup_ratio, decay_style=decay_style, min_lr=min_lr,
                                            betas=betas, wsd_decay_steps=wsd_decay_steps, wsd_decay_style=wsd_decay_style)
         self.global_step = 0
+        self.expert_replica_group = None     # set with expert parallelism: ranks that hold the same experts
         self._pool: Dict[str, List[torch.Tensor]] = {}
         self._last: Dict[str, torch.Tensor] = {}
         self.post_step_hooks = []
@@ -157,7 +158,11 @@ class DraftTrainer:
                 pooled[k] = flat[off:off + m].view_as(pooled[k])
                 off += m
             if not self.sharded:            # the sharded optimizer reduces its own shard from the peers' buffers
-                dist.all_reduce(opt.flat_grad, group=self.dp_group)
+                dense = getattr(opt, "dense_numel", opt.flat_grad.numel())
+                dist.all_reduce(opt.flat_grad[:dense], group=self.dp_group)
+                if dense < opt.flat_grad.numel() and self.expert_replica_group is not None:
+                    # an expert's gradient already holds every token routed to it; only its replicas are summed
+                    dist.all_reduce(opt.flat_grad[dense:], group=self.expert_replica_group)
         for hook in self.pre_step_hooks:     # debug dumps read the accumulated (not yet scaled) gradients here
             hook(self)
         den = pooled["loss"][1]

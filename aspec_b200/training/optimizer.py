@@ -66,10 +66,15 @@ class BF16Optimizer(_AppliedSteps):
                  norm_group: Optional[dist.ProcessGroup] = None, shard_group: Optional[dist.ProcessGroup] = None):
         self.model = model
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        # expert-parallel shards go last: the flat buffers are then a replicated region followed by a region that
+        # differs from rank to rank, and each is reduced over its own set of ranks
+        named.sort(key=lambda item: bool(getattr(item[1], "expert_parallel", False)))
         self.param_names = [n for n, _ in named]
         self.model_params = [p for _, p in named]
         if not self.model_params:
             raise ValueError("BF16Optimizer needs at least one trainable parameter")
+        self.expert_group = None        # ranks that together hold all experts: their expert norms add up
+        self.expert_names: Dict[str, tuple] = {}   # name -> (ep_rank, ep_size): state dicts carry whole banks
         self.max_grad_norm = float(max_grad_norm)
         self.weight_decay, self.betas, self.eps = float(weight_decay), betas, float(eps)
         self.lr = float(lr)
@@ -84,6 +89,9 @@ class BF16Optimizer(_AppliedSteps):
             self.offsets.append(off)
             off += p.numel()
         self.numel = _align(off)
+        # first element of the expert-parallel region (== numel when there is none)
+        self.dense_numel = next((o for p, o in zip(self.model_params, self.offsets) if getattr(p, "expert_parallel", False)),
+                                self.numel)
         self.flat_param = torch.zeros(self.numel, dtype=dtype, device=dev)
         self.flat_master = torch.zeros(self.numel, dtype=torch.float32, device=dev)
         self.flat_grad = torch.zeros(self.numel, dtype=torch.float32, device=dev)
@@ -135,12 +143,14 @@ class BF16Optimizer(_AppliedSteps):
         self.fold_autograd_grads()
         ctrl = self._ctrl
         ctrl.zero_()
-        if self.use_kernel:
-            from aspec_b200.ops import elementwise_sm100 as E
-            E.sumsq(self.flat_grad, ctrl)
-        else:
-            ctrl[0] = self.flat_grad.double().pow(2).sum().float()
-            ctrl[1] = (~torch.isfinite(self.flat_grad)).any().float()
+        self._sumsq(self.flat_grad[: self.dense_numel], ctrl)
+        if self.dense_numel < self.numel:
+            # the expert region differs per rank of the expert-parallel group: its squares add up over that group
+            part = torch.zeros_like(ctrl)
+            self._sumsq(self.flat_grad[self.dense_numel:], part)
+            if self.expert_group is not None and dist.get_world_size(self.expert_group) > 1:
+                dist.all_reduce(part[0:2], group=self.expert_group)
+            ctrl[0:2] += part[0:2]
         if self.norm_group is not None and dist.get_world_size(self.norm_group) > 1:
             dist.all_reduce(ctrl[0:1], group=self.norm_group)
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
@@ -165,6 +175,38 @@ class BF16Optimizer(_AppliedSteps):
         self._grad_scale = torch.ones_like(self._grad_scale)
         self.scheduler.step()
         return grad_norm.clone()
+
+    def _sumsq(self, grad: torch.Tensor, ctrl: torch.Tensor) -> None:
+        """``ctrl[0] += sum(grad^2)``, ``ctrl[1] += non-finite``."""
+        if grad.numel() == 0:
+            return
+        if self.use_kernel:
+            from aspec_b200.ops import elementwise_sm100 as E
+            E.sumsq(grad, ctrl)
+        else:
+            ctrl[0] += grad.double().pow(2).sum().float()
+            ctrl[1] += (~torch.isfinite(grad)).any().float()
+
+    def set_expert_parallel(self, group, ep_rank: int, ep_size: int) -> None:
+        """Declare the expert-parallel layout of the parameters marked ``expert_parallel``."""
+        self.expert_group = group
+        self.expert_names = {n: (ep_rank, ep_size) for n, p in zip(self.param_names, self.model_params)
+                             if getattr(p, "expert_parallel", False)}
+
+    def _whole_bank(self, name: str, local: torch.Tensor) -> torch.Tensor:
+        if name not in self.expert_names or self.expert_group is None:
+            return local
+        _, ep = self.expert_names[name]
+        pieces = [torch.empty_like(local) for _ in range(ep)]
+        dist.all_gather(pieces, local.contiguous(), group=self.expert_group)
+        return torch.cat(pieces, 0)
+
+    def _local_bank(self, name: str, saved: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+        if name in self.expert_names and saved.shape[0] != like.shape[0]:
+            rank, ep = self.expert_names[name]
+            n = saved.shape[0] // ep
+            return saved[rank * n:(rank + 1) * n]
+        return saved
 
     def _step_reference(self, ctrl, b1, b2) -> None:
         bad = bool(ctrl[1] > 0) or not bool(torch.isfinite(ctrl[0]))
@@ -197,8 +239,9 @@ class BF16Optimizer(_AppliedSteps):
 
     def state_dict(self) -> dict:
         """AdamW state and fp32 masters keyed by parameter name."""
-        return {"step": self.step_count, "master": self._views(self.flat_master),
-                "exp_avg": self._views(self.exp_avg), "exp_avg_sq": self._views(self.exp_avg_sq),
+        whole = lambda flat: {n: self._whole_bank(n, t) for n, t in self._views(flat).items()}
+        return {"step": self.step_count, "master": whole(self.flat_master),
+                "exp_avg": whole(self.exp_avg), "exp_avg_sq": whole(self.exp_avg_sq),
                 "hyper": {"lr": self.lr, "betas": list(self.betas), "eps": self.eps,
                           "weight_decay": self.weight_decay, "max_grad_norm": self.max_grad_norm}}
 
@@ -212,7 +255,7 @@ class BF16Optimizer(_AppliedSteps):
                 if missing:
                     raise KeyError(f"optimizer state lacks {sorted(missing)[:3]}...")
                 for name, dst in views.items():
-                    dst.copy_(state[key][name].to(dst))
+                    dst.copy_(self._local_bank(name, state[key][name], dst).to(dst))
             self.flat_param.copy_(self.flat_master)
 
     def get_learning_rate(self) -> float:

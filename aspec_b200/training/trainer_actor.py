@@ -50,6 +50,22 @@ class TrainerActor:
         if self.args.get("initial_draft_model_path") and not self.args.get("load_path"):
             self._load_initial_weights(str(self.args["initial_draft_model_path"]))
         cfg = self.draft_config
+        self.expert_parallel = None
+        ep = max(int(self.args.get("expert_parallel_size", 1) or 1), 1)
+        if ep > 1:
+            # ranks [g * ep, (g + 1) * ep) hold all experts between them; ranks r, r + ep, ... hold replicas
+            if world < ep or world % ep:
+                raise ValueError("expert_parallel_size must divide the Draft world size")
+            if str(self.args.get("fsdp_strategy", "REPLICATE")).upper() == "FULL_SHARD":
+                raise ValueError("expert parallelism shards the experts itself; use fsdp_strategy=REPLICATE with it")
+            from aspec_b200.parallel.expert_wiring import apply_expert_parallel, attach_fused_exchange, build_groups
+            group, replicas = build_groups(rank, world, ep)
+            self.expert_parallel = apply_expert_parallel(self.model.draft_model, rank % ep, ep, group, replicas)
+            if self.cuda:
+                top_k = int(getattr(cfg, "num_experts_per_tok", 1) or 1)
+                rows = (int(getattr(self.model, "num_anchors", 0) or 0) * int(getattr(self.model, "block_size", 1) or 1)
+                        or int(self.args["max_seq_length"])) * top_k
+                attach_fused_exchange(self.expert_parallel, rows, int(cfg.hidden_size), self.device)
         self.cp_size = max(int(self.args.get("draft_context_parallel_size", 1) or 1), 1)
         if self.cp_size > 1 and hasattr(self.model, "context_parallel") and world > 1:
             # ranks [g * cp, (g + 1) * cp) share every row: each projects its context shard and carries its own blocks
@@ -198,6 +214,10 @@ class TrainerActor:
                                     warmup_ratio=a.get("warmup_ratio", 0.015), decay_style=a.get("lr_decay_style", "cosine"),
                                     accumulation=int(a.get("draft_accumulation_steps", 1)), device=self.device,
                                     fsdp_strategy=str(a.get("fsdp_strategy", "REPLICATE")))
+        if self.expert_parallel is not None:
+            plan = self.expert_parallel
+            self.trainer.optimizer.set_expert_parallel(plan.group, plan.ep_rank, plan.ep_size)
+            self.trainer.expert_replica_group = plan.replica_group
 
     # -- data ---------------------------------------------------------------------------------------
     def _batch(self, sample: TrainSample) -> dict:

@@ -5,7 +5,12 @@ that ``ncu --set full --clock-control none -k regex:<kernel> -c 1..3`` finishes 
 ``--clock-control none`` matters on shared GPUs: without it the profiler locks the clocks and a killed capture can
 leave them locked for the next user.  Capture one kernel on these small cases only, after the same command line has
 run to completion without the profiler.  Cases: ``gemm``, ``gemm_head``,
-``attn_fwd``, ``attn_bwd``, ``vocab_loss``, ``rmsnorm``, ``grouped_experts``.
+``attn_fwd``, ``attn_bwd``, ``vocab_loss``, ``rmsnorm``, ``grouped_experts``, ``sel_attn`` (selected-key attention
+forward + backward), ``indexer`` (scores + top-k), and the compute+collective kernels with every "peer" buffer placed on
+this same GPU - ``gemm_mirror`` (GEMM whose epilogue also stores the tile into two more destinations), ``gemm_scatter``
+(column-scatter epilogue of the Ulysses projection), ``shard_step`` (peer-sum of gradient shards + sum of squares, then
+AdamW with the bf16 weights stored into every replica), ``peer_lse`` (log-sum-exp merge over peers' statistics).  On one
+GPU these captures show the kernels' DRAM and tensor-pipe behaviour; NVLink traffic is by construction zero here.
 """
 from __future__ import annotations
 
@@ -88,6 +93,72 @@ def case_rmsnorm():
     x, w = _bf16(32768, 4096, scale=1.0), _bf16(4096, scale=1.0)
     for _ in range(3):
         E.rmsnorm_fwd(x, w, 1e-6)
+
+
+def case_sel_attn():
+    from aspec_b200.ops import sparse_attention as SA
+    n, T, L, hq, hkv = 1024, 65536, 1024 + 7, 32, 8
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (_bf16(n, hq, 128, scale=1.0).requires_grad_(), _bf16(T, hkv, 128, scale=1.0).requires_grad_(),
+               _bf16(T, hkv, 128, scale=1.0).requires_grad_())
+    sel = torch.randint(0, T, (n, L), generator=g).to(torch.int32).cuda()
+    for _ in range(2):
+        out, _ = SA.selected_attention(q, k, v, sel, 128 ** -0.5)
+        out.backward(torch.ones_like(out))
+
+
+def case_indexer():
+    from aspec_b200.ops import sparse_attention as SA
+    n, T, H, d = 256, 16384, 64, 128
+    qi, ki = _bf16(n, H, d, scale=1.0), _bf16(T, d, scale=1.0)
+    w = torch.rand(n, H, device="cuda") * 0.1
+    lo = torch.zeros(n, dtype=torch.int32, device="cuda")
+    hi = torch.randint(T // 2, T, (n,), device="cuda").to(torch.int32)
+    for _ in range(2):
+        s = SA.indexer_scores(qi, ki, w, lo, hi)
+        SA.topk_select(s, lo, hi, 1024)
+
+
+def case_gemm_mirror():
+    from aspec_b200.ops import gemm as G
+    a, b = _bf16(8192, 4096), _bf16(4096, 4096)
+    out = torch.empty(8192, 4096, device="cuda", dtype=torch.bfloat16)
+    mirrors = [torch.empty_like(out), torch.empty_like(out)]
+    for _ in range(3):
+        G.gemm(a, b, out=out, mirrors=mirrors)
+
+
+def case_gemm_scatter():
+    from aspec_b200.ops import gemm as G
+    a, b = _bf16(8192, 4096), _bf16(6144, 4096)
+    dests = [torch.empty(8192, 6144 // 4, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+    for _ in range(3):
+        G.gemm(a, b, mirrors=dests, scatter_cols=6144 // 4)
+
+
+def case_shard_step():
+    from aspec_b200.ops import comm
+    n, peers = 64 << 20, 4
+    grads = [torch.randn(n, device="cuda") for _ in range(peers)]
+    params = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(peers)]
+    shard, master, m, v = (torch.zeros(n, device="cuda") for _ in range(4))
+    ctrl = torch.zeros(8, device="cuda")
+    for _ in range(2):
+        ctrl.zero_()
+        comm.shard_reduce_sumsq(grads, 0, shard, ctrl)
+        ctrl[2] = 1.0
+        ctrl[4] = 1.0
+        comm.shard_adamw_scatter(master, shard, m, v, params, 0, ctrl, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0,
+                                 step=None, max_norm=1.0)
+
+
+def case_peer_lse():
+    from aspec_b200.ops import comm
+    n, peers = 32 << 20, 8
+    parts = [torch.randn(n, device="cuda") for _ in range(peers)]
+    out = torch.empty(n, device="cuda")
+    for _ in range(3):
+        comm.peer_lse_merge(parts, out)
 
 
 CASES = {n[5:]: f for n, f in globals().items() if n.startswith("case_")}
