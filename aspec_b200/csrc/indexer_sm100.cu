@@ -6,7 +6,7 @@
 // lanes), the (query, head) pairs of a tile are the N dimension (columns).  The epilogue thread of a key lane then
 // owns every head of a query in its own registers: ReLU, the per-head weight and the head sum need no cross-thread
 // reduction, and the 128 lanes write 128 consecutive keys of a score row (coalesced).  [n*H, T] logits never exist.
-//   warp 0      TMA producer: the tile's 128 (query, head) rows once, then key tiles through a 3-stage ring
+//   warp 0      TMA producer: the tile's 128 (query, head) rows once, then key tiles through a 5-stage ring
 //   warp 1      tcgen05.mma issuer, two 128-column accumulators so that the epilogue of tile j runs under tile j+1
 //   warps 2..9  epilogue: two warpgroups, each takes half of the accumulator's columns (whole queries when H <= 64), so
 //               two warps per scheduler hide each other's tensor-memory load latency
@@ -23,7 +23,7 @@ namespace idx {
 
 static constexpr int BM = 128;   // keys per tile
 static constexpr int BN = 128;   // (query, head) pairs per tile
-static constexpr int kStages = 3;
+static constexpr int kStages = 5;   // 160 KB of key tiles in flight per SM: enough to cover the L2 round trip at one tile per 512 cycles
 static constexpr int kThreads = 320;   // TMA warp, MMA warp, two epilogue warpgroups
 
 struct alignas(64) IdxMaps {
@@ -79,11 +79,10 @@ static constexpr int kTileBytes = 128 * 128 * 2;   // 32 KB at d = 128 (two 64-c
 static constexpr int kChunkBytes = 128 * 128;
 static constexpr int kSmemBytes = (1 + kStages) * kTileBytes + 1024 /*w, lo, hi*/ + 256 /*barriers*/ + 1024;
 
-template <int H>
+template <int H, int kSplit>     // kSplit: epilogue warpgroups that share an accumulator (2 needs H <= 64)
 __global__ void __launch_bounds__(kThreads, 1)
 indexer_scores_kernel(const __grid_constant__ IdxMaps maps, const IdxParams p) {
   constexpr int NQ = BN / H;   // queries per tile
-  constexpr int kSplit = H <= 64 ? 2 : 1;      // epilogue warpgroups that share an accumulator
   constexpr int kCols = BN / kSplit;           // accumulator columns per epilogue thread
   constexpr int NQL = kCols / H;               // queries per epilogue thread
   extern __shared__ uint8_t smem_raw[];
@@ -191,24 +190,31 @@ indexer_scores_kernel(const __grid_constant__ IdxMaps maps, const IdxParams p) {
       const int acc = j & 1;
       if (!mbar_wait(&acc_full[acc], (j >> 1) & 1, abort_word)) break;
       tc_fence_after();
-      float sum[NQL];
+      // four independent partial sums per query: a single chain of H dependent FMAs per tile would take as long as
+      // the tile's MMAs
+      float part[NQL][4];
 #pragma unroll
-      for (int i = 0; i < NQL; ++i) sum[i] = 0.f;
+      for (int i = 0; i < NQL; ++i) part[i][0] = part[i][1] = part[i][2] = part[i][3] = 0.f;
+      // all tensor-memory loads of this thread's columns are issued before the one wait: their latencies overlap
+      uint32_t s[kCols / 32][32];
+#pragma unroll
+      for (int c = 0; c < kCols / 32; ++c) tmem_ld_32x32(tmem + lane_base + acc * BN + cbeg + c * 32, s[c]);
+      tmem_ld_wait();
 #pragma unroll
       for (int c = 0; c < kCols; c += 32) {
-        uint32_t s[32];
-        tmem_ld_32x32(tmem + lane_base + acc * BN + cbeg + c, s);
-        tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 w4 = *reinterpret_cast<const float4*>(sW + cbeg + c + i);   // same address in every lane: broadcast
-          float& dst = sum[(c + i) / H];
-          dst = fmaf(fmaxf(__uint_as_float(s[i + 0]), 0.f), w4.x, dst);
-          dst = fmaf(fmaxf(__uint_as_float(s[i + 1]), 0.f), w4.y, dst);
-          dst = fmaf(fmaxf(__uint_as_float(s[i + 2]), 0.f), w4.z, dst);
-          dst = fmaf(fmaxf(__uint_as_float(s[i + 3]), 0.f), w4.w, dst);
+          float* dst = part[(c + i) / H];
+          dst[0] = fmaf(fmaxf(__uint_as_float(s[c / 32][i + 0]), 0.f), w4.x, dst[0]);
+          dst[1] = fmaf(fmaxf(__uint_as_float(s[c / 32][i + 1]), 0.f), w4.y, dst[1]);
+          dst[2] = fmaf(fmaxf(__uint_as_float(s[c / 32][i + 2]), 0.f), w4.z, dst[2]);
+          dst[3] = fmaf(fmaxf(__uint_as_float(s[c / 32][i + 3]), 0.f), w4.w, dst[3]);
         }
       }
+      float sum[NQL];
+#pragma unroll
+      for (int i = 0; i < NQL; ++i) sum[i] = (part[i][0] + part[i][1]) + (part[i][2] + part[i][3]);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -235,18 +241,26 @@ indexer_scores_kernel(const __grid_constant__ IdxMaps maps, const IdxParams p) {
   if (warp == 1) { __syncwarp(); tmem_dealloc(tmem, 256); }
 }
 
-template <int H>
-static int launch_scores(const IdxMaps& maps, const IdxParams& p, cudaStream_t stream) {
+template <int H, int SPLIT>
+static int launch_scores_v(const IdxMaps& maps, const IdxParams& p, cudaStream_t stream) {
   static std::atomic<unsigned long long> attr_done{0};
   if (!once_per_device(attr_done, [&] {
-        return cudaFuncSetAttribute(indexer_scores_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) ==
-               cudaSuccess;
+        return cudaFuncSetAttribute(indexer_scores_kernel<H, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes) == cudaSuccess;
       }))
     return -3;
   const int nq = BN / H;
   const int q_tiles = (p.n + nq - 1) / nq;
-  indexer_scores_kernel<H><<<dim3(q_tiles, p.key_splits), kThreads, kSmemBytes, stream>>>(maps, p);
+  indexer_scores_kernel<H, SPLIT><<<dim3(q_tiles, p.key_splits), kThreads, kSmemBytes, stream>>>(maps, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+// epilogue_groups: 0 = default (two warpgroups when H <= 64), 1 or 2 = forced (benchmarks)
+template <int H>
+static int launch_scores(const IdxMaps& maps, const IdxParams& p, cudaStream_t stream, int epilogue_groups) {
+  if constexpr (H <= 64) {
+    if (epilogue_groups != 1) return launch_scores_v<H, 2>(maps, p, stream);
+  }
+  return launch_scores_v<H, 1>(maps, p, stream);
 }
 
 // ------------------------------------------------------------------------------------ top-k ----
@@ -339,7 +353,8 @@ topk_select_kernel(const float* __restrict__ scores, long long ld, const int* __
 // (-inf outside the row's own [lo, hi)); other entries are left untouched, so a caller that reads whole rows
 // pre-fills `out` with -inf.  H in {8, 16, 32, 64, 128}, d in {64, 128}.
 extern "C" int ab_indexer_scores(const void* qi, const void* ki, const float* w, const int* lo, const int* hi, float* out,
-                                 long long ld_out, int n, int T, int H, int d, long long k_ld, int* status, void* stream) {
+                                 long long ld_out, int n, int T, int H, int d, long long k_ld, int epilogue_groups,
+                                 int* status, void* stream) {
   using namespace ab;
   using namespace ab::idx;
   if (d != 64 && d != 128) return -10;
@@ -365,11 +380,11 @@ extern "C" int ab_indexer_scores(const void* qi, const void* ki, const float* w,
   p.key_splits = splits;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (H) {
-    case 8: return launch_scores<8>(maps, p, s);
-    case 16: return launch_scores<16>(maps, p, s);
-    case 32: return launch_scores<32>(maps, p, s);
-    case 64: return launch_scores<64>(maps, p, s);
-    case 128: return launch_scores<128>(maps, p, s);
+    case 8: return launch_scores<8>(maps, p, s, epilogue_groups);
+    case 16: return launch_scores<16>(maps, p, s, epilogue_groups);
+    case 32: return launch_scores<32>(maps, p, s, epilogue_groups);
+    case 64: return launch_scores<64>(maps, p, s, epilogue_groups);
+    case 128: return launch_scores<128>(maps, p, s, epilogue_groups);
     default: return -11;
   }
 }

@@ -99,44 +99,105 @@ def _p(t):
     return _c.c_void_p(t.data_ptr() if t is not None else 0)
 
 
+def selected_attention_backward_reference(q, keys, values, sel, out, lse, dout, scale, chunk_rows: int = 256):
+    """fp32 statement of the backward pass given the forward's ``out`` and ``lse [Hq, n]``.  ``out`` / ``lse`` may be
+    the results of a LARGER softmax (partials merged over shards): probabilities are then ``exp(s - lse)`` of that
+    softmax and the gradients are this key set's exact share.  Returns ``(dq, dk, dv)`` in fp32."""
+    n, hq, d = q.shape
+    hkv = keys.shape[1]
+    g = hq // hkv
+    dq = torch.zeros(n, hq, d, dtype=torch.float32, device=q.device)
+    dk = torch.zeros(keys.shape, dtype=torch.float32, device=q.device)
+    dv = torch.zeros(values.shape, dtype=torch.float32, device=q.device)
+    for lo in range(0, n, chunk_rows):
+        sl = slice(lo, min(lo + chunk_rows, n))
+        s_idx = sel[sl].long()
+        ok = (s_idx >= 0) & (s_idx < keys.shape[0])
+        safe = s_idx.clamp(0, max(keys.shape[0] - 1, 0))
+        kk = keys[safe].float().repeat_interleave(g, 2)                  # [c, L, Hq, d]
+        vv = values[safe].float().repeat_interleave(g, 2)
+        qf, do = q[sl].float(), dout[sl].float()
+        sc = torch.einsum("nhd,nlhd->nhl", qf, kk) * scale
+        l = lse[:, sl].t().float()
+        has = torch.isfinite(l)
+        p = torch.exp(sc - torch.where(has, l, torch.zeros_like(l))[..., None])
+        p = torch.where(ok[:, None] & has[..., None], p, torch.zeros_like(p))
+        delta = (out[sl].float() * do).sum(-1)                           # [c, Hq]
+        dp = torch.einsum("nhd,nlhd->nhl", do, vv)
+        ds = p * (dp - delta[..., None]) * scale
+        dq[sl] = torch.einsum("nhl,nlhd->nhd", ds, kk)
+        c, L = s_idx.shape
+        dk_rows = torch.einsum("nhl,nhd->nlhd", ds, qf).reshape(c, L, hkv, g, d).sum(3)
+        dv_rows = torch.einsum("nhl,nhd->nlhd", p, do).reshape(c, L, hkv, g, d).sum(3)
+        flat = safe.reshape(-1)
+        keep = ok.reshape(-1, 1, 1).float()
+        dk.index_add_(0, flat, dk_rows.reshape(c * L, hkv, d) * keep)
+        dv.index_add_(0, flat, dv_rows.reshape(c * L, hkv, d) * keep)
+    return dq, dk, dv
+
+
+@torch.no_grad()
+def selected_attention_forward(q, keys, values, sel, scale) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(out, lse)`` without autograd: the kernel on a GPU (bf16, head dim 128), the fp32 statement elsewhere."""
+    if not _kernel_ok(q, keys, values):
+        return selected_attention_reference(q, keys, values, sel, scale)
+    from aspec_b200 import _native
+    from aspec_b200.ops.gemm import status_word
+    n, hq, d = q.shape
+    q = q.contiguous()
+    k, k_ld = _rows(keys)
+    v, v_ld = _rows(values)
+    sel = sel.to(torch.int32).contiguous()
+    out = torch.empty_like(q)
+    lse = torch.empty(hq, n, dtype=torch.float32, device=q.device)
+    st = status_word(q.device)
+    rc = _native.kernels().ab_sel_attn_fwd(_p(q), _p(k), _p(v), _p(sel), _p(out), _p(lse), n, k.shape[0], sel.shape[1], hq,
+                                           k.shape[1], d, _c.c_longlong(k_ld), _c.c_longlong(v_ld), _c.c_float(scale),
+                                           _p(st), _stream(q))
+    if rc != 0:
+        raise RuntimeError(f"ab_sel_attn_fwd refused the launch (code {rc})")
+    return out, lse
+
+
+@torch.no_grad()
+def selected_attention_backward(q, keys, values, sel, out, lse, dout, scale):
+    """``(dq [n, Hq, d] in q's dtype, dk, dv fp32)`` from the forward's ``out`` / ``lse`` (or merged global ones)."""
+    if not _kernel_ok(q, keys, values):
+        dq, dk, dv = selected_attention_backward_reference(q, keys, values, sel, out, lse, dout, scale)
+        return dq.to(q.dtype), dk, dv
+    from aspec_b200 import _native
+    from aspec_b200.ops.gemm import status_word
+    n, hq, d = q.shape
+    q = q.contiguous()
+    k, k_ld = _rows(keys)
+    v, v_ld = _rows(values)
+    sel = sel.to(torch.int32).contiguous()
+    out, lse, dout = out.contiguous(), lse.float().contiguous(), dout.contiguous()   # named: alive until after the launch
+    dq = torch.empty_like(q)
+    dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+    dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+    st = status_word(q.device)
+    rc = _native.kernels().ab_sel_attn_bwd(_p(q), _p(k), _p(v), _p(sel), _p(out), _p(lse), _p(dout), _p(dq), _p(dk), _p(dv), n,
+                                           k.shape[0], sel.shape[1], hq, k.shape[1], d, _c.c_longlong(k_ld),
+                                           _c.c_longlong(v_ld), _c.c_float(scale), _p(st), _stream(q))
+    if rc != 0:
+        raise RuntimeError(f"ab_sel_attn_bwd refused the launch (code {rc})")
+    return dq, dk, dv
+
+
 class _SelectedAttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, keys, values, sel, scale):
-        from aspec_b200 import _native
-        from aspec_b200.ops.gemm import status_word
-        n, hq, d = q.shape
-        k, k_ld = _rows(keys)
-        v, v_ld = _rows(values)
-        out = torch.empty_like(q)
-        lse = torch.empty(hq, n, dtype=torch.float32, device=q.device)
-        st = status_word(q.device)
-        rc = _native.kernels().ab_sel_attn_fwd(_p(q), _p(k), _p(v), _p(sel), _p(out), _p(lse), n, k.shape[0], sel.shape[1], hq,
-                                               k.shape[1], d, _c.c_longlong(k_ld), _c.c_longlong(v_ld), _c.c_float(scale),
-                                               _p(st), _stream(q))
-        if rc != 0:
-            raise RuntimeError(f"ab_sel_attn_fwd refused the launch (code {rc})")
-        ctx.save_for_backward(q, k, v, sel, out, lse)
+        out, lse = selected_attention_forward(q, keys, values, sel, scale)
+        ctx.save_for_backward(q, keys, values, sel, out, lse)
         ctx.scale = scale
         return out, lse
 
     @staticmethod
     def backward(ctx, dout, _dlse):
-        from aspec_b200 import _native
-        from aspec_b200.ops.gemm import status_word
-        q, k, v, sel, out, lse = ctx.saved_tensors
-        n, hq, d = q.shape
-        dq = torch.empty_like(q)
-        dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
-        dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
-        st = status_word(q.device)
-        dout = dout.contiguous()            # named: a temporary's memory could be reused before the launch
-        rc = _native.kernels().ab_sel_attn_bwd(_p(q), _p(k), _p(v), _p(sel), _p(out), _p(lse), _p(dout), _p(dq),
-                                               _p(dk), _p(dv), n, k.shape[0], sel.shape[1], hq, k.shape[1], d,
-                                               _c.c_longlong(k.stride(0)), _c.c_longlong(v.stride(0)), _c.c_float(ctx.scale),
-                                               _p(st), _stream(q))
-        if rc != 0:
-            raise RuntimeError(f"ab_sel_attn_bwd refused the launch (code {rc})")
-        return dq, dk.to(k.dtype), dv.to(v.dtype), None, None
+        q, keys, values, sel, out, lse = ctx.saved_tensors
+        dq, dk, dv = selected_attention_backward(q, keys, values, sel, out, lse, dout, ctx.scale)
+        return dq, dk.to(keys.dtype), dv.to(values.dtype), None, None
 
 
 def selected_attention(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, sel: torch.Tensor,
@@ -159,8 +220,10 @@ def indexer_kernel_ok(qi: torch.Tensor, ki: torch.Tensor) -> bool:
 
 
 @torch.no_grad()
-def indexer_scores(qi: torch.Tensor, ki: torch.Tensor, w: torch.Tensor, lo: torch.Tensor, hi: torch.Tensor) -> torch.Tensor:
-    """``[n, T]`` fp32 scores, ``-inf`` outside ``[lo, hi)``.  ``qi [n, H, d]``, ``ki [T, d]``, ``w [n, H]``."""
+def indexer_scores(qi: torch.Tensor, ki: torch.Tensor, w: torch.Tensor, lo: torch.Tensor, hi: torch.Tensor,
+                   epilogue_groups: int = 0) -> torch.Tensor:
+    """``[n, T]`` fp32 scores, ``-inf`` outside ``[lo, hi)``.  ``qi [n, H, d]``, ``ki [T, d]``, ``w [n, H]``.
+    ``epilogue_groups`` (1 or 2) forces how many warpgroups drain an accumulator; 0 takes the kernel's default."""
     n, H, d = qi.shape
     T = ki.shape[0]
     if not indexer_kernel_ok(qi, ki):
@@ -178,8 +241,8 @@ def indexer_scores(qi: torch.Tensor, ki: torch.Tensor, w: torch.Tensor, lo: torc
     # the same block to the next one
     w32, lo32, hi32 = w.float().contiguous(), lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
     rc = _native.kernels().ab_indexer_scores(_p(qi), _p(ki), _p(w32), _p(lo32), _p(hi32), _p(out),
-                                             _c.c_longlong(out.stride(0)), n, T, H, d, _c.c_longlong(ki.stride(0)), _p(st),
-                                             _stream(qi))
+                                             _c.c_longlong(out.stride(0)), n, T, H, d, _c.c_longlong(ki.stride(0)),
+                                             int(epilogue_groups), _p(st), _stream(qi))
     if rc != 0:
         raise RuntimeError(f"ab_indexer_scores refused the launch (code {rc})")
     return out

@@ -67,6 +67,7 @@ def main() -> None:
             total += e0.elapsed_time(e1)
         return total / a.iters, out
 
+    t_scores_one, _ = timed(lambda: SA.indexer_scores(qi, ki, w, lo, hi, epilogue_groups=1))
     t_scores, scores = timed(lambda: SA.indexer_scores(qi, ki, w, lo, hi))
     t_topk, sel = timed(lambda: SA.topk_select(scores, lo, hi, a.topk))
     sel_full = torch.cat([sel, own.to(torch.int32)], 1).contiguous()
@@ -85,7 +86,7 @@ def main() -> None:
     res = {
         "workload": f"DSA sparse stage, context {T}, {n} queries, top-k {a.topk} + {bs} own-block keys, {hq}/{hkv} heads",
         "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "kind": kind},
-        "indexer_scores_ms": t_scores, "indexer_tflops": 2.0 * H * d * pairs / t_scores / 1e9,
+        "indexer_scores_ms_one_epilogue_warpgroup": t_scores_one, "indexer_scores_ms": t_scores, "indexer_tflops": 2.0 * H * d * pairs / t_scores / 1e9,
         "topk_ms": t_topk, "topk_gbs": 5 * 4 * pairs / t_topk / 1e6,
         "selected_attention_fwd_ms": t_fwd, "fwd_gather_gbs": sel_n * hkv * 2 * 256 / t_fwd / 1e6,
         "selected_attention_bwd_ms": t_bwd, "bwd_gather_plus_reduce_gbs": sel_n * hkv * (2 * 256 + 2 * 512) / t_bwd / 1e6,
