@@ -286,8 +286,9 @@ class DFlashModel(nn.Module):
     def _context_parallel_backbone(self, cp, hidden_states, B, T, layout, keep_flat, embeds, ctx_pos, draft_pos, tables, aux):
         """This rank's share of the backbone: its context rows, its blocks; attention exchanges with the other owners."""
         from aspec_b200.parallel.context_parallel import local_intervals
-        if any(k not in ("full_attention", "sliding_attention") for k in (self._policy or {}).get("layer_types", [])):
-            raise NotImplementedError("context parallelism is wired for dense and sliding-window layers")
+        allowed = ("full_attention", "sliding_attention", "deepseek_sparse_attention")
+        if any(k not in allowed for k in (self._policy or {}).get("layer_types", [])):
+            raise NotImplementedError("context parallelism is wired for dense, sliding-window and DSA layers")
         bs, n, total = self.block_size, layout.n, B * T
         s, e = cp.context_bounds(total)
         lo, hi = cp.block_bounds(n)
@@ -300,7 +301,7 @@ class DFlashModel(nn.Module):
         for t in tables:
             key = id(t)
             if key not in cache:
-                cache[key] = {"cp": cp, "counts": counts,
+                cache[key] = {"cp": cp, "counts": counts, "shard": (s, e, total),
                               "tables": [local_intervals(t[a * bs:b * bs], s, e, total, own=(o == cp.rank), query_start=q_lo)
                                          for o, (a, b) in enumerate(owners)]}
             per_layer.append(cache[key])

@@ -39,6 +39,16 @@ def _rotary(values: torch.Tensor, positions: torch.Tensor, dim: int, theta: floa
     return torch.cat((rot, values[..., dim:]), -1)
 
 
+def dist_all_gather(parts, tensor, group) -> None:
+    import torch.distributed as dist
+    dist.all_gather(parts, tensor, group=group)
+
+
+def dist_all_reduce(tensor, group) -> None:
+    import torch.distributed as dist
+    dist.all_reduce(tensor, group=group)
+
+
 class DSALightningIndexer(nn.Module):
     def __init__(self, config):
         super().__init__()
@@ -95,6 +105,11 @@ class DSAAttention(DFlashAttention):
     def forward(self, x, ctx, q_pos, kv_pos, intervals, aux=None, attn_override=None):
         if self.stage == "dense":
             return super().forward(x, ctx, q_pos, kv_pos, intervals, aux=aux, attn_override=attn_override)
+        if isinstance(intervals, dict):
+            if self.stage != "sparse":
+                raise NotImplementedError("under context parallelism DSA runs its dense and sparse stages; warm the "
+                                          "indexer up on one rank per row (draft_context_parallel_size=1)")
+            return self._forward_context_parallel(x, ctx, q_pos, kv_pos, intervals, aux)
         Q, T = x.shape[0], ctx.shape[0]
         d, hk = self.head_dim, self.num_kv_heads
         from aspec_b200.ops.fused_params import fused_linear
@@ -201,6 +216,96 @@ class DSAAttention(DFlashAttention):
             kl = (t_sel * (torch.log(t_sel.clamp_min(1e-20)) - logp)).sum(-1)
             out.append(torch.where(ok.any(-1), kl, torch.zeros_like(kl)))
         return torch.cat(out) if out else q.new_zeros(0, dtype=torch.float32)
+
+    def _forward_context_parallel(self, x, ctx, q_pos, kv_pos, cpinfo, aux):
+        """Sparse stage with the context sharded over the group (``ctx`` = this rank's shard, ``x`` = its own blocks).
+
+        Queries and their indexer projections are gathered over the group; every rank scores all queries against ITS
+        keys; the per-shard top-k candidates are merged into one global selection; each rank attends the selected keys
+        it owns (the owner also its own block) and the partials are merged by log-sum-exp; the KL between the main
+        attention and the indexer on the selected set is assembled from per-shard pieces with two small reductions.
+        """
+        from aspec_b200.ops import sparse_attention as SA
+        from aspec_b200.ops.fused_params import fused_linear
+        from aspec_b200.parallel.cp_runtime import _AllGatherStack, _pad_rows
+        from aspec_b200.parallel.distributed_sparse import (_AllReduceSum, distributed_log_softmax,
+                                                            distributed_selected_attention, distributed_topk,
+                                                            split_selection)
+        cp, counts, tables = cpinfo["cp"], list(cpinfo["counts"]), cpinfo["tables"]
+        s0, s1, _total = cpinfo["shard"]
+        group, rank = cp.group, cp.rank
+        Q, T = x.shape[0], ctx.shape[0]
+        d, hk = self.head_dim, self.num_kv_heads
+        q = self.q_proj(x).view(Q, self.num_heads, d)
+        kv = fused_linear(torch.cat([ctx, x], 0), [self.k_proj.weight, self.v_proj.weight])
+        k = kv[:, : hk * d].reshape(T + Q, hk, d)
+        v = kv[:, hk * d:].reshape(T + Q, hk, d)
+        inv = self.rope_freqs.get(x.device)
+        q = qk_norm_rope(q, self.q_norm.weight, q_pos, inv, self.eps, self.rope_scaling)
+        k = qk_norm_rope(k, self.k_norm.weight, kv_pos, inv, self.eps, self.rope_scaling)
+        iq, ik, iw = self.indexer.project(x, ctx, q_pos, kv_pos[:T])
+        # -- gather the group's queries (padded to the largest owner), keep the valid rows in owner order ----------
+        cap = max(max(counts), 1)
+        valid = torch.cat([torch.arange(c, device=x.device) + o * cap for o, c in enumerate(counts)]) if sum(counts) else None
+        gather = lambda t: _AllGatherStack.apply(_pad_rows(t, cap), group).flatten(0, 1)[valid]
+        q_all, iq_all, iw_all = gather(q), gather(iq), gather(iw)
+        q_tot = q_all.shape[0]
+        owner_lo = sum(counts[:rank])
+        owner_hi = owner_lo + counts[rank]
+        table_all = torch.cat([t for t in tables if t.shape[0]]) if q_tot else tables[rank]
+        l_lo, l_hi = table_all[:, 0].contiguous(), table_all[:, 1].contiguous()        # eligible LOCAL key range
+        # -- selection: local scores of all queries, global top-k ------------------------------------------------
+        budget = self.indexer.token_budget
+        with torch.no_grad():
+            if T:
+                score = SA.indexer_scores(iq_all.detach(), ik.detach(), iw_all.detach(), l_lo, l_hi)
+            else:
+                score = torch.zeros(q_tot, 0, device=x.device)
+            sel = distributed_topk(score, l_lo.long() + s0, l_hi.long() + s0, budget, s0, group)      # global indices
+            del score
+        # -- attention over the selected keys of every shard + the query's own block on its owner ----------------
+        own = tables[rank]
+        width = int((own[:, 3] - own[:, 2]).max().item()) if own.shape[0] else 0
+        extra = torch.full((q_tot, max(width, 1)), -1, dtype=torch.int32, device=x.device)
+        if own.shape[0] and width:
+            blk = own[:, 2:3].long() + torch.arange(width, device=x.device)[None]
+            extra[owner_lo:owner_hi] = torch.where(blk < own[:, 3:4].long(), blk, torch.full_like(blk, -1)).to(torch.int32)
+        out = distributed_selected_attention(q_all, k, v, sel, s0, owner_lo, owner_hi, self.scale, group, extra_local=extra,
+                                             shard_len=T)
+        # -- KL(main attention || indexer) on the selected set, assembled over shards -----------------------------
+        if aux is not None and self.compute_auxiliary_loss:
+            local = split_selection(sel, s0, s0 + T).long()
+            ok = local >= 0
+            safe = local.clamp_min(0)
+            if T:
+                sel_score = (torch.einsum("nhd,nsd->nhs", iq_all.float(), ik[safe].float()).relu() * iw_all[:, :, None]).sum(1)
+            else:
+                sel_score = torch.zeros(q_tot, local.shape[1], device=x.device) + 0.0 * iq_all.float().sum()
+            logp, _ = distributed_log_softmax(sel_score, ok, group)
+            with torch.no_grad():
+                g = self.num_heads // self.num_kv_heads
+                ctx_only = torch.stack([l_lo, l_hi, torch.zeros_like(l_lo), torch.zeros_like(l_lo)], 1).to(torch.int32).contiguous()
+                if T:
+                    _, lse_loc = interval_attention(q_all.detach(), k[:T].detach(), k[:T].detach(), ctx_only, self.scale)
+                    lse_loc = lse_loc.float()
+                else:
+                    lse_loc = torch.full((self.num_heads, q_tot), float("-inf"), device=x.device)
+                parts = [torch.empty_like(lse_loc) for _ in range(cp.size)]
+                dist_all_gather(parts, lse_loc.contiguous(), group)
+                lse = torch.logsumexp(torch.stack(parts), 0)                                 # [Hq, Q_tot] over all shards
+                lse = torch.where(torch.isfinite(lse), lse, torch.zeros_like(lse)).t()
+                if T:
+                    logit = torch.einsum("nhd,nshd->nhs", q_all.float(), k[:T][safe].float().repeat_interleave(g, 2)) * self.scale
+                    t_loc = (torch.exp(logit - lse[:, :, None]) * ok[:, None]).sum(1)
+                else:
+                    t_loc = torch.zeros(q_tot, local.shape[1], device=x.device)
+                z = t_loc.sum(-1)
+                dist_all_reduce(z, group)
+                t_sel = t_loc / z.clamp_min(1e-20)[:, None]
+            kl_part = (t_sel * (torch.log(t_sel.clamp_min(1e-20)) - logp) * ok).sum(-1)
+            kl = _AllReduceSum.apply(kl_part, group)
+            aux.setdefault("dsa_losses", []).append(torch.where(z > 0, kl, torch.zeros_like(kl))[owner_lo:owner_hi])
+        return self.o_proj(out.reshape(Q, -1))
 
     def _selected_attention(self, q, k, v, sel, sel_ok, iv, T):
         """Each query attends its selected context tokens and the whole of its own draft block."""

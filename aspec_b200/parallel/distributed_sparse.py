@@ -180,16 +180,19 @@ class _ShardedSelectedAttention(torch.autograd.Function):
 
 def distributed_selected_attention(q_all: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
                                    sel_global: torch.Tensor, shard_lo: int, owner_lo: int, owner_hi: int, scale: float,
-                                   group=None, extra_local: Optional[torch.Tensor] = None) -> torch.Tensor:
+                                   group=None, extra_local: Optional[torch.Tensor] = None,
+                                   shard_len: Optional[int] = None) -> torch.Tensor:
     """Attention of the group's queries over globally selected keys that are spread over the shards.
 
     ``q_all [Q_tot, H, d]``: all queries of the group (gathered by the caller, whose gather sums the per-rank query
     gradients in its backward); ``k_local / v_local [T_loc, Hk, d]``: this rank's keys; ``sel_global [Q_tot, S]`` global
     key indices (``-1`` = none); ``[owner_lo, owner_hi)``: the rows of ``q_all`` this rank owns and whose merged outputs
     it returns.  ``extra_local [Q_tot, E]``: more LOCAL indices every query attends on this rank (for example its own
-    draft block on the owner; ``-1`` elsewhere).  Returns ``out [owner_hi - owner_lo, H, d]``.
+    draft block on the owner; ``-1`` elsewhere).  ``shard_len``: how many leading rows of ``k_local`` are the context
+    shard that ``sel_global`` indexes (default: all of them; the rest are rows only ``extra_local`` can name).
+    Returns ``out [owner_hi - owner_lo, H, d]``.
     """
-    t_loc = k_local.shape[0]
+    t_loc = k_local.shape[0] if shard_len is None else int(shard_len)
     local = split_selection(sel_global, shard_lo, shard_lo + t_loc)
     if extra_local is not None:
         local = torch.cat([local, extra_local.to(torch.int32)], 1)

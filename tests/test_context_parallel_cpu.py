@@ -149,3 +149,63 @@ def test_sequence_parallel_eagle3_over_gloo_matches_one_process(tmp_path):
         assert torch.equal(two["counts"], one["counts"])
         for name, g in one["grads"].items():
             assert torch.allclose(two["grads"][name], g, rtol=2e-3, atol=2e-5), name
+
+
+# ---- DSA sparse stage under context parallelism ------------------------------------------------------------------
+DSA_CFG = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+               vocab_size=256, num_target_layers=3, target_hidden_size=64, target_num_hidden_layers=8, markov_rank=16,
+               mask_token_id=255, layer_types=["deepseek_sparse_attention"], dsa_token_budget=10, dsa_index_n_heads=4,
+               dsa_index_head_dim=16, dsa_q_lora_rank=16, dsa_rope_dim=8, dsa_training_stage="sparse")
+
+
+def _dsa_model():
+    torch.manual_seed(0)
+    return DSparkModel(DSparkDraftModel(DSparkConfig(**DSA_CFG)), block_size=4, num_anchors=12)
+
+
+def _dsa_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from aspec_b200.parallel.cp_runtime import ContextParallel, attach
+    model = _dsa_model()
+    attach(model, ContextParallel(num_layers=1, max_queries=24, heads=4, head_dim=16))
+    ids, feats, mask, head, last, anchors, keep = _inputs()
+    res = model(ids, feats, mask, head, last_hidden_states=last, injected_anchors=anchors, injected_keep_mask=keep)
+    num, den = res[6]
+    num.backward()
+    grads = {n: (p.grad.clone() if p.grad is not None else torch.zeros_like(p)) for n, p in model.draft_model.named_parameters()}
+    stats = torch.stack([num.detach(), den.detach(), res[5]["dsa_indexer_loss"][0], res[5]["ce_loss"][0],
+                         res[5]["l1_loss"][0], res[5]["confidence_loss"][0]])
+    dist.all_reduce(stats)
+    for g in grads.values():
+        dist.all_reduce(g)
+    if rank == 0:
+        torch.save({"stats": stats, "grads": grads}, out)
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_dsa_sparse_stage_cp2_matches_single_rank(tmp_path):
+    """A budget that really prunes: the global top-k over two shards, the merged selected-key attention and the
+    selected-set KL must reproduce the one-rank loss terms and gradients."""
+    out = str(tmp_path / "dsa_cp.pt")
+    mp.spawn(_dsa_worker, args=(2, 29400 + os.getpid() % 200, out), nprocs=2, join=True)
+    got = torch.load(out)
+    model = _dsa_model()
+    ids, feats, mask, head, last, anchors, keep = _inputs()
+    res = model(ids, feats, mask, head, last_hidden_states=last, injected_anchors=anchors, injected_keep_mask=keep)
+    num, den = res[6]
+    num.backward()
+    assert torch.allclose(got["stats"][1], den.detach())
+    assert torch.allclose(got["stats"][3], res[5]["ce_loss"][0], rtol=1e-4, atol=1e-5)
+    assert torch.allclose(got["stats"][2], res[5]["dsa_indexer_loss"][0], rtol=1e-4, atol=1e-5)
+    # L1 / confidence terms pass through exp() of merged partial outputs: a little looser than the CE term
+    assert torch.allclose(got["stats"][4], res[5]["l1_loss"][0], rtol=1e-3)
+    assert torch.allclose(got["stats"][0], num.detach(), rtol=1e-3, atol=1e-5)
+    bad = {}
+    for name, p in model.draft_model.named_parameters():
+        want = p.grad if p.grad is not None else torch.zeros_like(p)
+        err = float((got["grads"][name] - want).abs().max() / want.abs().max().clamp_min(1e-9))
+        if not torch.allclose(got["grads"][name], want, rtol=2e-3, atol=2e-5):
+            bad[name] = round(err, 4)
+    assert not bad, str(bad)
