@@ -156,6 +156,30 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
         o, _ = interval_attention(q, k_all, v_all, intervals, attn.scale)
         return o, (k0, v0, dk, dv)
 
+    @staticmethod
+    def _attend_ring(attn, q, k, v, depth: int, cache, doc_start: torch.Tensor, ttt_length: int, row0: int, ring_group):
+        """``_attend`` when the rows are one shard of a sequence spread over a ring: the causal depth-0 keys live on every
+        rank of the ring (``parallel.ring_attention``), the keys of depths ``1..depth`` are each row's own and stay local.
+        ``doc_start`` holds GLOBAL row indices, ``row0`` is the global index of this shard's first row."""
+        from aspec_b200.parallel.ring_attention import ring_attention
+        S = q.shape[0]
+        L1 = max(ttt_length - 1, 1)
+        t = torch.arange(S, device=q.device)
+        if depth == 0:
+            k0, v0, dk, dv = k, v, [], []
+        else:
+            k0, v0, dk, dv = cache
+            dk, dv = dk + [k], dv + [v]
+        n_pad = L1 - len(dk)
+        k_all = torch.cat([k0, torch.stack(dk + [torch.zeros_like(k)] * n_pad, 1).reshape(S * L1, *k.shape[1:])])
+        v_all = torch.cat([v0, torch.stack(dv + [torch.zeros_like(v)] * n_pad, 1).reshape(S * L1, *v.shape[1:])])
+        tg = t + row0
+        window = getattr(attn, "window", None)
+        lo = doc_start if window is None else torch.maximum(doc_start, tg + 1 - window)
+        intervals = torch.stack([lo, tg + 1, S + t * L1, S + t * L1 + depth], -1).to(torch.int32)
+        o, _ = ring_attention(q, k_all, v_all, intervals, S, attn.scale, ring_group)
+        return o, (k0, v0, dk, dv)
+
     def _ulysses_attention(self, layer, x, positions_all, depth: int, cache, doc_start_all, ttt_length: int, ex):
         from aspec_b200.parallel.ulysses import group_qkv_rows
         from aspec_b200.parallel.ulysses_attention import ulysses_block
@@ -167,17 +191,26 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
         w_grouped = group_qkv_rows(sa.q_proj.weight, sa.k_proj.weight, sa.v_proj.weight, p, d)
         state = {}
 
-        def core(qkv: torch.Tensor) -> torch.Tensor:            # all rows, this rank's heads
+        ring = getattr(self, "ring", None)          # (ring index, ring size, process group): Ulysses x ring
+
+        def core(qkv: torch.Tensor) -> torch.Tensor:            # the exchange group's rows, this rank's heads
             T = qkv.shape[0]
             q = qkv[:, : hq * d].reshape(T, hq, d)
             k = qkv[:, hq * d:(hq + hk) * d].reshape(T, hk, d)
             v = qkv[:, (hq + hk) * d:].reshape(T, hk, d)
+            # with a ring stage the exchange group holds one contiguous shard of the packed sequence
+            row0 = ring[0] * T if ring is not None else 0
+            pos = positions_all[row0:row0 + T] + depth
+            starts = doc_start_all[row0:row0 + T]
             if sa.use_rope:
                 inv = sa.rope_freqs.get(qkv.device)
-                pos = positions_all + depth
                 q = qk_norm_rope(q.contiguous(), None, pos, inv, 0.0, sa.rope_scaling)
                 k = qk_norm_rope(k.contiguous(), None, pos, inv, 0.0, sa.rope_scaling)
-            o, state["cache"] = self._attend(sa, q, k.contiguous(), v.contiguous(), depth, cache, doc_start_all, ttt_length)
+            if ring is not None and ring[1] > 1:
+                o, state["cache"] = self._attend_ring(sa, q, k.contiguous(), v.contiguous(), depth, cache, starts, ttt_length,
+                                                      row0, ring[2])
+            else:
+                o, state["cache"] = self._attend(sa, q, k.contiguous(), v.contiguous(), depth, cache, starts, ttt_length)
             return o.reshape(T, hq * d)
 
         ex.set_rows(x.shape[0])

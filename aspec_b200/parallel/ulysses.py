@@ -223,6 +223,8 @@ class CollectiveUlyssesExchange:
         return slice(r * self.rows, (r + 1) * self.rows)
 
     def _gather(self, x: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:                      # a ring-only group: nothing to exchange
+            return x[None]
         parts = [torch.empty_like(x) for _ in range(self.world)]
         dist.all_gather(parts, x.contiguous(), group=self.group)
         return torch.stack(parts)

@@ -77,30 +77,48 @@ class TrainerActor:
             attach(self.model, ContextParallel(groups[rank // self.cp_size], num_layers=int(cfg.num_hidden_layers),
                                                max_queries=per_rank, heads=int(cfg.num_attention_heads),
                                                head_dim=int(cfg.head_dim), device=self.device))
-        # the reference splits a sequence-parallel group into Ulysses x ring; here the whole group exchanges heads
-        self.sp_size = max(int(self.args.get("sp_ulysses_size", 1) or 1), 1) * max(int(self.args.get("sp_ring_size", 1) or 1), 1)
+        # a sequence-parallel group of ``u * r`` ranks shares every row: ``u`` adjacent ranks exchange heads (Ulysses), the
+        # ``r`` blocks of ``u`` ranks pass key / value shards around a ring (reference: aspec/utils/distributed.py:117-201)
+        self.sp_ulysses = max(int(self.args.get("sp_ulysses_size", 1) or 1), 1)
+        self.sp_ring = max(int(self.args.get("sp_ring_size", 1) or 1), 1)
+        self.sp_size = self.sp_ulysses * self.sp_ring
         if self.sp_size > 1 and world > 1 and getattr(self.model, "supports_sequence_parallel", False):
-            # ranks [g * sp, (g + 1) * sp) share every row: each keeps a slice of the tokens, attention heads are exchanged
+            # ranks [g * sp, (g + 1) * sp) share every row: each keeps a slice of the tokens
+            u, r = self.sp_ulysses, self.sp_ring
             if world % self.sp_size:
-                raise ValueError("sp_ulysses_size must divide the Draft world size")
+                raise ValueError("sp_ulysses_size * sp_ring_size must divide the Draft world size")
             heads, kv_heads, hd = int(cfg.num_attention_heads), int(cfg.num_key_value_heads), int(cfg.head_dim)
-            if heads % self.sp_size or kv_heads % self.sp_size:
+            if heads % u or kv_heads % u:
                 raise ValueError("sp_ulysses_size must divide the attention head counts")
-            groups = [dist.new_group(list(range(g * self.sp_size, (g + 1) * self.sp_size))) for g in range(world // self.sp_size)]
-            mine = groups[rank // self.sp_size]
+            # every rank creates every group, in the same order
+            sp_groups = [dist.new_group(list(range(g * self.sp_size, (g + 1) * self.sp_size))) for g in range(world // self.sp_size)]
+            u_groups, ring_groups = {}, {}
+            for g in range(world // self.sp_size):
+                base = g * self.sp_size
+                for b in range(r):
+                    u_groups[(g, b)] = dist.new_group([base + b * u + i for i in range(u)]) if u > 1 else None
+                for i in range(u):
+                    ring_groups[(g, i)] = dist.new_group([base + b * u + i for b in range(r)]) if r > 1 else None
+            g, idx = rank // self.sp_size, rank % self.sp_size
+            mine = sp_groups[g]
+            u_group, ring_group = u_groups[(g, idx // u)], ring_groups[(g, idx % u)]
             if self.cuda:
                 from aspec_b200.parallel.group import exchange_workspaces, make_barrier
                 from aspec_b200.parallel.ulysses import UlyssesExchange, UlyssesWorkspace
                 rows = -(-int(self.args["max_seq_length"]) // self.sp_size) + 8
-                ws = exchange_workspaces(UlyssesWorkspace(self.sp_size, rows, (heads + 2 * kv_heads) * hd // self.sp_size,
-                                                          heads * hd // self.sp_size, device=self.device),
-                                         UlyssesWorkspace.open, group=mine)
-                exchange = UlyssesExchange(rank % self.sp_size, self.sp_size, ws, make_barrier(self.device, mine))
+                own = UlyssesWorkspace(u, rows, (heads + 2 * kv_heads) * hd // u, heads * hd // u, device=self.device)
+                if u > 1:
+                    ws = exchange_workspaces(own, UlyssesWorkspace.open, group=u_group)
+                    exchange = UlyssesExchange(idx % u, u, ws, make_barrier(self.device, u_group))
+                else:                            # ring only: the projections run through the same kernels, no peers
+                    exchange = UlyssesExchange(0, 1, [own], lambda: None)
             else:
                 from aspec_b200.parallel.ulysses import CollectiveUlyssesExchange
-                exchange = CollectiveUlyssesExchange(rank % self.sp_size, self.sp_size, mine)
+                exchange = CollectiveUlyssesExchange(idx % u, u, u_group)
             self.model.draft_model.ulysses = exchange
-            self.model.sequence_parallel = (rank % self.sp_size, self.sp_size, mine)
+            if r > 1:
+                self.model.draft_model.ring = (idx // u, r, ring_group)
+            self.model.sequence_parallel = (idx, self.sp_size, mine)
         layout = SlotLayout(int(self.args["max_seq_length"]), int(getattr(cfg, "num_target_layers", None)
                                                                    or getattr(cfg, "num_aux_hidden_states", 3)),
                             int(getattr(cfg, "target_hidden_size", cfg.hidden_size)),

@@ -209,3 +209,63 @@ def test_dsa_sparse_stage_cp2_matches_single_rank(tmp_path):
         if not torch.allclose(got["grads"][name], want, rtol=2e-3, atol=2e-5):
             bad[name] = round(err, 4)
     assert not bad, str(bad)
+
+
+def _usp_eagle_worker(rank, world, port, out, u, r):
+    """Ulysses x ring: ``u`` adjacent ranks exchange heads, ``r`` such blocks form the ring."""
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from aspec_b200.config.draft_config import AutoDraftModelConfig
+    from aspec_b200.parallel.ulysses import CollectiveUlyssesExchange
+    from aspec_b200.training.factory import build_training_model
+    raw = dict(architectures=["LlamaForCausalLMEagle3"], model_type="llama", hidden_size=32, intermediate_size=64,
+               num_attention_heads=4, num_key_value_heads=2, head_dim=8, vocab_size=96, draft_vocab_size=96, target_hidden_size=32,
+               num_aux_hidden_states=3, rope_theta=10000.0, max_position_embeddings=256)
+    torch.manual_seed(0)
+    model = build_training_model(AutoDraftModelConfig.from_dict(raw), dict(ttt_length=3, seed=0), "cpu", torch.float32)
+    model.train()
+    T = 45
+    g = torch.Generator().manual_seed(5)
+    batch = dict(input_ids=torch.randint(0, 90, (1, T), generator=g), hidden_states_list=torch.randn(1, T, 96, generator=g),
+                 loss_mask=torch.cat([torch.zeros(1, 6), torch.ones(1, T - 6)], 1),
+                 lm_head_weight=torch.randn(96, 32, generator=g) * 0.2, last_hidden_states=torch.randn(1, T, 32, generator=g),
+                 ctx_doc_ids=torch.cat([torch.zeros(1, 20), torch.ones(1, T - 20)], 1).long())
+    u_groups = [dist.new_group([b * u + i for i in range(u)]) if u > 1 else None for b in range(r)]
+    ring_groups = [dist.new_group([b * u + i for b in range(r)]) for i in range(u)]
+    model.draft_model.ulysses = CollectiveUlyssesExchange(rank % u, u, u_groups[rank // u])
+    model.draft_model.ring = (rank // u, r, ring_groups[rank % u])
+    model.sequence_parallel = (rank, world, None)
+    res = model(**batch)
+    res[6][0].backward()
+    num, den = res[6][0].detach().clone(), res[6][1].detach().clone()
+    grads = {n: (p.grad.clone() if p.grad is not None else torch.zeros_like(p)) for n, p in model.draft_model.named_parameters()
+             if p.requires_grad}
+    dist.all_reduce(num)
+    dist.all_reduce(den)
+    for v in grads.values():
+        dist.all_reduce(v)
+    torch.save({"loss": num / den, "counts": res[4], "grads": grads}, f"{out}.usp.{rank}")
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("u,r", [(2, 2), (1, 2)])
+def test_ulysses_times_ring_eagle3_matches_one_process(tmp_path, u, r):
+    """EAGLE3 (TTT depth keys stay local, depth-0 keys go round the ring) on ``u x r`` gloo ranks against one process."""
+    import os
+    import torch
+    import torch.multiprocessing as mp
+    out = str(tmp_path / "usp")
+    base = 29200 + os.getpid() % 80
+    mp.spawn(_sp_eagle_worker, args=(1, base, out), nprocs=1, join=True)
+    mp.spawn(_usp_eagle_worker, args=(u * r, base + 1, out, u, r), nprocs=u * r, join=True)
+    one = torch.load(f"{out}.1.0")
+    for rank in range(u * r):
+        two = torch.load(f"{out}.usp.{rank}")
+        assert torch.allclose(two["loss"], one["loss"], rtol=1e-4)
+        assert torch.equal(two["counts"], one["counts"])
+        for name, g in one["grads"].items():
+            assert torch.allclose(two["grads"][name], g, rtol=2e-3, atol=2e-5), name
