@@ -64,17 +64,27 @@ class TrainingController:
         max_len = int(a["max_seq_length"])
         min_loss = int(a.get("min_loss_tokens", 0))
         self.samples = []
+        rejected = {"longer_than_max_seq_length": 0, "no_supervised_position": 0, "fewer_loss_tokens_than_min_loss_tokens": 0}
+        source_rows = 0
         for s in samples:
+            source_rows += 1
             n = int(s["input_ids"].shape[-1])
             if n > max_len:
+                rejected["longer_than_max_seq_length"] += 1
                 continue
             if self.algorithm in ("eagle3", "eagle4", "mtp"):
                 useful = count_eagle_supervised_positions(s["packed_loss_mask"], n, int(a.get("ttt_length", 7)))
             else:
                 useful = count_eligible_anchor_starts(s["packed_loss_mask"], n, self.block_size)
-            if useful <= 0 or sum(int(v) for v in s["packed_loss_mask"].split(",")[1::2]) < min_loss:
+            if useful <= 0:
+                rejected["no_supervised_position"] += 1
+                continue
+            if sum(int(v) for v in s["packed_loss_mask"].split(",")[1::2]) < min_loss:
+                rejected["fewer_loss_tokens_than_min_loss_tokens"] += 1
                 continue
             self.samples.append({**s, "length": n, "useful": useful})
+        # source-to-runtime accounting for the run's evidence: every source row is admitted or rejected for a reason
+        self.admission = {"source_rows": source_rows, "rejected": {k: v for k, v in rejected.items() if v}}
         self._start_epoch()
         return len(self.samples)
 

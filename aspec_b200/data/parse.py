@@ -170,7 +170,165 @@ class ToolXMLParser(ThinkingParser):
         return text
 
 
-_PARSERS = {"general": GeneralParser, "thinking": ThinkingParser, "harmony": HarmonyParser, "tool_xml": ToolXMLParser}
+def _flatten_content(content: Any, image_text: str) -> str:
+    """Message content as text: a string, or a list of ``{"type": "text" | "image" | "image_url", ...}`` parts where
+    every image part becomes ``image_text``."""
+    if isinstance(content, str):
+        return content
+    if isinstance(content, (list, tuple)):
+        return "".join(part.get("text", "") if part.get("type") == "text" else
+                       image_text if part.get("type") in ("image", "image_url") else "" for part in content)
+    return "" if content is None else str(content)
+
+
+def _split_reasoning(text: str) -> Tuple[str, str]:
+    """``(reasoning, answer)`` of a reply that may hold one ``<think>`` block (whose opener may be missing)."""
+    if "</think>" not in text:
+        return "", text
+    head, tail = text.split("</think>", 1)
+    return head.split("<think>")[-1].strip("\n"), tail.strip("\n")
+
+
+class _DialectParser(Parser):
+    """Parsers whose turn syntax is fixed by the model family rather than by a template's header strings.
+
+    A subclass states the wire format as data (``ROLE_OPEN``, ``TURN_CLOSE``, ``IMAGE``) and writes one assistant turn in
+    ``_assistant_turn``; walking the conversation, image expansion, history trimming and the loss-mask pattern are shared.
+    ``expand_media_tokens=False`` keeps the dataset's image placeholder in the text (for a later multimodal processor).
+    """
+
+    ROLE_OPEN: Dict[str, str] = {}
+    TURN_CLOSE = ""
+    IMAGE = ""
+    PROMPT_OPEN = ""           # what follows the assistant header when a generation prompt is requested
+
+    def __init__(self, tokenizer, chat_template):
+        super().__init__(tokenizer, chat_template)
+        self.placeholder = chat_template.image_placeholder or "<image>"
+        self.assistant_pattern = re.escape(self.ROLE_OPEN["assistant"]) + r"(.*?" + re.escape(self.TURN_CLOSE) + r"|.*\Z)"
+
+    def _text_of(self, msg: Dict[str, Any], expand: bool) -> str:
+        image = (self.IMAGE + "\n") if expand else self.placeholder
+        text = _flatten_content(msg.get("content"), image)
+        if expand and isinstance(msg.get("content"), str) and msg["role"] == "user":
+            text = text.replace(self.placeholder, self.IMAGE + "\n")
+        return text
+
+    def _raw_messages(self, conversation) -> Conversation:
+        out = []
+        for msg in conversation:
+            role = msg.get("role", msg.get("from"))
+            if role not in _ROLES:
+                raise ValueError(f"unknown message role {role!r}")
+            out.append({**msg, "role": _ROLES[role], "content": msg.get("content", msg.get("value"))})
+        return out
+
+    def format(self, conversation, last_turn_only: bool = False, add_generation_prompt: bool = False,
+               expand_media_tokens: bool = True) -> str:
+        msgs = self._raw_messages(conversation)
+        pieces = self._walk(msgs, expand_media_tokens)
+        if add_generation_prompt:
+            pieces.append(self.ROLE_OPEN["assistant"] + self.PROMPT_OPEN)
+        return "".join(pieces)
+
+
+class KimiK25Parser(_DialectParser):
+    """Kimi-K2.5 (reference behaviour: aspec/data/parse.py:380-536).  No default system prompt; every assistant turn
+    opens with a ``<think>`` block (empty when there is no reasoning); only the last assistant turn keeps its reasoning;
+    tool calls use the family's inline section tokens; a tool result is a system-side ``tool`` turn."""
+
+    ROLE_OPEN = {"system": "<|im_system|>system<|im_middle|>", "user": "<|im_user|>user<|im_middle|>",
+                 "assistant": "<|im_assistant|>assistant<|im_middle|>", "tool": "<|im_system|>tool<|im_middle|>"}
+    TURN_CLOSE = "<|im_end|>"
+    IMAGE = "<|media_begin|>image<|media_content|><|media_pad|><|media_end|>"
+    PROMPT_OPEN = "<think>"
+
+    @staticmethod
+    def _calls(calls) -> str:
+        body = "".join(f"<|tool_call_begin|>{c.get('id', '')}<|tool_call_argument_begin|>"
+                       f"{c.get('function', {}).get('arguments', '')}<|tool_call_end|>" for c in calls)
+        return "<|tool_calls_section_begin|>" + body + "<|tool_calls_section_end|>"
+
+    def _walk(self, msgs, expand):
+        final = max((i for i, m in enumerate(msgs) if m["role"] == "assistant"), default=-1)
+        out = []
+        for i, m in enumerate(msgs):
+            text = self._text_of(m, expand)
+            if m["role"] == "assistant":
+                if "</think>" in text and "<think>" not in text:          # opener eaten by a generation prompt
+                    text = "<think>" + text
+                if i != final:
+                    text = _THINK.sub("", text)
+                elif m.get("reasoning_content") and "<think>" not in text:
+                    text = f"<think>{str(m['reasoning_content']).strip()}</think>{text}"
+                if m.get("tool_calls"):
+                    text += self._calls(m["tool_calls"])
+                if not text.startswith("<think>"):
+                    text = "<think></think>" + text
+            elif m["role"] == "tool" and m.get("tool_call_id"):
+                text = f"## Return of {m['tool_call_id']}\n{text}"
+            out.append(self.ROLE_OPEN[m["role"]] + text + self.TURN_CLOSE)
+        return out
+
+
+class MiniMaxParser(_DialectParser):
+    """MiniMax-M2 (reference behaviour: aspec/data/parse.py:539-700).  A system turn always opens the text; reasoning is
+    kept only in assistant turns after the last user message (interleaved thinking); tool calls are
+    ``<minimax:tool_call>`` XML; consecutive tool results share one ``tool`` turn."""
+
+    ROLE_OPEN = {"system": "]~!b[]~b]system\n", "user": "]~b]user\n", "assistant": "]~b]ai\n", "tool": "]~b]tool"}
+    TURN_CLOSE = "[e~["
+    IMAGE = "]<]start of image[>[]<]vision pad[>[]<]end of image[>["
+    PROMPT_OPEN = "<think>\n"
+    DEFAULT_SYSTEM = "You are a helpful assistant."
+
+    @staticmethod
+    def _calls(calls) -> str:
+        blocks = []
+        for call in calls:
+            fn = call.get("function", call)
+            args = fn.get("arguments", {})
+            if isinstance(args, str):
+                try:
+                    args = json.loads(args)
+                except ValueError:
+                    args = {"raw": args}
+            lines = [f'<invoke name="{fn.get("name", "")}">']
+            for key, value in (args.items() if isinstance(args, dict) else ()):
+                shown = value if isinstance(value, str) else json.dumps(value, ensure_ascii=False)
+                lines.append(f'<parameter name="{key}">{shown}</parameter>')
+            blocks.append("\n".join(lines + ["</invoke>"]))
+        return "\n<minimax:tool_call>\n" + "\n".join(blocks) + "\n</minimax:tool_call>"
+
+    def _walk(self, msgs, expand):
+        if msgs and msgs[0]["role"] == "system":
+            system, msgs = self._text_of(msgs[0], expand), msgs[1:]
+        else:
+            system = self.template.system_prompt or self.DEFAULT_SYSTEM
+        out = [self.ROLE_OPEN["system"] + system + self.TURN_CLOSE + "\n"]
+        last_user = max((i for i, m in enumerate(msgs) if m["role"] == "user"), default=-1)
+        for i, m in enumerate(msgs):
+            text = self._text_of(m, expand)
+            if m["role"] == "assistant":
+                reasoning = m.get("reasoning_content") or ""
+                if not reasoning:
+                    reasoning, text = _split_reasoning(text)
+                turn = (f"<think>\n{reasoning}\n</think>\n\n" if reasoning and i > last_user else "") + text
+                if m.get("tool_calls"):
+                    turn += self._calls(m["tool_calls"])
+                out.append(self.ROLE_OPEN["assistant"] + turn + self.TURN_CLOSE + "\n")
+            elif m["role"] == "tool":
+                opens = i == 0 or msgs[i - 1]["role"] != "tool"
+                closes = i == len(msgs) - 1 or msgs[i + 1]["role"] != "tool"
+                out.append((self.ROLE_OPEN["tool"] if opens else "") + f"\n<response>{text}</response>"
+                           + (self.TURN_CLOSE + "\n" if closes else ""))
+            else:
+                out.append(self.ROLE_OPEN[m["role"]] + text + self.TURN_CLOSE + "\n")
+        return out
+
+
+_PARSERS = {"general": GeneralParser, "thinking": ThinkingParser, "harmony": HarmonyParser, "tool_xml": ToolXMLParser,
+            "kimi-k25": KimiK25Parser, "minimax-m2": MiniMaxParser}
 
 
 def create_parser(tokenizer, chat_template: ChatTemplate) -> Parser:

@@ -12,7 +12,7 @@ class ChatTemplate:
     user_header: Optional[str]
     system_prompt: Optional[str]
     end_of_turn_token: Optional[str]
-    parser_type: str = "general"          # general | thinking | harmony | tool_xml
+    parser_type: str = "general"          # general | thinking | harmony | tool_xml | kimi-k25 | minimax-m2
     enable_thinking: bool = False
     system_header: Optional[str] = None
     bos: str = ""
@@ -60,6 +60,12 @@ for _name, _tpl in {
                             system_header="<|start|>system<|message|>"),
     "kimi-k2": ChatTemplate("<|im_assistant|>assistant<|im_middle|>", "<|im_user|>user<|im_middle|>", None, "<|im_end|>",
                             parser_type="tool_xml", system_header="<|im_system|>system<|im_middle|>"),
-    "minimax-m2": ChatTemplate("]~b]ai\n", "]~b]user\n", None, "[e~[\n", parser_type="tool_xml", system_header="]~!b[]~b]system\n"),
+    "kimi-k2-thinking": ChatTemplate("<|im_assistant|>assistant<|im_middle|>", "<|im_user|>user<|im_middle|>", None, "<|im_end|>",
+                                     parser_type="thinking", enable_thinking=True, system_header="<|im_system|>system<|im_middle|>"),
+    "kimi-k25-vlm": ChatTemplate("<|im_assistant|>assistant<|im_middle|>", "<|im_user|>user<|im_middle|>", None, "<|im_end|>",
+                                 parser_type="kimi-k25", system_header="<|im_system|>system<|im_middle|>",
+                                 image_placeholder="<|image|>"),
+    "minimax-m2": ChatTemplate("]~b]ai\n", "]~b]user\n", "You are a helpful assistant. Your name is MiniMax-M2.5 and is built by MiniMax.",
+                               "[e~[", parser_type="minimax-m2", system_header="]~!b[]~b]system\n"),
 }.items():
     TEMPLATE_REGISTRY.register(_name, _tpl)

@@ -20,7 +20,7 @@ import torch
 import torch.nn as nn
 
 from aspec_b200.config.draft_config import Eagle3Config
-from aspec_b200.config.rope import rope_inverse_frequencies
+from aspec_b200.config.rope import mrope_axis_of_frequency, rope_inverse_frequencies
 from aspec_b200.models.draft.base import Eagle3DraftModel
 from aspec_b200.models.draft.dflash import DFlashMLP, _Weight
 from aspec_b200.ops.attention import interval_attention
@@ -51,6 +51,10 @@ class EagleAttention(nn.Module):
             params.setdefault("original_max_position_embeddings", config.max_position_embeddings)
         inv, self.rope_scaling = rope_inverse_frequencies(d, params)
         self.rope_freqs = RopeFrequencies(inv)
+        # multi-axis RoPE: the stream (temporal / height / width) that rotates each frequency; used when a row brings
+        # three position streams, which only rows with image or video spans do
+        self.mrope_axes = (RopeFrequencies(mrope_axis_of_frequency(d, scaling["mrope_section"]))
+                           if scaling and params["rope_type"] == "mrope" else None)
         self.scale = d ** -0.5
 
     def project(self, x: torch.Tensor, positions: torch.Tensor):
@@ -63,8 +67,9 @@ class EagleAttention(nn.Module):
         v = qkv[:, (hq + hk) * d:].reshape(T, hk, d)
         if self.use_rope:
             inv = self.rope_freqs.get(x.device)
-            q = qk_norm_rope(q, None, positions, inv, 0.0, self.rope_scaling)
-            k = qk_norm_rope(k, None, positions, inv, 0.0, self.rope_scaling)
+            axes = self.mrope_axes.get(x.device) if self.mrope_axes is not None and positions.dim() == 2 else None
+            q = qk_norm_rope(q, None, positions, inv, 0.0, self.rope_scaling, axes)
+            k = qk_norm_rope(k, None, positions, inv, 0.0, self.rope_scaling, axes)
         return q, k.contiguous(), v.contiguous()
 
 
@@ -203,7 +208,7 @@ class LlamaForCausalLMEagle3(Eagle3DraftModel):
             pos = positions_all[row0:row0 + T] + depth
             starts = doc_start_all[row0:row0 + T]
             if sa.use_rope:
-                inv = sa.rope_freqs.get(qkv.device)
+                inv = sa.rope_freqs.get(qkv.device)          # text rows: one position stream, also under mrope
                 q = qk_norm_rope(q.contiguous(), None, pos, inv, 0.0, sa.rope_scaling)
                 k = qk_norm_rope(k.contiguous(), None, pos, inv, 0.0, sa.rope_scaling)
             if ring is not None and ring[1] > 1:

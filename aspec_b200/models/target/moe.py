@@ -4,8 +4,8 @@ Targets through its serving engine's ``bailing_moe`` models: compat/patches/sgla
 Routing: fp32 ``sigmoid(W_g x)``; the selection score adds ``expert_bias``; groups are ranked by the sum of their
 top-2 scores and ``topk_group`` groups stay; top-k inside; combine weights are the un-biased scores, renormalised
 and scaled by ``routed_scaling_factor``.  Tokens are sorted by expert once, every expert runs two GEMMs on its
-contiguous slice (tcgen05 GEMM on CUDA, SwiGLU in the first GEMM's epilogue when the stacked weights are
-tile-interleaved), results are scattered back with ``index_add``; the shared expert is a dense SwiGLU on all tokens.
+contiguous slice (on CUDA all experts of a layer share two grouped tcgen05 launches), results are scattered back with
+``index_add``; the shared expert is a dense SwiGLU on all tokens.
 """
 from __future__ import annotations
 
@@ -72,6 +72,13 @@ class TargetMoE(nn.Module):
         counts = torch.bincount(flat, minlength=self.gate.shape[0]).tolist()      # one host read per MoE layer
         rows = x[tokens].contiguous()
         out = torch.zeros(T, D, device=x.device, dtype=torch.float32)
+        I = self.gate_up_proj.shape[1] // 2
+        if x.is_cuda and x.dtype == torch.bfloat16 and D % 64 == 0 and I % 64 == 0 and T:
+            # all experts in two grouped tcgen05 launches (gate/up with the SwiGLU between, then down)
+            from aspec_b200.ops.grouped_gemm import grouped_experts
+            y = grouped_experts(rows, self.gate_up_proj, self.down_proj, counts, 0.0)
+            out.index_add_(0, tokens, y.float() * w.flatten()[order, None])
+            counts = []
         off = 0
         for e, n in enumerate(counts):
             if n:

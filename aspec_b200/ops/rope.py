@@ -29,19 +29,27 @@ class RopeFrequencies:
         return t
 
 
-def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, scaling: float = 1.0):
-    ang = positions.float()[:, None] * inv_freq.float()[None]
+def rope_tables(positions: torch.Tensor, inv_freq: torch.Tensor, scaling: float = 1.0, axes: Optional[torch.Tensor] = None):
+    """``cos, sin [N, d/2]``.  ``positions`` is ``[N]``, or ``[3, N]`` (temporal, height, width) with ``axes [d/2]``
+    naming the stream that rotates each frequency (multi-axis RoPE)."""
+    if positions.dim() == 2:
+        if axes is None:
+            raise ValueError("three position streams need the frequency-to-stream table")
+        per_freq = positions.float().t()[:, axes.long()]                     # [N, d/2]
+        ang = per_freq * inv_freq.float()[None]
+    else:
+        ang = positions.float()[:, None] * inv_freq.float()[None]
     return torch.cos(ang) * scaling, torch.sin(ang) * scaling
 
 
 def qk_norm_rope_reference(x: torch.Tensor, norm_weight: Optional[torch.Tensor], positions: torch.Tensor,
                            inv_freq: torch.Tensor, eps: float, scaling: float = 1.0,
-                           rope_dim: Optional[int] = None) -> torch.Tensor:
+                           rope_dim: Optional[int] = None, axes: Optional[torch.Tensor] = None) -> torch.Tensor:
     xf = x.float()
     if norm_weight is not None:
         xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * norm_weight.float()
     d = x.shape[-1] if rope_dim is None else rope_dim
-    cos, sin = rope_tables(positions, inv_freq, scaling)      # [N, d/2]
+    cos, sin = rope_tables(positions, inv_freq, scaling, axes)      # [N, d/2]
     cos, sin = cos[:, None], sin[:, None]
     x1, x2 = xf[..., : d // 2], xf[..., d // 2: d]
     rot = torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], -1)
@@ -76,8 +84,16 @@ class _QKNormRopeFn(torch.autograd.Function):
 
 
 def qk_norm_rope(x: torch.Tensor, norm_weight: Optional[torch.Tensor], positions: torch.Tensor,
-                 inv_freq: torch.Tensor, eps: float, scaling: float = 1.0) -> torch.Tensor:
-    """``x [N, H, d]`` -> normalised + rotated, same shape and dtype."""
+                 inv_freq: torch.Tensor, eps: float, scaling: float = 1.0, axes: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [N, H, d]`` -> normalised + rotated, same shape and dtype.
+
+    ``positions [3, N]`` with ``axes`` is multi-axis RoPE.  Rows whose three streams agree (all text) are exactly
+    ordinary RoPE and take the fused kernel; rows with distinct streams use the fp32 statement."""
+    if positions.dim() == 2:
+        if bool((positions[0] == positions[1]).all() & (positions[0] == positions[2]).all()):
+            positions = positions[0]
+        else:
+            return qk_norm_rope_reference(x, norm_weight, positions, inv_freq, eps, scaling, axes=axes)
     if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] in (64, 128, 256) and x.numel():
         holder = norm_weight if isinstance(norm_weight, torch.nn.Parameter) else None
         return _QKNormRopeFn.apply(x.contiguous(), norm_weight, positions.contiguous().to(torch.int32),

@@ -98,6 +98,90 @@ def estimate_memory(draft: dict, flat: Dict[str, Any], algorithm: str, shard: in
             "ring_bytes": ring, "estimated_total": total, "hbm_bytes": HBM_BYTES, "fits": total < 0.9 * HBM_BYTES}
 
 
+GPUS_PER_NODE = 8
+
+
+def validate_scope(flat: Dict[str, Any], draft: dict, algorithm: str, policy: dict, ffn: dict) -> List[str]:
+    """What this framework can run, checked before anything starts; returns notes for decisions it made on the way.
+
+    The rules are the ones a recipe can violate here (reference: aspec/planning.py:797-1238, whose checks about Ray
+    placement, the serving engine's parallelism and the store's transports have no counterpart in this process model):
+    GPU budget of one node, divisibility of every parallel degree, which attention variants each sequence-parallel
+    scheme covers, engine / dataset prerequisites, and schedule arithmetic."""
+    notes: List[str] = []
+    g = flat.get
+    world = int(flat["world_size"])
+    engine = g("inference_engine_type")
+    if engine not in ("native", "offline", "synthetic"):
+        raise ValueError(f"inference.inference_engine_type {engine!r} is not available: use native (in-framework Target), "
+                         "offline (stored features) or synthetic")
+    targets = int(g("inference_num_gpus") or 0) if engine == "native" else 0
+    if int(g("training_num_nodes", 1) or 1) != 1:
+        raise ValueError("training.training_num_nodes must be 1: processes are started on this node only")
+    if world < 1:
+        raise ValueError("at least one Draft GPU is needed")
+    if engine == "native" and targets < 1:
+        raise ValueError("the in-framework Target needs inference.inference_num_gpus >= 1")
+    if world + targets > GPUS_PER_NODE:
+        raise ValueError(f"{targets} Target + {world} Draft GPUs exceed the {GPUS_PER_NODE} GPUs of one node")
+    if engine == "offline" and not g("offline_feature_dir"):
+        raise ValueError("inference_engine_type=offline needs inference.offline.feature_dir")
+    per_engine = int(g("inference_num_gpus_per_engine", 1) or 1)
+    if engine == "native" and targets % per_engine:
+        raise ValueError(f"inference_num_gpus ({targets}) must be a multiple of inference_num_gpus_per_engine ({per_engine})")
+    if g("eval_data_path") and int(g("eval_interval") or 0) <= 0:
+        notes.append("dataset.eval_data_path is set but eval_interval is 0: evaluation never runs")
+    if int(g("micro_batch_size", 1)) < 1 or int(g("draft_accumulation_steps", 1)) < 1:
+        raise ValueError("micro_batch_size and draft_accumulation_steps must be positive")
+    # -- sequence / context parallel schemes ---------------------------------------------------------------
+    u, r = int(g("sp_ulysses_size", 1) or 1), int(g("sp_ring_size", 1) or 1)
+    cp = int(g("draft_context_parallel_size", 1) or 1)
+    eagle = algorithm in ("eagle3", "eagle4")
+    if u * r > 1:
+        if eagle:
+            heads, kv = int(draft["num_attention_heads"]), int(draft["num_key_value_heads"])
+            if heads % u or kv % u:
+                raise ValueError(f"sp_ulysses_size ({u}) must divide the attention head counts ({heads}, {kv})")
+        elif algorithm == "mtp":
+            raise ValueError("native-MTP training is not sharded over sequences: set sp_ulysses_size = sp_ring_size = 1")
+        else:
+            notes.append(f"block-drafting algorithms shard the context by ownership (direct context parallelism): "
+                         f"sp_ulysses_size x sp_ring_size = {u * r} is taken as draft_context_parallel_size")
+    if cp > 1 and not eagle:
+        kinds = set(policy.get("layer_types") or [])
+        unsupported = kinds - {"full_attention", "sliding_attention", "deepseek_sparse_attention"}
+        if unsupported:
+            raise ValueError(f"context parallelism covers dense, sliding-window and DSA layers, not {sorted(unsupported)}")
+        if "deepseek_sparse_attention" in kinds and draft.get("dsa_training_stage") == "indexer_warmup":
+            raise ValueError("the DSA indexer warm-up stage runs with draft_context_parallel_size=1")
+    if draft.get("mtp_conditioning") and cp != 1:
+        raise ValueError("MTP conditioning requires draft_context_parallel_size=1")
+    # -- head shapes the attention kernels cover ---------------------------------------------------------------
+    max_pos = draft.get("max_position_embeddings")
+    if max_pos and int(flat["max_seq_length"]) > int(max_pos) and not (draft.get("rope_scaling") or draft.get("rope_parameters")):
+        notes.append(f"max_seq_length {flat['max_seq_length']} exceeds the Draft's max_position_embeddings {max_pos} "
+                     "without a RoPE scaling rule")
+    # -- schedule ---------------------------------------------------------------------------------------------
+    steps = g("num_train_steps")
+    if steps is not None and int(steps) < 0:
+        raise ValueError("training.num_train_steps must not be negative")
+    warm, drain = int(g("performance_warmup_steps") or 0), int(g("performance_drain_steps") or 0)
+    if g("performance_measurement_required") and steps and int(steps) <= warm + drain:
+        notes.append(f"debug.performance_measurement_required needs more than {warm + drain} optimizer steps "
+                     f"(performance_warmup_steps + performance_drain_steps), the run has {steps}: it will end without a "
+                     "valid steady window and fail after writing its evidence")
+    save, keep = int(g("save_interval") or 0), g("max_checkpoints")
+    if keep is not None and int(keep) < 0:
+        raise ValueError("training.max_checkpoints must not be negative")
+    if g("continual_training") and not g("load_path"):
+        notes.append("training.continual_training is set without training.load_path: the run starts from random weights "
+                     "unless --load-path is given on the command line")
+    if save and steps and int(steps) and save > int(steps) and g("save_final_checkpoint") is False:
+        notes.append(f"save_interval {save} is larger than the run ({steps} steps) and the final checkpoint is off: "
+                     "nothing will be saved")
+    return notes
+
+
 def compile_execution_plan(config: Config) -> ExecutionPlan:
     flat = vars(config_to_flat_args(config)).copy()
     draft = _load_draft(flat)
@@ -140,6 +224,8 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
     align = context_shard_alignment(policy) if algorithm != "mtp" else 1
     if cp > 1 and int(flat["max_seq_length"]) // max(align, 1) < cp:
         raise ValueError("sequence too short to give every context-parallel rank an aligned shard")
+    for note in validate_scope(flat, draft, algorithm, policy, ffn):
+        caps.append(CapabilityDecision("scope", "note", note))
     # ---- capability decisions ------------------------------------------------------------------
     head_dim = draft.get("head_dim") or draft["hidden_size"] // draft["num_attention_heads"]
     mla = draft.get("attention_mode") == "mla" or draft.get("model_type") in ("k3_dspark", "deepseek_v3")

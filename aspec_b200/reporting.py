@@ -41,6 +41,11 @@ def build_run_report(run_dir: str) -> dict:
             "throughput_window": summary.get("window"), "committed_work": len(ledger.get("committed_work_ids", [])),
             "dropped_tail_samples": summary.get("dropped_tail_samples"), "latest_checkpoint": latest,
             "capabilities": plan.get("capabilities"), "capabilities_observed": observed or None,
+            "capabilities_activated": ev.get("capabilities_activated") or None,
+            "dataset_admission": (ev.get("sections") or {}).get("dataset_admission"),
+            "actor_initialization": (ev.get("sections") or {}).get("actor_initialization"),
+            "cluster_preflight_state": ((ev.get("sections") or {}).get("cluster_preflight") or {}).get("state"),
+            "cleanup": (ev.get("sections") or {}).get("cleanup"),
             "accelerators": ev.get("accelerators")}
 
 
@@ -52,6 +57,12 @@ def render_report(report: dict) -> str:
     w = report.get("throughput_window") or {}
     if w.get("valid"):
         lines.append(f"throughput {w['tokens_per_second']:.1f} input tokens/s over {w['steps']} steady updates")
+    adm = report.get("dataset_admission") or {}
+    if adm:
+        lines.append(f"dataset    {adm.get('admitted')} of {adm.get('source_rows')} source rows admitted"
+                     + (f", rejected {adm['rejected']}" if adm.get("rejected") else ""))
+    for name, act in (report.get("capabilities_activated") or {}).items():
+        lines.append(f"activated  {name}: {act.get('planned') or ''} ({act.get('rule')})")
     for p in report.get("problems", []):
         lines.append(f"PROBLEM    {p}")
     return "\n".join(lines)

@@ -7,7 +7,8 @@ on the real path (a Target-only prefill probe and a Draft-only training probe, e
 own engines), the balanced allocation is predicted from those rates, and the final choice is left to bounded
 end-to-end runs of the top candidates, whose evidence files are ranked.
 
-``python -m aspec_b200.topology plan --config R.yaml`` prints the study; ``rank --runs DIR...`` ranks finished
+``python -m aspec_b200.topology run --config R.yaml --gpus 8 --out DIR`` does all of that automatically
+(``topology_runner.run_study``); ``plan --config R.yaml`` prints the study; ``rank --runs DIR...`` ranks finished
 candidate runs by their steady-window tokens/s; ``predict --target-rate X --draft-rate Y --gpus N`` applies the
 balance rule to measured rates.
 """
@@ -126,7 +127,22 @@ def main(argv=None) -> int:
     pred.add_argument("--gpus", type=int, default=8)
     rank = sub.add_parser("rank")
     rank.add_argument("--runs", nargs="+", required=True)
+    run = sub.add_parser("run", help="calibrate, run the best candidates end to end and rank them")
+    run.add_argument("--config", required=True)
+    run.add_argument("--gpus", type=int, default=8)
+    run.add_argument("--out", required=True)
+    run.add_argument("--steps", type=int, default=24)
+    run.add_argument("--warmup", type=int, default=4)
+    run.add_argument("--top", type=int, default=3)
+    run.add_argument("--timeout", type=float, default=1800.0)
+    run.add_argument("overrides", nargs="*")
     a = ap.parse_args(argv)
+    if a.cmd == "run":
+        from aspec_b200.topology_runner import run_study
+        res = run_study(a.config, a.gpus, a.out, steps=a.steps, warmup=a.warmup, top=a.top, overrides=a.overrides,
+                        timeout=a.timeout)
+        print(json.dumps({k: res[k] for k in ("chosen", "chosen_overrides", "ranking", "calibration", "prediction_error")}, indent=2))
+        return 0 if res["chosen"] else 1
     if a.cmd == "plan":
         from aspec_b200.config.train_config import load_config
         print(json.dumps(compile_topology_study(load_config(a.config, a.overrides), a.gpus, target_rate=a.target_rate,

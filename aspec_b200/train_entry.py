@@ -126,7 +126,14 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
         controller = TrainingController(args, dp_size=dp, consumers_per_row=cp, algorithm=algorithm)
         n = controller.load_dataset(dataset)
         if evidence:
-            evidence.record("dataset_admission", {"samples": n, "fingerprint": controller.dataset_fingerprint()})
+            stats = getattr(controller, "admission", None) or {}
+            evidence.record_dataset_admission(dataset_size=n, admission={"admitted": n, "fingerprint": controller.dataset_fingerprint(),
+                                                                         **stats})
+            evidence.record_actor_initialization(
+                training_actors=[{"name": f"trainer{r}", "device": str(draft_devs[r]), "pid": getattr(t, "pid", None)}
+                                 for r, t in enumerate(trainers)],
+                inference_engines=[{"name": f"engine{i}", "device": str(target_devs[i]) if i < len(target_devs) else "cpu",
+                                    "pid": getattr(e, "pid", None)} for i, e in enumerate(engines)])
         if flat.get("load_path"):
             # collective inside the trainer group: start it on every rank before waiting for any
             futs = [t.call_async("load_model", flat["load_path"], bool(flat.get("continual_training"))) for t in trainers]
@@ -238,9 +245,11 @@ def main(argv=None) -> int:
     try:
         from aspec_b200.preflight import run_cluster_preflight
         pre = run_cluster_preflight(flat)
-        evidence.record("cluster_preflight", pre)
         with open(os.path.join(flat["output_dir"], "cluster-preflight.json"), "w") as f:
-            json.dump(pre, f, indent=2)
+            json.dump(pre, f, indent=2, default=str)
+        if pre.get("state") == "failed":
+            raise RuntimeError(f"node preflight failed: {pre['problems']} (details in cluster-preflight.json)")
+        evidence.record_cluster_preflight(pre)
         if a.preflight_only:
             evidence.complete({"preflight_only": True})
             return 0

@@ -17,6 +17,12 @@ which writes ``work_state.json``, verifies every required file (all RNG ranks in
 ``complete.json`` and renames staging -> final atomically.  ``load`` refuses a checkpoint without
 ``complete.json`` and, for exact resume, any change of logical topology / objective / model semantics;
 ``continual_training`` loads weights only and re-derives the fp32 masters.
+
+The directory layout and the two-phase protocol are the reference's; the file contents are this framework's own (schema
+tags under ``schema``, the optimizer as flat ``master / exp_avg / exp_avg_sq`` maps by parameter name, the scheduler as
+one ``last_epoch``).  Training checkpoints are therefore not interchangeable with the reference's in either direction;
+what is interchangeable are the exports (``commands/convert_to_hf.py``: HF and serving layouts with the reference's
+tensor names) and weights-only starts from such an export.
 """
 from __future__ import annotations
 
@@ -121,7 +127,9 @@ def validate_exact_resume_topology(saved: Mapping[str, Any], current: Mapping[st
 
 
 def _rng_state() -> dict:
-    state = {"schema": RNG_SCHEMA, "torch": torch.get_rng_state(), "python": random.getstate()}
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    state = {"schema": RNG_SCHEMA, "rank": _rank(), "world_size": world,
+             "torch": torch.get_rng_state(), "python": random.getstate()}
     if torch.cuda.is_available():
         state["cuda"] = torch.cuda.get_rng_state()
     try:
@@ -135,6 +143,12 @@ def _rng_state() -> dict:
 def _restore_rng(state: dict) -> None:
     if state.get("schema") != RNG_SCHEMA:
         raise ValueError("unknown RNG state schema")
+    # a generator stream belongs to one rank of one world size: a file moved between ranks would replay another
+    # rank's anchors (files written before the two fields existed carry neither and are taken as they are)
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    if "rank" in state and (state["rank"] != _rank() or state.get("world_size") != world):
+        raise ValueError(f"RNG state of rank {state['rank']} / world {state.get('world_size')} offered to "
+                         f"rank {_rank()} / world {world}")
     torch.set_rng_state(state["torch"])
     random.setstate(state["python"])
     if "cuda" in state and torch.cuda.is_available():

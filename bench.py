@@ -262,6 +262,7 @@ def run_ours(args):
                "ms_per_step": ms2 / args.steps, "loss": last.get("train/avg_loss")}
     collective = ("none (1 GPU)" if world == 1 else
                   "NCCL all-reduce of the flat fp32 gradient + replicated AdamW" if args.baseline else
+                  "sharded step over gloo collectives (CPU run)" if not cuda else
                   "peer-memory sharded step: shard_reduce_sumsq (peer loads) + shard_adamw_scatter (peer stores); "
                   "NCCL only for three scalar all-reduces per update")
     line = None
@@ -297,11 +298,40 @@ def run_ours(args):
         dist.destroy_process_group()
     if rank == 0:
         if world > 1 and cuda and not args.no_online and not args.small:
-            line["online"] = online_child(args)
+            line["online"] = online_with_split_search(args, draft_rate=value / world)
         print(json.dumps(line), flush=True)
 
 
-def online_child(args) -> dict:
+def online_with_split_search(args, draft_rate: float) -> dict:
+    """The online run at N/2 Target + N/2 Draft GPUs, then - when the measured service rates say another split is
+    faster - at the split the topology search picks.  The better measured run is reported; both are listed under
+    ``split_search`` so the choice can be checked."""
+    from aspec_b200.topology import legal_splits, predict
+    first = online_child(args)
+    tokens, busy = first.get("target_tokens") or [], first.get("target_busy_seconds") or []
+    per_gpu = sorted(t / b for t, b in zip(tokens, busy) if t and b)
+    search = {"draft_tokens_per_s_per_gpu": draft_rate, "rule": "min(T x target rate, D x draft rate) over the legal splits",
+              "runs": [{"split": f"{first.get('targets')}T+{first.get('drafts')}D", "value": first.get("value")}]}
+    first["split_search"] = search
+    if not per_gpu or not first.get("value"):
+        return first
+    target_rate = per_gpu[len(per_gpu) // 2]
+    search["target_tokens_per_s_per_gpu"] = target_rate
+    ranked = sorted(((predict(target_rate, draft_rate, t, d)[0], t, d) for t, d in legal_splits(args.gpus)), reverse=True)
+    search["predicted"] = [{"split": f"{t}T+{d}D", "tokens_per_s": p} for p, t, d in ranked[:3]]
+    best_p, best_t, best_d = ranked[0]
+    here = predict(target_rate, draft_rate, first["targets"], first["drafts"])[0]
+    if best_t == first["targets"] or best_p < 1.05 * here:
+        return first
+    second = online_child(args, targets=best_t)
+    search["runs"].append({"split": f"{best_t}T+{best_d}D", "value": second.get("value"), "error": second.get("error")})
+    if second.get("value") and second.get("ledger_validated") and second["value"] > first["value"]:
+        second["split_search"] = search
+        return second
+    return first
+
+
+def online_child(args, targets: int = 0) -> dict:
     """Run ``--mode online`` on the node's N GPUs in a child process (this process keeps only its CUDA context)."""
     time.sleep(3.0)                         # the other ranks are exiting and releasing their GPUs
     env = {k: v for k, v in os.environ.items()
@@ -311,7 +341,8 @@ def online_child(args) -> dict:
                         "GROUP_WORLD_SIZE", "ROLE_WORLD_SIZE", "TORCHELASTIC_ERROR_FILE")}
     cmd = [sys.executable, os.path.abspath(__file__), "--mode", "online", "--gpus", str(args.gpus),
            "--steps", str(args.online_steps), "--warmup", str(args.online_warmup), "--accum", str(args.accum),
-           "--layers", str(args.layers), "--min-len", str(args.min_len), "--max-len", str(args.max_len)]
+           "--layers", str(args.layers), "--min-len", str(args.min_len), "--max-len", str(args.max_len),
+           "--targets", str(targets or args.targets or 0)]
     t0 = time.perf_counter()
     try:
         res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=args.online_timeout, cwd=ROOT)
@@ -378,7 +409,7 @@ def run_online(args) -> dict:
             "steady_steps": w.get("steps"), "steady_tokens": w.get("tokens"), "steady_seconds": w.get("seconds"),
             "documents_per_update": args.accum * D, "ledger_validated": summary["ledger"]["validated"],
             "vs_baseline_8gpu": (w.get("tokens_per_second") / BASELINE_8GPU) if (w.get("valid") and n == 8) else None,
-            "target_busy_seconds": [e.get("busy_seconds") for e in eng],
+            "target_busy_seconds": [e.get("busy_seconds") for e in eng], "target_tokens": [e.get("tokens") for e in eng],
             "timing": "steady window: from completion of warm-up update W to the last optimizer completion; each "
                       "completion is observed after a device-to-host read on every Draft rank"}
 

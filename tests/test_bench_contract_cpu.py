@@ -35,5 +35,30 @@ def test_two_ranks_under_torchrun_print_one_line_with_the_aggregate():
     res = _run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
                 "--master-port", str(29600 + os.getpid() % 300), "bench.py", "--gpus", "2", "--small", "--steps", "1", "--warmup", "1",
                 "--no-e2e"], {"CUDA_VISIBLE_DEVICES": ""})
-    assert res["n_gpus"] == 2 and res["config"]["parallelism"] == "dp2" and res["config"]["global_batch"] == 32
+    assert res["n_gpus"] == 2 and res["config"]["parallelism"] == "dp2+sharded_optimizer" and res["config"]["global_batch"] == 32
     assert res["vs_baseline"] is None and "length sequence of the 1-GPU run" in res["config"]["dp_balance"]
+
+
+def test_online_split_search_runs_the_predicted_split_and_keeps_the_measured_best(monkeypatch):
+    import argparse
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    asked = []
+
+    def fake_child(args, targets=0):
+        t = targets or args.gpus // 2
+        d = args.gpus - t
+        asked.append(t)
+        value = min(64e3 * t, 96e3 * d) * 0.9
+        return {"value": value, "targets": t, "drafts": d, "ledger_validated": True,
+                "target_tokens": [64e3 * 20] * t, "target_busy_seconds": [20.0] * t}
+    monkeypatch.setattr(bench, "online_child", fake_child)
+    out = bench.online_with_split_search(argparse.Namespace(gpus=8, targets=0), draft_rate=96e3)
+    assert asked == [4, 5] and out["targets"] == 5 and out["drafts"] == 3
+    assert [r["split"] for r in out["split_search"]["runs"]] == ["4T+4D", "5T+3D"]
+    assert out["split_search"]["predicted"][0]["split"] == "5T+3D"
+    asked.clear()
+    out = bench.online_with_split_search(argparse.Namespace(gpus=4, targets=0), draft_rate=96e3)
+    assert asked == [2] and out["targets"] == 2                       # 2T+2D is already the balanced split of four GPUs

@@ -119,3 +119,15 @@ def test_rotation_keeps_newest(tmp_path):
         (root / f"iter_{i:07d}").mkdir(parents=True)
     assert ckpt.rotate(str(tmp_path), keep_last=2, protect={1}) == [2]
     assert sorted(os.listdir(root)) == ["iter_0000001", "iter_0000003", "iter_0000004"]
+
+
+def test_rng_file_is_bound_to_its_rank_and_world():
+    import pytest
+    from aspec_b200.training import checkpoint as C
+    state = C._rng_state()
+    assert state["rank"] == 0 and state["world_size"] == 1
+    C._restore_rng(state)
+    with pytest.raises(ValueError, match="offered to rank 0"):
+        C._restore_rng(dict(state, rank=1, world_size=2))
+    legacy = {k: v for k, v in state.items() if k not in ("rank", "world_size")}
+    C._restore_rng(legacy)

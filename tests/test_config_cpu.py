@@ -101,3 +101,59 @@ def test_auto_config_roundtrip(tmp_path):
     with pytest.raises(ValueError):
         DSparkConfig(markov_rank=0, enable_confidence_head=True)
     json.dumps(cfg.to_dict())
+
+
+def test_rope_llama3_dynamic_and_multi_axis_families():
+    import math
+    import torch
+    from aspec_b200.config.rope import mrope_axis_of_frequency
+    from aspec_b200.ops.rope import qk_norm_rope, qk_norm_rope_reference
+    d, theta = 128, 5e5
+    base, _ = rope_inverse_frequencies(d, {"rope_theta": theta, "rope_type": "default"})
+    p = {"rope_theta": theta, "rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+         "original_max_position_embeddings": 8192}
+    got, att = rope_inverse_frequencies(d, p)
+    assert att == 1.0
+    for f, g in zip(base, got):
+        wave = 2 * math.pi / f
+        if wave < 8192 / 4.0:
+            assert g == f
+        elif wave > 8192 / 1.0:
+            assert g == pytest.approx(f / 8.0)
+        else:
+            assert f / 8.0 <= g <= f
+    assert got[0] == base[0] and got[-1] == pytest.approx(base[-1] / 8.0)
+    try:                                         # the same rule as stated by the transformers library, where it is importable
+        from transformers import LlamaConfig
+        from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+        hf = LlamaConfig(hidden_size=d * 4, num_attention_heads=4, max_position_embeddings=131072,
+                         rope_parameters=dict(p, rope_type="llama3"))
+        want, _ = ROPE_INIT_FUNCTIONS["llama3"](hf, "cpu")
+        assert torch.allclose(torch.tensor(got), want.float(), rtol=1e-5)
+    except (ImportError, TypeError, KeyError, AttributeError):
+        pass
+    # dynamic NTK: unchanged inside the trained window, a larger base beyond it
+    dyn = {"rope_theta": 1e4, "rope_type": "dynamic", "factor": 2.0, "original_max_position_embeddings": 2048}
+    same, _ = rope_inverse_frequencies(64, dict(dyn, sequence_length=2048))
+    plain, _ = rope_inverse_frequencies(64, {"rope_theta": 1e4, "rope_type": "default"})
+    assert same == plain
+    longer, _ = rope_inverse_frequencies(64, dict(dyn, sequence_length=8192))
+    grown = 1e4 * ((2.0 * 8192 / 2048) - 1.0) ** (64 / 62)
+    assert longer[1] == pytest.approx(grown ** (-2 / 64)) and longer[-1] < plain[-1]
+    with pytest.raises(ValueError):
+        rope_inverse_frequencies(64, {"rope_theta": 1e4, "rope_type": "longrope", "factor": 2.0})
+    # multi-axis: equal streams are ordinary RoPE; distinct streams rotate each frequency band by its own stream
+    axes = mrope_axis_of_frequency(16, [2, 3, 3])
+    assert axes == [0, 0, 1, 1, 1, 2, 2, 2]
+    with pytest.raises(ValueError):
+        mrope_axis_of_frequency(16, [2, 3])
+    x = torch.randn(5, 2, 16)
+    inv = torch.tensor(rope_inverse_frequencies(16, {"rope_theta": 1e4, "rope_type": "mrope"})[0])
+    pos = torch.arange(5)
+    a = qk_norm_rope(x, None, torch.stack([pos, pos, pos]), inv, 0.0, 1.0, torch.tensor(axes))
+    assert torch.equal(a, qk_norm_rope_reference(x, None, pos, inv, 0.0))
+    streams = torch.stack([pos, pos + 3, pos * 2])
+    b = qk_norm_rope(x, None, streams, inv, 0.0, 1.0, torch.tensor(axes))
+    for band, axis in ((slice(0, 2), 0), (slice(2, 5), 1), (slice(5, 8), 2)):
+        one = qk_norm_rope_reference(x, None, streams[axis], inv, 0.0)
+        assert torch.allclose(b[..., band], one[..., band]) and torch.allclose(b[..., 8:][..., band], one[..., 8:][..., band])

@@ -187,3 +187,49 @@ def test_workload_builders_are_deterministic_and_load_as_training_samples(tmp_pa
     assert mixed[1]["input_ids"] == rows[1]["input_ids"][:40] and mixed[1]["loss_tokens"] == 24 and mixed[0]["loss_tokens"] == 0
     samples = load_training_samples(str(tmp_path / "m.jsonl"), {"max_seq_length": 64})
     assert len(samples) >= 4                                            # rows without supervised tokens may be dropped
+
+
+def test_kimi_and_minimax_dialects_format_history_tools_and_images():
+    from aspec_b200.data.parse import create_parser
+    from aspec_b200.data.template import TEMPLATE_REGISTRY
+    tok = Tok()
+    convo = [
+        {"role": "user", "content": [{"type": "text", "text": "look "}, {"type": "image"}]},
+        {"role": "assistant", "content": "<think>old thought</think>first", "tool_calls": [
+            {"id": "call_1", "function": {"name": "add", "arguments": "{\"a\": 1, \"b\": [2]}"}}]},
+        {"role": "tool", "content": "3", "tool_call_id": "call_1"},
+        {"role": "tool", "content": "4"},
+        {"role": "user", "content": "and now?"},
+        {"role": "assistant", "content": "answer", "reasoning_content": "new thought"},
+    ]
+    kimi = create_parser(tok, TEMPLATE_REGISTRY.get("kimi-k25-vlm"))
+    text = kimi.format(convo)
+    assert text.startswith("<|im_user|>user<|im_middle|>look <|media_begin|>image<|media_content|><|media_pad|><|media_end|>\n<|im_end|>")
+    # history turn: reasoning dropped, an empty block in its place, the call section after the text
+    assert ("<|im_assistant|>assistant<|im_middle|><think></think>first<|tool_calls_section_begin|><|tool_call_begin|>call_1"
+            "<|tool_call_argument_begin|>{\"a\": 1, \"b\": [2]}<|tool_call_end|><|tool_calls_section_end|><|im_end|>") in text
+    assert "<|im_system|>tool<|im_middle|>## Return of call_1\n3<|im_end|><|im_system|>tool<|im_middle|>4<|im_end|>" in text
+    assert text.endswith("<|im_assistant|>assistant<|im_middle|><think>new thought</think>answer<|im_end|>")
+    assert "old thought" not in text
+    assert kimi.format(convo[:1], add_generation_prompt=True).endswith("<|im_assistant|>assistant<|im_middle|><think>")
+    assert "<|image|>" in kimi.format(convo[:1], expand_media_tokens=False)
+    ids, mask = kimi.parse(convo, 4096)
+    assert ids.shape == mask.shape and 0 < int(mask.sum()) < len(ids)
+    _, last = kimi.parse(convo, 4096, last_turn_only=True)
+    assert 0 < int(last.sum()) < int(mask.sum())
+    supervised = "".join(chr(int(t)) for t, m in zip(ids, last) if m and t < 1000)
+    assert supervised.startswith("new thought") or "answer" in supervised
+
+    mm = create_parser(tok, TEMPLATE_REGISTRY.get("minimax-m2"))
+    text = mm.format(convo)
+    assert text.startswith("]~!b[]~b]system\nYou are a helpful assistant. Your name is MiniMax-M2.5")
+    assert "]~b]user\nlook ]<]start of image[>[]<]vision pad[>[]<]end of image[>[\n[e~[\n" in text
+    assert ("]~b]ai\nfirst\n<minimax:tool_call>\n<invoke name=\"add\">\n<parameter name=\"a\">1</parameter>\n"
+            "<parameter name=\"b\">[2]</parameter>\n</invoke>\n</minimax:tool_call>[e~[\n") in text
+    assert "]~b]tool\n<response>3</response>\n<response>4</response>[e~[\n" in text          # one tool turn for both results
+    assert text.endswith("]~b]ai\n<think>\nnew thought\n</think>\n\nanswer[e~[\n") and "old thought" not in text
+    own_system = mm.format([{"role": "system", "content": "be brief"}] + convo[4:])
+    assert own_system.startswith("]~!b[]~b]system\nbe brief[e~[\n]~b]user\nand now?[e~[\n")
+    ids, mask = mm.parse(convo, 4096)
+    assert 0 < int(mask.sum()) < len(ids)
+    assert mm.format(convo[:1], add_generation_prompt=True).endswith("]~b]ai\n<think>\n")

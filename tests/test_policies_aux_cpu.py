@@ -263,3 +263,43 @@ def test_recipes_command_list_show_plan(capsys):
     assert "dspark_tiny" in capsys.readouterr().out
     assert recipes.main(["plan", "quickstart_tiny"]) == 0
     assert "sha256:" in capsys.readouterr().out
+
+
+def test_typed_evidence_sections_are_checked_against_the_plan(tmp_path):
+    from types import SimpleNamespace
+    import pytest
+    from aspec_b200.evidence import EvidenceError, RunEvidenceRecorder
+    caps = [SimpleNamespace(subsystem="attention", choice="tcgen05_interval_flash", reason=""),
+            SimpleNamespace(subsystem="feature_transport", choice="peer_memory", reason=""),
+            SimpleNamespace(subsystem="data_parallel", choice="REPLICATE", reason="")]
+    plan = SimpleNamespace(plan_id="sha256:aa", capabilities=caps, policy={"draft_gpus": 2, "target_gpus": 1})
+    rec = RunEvidenceRecorder(plan, str(tmp_path))
+    with pytest.raises(EvidenceError):       # 10 source rows cannot be 7 admitted + 2 rejected
+        rec.record_dataset_admission(dataset_size=7, admission={"source_rows": 10, "admitted": 7, "rejected": {"too_long": 2}})
+    rec.record_dataset_admission(dataset_size=7, admission={"source_rows": 10, "admitted": 7, "rejected": {"too_long": 3}, "fingerprint": "f"})
+    with pytest.raises(EvidenceError):       # the plan has two Draft trainers
+        rec.record_actor_initialization(training_actors=[{"name": "t0", "device": "cuda:1"}], inference_engines=[{"name": "e0", "device": "cuda:0"}])
+    with pytest.raises(EvidenceError):       # two processes on one GPU
+        rec.record_actor_initialization(training_actors=[{"name": "t0", "device": "cuda:1"}, {"name": "t1", "device": "cuda:1"}],
+                                        inference_engines=[{"name": "e0", "device": "cuda:0"}])
+    rec.record_actor_initialization(training_actors=[{"name": "t0", "device": "cuda:1"}, {"name": "t1", "device": "cuda:2"}],
+                                    inference_engines=[{"name": "e0", "device": "cuda:0"}])
+    with pytest.raises(EvidenceError):
+        rec.record_cluster_preflight({"state": "failed", "problems": ["peer_access"]})
+    with pytest.raises(EvidenceError):
+        rec.record_cluster_preflight({"state": "validated", "gpu_count": 2})
+    rec.record_cluster_preflight({"state": "validated", "gpu_count": 8})
+    with pytest.raises(EvidenceError):       # committed work without a validated ledger is not evidence
+        rec.record_training({"completed_steps": 3, "ledger": {"validated": False}})
+    rec.observe_capability("attention", {"tcgen05_interval_flash": 12, "dense_mask_fp32": 1})
+    rec.record_training({"completed_steps": 3, "ledger": {"validated": True, "committed": 48}})
+    with pytest.raises(EvidenceError):
+        rec.record_cleanup({"order": ["trainers", "engines"]})
+    rec.record_cleanup({"order": ["manager", "engines", "trainers"], "engines_observed_dead": True})
+    rec.complete({"completed_steps": 3})
+    doc = json.loads((tmp_path / "evidence.json").read_text())
+    assert doc["phase"] == "completed" and doc["sections"]["dataset_admission"]["rejected"] == {"too_long": 3}
+    act = doc["capabilities_activated"]
+    assert act["attention"]["launches"] == 12 and act["feature_transport"]["optimizer_steps_observed"] == 3
+    assert act["data_parallel"]["draft_gpus"] == 2 and act["work_ledger"]["committed"] == 48
+    assert doc["sections"]["actor_initialization"]["training_actor_count"] == 2

@@ -52,3 +52,32 @@ def test_bundled_draft_config_builds(path):
     assert sum(p.numel() for p in model.parameters()) > 0
     again = AutoDraftModelConfig.from_dict(cfg.to_dict())
     assert again.to_dict() == cfg.to_dict()
+
+
+def _plan(recipe, *overrides):
+    return compile_execution_plan(load_config(os.path.join(ROOT, "recipes", recipe), list(overrides)))
+
+
+@pytest.mark.parametrize("recipe,overrides,message", [
+    ("qwen3_8b_dspark.yaml", ["training.training_num_gpus_per_node=8", "inference.inference_num_gpus=4"], "exceed the 8 GPUs"),
+    ("qwen3_8b_dspark.yaml", ["inference.inference_engine_type=offline"], "feature_dir"),
+    ("qwen3_8b_dspark.yaml", ["inference.inference_engine_type=remote_http"], "must be native, offline or synthetic"),
+    ("qwen3_8b_dspark.yaml", ["training.training_num_nodes=2"], "training_num_nodes"),
+    ("qwen3_8b_dspark.yaml", ["inference.inference_num_gpus=3", "inference.inference_num_gpus_per_engine=2"], "multiple of"),
+    ("qwen3_8b_eagle3.yaml", ["training.sp_ulysses_size=3", "training.training_num_gpus_per_node=3"], "must divide the attention head counts"),
+    ("qwen3_5_9b_mtp.yaml", ["training.sp_ring_size=2", "training.training_num_gpus_per_node=2"], "not sharded over sequences"),
+])
+def test_the_planner_refuses_what_cannot_run(recipe, overrides, message):
+    with pytest.raises(ValueError, match=message):
+        _plan(recipe, *overrides)
+
+
+def test_scope_notes_are_recorded_as_decisions():
+    plan = _plan("qwen3_8b_dspark.yaml", "training.sp_ulysses_size=2", "training.training_num_gpus_per_node=2",
+                 "inference.inference_num_gpus=1")
+    notes = [c.reason for c in plan.capabilities if c.subsystem == "scope"]
+    assert any("direct context parallelism" in n for n in notes)
+    assert plan.policy["context_parallel"] == 2
+    short = _plan("qwen3_8b_dspark.yaml", "debug.performance_measurement_required=true", "debug.performance_warmup_steps=4",
+                  "debug.performance_drain_steps=2", "training.num_train_steps=6")
+    assert any("needs more than 6 optimizer steps" in c.reason for c in short.capabilities if c.subsystem == "scope")

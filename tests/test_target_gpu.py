@@ -26,3 +26,32 @@ def test_target_prefill_matches_cpu_reference_and_mirrors():
         assert (a - b).abs().max() < 0.08 * max(1.0, b.abs().max().item()), key
     # the captured layers were written by the GEMM epilogue into the sink (strided column blocks)
     assert torch.equal(got["hidden_states"], sink.hidden_states)
+
+
+def test_moe_target_prefill_matches_cpu_reference():
+    """Ling-style MoE Target (sigmoid router, expert groups, shared expert, one leading dense layer): the grouped
+    expert kernels against the per-expert fp32 statement on CPU."""
+    from aspec_b200.models.target.dense import DenseTarget, TargetConfig
+    from aspec_b200.ops.gemm import check_status
+    cfg = TargetConfig(model_type="ling_moe", hidden_size=256, intermediate_size=512, num_hidden_layers=3, num_attention_heads=2,
+                       num_key_value_heads=1, head_dim=128, vocab_size=1000, num_experts=16, num_experts_per_tok=4,
+                       moe_intermediate_size=128, num_shared_experts=1, moe_shared_expert_intermediate_size=128,
+                       n_group=4, topk_group=2, routed_scaling_factor=2.5, first_k_dense_replace=1)
+    torch.manual_seed(0)
+    ref = DenseTarget(cfg).init_random(0, std=0.05)
+    gpu = DenseTarget(cfg).to("cuda", torch.bfloat16)
+    gpu.load_state_dict({k: (v.to(torch.bfloat16) if v.is_floating_point() and "expert_bias" not in k else v)
+                         for k, v in ref.state_dict().items()})
+    ref.load_state_dict({k: v.float() for k, v in gpu.state_dict().items()})
+    assert any(getattr(layer, "is_moe", False) for layer in gpu.layers)
+    lens = [130, 61]
+    ids = torch.randint(0, 1000, (sum(lens),))
+    want = ref.prefill(ids, lens, [0, 2])
+    got = gpu.prefill(ids.cuda(), lens, [0, 2])
+    check_status("cuda")
+    for key in ("hidden_states", "last_hidden_states"):
+        a, b = got[key].float().cpu(), want[key]
+        # a token whose routing flips between the bf16 and fp32 routers differs by a whole expert: judge the bulk
+        err = (a - b).abs()
+        assert err.median() < 0.02 * max(1.0, b.abs().max().item()), key
+        assert (err > 0.1 * max(1.0, b.abs().max().item())).float().mean() < 0.02, key
