@@ -79,6 +79,11 @@ class DebugConfig:
     timeline_output_dir: str = ""
     timeline_run_id: str = ""
     use_pytorch_profiler: bool = False
+    # host-side fault injection for validation runs (never on by default; nothing here touches a GPU):
+    # {"kind": "raise" | "sleep", "step": k, "rank": r, "seconds": s} makes trainer r raise / stall at update k
+    fault_injection: Optional[dict] = None
+    producer_fail_after: Optional[int] = None      # the Target engine raises after this many rows
+    producer_delay_seconds: float = 0.0            # synthetic engine: sleep per row (a slow producer)
 
 
 @dataclass
@@ -473,8 +478,8 @@ def validate_config(c: Config) -> None:
         raise ValueError("training.min_lr must not exceed training.learning_rate")
     if not 0.0 <= t.warmup_ratio < 1.0:
         raise ValueError("training.warmup_ratio must be in [0, 1)")
-    if t.fsdp_strategy not in ("REPLICATE", "FULL_SHARD"):
-        raise ValueError("training.fsdp_strategy must be REPLICATE or FULL_SHARD")
+    if t.fsdp_strategy not in ("REPLICATE", "SHARD_OPTIMIZER", "FULL_SHARD"):
+        raise ValueError("training.fsdp_strategy must be REPLICATE, SHARD_OPTIMIZER or FULL_SHARD")
     if t.fsdp_reduce_dtype not in ("float32", "bfloat16"):
         raise ValueError("training.fsdp_reduce_dtype must be float32 or bfloat16")
     if t.lr_decay_style not in ("constant", "linear", "cosine", "inverse-square-root", "WSD"):

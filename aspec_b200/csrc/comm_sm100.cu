@@ -130,6 +130,62 @@ __global__ void shard_reduce_sumsq_kernel(PeerPtrsF peers, int n_peers, long lon
   }
 }
 
+// ---- flags between ranks, for protocols that never call a library collective.  Every rank owns an array
+// flags[slot * world + writer]; rank w publishes into element (slot, w) of EVERY rank's array, and a rank waits until
+// all `world` elements of one of its own slots reach a value.  Values only grow, so a late waiter still passes.
+struct PeerFlagPtrs {
+  long long* p[8];
+};
+__global__ void flags_signal_kernel(PeerFlagPtrs flags, int n_peers, long long index, long long value) {
+  if (threadIdx.x < n_peers) {
+    __threadfence_system();          // everything this GPU wrote before the launch is visible before the flag
+    asm volatile("st.release.sys.global.s64 [%0], %1;" ::"l"(flags.p[threadIdx.x] + index), "l"(value) : "memory");
+  }
+}
+// One thread per flag; bounded like flag_wait_kernel.  status[0] = kStatusPeerTimeout when any flag stayed low.
+__global__ void flags_wait_all_kernel(const long long* flags, int count, long long value, unsigned long long limit_ns,
+                                      int* status) {
+  if (threadIdx.x >= count) return;
+  const unsigned long long t0 = globaltimer_ns();
+  long long seen;
+  for (;;) {
+    asm volatile("ld.acquire.sys.global.s64 %0, [%1];" : "=l"(seen) : "l"(flags + threadIdx.x) : "memory");
+    if (seen >= value) return;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      if (status) atomicExch(status, kStatusPeerTimeout);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+
+// Parameter all-gather by peer loads: dst[r * shard_vec + i] = shard_r[i] (16-byte vectors); block y = source rank.
+struct PeerPtrsV {
+  const uint4* p[8];
+};
+__global__ void peer_gather_kernel(PeerPtrsV shards, long long shard_vec, uint4* __restrict__ dst) {
+  const uint4* __restrict__ src = shards.p[blockIdx.y];
+  uint4* out = dst + (long long)blockIdx.y * shard_vec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < shard_vec;
+       i += (long long)gridDim.x * blockDim.x)
+    out[i] = src[i];
+}
+
+// Gradient reduce-scatter by peer loads, accumulating: shard[i] += sum_r peer_grad[r][lo + i].
+__global__ void shard_reduce_accum_kernel(PeerPtrsF peers, int n_peers, long long lo, float* __restrict__ shard,
+                                          long long n) {
+  const long long nv = n >> 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = reinterpret_cast<float4*>(shard)[i];
+    for (int r = 0; r < n_peers; ++r) {
+      const float4 v = *reinterpret_cast<const float4*>(peers.p[r] + lo + 4 * i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    reinterpret_cast<float4*>(shard)[i] = acc;
+  }
+}
+
 struct PeerPtrsW {
   __nv_bfloat16* p[8];
 };
@@ -326,6 +382,47 @@ int ab_shard_adamw_scatter(float* master, const float* grad, float* m, float* v,
   if (grid > 148 * 8) grid = 148 * 8;
   shard_adamw_scatter_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       master, grad, m, v, pp, n_peers, lo, n, ctrl, lr, beta1, beta2, eps, wd, bc1, bc2, max_norm);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+int ab_flags_signal(void* const* peer_flags, int n_peers, long long index, long long value, void* stream) {
+  if (n_peers < 1 || n_peers > 8 || index < 0) return -10;
+  PeerFlagPtrs pp;
+  for (int i = 0; i < n_peers; ++i) pp.p[i] = reinterpret_cast<long long*>(peer_flags[i]);
+  flags_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pp, n_peers, index, value);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+int ab_flags_wait_all(const long long* flags, int count, long long value, double limit_ms, int* status, void* stream) {
+  if (limit_ms <= 0 || limit_ms > 10000.0 || count < 1 || count > 32) return -10;   // waits are always bounded (<= 10 s)
+  flags_wait_all_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      flags, count, value, static_cast<unsigned long long>(limit_ms * 1e6), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+int ab_peer_gather(const void* const* peer_shards, int n_peers, long long shard_bytes, void* dst, void* stream) {
+  if (n_peers < 1 || n_peers > 8 || shard_bytes < 0 || (shard_bytes & 15) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -10;
+  if (shard_bytes == 0) return 0;
+  PeerPtrsV pp;
+  for (int i = 0; i < n_peers; ++i) {
+    if (reinterpret_cast<uintptr_t>(peer_shards[i]) & 15) return -10;
+    pp.p[i] = reinterpret_cast<const uint4*>(peer_shards[i]);
+  }
+  const long long nv = shard_bytes >> 4;
+  long long gx = (nv + 255) / 256;
+  const long long cap = (148 * 8 + n_peers - 1) / n_peers;
+  if (gx > cap) gx = cap;
+  peer_gather_kernel<<<dim3((unsigned)gx, (unsigned)n_peers), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      pp, nv, reinterpret_cast<uint4*>(dst));
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+int ab_shard_reduce_accum(const void* const* peer_grads, int n_peers, long long lo, float* shard, long long n,
+                          void* stream) {
+  if (n_peers < 1 || n_peers > 8 || n < 0 || (n & 3) || (lo & 3)) return -10;
+  if (n == 0) return 0;
+  PeerPtrsF pp;
+  for (int i = 0; i < n_peers; ++i) pp.p[i] = reinterpret_cast<const float*>(peer_grads[i]);
+  long long grid = ((n >> 2) + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  shard_reduce_accum_kernel<<<(int)grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pp, n_peers, lo, shard, n);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

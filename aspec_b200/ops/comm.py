@@ -55,6 +55,38 @@ def shard_adamw_scatter(master, grad, m, v, peer_params: Sequence[torch.Tensor],
         _stream(master)), "ab_shard_adamw_scatter")
 
 
+def flags_signal(peer_flags: Sequence[torch.Tensor], index: int, value: int, stream=None) -> None:
+    """Store ``value`` (release, system scope) into element ``index`` of every rank's int64 flag array."""
+    st = C.c_void_p(stream.cuda_stream) if stream is not None else _stream(peer_flags[0])
+    _check(_native.kernels().ab_flags_signal(_ptrs(peer_flags), len(peer_flags), C.c_longlong(index), C.c_longlong(value), st),
+           "ab_flags_signal")
+
+
+def flags_wait_all(flags: torch.Tensor, first: int, count: int, value: int, status: torch.Tensor, limit_ms: float = 5000.0,
+                   stream=None) -> None:
+    """Stream-ordered bounded wait until ``flags[first : first + count] >= value``; on expiry ``status`` holds the
+    peer-timeout code and the stream continues (the host reads ``status`` at the end of the update)."""
+    st = C.c_void_p(stream.cuda_stream) if stream is not None else _stream(flags)
+    _check(_native.kernels().ab_flags_wait_all(C.c_void_p(flags.data_ptr() + 8 * first), count, C.c_longlong(value),
+                                               C.c_double(limit_ms), C.c_void_p(status.data_ptr()), st), "ab_flags_wait_all")
+
+
+def peer_gather(peer_shards: Sequence[torch.Tensor], dst: torch.Tensor, stream=None) -> None:
+    """``dst = cat(peer_shards)`` by peer loads (every shard the same byte size, a multiple of 16)."""
+    nbytes = peer_shards[0].numel() * peer_shards[0].element_size()
+    st = C.c_void_p(stream.cuda_stream) if stream is not None else _stream(dst)
+    _check(_native.kernels().ab_peer_gather(_ptrs(peer_shards), len(peer_shards), C.c_longlong(nbytes),
+                                            C.c_void_p(dst.data_ptr()), st), "ab_peer_gather")
+
+
+def shard_reduce_accum(peer_grads: Sequence[torch.Tensor], lo: int, shard: torch.Tensor, stream=None) -> None:
+    """``shard += sum_r peer_grads[r][lo : lo + len(shard)]`` (fp32)."""
+    st = C.c_void_p(stream.cuda_stream) if stream is not None else _stream(shard)
+    _check(_native.kernels().ab_shard_reduce_accum(_ptrs(peer_grads), len(peer_grads), C.c_longlong(lo),
+                                                   C.c_void_p(shard.data_ptr()), C.c_longlong(shard.numel()), st),
+           "ab_shard_reduce_accum")
+
+
 def peer_lse_merge(peer_lse: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
     """``out[i] = logsumexp_r peer_lse[r][i]`` (fp32)."""
     _check(_native.kernels().ab_peer_lse_merge(_ptrs(peer_lse), len(peer_lse), C.c_void_p(out.data_ptr()),

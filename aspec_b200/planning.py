@@ -72,9 +72,11 @@ def resolve_batch_size(flat: Dict[str, Any], dp: int) -> dict:
             "max_tokens_per_update": per_update * int(flat["max_seq_length"])}
 
 
-def estimate_memory(draft: dict, flat: Dict[str, Any], algorithm: str, shard: int) -> dict:
-    """Resident bytes per Draft GPU: bf16 weights + fp32 master/grad/moments (sharded by FSDP), frozen head
-    and embedding, ring slots and the largest vocabulary-sized activations.  Sized for 180 GB of HBM3e."""
+def estimate_memory(draft: dict, flat: Dict[str, Any], algorithm: str, shard: int, strategy: str = "REPLICATE") -> dict:
+    """Resident bytes per Draft GPU: bf16 weights, fp32 gradient, master and moments (what of them the strategy shards
+    over ``shard`` ranks), frozen head and embedding, ring slots and the largest vocabulary-sized activations.
+    REPLICATE keeps all 18 bytes per parameter; SHARD_OPTIMIZER keeps weights and gradients (6) and shards masters and
+    moments (12); FULL_SHARD shards all 18 and adds two whole layers of working copies (weights + gradients)."""
     D, V, L = draft["hidden_size"], draft["vocab_size"], draft["num_hidden_layers"]
     I = draft.get("intermediate_size", 4 * D)
     hq, hk = draft["num_attention_heads"], draft["num_key_value_heads"]
@@ -92,9 +94,19 @@ def estimate_memory(draft: dict, flat: Dict[str, Any], algorithm: str, shard: in
     logits = 2 * rows * V * 2
     slot = int(flat["max_seq_length"]) * (n_tl + 1) * Dt * 2 + int(flat["max_seq_length"]) * 8
     ring = slot * int(flat.get("transport_destination_ring_slots", 1))
-    total = trainable * 2 + trainable * 16 // max(shard, 1) + frozen * 2 + logits + ring
-    return {"trainable_parameters": trainable, "frozen_parameters": frozen, "weights_bf16": trainable * 2,
-            "optimizer_fp32": trainable * 16 // max(shard, 1), "frozen_bf16": frozen * 2, "vocab_activations": logits,
+    shard = max(shard, 1)
+    strategy = str(strategy).upper()
+    if strategy == "FULL_SHARD" and shard > 1:
+        root = trainable - L * per_layer
+        weights = trainable * 2 // shard + (2 * per_layer + root) * 2
+        state = trainable * 16 // shard + (2 * per_layer + root) * 4
+    elif strategy == "SHARD_OPTIMIZER" and shard > 1:
+        weights, state = trainable * 2, trainable * 4 + trainable * 12 // shard
+    else:
+        weights, state = trainable * 2, trainable * 16
+    total = weights + state + frozen * 2 + logits + ring
+    return {"trainable_parameters": trainable, "frozen_parameters": frozen, "weights_bf16": weights,
+            "optimizer_fp32": state, "frozen_bf16": frozen * 2, "vocab_activations": logits,
             "ring_bytes": ring, "estimated_total": total, "hbm_bytes": HBM_BYTES, "fits": total < 0.9 * HBM_BYTES}
 
 
@@ -252,8 +264,13 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
         flat["transport_destination_ring_slots"] = need_slots
     caps.append(CapabilityDecision("feature_transport", flat["transport_data_plane"],
                                    "Target epilogues store into the Draft ranks' ring slots over NVLink"))
-    caps.append(CapabilityDecision("data_parallel", flat["fsdp_strategy"],
-                                   "flat fp32 gradient buffer, one SUM reduction per update"))
+    caps.append(CapabilityDecision("data_parallel", flat["fsdp_strategy"], {
+        "REPLICATE": "whole replicas; flat fp32 gradient buffer, one SUM reduction per update",
+        "SHARD_OPTIMIZER": "whole bf16 replicas and gradient buffers; fp32 masters and moments sharded; reduce + AdamW + "
+                           "parameter scatter over peer memory once per update",
+        "FULL_SHARD": "parameters, gradients, masters and moments sharded per decoder layer; layers gathered by peer loads one "
+                      "ahead of compute; each layer's gradient reduce-scattered under the backward of the layers below",
+    }[str(flat["fsdp_strategy"]).upper()]))
     if cp > 1:
         caps.append(CapabilityDecision("context_parallel", f"ulysses{u}xring{r}" if u * r > 1 else f"direct_cp{cp}",
                                        f"context sharded contiguously per document, alignment {align}"))
@@ -275,7 +292,7 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
            "draft_gpus": world, "context_parallel": cp, "ulysses": u, "ring": r, "expert_parallel": ep,
            "vocab_parallel": vp, "fsdp_strategy": flat["fsdp_strategy"], **resolve_batch_size(flat, dp),
            "num_train_steps": flat.get("num_train_steps"), "seed": flat["seed"]}
-    memory = estimate_memory(draft, flat, algorithm, world if flat["fsdp_strategy"] == "FULL_SHARD" else 1)
+    memory = estimate_memory(draft, flat, algorithm, dp, flat["fsdp_strategy"])
     if not memory["fits"]:
         raise ValueError(f"estimated {memory['estimated_total'] / 2**30:.1f} GiB per Draft GPU exceeds 180 GB HBM3e; "
                          "use FULL_SHARD, fewer anchors or a smaller ring")

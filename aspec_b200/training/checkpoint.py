@@ -170,6 +170,14 @@ def _dcp_load(state: dict, path: str) -> None:
         dcp.load(state, checkpoint_id=path)
 
 
+def whole_parameters(optimizer, writeback: bool = False):
+    """With FULL_SHARD the layers' parameters live in rotating working buffers; inside this block they are all whole
+    (and, with ``writeback``, what the block wrote becomes the new shards).  A no-op for the other strategies."""
+    import contextlib
+    block = getattr(optimizer, "full_parameters", None)
+    return block(writeback=writeback) if block is not None else contextlib.nullcontext()
+
+
 def _optimizer_state(optimizer) -> dict:
     sd = optimizer.state_dict()
     flat = {"step": torch.tensor(sd["step"])}
@@ -190,8 +198,9 @@ def save(*, output_dir: str, step_id: int, model: torch.nn.Module, optimizer, dr
     if _world() > 1:
         dist.barrier()
     os.makedirs(os.path.join(stage, "rng"), exist_ok=True)
-    model_state = {k: v for k, v in model.state_dict().items()}
-    _dcp_save({"model_state": model_state}, os.path.join(stage, "model"))
+    with whole_parameters(optimizer):
+        model_state = {k: v for k, v in model.state_dict().items()}
+        _dcp_save({"model_state": model_state}, os.path.join(stage, "model"))
     _dcp_save({"optim_state": _optimizer_state(optimizer)}, os.path.join(stage, "optimizer"))
     _dcp_save({"lr_scheduler": {"last_epoch": torch.tensor(optimizer.scheduler.last_epoch)}},
               os.path.join(stage, "lr_scheduler"))
@@ -276,9 +285,10 @@ def load(*, load_path: str, model: torch.nn.Module, optimizer=None, topology: Op
         if meta.get("world_size") != topology.get("world_size"):
             raise ValueError(f"Exact resume refused: world size {topology.get('world_size')} != checkpoint {meta.get('world_size')}")
         validate_exact_resume_topology(meta.get("training_topology", {}), topology)
-    state = {"model_state": {k: torch.empty_like(v) for k, v in model.state_dict().items()}}
-    _dcp_load(state, os.path.join(ckpt, "model"))
-    model.load_state_dict(state["model_state"], strict=True)
+    with whole_parameters(optimizer, writeback=True):
+        state = {"model_state": {k: torch.empty_like(v) for k, v in model.state_dict().items()}}
+        _dcp_load(state, os.path.join(ckpt, "model"))
+        model.load_state_dict(state["model_state"], strict=True)
     if optimizer is not None:
         if continual_training:
             optimizer.sync_fp32_params_from_model()

@@ -45,10 +45,20 @@ class DraftTrainer:
         self.accumulation = int(accumulation)
         self.dp_group = dp_group
         self.device = device or next(model.parameters()).device
-        self.sharded = (fsdp_strategy == "FULL_SHARD" and dist.is_available() and dist.is_initialized()
-                        and dist.get_world_size(dp_group) > 1)
-        if self.sharded:
-            # gradients, masters and moments sharded over the data-parallel ranks; reduction and update over peer memory
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(dp_group) > 1
+        strategy = str(fsdp_strategy).upper()
+        self.sharded = strategy in ("FULL_SHARD", "SHARD_OPTIMIZER") and multi
+        if strategy == "FULL_SHARD" and multi:
+            # parameters, gradients, masters and moments sharded; layers are gathered for their forward and backward and
+            # each layer's gradient is reduce-scattered under the backward of the layers below it
+            from aspec_b200.training.full_shard import FullShardOptimizer
+            layers = list(getattr(self.draft, "layers", None) or [])
+            self.optimizer = FullShardOptimizer(self.draft, layers, lr=lr, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
+                                                total_steps=total_steps, warmup_ratio=warmup_ratio, decay_style=decay_style,
+                                                min_lr=min_lr, betas=betas, group=dp_group,
+                                                wsd_decay_steps=wsd_decay_steps, wsd_decay_style=wsd_decay_style)
+        elif self.sharded:
+            # whole replicas; masters and moments sharded; reduction and update over peer memory once per update
             from aspec_b200.training.sharded_optimizer import ShardedBF16Optimizer
             self.optimizer = ShardedBF16Optimizer(self.draft, lr=lr, weight_decay=weight_decay, max_grad_norm=max_grad_norm,
                                                   total_steps=total_steps, warmup_ratio=warmup_ratio, decay_style=decay_style,
@@ -116,6 +126,9 @@ class DraftTrainer:
         loss, acc, loss_pp, acc_pp, count_pp, comps, (num, den) = out
         if num.requires_grad:
             num.backward()
+            close = getattr(self.optimizer, "finish_micro_batch", None)
+            if close is not None:            # FULL_SHARD: the root unit's gradients join the reduce-scatter here
+                close()
         pool = self._pool
         pool.setdefault("loss", []).append(torch.stack([num.detach().float(), den.float()]))
         pool.setdefault("acc_pp", []).append(torch.stack([acc_pp * count_pp.clamp(min=1.0) * (count_pp > 0), count_pp]))

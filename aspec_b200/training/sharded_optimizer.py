@@ -1,4 +1,4 @@
-"""FULL_SHARD optimizer over peer memory: gradients, fp32 masters and Adam moments are sharded over the
+"""SHARD_OPTIMIZER strategy (optimizer state sharded, replicas whole) over peer memory: fp32 masters and Adam moments are sharded over the
 data-parallel ranks of one node; the reduce-scatter, the gradient norm, AdamW and the parameter all-gather are two
 kernels that read and write the peers' buffers directly over NVLink.
 

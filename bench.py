@@ -58,7 +58,8 @@ def parse_args():
     ap.add_argument("--length-group", type=int, default=32,
                     help="online: the controller's length_group_size (documents of similar length go to different Draft ranks "
                          "in the same micro-step; 1 disables the grouping)")
-    ap.add_argument("--fsdp", action="store_true", help="(kept for old command lines: the peer-memory sharded step is the default for N >= 2)")
+    ap.add_argument("--fsdp", action="store_true", help="draft mode, N >= 2: FULL_SHARD (parameters and gradients sharded per layer as well, gathered / reduce-scattered "
+                         "over peer memory around every layer) instead of the default SHARD_OPTIMIZER step")
     ap.add_argument("--baseline", action="store_true",
                     help="draft mode, N >= 2: NCCL all-reduce of the flat gradient + replicated AdamW instead of the peer-memory sharded step")
     ap.add_argument("--no-online", action="store_true", help="N >= 2: do not append the online Target + Draft run")
@@ -183,7 +184,7 @@ def run_ours(args):
     sharded = world > 1 and not args.baseline
     trainer = DraftTrainer(model, lm_head, lr=6e-4, min_lr=6e-5, weight_decay=0.0, max_grad_norm=1.0,
                            total_steps=max(total_updates, 32), warmup_ratio=0.04, accumulation=args.accum,
-                           device=device, fsdp_strategy="FULL_SHARD" if sharded else "REPLICATE")
+                           device=device, fsdp_strategy=("FULL_SHARD" if args.fsdp else "SHARD_OPTIMIZER") if sharded else "REPLICATE")
     n_docs = args.pool or args.accum * 2
     pool = make_pool(args, cfg, model, rank, n_docs, pin=cuda)
     resident = [dict(trainer.to_device(b), host_loss_mask=b["host_loss_mask"]) for b in pool]
@@ -263,6 +264,9 @@ def run_ours(args):
     collective = ("none (1 GPU)" if world == 1 else
                   "NCCL all-reduce of the flat fp32 gradient + replicated AdamW" if args.baseline else
                   "sharded step over gloo collectives (CPU run)" if not cuda else
+                  "FULL_SHARD: per-layer peer_gather (peer loads) before forward and backward, per-layer shard_reduce_accum "
+                  "(peer loads) under the backward of the layers below, flags in peer memory; NCCL only for the two-scalar "
+                  "norm and the pooled metrics" if args.fsdp else
                   "peer-memory sharded step: shard_reduce_sumsq (peer loads) + shard_adamw_scatter (peer stores); "
                   "NCCL only for three scalar all-reduces per update")
     line = None
@@ -277,7 +281,7 @@ def run_ours(args):
             "config": {"model": f"Qwen3-8B-shaped DSpark draft, {args.layers} layer(s), {args.target_layers} captured layers, vocab {cfg.vocab_size}",
                        "global_batch": args.accum * world, "seq_len": args.max_len,
                        "doc_lengths": f"log-uniform [{args.min_len},{args.max_len}]",
-                       "parallelism": f"dp{world}" + ("+sharded_optimizer" if sharded else ""),
+                       "parallelism": f"dp{world}" + (("+full_shard" if args.fsdp else "+sharded_optimizer") if sharded else ""),
                        "collective": collective,
                        "anchors_sampled": "inside the timed region, every micro-batch",
                        "dp_balance": "every rank draws documents with the length sequence of the 1-GPU run (own token ids and features)" if world > 1 else "n/a", "micro_batch": "1 document (MBS1)", "anchors": model.num_anchors,

@@ -344,3 +344,88 @@ def test_sequence_parallel_eagle3_pipeline_matches_one_gpu(tmp_path):
         losses[name] = [l["train/avg_loss"] for l in logs]
     assert losses["one"][0] == pytest.approx(losses["sp2"][0], rel=3e-2)
     assert losses["one"][-1] == pytest.approx(losses["sp2"][-1], rel=6e-2)
+
+
+def _full_shard_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    res = {}
+    try:
+        from aspec_b200.training.full_shard import FullShardOptimizer
+        from aspec_b200.training.optimizer import BF16Optimizer
+
+        class Layer(torch.nn.Module):
+            def __init__(self, d):
+                super().__init__()
+                self.a, self.b = torch.nn.Linear(d, d, bias=False), torch.nn.Linear(d, d, bias=False)
+
+            def forward(self, x, ctx):
+                return x + torch.tanh(self.a(x) + self.b(ctx)) * 0.5
+
+        class Net(torch.nn.Module):
+            def __init__(self, d=256, n=4):
+                super().__init__()
+                self.inp = torch.nn.Linear(64, d, bias=False)
+                self.layers = torch.nn.ModuleList([Layer(d) for _ in range(n)])
+                self.out = torch.nn.Linear(d, 32, bias=False)
+
+            def forward(self, x, feats):
+                ctx = self.inp(feats)
+                for layer in self.layers:
+                    x = layer(x, ctx)
+                return self.out(x).float().pow(2).mean()
+
+        torch.manual_seed(0)
+        a = Net().to(dev, torch.bfloat16)
+        b = Net().to(dev, torch.bfloat16)
+        b.load_state_dict(a.state_dict())
+        opt_a = FullShardOptimizer(a, list(a.layers), lr=1e-2, weight_decay=0.01, max_grad_norm=0.5, total_steps=100,
+                                   wait_limit_ms=4000.0)
+        opt_b = BF16Optimizer(b, lr=1e-2, weight_decay=0.01, max_grad_norm=0.5, total_steps=100)
+        norms = []
+        for step in range(3):
+            for mb in range(2):
+                g = torch.Generator(device=dev).manual_seed(1000 * step + 10 * rank + mb)
+                x = torch.randn(48, 256, device=dev, generator=g).bfloat16()       # no gradient into layer 0 through x
+                feats = torch.randn(48, 64, device=dev, generator=g).bfloat16()
+                a(x, feats).backward()
+                opt_a.finish_micro_batch()
+                b(x, feats).backward()
+            opt_b.fold_autograd_grads()
+            dist.all_reduce(opt_b.flat_grad)
+            opt_a.set_grad_scale(0.25)
+            opt_b.set_grad_scale(0.25)
+            norms.append((opt_a.step(), opt_b.step()))
+        res["norms"] = all(_close(x, y, 2e-2, 1e-4) for x, y in norms)
+        with opt_a.full_parameters():
+            res["params"] = all(_close(p, q, 0, 2e-2) for p, q in zip(a.parameters(), b.parameters()))
+        sd = opt_a.state_dict()
+        ref_master = opt_b.state_dict()["master"]
+        res["masters"] = all(_close(sd["master"][n], ref_master[n], 0, 2e-2) for n in ref_master)
+        rep = opt_a.memory_report()
+        res["at_rest_half"] = rep["at_rest_bytes"] * 2 <= rep["replicated_bytes"] * 1.05 + 4096
+        res["status_clean"] = int(opt_a.status.item()) == 0
+        dist.barrier()
+        opt_a.close()
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        res["error"] = f"{type(exc).__name__}: {exc}\n{traceback.format_exc()[-1500:]}"
+    torch.save(res, f"{out_path}.{rank}")
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_full_shard_trains_like_the_replicated_optimizer_on_two_gpus(tmp_path):
+    """Parameters, gradients and optimizer state sharded per layer over two real GPUs: gathers by peer loads, the
+    reduce-scatter by peer loads, ordering by flags in peer memory (no library collective but the two-scalar norm)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = str(tmp_path / "res")
+    mp.spawn(_full_shard_worker, args=(2, 29300 + os.getpid() % 500, out), nprocs=2, join=True)
+    for rank in range(2):
+        res = torch.load(f"{out}.{rank}")
+        assert "error" not in res, res.get("error")
+        bad = [k for k, v in res.items() if v is not True]
+        assert not bad, (rank, bad, res)

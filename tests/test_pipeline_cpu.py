@@ -98,9 +98,10 @@ def test_step_deadline_terminates_trainers(tmp_path):
 
 @pytest.mark.timeout(600)
 def test_full_shard_matches_replicate(tmp_path):
-    """Same recipe under REPLICATE and FULL_SHARD: identical losses, and the sharded run's checkpoint resumes."""
+    """Same recipe under REPLICATE, SHARD_OPTIMIZER (optimizer state sharded) and FULL_SHARD (parameters and gradients
+    sharded per layer too): identical losses, and the fully sharded run's checkpoint resumes."""
     losses = {}
-    for strategy in ("REPLICATE", "FULL_SHARD"):
+    for strategy in ("REPLICATE", "SHARD_OPTIMIZER", "FULL_SHARD"):
         plan = _plan(tmp_path / strategy if (tmp_path / strategy).mkdir() is None else tmp_path, [f"training.fsdp_strategy={strategy}"])
         flat = plan.to_runtime_args()
         flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=2, save_final_checkpoint=False)
@@ -116,6 +117,7 @@ def test_full_shard_matches_replicate(tmp_path):
             assert logs2[0]["train/step"] == 2
             assert logs2[0]["train/avg_loss"] == pytest.approx(logs[2]["train/avg_loss"], rel=1e-5)
     assert losses["FULL_SHARD"] == pytest.approx(losses["REPLICATE"], rel=1e-5)
+    assert losses["SHARD_OPTIMIZER"] == pytest.approx(losses["REPLICATE"], rel=1e-5)
 
 
 @pytest.mark.timeout(600)
