@@ -28,6 +28,19 @@ from aspec_b200.utils.types import InferenceOutput, RowRequest
 from aspec_b200.work_lifecycle import WorkLifecycleLedger, build_work_identity
 
 
+def draft_vocabulary_from_samples(samples, draft_config: dict, args: dict):
+    """``(d2t, t2d)`` for a Draft whose head covers ``draft_vocab_size < vocab_size`` tokens: the most frequent
+    supervised tokens of the admitted dataset (reference: aspec/data/preprocessing.py ``generate_vocab_mapping_file``).
+    ``None`` when the head is not pruned, or when ``model.keep_initial_vocab_mapping`` keeps the mapping that came with
+    the initial Draft asset."""
+    vocab = int(draft_config.get("vocab_size") or 0)
+    small = int(draft_config.get("draft_vocab_size") or vocab)
+    if not vocab or small >= vocab or args.get("keep_initial_vocab_mapping"):
+        return None
+    from aspec_b200.data.preprocessing import generate_vocab_mapping
+    return generate_vocab_mapping(samples, vocab, small)
+
+
 class TrainingController:
     def __init__(self, args: Dict[str, Any], dp_size: int, consumers_per_row: int = 1, algorithm: str = "dspark"):
         self.args = dict(args)

@@ -188,6 +188,18 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
         common = _common_samples(controllers, dataset)
         for c in controllers.values():
             c.load_dataset(common)
+        # packed rows are cut by a per-document work measure that depends on the algorithm (anchor starts, TTT positions);
+        # readers of one Target pass must cut the same rows, so all of them pack by the first experiment's measure
+        work = {s["data_id"]: s["useful"] for s in controllers[names[0]].samples}
+        for n in names[1:]:
+            for s in controllers[n].samples:
+                s["useful"] = work[s["data_id"]]
+        from aspec_b200.controller.training_controller import draft_vocabulary_from_samples
+        for n in names:
+            mapping = draft_vocabulary_from_samples(common, plan.plans[n].draft_config, groups[n]["flat"])
+            if mapping is not None:
+                for fut in [t.call_async("set_vocab_mapping", *mapping) for t in groups[n]["trainers"]]:
+                    fut.get(timeout=300)
         manager = InferenceManager(engines, all_rings, on_result=lambda o, r: None,
                                    batch_size=int(base.get("inference_batch_size", 1)),
                                    acquire_timeout=float(base.get("transport_acquire_timeout_seconds", 120.0)))
@@ -208,6 +220,7 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
                                            consumer_of_rank=lambda r: list(range(r * cp, (r + 1) * cp)))
             except BaseException as exc:                       # noqa: BLE001 - one experiment must not stop the others
                 results[n] = {"failed": f"{type(exc).__name__}: {exc}"}
+                log({"experiment": n, "failed": results[n]["failed"][:400]})
                 shared.fence(n, results[n]["failed"])
                 for t in g["trainers"]:
                     t.terminate()

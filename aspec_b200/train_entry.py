@@ -125,6 +125,11 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
         start_step = 0
         controller = TrainingController(args, dp_size=dp, consumers_per_row=cp, algorithm=algorithm)
         n = controller.load_dataset(dataset)
+        from aspec_b200.controller.training_controller import draft_vocabulary_from_samples
+        mapping = draft_vocabulary_from_samples(controller.samples, draft_config, flat)
+        if mapping is not None:                      # pruned Draft head: the tokens it predicts come from the corpus
+            for fut in [t.call_async("set_vocab_mapping", *mapping) for t in trainers]:
+                fut.get(timeout=300)
         if evidence:
             stats = getattr(controller, "admission", None) or {}
             evidence.record_dataset_admission(dataset_size=n, admission={"admitted": n, "fingerprint": controller.dataset_fingerprint(),

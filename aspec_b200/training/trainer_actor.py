@@ -182,6 +182,14 @@ class TrainerActor:
         """One handle per producer process that will map this ring."""
         return [self.ring.export() for _ in range(max(int(copies), 1))]
 
+    def set_vocab_mapping(self, d2t: torch.Tensor, t2d: torch.Tensor) -> None:
+        """Draft vocabulary of a pruned output head: which Target tokens it predicts (reference:
+        aspec/training/eagle3_trainer.py, ``vocab_mapping_path``).  A checkpoint loaded afterwards overrides it."""
+        draft = self.model.draft_model
+        if not getattr(draft, "vocab_pruned", False):
+            raise ValueError("this Draft predicts the whole Target vocabulary")
+        draft.set_vocab_buffers(d2t.to(draft.d2t.device), t2d.to(draft.t2d.device))
+
     def set_head(self, lm_head: Optional[torch.Tensor], embedding: Optional[torch.Tensor] = None) -> None:
         """Frozen Target output head (and embedding): a tensor, a relayable handle, ``{"file": path}`` (a head stored
         beside offline features) or ``None`` -> deterministic random init (feature stores without a head)."""

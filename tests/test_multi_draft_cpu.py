@@ -101,3 +101,66 @@ def test_multi_draft_from_the_command_line_writes_per_experiment_metrics(tmp_pat
         rows = [json.loads(line) for line in (run / "experiments" / name / "runs" / "metrics.jsonl").read_text().splitlines()]
         assert [r["step"] for r in rows] == [0, 1, 2] and all("experiment" not in r for r in rows)
         assert json.loads((run / "experiments" / name / "tracking.json").read_text())["active"] == ["jsonl"]
+
+
+@pytest.mark.timeout(600)
+def test_three_families_share_packed_rows_with_sharded_drafts(tmp_path):
+    """DSpark, EAGLE3 with a pruned draft vocabulary and a 2-layer sliding-window DFlash read one packed row stream; every
+    Draft is FULL_SHARD over two ranks.  The algorithms measure a document's work differently, so the rows are cut by
+    the first experiment's measure; the pruned vocabulary comes from the admitted corpus."""
+    import json
+    eagle = tmp_path / "eagle.json"
+    eagle.write_text(json.dumps(dict(
+        architectures=["LlamaForCausalLMEagle3"], model_type="llama", hidden_size=64, intermediate_size=128, num_attention_heads=4,
+        num_key_value_heads=2, head_dim=16, vocab_size=512, draft_vocab_size=128, num_hidden_layers=1, rope_theta=10000.0,
+        max_position_embeddings=2048, target_hidden_size=64, target_num_hidden_layers=4, num_aux_hidden_states=3,
+        target_layer_ids=[0, 1, 3])))
+    flash = json.load(open(DFLASH))
+    flash.update(num_hidden_layers=2, sliding_window=32)
+    (tmp_path / "flash.json").write_text(json.dumps(flash))
+    recipe = tmp_path / "recipe.yaml"
+    recipe.write_text(f"""
+model:
+  draft_model_config: {DSPARK}
+dataset:
+  train_data_path: synthetic
+  synthetic_num_documents: 96
+  synthetic_min_length: 32
+  synthetic_max_length: 96
+inference:
+  inference_engine_type: synthetic
+training:
+  training_num_gpus_per_node: 2
+  fsdp_strategy: FULL_SHARD
+  micro_batch_size: 1
+  draft_accumulation_steps: 2
+  max_seq_length: 256
+  dflash_packing: true
+  num_train_steps: 2
+  learning_rate: 1e-3
+  dspark_block_size: 4
+  dspark_num_anchors: 16
+  dflash_block_size: 4
+  dflash_num_anchors: 16
+  ttt_length: 3
+  save_interval: 0
+  seed: 7
+transport:
+  destination_ring_slots: 5
+experiments:
+  - name: spark
+  - name: eagle
+    model:
+      draft_model_config: {eagle}
+  - name: flash
+    model:
+      draft_model_config: {tmp_path / 'flash.json'}
+output_dir: {tmp_path / 'run'}
+""")
+    plan = compile_multi_draft_plan(load_config(str(recipe)))
+    for p in plan.plans.values():
+        p.runtime_args.update(synthetic_vocab_size=500, force_cpu=True)
+    out = run_multi_draft(plan, log=lambda m: None)
+    assert all(out[n].get("completed_steps") == 2 for n in ("spark", "eagle", "flash")), out
+    assert out["shared_source"]["fenced"] == {} and out["shared_source"]["rows_shared"] == 2 * 2 * 2
+    assert out["spark"]["ledger"]["committed_work_ids"] == out["eagle"]["ledger"]["committed_work_ids"]
