@@ -429,7 +429,7 @@ class DFlashModel(nn.Module):
         num, ce, l1, correct = head_loss(
             hidden, lm_head_weight, target_ids.reshape(-1), obj_w.reshape(-1),
             teacher_hidden=teacher_hidden, t_index=t_index, a_ce=self.ce_loss_alpha,
-            a_l1=self.l1_loss_alpha if teacher_hidden is not None else 0.0)
+            a_l1=self.l1_loss_alpha if teacher_hidden is not None else 0.0, chunk_rows=self.num_anchors * bs)
         den = obj_w.sum()
         aux_num, comps = self._aux_losses(aux, obj_w, den)
         num = num + aux_num

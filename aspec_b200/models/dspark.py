@@ -125,7 +125,10 @@ class DSparkModel(DFlashModel):
             num_ce_l1, ce, l1, correct = vocab_parallel_head_loss(vp, hidden, lm_head_weight, target_ids.reshape(-1),
                                                                   w.reshape(-1), **head_kw)
         else:
-            num_ce_l1, ce, l1, correct = head_loss(hidden, lm_head_weight, target_ids.reshape(-1), w.reshape(-1), **head_kw)
+            # a packed row can hold more blocks than one document's anchor budget: the head then runs per
+            # anchor-budget-sized chunk, recomputing each chunk's logits in backward
+            num_ce_l1, ce, l1, correct = head_loss(hidden, lm_head_weight, target_ids.reshape(-1), w.reshape(-1),
+                                                   chunk_rows=self.num_anchors * self.block_size, **head_kw)
         wf = w.reshape(-1)
         if sampled:
             # L1 on the distributions a sampler would draw from (temperature / top-p / top-k): row-chunked logits

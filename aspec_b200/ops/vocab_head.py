@@ -125,9 +125,15 @@ class _HeadLossFn(torch.autograd.Function):
 def head_loss(hidden: torch.Tensor, lm_w: torch.Tensor, labels: torch.Tensor, weight: torch.Tensor, *,
               prev_emb: Optional[torch.Tensor] = None, markov_w2: Optional[torch.Tensor] = None,
               teacher_hidden: Optional[torch.Tensor] = None, t_index: Optional[torch.Tensor] = None,
-              a_ce: float = 1.0, a_l1: float = 0.0, mode: int = 0, teacher_w: Optional[torch.Tensor] = None
-              ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+              a_ce: float = 1.0, a_l1: float = 0.0, mode: int = 0, teacher_w: Optional[torch.Tensor] = None,
+              chunk_rows: int = 0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
     """Weighted loss numerator plus detached per-row ``ce``, ``l1`` and ``correct``.
+
+    ``chunk_rows > 0`` bounds the vocabulary-sized intermediates: rows are processed ``chunk_rows`` at a time and each
+    chunk's logits are recomputed in its backward instead of being kept (what the reference does per anchor-sized chunk of
+    a packed row under activation checkpointing, aspec/models/dspark.py:339-483).  Peak memory is then two
+    ``[chunk_rows, V]`` bf16 matrices whatever the row's number of blocks; a call with no more rows than that is
+    unchanged.
 
     ``hidden [R, D]``; ``lm_w [V, D]`` frozen; ``labels [R]`` int64; ``weight [R]`` fp32 (0 for rows
     that are not supervised); ``prev_emb [R, r]`` with ``markov_w2 [V, r]`` adds the Markov bias;
@@ -136,6 +142,10 @@ def head_loss(hidden: torch.Tensor, lm_w: torch.Tensor, labels: torch.Tensor, we
     ``logsumexp(z) - sum_v softmax(teacher)_v z_v``; there ``correct`` compares the two arg-maxima and
     ``lm_w`` may be a trainable parameter.
     """
+    if chunk_rows and hidden.shape[0] > chunk_rows:
+        return _chunked_head_loss(hidden, lm_w, labels, weight, int(chunk_rows), prev_emb=prev_emb, markov_w2=markov_w2,
+                                  teacher_hidden=teacher_hidden, t_index=t_index, a_ce=a_ce, a_l1=a_l1, mode=mode,
+                                  teacher_w=teacher_w)
     use_kernel = (hidden.is_cuda and hidden.dtype == torch.bfloat16 and lm_w.dtype == torch.bfloat16
                   and lm_w.shape[0] % 8 == 0 and hidden.shape[1] % 8 == 0 and hidden.shape[0] > 0)
     if (not use_kernel and hidden.is_cuda and hidden.dtype == torch.bfloat16 and lm_w.dtype == torch.bfloat16
@@ -156,3 +166,30 @@ def head_loss(hidden: torch.Tensor, lm_w: torch.Tensor, labels: torch.Tensor, we
         t_index.to(torch.int32).contiguous() if t_index is not None else None,
         labels.long().contiguous(), weight.float().contiguous(), float(a_ce), float(a_l1), int(mode), holder,
         teacher_w, lm_w if isinstance(lm_w, torch.nn.Parameter) else None)
+
+
+def _chunked_head_loss(hidden, lm_w, labels, weight, chunk_rows, *, prev_emb, markov_w2, teacher_hidden, t_index, a_ce, a_l1,
+                       mode, teacher_w):
+    """Row chunks of the head, each under activation checkpointing.  A chunk brings its own teacher rows (gathered by
+    ``t_index``, so rows shared between chunks are projected once per chunk that uses them) - no host synchronisation."""
+    from torch.utils.checkpoint import checkpoint
+    R = hidden.shape[0]
+    recompute = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (hidden, lm_w, prev_emb, markov_w2))
+
+    def one(h, lab, wgt, prev, teach):
+        return head_loss(h, lm_w, lab, wgt, prev_emb=prev, markov_w2=markov_w2, teacher_hidden=teach, t_index=None,
+                         a_ce=a_ce, a_l1=a_l1, mode=mode, teacher_w=teacher_w)
+
+    nums, ces, l1s, oks = [], [], [], []
+    for s in range(0, R, chunk_rows):
+        sl = slice(s, min(s + chunk_rows, R))
+        teach = None
+        if teacher_hidden is not None:
+            teach = teacher_hidden[sl] if t_index is None else teacher_hidden.index_select(0, t_index[sl].long())
+        args = (hidden[sl], labels[sl], weight[sl], prev_emb[sl] if prev_emb is not None else None, teach)
+        num, ce, l1, ok = checkpoint(one, *args, use_reentrant=False) if recompute else one(*args)
+        nums.append(num)
+        ces.append(ce.detach())
+        l1s.append(l1.detach())
+        oks.append(ok.detach())
+    return torch.stack(nums).sum(), torch.cat(ces), torch.cat(l1s), torch.cat(oks)

@@ -126,6 +126,29 @@ def test_head_loss_matches_reference(with_teacher, markov):
         assert (g3 - g3r).abs().max() / g3r.abs().max() < 5e-2
 
 
+def test_chunked_head_loss_on_the_kernel_path_matches_the_whole_head():
+    """Row chunks under activation checkpointing (bounded vocabulary-sized memory) against one call over all rows."""
+    from aspec_b200.ops.vocab_head import head_loss
+    torch.manual_seed(6)
+    R, D, V, r, Tt = 300, 128, 1000, 32, 170
+    lm_w = (torch.randn(V, D, device="cuda") * 0.2).bfloat16()
+    labels = torch.randint(0, V, (R,), device="cuda")
+    weight = torch.rand(R, device="cuda")
+    teacher = torch.randn(Tt, D, device="cuda").bfloat16()
+    t_index = torch.randint(0, Tt, (R,), device="cuda", dtype=torch.int32)
+    h0, p0 = torch.randn(R, D, device="cuda").bfloat16(), torch.randn(R, r, device="cuda").bfloat16()
+    w20 = (torch.randn(V, r, device="cuda") * 0.2).bfloat16()
+    outs = []
+    for chunk in (0, 128):
+        h, p, w2 = h0.clone().requires_grad_(), p0.clone().requires_grad_(), w20.clone().requires_grad_()
+        num, ce, l1, ok = head_loss(h, lm_w, labels, weight, prev_emb=p, markov_w2=w2, teacher_hidden=teacher, t_index=t_index,
+                                    a_ce=0.1, a_l1=0.9, chunk_rows=chunk)
+        num.backward()
+        outs.append((num.detach().float().reshape(1), ce.float(), l1.float(), ok.float(), h.grad.float(), p.grad.float(), w2.grad.float()))
+    for a, b in zip(*outs):
+        assert (a - b).abs().max() <= 2e-2 * max(1.0, b.abs().max().item())
+
+
 def test_flat_adamw_matches_torch():
     from aspec_b200.ops import elementwise_sm100 as E
     torch.manual_seed(5)

@@ -241,3 +241,31 @@ def test_dspark_l1_sampling_changes_the_loss_and_trains():
         assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
         out[name] = float(res[5]["l1_loss"][0])
     assert out["plain"] != out["topk"]
+
+
+def test_chunked_head_loss_equals_the_whole_head():
+    """Rows in chunks with recomputed logits: same loss, per-row outputs and gradients as one call over all rows."""
+    from aspec_b200.ops.vocab_head import head_loss
+    torch.manual_seed(0)
+    R, D, V, Tt, rk = 37, 16, 64, 20, 4
+    W = torch.randn(V, D) * 0.3
+    w2 = torch.nn.Parameter(torch.randn(V, rk) * 0.3)
+    teacher = torch.randn(Tt, D)
+    t_index = torch.randint(0, Tt, (R,), dtype=torch.int32)
+    labels = torch.randint(0, V, (R,))
+    weight = torch.rand(R)
+    outs = []
+    for chunk in (0, 8):
+        h = torch.randn(R, D, generator=torch.Generator().manual_seed(1)).requires_grad_(True)
+        p = torch.randn(R, rk, generator=torch.Generator().manual_seed(2)).requires_grad_(True)
+        w2.grad = None
+        num, ce, l1, ok = head_loss(h, W, labels, weight, prev_emb=p, markov_w2=w2, teacher_hidden=teacher, t_index=t_index,
+                                    a_ce=0.3, a_l1=0.7, chunk_rows=chunk)
+        num.backward()
+        outs.append((num.detach(), ce, l1, ok, h.grad.clone(), p.grad.clone(), w2.grad.clone()))
+    for a, b in zip(*outs):
+        assert torch.allclose(a, b, atol=1e-5)
+    with torch.no_grad():
+        n2, *_ = head_loss(torch.randn(R, D, generator=torch.Generator().manual_seed(1)), W, labels, weight, chunk_rows=8, a_ce=1.0)
+        n1, *_ = head_loss(torch.randn(R, D, generator=torch.Generator().manual_seed(1)), W, labels, weight, a_ce=1.0)
+    assert torch.allclose(n1, n2, atol=1e-5)
