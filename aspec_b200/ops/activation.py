@@ -45,6 +45,9 @@ def swiglu_backward(gu: torch.Tensor, dact: torch.Tensor, clamp: float = 0.0) ->
     if gu.is_cuda and gu.dtype == torch.bfloat16 and gu.shape[-1] % 16 == 0 and gu.numel():
         from aspec_b200.ops import elementwise_sm100 as E
         return E.swiglu_bwd(gu.reshape(-1, gu.shape[-1]).contiguous(), dact.reshape(-1, dact.shape[-1]).contiguous(), float(clamp)).view(gu.shape)
-    g = gu.detach().clone().requires_grad_(True)
-    swiglu_reference(g, clamp).backward(dact.to(gu.dtype))
+    if gu.numel() == 0:
+        return torch.zeros_like(gu)
+    with torch.enable_grad():            # callers sit inside an autograd backward, where recording is off
+        g = gu.detach().clone().requires_grad_(True)
+        swiglu_reference(g, clamp).backward(dact.to(gu.dtype))
     return g.grad

@@ -151,6 +151,9 @@ class FusedExpertParallel:
         from aspec_b200.ops.grouped_gemm import rows_gemm
         src, le, row0, rows, pstart, ptotal, span0, span = self._problems(count_matrix)
         zeros = np.zeros_like(src)
+        if ptotal == 0:                  # nothing routed here: the peers' y rows come from the other expert owners
+            self._saved = (src, le, row0, rows, pstart, ptotal, span0, span, None, None, None)
+            return
         xs = self._pull([w.x for w in self.ws], span0, span)
         gu = torch.zeros(ptotal, gate_up.shape[1], dtype=gate_up.dtype, device=gate_up.device)
         rows_gemm(xs, gate_up, [gu], src=src, a_row=row0, rows=rows, expert=le, dst=zeros, out_row=pstart)
@@ -174,6 +177,10 @@ class FusedExpertParallel:
         from aspec_b200.ops.activation import swiglu_backward
         from aspec_b200.ops.grouped_gemm import rows_gemm, wgrad_gemm
         src, le, row0, rows, pstart, ptotal, span0, span, xs, gu, act = self._saved
+        if ptotal == 0:                  # no token of any rank chose this rank's experts in this micro-batch
+            self._saved = None
+            return (torch.zeros(gate_up.shape, dtype=torch.float32, device=gate_up.device),
+                    torch.zeros(down.shape, dtype=torch.float32, device=down.device))
         zeros = np.zeros_like(src)
         dys = self._pull([w.dy for w in self.ws], span0, span)
         d_act = torch.zeros(ptotal, down.shape[2], dtype=down.dtype, device=down.device)

@@ -63,7 +63,7 @@ def parse_args():
     ap.add_argument("--baseline", action="store_true",
                     help="draft mode, N >= 2: NCCL all-reduce of the flat gradient + replicated AdamW instead of the peer-memory sharded step")
     ap.add_argument("--no-online", action="store_true", help="N >= 2: do not append the online Target + Draft run")
-    ap.add_argument("--online-steps", type=int, default=56, help="measured updates of the appended online run (window >= 32 updates)")
+    ap.add_argument("--online-steps", type=int, default=64, help="measured updates of the appended online run (window >= 32 updates)")
     ap.add_argument("--online-warmup", type=int, default=8)
     ap.add_argument("--online-timeout", type=float, default=900.0, help="seconds before the appended online run is abandoned")
     return ap.parse_args()

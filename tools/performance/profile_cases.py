@@ -161,6 +161,21 @@ def case_peer_lse():
         comm.peer_lse_merge(parts, out)
 
 
+def case_full_shard():
+    """The two data kernels of FULL_SHARD with four ranks' buffers on one device: a layer's parameter gather
+    (4 x 64 MB bf16 shards -> one 256 MB working copy) and its gradient reduce-scatter (this rank's quarter of four
+    512 MB fp32 replicas, accumulated into the shard)."""
+    from aspec_b200.ops import comm
+    per, peers = 32 << 20, 4
+    shards = [torch.randn(per, device="cuda").bfloat16() for _ in range(peers)]
+    whole = torch.empty(per * peers, device="cuda", dtype=torch.bfloat16)
+    grads = [torch.randn(per * peers, device="cuda") for _ in range(peers)]
+    mine = torch.zeros(per, device="cuda")
+    for _ in range(3):
+        comm.peer_gather(shards, whole)
+        comm.shard_reduce_accum(grads, per, mine)
+
+
 CASES = {n[5:]: f for n, f in globals().items() if n.startswith("case_")}
 
 if __name__ == "__main__":
