@@ -134,8 +134,10 @@ def validate_scope(flat: Dict[str, Any], draft: dict, algorithm: str, policy: di
         raise ValueError("at least one Draft GPU is needed")
     if engine == "native" and targets < 1:
         raise ValueError("the in-framework Target needs inference.inference_num_gpus >= 1")
-    if world + targets > GPUS_PER_NODE:
-        raise ValueError(f"{targets} Target + {world} Draft GPUs exceed the {GPUS_PER_NODE} GPUs of one node")
+    shared = bool(g("colocate"))                     # both roles on the same GPUs
+    if (max(world, targets) if shared else world + targets) > GPUS_PER_NODE:
+        raise ValueError(f"{targets} Target + {world} Draft GPUs exceed the {GPUS_PER_NODE} GPUs of one node"
+                         + ("" if shared else " (training.colocate shares GPUs between the roles)"))
     if engine == "offline" and not g("offline_feature_dir"):
         raise ValueError("inference_engine_type=offline needs inference.offline.feature_dir")
     per_engine = int(g("inference_num_gpus_per_engine", 1) or 1)
