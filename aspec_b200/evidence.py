@@ -166,7 +166,8 @@ class RunEvidenceRecorder:
         if report.get("state") not in ("validated", "skipped"):
             raise EvidenceError(f"cluster preflight did not validate: {report.get('state')!r} {report.get('problems')}")
         pol = self._policy()
-        need = int(pol.get("draft_gpus") or 0) + int(pol.get("target_gpus") or 0)
+        roles = (int(pol.get("draft_gpus") or 0), int(pol.get("target_gpus") or 0))
+        need = max(roles) if pol.get("colocate") else sum(roles)          # colocated roles share GPUs
         have = report.get("gpu_count")
         if report.get("state") == "validated" and have is not None and need and int(have) < need:
             raise EvidenceError(f"preflight saw {have} GPUs, the plan needs {need}")

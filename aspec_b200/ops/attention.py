@@ -137,6 +137,20 @@ class _IntervalAttentionFn(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+def _group_split(hq: int, hkv: int):
+    """Widths (each one the kernels tile: 16, 8, 4, 2, 1) that add up to the query heads per key head, or ``None``."""
+    if hkv <= 0 or hq % hkv:
+        return None
+    g, parts = hq // hkv, []
+    if g in (1, 2, 4, 8, 16) or g > 31:
+        return None
+    for width in (16, 8, 4, 2, 1):
+        while g >= width:
+            parts.append(width)
+            g -= width
+    return parts
+
+
 def interval_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, intervals: torch.Tensor,
                        scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Differentiable interval attention: tcgen05 kernels on CUDA, fp32 reference on CPU."""
@@ -148,6 +162,23 @@ def interval_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, interv
             note("attention", "tcgen05_interval_flash")
             return _IntervalAttentionFn.apply(q.contiguous(), k.contiguous(), v.contiguous(),
                                               intervals.contiguous(), scale)
+        parts = _group_split(q.shape[1], k.shape[1])
+        if parts is not None and K.supported(q[:, : k.shape[1]], k, v):
+            # a query-head group the kernels do not tile (5, 6, 10, ...) is cut into groups they do (4 + 1, 4 + 2, 8 + 2):
+            # one launch per piece over the same keys; autograd sums the pieces' key / value gradients
+            note("attention", "tcgen05_interval_flash")
+            hkv, g = k.shape[1], q.shape[1] // k.shape[1]
+            qg = q.reshape(q.shape[0], hkv, g, q.shape[-1])
+            outs, lses, at = [], [], 0
+            kc, vc, ivc = k.contiguous(), v.contiguous(), intervals.contiguous()
+            for width in parts:
+                piece = qg[:, :, at:at + width].reshape(q.shape[0], hkv * width, q.shape[-1]).contiguous()
+                o, l = _IntervalAttentionFn.apply(piece, kc, vc, ivc, scale)
+                outs.append(o.reshape(q.shape[0], hkv, width, v.shape[-1]))
+                lses.append(l.reshape(hkv, width, q.shape[0]))
+                at += width
+            return (torch.cat(outs, 2).reshape(q.shape[0], q.shape[1], v.shape[-1]),
+                    torch.cat(lses, 1).reshape(q.shape[1], q.shape[0]))
         note("attention", "dense_mask_fp32")
         return K.unsupported_shape_fallback(q, k, v, intervals, scale)
     note("attention", "reference_fp32_cpu")

@@ -292,7 +292,7 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
                 "engine": flat["inference_engine_type"], "context_shard_alignment": align}
     pol = {"world_size": world, "target_gpus": int(flat["inference_num_gpus"]) if flat["inference_engine_type"] == "native" else 0,
            "draft_gpus": world, "context_parallel": cp, "ulysses": u, "ring": r, "expert_parallel": ep,
-           "vocab_parallel": vp, "fsdp_strategy": flat["fsdp_strategy"], **resolve_batch_size(flat, dp),
+           "vocab_parallel": vp, "fsdp_strategy": flat["fsdp_strategy"], "colocate": bool(flat.get("colocate")), **resolve_batch_size(flat, dp),
            "num_train_steps": flat.get("num_train_steps"), "seed": flat["seed"]}
     memory = estimate_memory(draft, flat, algorithm, dp, flat["fsdp_strategy"])
     if not memory["fits"]:

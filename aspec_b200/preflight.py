@@ -38,7 +38,9 @@ def run_cluster_preflight(flat: Dict) -> dict:
     except Exception:                                   # noqa: BLE001
         n = 0
     native = flat.get("inference_engine_type") == "native"
-    need = int(flat["world_size"]) + (int(flat.get("inference_num_gpus") or 0) if native else 0)
+    targets = int(flat.get("inference_num_gpus") or 0) if native else 0
+    # colocated roles share GPUs: the larger role sets the requirement
+    need = max(int(flat["world_size"]), targets) if flat.get("colocate") else int(flat["world_size"]) + targets
     out = {"mode": flat.get("cluster_mode", "single_node"), "host": socket.gethostname(), "gpu_count": n,
            "visible_gpus": n, "required_gpus": need, "checks": checks}
     if n == 0 or flat.get("force_cpu"):

@@ -409,9 +409,13 @@ def run_online(args) -> dict:
     summary = train_async_no_generation(flat, draft, log=lambda m: None)
     w = summary["window"]
     eng = summary.get("engines", [])
+    steady = summary.get("history", [])[args.warmup:]
+    med = lambda key: (sorted(h[key] for h in steady if key in h) or [None])[len([h for h in steady if key in h]) // 2]
     return {"value": w.get("tokens_per_second"), "unit": "tokens/s", "targets": T, "drafts": D,
             "steady_steps": w.get("steps"), "steady_tokens": w.get("tokens"), "steady_seconds": w.get("seconds"),
             "documents_per_update": args.accum * D, "ledger_validated": summary["ledger"]["validated"],
+            # where an update's wall time goes: inside the trainer (waiting for rows + compute) and around it (driver)
+            "median_trainer_step_seconds": med("perf/step_time"), "median_loop_step_seconds": med("perf/step_wall_time"),
             "vs_baseline_8gpu": (w.get("tokens_per_second") / BASELINE_8GPU) if (w.get("valid") and n == 8) else None,
             "target_busy_seconds": [e.get("busy_seconds") for e in eng], "target_tokens": [e.get("tokens") for e in eng],
             "timing": "steady window: from completion of warm-up update W to the last optimizer completion; each "

@@ -52,6 +52,8 @@ def test_forward_matches_reference(n_ctx, n_blocks, bs, hq, hkv, causal, window,
     (1536, 96, 7, 8, 2, False, None, 3),       # several packed documents
     (1500, 90, 7, 8, 2, True, 256, 3),         # window + causal inside the block + documents
     (4096, 512, 7, 32, 8, False, None, 1),     # the production head layout: 32 / 8 heads, 4 K context, 3584 queries
+    (600, 40, 7, 10, 2, False, None, 1),       # 5 query heads per key head: run as 4 + 1
+    (700, 30, 4, 12, 2, True, None, 2),        # 6 per key head: 4 + 2
 ])
 def test_backward_matches_reference(n_ctx, n_blocks, bs, hq, hkv, causal, window, docs):
     from aspec_b200.ops.attention import interval_attention, interval_attention_reference
@@ -66,6 +68,7 @@ def test_backward_matches_reference(n_ctx, n_blocks, bs, hq, hkv, causal, window
     qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
     ref, _ = interval_attention_reference(qr, kr, vr, iv, scale)
     ref.backward(do.float())
+    assert (out.float() - ref.detach()).abs().max().item() < 3e-2 * max(1.0, ref.abs().max().item())
     for name, a, b in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
         err = (a.float() - b).abs().max().item()
         assert err < 6e-2 * max(1.0, b.abs().max().item()), f"{name} err {err}"

@@ -429,3 +429,84 @@ def test_full_shard_trains_like_the_replicated_optimizer_on_two_gpus(tmp_path):
         assert "error" not in res, res.get("error")
         bad = [k for k, v in res.items() if v is not True]
         assert not bad, (rank, bad, res)
+
+
+def _ring_problem(world, S, E, HQ, HKV, D):
+    g = torch.Generator().manual_seed(world)
+    T = world * S
+    q = torch.randn(world, S, HQ, D, generator=g) * 0.5
+    k = torch.randn(T, HKV, D, generator=g) * 0.5
+    v = torch.randn(T, HKV, D, generator=g) * 0.5
+    ke = torch.randn(world, E, HKV, D, generator=g) * 0.5
+    ve = torch.randn(world, E, HKV, D, generator=g) * 0.5
+    iv = []
+    for r in range(world):
+        pos = r * S + torch.arange(S)
+        lo = torch.randint(0, T // 2, (S,), generator=g).clamp(max=pos)
+        n_extra = torch.randint(0, E + 1, (S,), generator=g)
+        iv.append(torch.stack([lo, pos + 1, torch.full((S,), S), S + n_extra], -1).to(torch.int32))
+    dout = torch.randn(world, S, HQ, D, generator=g) * 0.5
+    return q, k, v, ke, ve, iv, dout
+
+
+def _ring_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    res = {}
+    try:
+        from aspec_b200.ops.attention import interval_attention_reference
+        from aspec_b200.ops.gemm import check_status
+        from aspec_b200.parallel.ring_attention import ring_attention
+        S, E, HQ, HKV, D = 384, 16, 8, 2, 128
+        bf = torch.bfloat16
+        q, k, v, ke, ve, iv, dout = _ring_problem(world, S, E, HQ, HKV, D)
+        ql = q[rank].to(dev, bf).requires_grad_()
+        kl = torch.cat([k[rank * S:(rank + 1) * S], ke[rank]]).to(dev, bf).requires_grad_()
+        vl = torch.cat([v[rank * S:(rank + 1) * S], ve[rank]]).to(dev, bf).requires_grad_()
+        o, lse = ring_attention(ql, kl, vl, iv[rank].to(dev), S, D ** -0.5)
+        o.backward(dout[rank].to(dev, bf))
+        check_status(dev)
+        # fp32 statement of the unsharded problem on this rank's queries (keys: the whole sequence, then own extra rows)
+        T = world * S
+        qr = q[rank].to(bf).float().requires_grad_()
+        kr = torch.cat([k, ke[rank]]).to(bf).float().requires_grad_()
+        vr = torch.cat([v, ve[rank]]).to(bf).float().requires_grad_()
+        table = iv[rank].clone()
+        table[:, 2:] += T - S
+        ref, ref_lse = interval_attention_reference(qr, kr, vr, table, D ** -0.5)
+        ref.backward(dout[rank].to(bf).float())
+        fin = torch.isfinite(ref_lse)
+        res["out"] = _close(o.cpu(), ref.detach(), 3e-2, 3e-2)
+        res["lse"] = _close(lse.cpu()[fin], ref_lse.detach()[fin], 2e-2, 2e-2)
+        res["dq"] = _close(ql.grad.cpu(), qr.grad, 5e-2, 3e-2 * qr.grad.abs().max().item())
+        # this shard's own keys collect gradient from every rank's queries: compare the sum over ranks through rank 0
+        mine = torch.zeros(T, HKV, D)
+        mine[rank * S:(rank + 1) * S] = kl.grad[:S].float().cpu()
+        total = mine.to(dev)
+        dist.all_reduce(total)
+        want = kr.grad[:T].to(dev)
+        dist.all_reduce(want)                        # every rank's reference holds only its own queries' share
+        res["dk"] = _close(total.cpu(), want.cpu(), 5e-2, 3e-2 * want.abs().max().item())
+        res["dk_extra"] = _close(kl.grad[S:].cpu(), kr.grad[T:], 5e-2, 3e-2 * max(kr.grad[T:].abs().max().item(), 1e-3))
+    except Exception as exc:  # noqa: BLE001
+        import traceback
+        res["error"] = f"{type(exc).__name__}: {exc}\n{traceback.format_exc()[-1500:]}"
+    torch.save(res, f"{out_path}.{rank}")
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_ring_attention_on_two_gpus_matches_the_unsharded_statement(tmp_path):
+    """Key / value blocks travel the ring over NCCL point-to-point while each stop runs the interval attention kernels;
+    output, log-sum-exp and all gradients against fp32 attention over the whole sequence."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    out = str(tmp_path / "ring")
+    mp.spawn(_ring_worker, args=(2, 29100 + os.getpid() % 500, out), nprocs=2, join=True)
+    for rank in range(2):
+        res = torch.load(f"{out}.{rank}")
+        assert "error" not in res, res.get("error")
+        bad = [k for k, v in res.items() if v is not True]
+        assert not bad, (rank, bad, res)

@@ -184,6 +184,9 @@ def test_preflight_without_gpus():
     if not torch.cuda.is_available():
         assert out["visible_gpus"] == 0 and out["ok"] is True
     assert run_cluster_preflight({"world_size": 2, "inference_num_gpus": 2, "inference_engine_type": "synthetic"})["required_gpus"] == 2
+    # colocated roles share GPUs: the larger role sets the requirement
+    assert run_cluster_preflight({"world_size": 8, "inference_num_gpus": 2, "inference_engine_type": "native",
+                                  "colocate": True})["required_gpus"] == 8
 
 
 # -- timeline, dumps, profiling windows --------------------------------------------------------------------------------
