@@ -30,7 +30,7 @@ LAYER_KINDS = (
 STAGES = ("dense", "indexer_warmup", "sparse")
 _EAGLE_ARCHS = (["LlamaForCausalLMEagle3"], ["LlamaForCausalLMEagle4"], ["Eagle3DeepseekV2ForCausalLM"])
 _MLA_ARCHS = (["K3DSparkModel"], ["Eagle3DeepseekV2ForCausalLM"])
-DEFAULT_WORKSPACE = 128 * 1024 * 1024
+DEFAULT_WORKSPACE = 2 * 1024 * 1024 * 1024      # transient budget of the sparse stages' row chunks; sized for a 180 GB GPU
 
 
 def resolve_head_layout(raw: Mapping) -> dict:

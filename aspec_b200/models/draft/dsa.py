@@ -188,6 +188,28 @@ class DSAAttention(DFlashAttention):
         ok = torch.cat([sel >= 0, blk_ok], 1)
         return indexed_attention(q, k, v, idx, ok, self.scale)
 
+    @torch.no_grad()
+    def _teacher_mass_on_selected(self, q, k_ctx, idx, ok, lse_rows):
+        """Sum over heads of the main attention's probability of each selected key, ``[n, S]`` fp32.
+
+        ``idx [n, S]`` indexes ``k_ctx [T, Hkv, d]`` (clamped; ``ok`` marks real entries); ``lse_rows [n, Hq]`` is the
+        log-sum-exp of each query head over its whole eligible context (0 where empty).  Rows are processed in chunks
+        sized by the indexer's workspace budget, and the key-head group is kept as a dimension instead of repeating the
+        gathered keys per query head, so the transient is ``S x Hkv x d`` per row."""
+        n, S = idx.shape
+        hk, d = self.num_kv_heads, self.head_dim
+        g = self.num_heads // hk
+        per_row = S * (hk * d * 6 + self.num_heads * 8)
+        rows = max(int(self.indexer.workspace_bytes // max(per_row, 1)), 1)
+        out = torch.empty(n, S, dtype=torch.float32, device=q.device)
+        for r0 in range(0, n, rows):
+            sl = slice(r0, min(r0 + rows, n))
+            kk = k_ctx[idx[sl]].float()                                               # [c, S, Hkv, d]
+            qq = q[sl].float().reshape(-1, hk, g, d)
+            logit = torch.einsum("nkgd,nskd->nkgs", qq, kk).reshape(qq.shape[0], hk * g, S) * self.scale
+            out[sl] = (torch.exp(logit - lse_rows[sl][:, :, None]) * ok[sl][:, None]).sum(1)
+        return out
+
     def _selected_set_kl(self, q, k, iq, ik, iw, sel, intervals, T):
         """``KL(teacher || indexer)`` per query over its selected keys.  teacher(s) is proportional to the sum over heads
         of the main attention's probability of key ``s`` under the softmax over the whole eligible context."""
@@ -206,11 +228,9 @@ class DSAAttention(DFlashAttention):
             ok = sel[sl] >= 0
             sel_score = (torch.einsum("nhd,nsd->nhs", iq[sl].float(), ik[s_idx].float()).relu() * iw[sl][:, :, None]).sum(1)
             with torch.no_grad():
-                kk = k[:T][s_idx].float().repeat_interleave(g, 2)                       # [c, S, Hq, d]
-                logit = torch.einsum("nhd,nshd->nhs", q[sl].float(), kk) * self.scale
                 l = lse[:, sl].t()
                 l = torch.where(torch.isfinite(l), l, torch.zeros_like(l))
-                t_sel = (torch.exp(logit - l[:, :, None]) * ok[:, None]).sum(1)
+                t_sel = self._teacher_mass_on_selected(q[sl].detach(), k[:T].detach(), s_idx, ok, l)
                 t_sel = t_sel / t_sel.sum(-1, keepdim=True).clamp_min(1e-20)
             logp = torch.log_softmax(sel_score.masked_fill(~ok, float("-inf")), -1).masked_fill(~ok, 0.0)
             kl = (t_sel * (torch.log(t_sel.clamp_min(1e-20)) - logp)).sum(-1)
@@ -295,8 +315,7 @@ class DSAAttention(DFlashAttention):
                 lse = torch.logsumexp(torch.stack(parts), 0)                                 # [Hq, Q_tot] over all shards
                 lse = torch.where(torch.isfinite(lse), lse, torch.zeros_like(lse)).t()
                 if T:
-                    logit = torch.einsum("nhd,nshd->nhs", q_all.float(), k[:T][safe].float().repeat_interleave(g, 2)) * self.scale
-                    t_loc = (torch.exp(logit - lse[:, :, None]) * ok[:, None]).sum(1)
+                    t_loc = self._teacher_mass_on_selected(q_all.detach(), k[:T].detach(), safe, ok, lse)
                 else:
                     t_loc = torch.zeros(q_tot, local.shape[1], device=x.device)
                 z = t_loc.sum(-1)
