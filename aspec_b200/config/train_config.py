@@ -178,6 +178,7 @@ class TrainingConfig:
     streaming_dispatch_with_training: bool = False
     pipeline_dispatch_with_training: bool = False
     prefetch_depth: int = 2
+    dispatch_ahead_updates: int = 1      # updates whose rows are at the Target engines beyond the one in training
     save_interval: int = 5000
     save_per_epoch: bool = False
     save_final_checkpoint: bool = True

@@ -93,15 +93,25 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
         submitted_plans[step] = rows
         return True
 
+    # how many updates beyond the one in training have their rows at the producers: 1 keeps the Targets one update
+    # ahead; a long-context run with one row per update needs as many as there are Target GPUs to keep them all busy
+    ahead = max(int(args.get("dispatch_ahead_updates", 1) or 1), 1)
     completed = 0
     step = start_step
     have_next = submit(step)
+    submitted_to = step if have_next else step - 1        # last update whose rows were handed to the producers
+    exhausted = not have_next
     while have_next and completed < num_steps:
         t_step = time.perf_counter()
         deadline = t_step + budget
         futures = [t.call_async("train_from_queue", step, accumulation, budget) for t in trainers]
         # dispatch-ahead: the producers work on the next update while the trainers compute this one
-        have_next = (completed + 1 < num_steps) and submit(step + 1)
+        while not exhausted and submitted_to < min(step + ahead, start_step + num_steps - 1):
+            if submit(submitted_to + 1):
+                submitted_to += 1
+            else:
+                exhausted = True
+        have_next = (completed + 1 < num_steps) and submitted_to >= step + 1
         outs = [None] * len(futures)
         pending = set(range(len(futures)))
         while pending:
@@ -131,17 +141,24 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
             time.sleep(0.02)
         # release leases, then commit the work of this optimizer step
         committed: List[str] = []
+        lease_row = {tuple(l): row_id for row_id, (_o, rq) in results_by_row.items() for l in rq.leases}
+        trained_rows: Dict[str, List[int]] = {}               # rows this update really consumed -> their readers
         for out in outs:
             for consumer, slot, gen in out["releases"]:
-                rings[consumer].release_acknowledged(slot, gen, _owner(results_by_row, consumer, slot, gen))
+                row_id = lease_row.get((consumer, slot, gen))
+                rings[consumer].release_acknowledged(slot, gen, f"row:{row_id or 'unknown'}")
+                if row_id is None:
+                    raise RuntimeError(f"trainer {consumer} released slot {slot} (generation {gen}) that no reported row leased")
+                trained_rows.setdefault(row_id, []).append(consumer)
             committed.extend(out["committed"])
+        # with several producers, rows finish in any order: an update trains on the rows that arrived, which need not
+        # be the ones planned under its number (the ledger commits what was really consumed)
+        submitted_plans.pop(step, None)
         tokens = 0
-        for rank, req in submitted_plans.pop(step):
-            res = results_by_row.pop(req.row_id, None)
-            if res is None:
-                raise RuntimeError(f"row {req.row_id} was trained on but never reported by its engine")
-            for consumer in consumer_of_rank(rank):          # every reader of the row releases its own lease
-                controller.release_result(res[0], participant=f"trainer{consumer}")
+        for row_id, consumers in trained_rows.items():
+            res, req = results_by_row.pop(row_id)
+            for consumer in consumers:                         # every reader of the row releases its own lease
+                controller.release_result(res, participant=f"trainer{consumer}")
             tokens += sum(req.document_lengths)
         controller.commit_optimizer_step(step, committed)
         completed += 1

@@ -258,7 +258,8 @@ def compile_execution_plan(config: Config) -> ExecutionPlan:
     caps.append(CapabilityDecision("vocab_head", "fused_rowstats_gemm+streaming_loss", "logits stay bf16; no fp32 [rows, V]"))
     # a trainer holds the slots of all micro-batches of an update until its optimizer step commits, and the next
     # update's rows are dispatched meanwhile: fewer slots than that deadlock the producer against the consumer
-    need_slots = int(flat["draft_accumulation_steps"]) * int(flat["micro_batch_size"]) + 1
+    ahead = max(int(flat.get("dispatch_ahead_updates", 1) or 1), 1)
+    need_slots = int(flat["draft_accumulation_steps"]) * int(flat["micro_batch_size"]) * (1 if ahead == 1 else ahead) + 1
     if int(flat.get("transport_destination_ring_slots", 1) or 1) < need_slots:
         caps.append(CapabilityDecision("feature_ring", f"destination_ring_slots raised to {need_slots}",
                                        f"configured {flat.get('transport_destination_ring_slots')}: one update keeps "

@@ -217,3 +217,17 @@ def test_checkpoint_at_every_epoch_end(tmp_path):
     assert summary["completed_steps"] == 5
     ck = os.path.join(flat["output_dir"], "checkpoints")
     assert sorted(d for d in os.listdir(ck) if d.startswith("iter_")) == ["iter_0000002", "iter_0000004", "iter_0000005"]
+
+
+@pytest.mark.timeout(600)
+def test_rows_dispatched_several_updates_ahead(tmp_path):
+    """``dispatch_ahead_updates`` keeps the producers several updates ahead of the trainers; the plan sizes the rings for
+    it, every update trains on rows that really arrived, and the ledger validates."""
+    plan = _plan(tmp_path, ["training.dispatch_ahead_updates=3", "training.num_train_steps=5"])
+    flat = plan.to_runtime_args()
+    assert flat["transport_destination_ring_slots"] >= 3 * 2 + 1
+    flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=0, save_final_checkpoint=False)
+    os.makedirs(flat["output_dir"], exist_ok=True)
+    summary = train_async_no_generation(flat, plan.draft_config, log=lambda m: None)
+    assert summary["completed_steps"] == 5 and summary["ledger"]["validated"]
+    assert len(summary["ledger"]["committed_work_ids"]) == 5 * 2 * 2
