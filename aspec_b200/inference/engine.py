@@ -94,9 +94,10 @@ class InferenceEngine:
 class NativeTargetEngine(InferenceEngine):
     def __init__(self, target_config: dict, layer_ids: Sequence[int], device: str = "cuda:0", dtype: str = "bfloat16",
                  seed: int = 0, name: str = "target0", device_flags: bool = False, weights_path: Optional[str] = None,
-                 fail_after: Optional[int] = None):
+                 fail_after: Optional[int] = None, delay_s: float = 0.0):
         from aspec_b200.models.target.dense import DenseTarget, TargetConfig
         self.name = name
+        self.delay_s = float(delay_s or 0.0)    # a slow producer for pipeline experiments (host sleep per call)
         self.device = torch.device(device)
         self.layer_ids = tuple(layer_ids)
         self.device_flags = device_flags
@@ -137,6 +138,8 @@ class NativeTargetEngine(InferenceEngine):
         outs = []
         if self.fail_after is not None and getattr(self, "rows_done", 0) + len(requests) > self.fail_after:
             raise RuntimeError(f"{self.name}: injected producer failure")
+        if self.delay_s:
+            time.sleep(self.delay_s)
         # all requests of the call run as ONE packed prefill (bigger GEMMs); each request's rows go to its own slots
         all_views, segments, off = [], [], 0
         for req in requests:

@@ -34,7 +34,8 @@ def create_engines(flat: Dict, draft_config: dict, layer_ids: List[int], target_
         tcfg = target_config_from_args(flat, draft_config)
         engines = [ProcessActor(NativeTargetEngine, tcfg, layer_ids, dev, "bfloat16" if dev.startswith("cuda") else "float32",
                                 int(flat.get("seed", 0)), f"target{i}", bool(flat.get("device_flags", False)),
-                                flat.get("target_weights_path"), fault, name=f"target{i}")
+                                flat.get("target_weights_path"), fault, float(flat.get("producer_delay_seconds", 0.0) or 0.0),
+                                name=f"target{i}")
                    for i, dev in enumerate(target_devices)]
         for i, e in enumerate(engines):
             e.wait_ready()
