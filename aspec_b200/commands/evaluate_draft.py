@@ -56,6 +56,10 @@ def main(argv=None) -> int:
     ap.add_argument("--block-size", type=int, default=7)
     ap.add_argument("--anchors-per-doc", type=int, default=16)
     ap.add_argument("--max-docs", type=int, default=256)
+    ap.add_argument("--generate", type=int, default=0, metavar="N",
+                    help="also run the speculative decode loop: from each document's prompt (the tokens before its first "
+                         "supervised position) generate N tokens with the live Target and report tokens per Target pass")
+    ap.add_argument("--generate-docs", type=int, default=16)
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--output")
     a = ap.parse_args(argv)
@@ -96,6 +100,25 @@ def main(argv=None) -> int:
         raise ValueError("this offline feature dataset has no lm_head.pt; compute features with the in-framework Target instead (omit --features)")
     res = evaluate(consumer, lm_head, docs, features_of, anchors_per_doc=a.anchors_per_doc)
     res.update(asset=a.asset_dir, algorithm=manifest.get("algorithm"), documents=len(docs), block_size=a.block_size)
+    if a.generate > 0:
+        if a.features:
+            raise ValueError("--generate needs the live Target (omit --features)")
+        from aspec_b200.data.utils import unpack_loss_mask
+        from aspec_b200.inference.speculative_decode import speculative_generate
+        rounds, tokens, passes = [], 0, 0
+        for d in docs[: a.generate_docs]:
+            ids = d["input_ids"].reshape(-1)
+            mask = unpack_loss_mask(d["packed_loss_mask"], ids.numel(), dtype=torch.bool)
+            first = int(mask.float().argmax()) if bool(mask.any()) else ids.numel() // 2
+            if first < 2:
+                continue
+            out = speculative_generate(target, consumer, ids[:first].to(dev), layers, max_new_tokens=a.generate)
+            rounds += out["accepted_per_round"]
+            tokens += len(out["tokens"])
+            passes += out["target_passes"]
+        res["generation"] = {"documents": min(len(docs), a.generate_docs), "new_tokens": tokens, "target_passes": passes,
+                             "tokens_per_target_pass": tokens / max(passes, 1),
+                             "mean_accepted_draft_tokens": sum(rounds) / max(len(rounds), 1)}
     text = json.dumps(res, indent=2)
     if a.output:
         open(a.output, "w").write(text + "\n")

@@ -122,7 +122,7 @@ def route_and_run(bank: ExpertBank, hidden: torch.Tensor, selected: torch.Tensor
     order = torch.argsort(flat_expert, stable=True)
     token_of = order // k
     sorted_expert = flat_expert[order]
-    x_sorted = hidden[token_of]
+    x_sorted = hidden.index_select(0, token_of)        # backward: atomic index_add_ (every token repeats top-k times)
     if bank.ep_size > 1:
         group = ep_group if ep_group is not None else bank.ep_group
         if bank.fused_ep is not None and x_sorted.is_cuda:

@@ -71,6 +71,14 @@ def test_evaluate_exported_asset_with_live_target(quickstart_run, tmp_path, caps
     assert len(result["accept_rate_at"]) == 3 and 1.0 <= result["tau"] <= 4.0
     rates = result["accept_rate_at"]
     assert all(0.0 <= r <= 1.0 for r in rates) and rates == sorted(rates, reverse=True)
+    # the decode loop: greedy speculative generation from every document's prompt with the live Target
+    rc = evaluate_draft.main(["--asset-dir", str(quickstart_run / "stage-2" / "asset"), "--data", data, "--block-size", "4",
+                              "--anchors-per-doc", "1", "--device", "cpu", "--output", str(out), "--generate", "6",
+                              "--generate-docs", "3"])
+    capsys.readouterr()
+    gen = json.loads(out.read_text())["generation"]
+    assert rc == 0 and gen["new_tokens"] == 18 and gen["target_passes"] >= 3
+    assert 1.0 <= gen["tokens_per_target_pass"] <= 4.0 and 0.0 <= gen["mean_accepted_draft_tokens"] <= 3.0
 
 
 def test_prepare_target_data_then_evaluate_from_store(quickstart_run, tmp_path, capsys):
