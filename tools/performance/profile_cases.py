@@ -9,7 +9,8 @@ run to completion without the profiler.  Cases: ``gemm``, ``gemm_head``,
 forward + backward), ``indexer`` (scores + top-k), and the compute+collective kernels with every "peer" buffer placed on
 this same GPU - ``gemm_mirror`` (GEMM whose epilogue also stores the tile into two more destinations), ``gemm_scatter``
 (column-scatter epilogue of the Ulysses projection), ``shard_step`` (peer-sum of gradient shards + sum of squares, then
-AdamW with the bf16 weights stored into every replica), ``peer_lse`` (log-sum-exp merge over peers' statistics).  On one
+AdamW with the bf16 weights stored into every replica), ``peer_lse`` (log-sum-exp merge over peers' statistics), ``full_shard`` (a layer's parameter
+gather and gradient reduce-scatter of the FULL_SHARD strategy).  On one
 GPU these captures show the kernels' DRAM and tensor-pipe behaviour; NVLink traffic is by construction zero here.
 """
 from __future__ import annotations
