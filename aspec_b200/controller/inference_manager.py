@@ -79,6 +79,16 @@ class InferenceManager:
                 return True
         return _Done()
 
+    def _pick_engine(self) -> int:
+        """Least-loaded engine; among equally loaded ones the one after the last pick, so that a stream of rows that
+        arrive one at a time (long-context runs) rotates over all Target GPUs instead of always taking the first."""
+        n = len(self.engines)
+        start = (getattr(self, "_last_engine", -1) + 1) % n
+        order = [(start + i) % n for i in range(n)]
+        eng = min(order, key=lambda i: self._engine_load[i])
+        self._last_engine = eng
+        return eng
+
     def _collect(self, block: bool) -> None:
         while self._inflight:
             fut, reqs, eng = self._inflight[0]
@@ -99,10 +109,10 @@ class InferenceManager:
             nonlocal batch
             if not batch:
                 return
-            eng = min(range(len(self.engines)), key=lambda i: self._engine_load[i])
+            eng = self._pick_engine()
             while self._engine_load[eng] >= self.max_inflight:
                 self._collect(block=True)
-                eng = min(range(len(self.engines)), key=lambda i: self._engine_load[i])
+                eng = self._pick_engine()
             self._inflight.append((self._call(self.engines[eng], "generate", batch), batch, eng))
             self._engine_load[eng] += 1
             batch = []
