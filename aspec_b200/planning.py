@@ -175,6 +175,12 @@ def validate_scope(flat: Dict[str, Any], draft: dict, algorithm: str, policy: di
     if max_pos and int(flat["max_seq_length"]) > int(max_pos) and not (draft.get("rope_scaling") or draft.get("rope_parameters")):
         notes.append(f"max_seq_length {flat['max_seq_length']} exceeds the Draft's max_position_embeddings {max_pos} "
                      "without a RoPE scaling rule")
+    # -- keys that would change what is trained and have no implementation (the reference refuses these too) -----
+    if int(g("eagle3_num_anchors") or 0):
+        raise ValueError("anchored EAGLE3 (training.eagle3_num_anchors) is not part of the training path: EAGLE3 / EAGLE4 "
+                         "train on every supervised position")
+    if g("compile_model"):
+        notes.append("training.compile_model has no effect: there is no tracing compiler on this path")
     # -- schedule ---------------------------------------------------------------------------------------------
     steps = g("num_train_steps")
     if steps is not None and int(steps) < 0:

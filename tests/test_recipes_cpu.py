@@ -66,6 +66,7 @@ def _plan(recipe, *overrides):
     ("qwen3_8b_dspark.yaml", ["inference.inference_num_gpus=3", "inference.inference_num_gpus_per_engine=2"], "multiple of"),
     ("qwen3_8b_eagle3.yaml", ["training.sp_ulysses_size=3", "training.training_num_gpus_per_node=3"], "must divide the attention head counts"),
     ("qwen3_5_9b_mtp.yaml", ["training.sp_ring_size=2", "training.training_num_gpus_per_node=2"], "not sharded over sequences"),
+    ("qwen3_8b_eagle3.yaml", ["training.eagle3_num_anchors=64"], "anchored EAGLE3"),
 ])
 def test_the_planner_refuses_what_cannot_run(recipe, overrides, message):
     with pytest.raises(ValueError, match=message):
