@@ -311,20 +311,24 @@ def online_with_split_search(args, draft_rate: float) -> dict:
     faster - at the split the topology search picks.  The better measured run is reported; both are listed under
     ``split_search`` so the choice can be checked."""
     from aspec_b200.topology import legal_splits, predict
+    # a Draft rank fed over the feature rings trains at about 0.8 of its resident-feature rate (measured on B200s:
+    # 78 K against 97.8 K tokens/s at 5 Target + 3 Draft GPUs); the rule is given that, not the resident rate
+    ring_fed = 0.8
     first = online_child(args)
     tokens, busy = first.get("target_tokens") or [], first.get("target_busy_seconds") or []
     per_gpu = sorted(t / b for t, b in zip(tokens, busy) if t and b)
-    search = {"draft_tokens_per_s_per_gpu": draft_rate, "rule": "min(T x target rate, D x draft rate) over the legal splits",
+    search = {"draft_tokens_per_s_per_gpu": draft_rate, "ring_fed_draft_efficiency": ring_fed,
+              "rule": "min(T x target rate, D x draft rate x ring-fed efficiency) over the legal splits",
               "runs": [{"split": f"{first.get('targets')}T+{first.get('drafts')}D", "value": first.get("value")}]}
     first["split_search"] = search
     if not per_gpu or not first.get("value"):
         return first
     target_rate = per_gpu[len(per_gpu) // 2]
     search["target_tokens_per_s_per_gpu"] = target_rate
-    ranked = sorted(((predict(target_rate, draft_rate, t, d)[0], t, d) for t, d in legal_splits(args.gpus)), reverse=True)
+    ranked = sorted(((predict(target_rate, draft_rate, t, d, ring_fed)[0], t, d) for t, d in legal_splits(args.gpus)), reverse=True)
     search["predicted"] = [{"split": f"{t}T+{d}D", "tokens_per_s": p} for p, t, d in ranked[:3]]
     best_p, best_t, best_d = ranked[0]
-    here = predict(target_rate, draft_rate, first["targets"], first["drafts"])[0]
+    here = predict(target_rate, draft_rate, first["targets"], first["drafts"], ring_fed)[0]
     if best_t == first["targets"] or best_p < 1.05 * here:
         return first
     second = online_child(args, targets=best_t)

@@ -47,18 +47,26 @@ def test_online_split_search_runs_the_predicted_split_and_keeps_the_measured_bes
     spec.loader.exec_module(bench)
     asked = []
 
+    rate = {"target": 40e3}
+
     def fake_child(args, targets=0):
         t = targets or args.gpus // 2
         d = args.gpus - t
         asked.append(t)
-        value = min(64e3 * t, 96e3 * d) * 0.9
+        value = min(rate["target"] * t, 96e3 * 0.8 * d) * 0.95
         return {"value": value, "targets": t, "drafts": d, "ledger_validated": True,
-                "target_tokens": [64e3 * 20] * t, "target_busy_seconds": [20.0] * t}
+                "target_tokens": [rate["target"] * 20] * t, "target_busy_seconds": [20.0] * t}
     monkeypatch.setattr(bench, "online_child", fake_child)
+    # a slow Target: five Target GPUs beat four even with ring-fed Drafts at 0.8 of their resident rate
     out = bench.online_with_split_search(argparse.Namespace(gpus=8, targets=0), draft_rate=96e3)
     assert asked == [4, 5] and out["targets"] == 5 and out["drafts"] == 3
     assert [r["split"] for r in out["split_search"]["runs"]] == ["4T+4D", "5T+3D"]
     assert out["split_search"]["predicted"][0]["split"] == "5T+3D"
+    # the measured B200 rates: 4T+4D stays, no second run
+    asked.clear()
+    rate["target"] = 68.5e3
+    out = bench.online_with_split_search(argparse.Namespace(gpus=8, targets=0), draft_rate=97.8e3)
+    assert asked == [4] and out["targets"] == 4 and out["split_search"]["predicted"][0]["split"] == "4T+4D"
     asked.clear()
     out = bench.online_with_split_search(argparse.Namespace(gpus=4, targets=0), draft_rate=96e3)
     assert asked == [2] and out["targets"] == 2                       # 2T+2D is already the balanced split of four GPUs
