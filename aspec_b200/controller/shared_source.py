@@ -54,9 +54,10 @@ class SharedSourceState:
             if experiment in self.live:
                 self.live.remove(experiment)
                 self.fenced[experiment] = reason
-                world = max([c for n, c in self.offsets.items() if c > self.offsets[experiment]] + [10 ** 9])
+                # its consumers are [its offset, the next experiment's offset)
+                end = min([c for c in self.offsets.values() if c > self.offsets[experiment]] + [10 ** 9])
                 self.manager.dead_consumers |= {c for c in self.manager.rings
-                                                if self.offsets[experiment] <= c < world}
+                                                if self.offsets[experiment] <= c < end}
                 for entry in self._pending.values():
                     entry.pop(experiment, None)
                 self._flush_ready()

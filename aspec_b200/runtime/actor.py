@@ -120,8 +120,11 @@ class ProcessActor:
 
     def _poll(self, call_id: int) -> bool:
         with self._lock:
-            while self._parent.poll(0):
-                self._drain(0)
+            try:
+                while self._parent.poll(0):
+                    self._drain(0)
+            except (EOFError, OSError):
+                return True               # the process is gone: ``get`` reports how it ended
             return call_id in self._results
 
     def _wait(self, call_id: int, method: str, timeout: Optional[float]) -> Any:
@@ -137,7 +140,8 @@ class ProcessActor:
                 try:
                     self._drain(remaining)
                 except (EOFError, OSError):
-                    raise ActorError(f"{self.name} died during {method}") from None
+                    self._proc.join(1.0)
+                    raise ActorError(f"{self.name} exited (code {self._proc.exitcode}) during {method}") from None
             if not self._proc.is_alive() and not self._parent.poll(0):
                 raise ActorError(f"{self.name} exited (code {self._proc.exitcode}) during {method}")
             if deadline is not None and time.monotonic() >= deadline:

@@ -304,6 +304,8 @@ class TrainerActor:
         if self.fault and int(self.fault.get("step", -1)) == step and int(self.fault.get("rank", 0)) == self.rank:
             if self.fault.get("kind") == "sleep":
                 time.sleep(float(self.fault.get("seconds", 3600)))
+            elif self.fault.get("kind") == "exit":          # the process disappears between two updates (a lost node)
+                os._exit(int(self.fault.get("code", 17)))
             else:
                 raise RuntimeError(f"trainer {self.rank}: injected failure at step {step}")
         consumed, keys = [], []

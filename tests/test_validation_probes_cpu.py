@@ -32,7 +32,7 @@ def test_resume_replay_is_exact_and_the_audit_sees_a_changed_state(tmp_path):
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("action", ["trainer_raise", "producer_fail"])
+@pytest.mark.parametrize("action", ["trainer_raise", "producer_fail", "trainer_exit"])
 def test_injected_host_faults_fail_the_run_and_leave_nothing_behind(tmp_path, action):
     res = _probe("recipe_faults", "--config", RECIPE, "--action", action, "--out", str(tmp_path / action))
     assert res["ok"], res
@@ -44,3 +44,24 @@ def test_layouts_are_compared_update_by_update(tmp_path):
                  "--a", "training.fsdp_strategy=REPLICATE", "--b", "training.fsdp_strategy=SHARD_OPTIMIZER", "--",
                  "training.training_num_gpus_per_node=2", "transport.destination_ring_slots=5")
     assert res["metrics_agree"] and res["updates"] == [3, 3]
+
+
+@pytest.mark.timeout(600)
+def test_a_failing_experiment_is_fenced_while_its_siblings_finish(tmp_path):
+    import yaml
+    recipe = tmp_path / "multi.yaml"
+    drafts = os.path.join(ROOT, "aspec_b200", "config", "drafts")
+    recipe.write_text(yaml.safe_dump({
+        "model": {"draft_model_config": os.path.join(drafts, "dspark_tiny.json")},
+        "dataset": {"train_data_path": "synthetic", "synthetic_num_documents": 48, "synthetic_min_length": 32,
+                    "synthetic_max_length": 96, "synthetic_vocab_size": 500},
+        "inference": {"inference_engine_type": "synthetic"},
+        "training": {"training_num_gpus_per_node": 1, "micro_batch_size": 1, "draft_accumulation_steps": 2, "max_seq_length": 128,
+                     "num_train_steps": 3, "learning_rate": 1e-3, "dspark_block_size": 4, "dspark_num_anchors": 16,
+                     "dflash_block_size": 4, "dflash_num_anchors": 16, "save_interval": 0, "seed": 7},
+        "transport": {"destination_ring_slots": 3},
+        "experiments": [{"name": "spark"}, {"name": "flash", "model": {"draft_model_config": os.path.join(drafts, "dflash_tiny.json")}},
+                        {"name": "spark2"}],
+    }))
+    res = _probe("multi_draft_faults", "--config", str(recipe), "--victim", "flash", "--action", "exit", "--out", str(tmp_path / "run"))
+    assert res["ok"] and res["sibling_steps"] == {"spark": 3, "spark2": 3}, res

@@ -7,6 +7,8 @@
 * ``trainer_stall``  - trainer ``rank`` sleeps inside update ``step`` past ``training.optimizer_step_timeout_seconds``:
   the controller's deadline ends the run and terminates the trainers.
 * ``producer_fail``  - the Target engine raises after ``--rows`` rows: the run fails with the producer's error.
+* ``trainer_exit``   - trainer ``rank``'s process exits at the start of update ``step`` (between updates, nothing of its
+  own in flight - what losing a node looks like): the controller notices the missing process and ends the run.
 
 Every fault is made on the host (an exception, a sleep); no GPU is faulted or hung.  After the failure the probe checks
 that ``evidence.json`` says ``failed`` with the error recorded, that the cleanup section lists every actor as stopped,
@@ -23,7 +25,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 
 from aspec_b200 import train_entry  # noqa: E402
 
-EXPECT = {"trainer_raise": "injected failure", "trainer_stall": "Timeout", "producer_fail": "injected producer failure"}
+EXPECT = {"trainer_raise": "injected failure", "trainer_stall": "Timeout", "producer_fail": "injected producer failure",
+          "trainer_exit": "exited"}
 
 
 def main(argv=None) -> int:
@@ -39,7 +42,8 @@ def main(argv=None) -> int:
     inject = {"trainer_raise": [f"debug.fault_injection={{kind: raise, step: {a.step}, rank: {a.rank}}}"],
               "trainer_stall": [f"debug.fault_injection={{kind: sleep, step: {a.step}, rank: {a.rank}, seconds: 120}}",
                                 "training.optimizer_step_timeout_seconds=3"],
-              "producer_fail": [f"debug.producer_fail_after={a.rows}"]}[a.action]
+              "producer_fail": [f"debug.producer_fail_after={a.rows}"],
+              "trainer_exit": [f"debug.fault_injection={{kind: exit, step: {a.step}, rank: {a.rank}}}"]}[a.action]
     import psutil
     me = psutil.Process()
     before = {p.pid for p in me.children(recursive=True)}
