@@ -265,8 +265,10 @@ class TrainerActor:
             batch["packed_document_lengths"] = lens
         if hasattr(self.model, "sample_anchors"):
             seed = None
-            if getattr(self, "cp_size", 1) > 1:
-                # every rank of a context-parallel group must draw the same anchors for the row
+            if getattr(self, "cp_size", 1) > 1 or self.args.get("deterministic_anchor_sampling"):
+                # every rank of a context-parallel group must draw the same anchors for the row; with
+                # ``deterministic_anchor_sampling`` the draw depends on the row alone, so that the same recipe trains
+                # on the same blocks under any parallel layout
                 import zlib
                 seed = zlib.crc32(str(sample.row_id).encode()) ^ int(self.args.get("seed", 0))
             anchors, keep = self.model.sample_anchors(loss_mask, ctx_docs, lens if len(lens) > 1 else None, anchor_seed=seed)

@@ -44,6 +44,12 @@ def test_layouts_are_compared_update_by_update(tmp_path):
                  "--a", "training.fsdp_strategy=REPLICATE", "--b", "training.fsdp_strategy=SHARD_OPTIMIZER", "--",
                  "training.training_num_gpus_per_node=2", "transport.destination_ring_slots=5")
     assert res["metrics_agree"] and res["updates"] == [3, 3]
+    # context parallel 1 against 2: with row-derived anchor draws both layouts train on the same blocks
+    res = _probe("layout_compare", "--config", RECIPE, "--out", str(tmp_path / "cp"), "--steps", "3", "--rtol", "1e-4",
+                 "--a", "training.draft_context_parallel_size=1", "training.training_num_gpus_per_node=1",
+                 "--b", "training.draft_context_parallel_size=2", "training.training_num_gpus_per_node=2", "--",
+                 "transport.destination_ring_slots=5", "training.deterministic_anchor_sampling=true")
+    assert res["metrics_agree"] and res["worst_relative_difference"] < 1e-5
 
 
 @pytest.mark.timeout(600)
