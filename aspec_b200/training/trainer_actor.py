@@ -270,7 +270,8 @@ class TrainerActor:
                 # ``deterministic_anchor_sampling`` the draw depends on the row alone, so that the same recipe trains
                 # on the same blocks under any parallel layout
                 import zlib
-                seed = zlib.crc32(str(sample.row_id).encode()) ^ int(self.args.get("seed", 0))
+                # (by the documents it holds, not by its number: row numbers depend on how updates are dealt to ranks)
+                seed = zlib.crc32("|".join(str(d) for d in sample.data_ids).encode()) ^ int(self.args.get("seed", 0))
             anchors, keep = self.model.sample_anchors(loss_mask, ctx_docs, lens if len(lens) > 1 else None, anchor_seed=seed)
             batch["injected_anchors"], batch["injected_keep_mask"] = anchors, keep
         return batch

@@ -50,6 +50,12 @@ def test_layouts_are_compared_update_by_update(tmp_path):
                  "--b", "training.draft_context_parallel_size=2", "training.training_num_gpus_per_node=2", "--",
                  "transport.destination_ring_slots=5", "training.deterministic_anchor_sampling=true")
     assert res["metrics_agree"] and res["worst_relative_difference"] < 1e-5
+    # one rank accumulating four rows against two ranks accumulating two: the same documents per update, pooled the same way
+    res = _probe("layout_compare", "--config", RECIPE, "--out", str(tmp_path / "dp"), "--steps", "3", "--rtol", "1e-4",
+                 "--a", "training.training_num_gpus_per_node=1", "training.draft_accumulation_steps=4",
+                 "--b", "training.training_num_gpus_per_node=2", "training.draft_accumulation_steps=2", "--",
+                 "transport.destination_ring_slots=6", "training.deterministic_anchor_sampling=true", "dataset.length_group_size=1")
+    assert res["metrics_agree"] and res["worst_relative_difference"] < 1e-5
 
 
 @pytest.mark.timeout(600)
