@@ -182,9 +182,14 @@ class SyntheticEngine(InferenceEngine):
                 time.sleep(self.delay_s)
             views = self._slot_views(req)
             n = int(req.input_ids.shape[0])
-            g = torch.Generator().manual_seed(self.seed * 7919 + int(req.input_ids.sum()) % (2 ** 31))
-            hs = torch.randn(n, len(self.layer_ids) * self.hidden, generator=g)
-            last = torch.randn(n, self.hidden, generator=g)
+            # one stream per (document, layer): a layer's features do not depend on which other layers are captured, so
+            # a Draft sees the same features alone and as one reader of a shared stream
+            doc = self.seed * 7919 + int(req.input_ids.sum()) % (2 ** 31)
+            parts = []
+            for layer in (*self.layer_ids, -1):
+                g = torch.Generator().manual_seed((doc * 1000003 + int(layer) + 1) % (2 ** 63 - 1))
+                parts.append(torch.randn(n, self.hidden, generator=g))
+            hs, last = torch.cat(parts[:-1], -1), parts[-1]
             self._copy_features(req, views, hs, last)
             outs.append(self._finish(req, views, self.layer_ids, device_flags=True))
         return outs

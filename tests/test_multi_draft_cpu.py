@@ -164,3 +164,27 @@ output_dir: {tmp_path / 'run'}
     assert all(out[n].get("completed_steps") == 2 for n in ("spark", "eagle", "flash")), out
     assert out["shared_source"]["fenced"] == {} and out["shared_source"]["rows_shared"] == 2 * 2 * 2
     assert out["spark"]["ledger"]["committed_work_ids"] == out["eagle"]["ledger"]["committed_work_ids"]
+
+
+@pytest.mark.timeout(600)
+def test_a_reader_of_a_shared_stream_trains_like_the_same_draft_alone(tmp_path):
+    """Same recipe once on its own and once as one of two experiments: identical loss and gradient-norm trajectory
+    (shared rows, per-reader layer subsets of the union, row-keyed anchor draws)."""
+    from aspec_b200.planning import compile_execution_plan
+    from aspec_b200.train_entry import train_async_no_generation
+    plan = _plan(tmp_path)
+    for p in plan.plans.values():
+        p.runtime_args.update(deterministic_anchor_sampling=True)
+    logs = []
+    run_multi_draft(plan, log=logs.append)
+    shared = [(m["train/avg_loss"], m["train/grad_norm"]) for m in logs if m.get("experiment") == "spark" and "train/avg_loss" in m]
+    alone_plan = plan.plans["spark"]
+    flat = alone_plan.to_runtime_args()
+    flat.update(output_dir=str(tmp_path / "alone"), deterministic_anchor_sampling=True)
+    os.makedirs(flat["output_dir"], exist_ok=True)
+    alone_logs = []
+    train_async_no_generation(flat, alone_plan.draft_config, log=alone_logs.append)
+    alone = [(m["train/avg_loss"], m["train/grad_norm"]) for m in alone_logs if "train/avg_loss" in m]
+    assert len(shared) == len(alone) == 3
+    for (a, b), (c, d) in zip(shared, alone):
+        assert a == pytest.approx(c, rel=1e-6) and b == pytest.approx(d, rel=1e-6)
