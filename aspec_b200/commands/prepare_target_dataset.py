@@ -57,7 +57,8 @@ def main(argv=None) -> int:
 
     docs = ({"data_id": s.get("data_id", i), "input_ids": s["input_ids"], "packed_loss_mask": s["packed_loss_mask"]}
             for i, s in enumerate(samples))
-    store = materialize(a.output_dir, docs, features, binding, split=a.split, resume=a.resume, lm_head=target.lm_head)
+    store = materialize(a.output_dir, docs, features, binding, split=a.split, resume=a.resume, lm_head=target.lm_head,
+                        embedding=target.embed_tokens.weight)
     print(json.dumps({"output_dir": a.output_dir, "samples": len(store), "contract_id": binding["feature_contract"]["contract_id"]}))
     return 0
 

@@ -60,5 +60,7 @@ def create_engines(flat: Dict, draft_config: dict, layer_ids: List[int], target_
                              f"this Draft needs layers {list(layer_ids)} of width {hidden}")
         eng.attach_rings({c: hs[0] for c, hs in ring_handles.items()})
         head_file = os.path.join(flat["offline_feature_dir"], "lm_head.pt")      # written by prepare-target-data
-        return [eng], ({"file": head_file} if os.path.isfile(head_file) else None), None
+        embed_file = os.path.join(flat["offline_feature_dir"], "embed_tokens.pt")
+        return ([eng], ({"file": head_file} if os.path.isfile(head_file) else None),
+                ({"file": embed_file} if os.path.isfile(embed_file) else None))
     raise ValueError(f"unknown inference engine type {kind!r}")

@@ -129,11 +129,17 @@ class DenseTarget(nn.Module):
 
     @torch.no_grad()
     def init_random(self, seed: int = 0, std: float = 0.02) -> "DenseTarget":
-        g = torch.Generator(device="cpu").manual_seed(seed)
+        # one generator per device, seeded here: the weights depend on ``seed`` alone, not on what else drew from the
+        # global generator before (every Target replica of a run, and a Target built later to store features offline, are
+        # the same model); generated on the parameter's device, so host memory stays flat
+        gens = {}
         for name, p in self.named_parameters():
             if p.dim() >= 2:
-                # generate on the parameter's device in chunks to keep host memory flat
-                p.normal_(0.0, std)
+                g = gens.get(p.device)
+                if g is None:
+                    g = gens[p.device] = torch.Generator(device=p.device)
+                    g.manual_seed(int(seed))
+                p.normal_(0.0, std, generator=g)
         return self
 
     # -- pieces ---------------------------------------------------------------------------------

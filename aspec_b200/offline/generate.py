@@ -26,10 +26,11 @@ def target_binding(target_identity: Dict, draft_config: Dict, family: str, store
 
 def materialize(output_dir: str, documents: Iterable[dict], features: Callable[[torch.Tensor], tuple], binding: dict,
                 *, split: str = "train", resume: bool = False, progress: Optional[Callable[[int], None]] = None,
-                lm_head: Optional[torch.Tensor] = None) -> OfflineFeatureStore:
+                lm_head: Optional[torch.Tensor] = None, embedding: Optional[torch.Tensor] = None) -> OfflineFeatureStore:
     """``documents`` yield ``{"data_id", "input_ids", "loss_mask"}``; ``features(ids)`` returns the contract's tensors.
-    ``lm_head`` (the Target's frozen output head) is saved beside the features as ``lm_head.pt`` so that decode
-    evaluation can run from the dataset alone."""
+    ``lm_head`` (the Target's frozen output head) and ``embedding`` (its token embedding, which Drafts borrow frozen)
+    are saved beside the features as ``lm_head.pt`` / ``embed_tokens.pt`` in the Target's own dtype, so that training
+    and decode evaluation from the dataset alone see the model that made the features."""
     store = (OfflineFeatureStore(output_dir, allow_incomplete=True) if resume
              else OfflineFeatureStore(output_dir, create=True, binding=binding, last_hidden_states_prenorm=False))
     if resume and store.binding["feature_contract"]["contract_id"] != binding["feature_contract"]["contract_id"]:
@@ -51,6 +52,9 @@ def materialize(output_dir: str, documents: Iterable[dict], features: Callable[[
             progress(n + 1)
     if lm_head is not None:
         import os
-        torch.save(lm_head.detach().to(torch.bfloat16).cpu(), os.path.join(output_dir, "lm_head.pt"))
+        torch.save(lm_head.detach().cpu(), os.path.join(output_dir, "lm_head.pt"))
+    if embedding is not None:
+        import os
+        torch.save(embedding.detach().cpu(), os.path.join(output_dir, "embed_tokens.pt"))
     store.mark_complete()
     return store

@@ -201,7 +201,9 @@ class TrainerActor:
                 raise ValueError(f"stored Target head {tuple(lm_head.shape)} does not fit the Draft configuration")
         elif isinstance(lm_head, dict):
             lm_head = import_tensor(lm_head)
-        if isinstance(embedding, dict):
+        if isinstance(embedding, dict) and "file" in embedding:
+            embedding = torch.load(embedding["file"], map_location="cpu")
+        elif isinstance(embedding, dict):
             embedding = import_tensor(embedding)
         if lm_head is None:
             g = torch.Generator().manual_seed(1234)

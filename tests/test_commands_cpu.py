@@ -248,6 +248,18 @@ output_dir: {tmp_path / 'run'}
     evidence = json.loads((tmp_path / "run" / "evidence.json").read_text())
     assert evidence["state"] == "completed" and evidence["training_summary"]["completed_steps"] == 2
     assert evidence["training_summary"]["ledger"]["validated"]
+    assert (feats / "embed_tokens.pt").exists()
+    # the same recipe with the live Target (same seed, hence the same model) trains the same trajectory: the stored
+    # features, output head and embedding are the ones the live run uses
+    def losses(run_dir):
+        return [json.loads(l)["train/avg_loss"] for l in open(run_dir / "runs" / "metrics.jsonl") if "train/avg_loss" in l]
+    common = ["training.deterministic_anchor_sampling=true", "training.save_final_checkpoint=false"]
+    assert train_entry.main(["--config", str(recipe), *common, f"output_dir={tmp_path / 'stored'}"]) == 0
+    assert train_entry.main(["--config", str(recipe), *common, "inference.inference_engine_type=native",
+                             "inference.inference_num_gpus=1", f"output_dir={tmp_path / 'live'}"]) == 0
+    capsys.readouterr()
+    stored, live = losses(tmp_path / "stored"), losses(tmp_path / "live")
+    assert len(stored) == len(live) == 2 and stored == pytest.approx(live, rel=2e-3)
     with pytest.raises(ValueError, match="offline features hold layers"):
         train_entry.main(["--config", str(recipe), "model.draft_model_config=dflash_tiny.json",
                           f"output_dir={tmp_path / 'other'}"])
