@@ -45,6 +45,15 @@ class TrainerActor:
                                     device_id=self.device if self.cuda else None,
                                     timeout=timedelta(minutes=float(self.args.get("distributed_timeout_minutes") or 10)))
         torch.manual_seed(int(self.args.get("seed", 0)))
+        # nothing in training draws from these two, but they are part of the checkpointed RNG state: seeded, two runs of
+        # one recipe write identical checkpoints
+        import random
+        random.seed(int(self.args.get("seed", 0)) * 1000003 + rank)
+        try:
+            import numpy as np
+            np.random.seed((int(self.args.get("seed", 0)) * 1000003 + rank) % (2 ** 32))
+        except ImportError:          # pragma: no cover
+            pass
         self.draft_config = AutoDraftModelConfig.from_dict(draft_config)
         self.model = build_training_model(self.draft_config, self.args, self.device, self.dtype)
         if self.args.get("initial_draft_model_path") and not self.args.get("load_path"):

@@ -6,6 +6,12 @@ Three bounded runs of the ordinary train entry: ``whole`` (0 -> N, checkpoints a
 ``whole``'s checkpoint K, continues to N).  The two final checkpoints are compared section by section with the
 checkpoint audit: weights, fp32 masters, both moments, the applied-step count, the scheduler, every rank's RNG streams and
 the committed-work state.  Prints one JSON verdict; exit code 0 when every section agrees.
+
+Bit-exactness of the Draft state presupposes bit-identical features.  Synthetic and stored features are; the in-framework
+Target's features can differ in the last bit when rows are batched differently into one prefill (the reduction order of a
+GEMM depends on its row count), and a resumed run batches its first rows differently from the uninterrupted run.  Pass
+``inference.inference_batch_size=1 inference.inference_batch_tokens=0`` (one row per prefill) to check exact resume with
+the live Target.
 """
 import argparse
 import json
