@@ -221,4 +221,5 @@ class TrainingController:
             raise ValueError("checkpoint was written for a different dataset (fingerprint mismatch)")
         self.epoch = int(work_state.get("dataset_epoch", 0))
         self.committed_ids = set(work_state.get("committed_work_ids", []))
+        self.dropped_tail = int(work_state.get("dropped_tail_samples", 0))      # the count runs over the whole run
         self._start_epoch()
