@@ -95,6 +95,20 @@ def compile_multi_draft_plan(config: Config) -> MultiDraftPlan:
     return MultiDraftPlan(names, plans, union, offsets)
 
 
+def experiment_load_path(flat: Dict[str, Any], name: str) -> Optional[str]:
+    """Where one experiment resumes from.  ``training.load_path`` may name that experiment's own run directory or
+    checkpoint, or the root of an earlier shared-Target run (the directory that holds ``experiments/``), in which case
+    every experiment takes ``<root>/experiments/<its name>``.  ``{experiment}`` in the path stands for the name, which
+    lets one base setting point every experiment at an earlier checkpoint of its own
+    (``<root>/experiments/{experiment}/checkpoints/iter_0000100``)."""
+    path = flat.get("load_path")
+    if not path:
+        return None
+    path = str(path).replace("{experiment}", name)
+    nested = os.path.join(str(path), "experiments", name)
+    return nested if os.path.isdir(nested) else str(path)
+
+
 def _common_samples(controllers: Dict[str, Any], dataset: Optional[List[dict]]) -> List[dict]:
     """Admit a document only if every experiment admits it, so that all of them see the same stream."""
     admitted = None
@@ -200,6 +214,22 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
             if mapping is not None:
                 for fut in [t.call_async("set_vocab_mapping", *mapping) for t in groups[n]["trainers"]]:
                     fut.get(timeout=300)
+        # ---- resume: every experiment loads its own checkpoint; readers of one stream must stand at the same row ------
+        start_steps = {n: 0 for n in names}
+        for n in names:
+            g = groups[n]
+            load_path = experiment_load_path(g["flat"], n)
+            if not load_path:
+                continue
+            continual = bool(g["flat"].get("continual_training"))
+            infos = [f.get(timeout=1800) for f in [t.call_async("load_model", load_path, continual) for t in g["trainers"]]]
+            if not continual or g["flat"].get("continue_source_cursor"):
+                controllers[n].restore(infos[0]["work_state"])
+            start_steps[n] = int(infos[0]["next_step"])
+        cursors = {n: (start_steps[n], len(controllers[n].committed_ids)) for n in names}
+        if len(set(cursors.values())) > 1:
+            raise ValueError("experiments of a shared-Target run must resume from the same update and the same committed rows: "
+                             + ", ".join(f"{n}: update {s}, {c} rows" for n, (s, c) in cursors.items()))
         manager = InferenceManager(engines, all_rings, on_result=lambda o, r: None,
                                    batch_size=int(base.get("inference_batch_size", 1)),
                                    acquire_timeout=float(base.get("transport_acquire_timeout_seconds", 120.0)))
@@ -215,7 +245,8 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
             cp = g["cp"]
             try:
                 results[n] = training_loop(controller=c, manager=shared.proxy(n), trainers=g["trainers"], rings=g["rings"],
-                                           train_queues=g["queues"], args=g["args"], layer_ids=g["layer_ids"], num_steps=steps,
+                                           train_queues=g["queues"], args=g["args"], layer_ids=g["layer_ids"],
+                                           num_steps=steps - start_steps[n], start_step=start_steps[n],
                                            log=lambda m, n=n: log({"experiment": n, **m}),
                                            consumer_of_rank=lambda r: list(range(r * cp, (r + 1) * cp)))
             except BaseException as exc:                       # noqa: BLE001 - one experiment must not stop the others

@@ -188,3 +188,39 @@ def test_a_reader_of_a_shared_stream_trains_like_the_same_draft_alone(tmp_path):
     assert len(shared) == len(alone) == 3
     for (a, b), (c, d) in zip(shared, alone):
         assert a == pytest.approx(c, rel=1e-6) and b == pytest.approx(d, rel=1e-6)
+
+
+@pytest.mark.timeout(900)
+def test_a_shared_target_run_resumes_every_experiment_from_its_own_checkpoint(tmp_path):
+    """Four updates in one go against the last two of them again from every experiment's own checkpoint of update two:
+    both experiments end with the same weights either way."""
+    from aspec_b200.training.checkpoint_audit import checkpoint_hashes, compare
+
+    def run(out, steps, extra=""):
+        recipe = tmp_path / f"{os.path.basename(str(out))}.yaml"
+        text = open(_recipe_text(tmp_path)).read().replace("num_train_steps: 3", f"num_train_steps: {steps}") \
+            .replace("save_interval: 0", "save_interval: 2\n  deterministic_anchor_sampling: true" + extra)
+        text = text[: text.index("output_dir:")] + f"output_dir: {out}\n"
+        recipe.write_text(text)
+        plan = compile_multi_draft_plan(load_config(str(recipe)))
+        for p in plan.plans.values():
+            p.runtime_args.update(synthetic_vocab_size=500, force_cpu=True)
+        return run_multi_draft(plan, log=lambda m: None)
+
+    whole = run(tmp_path / "whole", 4)
+    middle = tmp_path / "whole" / "experiments" / "{experiment}" / "checkpoints" / "iter_0000002"
+    second = run(tmp_path / "second", 4, f"\n  load_path: {middle}")
+    assert whole["spark"]["completed_steps"] == 4
+    assert second["spark"]["completed_steps"] == 2 and second["flash"]["completed_steps"] == 2
+    # the root of an earlier run names every experiment's latest checkpoint: nothing is left to train
+    done = run(tmp_path / "done", 4, f"\n  load_path: {tmp_path / 'whole'}")
+    assert done["spark"]["completed_steps"] == 0
+    for name in ("spark", "flash"):
+        a = checkpoint_hashes(str(tmp_path / "whole" / "experiments" / name / "checkpoints" / "iter_0000004"))
+        b = checkpoint_hashes(str(tmp_path / "second" / "experiments" / name / "checkpoints" / "iter_0000004"))
+        assert not compare(a, b), (name, sorted(compare(a, b)))
+
+
+def _recipe_text(tmp_path):
+    _plan(tmp_path)
+    return str(tmp_path / "recipe.yaml")
