@@ -8,6 +8,7 @@ trainers work on step ``s`` (dispatch-ahead, bounded by the ring slots).
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import Callable, Dict, List, Optional
 
@@ -96,6 +97,10 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
     # how many updates beyond the one in training have their rows at the producers: 1 keeps the Targets one update
     # ahead; a long-context run with one row per update needs as many as there are Target GPUs to keep them all busy
     ahead = max(int(args.get("dispatch_ahead_updates", 1) or 1), 1)
+    # train-with-decode: every ``decode_weight_sync_interval`` updates the decoding Target engines reload the live Draft
+    sync_every = (int(args.get("decode_weight_sync_interval", 500)) if args.get("train_with_decode")
+                  and args.get("decode_weight_sync_enabled") and output_dir and hasattr(manager, "engines") else 0)
+    synced = 0
     completed = 0
     step = start_step
     have_next = submit(step)
@@ -155,11 +160,14 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
         # be the ones planned under its number (the ledger commits what was really consumed)
         submitted_plans.pop(step, None)
         tokens = 0
+        decode_stats: Dict[str, int] = {}
         for row_id, consumers in trained_rows.items():
             res, req = results_by_row.pop(row_id)
             for consumer in consumers:                         # every reader of the row releases its own lease
                 controller.release_result(res, participant=f"trainer{consumer}")
-            tokens += sum(req.document_lengths)
+            tokens += sum(res.document_lengths)              # of the row as produced (a decoding Target lengthens it)
+            for k, v in (res.stats or {}).items():
+                decode_stats[k] = decode_stats.get(k, 0) + v
         controller.commit_optimizer_step(step, committed)
         completed += 1
         window.add(completed, tokens)
@@ -167,6 +175,11 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
         metrics["perf/step_wall_time"] = time.perf_counter() - t_step
         metrics["perf/input_tokens"] = tokens
         metrics["train/step"] = step
+        if decode_stats:
+            metrics["decode/generated_tokens"] = decode_stats["generated_tokens"]
+            metrics["decode/tokens_per_target_pass"] = decode_stats["generated_tokens"] / max(decode_stats["target_passes"], 1)
+            if decode_stats.get("verify_rounds"):
+                metrics["decode/accepted_draft_tokens_per_round"] = decode_stats["accepted_draft_tokens"] / decode_stats["verify_rounds"]
         history.append(metrics)
         log(metrics)
         if timeline:
@@ -176,6 +189,9 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
                            or (args.get("save_per_epoch") and next_step_id in epoch_boundaries)):
             save_checkpoint(trainers, controller, output_dir, next_step_id, args)
             last_saved = next_step_id
+        if sync_every and next_step_id % sync_every == 0:
+            sync_draft_weights(trainers, manager.engines, os.path.join(output_dir, "decode_draft"), args)
+            synced += 1
         if on_step is not None:
             on_step(next_step_id, metrics)          # held-out evaluation, trackers
         step += 1
@@ -184,6 +200,8 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
     summary = {"completed_steps": completed, "last_step": step - 1, "window": window.summary(),
                "ledger": controller.ledger.status(), "dropped_tail_samples": controller.dropped_tail,
                "history": history}
+    if sync_every:
+        summary["decode_weight_syncs"] = synced
     return summary
 
 
@@ -192,6 +210,17 @@ def _owner(results_by_row, consumer, slot, gen) -> str:
         if (consumer, slot, gen) in [tuple(l) for l in req.leases]:
             return f"row:{row_id}"
     return "row:unknown"
+
+
+def sync_draft_weights(trainers, engines, asset_dir: str, args: Dict) -> None:
+    """The trainers write the live Draft as a native asset (rank 0 writes, all ranks join a sharded gather) and every
+    Target engine loads it between two of its calls; rows already being decoded finish with the older weights, which
+    changes their speed, never their text."""
+    timeout = float(args.get("checkpoint_timeout_seconds", 1800.0))
+    for fut in [t.call_async("export_draft_asset", asset_dir) for t in trainers]:
+        fut.get(timeout=timeout)
+    for fut in [e.call_async("load_draft", asset_dir) for e in engines]:
+        fut.get(timeout=timeout)
 
 
 def save_checkpoint(trainers, controller, output_dir: str, step_id: int, args: Dict) -> str:

@@ -17,6 +17,7 @@ by its trainers and committed with the optimizer step.
 from __future__ import annotations
 
 import random
+import zlib
 from typing import Any, Dict, List, Optional, Sequence
 
 import torch
@@ -39,6 +40,21 @@ def draft_vocabulary_from_samples(samples, draft_config: dict, args: dict):
         return None
     from aspec_b200.data.preprocessing import generate_vocab_mapping
     return generate_vocab_mapping(samples, vocab, small)
+
+
+def prompt_of(sample: dict) -> torch.Tensor:
+    """The tokens before the LAST supervised span of a document: earlier turns stay as context, the final response is
+    what a decoding Target writes anew (reference: the dataset is rendered with a generation prompt when training with
+    decode, aspec/data/dataset.py:285-360)."""
+    ids = sample["input_ids"].reshape(-1)
+    runs = [int(v) for v in str(sample["packed_loss_mask"]).split(",") if v != ""]
+    # runs alternate unsupervised, supervised, ...; find where the last non-empty supervised run starts
+    start, last = 0, None
+    for i, n in enumerate(runs):
+        if i % 2 == 1 and n > 0:
+            last = start
+        start += n
+    return ids[: last if last is not None else ids.numel()].clone()
 
 
 class TrainingController:
@@ -79,8 +95,24 @@ class TrainingController:
         self.samples = []
         rejected = {"longer_than_max_seq_length": 0, "no_supervised_position": 0, "fewer_loss_tokens_than_min_loss_tokens": 0}
         source_rows = 0
+        decode = bool(a.get("train_with_decode"))
+        if decode:
+            rejected.update(no_prompt=0, no_room_for_a_response=0)
         for s in samples:
             source_rows += 1
+            if decode:
+                # the document gives the prompt only (everything before its last supervised span); the Target engine
+                # writes the response, for which the row keeps room up to ``decode_max_new_tokens``
+                prompt = prompt_of(s)
+                room = min(int(a.get("decode_max_new_tokens", 512)), max_len - int(prompt.numel()))
+                if prompt.numel() < 1:
+                    rejected["no_prompt"] += 1
+                elif room < max(int(a.get("decode_min_new_tokens", 2)), self.block_size, 1):
+                    rejected["no_room_for_a_response"] += 1
+                else:
+                    self.samples.append({**s, "input_ids": prompt, "packed_loss_mask": str(int(prompt.numel())),
+                                         "length": int(prompt.numel()) + room, "useful": room, "max_new_tokens": room})
+                continue
             n = int(s["input_ids"].shape[-1])
             if n > max_len:
                 rejected["longer_than_max_seq_length"] += 1
@@ -184,11 +216,21 @@ class TrainingController:
     def row_request(self, sample_indices: Sequence[int], layer_ids) -> RowRequest:
         docs = [self.samples[i] for i in sample_indices]
         self.rows_planned += 1
+        decode = None
+        if self.args.get("train_with_decode"):
+            a = self.args
+            seed = int(a.get("seed", 0))
+            decode = {"max_new_tokens": [int(d["max_new_tokens"]) for d in docs],
+                      # a document's noise depends on the document, the epoch and the run's seed - not on its row or engine
+                      "seeds": [zlib.crc32(f"{d['data_id']}|{self.epoch}".encode()) ^ seed for d in docs],
+                      "min_new_tokens": int(a.get("decode_min_new_tokens", 2)), "stop_token_ids": list(a.get("decode_stop_token_ids") or ()),
+                      "temperature": float(a.get("decode_temperature", 1.0)), "top_k": int(a.get("decode_top_k", -1)),
+                      "top_p": float(a.get("decode_top_p", 1.0))}
         return RowRequest(row_id=f"row-{self.epoch}-{self.rows_planned}", data_ids=[d["data_id"] for d in docs],
                           input_ids=torch.cat([d["input_ids"].reshape(-1) for d in docs]),
-                          document_lengths=tuple(d["length"] for d in docs),
+                          document_lengths=tuple(int(d["input_ids"].numel()) for d in docs),
                           packed_loss_masks=[d["packed_loss_mask"] for d in docs],
-                          metadata=[self._identity(d) for d in docs], layer_ids=tuple(layer_ids))
+                          metadata=[self._identity(d) for d in docs], layer_ids=tuple(layer_ids), decode=decode)
 
     # -- ledger ------------------------------------------------------------------------------------
     def register_result(self, out: InferenceOutput) -> None:

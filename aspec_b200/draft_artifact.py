@@ -55,6 +55,46 @@ def load_native_draft(asset_dir, *, device="cpu", dtype: Optional[torch.dtype] =
     return model.to(device).eval(), manifest
 
 
+def write_live_asset(draft_model, output_dir, *, block_size: Optional[int] = None, source: str = "live weights") -> dict:
+    """Write the weights a Draft holds RIGHT NOW as a native asset (same files and manifest fields as an export of a
+    checkpoint), first under a temporary name and then renamed, so that a reader never sees half of it.  This is what a
+    training run hands its decoding Target engines when it syncs weights
+    (reference: weight sync to the serving engine, aspec/inference/engine/sgl_engine_decode.py:39-424)."""
+    import os
+    import shutil
+    from safetensors.torch import save_file
+    from aspec_b200 import __version__
+    from aspec_b200.commands.convert_to_hf import draft_structure_manifest
+    output_dir = Path(output_dir)
+    staging = output_dir.with_name(output_dir.name + ".staging")
+    if staging.exists():
+        shutil.rmtree(staging)
+    staging.mkdir(parents=True)
+    raw = draft_model.config.to_dict()
+    algorithm = resolve_draft_algorithm(raw)
+    tensors = {k: v.detach().cpu().contiguous().clone() for k, v in draft_model.state_dict().items()}
+    save_file(tensors, str(staging / "model.safetensors"), metadata={"format": "pt", "aspec_version": __version__})
+    floats = [v.dtype for v in tensors.values() if v.is_floating_point()]
+    dtype = max(set(floats), key=floats.count) if floats else torch.float32
+    export_config = json.loads(json.dumps(raw))
+    export_config.update(draft_vocab_size=int(raw.get("draft_vocab_size") or raw["vocab_size"]), _aspec_version=__version__,
+                         torch_dtype=str(dtype).removeprefix("torch."))
+    contract = {"algorithm": algorithm}
+    if block_size:
+        contract["block_size"] = export_config["block_size"] = int(block_size)
+    (staging / "config.json").write_text(json.dumps(export_config, indent=2, sort_keys=True) + "\n")
+    manifest = {"schema_version": SCHEMA, "storage_format": "aspec_native", "source_checkpoint": source,
+                "model_sha256": sha256_file(staging / "model.safetensors"), "config_sha256": sha256_file(staging / "config.json"),
+                "tensor_count": len(tensors), "dtype": str(dtype), "algorithm": algorithm, "training_contract": contract,
+                "architecture": export_config.get("architectures"), "model_type": export_config.get("model_type"),
+                "draft_structure": draft_structure_manifest(raw)}
+    (staging / "export_manifest.json").write_text(json.dumps(manifest, indent=2, sort_keys=True) + "\n")
+    if output_dir.exists():
+        shutil.rmtree(output_dir)
+    os.replace(staging, output_dir)
+    return manifest
+
+
 class BlockDraftConsumer:
     def __init__(self, draft_model, *, block_size: int):
         from aspec_b200.models.dflash import DFlashModel

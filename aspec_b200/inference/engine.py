@@ -132,10 +132,83 @@ class NativeTargetEngine(InferenceEngine):
         from aspec_b200.transport.feature_ring import export_tensor
         return [export_tensor(self.model.embed_tokens.weight.detach()) for _ in range(copies)]
 
+    # -- train-with-decode: the engine continues the prompts itself -----------------------------------------------------
+    def load_draft(self, asset_dir: str) -> dict:
+        """Load (first call) or hot-reload (later calls) the Draft that proposes blocks while this engine decodes.  The
+        text does not depend on it - every kept token is the Target's own draw - only the tokens per Target pass do
+        (reference: speculative decode with weight sync, aspec/inference/engine/sgl_engine_decode.py:39-424)."""
+        from aspec_b200.draft_artifact import BlockDraftConsumer, load_native_draft
+        if getattr(self, "draft", None) is None:
+            model, manifest = load_native_draft(asset_dir, device=self.device, dtype=self.model.lm_head.dtype)
+            block = int(manifest.get("training_contract", {}).get("block_size") or getattr(model.config, "block_size", 0) or 0)
+            self.draft = BlockDraftConsumer(model, block_size=block)
+            self.draft_layers = tuple(int(l) for l in model.config.target_layer_ids)
+        else:
+            manifest = self.draft.update_weights_from_disk(asset_dir)
+        self.draft_loads = getattr(self, "draft_loads", 0) + 1
+        return {"algorithm": manifest["algorithm"], "loads": self.draft_loads}
+
+    @torch.no_grad()
+    def _decode(self, requests: Sequence[RowRequest]) -> List[RowRequest]:
+        """Continue every document of every request; returns requests over prompt + response with the response as the
+        supervised span.  A response never outgrows what the planner reserved for its document."""
+        import dataclasses
+        from aspec_b200.data.utils import pack_loss_mask
+        from aspec_b200.inference.speculative_decode import batched_generate
+        prompts, budgets, seeds = [], [], []
+        for req in requests:
+            off = 0
+            for j, n in enumerate(req.document_lengths):
+                prompts.append(req.input_ids[off:off + n])
+                budgets.append(int(req.decode["max_new_tokens"][j]))
+                seeds.append(int(req.decode["seeds"][j]))
+                off += n
+        d = requests[0].decode
+        consumer = getattr(self, "draft", None)
+        res = batched_generate(self.model, prompts, max_new_tokens=budgets, min_new_tokens=int(d.get("min_new_tokens", 0)),
+                               stop_token_ids=d.get("stop_token_ids") or (), temperature=float(d.get("temperature", 1.0)),
+                               top_k=int(d.get("top_k", -1)), top_p=float(d.get("top_p", 1.0)), seeds=seeds, consumer=consumer,
+                               layer_ids=getattr(self, "draft_layers", ()))
+        out, i = [], 0
+        for req in requests:
+            ids, lengths, masks = [], [], []
+            stats = {"generated_tokens": 0, "target_passes": 0, "accepted_draft_tokens": 0, "verify_rounds": 0}
+            off = 0
+            for n in req.document_lengths:
+                new = res[i]["tokens"]
+                ids += [req.input_ids[off:off + n].reshape(-1), torch.tensor(new, dtype=torch.long)]
+                lengths.append(n + len(new))
+                masks.append(pack_loss_mask([0] * n + [1] * len(new)))
+                stats["generated_tokens"] += len(new)
+                stats["target_passes"] += res[i]["target_passes"]
+                stats["accepted_draft_tokens"] += sum(res[i]["accepted_per_round"])
+                stats["verify_rounds"] += len(res[i]["accepted_per_round"])
+                off += n
+                i += 1
+            done = dataclasses.replace(req, input_ids=torch.cat(ids), document_lengths=tuple(lengths), packed_loss_masks=masks,
+                                       decode=None)
+            done.decode_stats = stats
+            out.append(done)
+        for k in ("generated_tokens", "target_passes", "accepted_draft_tokens", "verify_rounds"):
+            setattr(self, "decode_" + k, getattr(self, "decode_" + k, 0) + sum(r.decode_stats[k] for r in out))
+        return out
+
+    def get_status(self) -> dict:
+        st = super().get_status()
+        if getattr(self, "decode_generated_tokens", 0):
+            st["decode"] = {k: getattr(self, "decode_" + k, 0) for k in
+                            ("generated_tokens", "target_passes", "accepted_draft_tokens", "verify_rounds")}
+            st["decode"]["draft_loads"] = getattr(self, "draft_loads", 0)
+        return st
+
     @torch.no_grad()
     def generate(self, requests: Sequence[RowRequest]) -> List[InferenceOutput]:
         t0 = time.perf_counter()
         outs = []
+        if any(req.decode for req in requests):
+            if not all(req.decode for req in requests):
+                raise ValueError("one call holds either prompts to continue or rows to prefill, not both")
+            requests = self._decode(requests)
         if self.fail_after is not None and getattr(self, "rows_done", 0) + len(requests) > self.fail_after:
             raise RuntimeError(f"{self.name}: injected producer failure")
         if self.delay_s:
@@ -154,6 +227,7 @@ class NativeTargetEngine(InferenceEngine):
         self.model.prefill(ids, lengths, self.layer_ids, sink=segments if len(requests) > 1 else segments[0][2])
         for req, views in zip(requests, all_views):
             outs.append(self._finish(req, views, self.layer_ids, self.device_flags))
+            outs[-1].stats = dict(getattr(req, "decode_stats", {}))
         if self.device.type == "cuda" and not self.device_flags:
             torch.cuda.current_stream(self.device).synchronize()     # host-ordered readiness
         self.busy_seconds += time.perf_counter() - t0

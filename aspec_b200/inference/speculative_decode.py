@@ -73,3 +73,134 @@ def speculative_generate(target, consumer, prompt_ids: torch.Tensor, layer_ids: 
     return {"tokens": tokens, "accepted_per_round": per_round, "target_passes": passes,
             "tau": (len(tokens) - 1) / max(len(per_round), 1) if per_round else 1.0,
             "mean_accepted_draft_tokens": sum(per_round) / max(len(per_round), 1)}
+
+
+# -- generation with cached keys / values, several sequences per pass ----------------------------------------------------
+def filter_logits(logits: torch.Tensor, temperature: float, top_k: int, top_p: float) -> torch.Tensor:
+    """Log-weights of the sampling distribution: temperature, then top-k, then nucleus (top-p) filtering; removed entries
+    are ``-inf``.  ``temperature <= 0`` means greedy and returns the logits untouched."""
+    x = logits.float()
+    if temperature <= 0:
+        return x
+    x = x / float(temperature)
+    if top_k and 0 < top_k < x.shape[-1]:
+        kth = x.topk(int(top_k), -1).values[..., -1:]
+        x = x.masked_fill(x < kth, float("-inf"))
+    if 0.0 < top_p < 1.0:
+        sorted_x, order = x.sort(-1, descending=True)
+        probs = torch.softmax(sorted_x, -1)
+        before = probs.cumsum(-1) - probs                      # mass of the strictly more likely tokens
+        drop = before >= top_p                                 # the most likely token always stays
+        x = x.masked_fill(torch.zeros_like(drop).scatter(-1, order, drop), float("-inf"))
+    return x
+
+
+def sample_tokens(logits: torch.Tensor, temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0,
+                  generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """One token per row of ``logits [m, V]``.  Sampling is Gumbel-max on the filtered log-weights with noise from
+    ``generator``: the m draws of a call are independent, and a sequence that owns its generator samples the same text
+    whichever other sequences share its passes."""
+    x = filter_logits(logits, temperature, top_k, top_p)
+    if temperature <= 0:
+        return x.argmax(-1)
+    u = torch.rand(x.shape, generator=generator, device=x.device, dtype=torch.float32).clamp_(1e-20, 1.0)
+    return (x - torch.log(-torch.log(u))).argmax(-1)
+
+
+@torch.no_grad()
+def batched_generate(target, prompts: Sequence[torch.Tensor], *, max_new_tokens: Sequence[int], min_new_tokens: int = 0,
+                     stop_token_ids: Sequence[int] = (), temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0,
+                     seeds: Optional[Sequence[int]] = None, consumer=None, layer_ids: Sequence[int] = ()) -> List[dict]:
+    """Continue every prompt with the Target's own tokens; all sequences share each Target pass and keep their keys and
+    values in one cache (``DenseTarget.extend``), so a pass costs the new tokens only.
+
+    With ``consumer`` (a ``draft_artifact.BlockDraftConsumer``) a pass verifies a Draft block per sequence: the Target's
+    token is drawn at every proposed position, the proposal is accepted as long as it equals those draws, and the first
+    draw that differs is kept - every kept token is a draw from the Target's distribution given its prefix, so the text
+    is distributed exactly as without a Draft (and is identical for greedy decoding); the Draft only changes how many
+    tokens a pass yields.  Stop tokens are masked out until ``min_new_tokens`` tokens exist.  ``seeds[r]`` seeds sequence
+    ``r``'s own noise generator.
+
+    Returns per sequence ``{"tokens", "target_passes", "accepted_per_round", "stopped"}``."""
+    dev = target.lm_head.device
+    R = len(prompts)
+    if R == 0:
+        return []
+    block = int(consumer.block_size) if consumer is not None else 1
+    budget = [int(m) for m in max_new_tokens]
+    capacity = max(int(p.numel()) + b for p, b in zip(prompts, budget)) + block
+    cache = target.new_decode_cache(R, capacity)
+    gens = []
+    for r in range(R):
+        g = torch.Generator(device=dev)
+        g.manual_seed(int(seeds[r]) if seeds is not None else r)
+        gens.append(g)
+    stops = [int(t) for t in (stop_token_ids or ())]
+    lm_head = target.lm_head.detach()
+    capture = list(layer_ids) if consumer is not None else []
+    seqs = [[int(t) for t in p.reshape(-1)] for p in prompts]
+    n0 = [len(s) for s in seqs]
+    feats: List[Optional[torch.Tensor]] = [None] * R
+    out = [{"tokens": [], "target_passes": 0, "accepted_per_round": [], "stopped": "length"} for _ in range(R)]
+    active = [r for r in range(R) if budget[r] > 0]
+
+    def draw(r: int, logits: torch.Tensor, already: int) -> List[int]:
+        """Target tokens at consecutive positions of sequence ``r``; position ``i`` has ``already + i`` new tokens before it."""
+        if stops and min_new_tokens > 0:
+            logits = logits.clone()
+            for i in range(logits.shape[0]):
+                if already + i < min_new_tokens:
+                    logits[i, stops] = float("-inf")
+        return sample_tokens(logits, temperature, top_k, top_p, gens[r]).tolist()
+
+    def keep(r: int, new: List[int]) -> None:
+        room = budget[r] - (len(seqs[r]) - n0[r])
+        new = new[:room]
+        for i, t in enumerate(new):
+            if t in stops:
+                new = new[: i + 1]
+                out[r]["stopped"] = "stop_token"
+                break
+        seqs[r] += new
+        if out[r]["stopped"] == "stop_token" or len(seqs[r]) - n0[r] >= budget[r]:
+            active.remove(r)
+
+    # the prompts: one pass, the first new token of every sequence
+    first = target.extend(cache, [torch.tensor(seqs[r]) if r in active else torch.empty(0, dtype=torch.long) for r in range(R)], capture)
+    for r in list(active):
+        lo, hi = first["offsets"][r], first["offsets"][r + 1]
+        cache.accept(r, hi - lo)
+        if consumer is not None:
+            feats[r] = first["hidden_states"][lo:hi]
+        out[r]["target_passes"] += 1
+        keep(r, draw(r, first["logits"][hi - 1:hi], 0))
+    while active:
+        trial = {}
+        for r in active:
+            proposal: List[int] = []
+            if consumer is not None:
+                known = len(seqs[r]) - 1                      # every token but the newest has features
+                padded = torch.cat([feats[r][:known], feats[r].new_zeros(1, feats[r].shape[-1])])[None]
+                ids = torch.tensor(seqs[r], device=dev)[None]
+                proposal = [int(t) for t in consumer.propose(ids, padded, lm_head_weight=lm_head)["token_ids"].reshape(-1)[: block - 1]]
+                proposal = proposal[: max(budget[r] - (len(seqs[r]) - n0[r]) - 1, 0)]
+            trial[r] = proposal
+        step = target.extend(cache, [torch.tensor([seqs[r][-1]] + trial[r]) if r in trial else torch.empty(0, dtype=torch.long)
+                                     for r in range(R)], capture)
+        for r in list(active):
+            lo, hi = step["offsets"][r], step["offsets"][r + 1]
+            proposal = trial[r]
+            drawn = draw(r, step["logits"][lo:hi], len(seqs[r]) - n0[r])
+            n = 0
+            while n < len(proposal) and proposal[n] == drawn[n]:
+                n += 1
+            cache.accept(r, 1 + n)                            # the newest token and the accepted proposals are cached now
+            if consumer is not None:
+                feats[r] = torch.cat([feats[r][: len(seqs[r]) - 1], step["hidden_states"][lo:lo + 1 + n]])
+            out[r]["target_passes"] += 1
+            if consumer is not None:
+                out[r]["accepted_per_round"].append(n)
+            keep(r, proposal[:n] + [drawn[n]])
+    for r in range(R):
+        out[r]["tokens"] = seqs[r][n0[r]:]
+    return out

@@ -113,6 +113,32 @@ class _Layer(nn.Module):
         self._gate_up_tiled = None
 
 
+class DecodeCache:
+    """Keys and values of ``sequences`` independent token sequences, ``capacity`` rows each, for every layer.
+
+    One buffer per layer holds all sequences back to back (sequence ``r`` owns rows ``[r * capacity, (r + 1) *
+    capacity)``), so that one attention launch serves all of them: a query names its own sequence's rows through its
+    key interval, exactly as packed documents do in prefill."""
+
+    def __init__(self, model: "DenseTarget", sequences: int, capacity: int):
+        cfg = model.config
+        dev, dtype = model.lm_head.device, model.lm_head.dtype
+        self.sequences, self.capacity = int(sequences), int(capacity)
+        shape = (self.sequences * self.capacity, cfg.num_key_value_heads, cfg.head_dim)
+        self.k = [torch.zeros(shape, device=dev, dtype=dtype) for _ in range(cfg.num_hidden_layers)]
+        self.v = [torch.zeros(shape, device=dev, dtype=dtype) for _ in range(cfg.num_hidden_layers)]
+        self.lengths = [0] * self.sequences
+
+    def accept(self, sequence: int, tokens: int) -> None:
+        """Keep the first ``tokens`` rows that the last ``extend`` wrote for ``sequence``."""
+        if tokens < 0 or self.lengths[sequence] + tokens > self.capacity:
+            raise ValueError("accepted rows outside the cache")
+        self.lengths[sequence] += int(tokens)
+
+    def bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.k + self.v)
+
+
 class DenseTarget(nn.Module):
     """Qwen3 / Llama-shaped (optionally MoE) Target for prefill-only feature generation."""
 
@@ -157,7 +183,7 @@ class DenseTarget(nn.Module):
                 .reshape(2 * I, -1).contiguous()
         return layer._gate_up_tiled
 
-    def _attention(self, layer: _Layer, x, positions, intervals):
+    def _attention(self, layer: _Layer, x, positions, intervals, kv=None):
         cfg = self.config
         hq, hk, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         T = x.shape[0]
@@ -174,6 +200,8 @@ class DenseTarget(nn.Module):
             kn = layer.k_norm if cfg.qk_norm else None
             q, _ = E.qk_norm_rope_fwd(q.contiguous(), qn, positions, inv_freq, cfg.rms_norm_eps, 1.0)
             k, _ = E.qk_norm_rope_fwd(k.contiguous(), kn, positions, inv_freq, cfg.rms_norm_eps, 1.0)
+            if kv is not None:          # decode: the new rows join the cached keys / values and attend all of them
+                k, v = kv[0].index_copy_(0, kv[2], k), kv[1].index_copy_(0, kv[2], v)
             o, _ = A.forward(q, k, v, intervals, d ** -0.5)
             return o.view(T, hq * d)
         qkv = F.linear(x, layer.qkv_proj)
@@ -182,6 +210,8 @@ class DenseTarget(nn.Module):
         v = qkv[:, (hq + hk) * d:].reshape(T, hk, d)
         q = qk_norm_rope_reference(q, layer.q_norm if cfg.qk_norm else None, positions, inv_freq, cfg.rms_norm_eps)
         k = qk_norm_rope_reference(k, layer.k_norm if cfg.qk_norm else None, positions, inv_freq, cfg.rms_norm_eps)
+        if kv is not None:
+            k, v = kv[0].index_copy_(0, kv[2], k.to(kv[0].dtype)), kv[1].index_copy_(0, kv[2], v.to(kv[1].dtype))
         o, _ = interval_attention_reference(q, k, v, intervals, d ** -0.5)
         return o.reshape(T, hq * d)
 
@@ -292,6 +322,56 @@ class DenseTarget(nn.Module):
         if want_logits:
             out["logits"] = F.linear(final, self.lm_head)
         return out
+
+    # -- decode with cached keys / values ------------------------------------------------------------
+    def new_decode_cache(self, sequences: int, capacity: int) -> "DecodeCache":
+        return DecodeCache(self, sequences, capacity)
+
+    @torch.no_grad()
+    def extend(self, cache: "DecodeCache", new_ids: Sequence[torch.Tensor], capture_layers: Sequence[int] = ()) -> Dict[str, torch.Tensor]:
+        """One pass over the NEW tokens of several sequences at once (``new_ids[r]``: the tokens of sequence ``r`` that
+        the cache does not hold yet; empty for a sequence that sits this pass out).  Token ``j`` of sequence ``r`` takes
+        position ``cache.lengths[r] + j`` and attends the cached rows of its own sequence plus the new tokens up to
+        itself.  The new keys / values are written behind each sequence's cached rows but the lengths do not move: the
+        caller keeps what it accepts with ``cache.accept(r, n)`` and the rest is overwritten by the next pass - which is
+        what speculative verification needs (reference: the serving engine's decode and verify passes,
+        aspec/inference/engine/sgl_engine_decode.py:39-424).
+
+        Returns ``logits [M, V]``, ``hidden_states [M, K * D]`` of the captured layers and ``offsets`` (where each
+        sequence's rows start in those), ``M`` = all new tokens."""
+        cfg = self.config
+        dev = self.lm_head.device
+        counts = [int(t.numel()) for t in new_ids]
+        if len(counts) != cache.sequences:
+            raise ValueError("one (possibly empty) tensor of new tokens per cached sequence")
+        for r, m in enumerate(counts):
+            if cache.lengths[r] + m > cache.capacity:
+                raise ValueError(f"sequence {r}: {cache.lengths[r]} cached + {m} new tokens exceed the cache's {cache.capacity}")
+        M = sum(counts)
+        if M == 0:
+            raise ValueError("no new tokens")
+        pos = torch.cat([torch.arange(cache.lengths[r], cache.lengths[r] + m) for r, m in enumerate(counts)])
+        base = torch.cat([torch.full((m,), r * cache.capacity) for r, m in enumerate(counts)])
+        iv = torch.zeros(M, 4, dtype=torch.int32)
+        iv[:, 0] = base.to(torch.int32)
+        iv[:, 1] = (base + pos + 1).to(torch.int32)
+        rows = (base + pos).to(dev, non_blocking=True)
+        positions = pos.to(torch.int32).to(dev, non_blocking=True)
+        intervals = iv.to(dev, non_blocking=True)
+        x = self.embed_tokens(torch.cat([t.reshape(-1) for t in new_ids]).to(dev))
+        sink = FeatureSink(M, capture_layers, cfg.hidden_size, dev, x.dtype)
+        capture = set(capture_layers)
+        for i, layer in enumerate(self.layers):
+            h = self._norm(x, layer.input_layernorm)
+            a = self._attention(layer, h, positions, intervals, kv=(cache.k[i], cache.v[i], rows))
+            x = self._proj_residual(a, layer.o_proj, x)
+            h = self._norm(x, layer.post_attention_layernorm)
+            x = self._mlp(layer, h, x, sink.layer_views(i) if i in capture else None)
+        final = self._norm(x, self.norm)
+        offsets = [0]
+        for m in counts:
+            offsets.append(offsets[-1] + m)
+        return {"logits": F.linear(final, self.lm_head), "hidden_states": sink.hidden_states, "offsets": offsets}
 
     def memory_bytes(self) -> int:
         return sum(p.numel() * p.element_size() for p in self.parameters())

@@ -82,6 +82,10 @@ def compile_multi_draft_plan(config: Config) -> MultiDraftPlan:
         names.append(exp["name"])
         plans[exp["name"]] = compile_execution_plan(child_config(config, exp))
     first = plans[names[0]].runtime_args
+    for n in names:
+        if plans[n].runtime_args.get("train_with_decode"):
+            raise ValueError(f"experiment {n}: training.train_with_decode is a single-Draft mode; a shared-Target run prefills "
+                             "recorded responses")
     for n in names[1:]:
         for key in _SHARED_ROW_KEYS:
             if plans[n].runtime_args.get(key) != first.get(key):

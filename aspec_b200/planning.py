@@ -175,6 +175,26 @@ def validate_scope(flat: Dict[str, Any], draft: dict, algorithm: str, policy: di
     if max_pos and int(flat["max_seq_length"]) > int(max_pos) and not (draft.get("rope_scaling") or draft.get("rope_parameters")):
         notes.append(f"max_seq_length {flat['max_seq_length']} exceeds the Draft's max_position_embeddings {max_pos} "
                      "without a RoPE scaling rule")
+    # -- train with decode: the Target engines write the responses themselves ------------------------------------
+    if g("train_with_decode"):
+        if engine != "native":
+            raise ValueError("training.train_with_decode needs the in-framework Target (inference_engine_type=native): stored or "
+                             "synthetic features cannot be continued")
+        if int(g("decode_max_new_tokens", 512)) < max(int(g("decode_min_new_tokens", 2)), 1):
+            raise ValueError("decode.max_new_tokens must be at least decode.min_new_tokens and positive")
+        if float(g("decode_temperature", 1.0)) < 0 or not 0.0 < float(g("decode_top_p", 1.0)) <= 1.0:
+            raise ValueError("decode.temperature must not be negative and decode.top_p must lie in (0, 1]")
+        speculative = g("decode_weight_sync_enabled") or g("decode_speculative_draft_model_path")
+        if speculative and (algorithm not in ("dspark", "dflash") or draft.get("mtp_conditioning")):
+            raise ValueError("a decoding Target proposes with DSpark / DFlash block Drafts only (no MTP conditioning): "
+                             "turn decode.weight_sync_enabled and decode.speculative_draft_model_path off to decode with the "
+                             "Target alone")
+        if g("decode_weight_sync_enabled") and int(g("decode_weight_sync_interval", 500) or 0) < 1:
+            raise ValueError("decode.weight_sync_interval must be positive")
+        if g("experiments"):
+            raise ValueError("training.train_with_decode is a single-Draft mode: a shared-Target run prefills recorded responses")
+        notes.append("train_with_decode: documents give the prompt (everything before their last supervised span); responses "
+                     f"of up to {int(g('decode_max_new_tokens', 512))} tokens are drawn from the Target and supervised whole")
     # -- keys that would change what is trained and have no implementation (the reference refuses these too) -----
     if int(g("eagle3_num_anchors") or 0):
         raise ValueError("anchored EAGLE3 (training.eagle3_num_anchors) is not part of the training path: EAGLE3 / EAGLE4 "

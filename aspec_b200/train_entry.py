@@ -122,6 +122,10 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
         pick = lambda v, r: v[r] if isinstance(v, list) else v
         for fut in [t.call_async("set_head", pick(head, r), pick(embedding, r)) for r, t in enumerate(trainers)]:
             fut.get(timeout=600)
+        if flat.get("train_with_decode") and flat.get("decode_speculative_draft_model_path"):
+            # the decoding Targets start with this exported Draft; weight syncs replace it with the live one later
+            for fut in [e.call_async("load_draft", flat["decode_speculative_draft_model_path"]) for e in engines]:
+                fut.get(timeout=600)
         start_step = 0
         controller = TrainingController(args, dp_size=dp, consumers_per_row=cp, algorithm=algorithm)
         n = controller.load_dataset(dataset)
@@ -160,7 +164,8 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
         eval_history: list = []
         if flat.get("eval_data_path") and int(flat.get("eval_interval") or 0) > 0:
             from aspec_b200.controller.eval import EvalRunner
-            eval_args = dict(args, train_data_path=flat["eval_data_path"], shuffle_dataset=False,
+            # held-out rows are prefilled with their recorded responses even when training decodes its own
+            eval_args = dict(args, train_data_path=flat["eval_data_path"], shuffle_dataset=False, train_with_decode=False,
                              synthetic_num_documents=int(flat.get("eval_num_documents") or 32),
                              dataset_seed=int(flat.get("seed", 0)) + 1)
             eval_controller = TrainingController(eval_args, dp_size=dp, consumers_per_row=cp, algorithm=algorithm)

@@ -458,6 +458,16 @@ class TrainerActor:
                          optimizer=self.trainer.optimizer, draft_config=self.draft_config, topology=self.topology(),
                          global_step=self.trainer.global_step)
 
+    def export_draft_asset(self, output_dir: str) -> Optional[dict]:
+        """The live Draft weights as a native asset for the decoding Target engines.  Every rank joins (sharded
+        parameters are gathered); rank 0 writes."""
+        from aspec_b200.draft_artifact import write_live_asset
+        with ckpt.whole_parameters(self.trainer.optimizer):
+            if self.rank != 0:
+                return None
+            return write_live_asset(self.model.draft_model, output_dir, block_size=getattr(self.model, "block_size", None),
+                                    source=f"update {self.trainer.global_step}")
+
     def load_model(self, load_path: str, continual: bool = False) -> dict:
         info = ckpt.load(load_path=load_path, model=self.model.draft_model, optimizer=self.trainer.optimizer,
                          topology=self.topology(), continual_training=continual)

@@ -17,6 +17,9 @@ class RowRequest:
     metadata: List[Dict[str, Any]]          # work identity per document
     leases: List[Tuple[int, int, int]] = field(default_factory=list)   # (consumer, slot, generation)
     layer_ids: Tuple[int, ...] = ()
+    # train-with-decode: the documents are prompts and the engine writes the responses itself.  Keys: ``max_new_tokens``
+    # and ``seeds`` (one per document), ``min_new_tokens``, ``stop_token_ids``, ``temperature``, ``top_k``, ``top_p``
+    decode: Any = None
 
 
 @dataclass
@@ -30,6 +33,7 @@ class InferenceOutput:
     metadata: List[Dict[str, Any]]
     size_bytes: int
     engine: str = ""
+    stats: Dict[str, Any] = field(default_factory=dict)      # decode: generated tokens, Target passes, accepted Draft tokens
 
 
 @dataclass

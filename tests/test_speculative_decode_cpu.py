@@ -63,3 +63,59 @@ def test_a_draft_that_knows_the_answer_is_accepted_whole_and_eos_stops():
     stop = want[5]
     cut = speculative_generate(target, consumer, prompt, [0, 1, 3], max_new_tokens=13, eos_token_id=stop)
     assert cut["tokens"] == want[: want.index(stop) + 1]
+
+
+# -- cached passes and batched generation -------------------------------------------------------------------------------
+def test_cached_passes_equal_prefill_and_rejected_rows_are_overwritten():
+    target = _target()
+    ids = [torch.randint(0, 500, (n,), generator=torch.Generator().manual_seed(n)) for n in (9, 5)]
+    full = [target.prefill(t, [len(t)], [0, 2], want_logits=True) for t in ids]
+    cache = target.new_decode_cache(2, 16)
+    a = target.extend(cache, [ids[0][:6], ids[1][:2]], [0, 2])
+    cache.accept(0, 6)
+    cache.accept(1, 2)
+    target.extend(cache, [torch.tensor([7, 8, 9]), torch.empty(0, dtype=torch.long)])      # a rejected trial of sequence 0
+    b = target.extend(cache, [ids[0][6:], ids[1][2:]], [0, 2])
+    torch.testing.assert_close(torch.cat([a["logits"][:6], b["logits"][:3]]), full[0]["logits"], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(torch.cat([a["logits"][6:], b["logits"][3:]]), full[1]["logits"], rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(torch.cat([a["hidden_states"][:6], b["hidden_states"][:3]]), full[0]["hidden_states"], rtol=1e-4, atol=1e-5)
+    with pytest.raises(ValueError, match="exceed the cache"):
+        target.extend(cache, [torch.zeros(11, dtype=torch.long), torch.empty(0, dtype=torch.long)])
+
+
+@pytest.mark.parametrize("kind", [None, "dspark", "dflash"])
+def test_batched_generation_is_the_targets_text_with_or_without_a_draft(kind):
+    from aspec_b200.inference.speculative_decode import batched_generate
+    target = _target()
+    consumer = _consumer(kind) if kind else None
+    prompts = [torch.randint(0, 500, (n,), generator=torch.Generator().manual_seed(n)) for n in (11, 4, 7)]
+    budgets = [9, 12, 0]
+    got = batched_generate(target, prompts, max_new_tokens=budgets, temperature=0.0, consumer=consumer,
+                           layer_ids=LAYERS.get(kind, ()))
+    for p, g, n in zip(prompts, got, budgets):
+        assert g["tokens"] == (greedy_generate(target, p, n) if n else [])
+        if n and consumer is not None:
+            assert g["target_passes"] == len(g["accepted_per_round"]) + 1 <= n
+            assert 1 + sum(a + 1 for a in g["accepted_per_round"]) >= n
+    # sampled text belongs to the sequence and its seed, not to the batch it ran in
+    kw = dict(temperature=0.8, top_k=40, top_p=0.9, consumer=consumer, layer_ids=LAYERS.get(kind, ()))
+    both = batched_generate(target, prompts[:2], max_new_tokens=[8, 8], seeds=[21, 22], **kw)
+    alone = batched_generate(target, prompts[1:2], max_new_tokens=[8], seeds=[22], **kw)
+    assert both[1]["tokens"] == alone[0]["tokens"] and len(both[0]["tokens"]) == 8
+
+
+def test_stop_tokens_wait_for_the_minimum_length_and_filters_keep_the_head_of_the_distribution():
+    from aspec_b200.inference.speculative_decode import batched_generate, filter_logits
+    target = _target()
+    prompt = torch.randint(0, 500, (9,), generator=torch.Generator().manual_seed(4))
+    want = greedy_generate(target, prompt, 10)
+    stop = want[2]
+    cut = batched_generate(target, [prompt], max_new_tokens=[10], temperature=0.0, stop_token_ids=[stop])[0]
+    assert cut["tokens"] == want[:3] and cut["stopped"] == "stop_token"
+    held = batched_generate(target, [prompt], max_new_tokens=[10], temperature=0.0, stop_token_ids=[stop], min_new_tokens=5)[0]
+    assert len(held["tokens"]) >= 5 and stop not in held["tokens"][:5]
+    x = torch.tensor([[2.0, 1.0, 0.0, -1.0]])
+    assert filter_logits(x, 1.0, 2, 1.0).isinf().tolist() == [[False, False, True, True]]
+    assert filter_logits(x, 1.0, -1, 0.7).isinf().tolist() == [[False, False, True, True]]
+    assert filter_logits(x, 1.0, -1, 0.1).isinf().tolist() == [[False, True, True, True]]
+    torch.testing.assert_close(filter_logits(x, 0.5, -1, 1.0), x * 2)
