@@ -28,6 +28,11 @@ class InferenceEngine:
         raise NotImplementedError
 
     def attach_rings(self, handles: Dict[int, dict]) -> None:
+        if getattr(self, "tp_rank", 0) > 0:
+            return                      # only the first rank of a tensor-parallel engine stores features
+        self._attach(handles)
+
+    def _attach(self, handles: Dict[int, dict]) -> None:
         """``handles[c]`` maps consumer ``c``'s ring; an optional ``"layer_ids"`` entry names the subset of this
         engine's captured layers that the consumer wants (several Drafts sharing one Target)."""
         self.rings = {int(c): RemoteRing(h) for c, h in handles.items()}
@@ -94,8 +99,17 @@ class InferenceEngine:
 class NativeTargetEngine(InferenceEngine):
     def __init__(self, target_config: dict, layer_ids: Sequence[int], device: str = "cuda:0", dtype: str = "bfloat16",
                  seed: int = 0, name: str = "target0", device_flags: bool = False, weights_path: Optional[str] = None,
-                 fail_after: Optional[int] = None, delay_s: float = 0.0):
+                 fail_after: Optional[int] = None, delay_s: float = 0.0, tp_rank: int = 0, tp_size: int = 1,
+                 tp_address: Optional[str] = None):
+        """``tp_size > 1``: this process is rank ``tp_rank`` of a tensor-parallel engine whose ranks meet at ``tp_address``
+        (``tcp://host:port``).  All ranks run every call; rank 0 owns the rings and the answers."""
         from aspec_b200.models.target.dense import DenseTarget, TargetConfig
+        self.tp_rank, self.tp_size = int(tp_rank), int(tp_size)
+        if self.tp_size > 1:
+            import datetime
+            import torch.distributed as dist
+            dist.init_process_group("nccl" if str(device).startswith("cuda") else "gloo", init_method=tp_address,
+                                    rank=self.tp_rank, world_size=self.tp_size, timeout=datetime.timedelta(minutes=30))
         self.name = name
         self.delay_s = float(delay_s or 0.0)    # a slow producer for pipeline experiments (host sleep per call)
         self.device = torch.device(device)
@@ -109,10 +123,12 @@ class NativeTargetEngine(InferenceEngine):
         torch.set_default_dtype(getattr(torch, dtype))
         try:
             with torch.device(self.device):      # 8B+ parameters are created directly in device memory
-                self.model = DenseTarget(TargetConfig(**target_config))
+                self.model = DenseTarget(TargetConfig(**target_config), self.tp_rank, self.tp_size)
         finally:
             torch.set_default_dtype(prev)
-        if weights_path:
+        if weights_path and self.tp_size > 1:
+            self.model.load_whole_state_dict(torch.load(weights_path, map_location="cpu", mmap=True))
+        elif weights_path:
             self.model.load_state_dict(torch.load(weights_path, map_location=self.device), strict=True)
         else:
             self.model.init_random(seed)
@@ -213,6 +229,12 @@ class NativeTargetEngine(InferenceEngine):
             raise RuntimeError(f"{self.name}: injected producer failure")
         if self.delay_s:
             time.sleep(self.delay_s)
+        if self.tp_rank > 0:
+            # a tensor-parallel helper: same pass, same collectives, nothing to store and nothing to report
+            ids = torch.cat([req.input_ids.reshape(-1) for req in requests]).to(self.device, non_blocking=True)
+            self.model.prefill(ids, [n for req in requests for n in req.document_lengths], ())
+            self.busy_seconds += time.perf_counter() - t0
+            return []
         # all requests of the call run as ONE packed prefill (bigger GEMMs); each request's rows go to its own slots
         all_views, segments, off = [], [], 0
         for req in requests:

@@ -24,6 +24,13 @@ def target_config_from_args(flat: Dict, draft_config: dict) -> dict:
             "rope_theta": draft_config.get("rope_theta", 1e6)}
 
 
+def _free_port() -> int:
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def create_engines(flat: Dict, draft_config: dict, layer_ids: List[int], target_devices: List[str],
                    ring_handles: Dict[int, dict]):
     kind = flat["inference_engine_type"]
@@ -32,11 +39,26 @@ def create_engines(flat: Dict, draft_config: dict, layer_ids: List[int], target_
     if kind == "native":
         from aspec_b200.inference.engine import NativeTargetEngine
         tcfg = target_config_from_args(flat, draft_config)
-        engines = [ProcessActor(NativeTargetEngine, tcfg, layer_ids, dev, "bfloat16" if dev.startswith("cuda") else "float32",
+        tp = max(int(flat.get("target_tp_size", 1) or 1), 1)
+        if len(target_devices) % tp:
+            raise ValueError(f"{len(target_devices)} Target GPUs cannot form engines of target_tp_size={tp}")
+
+        def rank_actor(i, dev, tp_rank=0, address=None):
+            label = f"target{i}" if tp == 1 else f"target{i}.{tp_rank}"
+            return ProcessActor(NativeTargetEngine, tcfg, layer_ids, dev, "bfloat16" if dev.startswith("cuda") else "float32",
                                 int(flat.get("seed", 0)), f"target{i}", bool(flat.get("device_flags", False)),
                                 flat.get("target_weights_path"), fault, float(flat.get("producer_delay_seconds", 0.0) or 0.0),
-                                name=f"target{i}")
-                   for i, dev in enumerate(target_devices)]
+                                tp_rank, tp, address, name=label)
+        if tp == 1:
+            engines = [rank_actor(i, dev) for i, dev in enumerate(target_devices)]
+        else:
+            # one engine = ``tp`` processes, one per GPU, that meet on a port of their own and act as one actor
+            from aspec_b200.runtime.actor import ActorGroup
+            engines = []
+            for i in range(len(target_devices) // tp):
+                address = f"tcp://127.0.0.1:{_free_port()}"
+                engines.append(ActorGroup([rank_actor(i, target_devices[i * tp + r], r, address) for r in range(tp)],
+                                          name=f"target{i}"))
         for i, e in enumerate(engines):
             e.wait_ready()
             e.call("attach_rings", {c: hs[i] for c, hs in ring_handles.items()}, timeout=300)

@@ -136,6 +136,8 @@ def batched_generate(target, prompts: Sequence[torch.Tensor], *, max_new_tokens:
         g.manual_seed(int(seeds[r]) if seeds is not None else r)
         gens.append(g)
     stops = [int(t) for t in (stop_token_ids or ())]
+    # ranks of a tensor-parallel Target take rank 0's draws and proposals, so that all of them run the same passes
+    agree = getattr(target, "agree", lambda t: t)
     lm_head = target.lm_head.detach()
     capture = list(layer_ids) if consumer is not None else []
     seqs = [[int(t) for t in p.reshape(-1)] for p in prompts]
@@ -151,7 +153,7 @@ def batched_generate(target, prompts: Sequence[torch.Tensor], *, max_new_tokens:
             for i in range(logits.shape[0]):
                 if already + i < min_new_tokens:
                     logits[i, stops] = float("-inf")
-        return sample_tokens(logits, temperature, top_k, top_p, gens[r]).tolist()
+        return agree(sample_tokens(logits, temperature, top_k, top_p, gens[r])).tolist()
 
     def keep(r: int, new: List[int]) -> None:
         room = budget[r] - (len(seqs[r]) - n0[r])
@@ -182,7 +184,7 @@ def batched_generate(target, prompts: Sequence[torch.Tensor], *, max_new_tokens:
                 known = len(seqs[r]) - 1                      # every token but the newest has features
                 padded = torch.cat([feats[r][:known], feats[r].new_zeros(1, feats[r].shape[-1])])[None]
                 ids = torch.tensor(seqs[r], device=dev)[None]
-                proposal = [int(t) for t in consumer.propose(ids, padded, lm_head_weight=lm_head)["token_ids"].reshape(-1)[: block - 1]]
+                proposal = [int(t) for t in agree(consumer.propose(ids, padded, lm_head_weight=lm_head)["token_ids"].reshape(-1)[: block - 1])]
                 proposal = proposal[: max(budget[r] - (len(seqs[r]) - n0[r]) - 1, 0)]
             trial[r] = proposal
         step = target.extend(cache, [torch.tensor([seqs[r][-1]] + trial[r]) if r in trial else torch.empty(0, dtype=torch.long)

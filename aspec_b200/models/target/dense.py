@@ -91,10 +91,12 @@ class FeatureSink:
 
 
 class _Layer(nn.Module):
-    def __init__(self, cfg: TargetConfig, layer_idx: int):
+    def __init__(self, cfg: TargetConfig, layer_idx: int, tp_rank: int = 0, tp_size: int = 1):
         super().__init__()
         d, D = cfg.head_dim, cfg.hidden_size
-        hq, hk = cfg.num_attention_heads, cfg.num_key_value_heads
+        # tensor parallel: this rank holds ``1 / tp_size`` of the heads and of the feed-forward width
+        hq, hk = cfg.num_attention_heads // tp_size, cfg.num_key_value_heads // tp_size
+        self.hq, self.hk = hq, hk
         self.cfg = cfg
         self.qkv_proj = nn.Parameter(torch.empty((hq + 2 * hk) * d, D))
         self.o_proj = nn.Parameter(torch.empty(D, hq * d))
@@ -106,10 +108,10 @@ class _Layer(nn.Module):
         self.is_moe = cfg.num_experts > 0 and layer_idx >= cfg.first_k_dense_replace
         if self.is_moe:
             from aspec_b200.models.target.moe import TargetMoE
-            self.mlp = TargetMoE(cfg)
+            self.mlp = TargetMoE(cfg, tp_rank, tp_size)
         else:
-            self.gate_up_proj = nn.Parameter(torch.empty(2 * cfg.intermediate_size, D))   # rows [gate | up]
-            self.down_proj = nn.Parameter(torch.empty(D, cfg.intermediate_size))
+            self.gate_up_proj = nn.Parameter(torch.empty(2 * cfg.intermediate_size // tp_size, D))   # rows [gate | up]
+            self.down_proj = nn.Parameter(torch.empty(D, cfg.intermediate_size // tp_size))
         self._gate_up_tiled = None
 
 
@@ -124,7 +126,7 @@ class DecodeCache:
         cfg = model.config
         dev, dtype = model.lm_head.device, model.lm_head.dtype
         self.sequences, self.capacity = int(sequences), int(capacity)
-        shape = (self.sequences * self.capacity, cfg.num_key_value_heads, cfg.head_dim)
+        shape = (self.sequences * self.capacity, model.layers[0].hk, cfg.head_dim)       # this rank's heads
         self.k = [torch.zeros(shape, device=dev, dtype=dtype) for _ in range(cfg.num_hidden_layers)]
         self.v = [torch.zeros(shape, device=dev, dtype=dtype) for _ in range(cfg.num_hidden_layers)]
         self.lengths = [0] * self.sequences
@@ -140,13 +142,27 @@ class DecodeCache:
 
 
 class DenseTarget(nn.Module):
-    """Qwen3 / Llama-shaped (optionally MoE) Target for prefill-only feature generation."""
+    """Qwen3 / Llama-shaped (optionally MoE) Target for prefill-only feature generation.
 
-    def __init__(self, cfg: TargetConfig):
+    ``tp_size > 1`` shards every layer over a group of ranks the way serving engines shard a model that does not fit one
+    GPU (the reference passes ``target_tp_size`` to its serving engine, aspec/config/inference_config.py): attention
+    heads and the feed-forward width are split (q/k/v and gate/up by output rows, o_proj and down_proj by input
+    columns), experts of a mixture layer are dealt out whole, and the two partial sums per layer are all-reduced over
+    ``tp_group``.  Embedding, norms and the output head stay whole on every rank, so every rank ends a pass with the
+    same residual stream, features and logits."""
+
+    def __init__(self, cfg: TargetConfig, tp_rank: int = 0, tp_size: int = 1, tp_group=None):
         super().__init__()
         self.config = cfg
+        self.tp_rank, self.tp_size, self.tp_group = int(tp_rank), int(tp_size), tp_group
+        if tp_size > 1:
+            for what, n in (("num_attention_heads", cfg.num_attention_heads), ("num_key_value_heads", cfg.num_key_value_heads),
+                            ("intermediate_size", cfg.intermediate_size if not cfg.num_experts or cfg.first_k_dense_replace else tp_size),
+                            ("num_experts", cfg.num_experts or tp_size)):
+                if n % tp_size:
+                    raise ValueError(f"tensor parallel size {tp_size} must divide {what} ({n})")
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
-        self.layers = nn.ModuleList([_Layer(cfg, i) for i in range(cfg.num_hidden_layers)])
+        self.layers = nn.ModuleList([_Layer(cfg, i, self.tp_rank, self.tp_size) for i in range(cfg.num_hidden_layers)])
         self.norm = nn.Parameter(torch.ones(cfg.hidden_size))
         self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size))
         self.rope_freqs = RopeFrequencies(
@@ -165,8 +181,72 @@ class DenseTarget(nn.Module):
                 if g is None:
                     g = gens[p.device] = torch.Generator(device=p.device)
                     g.manual_seed(int(seed))
-                p.normal_(0.0, std, generator=g)
+                if self.tp_size == 1:
+                    p.normal_(0.0, std, generator=g)
+                else:
+                    # draw the WHOLE tensor (one at a time) and keep this rank's part: the sharded model is the unsharded
+                    # model of the same seed, whatever the group size
+                    whole = torch.empty(self.whole_shape(name, p), device=p.device, dtype=p.dtype).normal_(0.0, std, generator=g)
+                    p.copy_(self.shard_of(name, whole))
         return self
+
+    # -- tensor-parallel layout ---------------------------------------------------------------------
+    def whole_shape(self, name: str, p: torch.Tensor) -> tuple:
+        """Shape of parameter ``name`` in the unsharded model."""
+        t, leaf = self.tp_size, name.rsplit(".", 1)[-1]
+        if t == 1 or not name.startswith("layers."):
+            return tuple(p.shape)
+        if leaf in ("qkv_proj", "gate_up_proj", "shared_gate_up") and p.dim() == 2:
+            return (p.shape[0] * t, p.shape[1])
+        if leaf in ("o_proj", "down_proj", "shared_down") and p.dim() == 2:
+            return (p.shape[0], p.shape[1] * t)
+        if leaf in ("gate_up_proj", "down_proj") and p.dim() == 3:          # expert banks: experts are dealt out whole
+            return (p.shape[0] * t, *p.shape[1:])
+        return tuple(p.shape)
+
+    def shard_of(self, name: str, whole: torch.Tensor) -> torch.Tensor:
+        """This rank's part of an unsharded parameter (a checkpoint tensor, or a freshly drawn one)."""
+        t, r, leaf = self.tp_size, self.tp_rank, name.rsplit(".", 1)[-1]
+        if t == 1 or not name.startswith("layers."):
+            return whole
+        part = lambda x, dim: x.chunk(t, dim)[r]
+        if leaf == "qkv_proj":
+            d, cfg = self.config.head_dim, self.config
+            q, k, v = whole.split([cfg.num_attention_heads * d, cfg.num_key_value_heads * d, cfg.num_key_value_heads * d], 0)
+            return torch.cat([part(q, 0), part(k, 0), part(v, 0)], 0)
+        if leaf in ("gate_up_proj", "shared_gate_up") and whole.dim() == 2:
+            gate, up = whole.chunk(2, 0)
+            return torch.cat([part(gate, 0), part(up, 0)], 0)
+        if leaf in ("o_proj", "down_proj", "shared_down") and whole.dim() == 2:
+            return part(whole, 1)
+        if leaf in ("gate_up_proj", "down_proj") and whole.dim() == 3:
+            return part(whole, 0)
+        return whole
+
+    @torch.no_grad()
+    def load_whole_state_dict(self, state: Dict[str, torch.Tensor]) -> None:
+        """Load an unsharded checkpoint: every rank keeps its part of each tensor."""
+        own = dict(self.named_parameters())
+        own.update(dict(self.named_buffers()))
+        missing = sorted(set(own) - set(state))
+        if missing:
+            raise KeyError(f"checkpoint lacks {missing[:4]}")
+        for name, p in own.items():
+            p.copy_(self.shard_of(name, state[name]).to(p.device, p.dtype))
+
+    def _reduce(self, partial: torch.Tensor) -> torch.Tensor:
+        if self.tp_size > 1:
+            import torch.distributed as dist
+            dist.all_reduce(partial, group=self.tp_group)
+        return partial
+
+    def agree(self, values: torch.Tensor) -> torch.Tensor:
+        """Rank 0's values on every rank of the group: decisions taken from (equal, but separately computed) logits."""
+        if self.tp_size > 1:
+            import torch.distributed as dist
+            values = values.contiguous()
+            dist.broadcast(values, src=dist.get_global_rank(self.tp_group, 0) if self.tp_group is not None else 0, group=self.tp_group)
+        return values
 
     # -- pieces ---------------------------------------------------------------------------------
     def _use_kernels(self, x: torch.Tensor) -> bool:
@@ -175,8 +255,8 @@ class DenseTarget(nn.Module):
     def _tiled_gate_up(self, layer: _Layer) -> torch.Tensor:
         """gate/up rows interleaved in blocks of 128 so one GEMM tile holds matching gate and up columns."""
         if layer._gate_up_tiled is None:
-            I = self.config.intermediate_size
             w = layer.gate_up_proj
+            I = w.shape[0] // 2
             if I % 128:
                 return None
             layer._gate_up_tiled = torch.stack([w[:I].view(I // 128, 128, -1), w[I:].view(I // 128, 128, -1)], 1) \
@@ -185,7 +265,7 @@ class DenseTarget(nn.Module):
 
     def _attention(self, layer: _Layer, x, positions, intervals, kv=None):
         cfg = self.config
-        hq, hk, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        hq, hk, d = layer.hq, layer.hk, cfg.head_dim
         T = x.shape[0]
         inv_freq = self.rope_freqs.get(x.device)
         if self._use_kernels(x):
@@ -228,6 +308,14 @@ class DenseTarget(nn.Module):
         ``mirrors`` is a list of destination views of the whole output, or a list of ``(row_start, row_end, views)``
         segments when several requests were batched into one prefill: then the product runs once per segment so that
         each request's rows go to its own destinations."""
+        if self.tp_size > 1:
+            # partial product of this rank's columns, summed over the group, then the residual and the feature stores
+            if self._use_kernels(a):
+                from aspec_b200.ops import gemm as G
+                part = G.gemm(a, w)
+            else:
+                part = F.linear(a, w)
+            return self._finish_reduced(self._reduce(part), residual, mirrors)
         if mirrors and isinstance(mirrors[0], tuple):
             out = torch.empty_like(residual)
             for r0, r1, views in mirrors:
@@ -241,16 +329,20 @@ class DenseTarget(nn.Module):
             m.copy_(out)
         return out
 
+    @staticmethod
+    def _finish_reduced(reduced, residual, mirrors):
+        out = residual + reduced
+        for m in mirrors or ():
+            if isinstance(m, tuple):
+                for view in m[2]:
+                    view.copy_(out[m[0]:m[1]])
+            else:
+                m.copy_(out)
+        return out
+
     def _mlp(self, layer: _Layer, x, residual, mirrors):
         if layer.is_moe:
-            out = residual + layer.mlp(x)
-            for m in mirrors or ():
-                if isinstance(m, tuple):
-                    for view in m[2]:
-                        view.copy_(out[m[0]:m[1]])
-                else:
-                    m.copy_(out)
-            return out
+            return self._finish_reduced(self._reduce(layer.mlp(x)), residual, mirrors)
         if self._use_kernels(x):
             from aspec_b200.ops import gemm as G
             tiled = self._tiled_gate_up(layer)

@@ -15,19 +15,27 @@ import torch.nn.functional as F
 
 
 class TargetMoE(nn.Module):
-    def __init__(self, cfg):
+    """``tp_size > 1``: this rank holds ``E / tp_size`` whole experts and ``1 / tp_size`` of the shared expert's width; every
+    rank routes all tokens (the router is replicated), runs the rows that chose its experts, and returns a PARTIAL sum
+    that the caller adds up over the group."""
+
+    def __init__(self, cfg, tp_rank: int = 0, tp_size: int = 1):
         super().__init__()
         D, E, I = cfg.hidden_size, cfg.num_experts, cfg.moe_intermediate_size
         self.cfg = cfg
+        self.num_experts, self.local_experts, self.first_expert = E, E // tp_size, tp_rank * (E // tp_size)
         self.top_k = cfg.num_experts_per_tok
         self.n_group, self.topk_group = max(cfg.n_group, 1), max(cfg.topk_group, 1)
         self.scale = cfg.routed_scaling_factor
         self.gate = nn.Parameter(torch.empty(E, D))
         self.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32))
-        self.gate_up_proj = nn.Parameter(torch.empty(E, 2 * I, D))      # rows [gate | up] per expert
-        self.down_proj = nn.Parameter(torch.empty(E, D, I))
+        self.gate_up_proj = nn.Parameter(torch.empty(self.local_experts, 2 * I, D))      # rows [gate | up] per expert
+        self.down_proj = nn.Parameter(torch.empty(self.local_experts, D, I))
         if cfg.num_shared_experts:
             Is = (cfg.moe_shared_expert_intermediate_size or I) * cfg.num_shared_experts
+            if Is % tp_size:
+                raise ValueError(f"tensor parallel size {tp_size} must divide the shared expert width ({Is})")
+            Is //= tp_size
             self.shared_gate_up = nn.Parameter(torch.empty(2 * Is, D))
             self.shared_down = nn.Parameter(torch.empty(D, Is))
         else:
@@ -70,10 +78,16 @@ class TargetMoE(nn.Module):
         order = flat.argsort(stable=True)
         tokens = order // self.top_k
         counts = torch.bincount(flat, minlength=self.gate.shape[0]).tolist()      # one host read per MoE layer
+        if self.local_experts != self.num_experts:
+            # the sorted rows of this rank's experts are one contiguous run
+            lo = sum(counts[: self.first_expert])
+            counts = counts[self.first_expert: self.first_expert + self.local_experts]
+            order = order[lo: lo + sum(counts)]
+            tokens = tokens[lo: lo + sum(counts)]
         rows = x[tokens].contiguous()
         out = torch.zeros(T, D, device=x.device, dtype=torch.float32)
         I = self.gate_up_proj.shape[1] // 2
-        if x.is_cuda and x.dtype == torch.bfloat16 and D % 64 == 0 and I % 64 == 0 and T:
+        if x.is_cuda and x.dtype == torch.bfloat16 and D % 64 == 0 and I % 64 == 0 and rows.shape[0]:
             # all experts in two grouped tcgen05 launches (gate/up with the SwiGLU between, then down)
             from aspec_b200.ops.grouped_gemm import grouped_experts
             y = grouped_experts(rows, self.gate_up_proj, self.down_proj, counts, 0.0)

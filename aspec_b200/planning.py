@@ -110,6 +110,31 @@ def estimate_memory(draft: dict, flat: Dict[str, Any], algorithm: str, shard: in
             "ring_bytes": ring, "estimated_total": total, "hbm_bytes": HBM_BYTES, "fits": total < 0.9 * HBM_BYTES}
 
 
+def estimate_target_memory(target: dict, tp: int = 1, max_tokens: int = 0) -> dict:
+    """Resident bf16 bytes per GPU of one in-framework Target replica spread over ``tp`` GPUs: attention and feed-forward
+    (or expert) weights divide by ``tp``; embedding, output head and norms do not; plus the activations of one pass over
+    ``max_tokens`` tokens (residual stream, q/k/v, one feed-forward intermediate)."""
+    D, V, L = int(target["hidden_size"]), int(target["vocab_size"]), int(target["num_hidden_layers"])
+    hq, hk = int(target["num_attention_heads"]), int(target["num_key_value_heads"])
+    d = int(target.get("head_dim") or D // hq)
+    I = int(target.get("intermediate_size") or 4 * D)
+    E = int(target.get("num_experts") or 0)
+    dense_first = int(target.get("first_k_dense_replace") or 0) if E else L
+    attn = D * (hq + 2 * hk) * d + hq * d * D
+    dense_ffn = 3 * D * I
+    Im = int(target.get("moe_intermediate_size") or 0)
+    shared = int(target.get("num_shared_experts") or 0) * int(target.get("moe_shared_expert_intermediate_size") or Im)
+    moe_ffn = E * 3 * D * Im + 3 * D * shared
+    sharded = L * attn + dense_first * dense_ffn + (L - dense_first) * moe_ffn
+    whole = 2 * V * D + (L - dense_first) * E * D
+    tp = max(int(tp), 1)
+    width = max(I, Im * max(int(target.get("num_experts_per_tok") or 1), 1)) // tp
+    act = int(max_tokens) * (4 * D + (hq + 2 * hk) * d // tp + 3 * width) * 2
+    total = (sharded // tp + whole) * 2 + act
+    return {"parameters": sharded + whole, "weights_bf16_per_gpu": (sharded // tp + whole) * 2, "activations": act,
+            "estimated_total": total, "tp_size": tp, "fits": total < 0.9 * HBM_BYTES}
+
+
 GPUS_PER_NODE = 8
 
 
@@ -143,6 +168,23 @@ def validate_scope(flat: Dict[str, Any], draft: dict, algorithm: str, policy: di
     per_engine = int(g("inference_num_gpus_per_engine", 1) or 1)
     if engine == "native" and targets % per_engine:
         raise ValueError(f"inference_num_gpus ({targets}) must be a multiple of inference_num_gpus_per_engine ({per_engine})")
+    tp = int(g("target_tp_size", 1) or 1)
+    if engine == "native":
+        from aspec_b200.inference.factory import target_config_from_args
+        tcfg = target_config_from_args(flat, draft)
+        if tp > 1:
+            if targets % tp:
+                raise ValueError(f"inference_num_gpus ({targets}) must be a multiple of inference.target.tp_size ({tp})")
+            for key in ("num_attention_heads", "num_key_value_heads"):
+                if int(tcfg[key]) % tp:
+                    raise ValueError(f"inference.target.tp_size ({tp}) must divide the Target's {key} ({tcfg[key]})")
+            notes.append(f"Target engines are tensor parallel over {tp} GPUs each: {targets // tp} engine(s)")
+        need = estimate_target_memory(tcfg, tp, int(g("inference_batch_tokens") or 0) or int(flat["max_seq_length"]))
+        if not need["fits"]:
+            raise ValueError(f"one Target replica needs about {need['estimated_total'] / 2**30:.0f} GiB per GPU with "
+                             f"inference.target.tp_size={tp}, more than a GPU's 180 GB: raise inference.target.tp_size")
+    if int(g("target_pp_size", 1) or 1) != 1:
+        raise ValueError("inference.target.pp_size must be 1: the in-framework Target shards by tensor parallelism only")
     if g("eval_data_path") and int(g("eval_interval") or 0) <= 0:
         notes.append("dataset.eval_data_path is set but eval_interval is 0: evaluation never runs")
     if int(g("micro_batch_size", 1)) < 1 or int(g("draft_accumulation_steps", 1)) < 1:

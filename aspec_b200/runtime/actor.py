@@ -166,6 +166,57 @@ class ProcessActor:
                 self._proc.join(5.0)
 
 
+class _JoinedFuture:
+    """Done when every member's call is done; the result is the first member's."""
+
+    def __init__(self, futures: List[Future]):
+        self.futures = futures
+
+    def done(self) -> bool:
+        return all(f.done() for f in self.futures)
+
+    def get(self, timeout: Optional[float] = None) -> Any:
+        deadline = None if timeout is None else time.monotonic() + timeout
+        results = [f.get(None if deadline is None else max(deadline - time.monotonic(), 0.01)) for f in self.futures]
+        return results[0]
+
+
+class ActorGroup(ProcessActor):
+    """Several actor processes that act as one: every call goes to all members (ranks of one tensor-parallel engine must
+    all run every pass), completes when all have completed, and returns the first member's answer.  Stands wherever one
+    ``ProcessActor`` does."""
+
+    def __init__(self, members: List[ProcessActor], name: str = "group"):
+        self.members = list(members)
+        self.name = name
+
+    def wait_ready(self) -> "ActorGroup":
+        for m in self.members:
+            m.wait_ready()
+        return self
+
+    @property
+    def pid(self) -> int:
+        return self.members[0].pid
+
+    def is_alive(self) -> bool:
+        return all(m.is_alive() for m in self.members)
+
+    def call_async(self, method: str, *args, **kwargs) -> _JoinedFuture:
+        return _JoinedFuture([m.call_async(method, *args, **kwargs) for m in self.members])
+
+    def call(self, method: str, *args, timeout: Optional[float] = None, **kwargs) -> Any:
+        return self.call_async(method, *args, **kwargs).get(timeout)
+
+    def shutdown(self, timeout: float = 10.0) -> None:
+        for m in self.members:
+            m.shutdown(timeout)
+
+    def terminate(self) -> None:
+        for m in self.members:
+            m.terminate()
+
+
 def make_queue():
     return _CTX.Queue()
 

@@ -141,8 +141,10 @@ def train_async_no_generation(flat: Dict[str, Any], draft_config: dict, evidence
             evidence.record_actor_initialization(
                 training_actors=[{"name": f"trainer{r}", "device": str(draft_devs[r]), "pid": getattr(t, "pid", None)}
                                  for r, t in enumerate(trainers)],
-                inference_engines=[{"name": f"engine{i}", "device": str(target_devs[i]) if i < len(target_devs) else "cpu",
-                                    "pid": getattr(e, "pid", None)} for i, e in enumerate(engines)])
+                # one entry per engine PROCESS: a tensor-parallel engine has one per GPU it spans
+                inference_engines=[{"name": getattr(m, "name", f"engine{i}"), "device": str(target_devs[i]) if i < len(target_devs) else "cpu",
+                                    "pid": getattr(m, "pid", None)}
+                                   for i, m in enumerate(m for e in engines for m in getattr(e, "members", [e]))])
         if flat.get("load_path"):
             # collective inside the trainer group: start it on every rank before waiting for any
             futs = [t.call_async("load_model", flat["load_path"], bool(flat.get("continual_training"))) for t in trainers]

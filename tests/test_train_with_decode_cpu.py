@@ -89,8 +89,8 @@ def test_a_run_decodes_its_own_responses_syncs_weights_and_repeats_exactly(tmp_p
     path = tmp_path / "r.yaml"
     path.write_text(RECIPE)
 
-    def run(name):
-        assert train_entry.main(["--config", str(path), f"output_dir={tmp_path / name}"]) == 0
+    def run(name, *overrides):
+        assert train_entry.main(["--config", str(path), *overrides, f"output_dir={tmp_path / name}"]) == 0
         capsys.readouterr()
         rows = [json.loads(l) for l in open(tmp_path / name / "runs" / "metrics.jsonl")]
         return [r for r in rows if "train/avg_loss" in r], json.load(open(tmp_path / name / "evidence.json"))
@@ -112,3 +112,8 @@ def test_a_run_decodes_its_own_responses_syncs_weights_and_repeats_exactly(tmp_p
     again, _ = run("b")
     assert [s["train/avg_loss"] for s in again] == pytest.approx([s["train/avg_loss"] for s in steps], rel=1e-6)
     assert [s["perf/input_tokens"] for s in again] == [s["perf/input_tokens"] for s in steps]
+    # a Target engine spread over two tensor-parallel ranks writes the same text and features
+    sharded, ev = run("tp", "inference.inference_num_gpus=2", "inference.target.tp_size=2")
+    assert [s["perf/input_tokens"] for s in sharded] == [s["perf/input_tokens"] for s in steps]
+    assert [s["train/avg_loss"] for s in sharded] == pytest.approx([s["train/avg_loss"] for s in steps], rel=1e-4)
+    assert len(ev["training_summary"]["engines"]) == 1 and ev["sections"]["actor_initialization"]["inference_engine_count"] == 2
