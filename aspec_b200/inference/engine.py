@@ -105,11 +105,6 @@ class NativeTargetEngine(InferenceEngine):
         (``tcp://host:port``).  All ranks run every call; rank 0 owns the rings and the answers."""
         from aspec_b200.models.target.dense import DenseTarget, TargetConfig
         self.tp_rank, self.tp_size = int(tp_rank), int(tp_size)
-        if self.tp_size > 1:
-            import datetime
-            import torch.distributed as dist
-            dist.init_process_group("nccl" if str(device).startswith("cuda") else "gloo", init_method=tp_address,
-                                    rank=self.tp_rank, world_size=self.tp_size, timeout=datetime.timedelta(minutes=30))
         self.name = name
         self.delay_s = float(delay_s or 0.0)    # a slow producer for pipeline experiments (host sleep per call)
         self.device = torch.device(device)
@@ -118,6 +113,12 @@ class NativeTargetEngine(InferenceEngine):
         self.fail_after = fail_after            # fault injection on the host: raise after N rows
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
+        if self.tp_size > 1:
+            import datetime
+            import torch.distributed as dist
+            dist.init_process_group("nccl" if self.device.type == "cuda" else "gloo", init_method=tp_address,
+                                    rank=self.tp_rank, world_size=self.tp_size, timeout=datetime.timedelta(minutes=30),
+                                    device_id=self.device if self.device.type == "cuda" else None)
         torch.manual_seed(seed)
         prev = torch.get_default_dtype()
         torch.set_default_dtype(getattr(torch, dtype))
