@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import importlib
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 _EXPORTS = {
     "Eagle3Model": "aspec_b200.models.eagle3", "DFlashModel": "aspec_b200.models.dflash",
