@@ -89,7 +89,12 @@ class ProcessActor:
             return self
         if not self._parent.poll(self._start_timeout):
             raise ActorTimeout(f"{self.name} did not start within {self._start_timeout}s")
-        kind, payload = self._parent.recv()
+        try:
+            kind, payload = self._parent.recv()
+        except (EOFError, OSError):
+            self._proc.join(1.0)
+            raise ActorError(f"{self.name} exited (code {self._proc.exitcode}) before it was ready "
+                             "(a negative code is the signal that killed it, e.g. -9 when the host ran out of memory)") from None
         if kind != "ready":
             raise ActorError(f"{self.name} failed to start:\n{payload}")
         self._ready = True

@@ -77,3 +77,77 @@ def test_a_failing_experiment_is_fenced_while_its_siblings_finish(tmp_path):
     }))
     res = _probe("multi_draft_faults", "--config", str(recipe), "--victim", "flash", "--action", "exit", "--out", str(tmp_path / "run"))
     assert res["ok"] and res["sibling_steps"] == {"spark": 3, "spark2": 3}, res
+
+
+@pytest.mark.timeout(600)
+def test_rows_at_the_trainer_are_the_targets_own_features_of_those_documents(tmp_path):
+    """Packed rows, two Target engines, two trainers: every dumped micro-batch holds its documents' tokens, masks and
+    captured-layer features in packing order."""
+    recipe = tmp_path / "align.yaml"
+    recipe.write_text("""
+model:
+  draft_model_config: dspark_tiny.json
+dataset:
+  train_data_path: synthetic
+  synthetic_num_documents: 48
+  synthetic_min_length: 16
+  synthetic_max_length: 48
+  synthetic_vocab_size: 500
+inference:
+  inference_engine_type: native
+  inference_num_gpus: 2
+  inference_batch_size: 3
+training:
+  training_num_gpus_per_node: 2
+  micro_batch_size: 1
+  draft_accumulation_steps: 2
+  max_seq_length: 128
+  dflash_packing: true
+  learning_rate: 1e-3
+  dspark_block_size: 4
+  dspark_num_anchors: 16
+  seed: 11
+""")
+    res = _probe("pipeline_alignment", "--config", str(recipe), "--out", str(tmp_path / "a"))
+    assert res["ok"] and res["rows"] == 4 and res["documents"] > res["rows"] and res["max_abs_feature_error"] < 1e-4
+    # a Target of another seed is not the one whose features the trainer saw
+    res = _probe("pipeline_alignment", "--config", str(recipe), "--out", str(tmp_path / "a"), "--reference-seed", "12", expect=1)
+    assert not res["ok"] and "features differ" in res["problems"][0]
+
+
+@pytest.mark.timeout(600)
+def test_a_shared_target_run_resumes_exactly(tmp_path):
+    drafts = os.path.join(ROOT, "aspec_b200", "config", "drafts")
+    recipe = tmp_path / "md.yaml"
+    recipe.write_text(f"""
+model:
+  draft_model_config: {drafts}/dspark_tiny.json
+dataset:
+  train_data_path: synthetic
+  synthetic_num_documents: 48
+  synthetic_min_length: 32
+  synthetic_max_length: 96
+  synthetic_vocab_size: 500
+inference:
+  inference_engine_type: synthetic
+training:
+  training_num_gpus_per_node: 1
+  micro_batch_size: 1
+  draft_accumulation_steps: 2
+  max_seq_length: 128
+  learning_rate: 1e-3
+  dspark_block_size: 4
+  dspark_num_anchors: 16
+  dflash_block_size: 4
+  dflash_num_anchors: 16
+  seed: 7
+transport:
+  destination_ring_slots: 3
+experiments:
+  - name: spark
+  - name: flash
+    model:
+      draft_model_config: {drafts}/dflash_tiny.json
+""")
+    res = _probe("multi_draft_resume", "--config", str(recipe), "--out", str(tmp_path / "r"), "--force-cpu")
+    assert res["ok"] and all(v["exact"] for v in res["experiments"].values())
