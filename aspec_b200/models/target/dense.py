@@ -295,6 +295,12 @@ class DenseTarget(nn.Module):
         o, _ = interval_attention_reference(q, k, v, intervals, d ** -0.5)
         return o.reshape(T, hq * d)
 
+    def _logits(self, final):
+        if self._use_kernels(final) and self.lm_head.shape[0] % 8 == 0:
+            from aspec_b200.ops import gemm as G
+            return G.gemm(final, self.lm_head)
+        return F.linear(final, self.lm_head)
+
     def _norm(self, x, w, out=None):
         if self._use_kernels(x):
             from aspec_b200.ops import elementwise_sm100 as E
@@ -412,7 +418,7 @@ class DenseTarget(nn.Module):
         out = {"hidden_states": getattr(sink, "hidden_states", None),
                "last_hidden_states": getattr(sink, "last_hidden_states", None), "final_hidden": final}
         if want_logits:
-            out["logits"] = F.linear(final, self.lm_head)
+            out["logits"] = self._logits(final)
         return out
 
     # -- decode with cached keys / values ------------------------------------------------------------
@@ -463,7 +469,7 @@ class DenseTarget(nn.Module):
         offsets = [0]
         for m in counts:
             offsets.append(offsets[-1] + m)
-        return {"logits": F.linear(final, self.lm_head), "hidden_states": sink.hidden_states, "offsets": offsets}
+        return {"logits": self._logits(final), "hidden_states": sink.hidden_states, "offsets": offsets}
 
     def memory_bytes(self) -> int:
         return sum(p.numel() * p.element_size() for p in self.parameters())
