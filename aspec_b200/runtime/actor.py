@@ -181,8 +181,23 @@ class _JoinedFuture:
         return all(f.done() for f in self.futures)
 
     def get(self, timeout: Optional[float] = None) -> Any:
+        # a member that died leaves its peers waiting for it inside a collective: its exit is reported at once instead
+        # of after their timeout
         deadline = None if timeout is None else time.monotonic() + timeout
-        results = [f.get(None if deadline is None else max(deadline - time.monotonic(), 0.01)) for f in self.futures]
+        results: Dict[int, Any] = {}
+        while len(results) < len(self.futures):
+            for i, f in enumerate(self.futures):
+                if i not in results and f.done():
+                    results[i] = f.get(1.0)
+            if len(results) == len(self.futures):
+                break
+            for i, f in enumerate(self.futures):
+                if i not in results and not f.actor.is_alive() and not f.done():
+                    raise ActorError(f"{f.actor.name} exited (code {f.actor._proc.exitcode}) during {f.method}; "
+                                     "the other members of its group cannot finish the call")
+            if deadline is not None and time.monotonic() >= deadline:
+                raise ActorTimeout(f"{self.futures[0].actor.name}.{self.futures[0].method} exceeded {timeout}s")
+            time.sleep(0.005)
         return results[0]
 
 

@@ -13,12 +13,27 @@ import argparse
 import glob
 import json
 import os
+import shutil
 import subprocess
 import sys
+import tempfile
 
 from tools.release.audit_release import audit
 from tools.release.check_docs import main as check_docs
 from tools.release.check_wheel_install import check_install
+
+
+def build_wheel(root: str, out: str) -> subprocess.CompletedProcess:
+    """Build from a scratch copy of what the wheel is made of, so that the build leaves nothing in the checkout."""
+    with tempfile.TemporaryDirectory() as tmp:
+        stage = os.path.join(tmp, "src")
+        os.makedirs(stage)
+        for name in ("pyproject.toml", "README.md"):
+            shutil.copy(os.path.join(root, name), stage)
+        shutil.copytree(os.path.join(root, "aspec_b200"), os.path.join(stage, "aspec_b200"),
+                        ignore=shutil.ignore_patterns("__pycache__", "obj", "*.o"))
+        return subprocess.run([sys.executable, "-m", "pip", "wheel", stage, "--no-build-isolation", "--no-deps", "--no-index", "-w", out],
+                              capture_output=True, text=True)
 
 
 def main(argv=None) -> int:
@@ -37,8 +52,7 @@ def main(argv=None) -> int:
     os.makedirs(a.out, exist_ok=True)
     for old in glob.glob(os.path.join(a.out, "aspec_b200-*.whl")):
         os.remove(old)
-    res = subprocess.run([sys.executable, "-m", "pip", "wheel", root, "--no-build-isolation", "--no-deps", "--no-index", "-w", a.out],
-                         capture_output=True, text=True)
+    res = build_wheel(root, a.out)
     if res.returncode != 0:
         print(res.stdout[-2000:], res.stderr[-2000:])
         return res.returncode
