@@ -130,6 +130,8 @@ class DecodeCache:
         self.k = [torch.zeros(shape, device=dev, dtype=dtype) for _ in range(cfg.num_hidden_layers)]
         self.v = [torch.zeros(shape, device=dev, dtype=dtype) for _ in range(cfg.num_hidden_layers)]
         self.lengths = [0] * self.sequences
+        # query positions per attention tile; ``None`` = ask the kernel wrapper (set by hand to exercise the padding on CPU)
+        self.tile_positions: Optional[int] = None
 
     def accept(self, sequence: int, tokens: int) -> None:
         """Keep the first ``tokens`` rows that the last ``extend`` wrote for ``sequence``."""
@@ -139,6 +141,29 @@ class DecodeCache:
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.k + self.v)
+
+
+def tile_padding(counts: Sequence[int], per_tile: int, device):
+    """Index maps that give every sequence query tiles of its own.
+
+    The attention kernel walks, per query tile, the key tiles between the lowest and the highest key any row of the
+    tile may see.  New tokens of different sequences point at cache regions that lie a whole ``capacity`` apart, so a
+    tile shared by two sequences would walk everything between them.  Padding each sequence's rows to a multiple of the
+    tile's ``per_tile`` positions (with repeats of its last row, dropped again afterwards) keeps each tile inside one
+    sequence's region.  Returns ``(gather [Mp], keep [M])``: padded row -> source row, and where the real rows sit in the
+    padded layout."""
+    gather: List[int] = []
+    keep: List[int] = []
+    src = 0
+    for m in counts:
+        if m == 0:
+            continue
+        base = len(gather)
+        gather += list(range(src, src + m)) + [src + m - 1] * (-m % per_tile)
+        keep += list(range(base, base + m))
+        src += m
+    return (torch.tensor(gather, dtype=torch.long).to(device, non_blocking=True),
+            torch.tensor(keep, dtype=torch.long).to(device, non_blocking=True))
 
 
 class DenseTarget(nn.Module):
@@ -282,6 +307,9 @@ class DenseTarget(nn.Module):
             k, _ = E.qk_norm_rope_fwd(k.contiguous(), kn, positions, inv_freq, cfg.rms_norm_eps, 1.0)
             if kv is not None:          # decode: the new rows join the cached keys / values and attend all of them
                 k, v = kv[0].index_copy_(0, kv[2], k), kv[1].index_copy_(0, kv[2], v)
+                if kv[3] is not None:   # one sequence per query tile (see ``tile_padding``)
+                    o, _ = A.forward(q.index_select(0, kv[3][0]), k, v, intervals.index_select(0, kv[3][0]), d ** -0.5)
+                    return o.index_select(0, kv[3][1]).view(T, hq * d)
             o, _ = A.forward(q, k, v, intervals, d ** -0.5)
             return o.view(T, hq * d)
         qkv = F.linear(x, layer.qkv_proj)
@@ -292,6 +320,9 @@ class DenseTarget(nn.Module):
         k = qk_norm_rope_reference(k, layer.k_norm if cfg.qk_norm else None, positions, inv_freq, cfg.rms_norm_eps)
         if kv is not None:
             k, v = kv[0].index_copy_(0, kv[2], k.to(kv[0].dtype)), kv[1].index_copy_(0, kv[2], v.to(kv[1].dtype))
+            if kv[3] is not None:
+                o, _ = interval_attention_reference(q.index_select(0, kv[3][0]), k, v, intervals.index_select(0, kv[3][0]), d ** -0.5)
+                return o.index_select(0, kv[3][1]).reshape(T, hq * d)
         o, _ = interval_attention_reference(q, k, v, intervals, d ** -0.5)
         return o.reshape(T, hq * d)
 
@@ -457,11 +488,16 @@ class DenseTarget(nn.Module):
         positions = pos.to(torch.int32).to(dev, non_blocking=True)
         intervals = iv.to(dev, non_blocking=True)
         x = self.embed_tokens(torch.cat([t.reshape(-1) for t in new_ids]).to(dev))
+        per_tile = cache.tile_positions
+        if per_tile is None and self._use_kernels(x):
+            from aspec_b200.ops.attention_sm100 import positions_per_tile
+            per_tile = positions_per_tile(self.layers[0].hq, self.layers[0].hk)
+        padding = tile_padding(counts, per_tile, dev) if per_tile and sum(m > 0 for m in counts) > 1 else None
         sink = FeatureSink(M, capture_layers, cfg.hidden_size, dev, x.dtype)
         capture = set(capture_layers)
         for i, layer in enumerate(self.layers):
             h = self._norm(x, layer.input_layernorm)
-            a = self._attention(layer, h, positions, intervals, kv=(cache.k[i], cache.v[i], rows))
+            a = self._attention(layer, h, positions, intervals, kv=(cache.k[i], cache.v[i], rows, padding))
             x = self._proj_residual(a, layer.o_proj, x)
             h = self._norm(x, layer.post_attention_layernorm)
             x = self._mlp(layer, h, x, sink.layer_views(i) if i in capture else None)

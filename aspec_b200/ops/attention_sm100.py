@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import ctypes as _c
-from typing import Tuple
+from typing import Optional, Tuple
 
 import torch
 
@@ -46,6 +46,13 @@ def _rows_view(t: torch.Tensor) -> Tuple[torch.Tensor, int]:
     if t.stride(2) != 1 or t.stride(1) != t.shape[2] or t.stride(0) % 8 or t.data_ptr() % 16:
         t = t.contiguous()
     return t, t.stride(0)
+
+
+def positions_per_tile(hq: int, hkv: int) -> Optional[int]:
+    """Query positions that share one 128-row tile of the kernels (the head group of a key / value head is folded into
+    the tile's rows); ``None`` for a group the kernels do not tile in one piece."""
+    group = hq // max(hkv, 1)
+    return 128 // group if hq % max(hkv, 1) == 0 and group in (1, 2, 4, 8, 16) else None
 
 
 def forward(q, k, v, intervals, scale, out=None, lse=None) -> Tuple[torch.Tensor, torch.Tensor]:

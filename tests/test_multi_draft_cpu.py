@@ -212,9 +212,12 @@ def test_a_shared_target_run_resumes_every_experiment_from_its_own_checkpoint(tm
     second = run(tmp_path / "second", 4, f"\n  load_path: {middle}")
     assert whole["spark"]["completed_steps"] == 4
     assert second["spark"]["completed_steps"] == 2 and second["flash"]["completed_steps"] == 2
-    # the root of an earlier run names every experiment's latest checkpoint: nothing is left to train
-    done = run(tmp_path / "done", 4, f"\n  load_path: {tmp_path / 'whole'}")
-    assert done["spark"]["completed_steps"] == 0
+    # the root of an earlier run names every experiment's own directory (their latest checkpoints)
+    from aspec_b200.multi_draft import experiment_load_path
+    root = str(tmp_path / "whole")
+    assert experiment_load_path({"load_path": root}, "flash") == os.path.join(root, "experiments", "flash")
+    assert experiment_load_path({"load_path": str(middle)}, "spark").endswith("experiments/spark/checkpoints/iter_0000002")
+    assert experiment_load_path({}, "spark") is None
     for name in ("spark", "flash"):
         a = checkpoint_hashes(str(tmp_path / "whole" / "experiments" / name / "checkpoints" / "iter_0000004"))
         b = checkpoint_hashes(str(tmp_path / "second" / "experiments" / name / "checkpoints" / "iter_0000004"))

@@ -119,3 +119,28 @@ def test_stop_tokens_wait_for_the_minimum_length_and_filters_keep_the_head_of_th
     assert filter_logits(x, 1.0, -1, 0.7).isinf().tolist() == [[False, False, True, True]]
     assert filter_logits(x, 1.0, -1, 0.1).isinf().tolist() == [[False, True, True, True]]
     torch.testing.assert_close(filter_logits(x, 0.5, -1, 1.0), x * 2)
+
+
+def test_sequences_get_query_tiles_of_their_own_without_changing_the_result():
+    """The padding that keeps one sequence per attention tile (needed by the kernels, exercised here on the CPU path):
+    same logits and features as without it, for a pass with ragged new-token counts and an idle sequence."""
+    from aspec_b200.models.target.dense import tile_padding
+    gather, keep = tile_padding([3, 0, 5, 4], 4, "cpu")
+    assert gather.tolist() == [0, 1, 2, 2, 3, 4, 5, 6, 7, 7, 7, 7, 8, 9, 10, 11]
+    assert keep.tolist() == [0, 1, 2, 4, 5, 6, 7, 8, 12, 13, 14, 15]
+    assert gather[keep].tolist() == list(range(12))                     # the kept rows are the real rows, in order
+    target = _target()
+    ids = [torch.randint(0, 500, (n,), generator=torch.Generator().manual_seed(n)) for n in (9, 6, 7)]
+    plain, padded = target.new_decode_cache(3, 16), target.new_decode_cache(3, 16)
+    padded.tile_positions = 4
+    for step in ([ids[0][:5], ids[1][:2], ids[2][:7]], [ids[0][5:], torch.empty(0, dtype=torch.long), ids[2][:0]], [ids[0][:0], ids[1][2:], ids[2][:0]]):
+        if sum(t.numel() for t in step) == 0:
+            continue
+        a, b = target.extend(plain, step, [0, 2]), target.extend(padded, step, [0, 2])
+        torch.testing.assert_close(a["logits"], b["logits"], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(a["hidden_states"], b["hidden_states"], rtol=1e-5, atol=1e-6)
+        for r, t in enumerate(step):
+            plain.accept(r, t.numel())
+            padded.accept(r, t.numel())
+    from aspec_b200.ops.attention_sm100 import positions_per_tile
+    assert positions_per_tile(32, 8) == 32 and positions_per_tile(8, 8) == 128 and positions_per_tile(40, 8) is None

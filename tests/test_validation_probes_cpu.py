@@ -40,16 +40,13 @@ def test_injected_host_faults_fail_the_run_and_leave_nothing_behind(tmp_path, ac
 
 @pytest.mark.timeout(600)
 def test_layouts_are_compared_update_by_update(tmp_path):
-    res = _probe("layout_compare", "--config", RECIPE, "--out", str(tmp_path / "lc"), "--steps", "3",
-                 "--a", "training.fsdp_strategy=REPLICATE", "--b", "training.fsdp_strategy=SHARD_OPTIMIZER", "--",
-                 "training.training_num_gpus_per_node=2", "transport.destination_ring_slots=5")
-    assert res["metrics_agree"] and res["updates"] == [3, 3]
+    # (the three sharding strategies are compared update by update in tests/test_pipeline_cpu.py)
     # context parallel 1 against 2: with row-derived anchor draws both layouts train on the same blocks
     res = _probe("layout_compare", "--config", RECIPE, "--out", str(tmp_path / "cp"), "--steps", "3", "--rtol", "1e-4",
                  "--a", "training.draft_context_parallel_size=1", "training.training_num_gpus_per_node=1",
                  "--b", "training.draft_context_parallel_size=2", "training.training_num_gpus_per_node=2", "--",
                  "transport.destination_ring_slots=5", "training.deterministic_anchor_sampling=true")
-    assert res["metrics_agree"] and res["worst_relative_difference"] < 1e-5
+    assert res["metrics_agree"] and res["worst_relative_difference"] < 1e-5 and res["updates"] == [3, 3]
     # one rank accumulating four rows against two ranks accumulating two: the same documents per update, pooled the same way
     res = _probe("layout_compare", "--config", RECIPE, "--out", str(tmp_path / "dp"), "--steps", "3", "--rtol", "1e-4",
                  "--a", "training.training_num_gpus_per_node=1", "training.draft_accumulation_steps=4",
