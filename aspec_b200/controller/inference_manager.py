@@ -41,6 +41,8 @@ class InferenceManager:
         self.completed = 0
         self._engine_load = [0] * len(self.engines)
         self.dead_consumers: set = set()          # fenced readers: never leased again, pending waits are abandoned
+        # ``f(consumer, seconds) -> bool``: called when a consumer freed no slot in time; True = it was fenced, go on
+        self.on_consumer_stalled: Optional[Callable[[int, float], bool]] = None
 
     def start(self) -> None:
         self._thread.start()
@@ -143,6 +145,12 @@ class InferenceManager:
                                 flush()
                                 self._collect(block=False)
                                 if time.monotonic() > deadline or self._stop.is_set():
+                                    # several independent readers share this stream: one that stopped consuming is
+                                    # taken out (its owner decides) instead of ending the stream for all of them
+                                    if self.on_consumer_stalled is not None and not self._stop.is_set() \
+                                            and self.on_consumer_stalled(c, self.acquire_timeout) and c in self.dead_consumers:
+                                        lease = None
+                                        break
                                     raise TimeoutError(
                                         f"no free ring slot on consumer {c} within {self.acquire_timeout}s") from None
                         if lease is not None:

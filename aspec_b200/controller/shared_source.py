@@ -30,6 +30,7 @@ class SharedSourceState:
         self.rows_shared = 0
         self.fenced: Dict[str, str] = {}
         manager.on_result = self._on_result
+        manager.on_consumer_stalled = self._stalled
 
     # -- experiment side ------------------------------------------------------------------------------
     def proxy(self, experiment: str) -> "ExperimentManager":
@@ -47,6 +48,14 @@ class SharedSourceState:
                                        f"{first.data_ids} vs {request.data_ids}")
             entry[experiment] = (request, tuple(consumers))
             self._flush_ready()
+
+    def _stalled(self, consumer: int, seconds: float) -> bool:
+        """A reader freed no ring slot for ``seconds``: its experiment leaves the stream, the others go on."""
+        owner = max((n for n in self.offsets if self.offsets[n] <= consumer), key=lambda n: self.offsets[n], default=None)
+        if owner is None or owner not in self.live or len(self.live) < 2:
+            return False                      # the last reader standing: the stream has nobody else to serve
+        self.fence(owner, f"stalled: consumer {consumer} freed no ring slot within {seconds:.0f} s")
+        return True
 
     def fence(self, experiment: str, reason: str) -> None:
         """Remove an experiment; rows that only waited for it go to its siblings."""
