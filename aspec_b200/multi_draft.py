@@ -26,7 +26,9 @@ from aspec_b200.planning import ExecutionPlan, compile_execution_plan
 # what every experiment must share so that all of them plan identical rows
 _SHARED_ROW_KEYS = ("train_data_path", "max_seq_length", "micro_batch_size", "draft_accumulation_steps", "dflash_packing",
                     "seed", "dataset_seed", "num_epochs", "draft_context_parallel_size", "world_size",
-                    "synthetic_num_documents", "synthetic_min_length", "synthetic_max_length", "synthetic_vocab_size")
+                    "synthetic_num_documents", "synthetic_min_length", "synthetic_max_length", "synthetic_vocab_size",
+                    # held-out rows are produced once and read by all experiments, at the same updates
+                    "eval_data_path", "eval_interval", "eval_num_documents")
 
 
 @dataclasses.dataclass
@@ -212,6 +214,20 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
         for n in names[1:]:
             for s in controllers[n].samples:
                 s["useful"] = work[s["data_id"]]
+        # held-out split: the same admission rule (a document every experiment admits), so that all of them ask for the
+        # same held-out rows
+        eval_controllers = {}
+        if base.get("eval_data_path") and int(base.get("eval_interval") or 0) > 0:
+            for n in names:
+                g = groups[n]
+                eval_args = dict(g["args"], train_data_path=g["flat"]["eval_data_path"], shuffle_dataset=False, train_with_decode=False,
+                                 synthetic_num_documents=int(g["flat"].get("eval_num_documents") or 32),
+                                 dataset_seed=int(g["flat"].get("seed", 0)) + 1)
+                eval_controllers[n] = TrainingController(eval_args, dp_size=g["dp"], consumers_per_row=g["cp"],
+                                                         algorithm=resolve_draft_algorithm(plan.plans[n].draft_config))
+            held_out = _common_samples(eval_controllers, None)
+            for ec in eval_controllers.values():
+                ec.load_dataset(held_out)
         from aspec_b200.controller.training_controller import draft_vocabulary_from_samples
         for n in names:
             mapping = draft_vocabulary_from_samples(common, plan.plans[n].draft_config, groups[n]["flat"])
@@ -247,12 +263,29 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
                 len(c.samples) // max(g["dp"] * int(g["flat"].get("micro_batch_size", 1))
                                       * int(g["flat"].get("draft_accumulation_steps", 1)), 1), 1)
             cp = g["cp"]
+            consumer_of_rank = lambda r: list(range(r * cp, (r + 1) * cp))       # noqa: E731
+            on_step, runner = None, None
+            if n in eval_controllers:
+                # held-out evaluation: every experiment asks for the same held-out rows at the same updates; the shared
+                # stream produces each row once, and every experiment keeps its own cache, history and best checkpoint
+                from aspec_b200.controller.eval import EvalRunner
+                runner = EvalRunner(controller=eval_controllers[n], manager=shared.proxy(n), trainers=g["trainers"], rings=g["rings"],
+                                    train_queues=g["queues"], args=g["args"], layer_ids=g["layer_ids"],
+                                    consumer_of_rank=consumer_of_rank,
+                                    decode_anchors_per_doc=int(g["flat"].get("eval_decode_anchors_per_doc") or 0))
+                interval = int(g["flat"]["eval_interval"])
+
+                def on_step(next_step: int, metrics: dict, n=n, runner=runner, interval=interval) -> None:
+                    if next_step % interval == 0:
+                        log({"experiment": n, "train/step": next_step - 1, **runner.run(next_step)})
             try:
                 results[n] = training_loop(controller=c, manager=shared.proxy(n), trainers=g["trainers"], rings=g["rings"],
                                            train_queues=g["queues"], args=g["args"], layer_ids=g["layer_ids"],
                                            num_steps=steps - start_steps[n], start_step=start_steps[n],
                                            log=lambda m, n=n: log({"experiment": n, **m}),
-                                           consumer_of_rank=lambda r: list(range(r * cp, (r + 1) * cp)))
+                                           consumer_of_rank=consumer_of_rank, on_step=on_step)
+                if runner is not None:
+                    results[n]["evaluation"] = {"history": runner.history, "best": runner.best}
             except BaseException as exc:                       # noqa: BLE001 - one experiment must not stop the others
                 results[n] = {"failed": f"{type(exc).__name__}: {exc}"}
                 log({"experiment": n, "failed": results[n]["failed"][:400]})

@@ -227,3 +227,32 @@ def test_a_shared_target_run_resumes_every_experiment_from_its_own_checkpoint(tm
 def _recipe_text(tmp_path):
     _plan(tmp_path)
     return str(tmp_path / "recipe.yaml")
+
+
+@pytest.mark.timeout(600)
+def test_experiments_evaluate_on_held_out_rows_that_the_target_produces_once(tmp_path):
+    """Both experiments evaluate after updates 2 and 4: the first evaluation pulls the held-out rows through the shared
+    stream (each row produced once for both readers), the second replays every experiment's own cache."""
+    recipe_text = open(_recipe_text(tmp_path)).read().replace("num_train_steps: 3", "num_train_steps: 4") \
+        .replace("  synthetic_max_length: 96", "  synthetic_max_length: 96\n  eval_data_path: synthetic\n  eval_interval: 2\n  eval_num_documents: 6")
+    recipe = tmp_path / "eval.yaml"
+    recipe.write_text(recipe_text)
+    plan = compile_multi_draft_plan(load_config(str(recipe)))
+    for p in plan.plans.values():
+        p.runtime_args.update(synthetic_vocab_size=500, force_cpu=True)
+    logs = []
+    out = run_multi_draft(plan, log=logs.append)
+    train_rows = 4 * 2                                           # updates x micro-batches, one trainer per experiment
+    assert out["shared_source"]["rows_shared"] == train_rows + 6 and out["shared_source"]["fenced"] == {}
+    for name in ("spark", "flash"):
+        assert out[name]["completed_steps"] == 4 and out[name]["ledger"]["validated"]
+        history = out[name]["evaluation"]["history"]
+        assert [h["step"] for h in history] == [2, 4] and [h["from_cache"] for h in history] == [False, True]
+        assert history[0]["metrics"]["eval/avg_loss"] == history[0]["metrics"]["eval/avg_loss"]          # a number
+        assert out[name]["evaluation"]["best"]["step"] in (2, 4)
+        assert os.path.isfile(os.path.join(plan.plans[name].runtime_args["output_dir"], "evaluation.json"))
+        assert sum(1 for m in logs if m.get("experiment") == name and "eval/avg_loss" in m) == 2
+    other = tmp_path / "other.yaml"
+    other.write_text(recipe_text.replace("  - name: flash\n", "  - name: flash\n    dataset:\n      eval_interval: 3\n"))
+    with pytest.raises(ValueError, match="must agree on eval_interval"):
+        compile_multi_draft_plan(load_config(str(other)))
