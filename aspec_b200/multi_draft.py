@@ -38,9 +38,16 @@ class MultiDraftPlan:
     union: Dict[str, Any]                    # shared feature contract + per-reader views
     consumer_offsets: Dict[str, int]
     schema_version: str = "aspec.multi-draft-plan/v1"
+    configs: Dict[str, Config] = dataclasses.field(default_factory=dict)      # every experiment's resolved configuration
+
+    @property
+    def plan_id(self) -> str:
+        import hashlib
+        body = json.dumps({n: self.plans[n].plan_id for n in self.names}, sort_keys=True)
+        return "sha256:" + hashlib.sha256(body.encode()).hexdigest()
 
     def to_json(self) -> str:
-        return json.dumps({"schema_version": self.schema_version, "experiments": self.names,
+        return json.dumps({"schema_version": self.schema_version, "plan_id": self.plan_id, "experiments": self.names,
                            "consumer_offsets": self.consumer_offsets, "shared_feature_contract": self.union["contract"],
                            "reader_views": self.union["views"],
                            "plans": {n: json.loads(p.to_json()) for n, p in self.plans.items()}}, indent=2, default=str)
@@ -79,10 +86,11 @@ def child_config(config: Config, experiment: Dict[str, Any]) -> Config:
 def compile_multi_draft_plan(config: Config) -> MultiDraftPlan:
     if len(config.experiments) < 2:
         raise ValueError("a shared-Target run needs at least two experiments")
-    plans, names = {}, []
+    plans, names, configs = {}, [], {}
     for exp in config.experiments:
         names.append(exp["name"])
-        plans[exp["name"]] = compile_execution_plan(child_config(config, exp))
+        configs[exp["name"]] = child_config(config, exp)
+        plans[exp["name"]] = compile_execution_plan(configs[exp["name"]])
     first = plans[names[0]].runtime_args
     for n in names:
         if plans[n].runtime_args.get("train_with_decode"):
@@ -98,7 +106,7 @@ def compile_multi_draft_plan(config: Config) -> MultiDraftPlan:
     for n in names:
         offsets[n] = at
         at += int(plans[n].runtime_args["world_size"])
-    return MultiDraftPlan(names, plans, union, offsets)
+    return MultiDraftPlan(names, plans, union, offsets, configs=configs)
 
 
 def experiment_load_path(flat: Dict[str, Any], name: str) -> Optional[str]:
@@ -127,7 +135,9 @@ def _common_samples(controllers: Dict[str, Any], dataset: Optional[List[dict]]) 
 
 
 def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = None, log=print,
-                    cancel: Optional[Dict[str, threading.Event]] = None) -> Dict[str, Any]:
+                    cancel: Optional[Dict[str, threading.Event]] = None, claim_directories: bool = True) -> Dict[str, Any]:
+    """``claim_directories=False``: the caller has already claimed every experiment's run directory (and keeps their
+    evidence)."""
     from aspec_b200.controller.inference_manager import InferenceManager
     from aspec_b200.controller.loop import training_loop
     from aspec_b200.controller.shared_source import SharedSourceState
@@ -151,9 +161,10 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
         next_dev = 0
         for n in names:
             flat = plan.plans[n].to_runtime_args()
-            claim_run_directory(flat["output_dir"])
-            with open(os.path.join(flat["output_dir"], "plan.json"), "w") as f:
-                f.write(plan.plans[n].to_json())
+            if claim_directories:
+                claim_run_directory(flat["output_dir"])
+                with open(os.path.join(flat["output_dir"], "plan.json"), "w") as f:
+                    f.write(plan.plans[n].to_json())
             world = int(flat["world_size"])
             devs = flat.get("trainer_devices")
             if not devs:
@@ -206,6 +217,7 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
             controllers[n] = TrainingController(g["args"], dp_size=g["dp"], consumers_per_row=cp,
                                                 algorithm=resolve_draft_algorithm(plan.plans[n].draft_config))
         common = _common_samples(controllers, dataset)
+        own_admission = {n: dict(getattr(c, "admission", None) or {}) for n, c in controllers.items()}
         for c in controllers.values():
             c.load_dataset(common)
         # packed rows are cut by a per-document work measure that depends on the algorithm (anchor starts, TTT positions);
@@ -286,6 +298,15 @@ def run_multi_draft(plan: MultiDraftPlan, *, dataset: Optional[List[dict]] = Non
                                            consumer_of_rank=consumer_of_rank, on_step=on_step)
                 if runner is not None:
                     results[n]["evaluation"] = {"history": runner.history, "best": runner.best}
+                # a document is in the shared stream only if every experiment admits it: what this experiment's own rule
+                # rejected, and what it lost to its siblings' rules
+                own = own_admission[n]
+                rejected = dict(own.get("rejected") or {})
+                lost = int(own.get("source_rows", len(c.samples))) - sum(rejected.values()) - len(c.samples)
+                if lost > 0:
+                    rejected["not_admitted_by_every_experiment"] = lost
+                results[n]["admission"] = {"admitted": len(c.samples), "source_rows": own.get("source_rows", len(c.samples)),
+                                           "rejected": rejected, "fingerprint": c.dataset_fingerprint()}
             except BaseException as exc:                       # noqa: BLE001 - one experiment must not stop the others
                 results[n] = {"failed": f"{type(exc).__name__}: {exc}"}
                 log({"experiment": n, "failed": results[n]["failed"][:400]})
@@ -321,6 +342,31 @@ def run_multi_draft_from_config(config: Config, dry_run: bool = False) -> int:
     os.makedirs(config.output_dir, exist_ok=True)
     with open(os.path.join(config.output_dir, "multi-draft-plan.json"), "w") as f:
         f.write(plan.to_json())
+    # every experiment's directory is a run directory of its own (configuration, plan, evidence: ``--report`` works on
+    # it); the root keeps the session's evidence (reference: aspec/multi_draft.py:404-440)
+    from aspec_b200.config.train_config import save_config
+    from aspec_b200.evidence import RunEvidenceRecorder
+    from aspec_b200.train_entry import claim_run_directory
+    session = {"schema_version": "aspec.multi-draft-evidence/v1", "plan_id": plan.plan_id, "state": "running",
+               "started_at": time.time(), "experiments": {}}
+
+    def persist_session() -> None:
+        tmp = os.path.join(config.output_dir, "evidence.json.tmp")
+        with open(tmp, "w") as f:
+            json.dump(session, f, indent=2, sort_keys=True, default=str)
+        os.replace(tmp, os.path.join(config.output_dir, "evidence.json"))
+
+    recorders: Dict[str, RunEvidenceRecorder] = {}
+    for name in plan.names:
+        out_dir = plan.plans[name].runtime_args["output_dir"]
+        claim_run_directory(out_dir)
+        if name in plan.configs:
+            save_config(plan.configs[name], os.path.join(out_dir, "config.yaml"))
+        with open(os.path.join(out_dir, "plan.json"), "w") as f:
+            f.write(plan.plans[name].to_json())
+        recorders[name] = RunEvidenceRecorder(plan.plans[name], out_dir)
+        session["experiments"][name] = {"state": "running", "plan_id": plan.plans[name].plan_id, "output_dir": out_dir}
+    persist_session()
     from aspec_b200.utils.logging import Trackers
     trackers: Dict[str, Trackers] = {}
 
@@ -341,10 +387,30 @@ def run_multi_draft_from_config(config: Config, dry_run: bool = False) -> int:
         trackers[name].log({k: v for k, v in m.items() if k != "experiment"}, int(m.get("train/step") or 0))
 
     try:
-        results = run_multi_draft(plan, log=log)
+        results = run_multi_draft(plan, log=log, claim_directories=False)
+    except BaseException as exc:                                   # noqa: BLE001 - recorded, then re-raised
+        for name, rec in recorders.items():
+            rec.fail(exc)
+            session["experiments"][name]["state"] = "failed"
+        session.update(state="failed", finished_at=time.time(), failure=f"{type(exc).__name__}: {exc}"[:2000])
+        persist_session()
+        raise
     finally:
         for t in trackers.values():
             t.close()
+    for name, rec in recorders.items():
+        res = results.get(name) or {}
+        if "failed" in res:
+            rec.fail(RuntimeError(res["failed"]))
+        else:
+            adm = res.get("admission") or {}
+            rec.record_dataset_admission(dataset_size=int(adm.get("admitted", 0)), admission=adm)
+            rec.complete({k: v for k, v in res.items() if k not in ("history", "admission")})
+        session["experiments"][name].update(state="failed" if "failed" in res else "completed",
+                                            completed_steps=res.get("completed_steps"), failure=res.get("failed"))
+    session.update(state="completed" if all(e["state"] == "completed" for e in session["experiments"].values()) else "failed",
+                   finished_at=time.time(), shared_source=results.get("shared_source"))
+    persist_session()
     with open(os.path.join(config.output_dir, "multi-draft-summary.json"), "w") as f:
         json.dump({k: ({kk: vv for kk, vv in v.items() if kk != "history"} if isinstance(v, dict) else v)
                    for k, v in results.items()}, f, indent=2, default=str)

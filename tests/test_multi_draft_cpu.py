@@ -101,6 +101,19 @@ def test_multi_draft_from_the_command_line_writes_per_experiment_metrics(tmp_pat
         rows = [json.loads(line) for line in (run / "experiments" / name / "runs" / "metrics.jsonl").read_text().splitlines()]
         assert [r["step"] for r in rows] == [0, 1, 2] and all("experiment" not in r for r in rows)
         assert json.loads((run / "experiments" / name / "tracking.json").read_text())["active"] == ["jsonl"]
+        # every experiment's directory is a run directory of its own: configuration, plan, evidence, and a valid report
+        evidence = json.loads((run / "experiments" / name / "evidence.json").read_text())
+        assert evidence["state"] == "completed" and evidence["training_summary"]["completed_steps"] == 3
+        assert evidence["sections"]["dataset_admission"]["admitted"] > 0
+        assert evidence["plan_id"] == json.loads((run / "experiments" / name / "plan.json").read_text())["plan_id"]
+        assert (run / "experiments" / name / "config.yaml").exists()
+        assert train_entry.main(["--report", str(run / "experiments" / name), "--report-format", "json"]) == 0
+        assert json.loads(capsys.readouterr().out)["valid"]
+    session = json.loads((run / "evidence.json").read_text())
+    assert session["schema_version"] == "aspec.multi-draft-evidence/v1" and session["state"] == "completed"
+    assert {n: e["state"] for n, e in session["experiments"].items()} == {"spark": "completed", "flash": "completed"}
+    assert session["plan_id"] == json.loads((run / "multi-draft-plan.json").read_text())["plan_id"]
+    assert session["shared_source"]["rows_shared"] == 6
 
 
 @pytest.mark.timeout(600)
