@@ -367,6 +367,23 @@ def run_multi_draft_from_config(config: Config, dry_run: bool = False) -> int:
         recorders[name] = RunEvidenceRecorder(plan.plans[name], out_dir)
         session["experiments"][name] = {"state": "running", "plan_id": plan.plans[name].plan_id, "output_dir": out_dir}
     persist_session()
+    # node preflight for the whole session: the Draft GPUs of all experiments plus the shared Target pool
+    from aspec_b200.preflight import run_cluster_preflight
+    first = plan.plans[plan.names[0]].to_runtime_args()
+    pre = run_cluster_preflight(dict(first, world_size=sum(int(p.runtime_args["world_size"]) for p in plan.plans.values()),
+                                     output_dir=config.output_dir))
+    with open(os.path.join(config.output_dir, "cluster-preflight.json"), "w") as f:
+        json.dump(pre, f, indent=2, default=str)
+    for rec in recorders.values():
+        rec.record_cluster_preflight(pre)
+    if pre.get("state") == "failed":
+        exc = RuntimeError(f"node preflight failed: {pre['problems']} (details in cluster-preflight.json)")
+        for name, rec in recorders.items():
+            rec.fail(exc)
+            session["experiments"][name]["state"] = "failed"
+        session.update(state="failed", finished_at=time.time(), failure=str(exc))
+        persist_session()
+        raise exc
     from aspec_b200.utils.logging import Trackers
     trackers: Dict[str, Trackers] = {}
 

@@ -114,6 +114,7 @@ def test_multi_draft_from_the_command_line_writes_per_experiment_metrics(tmp_pat
     assert {n: e["state"] for n, e in session["experiments"].items()} == {"spark": "completed", "flash": "completed"}
     assert session["plan_id"] == json.loads((run / "multi-draft-plan.json").read_text())["plan_id"]
     assert session["shared_source"]["rows_shared"] == 6
+    assert json.loads((run / "cluster-preflight.json").read_text())["required_gpus"] == 2        # one Draft GPU per experiment
 
 
 @pytest.mark.timeout(600)
