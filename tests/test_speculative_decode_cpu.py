@@ -144,3 +144,11 @@ def test_sequences_get_query_tiles_of_their_own_without_changing_the_result():
             padded.accept(r, t.numel())
     from aspec_b200.ops.attention_sm100 import positions_per_tile
     assert positions_per_tile(32, 8) == 32 and positions_per_tile(8, 8) == 128 and positions_per_tile(40, 8) is None
+
+
+def test_the_decode_benchmark_runs_on_a_toy_shape(capsys):
+    from tools.performance import bench_decode
+    res = bench_decode.main(["--small", "--device", "cpu"])
+    capsys.readouterr()
+    assert res["generated_tokens"] == res["sequences"] * res["new_tokens"] and res["target_passes"] == res["new_tokens"]
+    assert res["generated_tokens_per_s"] > 0 and res["tokens_per_pass_per_sequence"] == 1.0
