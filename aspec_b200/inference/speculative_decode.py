@@ -95,15 +95,38 @@ def filter_logits(logits: torch.Tensor, temperature: float, top_k: int, top_p: f
     return x
 
 
+def _wrap64(value: int) -> int:
+    """A 64-bit constant as the signed integer an int64 tensor holds."""
+    value &= (1 << 64) - 1
+    return value - (1 << 64) if value >= 1 << 63 else value
+
+
+def keyed_uniform(seed: int, positions: torch.Tensor, width: int) -> torch.Tensor:
+    """Uniform numbers in (0, 1), ``[len(positions), width]``, that are a pure function of ``(seed, position, column)``:
+    a counter-based generator (the SplitMix64 finaliser over ``seed``, position and column, in wrapping int64
+    arithmetic).  A token position therefore meets the same noise whenever and with whatever neighbours it is drawn - in
+    a verify pass over a Draft block, one token at a time, before or after a restart."""
+    dev = positions.device
+    col = torch.arange(width, device=dev, dtype=torch.int64)[None]
+    z = col * _wrap64(0x9E3779B97F4A7C15) + (positions.to(torch.int64)[:, None] + 1) * _wrap64(0xD1B54A32D192ED03) \
+        + _wrap64(int(seed) * 0x2545F4914F6CDD1D + 0x632BE59BD9B4E019)
+    for shift, mult in ((30, 0xBF58476D1CE4E5B9), (27, 0x94D049BB133111EB)):
+        z = (z ^ ((z >> shift) & ((1 << (64 - shift)) - 1))) * _wrap64(mult)
+    z = z ^ ((z >> 31) & ((1 << 33) - 1))
+    top = (z >> 40) & ((1 << 24) - 1)                         # 24 high bits: exactly representable in float32
+    return (top.to(torch.float32) + 0.5) / float(1 << 24)
+
+
 def sample_tokens(logits: torch.Tensor, temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0,
-                  generator: Optional[torch.Generator] = None) -> torch.Tensor:
-    """One token per row of ``logits [m, V]``.  Sampling is Gumbel-max on the filtered log-weights with noise from
-    ``generator``: the m draws of a call are independent, and a sequence that owns its generator samples the same text
-    whichever other sequences share its passes."""
+                  seed: int = 0, first_position: int = 0) -> torch.Tensor:
+    """One token per row of ``logits [m, V]``; row ``i`` is the sequence's new token number ``first_position + i``.
+    Sampling is Gumbel-max on the filtered log-weights with noise keyed by ``(seed, token number)``: what a sequence
+    samples at a position depends on its logits there and on nothing else."""
     x = filter_logits(logits, temperature, top_k, top_p)
     if temperature <= 0:
         return x.argmax(-1)
-    u = torch.rand(x.shape, generator=generator, device=x.device, dtype=torch.float32).clamp_(1e-20, 1.0)
+    positions = torch.arange(first_position, first_position + x.shape[0], device=x.device)
+    u = keyed_uniform(seed, positions, x.shape[-1])
     return (x - torch.log(-torch.log(u))).argmax(-1)
 
 
@@ -116,10 +139,10 @@ def batched_generate(target, prompts: Sequence[torch.Tensor], *, max_new_tokens:
 
     With ``consumer`` (a ``draft_artifact.BlockDraftConsumer``) a pass verifies a Draft block per sequence: the Target's
     token is drawn at every proposed position, the proposal is accepted as long as it equals those draws, and the first
-    draw that differs is kept - every kept token is a draw from the Target's distribution given its prefix, so the text
-    is distributed exactly as without a Draft (and is identical for greedy decoding); the Draft only changes how many
-    tokens a pass yields.  Stop tokens are masked out until ``min_new_tokens`` tokens exist.  ``seeds[r]`` seeds sequence
-    ``r``'s own noise generator.
+    draw that differs is kept - every kept token is a draw from the Target's distribution given its prefix, and the noise
+    of a draw is keyed by the sequence's seed and the token's number (``sample_tokens``), so the text is THE SAME with any
+    Draft, with none, and in any batch; the Draft only changes how many tokens a pass yields.  Stop tokens are masked out
+    until ``min_new_tokens`` tokens exist.  ``seeds[r]`` is sequence ``r``'s noise seed.
 
     Returns per sequence ``{"tokens", "target_passes", "accepted_per_round", "stopped"}``."""
     dev = target.lm_head.device
@@ -130,11 +153,7 @@ def batched_generate(target, prompts: Sequence[torch.Tensor], *, max_new_tokens:
     budget = [int(m) for m in max_new_tokens]
     capacity = max(int(p.numel()) + b for p, b in zip(prompts, budget)) + block
     cache = target.new_decode_cache(R, capacity)
-    gens = []
-    for r in range(R):
-        g = torch.Generator(device=dev)
-        g.manual_seed(int(seeds[r]) if seeds is not None else r)
-        gens.append(g)
+    noise_seeds = [int(seeds[r]) if seeds is not None else r for r in range(R)]
     stops = [int(t) for t in (stop_token_ids or ())]
     # ranks of a tensor-parallel Target take rank 0's draws and proposals, so that all of them run the same passes
     agree = getattr(target, "agree", lambda t: t)
@@ -153,7 +172,7 @@ def batched_generate(target, prompts: Sequence[torch.Tensor], *, max_new_tokens:
             for i in range(logits.shape[0]):
                 if already + i < min_new_tokens:
                     logits[i, stops] = float("-inf")
-        return agree(sample_tokens(logits, temperature, top_k, top_p, gens[r])).tolist()
+        return agree(sample_tokens(logits, temperature, top_k, top_p, noise_seeds[r], already)).tolist()
 
     def keep(r: int, new: List[int]) -> None:
         room = budget[r] - (len(seqs[r]) - n0[r])

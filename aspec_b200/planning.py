@@ -92,7 +92,8 @@ def estimate_memory(draft: dict, flat: Dict[str, Any], algorithm: str, shard: in
     frozen = 2 * V * D
     rows = int(flat.get("dspark_num_anchors", 512)) * int(flat.get("dspark_block_size", 7))
     logits = 2 * rows * V * 2
-    slot = int(flat["max_seq_length"]) * (n_tl + 1) * Dt * 2 + int(flat["max_seq_length"]) * 8
+    row_tokens = int(flat["max_seq_length"]) * (1 if flat.get("dflash_packing") else max(int(flat.get("micro_batch_size", 1)), 1))
+    slot = row_tokens * (n_tl + 1) * Dt * 2 + row_tokens * 8
     ring = slot * int(flat.get("transport_destination_ring_slots", 1))
     shard = max(shard, 1)
     strategy = str(strategy).upper()

@@ -128,7 +128,9 @@ class TrainerActor:
             if r > 1:
                 self.model.draft_model.ring = (idx // u, r, ring_group)
             self.model.sequence_parallel = (idx, self.sp_size, mine)
-        layout = SlotLayout(int(self.args["max_seq_length"]), int(getattr(cfg, "num_target_layers", None)
+        # a row holds one packed row of at most ``max_seq_length`` tokens, or ``micro_batch_size`` whole documents
+        row_tokens = int(self.args["max_seq_length"]) * (1 if self.args.get("dflash_packing") else max(int(self.args.get("micro_batch_size", 1)), 1))
+        layout = SlotLayout(row_tokens, int(getattr(cfg, "num_target_layers", None)
                                                                    or getattr(cfg, "num_aux_hidden_states", 3)),
                             int(getattr(cfg, "target_hidden_size", cfg.hidden_size)),
                             bool(self.args.get("store_last_hidden_states", True)),

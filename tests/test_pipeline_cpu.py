@@ -231,3 +231,17 @@ def test_rows_dispatched_several_updates_ahead(tmp_path):
     summary = train_async_no_generation(flat, plan.draft_config, log=lambda m: None)
     assert summary["completed_steps"] == 5 and summary["ledger"]["validated"]
     assert len(summary["ledger"]["committed_work_ids"]) == 5 * 2 * 2
+
+
+@pytest.mark.timeout(300)
+def test_unpacked_rows_of_several_documents_fit_their_ring_slot(tmp_path):
+    """``micro_batch_size`` whole documents per row, each up to ``max_seq_length``: the slot is sized for all of them."""
+    plan = _plan(tmp_path, ("training.micro_batch_size=2", "training.max_seq_length=100", "dataset.synthetic_min_length=70",
+                            "dataset.synthetic_max_length=100", "training.num_train_steps=2", "training.training_num_gpus_per_node=1"))
+    flat = plan.to_runtime_args()
+    flat.update(synthetic_vocab_size=500, force_cpu=True, save_interval=0, save_final_checkpoint=False)
+    os.makedirs(flat["output_dir"], exist_ok=True)
+    logs = []
+    summary = train_async_no_generation(flat, plan.draft_config, log=logs.append)
+    assert summary["completed_steps"] == 2 and summary["ledger"]["validated"]
+    assert all(l["perf/input_tokens"] > 2 * 2 * 70 for l in logs)                # 2 micro-batches x 2 documents of >= 70 tokens

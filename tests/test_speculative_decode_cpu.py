@@ -102,6 +102,10 @@ def test_batched_generation_is_the_targets_text_with_or_without_a_draft(kind):
     both = batched_generate(target, prompts[:2], max_new_tokens=[8, 8], seeds=[21, 22], **kw)
     alone = batched_generate(target, prompts[1:2], max_new_tokens=[8], seeds=[22], **kw)
     assert both[1]["tokens"] == alone[0]["tokens"] and len(both[0]["tokens"]) == 8
+    # ... nor to the Draft that proposed (or to having one at all): the noise of a draw is keyed by seed and position
+    no_draft = batched_generate(target, prompts[:2], max_new_tokens=[8, 8], seeds=[21, 22], **{**kw, "consumer": None, "layer_ids": ()})
+    assert [g["tokens"] for g in no_draft] == [g["tokens"] for g in both]
+    assert both[0]["tokens"] != batched_generate(target, prompts[:1], max_new_tokens=[8], seeds=[23], **kw)[0]["tokens"]
 
 
 def test_stop_tokens_wait_for_the_minimum_length_and_filters_keep_the_head_of_the_distribution():
@@ -152,3 +156,16 @@ def test_the_decode_benchmark_runs_on_a_toy_shape(capsys):
     capsys.readouterr()
     assert res["generated_tokens"] == res["sequences"] * res["new_tokens"] and res["target_passes"] == res["new_tokens"]
     assert res["generated_tokens_per_s"] > 0 and res["tokens_per_pass_per_sequence"] == 1.0
+
+
+def test_keyed_noise_is_uniform_and_a_function_of_seed_position_and_column():
+    from aspec_b200.inference.speculative_decode import keyed_uniform
+    u = keyed_uniform(7, torch.arange(32), 40000)
+    assert 0.0 < float(u.min()) and float(u.max()) < 1.0
+    assert abs(float(u.mean()) - 0.5) < 2e-3 and abs(float(u.var()) - 1 / 12) < 1e-3
+    share = torch.histc(u.flatten(), bins=16, min=0, max=1) / u.numel()
+    assert float(share.min()) > 0.06 and float(share.max()) < 0.065
+    assert abs(float(torch.corrcoef(torch.stack([u[0], u[1]]))[0, 1])) < 0.02            # neighbouring positions
+    assert abs(float(torch.corrcoef(torch.stack([u[0, :-1], u[0, 1:]]))[0, 1])) < 0.02    # neighbouring columns
+    assert abs(float(torch.corrcoef(torch.stack([u[3], keyed_uniform(8, torch.tensor([3]), 40000)[0]]))[0, 1])) < 0.02
+    assert torch.equal(keyed_uniform(7, torch.tensor([3, 9]), 100), u[[3, 9], :100])      # any subset, any order of asking

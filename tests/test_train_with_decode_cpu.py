@@ -2,6 +2,7 @@
 verifying blocks of the live Draft after a weight sync), and the Draft trains on what was written (reference:
 aspec/inference/engine/sgl_engine_decode.py:39-424, aspec/train_entry.py:330-338)."""
 import json
+import os
 
 import pytest
 import torch
@@ -117,3 +118,23 @@ def test_a_run_decodes_its_own_responses_syncs_weights_and_repeats_exactly(tmp_p
     assert [s["perf/input_tokens"] for s in sharded] == [s["perf/input_tokens"] for s in steps]
     assert [s["train/avg_loss"] for s in sharded] == pytest.approx([s["train/avg_loss"] for s in steps], rel=1e-4)
     assert len(ev["training_summary"]["engines"]) == 1 and ev["sections"]["actor_initialization"]["inference_engine_count"] == 2
+
+
+@pytest.mark.timeout(900)
+def test_a_decoding_run_resumes_exactly_whatever_draft_its_engines_hold(tmp_path):
+    """Interrupted after update 2 and resumed: the engines of the resumed run start without a Draft while those of the
+    uninterrupted run verify blocks of the synced one, yet both write the same text (noise keyed by seed and token
+    number) and end in the same checkpoint, section by section.  One document per Target call, so that the live Target's
+    products do not depend on what else shared the call."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = tmp_path / "r.yaml"
+    path.write_text(RECIPE)
+    out = subprocess.run([sys.executable, "-m", "tools.validation.resume_replay", "--config", str(path), "--steps", "4", "--at", "2",
+                          "--out", str(tmp_path / "rr"), "inference.inference_batch_size=1", "training.micro_batch_size=1",
+                          "training.draft_accumulation_steps=4"], cwd=root, capture_output=True, text=True, timeout=800,
+                         env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert out.returncode == 0, out.stdout[-1500:] + out.stderr[-1500:]
+    verdict = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert verdict["exact"] and verdict["differing_sections"] == []
