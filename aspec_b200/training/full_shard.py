@@ -409,14 +409,17 @@ class FullShardOptimizer(_AppliedSteps):
         for u in self.units[:-1]:
             if any(p.grad is not None for p in u.params):
                 raise RuntimeError(f"layer {u.index} received a gradient after its reduce-scatter had started")
-        if self._root_open:
-            self._fold(self.root)
-            self._reduce(self.root)
-            self._root_open = False
+        # the root takes part in every micro-batch, also when no wrapped layer ran before it (a Draft whose decoder is not
+        # a ``layers`` list lives in the root whole): its buffer is cleared here, before its gradients are folded in
+        if not self._root_open:
+            self._open_grad_buffer(self.root)
+        self._fold(self.root)
+        self._reduce(self.root)
+        self._root_open = False
 
     # ---- the optimizer contract -----------------------------------------------------------------------------------
     def fold_autograd_grads(self) -> None:
-        if self._root_open or self._touched:
+        if self._root_open or self._touched or any(p.grad is not None for p in self.root.params):
             self.finish_micro_batch()
 
     def set_grad_scale(self, scale) -> None:

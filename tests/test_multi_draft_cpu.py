@@ -174,8 +174,14 @@ output_dir: {tmp_path / 'run'}
     plan = compile_multi_draft_plan(load_config(str(recipe)))
     for p in plan.plans.values():
         p.runtime_args.update(synthetic_vocab_size=500, force_cpu=True)
-    out = run_multi_draft(plan, log=lambda m: None)
+    logs = []
+    out = run_multi_draft(plan, log=logs.append)
     assert all(out[n].get("completed_steps") == 2 for n in ("spark", "eagle", "flash")), out
+    # every Draft really trains: gradients reach the sharded optimizer of each family (the EAGLE3 Draft has no ``layers``
+    # list and lives in the root unit whole)
+    for n in ("spark", "eagle", "flash"):
+        norms = [m["train/grad_norm"] for m in logs if m.get("experiment") == n and "train/grad_norm" in m]
+        assert len(norms) == 2 and all(g > 0 for g in norms), (n, norms)
     assert out["shared_source"]["fenced"] == {} and out["shared_source"]["rows_shared"] == 2 * 2 * 2
     assert out["spark"]["ledger"]["committed_work_ids"] == out["eagle"]["ledger"]["committed_work_ids"]
 
