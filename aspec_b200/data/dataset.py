@@ -19,7 +19,7 @@ from aspec_b200.data.preprocessing import preprocess_conversations
 from aspec_b200.data.template import TEMPLATE_REGISTRY
 from aspec_b200.data.utils import pack_loss_mask
 
-PARSER_VERSION = "1"
+PARSER_VERSION = "2"          # 2: every sample carries its data_id
 
 
 def _file_digest(path: str) -> str:
@@ -53,8 +53,17 @@ def _from_pretokenized(rows: List[dict], max_length: int) -> List[dict]:
             if mask.numel() != ids.numel():
                 raise ValueError(f"row {i}: loss_mask and input_ids differ in length")
             packed = pack_loss_mask(mask)
-        out.append({"input_ids": ids, "packed_loss_mask": packed, **({"data_id": str(r["data_id"])} if "data_id" in r else {})})
+        out.append({"input_ids": ids, "packed_loss_mask": packed, "data_id": row_identity(r, i)})
     return out
+
+
+def row_identity(row: dict, index: int) -> str:
+    """A document's identity in ledgers, feature stores and seeds: the row's own ``data_id`` / ``id`` when it has one, else
+    its place in the file."""
+    for key in ("data_id", "id"):
+        if row.get(key) not in (None, ""):
+            return str(row[key])
+    return str(index)
 
 
 def preprocessing_identity(path: str, args: Mapping[str, Any]) -> str:
@@ -78,6 +87,8 @@ def load_training_samples(path: str, args: Mapping[str, Any], tokenizer=None, re
     rows = read_rows(path)
     if is_pretokenized(rows):
         samples = _from_pretokenized(rows, max_length)
+        if len({s["data_id"] for s in samples}) != len(samples):
+            raise ValueError(f"{path}: two documents share one id; ids (data_id / id) must be unique")
         if report is not None:
             report.update({"seen": len(rows), "admitted": len(samples), "pretokenized": True})
         return samples
@@ -96,16 +107,21 @@ def load_training_samples(path: str, args: Mapping[str, Any], tokenizer=None, re
         from aspec_b200.data.renderers import RENDERER_REGISTRY
         renderer = RENDERER_REGISTRY.create(args["renderer"], tokenizer)
         samples = []
-        for r in rows:
+        for index, r in enumerate(rows):
             ids, mask = renderer.render(r.get("messages") or r.get("conversations"), tools=r.get("tools"),
                                         max_seq_length=max_length, last_turn_only=bool(args.get("last_turn_loss_only", False)))
             if int(mask.sum()):
-                samples.append({"input_ids": ids, "packed_loss_mask": pack_loss_mask(mask)})
+                samples.append({"input_ids": ids, "packed_loss_mask": pack_loss_mask(mask), "source_index": index})
         stats = {"seen": len(rows), "admitted": len(samples), "renderer": args["renderer"]}
     else:
         parser = create_parser(tokenizer, TEMPLATE_REGISTRY.get(args.get("chat_template") or "qwen"))
         samples = preprocess_conversations(parser, (r.get("conversations") or r.get("messages") or [] for r in rows), max_length,
                                            args.get("last_turn_loss_only"), stats)
+    for s in samples:                       # every document is named after its source row
+        idx = int(s.pop("source_index"))
+        s["data_id"] = row_identity(rows[idx], idx)
+    if len({s["data_id"] for s in samples}) != len(samples):
+        raise ValueError(f"{path}: two documents share one id; ids (data_id / id) must be unique")
     if cache_file:
         os.makedirs(os.path.dirname(cache_file), exist_ok=True)
         tmp = cache_file + ".tmp"

@@ -14,7 +14,8 @@ from aspec_b200.models.vocab import build_vocab_mapping
 
 def preprocess_conversations(parser: Parser, conversations: Iterable[Sequence[Dict[str, Any]]], max_length: int,
                              last_turn_loss_only: Optional[bool] = None, report: Optional[dict] = None) -> List[dict]:
-    """One record per admitted conversation: ``{"input_ids", "packed_loss_mask"}``.
+    """One record per admitted conversation: ``{"input_ids", "packed_loss_mask", "source_index"}`` (its place in the
+    input, so that the caller can name it after its source row).
 
     ``last_turn_loss_only=None`` decides per conversation: reasoning traces are only reproducible for the final
     turn (history turns lose their ``<think>`` blocks), so conversations with reasoning supervise the last turn.
@@ -42,7 +43,7 @@ def preprocess_conversations(parser: Parser, conversations: Iterable[Sequence[Di
             continue
         stats["admitted"] += 1
         stats["last_turn_only"] += int(last_only)
-        out.append({"input_ids": ids, "packed_loss_mask": pack_loss_mask(mask)})
+        out.append({"input_ids": ids, "packed_loss_mask": pack_loss_mask(mask), "source_index": stats["seen"] - 1})
     if report is not None:
         report.update(dict(stats))
     return out

@@ -311,7 +311,15 @@ class OfflineReplayEngine(InferenceEngine):
             views = self._slot_views(req)
             off = 0
             for data_id, n in zip(req.data_ids, req.document_lengths):
-                rec = self.store.load(data_id)
+                try:
+                    rec = self.store.load(data_id)
+                except KeyError:
+                    raise KeyError(f"document {data_id!r} of the training data has no stored features in {self.store.root}: the "
+                                   "store was made from other documents (or from the same file before its documents had "
+                                   "ids); prepare it again from this training file") from None
+                if int(rec["input_ids"].numel()) != int(n):
+                    raise ValueError(f"document {data_id!r}: the store holds {int(rec['input_ids'].numel())} tokens, the training "
+                                     f"data {int(n)} (another max_seq_length or tokenizer?)")
                 last = rec.get("last_hidden_states")
                 self._copy_features(req, views, rec["hidden_states"].reshape(n, -1),
                                     None if last is None else last.reshape(n, -1), slice(off, off + n))

@@ -79,6 +79,22 @@ def test_dataset_loader_cache_renderer_and_vocab_mapping(tmp_path):
     pre = tmp_path / "pre.jsonl"
     pre.write_text(json.dumps({"input_ids": [1, 2, 3, 4], "loss_mask": [0, 0, 1, 1]}) + "\n")
     assert load_training_samples(str(pre), {"max_seq_length": 8})[0]["packed_loss_mask"] == "2,2"
+    # every document has an identity (ledgers, feature stores and seeds key on it): its own id, else its place in the file
+    assert [s["data_id"] for s in samples] == ["0", "1", "2"] and [s["data_id"] for s in again] == ["0", "1", "2"]
+    assert [s["data_id"] for s in rendered] == ["0", "1", "2"]
+    named = tmp_path / "named.jsonl"
+    named.write_text("\n".join([json.dumps({"id": "a7", "conversations": CONV}), json.dumps({"conversations": CONV[:1]}),
+                                json.dumps({"data_id": 12, "conversations": CONV})]))
+    assert [s["data_id"] for s in load_training_samples(str(named), args, tokenizer=Tok())] == ["a7", "12"]   # row 1 has no reply
+    pre.write_text("\n".join(json.dumps({"id": i, "input_ids": [1, 2, 3], "loss_mask": [0, 1, 1]}) for i in ("x", "y")))
+    assert [s["data_id"] for s in load_training_samples(str(pre), {"max_seq_length": 8})] == ["x", "y"]
+    pre.write_text("\n".join(json.dumps({"id": i, "input_ids": [1, 2, 3], "loss_mask": [0, 1, 1]}) for i in ("x", "y", "x")))
+    with pytest.raises(ValueError, match="share one id"):
+        load_training_samples(str(pre), {"max_seq_length": 8})
+    dup = tmp_path / "dup.jsonl"
+    dup.write_text("\n".join(json.dumps({"id": "same", "conversations": CONV}) for _ in range(2)))
+    with pytest.raises(ValueError, match="share one id"):
+        load_training_samples(str(dup), {"max_seq_length": 512, "chat_template": "qwen"}, tokenizer=Tok())
 
 
 def test_native_assistant_span_scan():
