@@ -39,6 +39,7 @@ class DatasetConfig:
     eval_micro_batch_size: Optional[int] = None
     eval_prompt_key: Optional[str] = None
     last_turn_loss_only: Any = "auto"
+    tokenizer_path: Optional[str] = None          # directory of a Hugging Face tokenizer; default: model.target_model_path
     length_group_size: int = 32
     min_loss_tokens: int = 0
     prompt_key: str = "conversations"
@@ -314,7 +315,7 @@ class Config:
 
 # ------------------------------------------------------------------ loading -------------------
 _ENV = re.compile(r"\$\{oc\.env:([A-Za-z_][A-Za-z0-9_]*)(?:,([^}]*))?\}")
-_PATH_KEYS = {("model", "draft_model_config"), ("model", "target_model_config"), ("dataset", "train_data_path"),
+_PATH_KEYS = {("model", "draft_model_config"), ("model", "target_model_config"), ("dataset", "train_data_path"), ("dataset", "tokenizer_path"),
               ("dataset", "eval_data_path"), ("training", "load_path"), ("model", "initial_draft_model_path")}
 # `mooncake:` keys of reference recipes that have a transport meaning here
 _MOONCAKE_ALIASES = {"p2p_source_slots": "source_ring_slots", "p2p_destination_slots": "destination_ring_slots",

@@ -2,6 +2,7 @@
 report, export), acceptance evaluation of the exported asset with live and with stored Target features, and the
 corpus preparation commands."""
 import json
+import os
 
 import pytest
 import torch
@@ -343,3 +344,43 @@ def test_required_throughput_measurement(tmp_path, capsys):
     window = json.loads((tmp_path / "long" / "evidence.json").read_text())["training_summary"]["window"]
     assert window["valid"] and window["steps"] == 2 and window["tokens_per_second"] > 0
     capsys.readouterr()
+
+
+def _tiny_tokenizer(path):
+    """A byte-level tokenizer with the chat template's special tokens, saved where ``AutoTokenizer`` finds it offline."""
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    specials = ["<|im_start|>", "<|im_end|>", "<|endoftext|>", "<think>", "</think>"]
+    vocab = {s: i for i, s in enumerate(specials)}
+    for ch in sorted(pre_tokenizers.ByteLevel.alphabet()):
+        vocab[ch] = len(vocab)
+    tok = Tokenizer(models.BPE(vocab=vocab, merges=[]))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    tok.add_special_tokens(specials)
+    PreTrainedTokenizerFast(tokenizer_object=tok, eos_token="<|im_end|>", pad_token="<|endoftext|>").save_pretrained(str(path))
+    return str(path)
+
+
+@pytest.mark.timeout(600)
+def test_training_from_the_bundled_conversation_file(tmp_path, capsys):
+    """Conversations -> chat template -> tokens and assistant masks -> rows -> updates, through the command line; every
+    document is named after its row's ``id`` in the ledger."""
+    from aspec_b200 import assets, train_entry
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    data = os.path.join(root, "examples", "data", "sample_conversations.jsonl")
+    common = ["--config", assets.find_asset("quickstart_tiny.yaml"), f"dataset.train_data_path={data}",
+              f"dataset.tokenizer_path={_tiny_tokenizer(tmp_path / 'tok')}", "dataset.chat_template=qwen", "training.max_seq_length=700",
+              "training.num_train_steps=2", "training.save_final_checkpoint=false"]
+    assert train_entry.main([*common, f"output_dir={tmp_path / 'run'}"]) == 0
+    evidence = json.loads((tmp_path / "run" / "evidence.json").read_text())
+    adm = evidence["sections"]["dataset_admission"]
+    assert evidence["state"] == "completed" and adm["admitted"] == adm["source_rows"] > 0 and not adm["rejected"]
+    assert evidence["training_summary"]["ledger"]["validated"]
+    # the same file, but the Target writes the final replies itself (stops at the end-of-turn token)
+    assert train_entry.main([*common, "inference.inference_engine_type=native", "inference.inference_num_gpus=1",
+                             "training.train_with_decode=true", "decode.max_new_tokens=12", "decode.stop_token_ids=[1]",
+                             f"output_dir={tmp_path / 'decode'}"]) == 0
+    capsys.readouterr()
+    rows = [json.loads(l) for l in open(tmp_path / "decode" / "runs" / "metrics.jsonl")]
+    assert all(0 < r["decode/generated_tokens"] <= 4 * 12 for r in rows if "decode/generated_tokens" in r)
