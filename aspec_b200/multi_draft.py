@@ -25,7 +25,7 @@ from aspec_b200.planning import ExecutionPlan, compile_execution_plan
 
 # what every experiment must share so that all of them plan identical rows
 _SHARED_ROW_KEYS = ("train_data_path", "max_seq_length", "micro_batch_size", "draft_accumulation_steps", "dflash_packing",
-                    "seed", "dataset_seed", "num_epochs", "draft_context_parallel_size", "world_size",
+                    "seed", "dataset_seed", "num_epochs",
                     "synthetic_num_documents", "synthetic_min_length", "synthetic_max_length", "synthetic_vocab_size",
                     # held-out rows are produced once and read by all experiments, at the same updates
                     "eval_data_path", "eval_interval", "eval_num_documents")
@@ -101,6 +101,12 @@ def compile_multi_draft_plan(config: Config) -> MultiDraftPlan:
             if plans[n].runtime_args.get(key) != first.get(key):
                 raise ValueError(f"experiments that share a Target must agree on {key}: "
                                  f"{names[0]}={first.get(key)!r}, {n}={plans[n].runtime_args.get(key)!r}")
+    # rows are dealt to data-parallel ranks: experiments may shard their rows over different context-parallel degrees (each
+    # reads its own views of the one stored row), but all of them must have the same number of data-parallel ranks
+    widths = {n: int(plans[n].policy.get("dp_size") or 1) for n in names}
+    if len(set(widths.values())) > 1:
+        raise ValueError("experiments that share a Target must have the same number of data-parallel ranks "
+                         f"(world size / context-parallel size): {widths}")
     union = shared_feature_union([_contract(plans[n].draft_config) for n in names])
     offsets, at = {}, 0
     for n in names:

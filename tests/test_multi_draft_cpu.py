@@ -276,3 +276,22 @@ def test_experiments_evaluate_on_held_out_rows_that_the_target_produces_once(tmp
     other.write_text(recipe_text.replace("  - name: flash\n", "  - name: flash\n    dataset:\n      eval_interval: 3\n"))
     with pytest.raises(ValueError, match="must agree on eval_interval"):
         compile_multi_draft_plan(load_config(str(other)))
+
+
+@pytest.mark.timeout(600)
+def test_experiments_may_shard_the_shared_rows_over_different_context_parallel_degrees(tmp_path):
+    """One experiment reads whole rows on one rank, the other shards every row over two context-parallel ranks: both
+    have one data-parallel rank, so they plan the same rows; a different data-parallel width is refused."""
+    cp2 = "    training:\n      training_num_gpus_per_node: 2\n      draft_context_parallel_size: 2"
+    plan = _plan(tmp_path, second_extra=cp2)
+    assert plan.consumer_offsets == {"spark": 0, "flash": 1}
+    for p in plan.plans.values():
+        p.runtime_args.update(deterministic_anchor_sampling=True, transport_destination_ring_slots=5)
+    logs = []
+    out = run_multi_draft(plan, log=logs.append)
+    assert out["spark"]["completed_steps"] == out["flash"]["completed_steps"] == 3
+    assert out["spark"]["ledger"]["committed_work_ids"] == out["flash"]["ledger"]["committed_work_ids"]
+    assert out["shared_source"]["rows_shared"] == 3 * 2 and out["shared_source"]["fenced"] == {}
+    assert all(m["train/grad_norm"] > 0 for m in logs if "train/grad_norm" in m)
+    with pytest.raises(ValueError, match="same number of data-parallel ranks"):
+        _plan(tmp_path, second_extra="    training:\n      training_num_gpus_per_node: 2")
