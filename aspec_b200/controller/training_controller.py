@@ -224,6 +224,7 @@ class TrainingController:
                       # a document's noise depends on the document, the epoch and the run's seed - not on its row or engine
                       "seeds": [zlib.crc32(f"{d['data_id']}|{self.epoch}".encode()) ^ seed for d in docs],
                       "min_new_tokens": int(a.get("decode_min_new_tokens", 2)), "stop_token_ids": list(a.get("decode_stop_token_ids") or ()),
+                      "max_running_requests": a.get("decode_max_running_requests"),
                       "temperature": float(a.get("decode_temperature", 1.0)), "top_k": int(a.get("decode_top_k", -1)),
                       "top_p": float(a.get("decode_top_p", 1.0))}
         return RowRequest(row_id=f"row-{self.epoch}-{self.rows_planned}", data_ids=[d["data_id"] for d in docs],

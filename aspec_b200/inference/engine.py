@@ -182,10 +182,22 @@ class NativeTargetEngine(InferenceEngine):
                 off += n
         d = requests[0].decode
         consumer = getattr(self, "draft", None)
-        res = batched_generate(self.model, prompts, max_new_tokens=budgets, min_new_tokens=int(d.get("min_new_tokens", 0)),
-                               stop_token_ids=d.get("stop_token_ids") or (), temperature=float(d.get("temperature", 1.0)),
-                               top_k=int(d.get("top_k", -1)), top_p=float(d.get("top_p", 1.0)), seeds=seeds, consumer=consumer,
-                               layer_ids=getattr(self, "draft_layers", ()))
+        # documents decoded together share every Target pass but each holds its keys and values for its whole reserved
+        # length: ``decode.max_running_requests`` and a byte budget for the cache bound how many run at once (a document's
+        # text does not depend on which others it ran with)
+        cfg = self.model.config
+        row_bytes = 2 * cfg.num_hidden_layers * self.model.layers[0].hk * cfg.head_dim * self.model.lm_head.element_size()
+        longest = max(int(p.numel()) + b for p, b in zip(prompts, budgets)) + 16
+        fit = max(int(float(d.get("cache_budget_bytes") or 24 * 2 ** 30) // max(row_bytes * longest, 1)), 1)
+        wave = max(min(fit, int(d.get("max_running_requests") or len(prompts)), len(prompts)), 1)
+        res = []
+        for lo in range(0, len(prompts), wave):
+            res += batched_generate(self.model, prompts[lo:lo + wave], max_new_tokens=budgets[lo:lo + wave],
+                                    min_new_tokens=int(d.get("min_new_tokens", 0)), stop_token_ids=d.get("stop_token_ids") or (),
+                                    temperature=float(d.get("temperature", 1.0)), top_k=int(d.get("top_k", -1)),
+                                    top_p=float(d.get("top_p", 1.0)), seeds=seeds[lo:lo + wave], consumer=consumer,
+                                    layer_ids=getattr(self, "draft_layers", ()))
+        self.decode_waves = getattr(self, "decode_waves", 0) + -(-len(prompts) // wave)
         out, i = [], 0
         for req in requests:
             ids, lengths, masks = [], [], []
@@ -216,6 +228,7 @@ class NativeTargetEngine(InferenceEngine):
             st["decode"] = {k: getattr(self, "decode_" + k, 0) for k in
                             ("generated_tokens", "target_passes", "accepted_draft_tokens", "verify_rounds")}
             st["decode"]["draft_loads"] = getattr(self, "draft_loads", 0)
+            st["decode"]["waves"] = getattr(self, "decode_waves", 0)
         return st
 
     @torch.no_grad()

@@ -109,8 +109,10 @@ def test_a_run_decodes_its_own_responses_syncs_weights_and_repeats_exactly(tmp_p
     # the Target decodes alone until the first sync and verifies Draft blocks afterwards
     assert "decode/accepted_draft_tokens_per_round" not in steps[0] and engine["verify_rounds"] > 0
     assert (tmp_path / "a" / "decode_draft" / "export_manifest.json").exists()
-    # the text a document gets depends on the document and the seed alone: a second run repeats the first
-    again, _ = run("b")
+    # the text a document gets depends on the document and the seed alone: a second run repeats the first, also when
+    # its engine decodes the documents of a call one at a time
+    again, ev_b = run("b", "decode.max_running_requests=1")
+    assert ev_b["training_summary"]["engines"][0]["decode"]["waves"] == 16
     assert [s["train/avg_loss"] for s in again] == pytest.approx([s["train/avg_loss"] for s in steps], rel=1e-6)
     assert [s["perf/input_tokens"] for s in again] == [s["perf/input_tokens"] for s in steps]
     # a Target engine spread over two tensor-parallel ranks writes the same text and features
