@@ -190,7 +190,7 @@ def training_loop(*, controller, manager, trainers, rings, train_queues, args: D
             save_checkpoint(trainers, controller, output_dir, next_step_id, args)
             last_saved = next_step_id
         if sync_every and next_step_id % sync_every == 0:
-            sync_draft_weights(trainers, manager.engines, os.path.join(output_dir, "decode_draft"), args)
+            sync_draft_weights(trainers, manager.engines, os.path.join(output_dir, "scratch_draft_model"), args)
             synced += 1
         if on_step is not None:
             on_step(next_step_id, metrics)          # held-out evaluation, trackers

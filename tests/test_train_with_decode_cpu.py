@@ -108,7 +108,7 @@ def test_a_run_decodes_its_own_responses_syncs_weights_and_repeats_exactly(tmp_p
         assert s["decode/tokens_per_target_pass"] >= 1.0
     # the Target decodes alone until the first sync and verifies Draft blocks afterwards
     assert "decode/accepted_draft_tokens_per_round" not in steps[0] and engine["verify_rounds"] > 0
-    assert (tmp_path / "a" / "decode_draft" / "export_manifest.json").exists()
+    assert (tmp_path / "a" / "scratch_draft_model" / "export_manifest.json").exists()
     # the text a document gets depends on the document and the seed alone: a second run repeats the first, also when
     # its engine decodes the documents of a call one at a time
     again, ev_b = run("b", "decode.max_running_requests=1")
