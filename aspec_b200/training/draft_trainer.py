@@ -16,6 +16,7 @@ performs the single device->host read of an update.
 """
 from __future__ import annotations
 
+import time
 from typing import Dict, Iterable, List, Optional
 
 import torch
@@ -30,6 +31,42 @@ _BATCH_TENSOR_KEYS = ("input_ids", "hidden_states", "loss_mask", "last_hidden_st
 
 # anchors sampled by the data pipeline stay on the host: the block layout is compacted there
 _HOST_KEYS = ("injected_anchors", "injected_keep_mask")
+
+
+class _PhaseClock:
+    """Where an update's time goes, without a host synchronisation of its own: phase boundaries are CUDA events on the
+    compute stream (host clock on the CPU) and are read when the update's metrics are fetched, which synchronises anyway.
+    ``perf/data_time`` is host time spent waiting for rows; the others are device time
+    (reference: the perf/* metrics of aspec/training/trainer.py:118-128)."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.reset()
+
+    def reset(self) -> None:
+        self.spans: List[tuple] = []
+        self.host: Dict[str, float] = {}
+
+    def now(self):
+        if not self.cuda:
+            return time.perf_counter()
+        e = torch.cuda.Event(enable_timing=True)
+        e.record(torch.cuda.current_stream(self.device))
+        return e
+
+    def span(self, name: str, start, end) -> None:
+        self.spans.append((name, start, end))
+
+    def add_host(self, name: str, seconds: float) -> None:
+        self.host[name] = self.host.get(name, 0.0) + seconds
+
+    def totals(self) -> Dict[str, float]:
+        """Seconds per phase; call only after the stream has been synchronised."""
+        out = dict(self.host)
+        for name, a, b in self.spans:
+            out[name] = out.get(name, 0.0) + (a.elapsed_time(b) / 1e3 if self.cuda else b - a)
+        return out
 
 
 class DraftTrainer:
@@ -74,6 +111,7 @@ class DraftTrainer:
         self._pool: Dict[str, List[torch.Tensor]] = {}
         self._last: Dict[str, torch.Tensor] = {}
         self.post_step_hooks = []
+        self.clock = _PhaseClock(self.device)
         self.pre_step_hooks: list = []
         self._copy_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
 
@@ -114,6 +152,7 @@ class DraftTrainer:
 
     # -- one micro-batch ----------------------------------------------------------------
     def _forward_backward(self, batch: dict) -> None:
+        t0 = self.clock.now()
         out = self.model(
             batch["input_ids"], batch["hidden_states"], batch["loss_mask"], self.lm_head_weight,
             last_hidden_states=batch.get("last_hidden_states"), ctx_doc_ids=batch.get("ctx_doc_ids"),
@@ -125,10 +164,13 @@ class DraftTrainer:
             attention_mask=batch.get("attention_mask"))
         loss, acc, loss_pp, acc_pp, count_pp, comps, (num, den) = out
         if num.requires_grad:
+            t1 = self.clock.now()
             num.backward()
             close = getattr(self.optimizer, "finish_micro_batch", None)
             if close is not None:            # FULL_SHARD: the root unit's gradients join the reduce-scatter here
                 close()
+            self.clock.span("forward_time", t0, t1)
+            self.clock.span("backward_time", t1, self.clock.now())
         pool = self._pool
         pool.setdefault("loss", []).append(torch.stack([num.detach().float(), den.float()]))
         pool.setdefault("acc_pp", []).append(torch.stack([acc_pp * count_pp.clamp(min=1.0) * (count_pp > 0), count_pp]))
@@ -145,12 +187,20 @@ class DraftTrainer:
         """Run ``accumulation`` micro-batches and one optimizer step.  No host synchronisation."""
         self.model.train()
         self._pool = {}
+        self.clock.reset()
         n = 0
         it = iter(batches)
-        staged = self._stage(next(it, None))
+
+        def fetch():
+            h0 = time.perf_counter()
+            staged = self._stage(next(it, None))
+            self.clock.add_host("data_time", time.perf_counter() - h0)
+            return staged
+
+        staged = fetch()
         while staged is not None:
             batch, ready = staged
-            staged = self._stage(next(it, None))          # the next micro-batch's copies run under this one's compute
+            staged = fetch()                              # the next micro-batch's copies run under this one's compute
             if ready is not None:
                 torch.cuda.current_stream(self.device).wait_event(ready)
             self._forward_backward(batch)
@@ -158,6 +208,7 @@ class DraftTrainer:
         if n == 0:
             raise ValueError("train_update needs at least one micro-batch")
         opt = self.optimizer
+        t_opt = self.clock.now()
         opt.fold_autograd_grads()
         pooled = {k: torch.stack(v).sum(0) for k, v in self._pool.items()}
         world = dist.get_world_size(self.dp_group) if (dist.is_available() and dist.is_initialized()) else 1
@@ -181,6 +232,7 @@ class DraftTrainer:
         den = pooled["loss"][1]
         opt.set_grad_scale(torch.where(den > 0, 1.0 / den.clamp(min=1e-12), torch.zeros_like(den)))
         grad_norm = opt.step()
+        self.clock.span("optimizer_time", t_opt, self.clock.now())      # gradient reduction, clipping and the update
         self.global_step += 1
         counts = pooled.pop("x/_ling_router_counts", None)
         if counts is not None:
@@ -263,6 +315,10 @@ class DraftTrainer:
             vals[k] = flat[off:off + m].view_as(p[k].cpu())
             off += m
         out["train/grad_norm"] = float(flat[-1])
+        phases = self.clock.totals()                     # the transfer above synchronised the stream: the events are done
+        for name in ("data_time", "forward_time", "backward_time", "optimizer_time"):
+            out["perf/" + name] = float(phases.get(name, 0.0))
+        out["perf/compute_time"] = out["perf/forward_time"] + out["perf/backward_time"]
         num, den = vals["loss"]
         out["train/avg_loss"] = float(num / den) if den > 0 else 0.0
         a, c = vals["acc_pp"]

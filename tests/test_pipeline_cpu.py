@@ -54,6 +54,10 @@ def test_two_trainers_train_checkpoint_and_resume(tmp_path):
     summary = train_async_no_generation(flat, plan.draft_config, log=logs.append)
     assert summary["completed_steps"] == 3 and len(logs) == 3
     assert all(l["train/avg_loss"] == l["train/avg_loss"] for l in logs)
+    for l in logs:                                   # where the update's time went
+        assert all(l[f"perf/{k}"] >= 0 for k in ("data_time", "forward_time", "backward_time", "optimizer_time", "step_time"))
+        assert l["perf/compute_time"] == pytest.approx(l["perf/forward_time"] + l["perf/backward_time"]) and l["perf/compute_time"] > 0
+        assert l["perf/compute_time"] + l["perf/optimizer_time"] <= l["perf/step_wall_time"] * 1.05
     led = summary["ledger"]
     assert led["validated"] and led["committed_steps"] == [0, 1, 2] and len(led["committed_work_ids"]) == 12
     ck = os.path.join(flat["output_dir"], "checkpoints")
