@@ -267,7 +267,8 @@ class TrainerActor:
         masks = [unpack_loss_mask(m, n) for m, n in zip(sample.packed_loss_masks, lens)]
         loss_mask = torch.cat(masks)[None]
         batch = {"input_ids": views["input_ids"][None], "hidden_states": views["hidden_states"][None],
-                 "loss_mask": loss_mask, "_work": sample.metadata, "_key": sample.feature_key}
+                 "loss_mask": loss_mask, "_work": sample.metadata, "_aspec_work": sample.metadata,
+                 "_key": sample.feature_key}
         if "last_hidden_states" in views:
             batch["last_hidden_states"] = views["last_hidden_states"][None]
         ctx_docs = None
