@@ -371,7 +371,7 @@ def test_training_from_the_bundled_conversation_file(tmp_path, capsys):
     data = os.path.join(root, "examples", "data", "sample_conversations.jsonl")
     common = ["--config", assets.find_asset("quickstart_tiny.yaml"), f"dataset.train_data_path={data}",
               f"dataset.tokenizer_path={_tiny_tokenizer(tmp_path / 'tok')}", "dataset.chat_template=qwen", "training.max_seq_length=700",
-              "training.num_train_steps=2", "training.save_final_checkpoint=false"]
+              "training.num_train_steps=2", "training.save_final_checkpoint=false", f"cache_dir={tmp_path / 'cache'}"]
     assert train_entry.main([*common, f"output_dir={tmp_path / 'run'}"]) == 0
     evidence = json.loads((tmp_path / "run" / "evidence.json").read_text())
     adm = evidence["sections"]["dataset_admission"]
