@@ -47,8 +47,11 @@ def evaluate(consumer, lm_head, documents, features_of, *, anchors_per_doc: int 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="aspec-b200 evaluate", description=__doc__)
     ap.add_argument("--asset-dir", required=True, help="directory written by `aspec-b200 export --format aspec`")
-    ap.add_argument("--data", required=True, help="held-out conversations or pre-tokenised .jsonl")
-    ap.add_argument("--features", help="offline feature dataset directory (else the in-framework Target computes them)")
+    ap.add_argument("--data", help="held-out conversations or pre-tokenised .jsonl (default: the documents of --features, "
+                                   "or --synthetic N)")
+    ap.add_argument("--synthetic", type=int, default=0, metavar="N", help="evaluate on N synthetic documents instead of --data")
+    ap.add_argument("--features", "--feature-dir", dest="features",
+                    help="offline feature dataset directory (else the in-framework Target computes them)")
     ap.add_argument("--target-weights")
     ap.add_argument("--tokenizer")
     ap.add_argument("--chat-template", default="qwen")
@@ -71,11 +74,27 @@ def main(argv=None) -> int:
     draft, manifest = load_native_draft(a.asset_dir, device=dev, dtype=dtype)
     consumer = BlockDraftConsumer(draft, block_size=a.block_size)
     cfg = draft.config
-    docs = load_training_samples(a.data, {"tokenizer_path": a.tokenizer, "chat_template": a.chat_template,
-                                          "max_seq_length": a.max_seq_length})[: a.max_docs]
+    store = None
     if a.features:
         from aspec_b200.offline.dataset import OfflineFeatureStore
         store = OfflineFeatureStore(a.features)
+    if a.data:
+        docs = load_training_samples(a.data, {"tokenizer_path": a.tokenizer, "chat_template": a.chat_template,
+                                              "max_seq_length": a.max_seq_length})[: a.max_docs]
+    elif a.synthetic > 0:
+        from aspec_b200.data.synthetic import SyntheticSpec, make_document
+        limit = min(a.max_seq_length, int(getattr(cfg, "max_position_embeddings", a.max_seq_length) or a.max_seq_length))
+        spec = SyntheticSpec(vocab_size=int(cfg.vocab_size) - 16, min_len=min(64, limit // 2), max_len=min(1024, limit), seed=20240229)
+        docs = [make_document(spec, i) for i in range(a.synthetic)]
+    elif store is not None:
+        # the store's own documents, in the order they were written
+        docs = []
+        for row in list(store.rows("train"))[: a.max_docs]:
+            rec = store.load(row["data_id"])
+            docs.append({"data_id": row["data_id"], "input_ids": rec["input_ids"], "packed_loss_mask": rec["packed_loss_mask"]})
+    else:
+        ap.error("one of --data, --synthetic N or --features is needed")
+    if store is not None:
         import os
         head_path = os.path.join(a.features, "lm_head.pt")      # optional: written next to the features by the generator
         lm_head = torch.load(head_path, map_location=dev).to(dtype) if os.path.exists(head_path) else None

@@ -128,6 +128,10 @@ class ModelConfig:
     target_model_backend: str = "native"
     target_model_path: str = ""
     target_model_config: Optional[str] = None      # JSON of a Target architecture for random-init runs
+    # fields laid over the Draft configuration file (``model.draft_overrides.dsa_training_stage=sparse``): a training
+    # stage or a budget can change between phases without a second JSON file
+    draft_overrides: Dict[str, Any] = field(default_factory=dict)
+    mtp_source_path: Optional[str] = None          # checkpoint directory with the native ``mtp.*`` tensors (default: target_model_path)
     trust_remote_code: bool = False
 
 
@@ -315,7 +319,7 @@ class Config:
 
 # ------------------------------------------------------------------ loading -------------------
 _ENV = re.compile(r"\$\{oc\.env:([A-Za-z_][A-Za-z0-9_]*)(?:,([^}]*))?\}")
-_PATH_KEYS = {("model", "draft_model_config"), ("model", "target_model_config"), ("dataset", "train_data_path"), ("dataset", "tokenizer_path"),
+_PATH_KEYS = {("model", "draft_model_config"), ("model", "target_model_config"), ("dataset", "train_data_path"), ("dataset", "tokenizer_path"), ("model", "mtp_source_path"),
               ("dataset", "eval_data_path"), ("training", "load_path"), ("model", "initial_draft_model_path")}
 # `mooncake:` keys of reference recipes that have a transport meaning here
 _MOONCAKE_ALIASES = {"p2p_source_slots": "source_ring_slots", "p2p_destination_slots": "destination_ring_slots",

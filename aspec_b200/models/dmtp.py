@@ -66,6 +66,28 @@ class FrozenMTPFeatures(MTPPredictor):
         return self.predict_embeddings(hidden.detach(), embeds.detach(), positions, intervals).detach()
 
 
+def read_native_mtp_tensors(checkpoint_dir: str) -> Dict[str, torch.Tensor]:
+    """The ``mtp.*`` tensors of a Target checkpoint directory (safetensors, single file or sharded with
+    ``model.safetensors.index.json``; also the output of ``stitch-mtp``).  Only the shards that hold them are opened.
+    (reference: native predictor initialisation, aspec/training/mtp_trainer.py:24-61)"""
+    import json
+    import os
+    from safetensors import safe_open
+    index = os.path.join(checkpoint_dir, "model.safetensors.index.json")
+    if os.path.isfile(index):
+        weight_map = json.load(open(index))["weight_map"]
+        shards = sorted({f for k, f in weight_map.items() if k.startswith("mtp.")})
+    else:
+        shards = sorted(f for f in os.listdir(checkpoint_dir) if f.endswith(".safetensors"))
+    out: Dict[str, torch.Tensor] = {}
+    for shard in shards:
+        with safe_open(os.path.join(checkpoint_dir, shard), framework="pt") as f:
+            for key in f.keys():
+                if key.startswith("mtp."):
+                    out[key] = f.get_tensor(key)
+    return out
+
+
 def _document_length(input_ids: torch.Tensor, attention_mask: Optional[torch.Tensor]) -> int:
     """Tokens of the (single, right-padded) document in the row."""
     total = input_ids.shape[1]

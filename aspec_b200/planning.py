@@ -61,7 +61,9 @@ def _load_draft(flat: Dict[str, Any]) -> dict:
     if not path:
         raise ValueError("model.draft_model_config is required")
     from aspec_b200.assets import load_draft_config
-    return AutoDraftModelConfig.from_dict(load_draft_config(path)).to_dict()
+    raw = dict(load_draft_config(path))
+    raw.update(flat.get("draft_overrides") or {})          # model.draft_overrides: fields laid over the file
+    return AutoDraftModelConfig.from_dict(raw).to_dict()
 
 
 def resolve_batch_size(flat: Dict[str, Any], dp: int) -> dict:

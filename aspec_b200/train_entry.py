@@ -41,7 +41,9 @@ def resolve_draft_config(flat: Dict[str, Any]) -> dict:
     if not path:
         raise ValueError("model.draft_model_config is required")
     from aspec_b200.assets import load_draft_config
-    return AutoDraftModelConfig.from_dict(load_draft_config(path)).to_dict()
+    raw = dict(load_draft_config(path))
+    raw.update(flat.get("draft_overrides") or {})
+    return AutoDraftModelConfig.from_dict(raw).to_dict()
 
 
 def claim_run_directory(output_dir: str) -> None:

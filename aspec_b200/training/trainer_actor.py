@@ -56,6 +56,7 @@ class TrainerActor:
             pass
         self.draft_config = AutoDraftModelConfig.from_dict(draft_config)
         self.model = build_training_model(self.draft_config, self.args, self.device, self.dtype)
+        self._load_native_mtp()                  # before the optimizer takes its fp32 masters from the weights
         if self.args.get("initial_draft_model_path") and not self.args.get("load_path"):
             self._load_initial_weights(str(self.args["initial_draft_model_path"]))
         cfg = self.draft_config
@@ -142,6 +143,33 @@ class TrainerActor:
         self.fault: Optional[dict] = self.args.get("fault_injection")      # host-side: {"kind": "raise"|"sleep", "step": k}
         self._pending_releases: List[tuple] = []
         self._debug_instruments()
+
+    @torch.no_grad()
+    def _load_native_mtp(self) -> None:
+        """Native MTP predictors start from (native-MTP training) or stay frozen at (MTP-conditioned blocks) the ``mtp.*``
+        tensors of the Target checkpoint: ``model.mtp_source_path``, else ``model.target_model_path`` when that is a
+        checkpoint directory that holds them.  A resume or an initial Draft asset loaded afterwards takes precedence for
+        trainable tensors."""
+        draft = self.model.draft_model
+        if getattr(draft, "mtp_source", None) is not None:
+            load = draft.initialize_mtp_conditioning
+        elif type(draft).__name__ == "NativeMTPDraftModel":
+            load = draft.initialize_native_weights
+        else:
+            return
+        explicit = self.args.get("mtp_source_path")
+        source = explicit or self.args.get("target_model_path")
+        if not source or not os.path.isdir(str(source)):
+            if explicit:
+                raise FileNotFoundError(f"model.mtp_source_path {explicit} is not a checkpoint directory")
+            return
+        from aspec_b200.models.dmtp import read_native_mtp_tensors
+        tensors = read_native_mtp_tensors(str(source))
+        if not tensors:
+            if explicit:
+                raise ValueError(f"{explicit} holds no mtp.* tensors")
+            return
+        load({k: v.to(self.device) for k, v in tensors.items()})
 
     @torch.no_grad()
     def _load_initial_weights(self, asset_dir: str) -> None:

@@ -166,3 +166,28 @@ def test_dspark_with_mixture_of_experts_feed_forward_trains(ffn):
         update_ling_bias(layers, counts.clone(), update_rate=1e-3)
         assert any(not torch.equal(b, l.gate.expert_bias) for b, l in zip(before, layers))
         assert all(l.gate.expert_bias.dtype == torch.float32 for l in layers)
+
+
+def test_native_mtp_tensors_are_read_from_a_sharded_checkpoint_directory(tmp_path):
+    """Only ``mtp.*`` tensors, only from the shards that hold them; a frozen MTP source loads them and then validates
+    against them."""
+    import json
+    from safetensors.torch import save_file
+    from aspec_b200.models.dmtp import FrozenMTPFeatures, read_native_mtp_tensors
+    from aspec_b200.models.draft.mtp import native_key
+    source = FrozenMTPFeatures(NATIVE)
+    torch.manual_seed(5)
+    native = {native_key(n): torch.randn_like(t) for n, t in source.state_dict().items()}
+    assert all(k.startswith("mtp.") for k in native)
+    save_file({"model.layers.0.weight": torch.zeros(2)}, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file(native, str(tmp_path / "model-00002-of-00002.safetensors"))
+    index = {"weight_map": {"model.layers.0.weight": "model-00001-of-00002.safetensors",
+                            **{k: "model-00002-of-00002.safetensors" for k in native}}}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    got = read_native_mtp_tensors(str(tmp_path))
+    assert set(got) == set(native) and all(torch.equal(got[k], native[k]) for k in native)
+    source.initialize_native_weights(got)
+    source.validate_native_weights(got)
+    assert not any(p.requires_grad for p in source.parameters())
+    (tmp_path / "model.safetensors.index.json").unlink()            # unsharded layout: every safetensors file is looked at
+    assert set(read_native_mtp_tensors(str(tmp_path))) == set(native)

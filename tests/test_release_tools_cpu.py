@@ -46,3 +46,63 @@ def test_a_wheel_of_this_tree_passes_the_audit_and_runs_when_installed(tmp_path)
     installed = check_wheel_install.check_install(wheel)
     assert installed["ok"], installed
     assert installed["planned"] == installed["recipes"] == report["recipes"] and installed["package_dir"].startswith("site")
+
+
+@pytest.mark.timeout(600)
+def test_every_command_line_shown_in_the_documents_and_examples_parses():
+    """Each ``aspec_b200.cli`` invocation in README, MIGRATION and the examples names a sub-command that exists and only
+    options that sub-command accepts (its ``--help`` lists them)."""
+    import re
+    files = [os.path.join(ROOT, "README.md"), os.path.join(ROOT, "MIGRATION.md")]
+    files += glob.glob(os.path.join(ROOT, "examples", "*", "run.sh")) + glob.glob(os.path.join(ROOT, "examples", "*", "README.md"))
+    helps = {}
+
+    def options_of(*sub):
+        if sub not in helps:
+            # without a sub-command the command line is the train entry's
+            module = ["aspec_b200.cli", *sub] if sub else ["aspec_b200.train_entry"]
+            out = subprocess.run([sys.executable, "-m", *module, "--help"], cwd=ROOT, capture_output=True, text=True,
+                                 env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+            helps[sub] = (out.returncode, set(re.findall(r"(?<![\w-])--[a-z][a-z0-9-]*", out.stdout)))
+        return helps[sub]
+
+    checked, problems, overrides = 0, [], set()
+    for path in files:
+        text = open(path).read().replace("\\\n", " ")
+        for line in text.splitlines():
+            m = re.search(r"(?:aspec_b200\.cli|\$CLI|aspec-b200)\s+(.*)", line)
+            if not m or line.lstrip().startswith("#") and "cli" not in line:
+                continue
+            words = m.group(1).split("#")[0].split()
+            if not words or words[0].startswith(("`", "(", "|")):
+                continue
+            sub = [] if words[0].startswith("--") else [words[0]]
+            if sub and not re.fullmatch(r"[a-z][a-z0-9-]*", sub[0]):
+                continue                                      # prose, not a command
+            flags = {w.split("=")[0] for w in words if re.fullmatch(r"--[a-z][a-z0-9-]*(=.*)?", w)}
+            if not sub:                                        # a training command line: its KEY=VALUE overrides must be configuration keys
+                for w in words:
+                    key = re.fullmatch(r"'?([a-z_]+(?:\.[a-z_0-9]+)+)=.*", w)
+                    if key:
+                        overrides.add((os.path.relpath(path, ROOT), key.group(1)))
+            rc, allowed = options_of(*sub)
+            if rc != 0:
+                problems.append(f"{os.path.relpath(path, ROOT)}: unknown sub-command in `{line.strip()[:100]}`")
+                continue
+            if sub and len(words) > 1 and re.fullmatch(r"[a-z][a-z0-9-]*", words[1]):
+                rc2, nested = options_of(sub[0], words[1])     # nested sub-commands (recipes plan, quickstart tiny)
+                if rc2 == 0:
+                    allowed = allowed | nested
+            checked += 1
+            for f in sorted(flags - allowed):
+                problems.append(f"{os.path.relpath(path, ROOT)}: `{' '.join(sub) or 'train'}` has no option {f}: `{line.strip()[:100]}`")
+    from aspec_b200 import assets
+    from aspec_b200.config.train_config import load_config
+    recipe = assets.find_asset("quickstart_tiny.yaml")
+    for where, key in sorted(overrides):
+        try:
+            load_config(recipe, [f"{key}=1"])
+        except Exception as exc:                               # noqa: BLE001 - only the key's existence is checked here
+            if "Unknown config key" in str(exc):
+                problems.append(f"{where}: `{key}` is not a configuration key")
+    assert checked >= 20 and len(overrides) >= 15 and not problems, "\n".join(problems)
